@@ -1,0 +1,141 @@
+"""The step function: run a batch of (request, its next tokens) from the cache
+and return the logits at the wanted places.
+
+It runs only the tokens it is given, as one ragged batch: portions of prompts
+beside single decoded tokens, cut anywhere.  It never allocates pages (the
+caller did, with ``CacheManager.extend``) and mutates nothing but the cache
+contents of the new tokens and each request's cached length.  LitInfer's
+counterpart, ``engine_step`` (src/llaisys/models/qwen2.cpp:922-1080), also
+schedules, samples and frees; here those live in the scheduler above.
+
+Steps that consist of single tokens only can be replayed from a captured CUDA
+graph per batch-size bucket: the launch sequence of a decode step is fixed, so
+one graph launch replaces a few hundred kernel launches.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..models.decoder import DecoderModel
+from .batch import StepContext, StepItem, context_from, pack_step
+
+
+class _DecodeGraph:
+    def __init__(self, graph, meta_buf, logits, layout):
+        self.graph = graph
+        self.meta_buf = meta_buf
+        self.logits = logits
+        self.layout = layout
+
+
+class ModelRunner:
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+    def __init__(self, model: DecoderModel, manager: CacheManager, use_graphs: bool = False,
+                 max_context: Optional[int] = None) -> None:
+        self.model = model
+        self.manager = manager
+        self.device = model.device
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        self.max_context = int(max_context or model.spec.max_position_embeddings)
+        self._graphs: Dict[int, _DecodeGraph] = {}
+        self._pinned: Optional[torch.Tensor] = None
+        self._copy_done = None
+        self.steps_run = 0
+        self.graph_replays = 0
+
+    # ------------------------------------------------------------------
+    def _upload(self, buf: np.ndarray, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One host-to-device copy of the packed metadata, through pinned memory."""
+        n = buf.shape[0]
+        if self.device.type != "cuda":
+            t = torch.from_numpy(buf.copy())
+            if into is not None:
+                into[:n].copy_(t)
+                return into
+            return t
+        if self._pinned is None or self._pinned.numel() < n:
+            if self._copy_done is not None:
+                self._copy_done.synchronize()
+            self._pinned = torch.empty(max(2 * n, 1 << 16), dtype=torch.int32).pin_memory()
+            self._pinned_np = self._pinned.numpy()
+            self._copy_done = torch.cuda.Event()
+        else:
+            self._copy_done.synchronize()         # the last copy out of the pinned buffer has finished
+        self._pinned_np[:n] = buf
+        if into is None:
+            into = torch.empty(n, dtype=torch.int32, device=self.device)
+        into[:n].copy_(self._pinned[:n], non_blocking=True)
+        self._copy_done.record(torch.cuda.current_stream(self.device))
+        return into
+
+    # ------------------------------------------------------------------
+    def step(self, items: Sequence[StepItem]) -> torch.Tensor:
+        """Float32 logits ``[wanted, vocab]`` in the order of the items and of their ``want``."""
+        items = list(items)
+        decode_only = all(len(it.tokens) == 1 for it in items)
+        if self.use_graphs and decode_only and len(items) <= self.GRAPH_BUCKETS[-1]:
+            logits = self._step_graph(items)
+        else:
+            buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size)
+            ctx = context_from(self._upload(buf), layout, self.manager.page_size)
+            logits = self.model.forward(ctx, self.manager.entries)
+        for it in items:
+            self.manager.commit(it.cache, it.cache.length + len(it.tokens))
+        self.steps_run += 1
+        return logits
+
+    # ------------------------------------------------------------------
+    def _bucket(self, n: int) -> int:
+        for b in self.GRAPH_BUCKETS:
+            if n <= b:
+                return b
+        raise ValueError(n)
+
+    def _step_graph(self, items: List[StepItem]) -> torch.Tensor:
+        """Decode-only step through a captured graph.  Every item wants its one token's
+        logits in the captured layout; rows of items that want nothing are dropped after."""
+        B = self._bucket(len(items))
+        max_blocks = -(-self.max_context // self.manager.page_size)
+        wanted = [bool(len(it.want)) for it in items]
+        full = [StepItem(it.cache, it.tokens, (0,)) for it in items]
+        buf, layout = pack_step(full, self.manager, self.model.spec.vocab_size, pad_seqs=B, max_blocks=max_blocks)
+        g = self._graphs.get(B)
+        if g is None:
+            g = self._capture(B, max_blocks, buf, layout)
+        if layout["fields"] != g.layout["fields"]:
+            raise RuntimeError("decode graph: metadata layout changed between capture and replay")
+        self._upload(buf, g.meta_buf)
+        g.graph.replay()
+        self.graph_replays += 1
+        rows = [i for i, w in enumerate(wanted) if w]
+        if len(rows) == len(items) == B:
+            return g.logits
+        return g.logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else g.logits[:0]
+
+    def _capture(self, B: int, max_blocks: int, buf: np.ndarray, layout) -> _DecodeGraph:
+        meta = torch.zeros(buf.shape[0], dtype=torch.int32, device=self.device)
+        self._upload(buf, meta)
+        lay = dict(layout)
+        # a captured attention launch must cover any context up to the maximum
+        lay["max_ctx_len"] = self.max_context
+        lay["max_q_len"] = 1
+        ctx = context_from(meta, lay, self.manager.page_size)
+        stream = torch.cuda.Stream(self.device)
+        stream.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(stream):
+            for _ in range(2):                    # warm-up outside capture (first-call set-up, allocator)
+                self.model.forward(ctx, self.manager.entries)
+        torch.cuda.current_stream(self.device).wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx, self.manager.entries)
+        g = _DecodeGraph(graph, meta, logits, lay)
+        self._graphs[B] = g
+        return g

@@ -1,0 +1,241 @@
+"""Python face of the CUDA kernels in ``csrc/``: one function per kernel.
+
+Each function checks its arguments (device, dtype, shape, contiguity) and
+launches on the current CUDA stream of torch through the library's C
+interface.  There is no other implementation behind these names: tensors that
+are not on a CUDA device, a missing compiler or a failed build raise an error.
+
+Conventions: the residual stream ``x32`` is float32; activations, matrices
+and the cache are in the run dtype (bfloat16 or float32, never mixed in one
+call); norm weights, biases and logits are float32; index tensors are int32.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+from .csrc.build import ensure_built
+
+_lib = None
+_lib_lock = threading.Lock()
+
+_F32, _BF16 = 0, 1
+launches = 0            # kernels launched through this module since import (bench reads it)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def library() -> ctypes.CDLL:
+    """The kernel library, built on first use."""
+    global _lib
+    if _lib is None:
+        with _lib_lock:
+            if _lib is None:
+                path = ensure_built()
+                lib = ctypes.CDLL(str(path))
+                lib.li_last_error.restype = ctypes.c_char_p
+                _lib = lib
+    return _lib
+
+
+def library_file() -> str:
+    library()
+    return str(ensure_built(verbose=False))
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"run dtype must be float32 or bfloat16, got {t.dtype}")
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise KernelError(f"{name}: expected a tensor, got {type(t).__name__}")
+    if t.device.type != "cuda":
+        raise KernelError(f"{name}: the kernels run on CUDA devices only, tensor is on '{t.device}'")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _check(rc: int, what: str) -> None:
+    global launches
+    launches += 1
+    if rc != 0:
+        msg = library().li_last_error()
+        raise KernelError(f"{what}: {msg.decode() if msg else 'error ' + str(rc)}")
+
+
+_i = ctypes.c_int
+_f = ctypes.c_float
+_l = ctypes.c_longlong
+
+
+# --------------------------------------------------------------------------
+def embedding(table: torch.Tensor, ids: torch.Tensor, out32: torch.Tensor) -> None:
+    """out32[t, :] = float(table[ids[t], :])."""
+    V, H = table.shape
+    T = ids.shape[0]
+    _need(table, "embedding table")
+    _need(ids, "token ids", torch.int32)
+    _need(out32, "embedding output", torch.float32, (T, H))
+    _check(library().li_embedding(_p(table), _i(_dt(table)), _p(ids), _p(out32), _i(T), _i(H), _i(V), _stream(out32)), "embedding")
+
+
+def rmsnorm(x32: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    T, H = x32.shape
+    _need(x32, "rmsnorm input", torch.float32)
+    _need(weight, "rmsnorm weight", torch.float32, (H,))
+    _need(out, "rmsnorm output", None, (T, H))
+    _check(library().li_rmsnorm(_p(x32), _p(weight), _f(eps), _p(out), _i(_dt(out)), _i(T), _i(H), _stream(out)), "rmsnorm")
+
+
+def add_rmsnorm(x32: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """x32 += delta (float32 sum, kept in x32); out = rmsnorm(x32)."""
+    T, H = x32.shape
+    _need(x32, "add_rmsnorm residual", torch.float32)
+    _need(delta, "add_rmsnorm delta", None, (T, H))
+    _need(weight, "rmsnorm weight", torch.float32, (H,))
+    _need(out, "add_rmsnorm output", delta.dtype, (T, H))
+    _check(library().li_add_rmsnorm(_p(x32), _p(delta), _i(_dt(delta)), _p(weight), _f(eps), _p(out), _i(T), _i(H), _stream(out)),
+           "add_rmsnorm")
+
+
+def gather_rmsnorm(x32: torch.Tensor, rows: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out[r] = rmsnorm(x32[rows[r]])."""
+    T, H = x32.shape
+    R = rows.shape[0]
+    _need(x32, "gather_rmsnorm input", torch.float32)
+    _need(rows, "gather_rmsnorm rows", torch.int32)
+    _need(weight, "rmsnorm weight", torch.float32, (H,))
+    _need(out, "gather_rmsnorm output", None, (R, H))
+    _check(library().li_gather_rmsnorm(_p(x32), _p(rows), _p(weight), _f(eps), _p(out), _i(_dt(out)), _i(R), _i(T), _i(H), _stream(out)),
+           "gather_rmsnorm")
+
+
+def residual_add(x32: torch.Tensor, delta: torch.Tensor) -> None:
+    _need(x32, "residual", torch.float32)
+    _need(delta, "delta", None, x32.shape)
+    _check(library().li_residual_add(_p(x32), _p(delta), _i(_dt(delta)), _l(x32.numel()), _stream(x32)), "residual_add")
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[M, N] = a[M, K] weight[N, K]^T (+ bias[N]); float32 accumulation;
+    out is in the run dtype or float32."""
+    M, Kd = a.shape
+    N = weight.shape[0]
+    _need(a, "linear input")
+    _need(weight, "linear weight", a.dtype, (N, Kd))
+    if bias is not None:
+        _need(bias, "linear bias", torch.float32, (N,))
+    _need(out, "linear output", None, (M, N))
+    if out.dtype not in (a.dtype, torch.float32):
+        raise KernelError(f"linear output must be {a.dtype} or float32, got {out.dtype}")
+    if M == 0:
+        return
+    _check(library().li_linear(_p(a), _p(weight), _p(bias), _p(out), _i(_dt(a)), _i(_dt(out)), _i(M), _i(N), _i(Kd), _stream(out)),
+           "linear")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torch.Tensor, rotary_dim: int,
+                  slot_mapping: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                  num_heads: int, num_kv_heads: int, head_dim: int, write: bool = True) -> None:
+    """Rotate q (in place in ``qkv``) and k; store rotated k and plain v at each
+    token's slot of the caches ``[pages, kv_heads, page_size, head_dim]``.
+    With ``write`` false only q is rotated."""
+    T = qkv.shape[0]
+    _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
+    _need(positions, "positions", torch.int32, (T,))
+    _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
+    _need(slot_mapping, "slot mapping", torch.int32, (T,))
+    _need(k_cache, "key cache", qkv.dtype)
+    _need(v_cache, "value cache", qkv.dtype, k_cache.shape)
+    pages, nkv, page_size, dh = k_cache.shape
+    if nkv != num_kv_heads or dh != head_dim:
+        raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
+    _check(library().li_rope_kv_write(
+        _p(qkv), _i(_dt(qkv)), _p(positions), _p(denominators), _i(rotary_dim), _p(slot_mapping), _p(k_cache), _p(v_cache),
+        _i(T), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _i(1 if write else 0), _stream(qkv)),
+        "rope_kv_write")
+
+
+def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                    block_table: torch.Tensor, q_start: torch.Tensor, ctx_lens: torch.Tensor,
+                    seq_of_token: torch.Tensor, positions: torch.Tensor,
+                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
+                    max_q_len: int, max_ctx_len: int) -> None:
+    """Causal grouped-query attention of the step's tokens over the paged cache.
+
+    Queries are the first ``num_heads * head_dim`` columns of ``qkv`` (already
+    rotated).  The token at position p of sequence s sees the cached keys
+    ``max(0, p - window + 1) .. p`` of s, found through ``block_table[s]``."""
+    T = qkv.shape[0]
+    S = ctx_lens.shape[0]
+    _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
+    _need(out, "attention output", qkv.dtype, (T, num_heads * head_dim))
+    _need(k_cache, "key cache", qkv.dtype)
+    _need(v_cache, "value cache", qkv.dtype, k_cache.shape)
+    _need(block_table, "block table", torch.int32)
+    _need(q_start, "q_start", torch.int32, (S + 1,))
+    _need(ctx_lens, "ctx_lens", torch.int32, (S,))
+    _need(seq_of_token, "seq_of_token", torch.int32, (T,))
+    _need(positions, "positions", torch.int32, (T,))
+    pages, nkv, page_size, dh = k_cache.shape
+    if block_table.dim() != 2 or block_table.shape[0] != S:
+        raise KernelError(f"block table must be [{S}, max_blocks], got {tuple(block_table.shape)}")
+    if nkv != num_kv_heads or dh != head_dim:
+        raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
+    if block_table.shape[1] * page_size < max_ctx_len:
+        raise KernelError(f"block table of {block_table.shape[1]} pages cannot cover a context of {max_ctx_len}")
+    _check(library().li_paged_attention(
+        _p(qkv), _p(out), _p(k_cache), _p(v_cache), _i(_dt(qkv)), _p(block_table), _i(block_table.shape[1]),
+        _p(q_start), _p(ctx_lens), _p(seq_of_token), _p(positions), _i(T), _i(S),
+        _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _f(scale),
+        _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _stream(out)),
+        "paged_attention")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = up * gate / (1 + exp(-gate)) with gate_up = [gate | up] along the last axis."""
+    T, I2 = gate_up.shape
+    _need(gate_up, "gate_up")
+    _need(out, "swiglu output", gate_up.dtype, (T, I2 // 2))
+    _check(library().li_swiglu(_p(gate_up), _p(out), _i(_dt(out)), _i(T), _i(I2 // 2), _stream(out)), "swiglu")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    """Index of the first maximum of each row."""
+    R, V = logits.shape
+    _need(logits, "logits", torch.float32)
+    _need(out, "argmax output", torch.int32, (R,))
+    _check(library().li_argmax(_p(logits), _p(out), _i(R), _i(V), _stream(out)), "argmax")
+
+
+def sample(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor) -> None:
+    """One token per row.  ``params`` int32 [R, 6]: temperature (float bits; <= 0
+    is argmax), top_k, top_p (float bits), seed low, seed high, output index."""
+    R, V = logits.shape
+    _need(logits, "logits", torch.float32)
+    _need(params, "sampling parameters", torch.int32, (R, 6))
+    _need(out, "sample output", torch.int32, (R,))
+    _check(library().li_sample(_p(logits), _p(params), _p(out), _i(R), _i(V), _stream(out)), "sample")

@@ -1,0 +1,71 @@
+"""Grouped-query attention over a paged cache of keys and values.
+
+Formulas (src/llaisys/models/qwen2.cpp:613-699, src/ops/paged_attention/op.cpp:194-234):
+q, k, v = h Wq^T + bq, h Wk^T + bk, h Wv^T + bv; position encoding on q and k;
+k (after encoding) and v go into the cache at the token's position; query
+head ``i`` reads key head ``i // (heads / kv_heads)``; the query at position p
+sees keys 0..p, or with a window only those with p - t < window;
+scores * scale, softmax in float32, weighted sum of v; output map without
+bias unless the spec says so.  Sizes, scale, window and bias flags are
+parameters of the spec; the position encoding is a part of its own.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import kernels as K
+from ..weights.loader import ParamSpec
+from .base import MIXERS, POSITIONS, Mixer, PagedKV
+from .linear import FusedLinear
+
+
+@MIXERS.register("attention")
+class PagedAttention(Mixer):
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.hidden = int(spec["hidden_size"])
+        self.num_heads = int(spec["num_heads"])
+        self.num_kv_heads = int(spec["num_kv_heads"])
+        self.head_dim = int(spec["head_dim"])
+        self.scale = float(spec["scale"])
+        self.window = spec.get("window")
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} key/value heads")
+        names = spec.get("names", {})
+        self.q_dim = self.num_heads * self.head_dim
+        self.kv_dim = self.num_kv_heads * self.head_dim
+        self.qkv = FusedLinear(
+            prefix, [names.get("q", "q_proj"), names.get("k", "k_proj"), names.get("v", "v_proj")],
+            self.hidden, [self.q_dim, self.kv_dim, self.kv_dim], bool(spec.get("qkv_bias", False)), dtype)
+        self.out = FusedLinear(prefix, [names.get("o", "o_proj")], self.q_dim, [self.hidden], bool(spec.get("out_bias", False)), dtype)
+        self.position = POSITIONS.build(spec["position"], prefix, dtype, device, head_dim=self.head_dim)
+
+    def params(self) -> List[ParamSpec]:
+        return self.qkv.params() + self.out.params()
+
+    def parts(self):
+        return [self.position]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.qkv.bind(tensors)
+        self.out.bind(tensors)
+
+    def cache_requirement(self):
+        return PagedKV(self.num_kv_heads, self.head_dim, self.window)
+
+    def forward(self, h, ctx, cache):
+        qkv = self.qkv(h)                                   # [T, (heads + 2 kv_heads) * head_dim]
+        view = ctx.group(cache.group)
+        K.rope_kv_write(
+            qkv, ctx.positions, self.position.denominators, self.position.rotary_dim,
+            view.slot_mapping, cache.k, cache.v,
+            self.num_heads, self.num_kv_heads, self.head_dim, cache.writes)
+        o = torch.empty((h.shape[0], self.q_dim), dtype=self.dtype, device=h.device)
+        K.paged_attention(
+            qkv, o, cache.k, cache.v, view.block_table, ctx.q_start, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,
+            self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
+            ctx.max_q_len, ctx.max_ctx_len)
+        return self.out(o)

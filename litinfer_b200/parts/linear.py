@@ -1,0 +1,52 @@
+"""Linear map out = x W^T (+ b) with W stored [out, in], as LitInfer's linear
+op reads it (src/ops/linear/cpu/linear_cpu.cpp:45-60): accumulation in
+float32, bias added in float32, one rounding.  Several maps of the same input
+can be declared under their own tensor names and fused into one matrix when
+the weights are bound (q|k|v, gate|up), so that one product serves them."""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import kernels as K
+from ..weights.loader import ParamSpec
+
+
+class FusedLinear:
+    """``names``: tensor-name stems (without .weight / .bias); ``outs``: their output sizes."""
+
+    def __init__(self, prefix: str, names: Sequence[str], in_features: int, outs: Sequence[int], bias: bool,
+                 dtype: torch.dtype, std: float = 0.02) -> None:
+        self.prefix = prefix
+        self.names = list(names)
+        self.in_features = int(in_features)
+        self.outs = [int(o) for o in outs]
+        self.out_features = sum(self.outs)
+        self.has_bias = bool(bias)
+        self.dtype = dtype
+        self.std = std
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def params(self) -> List[ParamSpec]:
+        out = []
+        for n, o in zip(self.names, self.outs):
+            out.append(ParamSpec(f"{self.prefix}{n}.weight", (o, self.in_features), role="matrix", std=self.std))
+            if self.has_bias:
+                out.append(ParamSpec(f"{self.prefix}{n}.bias", (o,), role="vector", std=self.std))
+        return out
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        ws = [tensors.pop(f"{self.prefix}{n}.weight") for n in self.names]
+        self.weight = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
+        del ws
+        if self.has_bias:
+            bs = [tensors.pop(f"{self.prefix}{n}.bias") for n in self.names]
+            self.bias = bs[0] if len(bs) == 1 else torch.cat(bs, dim=0).contiguous()
+
+    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or self.dtype, device=x.device)
+        K.linear(x, self.weight, self.bias, out)
+        return out

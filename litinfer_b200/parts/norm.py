@@ -1,0 +1,43 @@
+"""RMSNorm: y_j = w_j * x_j / sqrt(mean(x^2) + eps), per token
+(src/ops/rms_norm/op.cpp:13-24).  Sum, reciprocal root and products in
+float32 on the float32 residual stream; one rounding of y to the run dtype."""
+
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+
+from .. import kernels as K
+from ..weights.loader import ParamSpec
+from .base import NORMS, Norm
+
+
+@NORMS.register("rmsnorm")
+class RMSNorm(Norm):
+    def __init__(self, spec, prefix, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.weight = None
+
+    def params(self) -> List[ParamSpec]:
+        return [ParamSpec(self.prefix + "weight", (self.size,), role="vector", init="ones_normal")]
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.weight = tensors.pop(self.prefix + "weight")
+
+    def forward(self, x32):
+        out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+        K.rmsnorm(x32, self.weight, self.eps, out)
+        return out
+
+    def add_forward(self, x32, delta):
+        out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+        K.add_rmsnorm(x32, delta, self.weight, self.eps, out)
+        return out
+
+    def gather_forward(self, x32, rows):
+        out = torch.empty((rows.shape[0], x32.shape[1]), dtype=self.dtype, device=x32.device)
+        K.gather_rmsnorm(x32, rows, self.weight, self.eps, out)
+        return out

@@ -1,0 +1,76 @@
+"""Choosing the next token: greedy, temperature, top-k, top-p.
+
+Which tokens stay candidates follows LitInfer's sampler
+(src/llaisys/models/qwen2.cpp:890-920): logits / temperature; the ``top_k``
+largest if 0 < k < vocab; softmax over those; the shortest prefix (in
+descending order) whose cumulative probability reaches ``top_p`` if
+0 < p < 1; softmax again over what is left; draw.  Greedy when ``top_k == 1``
+(the default of ``generate``, python/llaisys/models/qwen2.py:305-311) or when
+``temperature <= 0`` (qwen2.cpp:893-895): the first maximum wins
+(src/ops/argmax/op.cpp:28-33).
+
+The draw differs from LitInfer's on purpose.  LitInfer consumes one shared
+``mt19937`` in batch order, so a request's tokens depend on what else is
+running.  Here the draw is Gumbel-max, ``argmax_i(z_i + g_i)`` over the
+candidates with ``g_i = -log(-log(u_i))``, which samples exactly from their
+softmax, and ``u_i`` comes from a counter-based generator keyed on (the
+request's seed, the index of the output token, the token id i): the result
+depends on nothing but the request itself.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Sequence
+
+import torch
+
+from .. import kernels as K
+
+
+@dataclass(frozen=True)
+class SamplingParams:
+    temperature: float = 1.0
+    top_k: int = 1
+    top_p: float = 1.0
+    seed: int = 0
+
+    @property
+    def greedy(self) -> bool:
+        return self.top_k == 1 or self.temperature <= 0.0
+
+
+class Sampler:
+    """Device-side sampling of one token per logits row."""
+
+    def __init__(self, device) -> None:
+        self.device = torch.device(device)
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], output_index: Sequence[int]) -> torch.Tensor:
+        """``logits`` float32 [R, V]; returns int32 [R] on the device."""
+        R = logits.shape[0]
+        if len(params) != R or len(output_index) != R:
+            raise ValueError("one SamplingParams and one output index per logits row")
+        out = torch.empty(R, dtype=torch.int32, device=logits.device)
+        if R == 0:
+            return out
+        if all(p.greedy for p in params):
+            K.argmax(logits, out)
+            return out
+        # rows that are greedy get temperature 0, which the kernel reads as argmax
+        host = torch.empty((R, 6), dtype=torch.int32)
+        f = host.view(torch.float32)
+        for r, (p, idx) in enumerate(zip(params, output_index)):
+            f[r, 0] = 0.0 if p.greedy else float(p.temperature)
+            host[r, 1] = int(p.top_k)
+            f[r, 2] = float(p.top_p)
+            seed = int(p.seed) & 0xFFFF_FFFF_FFFF_FFFF
+            host[r, 3] = _as_i32(seed & 0xFFFF_FFFF)
+            host[r, 4] = _as_i32(seed >> 32)
+            host[r, 5] = int(idx)
+        K.sample(logits, host.to(logits.device), out)
+        return out
+
+
+def _as_i32(u: int) -> int:
+    return u - (1 << 32) if u >= (1 << 31) else u

@@ -1,0 +1,79 @@
+"""Shared fixtures: tiny configurations, model folders in temporary places,
+and the switch that lets host-side logic run on the CPU against the plain
+kernel references."""
+
+from __future__ import annotations
+
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+if str(ROOT / "tests") not in sys.path:
+    sys.path.insert(0, str(ROOT / "tests"))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on a B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+# Two tiny Qwen2 configurations that differ in every size and option: layers,
+# width, heads and groups (2 per key head / 3 on a single key head), head size,
+# feed-forward width, vocabulary (no power of two in B), rope base, norm eps,
+# tied or own lm_head, position limit, and the window (none / 24 keys on the
+# last two layers).
+TINY_A = dict(
+    architectures=["Qwen2ForCausalLM"], torch_dtype="float32", num_hidden_layers=2, hidden_size=64,
+    num_attention_heads=4, num_key_value_heads=2, head_dim=16, intermediate_size=128, vocab_size=256,
+    rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=128,
+    eos_token_id=None, use_sliding_window=False)
+TINY_B = dict(
+    architectures=["Qwen2ForCausalLM"], torch_dtype="float32", num_hidden_layers=3, hidden_size=96,
+    num_attention_heads=3, num_key_value_heads=1, head_dim=32, intermediate_size=272, vocab_size=389,
+    rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256,
+    eos_token_id=None, use_sliding_window=True, sliding_window=24, max_window_layers=1)
+# A third one for long sequences: more positions, a head size of 48 (a multiple of 16 that is no power of two).
+TINY_C = dict(
+    architectures=["Qwen2ForCausalLM"], torch_dtype="float32", num_hidden_layers=2, hidden_size=80,
+    num_attention_heads=6, num_key_value_heads=2, head_dim=48, intermediate_size=176, vocab_size=300,
+    rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1024,
+    eos_token_id=None, use_sliding_window=False)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+@pytest.fixture(scope="session")
+def model_dirs(tmp_path_factory):
+    """Model folders of the tiny configurations with random float32 weights."""
+    from litinfer_b200.weights import write_model_folder
+
+    out = {}
+    for name, cfg in TINY.items():
+        d = tmp_path_factory.mktemp(f"tiny{name}")
+        write_model_folder(d, dict(cfg), seed=1234 + ord(name), store_dtype="float32")
+        out[name] = d
+    return out
+
+
+@pytest.fixture
+def cpu_kernels(monkeypatch):
+    """Replace every kernel by its plain reference, so that host-side logic runs on the CPU."""
+    import kernel_refs
+    from litinfer_b200 import kernels
+
+    for name in kernel_refs.ALL:
+        monkeypatch.setattr(kernels, name, getattr(kernel_refs, name))
+    return kernels

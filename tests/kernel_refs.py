@@ -1,0 +1,190 @@
+"""Plain references of the package's kernels, one per function of
+``litinfer_b200.kernels``, with the same signatures, in float32 torch on
+whatever device the tensors are on.
+
+Two uses: the GPU tests compare each kernel alone with its reference here;
+the CPU tests patch these in place of the kernels, so that the cache manager,
+the step function and the scheduler can be checked against the plain model
+without a GPU.  They are test code: nothing in the package imports them.
+"""
+
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+
+def _store(out, value):
+    out.copy_(value.to(out.dtype))
+
+
+def embedding(table, ids, out32):
+    _store(out32, table[ids.long()].float())
+
+
+def _rms(x, weight, eps):
+    x = x.float()
+    r = 1.0 / torch.sqrt((x * x).sum(-1, keepdim=True) / x.shape[-1] + eps)
+    return (weight * x) * r
+
+
+def rmsnorm(x32, weight, eps, out):
+    _store(out, _rms(x32, weight, eps))
+
+
+def add_rmsnorm(x32, delta, weight, eps, out):
+    x32.add_(delta.float())
+    _store(out, _rms(x32, weight, eps))
+
+
+def gather_rmsnorm(x32, rows, weight, eps, out):
+    _store(out, _rms(x32[rows.long()], weight, eps))
+
+
+def residual_add(x32, delta):
+    x32.add_(delta.float())
+
+
+def linear(a, weight, bias, out):
+    y = a.float() @ weight.float().t()
+    if bias is not None:
+        y = y + bias
+    _store(out, y)
+
+
+def rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cache, v_cache,
+                  num_heads, num_kv_heads, head_dim, write=True):
+    T = qkv.shape[0]
+    q_dim, kv_dim = num_heads * head_dim, num_kv_heads * head_dim
+    phi = positions.float()[:, None] / denominators[None, :]
+    cos, sin = torch.cos(phi)[:, None, :], torch.sin(phi)[:, None, :]
+    half = rotary_dim // 2
+
+    def rot(x):
+        x = x.float().clone()
+        a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
+        x[..., :half] = a * cos - b * sin
+        x[..., half:rotary_dim] = b * cos + a * sin
+        return x
+
+    q = rot(qkv[:, :q_dim].reshape(T, num_heads, head_dim))
+    qkv[:, :q_dim] = q.reshape(T, q_dim).to(qkv.dtype)
+    if not write:
+        return
+    k = rot(qkv[:, q_dim:q_dim + kv_dim].reshape(T, num_kv_heads, head_dim)).to(qkv.dtype)
+    v = qkv[:, q_dim + kv_dim:].reshape(T, num_kv_heads, head_dim)
+    page_size = k_cache.shape[2]
+    page = (slot_mapping // page_size).long()
+    off = (slot_mapping % page_size).long()
+    k_cache[page, :, off] = k
+    v_cache[page, :, off] = v
+
+
+def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
+                    num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len):
+    T = qkv.shape[0]
+    page_size = k_cache.shape[2]
+    group = num_heads // num_kv_heads
+    q = qkv[:, :num_heads * head_dim].reshape(T, num_heads, head_dim).float()
+    res = torch.zeros(T, num_heads, head_dim, dtype=torch.float32, device=qkv.device)
+    seqs = seq_of_token.tolist()
+    poss = positions.tolist()
+    for t in range(T):
+        s, p = seqs[t], poss[t]
+        lo = 0 if not window else max(0, p - window + 1)
+        keys = torch.arange(lo, p + 1, device=qkv.device)
+        pages = block_table[s].long()[keys // page_size]
+        offs = keys % page_size
+        k = k_cache[pages, :, offs].float()          # [n, kv_heads, dh]
+        v = v_cache[pages, :, offs].float()
+        for h in range(num_heads):
+            sc = (k[:, h // group] @ q[t, h]) * scale
+            pr = torch.softmax(sc, dim=0)
+            res[t, h] = pr @ v[:, h // group]
+    _store(out, res.reshape(T, num_heads * head_dim))
+
+
+def swiglu(gate_up, out):
+    I = gate_up.shape[1] // 2
+    g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
+    _store(out, u * (g / (1.0 + torch.exp(-g))))
+
+
+def argmax(logits, out):
+    # first maximum
+    m = logits.max(dim=1, keepdim=True).values
+    idx = torch.where(logits == m, torch.arange(logits.shape[1], device=logits.device)[None, :], logits.shape[1]).min(dim=1).values
+    out.copy_(idx.to(torch.int32))
+
+
+# ---- sampling ---------------------------------------------------------------
+
+_M64 = (1 << 64) - 1
+
+
+def _splitmix64(x: int) -> int:
+    x = (x + 0x9E3779B97F4A7C15) & _M64
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _M64
+    return x ^ (x >> 31)
+
+
+def uniform_for(seed: int, output_index: int, token: int) -> float:
+    """The generator of the sample kernel: 24 bits of a hash of (seed, index, token), in (0, 1)."""
+    key = _splitmix64((seed & _M64) ^ _splitmix64(output_index & _M64))
+    bits = _splitmix64(key ^ ((token * 0xD1342543DE82EF95) & _M64)) >> 40
+    return (bits + 0.5) / 16777216.0
+
+
+def sample_row(logits_row, temperature, top_k, top_p, seed, output_index):
+    """(token, kept ids) as the sample kernel computes them."""
+    z = logits_row.float().cpu()
+    V = z.numel()
+    if temperature <= 0.0 or top_k == 1:
+        m = z.max()
+        return int(torch.nonzero(z == m)[0]), None
+    z = z / np.float32(temperature)
+    keep = torch.ones(V, dtype=torch.bool)
+    if 0 < top_k < V:
+        kth = torch.topk(z, top_k).values[-1]
+        keep &= z >= kth
+    if 0.0 < top_p < 1.0:
+        m = z[keep].max()
+        e = torch.where(keep, torch.exp(z - m), torch.zeros(()))
+        p = e / e.sum()
+        # kept iff the probability mass of strictly larger candidates is below top_p
+        order = torch.argsort(z, descending=True, stable=True)
+        ps = p[order]
+        zs = z[order]
+        before = torch.cumsum(ps, 0) - ps
+        # equal values share the mass before the first of them
+        first_of_value = torch.ones(V, dtype=torch.bool)
+        first_of_value[1:] = zs[1:] != zs[:-1]
+        idx = torch.where(first_of_value, torch.arange(V), torch.zeros((), dtype=torch.long))
+        idx = torch.cummax(idx, 0).values
+        before = before[idx]
+        ok = torch.zeros(V, dtype=torch.bool)
+        ok[order] = before < top_p
+        keep &= ok
+    u = torch.tensor([uniform_for(seed, output_index, i) for i in range(V)], dtype=torch.float32)
+    g = -torch.log(-torch.log(u))
+    score = torch.where(keep, z + g, torch.full((), float("-inf")))
+    m = score.max()
+    return int(torch.nonzero(score == m)[0]), torch.nonzero(keep).flatten().tolist()
+
+
+def sample(logits, params, out):
+    host = params.cpu()
+    f = host.view(torch.float32)
+    res = []
+    for r in range(logits.shape[0]):
+        seed = (int(host[r, 3]) & 0xFFFFFFFF) | ((int(host[r, 4]) & 0xFFFFFFFF) << 32)
+        tok, _ = sample_row(logits[r], float(f[r, 0]), int(host[r, 1]), float(f[r, 2]), seed, int(host[r, 5]))
+        res.append(tok)
+    out.copy_(torch.tensor(res, dtype=torch.int32))
+
+
+ALL = ["embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
+       "paged_attention", "swiglu", "argmax", "sample"]
