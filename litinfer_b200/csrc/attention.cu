@@ -1,0 +1,75 @@
+// li_paged_attention: attention of the step's tokens over the paged cache,
+// chosen by dtype and batch shape.
+//
+//   float32                          -> general kernel (attention_generic.cu)
+//   bfloat16, every item one token   -> split-context decode kernel (attention_decode.cu)
+//   bfloat16, portions of prompts    -> tiled tensor-core kernel (attention_prefill.cu);
+//                                       single tokens in the same batch are portions of length one
+//   sizes those refuse               -> general kernel
+#include "common.cuh"
+
+int li_attention_generic(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype, const int* block_table,
+                         int max_blocks, const int* seq_of_token, const int* positions, int T, int nh, int nkv, int dh,
+                         int page_size, int num_pages, float scale, int window, cudaStream_t stream);
+bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size);
+int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
+                        const int* ctx_lens, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window,
+                        int max_ctx_len, cudaStream_t stream);
+bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size);
+int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
+                         const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size,
+                         int num_pages, float scale, int window, int max_q_len, cudaStream_t stream);
+
+static int validate(int T, int S, int nh, int nkv, int dh, int page_size, int window) {
+    LI_REQUIRE(T >= 0 && S > 0, "attention: bad batch T=%d S=%d", T, S);
+    LI_REQUIRE(nh > 0 && nkv > 0 && nh % nkv == 0, "attention: %d heads are not a multiple of %d key/value heads", nh, nkv);
+    LI_REQUIRE(dh > 0, "attention: bad head_dim %d", dh);
+    LI_REQUIRE(page_size >= 1, "attention: bad page size %d", page_size);
+    LI_REQUIRE(window >= 0, "attention: bad window %d", window);
+    return 0;
+}
+
+LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype,
+                                 const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens,
+                                 const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
+                                 int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
+                                 cudaStream_t stream) {
+    if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
+    if (T == 0) return 0;
+    if (dtype == LI_BF16) {
+        if (max_q_len == 1 && T == S && li_attention_decode_accepts(nh, nkv, dh, page_size))
+            return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, S, nh, nkv, dh, page_size,
+                                       num_pages, scale, window, max_ctx_len, stream);
+        if (li_attention_prefill_accepts(nh, nkv, dh, page_size))
+            return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh,
+                                        page_size, num_pages, scale, window, max_q_len, stream);
+    }
+    return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv, dh,
+                                page_size, num_pages, scale, window, stream);
+}
+
+// Force one implementation, for tests of each kernel alone: 0 general, 1 decode, 2 prefill.
+LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, const void* kcache, const void* vcache, int dtype,
+                                      const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens,
+                                      const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
+                                      int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
+                                      cudaStream_t stream) {
+    if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
+    if (T == 0) return 0;
+    if (which == 0)
+        return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv,
+                                    dh, page_size, num_pages, scale, window, stream);
+    LI_REQUIRE(dtype == LI_BF16, "attention: implementation %d takes bfloat16 only", which);
+    if (which == 1) {
+        LI_REQUIRE(max_q_len == 1 && T == S, "attention: the decode kernel takes one token per sequence");
+        LI_REQUIRE(li_attention_decode_accepts(nh, nkv, dh, page_size), "attention: the decode kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
+        return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, S, nh, nkv, dh, page_size, num_pages,
+                                   scale, window, max_ctx_len, stream);
+    }
+    if (which == 2) {
+        LI_REQUIRE(li_attention_prefill_accepts(nh, nkv, dh, page_size), "attention: the prefill kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
+        return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
+                                    num_pages, scale, window, max_q_len, stream);
+    }
+    return li_fail("attention: unknown implementation %d", which);
+}

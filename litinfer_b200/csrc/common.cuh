@@ -1,0 +1,65 @@
+// Shared helpers of the kernels: error reporting across the C interface,
+// element types, 32-bit conversions and reductions.
+//
+// Every exported function returns 0 on success.  On failure it stores a
+// message that li_last_error() returns, and launches nothing (or reports the
+// launch error).  Arithmetic that the engine promises in 32-bit (norms,
+// softmax, rotation angles, residual sums) uses float and the full-precision
+// math functions; this library is compiled without fast-math.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#define LI_EXPORT extern "C" __attribute__((visibility("default")))
+
+enum LiDtype : int { LI_F32 = 0, LI_BF16 = 1 };
+
+int li_fail(const char* fmt, ...);            // stores the message, returns 1
+int li_check_launch(const char* what);        // cudaGetLastError -> message
+
+#define LI_REQUIRE(cond, ...)            \
+    do {                                 \
+        if (!(cond)) return li_fail(__VA_ARGS__); \
+    } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// The order of the additions is fixed by the block size, not by the data.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = (lane < nwarps) ? scratch[lane] : 0.0f;
+    r = warp_sum(r);
+    return r;
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }

@@ -1,0 +1,139 @@
+// Embedding gather, RMSNorm (plain, fused with the residual add, gathered
+// rows), residual add and SwiGLU.
+//
+// RMSNorm per row: ss = sum x_j^2; r = 1 / sqrt(ss / H + eps); y_j = (w_j x_j) r,
+// all in float, one rounding of y (LitInfer: src/ops/rms_norm/op.cpp:13-24).
+// SwiGLU: up * gate / (1 + exp(-gate)) (src/ops/swiglu/op.cpp:17-23).
+// One block per row; every thread owns the elements j = tid, tid + B, ... in
+// both passes, so the second pass re-reads only what the same thread wrote.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out, int H, int V) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);          // ids are validated on the host; never read outside the table
+    const T* row = table + (size_t)id * H;
+    float* dst = out + (size_t)t * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) dst[j] = to_float(row[j]);
+}
+
+// mode 0: y = norm(x[row]); mode 1: x[row] += delta[row] first (stored back).
+template <typename T, bool kAdd>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
+                               const float* __restrict__ w, float eps, T* __restrict__ out, int H, int T_rows) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    int src = rows ? rows[r] : r;
+    if (src < 0 || src >= T_rows) src = 0;
+    float* xr = x + (size_t)src * H;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float v = xr[j];
+        if (kAdd) {
+            v += to_float(delta[(size_t)src * H + j]);
+            xr[j] = v;
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_float<T>((w[j] * xr[j]) * rinv);
+}
+
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ delta, long long n) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) x[i] += to_float(delta[i]);
+}
+
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, long long n) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        const long long t = i / I;
+        const int j = (int)(i - t * I);
+        const float g = to_float(gate_up[t * 2 * I + j]);
+        const float u = to_float(gate_up[t * 2 * I + I + j]);
+        out[i] = from_float<T>(u * (g / (1.0f + expf(-g))));
+    }
+}
+
+int grid_for(long long n, int threads) {
+    long long b = ceil_div_ll(n, threads);
+    if (b > 148LL * 16) b = 148LL * 16;
+    return (int)(b < 1 ? 1 : b);
+}
+
+}  // namespace
+
+LI_EXPORT int li_embedding(const void* table, int dtype, const int* ids, float* out, int T, int H, int V, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && H > 0 && V > 0, "embedding: bad sizes T=%d H=%d V=%d", T, H, V);
+    if (T == 0) return 0;
+    if (dtype == LI_F32)
+        embedding_kernel<float><<<T, kRowThreads, 0, stream>>>((const float*)table, ids, out, H, V);
+    else if (dtype == LI_BF16)
+        embedding_kernel<bf16><<<T, kRowThreads, 0, stream>>>((const bf16*)table, ids, out, H, V);
+    else
+        return li_fail("embedding: unknown dtype %d", dtype);
+    return li_check_launch("embedding");
+}
+
+template <bool kAdd>
+static int launch_norm(float* x, const void* delta, int dtype, const int* rows, const float* w, float eps, void* out, int R, int T,
+                       int H, cudaStream_t stream, const char* what) {
+    LI_REQUIRE(R >= 0 && H > 0, "%s: bad sizes rows=%d H=%d", what, R, H);
+    if (R == 0) return 0;
+    if (dtype == LI_F32)
+        rmsnorm_kernel<float, kAdd><<<R, kRowThreads, 0, stream>>>(x, (const float*)delta, rows, w, eps, (float*)out, H, T);
+    else if (dtype == LI_BF16)
+        rmsnorm_kernel<bf16, kAdd><<<R, kRowThreads, 0, stream>>>(x, (const bf16*)delta, rows, w, eps, (bf16*)out, H, T);
+    else
+        return li_fail("%s: unknown dtype %d", what, dtype);
+    return li_check_launch(what);
+}
+
+LI_EXPORT int li_rmsnorm(const float* x, const float* w, float eps, void* out, int dtype, int T, int H, cudaStream_t stream) {
+    return launch_norm<false>(const_cast<float*>(x), nullptr, dtype, nullptr, w, eps, out, T, T, H, stream, "rmsnorm");
+}
+
+LI_EXPORT int li_add_rmsnorm(float* x, const void* delta, int dtype, const float* w, float eps, void* out, int T, int H,
+                             cudaStream_t stream) {
+    return launch_norm<true>(x, delta, dtype, nullptr, w, eps, out, T, T, H, stream, "add_rmsnorm");
+}
+
+LI_EXPORT int li_gather_rmsnorm(const float* x, const int* rows, const float* w, float eps, void* out, int dtype, int R, int T, int H,
+                                cudaStream_t stream) {
+    return launch_norm<false>(const_cast<float*>(x), nullptr, dtype, rows, w, eps, out, R, T, H, stream, "gather_rmsnorm");
+}
+
+LI_EXPORT int li_residual_add(float* x, const void* delta, int dtype, long long n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (dtype == LI_F32)
+        residual_add_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>(x, (const float*)delta, n);
+    else if (dtype == LI_BF16)
+        residual_add_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>(x, (const bf16*)delta, n);
+    else
+        return li_fail("residual_add: unknown dtype %d", dtype);
+    return li_check_launch("residual_add");
+}
+
+LI_EXPORT int li_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && I > 0, "swiglu: bad sizes T=%d I=%d", T, I);
+    const long long n = (long long)T * I;
+    if (n == 0) return 0;
+    if (dtype == LI_F32)
+        swiglu_kernel<float><<<grid_for(n, 256), 256, 0, stream>>>((const float*)gate_up, (float*)out, I, n);
+    else if (dtype == LI_BF16)
+        swiglu_kernel<bf16><<<grid_for(n, 256), 256, 0, stream>>>((const bf16*)gate_up, (bf16*)out, I, n);
+    else
+        return li_fail("swiglu: unknown dtype %d", dtype);
+    return li_check_launch("swiglu");
+}

@@ -1,0 +1,47 @@
+// li_linear: out[M, N] = a[M, K] w[N, K]^T (+ bias[N]), chosen by dtype and size.
+//
+//   float32            -> CUDA-core kernel (gemm_simt.cu), always: a true 32-bit product
+//   bfloat16, M <= 16  -> weight-streaming kernel (gemv_bf16.cu): decode is bound by
+//                         reading every weight once
+//   bfloat16, larger M -> tcgen05 kernel with TMA-fed operands and the accumulator
+//                         in tensor memory (gemm_tcgen05.cu), when the sizes meet its
+//                         alignment rules (K a multiple of 8 elements = 16 bytes per row)
+//   otherwise          -> CUDA-core kernel
+#include "common.cuh"
+
+int li_linear_simt(const void* a, const void* w, const float* bias, void* out, int dtype_in, int dtype_out, int M, int N, int K,
+                   cudaStream_t stream);
+int li_linear_gemv_bf16(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
+                        cudaStream_t stream);
+bool li_gemv_bf16_accepts(int M, int N, int K);
+int li_linear_tcgen05(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
+                      cudaStream_t stream);
+bool li_tcgen05_accepts(const void* a, const void* w, const void* out, int dtype_out, int M, int N, int K);
+
+LI_EXPORT int li_linear(const void* a, const void* w, const float* bias, void* out, int dtype_in, int dtype_out, int M, int N, int K,
+                        cudaStream_t stream) {
+    LI_REQUIRE(M >= 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
+    if (M == 0) return 0;
+    if (dtype_in == LI_BF16) {
+        if (li_gemv_bf16_accepts(M, N, K)) return li_linear_gemv_bf16(a, w, bias, out, dtype_out, M, N, K, stream);
+        if (li_tcgen05_accepts(a, w, out, dtype_out, M, N, K)) return li_linear_tcgen05(a, w, bias, out, dtype_out, M, N, K, stream);
+    }
+    return li_linear_simt(a, w, bias, out, dtype_in, dtype_out, M, N, K, stream);
+}
+
+// Force one implementation, for tests of each kernel alone: 0 simt, 1 gemv, 2 tcgen05.
+LI_EXPORT int li_linear_with(int which, const void* a, const void* w, const float* bias, void* out, int dtype_in, int dtype_out, int M,
+                             int N, int K, cudaStream_t stream) {
+    LI_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
+    if (which == 0) return li_linear_simt(a, w, bias, out, dtype_in, dtype_out, M, N, K, stream);
+    LI_REQUIRE(dtype_in == LI_BF16, "linear: implementation %d takes bfloat16 input only", which);
+    if (which == 1) {
+        LI_REQUIRE(li_gemv_bf16_accepts(M, N, K), "linear: the weight-streaming kernel refuses M=%d N=%d K=%d", M, N, K);
+        return li_linear_gemv_bf16(a, w, bias, out, dtype_out, M, N, K, stream);
+    }
+    if (which == 2) {
+        LI_REQUIRE(li_tcgen05_accepts(a, w, out, dtype_out, M, N, K), "linear: the tcgen05 kernel refuses M=%d N=%d K=%d (K must be a multiple of 8, pointers 16-byte aligned)", M, N, K);
+        return li_linear_tcgen05(a, w, bias, out, dtype_out, M, N, K, stream);
+    }
+    return li_fail("linear: unknown implementation %d", which);
+}

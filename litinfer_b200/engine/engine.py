@@ -52,6 +52,13 @@ class Engine:
         self.sampler = Sampler(model.device)
         self.tokens_run = 0
 
+    @staticmethod
+    def bytes_per_page(model: DecoderModel, page_size: int = 16) -> int:
+        """Device bytes one page id stands for, over all cache groups and their entries."""
+        probe = CacheManager(model.cache_requirements(), [e.cache_from for e in model.spec.schedule], 1, page_size, 1,
+                             model.dtype, "cpu", allocate=False)
+        return probe.bytes_per_page()
+
     # ------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], max_new_tokens: int = 128, params: Optional[SamplingParams] = None) -> int:
         vocab = self.model.spec.vocab_size

@@ -157,6 +157,23 @@ def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], 
            "linear")
 
 
+LINEAR_IMPLEMENTATIONS = {"simt": 0, "gemv": 1, "tcgen05": 2}
+
+
+def linear_with(which: str, a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """:func:`linear` through one named kernel (``simt``, ``gemv``, ``tcgen05``); an error
+    if that kernel refuses the sizes.  For tests and measurements of a kernel alone."""
+    M, Kd = a.shape
+    N = weight.shape[0]
+    _need(a, "linear input")
+    _need(weight, "linear weight", a.dtype, (N, Kd))
+    if bias is not None:
+        _need(bias, "linear bias", torch.float32, (N,))
+    _need(out, "linear output", None, (M, N))
+    _check(library().li_linear_with(_i(LINEAR_IMPLEMENTATIONS[which]), _p(a), _p(weight), _p(bias), _p(out), _i(_dt(a)),
+                                    _i(_dt(out)), _i(M), _i(N), _i(Kd), _stream(out)), f"linear[{which}]")
+
+
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torch.Tensor, rotary_dim: int,
                   slot_mapping: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   num_heads: int, num_kv_heads: int, head_dim: int, write: bool = True) -> None:
@@ -179,16 +196,21 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torc
         "rope_kv_write")
 
 
+ATTENTION_IMPLEMENTATIONS = {"general": 0, "decode": 1, "prefill": 2}
+
+
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     block_table: torch.Tensor, q_start: torch.Tensor, ctx_lens: torch.Tensor,
                     seq_of_token: torch.Tensor, positions: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-                    max_q_len: int, max_ctx_len: int) -> None:
+                    max_q_len: int, max_ctx_len: int, implementation: Optional[str] = None) -> None:
     """Causal grouped-query attention of the step's tokens over the paged cache.
 
     Queries are the first ``num_heads * head_dim`` columns of ``qkv`` (already
     rotated).  The token at position p of sequence s sees the cached keys
-    ``max(0, p - window + 1) .. p`` of s, found through ``block_table[s]``."""
+    ``max(0, p - window + 1) .. p`` of s, found through ``block_table[s]``.
+    ``implementation`` (``general``, ``decode``, ``prefill``) forces one kernel, for
+    tests and measurements; it is an error if that kernel refuses the sizes."""
     T = qkv.shape[0]
     S = ctx_lens.shape[0]
     _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
@@ -207,12 +229,15 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
     if block_table.shape[1] * page_size < max_ctx_len:
         raise KernelError(f"block table of {block_table.shape[1]} pages cannot cover a context of {max_ctx_len}")
-    _check(library().li_paged_attention(
-        _p(qkv), _p(out), _p(k_cache), _p(v_cache), _i(_dt(qkv)), _p(block_table), _i(block_table.shape[1]),
-        _p(q_start), _p(ctx_lens), _p(seq_of_token), _p(positions), _i(T), _i(S),
-        _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _f(scale),
-        _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _stream(out)),
-        "paged_attention")
+    args = (_p(qkv), _p(out), _p(k_cache), _p(v_cache), _i(_dt(qkv)), _p(block_table), _i(block_table.shape[1]),
+            _p(q_start), _p(ctx_lens), _p(seq_of_token), _p(positions), _i(T), _i(S),
+            _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _f(scale),
+            _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _stream(out))
+    if implementation is None:
+        _check(library().li_paged_attention(*args), "paged_attention")
+    else:
+        _check(library().li_paged_attention_with(_i(ATTENTION_IMPLEMENTATIONS[implementation]), *args),
+               f"paged_attention[{implementation}]")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:

@@ -83,7 +83,7 @@ def rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cach
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
-                    num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len):
+                    num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None):
     T = qkv.shape[0]
     page_size = k_cache.shape[2]
     group = num_heads // num_kv_heads
@@ -132,10 +132,10 @@ def _splitmix64(x: int) -> int:
 
 
 def uniform_for(seed: int, output_index: int, token: int) -> float:
-    """The generator of the sample kernel: 24 bits of a hash of (seed, index, token), in (0, 1)."""
+    """The generator of the sample kernel: 23 bits of a hash of (seed, index, token), in (0, 1)."""
     key = _splitmix64((seed & _M64) ^ _splitmix64(output_index & _M64))
-    bits = _splitmix64(key ^ ((token * 0xD1342543DE82EF95) & _M64)) >> 40
-    return (bits + 0.5) / 16777216.0
+    bits = _splitmix64(key ^ ((token * 0xD1342543DE82EF95) & _M64)) >> 41
+    return (bits + 0.5) / 8388608.0
 
 
 def sample_row(logits_row, temperature, top_k, top_p, seed, output_index):

@@ -1,0 +1,100 @@
+"""The host side of the engine (cache manager, block tables, slot mapping, step
+metadata, schedule, page release behind a window) checked on the CPU: the
+kernels are replaced by their plain references, everything else is the
+product code, and the logits are compared with the plain model."""
+
+from __future__ import annotations
+
+import json
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as P
+from conftest import TINY
+from helpers import check_logits, plain_logits, random_tokens, stack
+from test_replay_gpu import build_trace
+
+
+def replay_in_process(model_dir, dtype, trace, max_tokens, vocab, tmp_path, spec=None):
+    from litinfer_b200.engine.replay import replay
+    from litinfer_b200.models import DecoderModel
+
+    model = DecoderModel.from_dir(model_dir, dtype, "cpu", spec=spec)
+    replay(model, trace.lines().splitlines(), tmp_path, max_tokens, use_graphs=False)
+    res = {}
+    for i, rows in enumerate(trace.where):
+        if not rows:
+            continue
+        lg = torch.from_numpy(np.fromfile(tmp_path / f"{i}.f32", dtype="<f4").reshape(len(rows), vocab).copy())
+        for (rid, pos), row in zip(rows, lg):
+            res.setdefault(rid, {})[pos] = row
+    return res
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_on_cpu_references(name, dtype, model_dirs, tmp_path, cpu_kernels):
+    cfg = TINY[name]
+    vocab = cfg["vocab_size"]
+    tr, seqs, need = build_trace(vocab, cfg["max_position_embeddings"])
+    got = replay_in_process(model_dirs[name], dtype, tr, need, vocab, tmp_path)
+    for rid, toks in seqs.items():
+        check_logits(stack(got[rid]), plain_logits(model_dirs[name], toks, dtype), dtype, f"{name} {dtype} {rid}")
+
+
+def test_pool_too_small_is_an_error(model_dirs, tmp_path, cpu_kernels):
+    from litinfer_b200.cache import OutOfPages
+    from helpers import Trace
+
+    tr = Trace()
+    tr.step([("a", random_tokens(70, 256, 1), True)])
+    with pytest.raises(OutOfPages):
+        replay_in_process(model_dirs["A"], "float32", tr, 64, 256, tmp_path)
+
+
+def test_schedule_with_repeated_block_and_shared_cache(model_dirs, tmp_path, cpu_kernels):
+    """The order of layers is data: block 0 twice, and an entry that reads the
+    keys and values of an earlier entry instead of its own."""
+    from litinfer_b200.config import ScheduleEntry, load_config
+    from helpers import Trace
+
+    spec = load_config(model_dirs["A"]).to_model_spec()
+    spec = spec.with_schedule([ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0), ScheduleEntry(1, cache_from=1)])
+    plain_schedule = [(0, None), (1, None), (0, None), (1, 1)]
+    toks = random_tokens(45, 256, 3)
+    tr = Trace()
+    tr.step([("s", toks[:17], True)])
+    tr.step([("s", toks[17:19], True)])
+    for t in toks[19:30]:
+        tr.step([("s", [t], True)])
+    tr.step([("s", toks[30:], True)])
+    got = replay_in_process(model_dirs["A"], "float32", tr, 64, 256, tmp_path, spec=spec)
+    ref = plain_logits(model_dirs["A"], toks, "float32", plain_schedule)
+    check_logits(stack(got["s"]), ref, "float32", "custom schedule")
+
+
+def test_engine_greedy_matches_plain(model_dirs, cpu_kernels):
+    from litinfer_b200.engine import Engine, EngineConfig
+    from litinfer_b200.models import DecoderModel
+
+    for name, lens, n_new in (("A", [5, 11, 17], 8), ("B", [1, 9, 33, 40], 12)):
+        cfg, w = P.read_model_folder(model_dirs[name])
+        model = DecoderModel.from_dir(model_dirs[name], "float32", "cpu")
+        eng = Engine(model, EngineConfig(num_pages=10, max_num_seqs=4, max_tokens_per_step=24, prefill_chunk=16, use_graphs=False))
+        prompts = [random_tokens(n, cfg["vocab_size"], 100 + n) for n in lens]
+        ids = [eng.add_request(p, n_new) for p in prompts]
+        eng.run_to_completion()
+        eng.manager.check()
+        assert eng.manager.num_free_pages(0) == 10 and eng.manager.num_free_slots() == 4
+        for rid, p in zip(ids, prompts):
+            ref, margin = P.plain_greedy(cfg, w, p, n_new)
+            assert margin > 1e-5, "the plain model's own choice is a near-tie; pick another seed"
+            assert eng.get_output(rid) == ref, f"config {name}, prompt of {len(p)}"
+
+
+def test_toy_mixer_with_state_on_cpu_references(model_dirs, cpu_kernels):
+    from test_engine_gpu import run_toy_mixer
+
+    run_toy_mixer(model_dirs, "cpu")

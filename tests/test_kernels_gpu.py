@@ -1,0 +1,353 @@
+"""Each kernel alone against its plain reference (tests/kernel_refs.py), at
+sizes other than the engine's tiny configurations: widths and vocabularies
+that are no power of two, head sizes in steps of 16, several head groupings.
+Where random data would hide a fault the inputs are made so that it shows: one
+far key that takes all the softmax weight, a key just inside and just outside
+a window, keys on both sides of a page's edge, scrambled page tables."""
+
+from __future__ import annotations
+
+import math
+
+import pytest
+import torch
+
+import kernel_refs as R
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def K():
+    from litinfer_b200 import kernels
+    return kernels
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(dev())
+
+
+def close(got, ref, dtype, what="", f32_tol=2e-5, scale=None):
+    got, ref = got.float(), ref.float()
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    s = float(ref.abs().max()) if scale is None else scale
+    tol = f32_tol * max(s, 1.0) if dtype == torch.float32 else (2.0 ** -7) * max(s, 1e-3)
+    err = float((got - ref).abs().max())
+    assert err <= tol, f"{what}: max |diff| {err:.3e} > {tol:.3e} (scale {s:.3f})"
+
+
+# --------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    V, H, T = 77, 100, 9
+    table = rnd(V, H, dtype=dtype, seed=1)
+    ids = torch.tensor([0, 76, 5, 5, 31, 2, 76, 0, 40], dtype=torch.int32, device=dev())
+    out = torch.empty(T, H, dtype=torch.float32, device=dev())
+    K().embedding(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [80, 1536, 3000])
+def test_rmsnorm_family(dtype, H):
+    T = 7
+    x = rnd(T, H, seed=2, scale=3.0)
+    w = 1 + 0.1 * rnd(H, seed=3)
+    eps = 1e-5
+    out = torch.empty(T, H, dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    K().rmsnorm(x, w, eps, out)
+    R.rmsnorm(x, w, eps, ref)
+    close(out, ref, dtype, "rmsnorm")
+    delta = rnd(T, H, dtype=dtype, seed=4)
+    x1, x2 = x.clone(), x.clone()
+    K().add_rmsnorm(x1, delta, w, eps, out)
+    R.add_rmsnorm(x2, delta, w, eps, ref)
+    close(x1, x2, torch.float32, "add_rmsnorm residual")
+    close(out, ref, dtype, "add_rmsnorm output")
+    rows = torch.tensor([6, 0, 3, 3], dtype=torch.int32, device=dev())
+    out = torch.empty(4, H, dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    K().gather_rmsnorm(x, rows, w, eps, out)
+    R.gather_rmsnorm(x, rows, w, eps, ref)
+    close(out, ref, dtype, "gather_rmsnorm")
+    x1, x2 = x.clone(), x.clone()
+    K().residual_add(x1, delta)
+    R.residual_add(x2, delta)
+    assert torch.equal(x1, x2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    T, I = 5, 272
+    gu = rnd(T, 2 * I, dtype=dtype, seed=5, scale=2.0)
+    out = torch.empty(T, I, dtype=dtype, device=dev())
+    ref = torch.empty_like(out)
+    K().swiglu(gu, out)
+    R.swiglu(gu, ref)
+    close(out, ref, dtype, "swiglu")
+
+
+LINEAR_SHAPES = [(1, 64, 64), (5, 100, 72), (33, 389, 96), (130, 200, 272), (64, 1536, 1536), (3, 1000, 8960), (300, 136, 40)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", LINEAR_SHAPES)
+def test_linear(dtype, shape):
+    M, N, Kd = shape
+    a = rnd(M, Kd, dtype=dtype, seed=6)
+    w = rnd(N, Kd, dtype=dtype, seed=7, scale=0.05)
+    b = rnd(N, seed=8)
+    for bias in (None, b):
+        for out_dtype in ({dtype, torch.float32}):
+            out = torch.empty(M, N, dtype=out_dtype, device=dev())
+            ref = torch.empty_like(out)
+            K().linear(a, w, bias, out)
+            R.linear(a, w, bias, ref)
+            close(out, ref, out_dtype, f"linear {shape} bias={bias is not None} out={out_dtype}", f32_tol=1e-5 * math.sqrt(Kd))
+
+
+@pytest.mark.parametrize("shape", LINEAR_SHAPES)
+def test_linear_simt_rows_do_not_depend_on_batch(shape):
+    """float32: a row's result is the same bits whether it runs alone or among others."""
+    M, N, Kd = shape
+    a = rnd(M, Kd, seed=6)
+    w = rnd(N, Kd, seed=7, scale=0.05)
+    full = torch.empty(M, N, device=dev())
+    K().linear(a, w, None, full)
+    one = torch.empty(1, N, device=dev())
+    K().linear(a[M - 1:M].contiguous(), w, None, one)
+    assert torch.equal(one[0], full[M - 1])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cfg", [(4, 2, 16, 16), (3, 1, 32, 32), (6, 2, 48, 32), (12, 2, 128, 128), (5, 5, 64, 32)])
+def test_rope_kv_write(dtype, cfg):
+    nh, nkv, dh, rot = cfg
+    T, pages, page = 11, 9, 16
+    qkv = rnd(T, (nh + 2 * nkv) * dh, dtype=dtype, seed=9)
+    positions = torch.tensor([0, 1, 2, 15, 16, 17, 100, 1000, 4000, 31, 32], dtype=torch.int32, device=dev())
+    theta = 10000.0
+    denom = torch.pow(torch.tensor(theta), torch.arange(rot // 2, dtype=torch.float32) * 2.0 / rot).to(dev())
+    g = torch.Generator().manual_seed(10)
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32).to(dev())
+    kc = torch.zeros(pages, nkv, page, dh, dtype=dtype, device=dev())
+    vc = torch.zeros_like(kc)
+    kc2, vc2, qkv2 = kc.clone(), vc.clone(), qkv.clone()
+    K().rope_kv_write(qkv, positions, denom, rot, slots, kc, vc, nh, nkv, dh, True)
+    R.rope_kv_write(qkv2, positions, denom, rot, slots, kc2, vc2, nh, nkv, dh, True)
+    # angles up to 4000 rad: float32 sine and cosine of such arguments differ by ~1e-4 between libraries
+    close(qkv, qkv2, dtype, "rope q", f32_tol=5e-4)
+    close(kc, kc2, dtype, "rope k cache", f32_tol=5e-4)
+    assert torch.equal(vc, vc2)
+    # without writing: q rotated, caches untouched
+    kc3, vc3, qkv3 = torch.zeros_like(kc), torch.zeros_like(vc), qkv2.clone()
+    K().rope_kv_write(qkv3, positions, denom, rot, slots, kc3, vc3, nh, nkv, dh, False)
+    assert not kc3.any() and not vc3.any()
+
+
+# --------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------
+
+def make_attention_case(q_lens, ctx_lens, nh, nkv, dh, page, dtype, seed=0, extra_pages=5):
+    """A ragged batch with scrambled page tables.  Returns the kernel arguments and the
+    logical (per sequence) keys and values so that tests can plant special ones."""
+    S = len(q_lens)
+    g = torch.Generator().manual_seed(seed)
+    blocks = [-(-c // page) for c in ctx_lens]
+    pages = sum(blocks) + extra_pages
+    perm = torch.randperm(pages, generator=g).tolist()
+    mb = max(blocks) + 1
+    bt = torch.full((S, mb), pages - 1, dtype=torch.int32)
+    it = iter(perm)
+    for s in range(S):
+        for b in range(blocks[s]):
+            bt[s, b] = next(it)
+    T = sum(q_lens)
+    qkv = (torch.randn(T, (nh + 2 * nkv) * dh, generator=g)).to(dtype)
+    keys = [torch.randn(c, nkv, dh, generator=g).to(dtype) for c in ctx_lens]
+    vals = [torch.randn(c, nkv, dh, generator=g).to(dtype) for c in ctx_lens]
+    q_start = [0]
+    for n in q_lens:
+        q_start.append(q_start[-1] + n)
+    seq_of, pos = [], []
+    for s, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+        seq_of += [s] * n
+        pos += list(range(c - n, c))
+    return dict(S=S, T=T, pages=pages, page=page, bt=bt, qkv=qkv, keys=keys, vals=vals, q_start=q_start, seq_of=seq_of, pos=pos,
+                ctx_lens=list(ctx_lens), q_lens=list(q_lens), nh=nh, nkv=nkv, dh=dh, dtype=dtype)
+
+
+def run_attention_case(c, window, implementation=None):
+    d = dev()
+    page, nkv, dh = c["page"], c["nkv"], c["dh"]
+    kc = torch.zeros(c["pages"], nkv, page, dh, dtype=c["dtype"])
+    vc = torch.zeros_like(kc)
+    for s in range(c["S"]):
+        for t in range(c["ctx_lens"][s]):
+            p = int(c["bt"][s, t // page])
+            kc[p, :, t % page] = c["keys"][s][t]
+            vc[p, :, t % page] = c["vals"][s][t]
+    args = dict(
+        qkv=c["qkv"].to(d), k_cache=kc.to(d), v_cache=vc.to(d), block_table=c["bt"].to(d),
+        q_start=torch.tensor(c["q_start"], dtype=torch.int32, device=d), ctx_lens=torch.tensor(c["ctx_lens"], dtype=torch.int32, device=d),
+        seq_of_token=torch.tensor(c["seq_of"], dtype=torch.int32, device=d), positions=torch.tensor(c["pos"], dtype=torch.int32, device=d))
+    out = torch.empty(c["T"], c["nh"] * dh, dtype=c["dtype"], device=d)
+    ref = torch.empty_like(out)
+    scale = 1.0 / math.sqrt(dh)
+    tail = (c["nh"], nkv, dh, scale, window, max(c["q_lens"]), max(c["ctx_lens"]))
+    K().paged_attention(args["qkv"], out, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
+                        args["seq_of_token"], args["positions"], *tail, implementation=implementation)
+    R.paged_attention(args["qkv"], ref, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
+                      args["seq_of_token"], args["positions"], *tail)
+    return out, ref
+
+
+HEADS = [(4, 2, 16), (3, 1, 32), (6, 2, 48), (12, 2, 128), (8, 8, 64), (14, 2, 80)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads", HEADS)
+@pytest.mark.parametrize("window", [None, 24])
+def test_attention_mixed_batch(dtype, heads, window):
+    nh, nkv, dh = heads
+    # a whole prompt, a portion with history, single tokens (one at a page's first slot, one at its last), a two-token portion
+    q_lens = [37, 20, 1, 1, 2, 1]
+    ctx_lens = [37, 75, 33, 48, 130, 1]
+    c = make_attention_case(q_lens, ctx_lens, nh, nkv, dh, 16, dtype, seed=nh * 100 + dh)
+    out, ref = run_attention_case(c, window)
+    close(out, ref, dtype, f"attention heads={heads} window={window}", f32_tol=2e-5)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads", [(4, 2, 16), (12, 2, 128), (6, 2, 48)])
+def test_attention_decode_batch(dtype, heads):
+    nh, nkv, dh = heads
+    ctx_lens = [1, 16, 17, 300, 777, 64, 255, 256, 257]
+    c = make_attention_case([1] * len(ctx_lens), ctx_lens, nh, nkv, dh, 16, dtype, seed=3)
+    out, ref = run_attention_case(c, None)
+    close(out, ref, dtype, f"decode attention heads={heads}")
+    out, ref = run_attention_case(c, 100)
+    close(out, ref, dtype, f"decode attention heads={heads} window=100")
+
+
+def _plant(c, s, h_kv, key_pos, q_token, strength=30.0):
+    """Make key ``key_pos`` of sequence s point along the query of ``q_token`` (all heads
+    of that key head), so that it takes nearly all the softmax weight if it is visible."""
+    nh, nkv, dh = c["nh"], c["nkv"], c["dh"]
+    group = nh // nkv
+    q = c["qkv"][q_token, (h_kv * group) * dh:(h_kv * group + 1) * dh].float()
+    c["keys"][s][key_pos, h_kv] = (q / q.norm() * strength).to(c["dtype"])
+    # all heads of the group share the direction of the first one
+    for g in range(1, group):
+        c["qkv"][q_token, (h_kv * group + g) * dh:(h_kv * group + g + 1) * dh] = c["qkv"][q_token, (h_kv * group) * dh:(h_kv * group + 1) * dh]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_far_key_among_hundreds(dtype):
+    """One key far back carries the answer: skipping it (a lost page, a wrong split) changes everything."""
+    nh, nkv, dh = 12, 2, 128
+    for far in (0, 3, 15, 16, 255, 256, 511):
+        c = make_attention_case([1, 5], [700, 640], nh, nkv, dh, 16, dtype, seed=far)
+        _plant(c, 0, 1, far, 0)
+        _plant(c, 1, 0, far, 5)              # last token of the 5-token portion
+        out, ref = run_attention_case(c, None)
+        close(out, ref, dtype, f"far key {far}")
+        # the planted key dominates: the output of that head is close to its value
+        v = c["vals"][0][far, 1].float().to(out.device)
+        got = out[0].float().view(nh, dh)[6]
+        assert (got - v).abs().max() < 0.1 * v.abs().max() + 0.05
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(dtype):
+    """The key at p - window + 1 is the oldest one seen; the one at p - window is not."""
+    nh, nkv, dh, W = 4, 2, 32, 40
+    for q_lens, ctx in (([1], [200]), ([3], [200])):
+        p_last = ctx[0] - 1
+        for key_pos, visible in ((p_last - W + 1, True), (p_last - W, False)):
+            c = make_attention_case(q_lens, ctx, nh, nkv, dh, 16, dtype, seed=key_pos)
+            _plant(c, 0, 0, key_pos, q_lens[0] - 1)
+            out, ref = run_attention_case(c, W)
+            close(out, ref, dtype, f"window edge key {key_pos}")
+            v = c["vals"][0][key_pos, 0].float().to(out.device)
+            got = out[-1].float().view(nh, dh)[0]
+            near = (got - v).abs().max() < 0.1 * v.abs().max() + 0.05
+            assert bool(near) == visible, f"key {key_pos} should be {'visible' if visible else 'hidden'}"
+
+
+# --------------------------------------------------------------------------
+# sampling
+# --------------------------------------------------------------------------
+
+def test_argmax_first_maximum():
+    V = 1000
+    lg = rnd(5, V, seed=11)
+    lg[0, 17] = lg[0, 900] = 50.0          # tie: the first wins
+    lg[1, 999] = 60.0
+    lg[2, 0] = 60.0
+    out = torch.empty(5, dtype=torch.int32, device=dev())
+    ref = torch.empty_like(out)
+    K().argmax(lg, out)
+    R.argmax(lg, ref)
+    assert out.tolist() == ref.tolist()
+    assert out.tolist()[:3] == [17, 999, 0]
+    big = rnd(3, 151936, seed=12)
+    out = torch.empty(3, dtype=torch.int32, device=dev())
+    K().argmax(big, out)
+    assert out.tolist() == big.argmax(dim=1).tolist()
+
+
+def _params(rows):
+    t = torch.empty(len(rows), 6, dtype=torch.int32)
+    f = t.view(torch.float32)
+    for r, (temp, k, p, seed, idx) in enumerate(rows):
+        f[r, 0] = temp
+        t[r, 1] = k
+        f[r, 2] = p
+        t[r, 3] = seed & 0x7FFFFFFF
+        t[r, 4] = (seed >> 32) & 0x7FFFFFFF
+        t[r, 5] = idx
+    return t.to(dev())
+
+
+def test_sample_matches_reference_and_is_batch_independent():
+    V = 389
+    lg = rnd(6, V, seed=13, scale=2.0)
+    rows = [(0.8, 0, 1.0, 5, 0), (1.0, 10, 1.0, 6, 3), (0.7, 0, 0.9, 7, 1), (1.3, 20, 0.5, 8, 2), (0.0, 0, 1.0, 9, 0), (1.0, 1, 1.0, 1, 0)]
+    out = torch.empty(6, dtype=torch.int32, device=dev())
+    K().sample(lg, _params(rows), out)
+    for r, (temp, k, p, seed, idx) in enumerate(rows):
+        tok, kept = R.sample_row(lg[r], temp, k, p, seed, idx)
+        assert out[r].item() == tok, f"row {r}"
+    # the same row alone gives the same token
+    for r in (1, 3):
+        one = torch.empty(1, dtype=torch.int32, device=dev())
+        K().sample(lg[r:r + 1].contiguous(), _params([rows[r]]), one)
+        assert one.item() == out[r].item()
+
+
+def test_sample_stays_in_candidates_and_follows_distribution():
+    V = 50
+    lg = rnd(1, V, seed=14, scale=1.5)
+    n = 4000
+    rows = [(1.0, 8, 0.95, 1000 + i, i) for i in range(n)]
+    out = torch.empty(n, dtype=torch.int32, device=dev())
+    K().sample(lg.expand(n, V).contiguous(), _params(rows), out)
+    import plain_qwen2 as P
+    ids, pr = P.plain_candidates(lg[0].cpu(), 1.0, 8, 0.95)
+    counts = torch.bincount(out.cpu().long(), minlength=V).float()
+    assert counts.sum() == n
+    allowed = torch.zeros(V, dtype=torch.bool)
+    allowed[ids] = True
+    assert counts[~allowed].sum() == 0, "a token outside top-k / top-p was drawn"
+    freq = counts[ids] / n
+    # 4000 draws: standard error of a frequency is below 0.008
+    assert (freq - pr).abs().max() < 0.04

@@ -1,0 +1,137 @@
+"""Trace replay through bin/trace_run, as a user runs it, against the plain model.
+
+For each tiny configuration and both dtypes one trace holds: a request whole;
+the same tokens with the last 32 decoded one by one; the same in portions of
+changing size down to two tokens; the first tokens of a sequence; and a mixed
+phase with up to four live requests, portions of some beside decoded tokens of
+others, in a pool so small that pages are used again.
+"""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from conftest import TINY
+from helpers import Trace, check_logits, plain_logits, random_tokens, run_trace, stack
+
+pytestmark = pytest.mark.gpu
+
+PORTIONS = [7, 16, 2, 33, 5, 2, 17, 3, 2, 11, 2, 29]
+MIX_PORTIONS = [5, 2, 16, 9, 3, 21, 2, 13]
+
+
+def round64(n):
+    return -(-n // 64) * 64
+
+
+def build_trace(vocab: int, max_pos: int):
+    tr = Trace()
+    seqs = {}
+    main_len = min(100, max_pos - 4)
+    main = random_tokens(main_len, vocab, 11)
+    # whole
+    seqs["whole"] = main
+    tr.step([("whole", main, True)], end=["whole"])
+    # most of it in one step, the last 32 one by one
+    seqs["tail"] = main
+    tr.step([("tail", main[:-32], True)])
+    for i in range(main_len - 32, main_len):
+        tr.step([("tail", [main[i]], True)], end=["tail"] if i == main_len - 1 else [])
+    # portions of changing size
+    seqs["cut"] = main
+    pos, i = 0, 0
+    while pos < main_len:
+        n = min(PORTIONS[i % len(PORTIONS)], main_len - pos)
+        last = pos + n == main_len
+        tr.step([("cut", main[pos:pos + n], True)], end=["cut"] if last else [])
+        pos += n
+        i += 1
+    # the first tokens of a sequence
+    for n in (1, 2, 3):
+        seqs[f"first{n}"] = random_tokens(n, vocab, 20 + n)
+        tr.step([(f"first{n}", seqs[f"first{n}"], True)], end=[f"first{n}"])
+    need = round64(main_len)
+    # mixed: up to four live requests
+    lens = [main_len, 60, min(90, max_pos - 2), 40, 75, 50, 33]
+    queue = [(f"mix{j}", main if j == 0 else random_tokens(n, vocab, 40 + j)) for j, n in enumerate(lens)]
+    for rid, toks in queue:
+        seqs[rid] = toks
+    live = []          # [rid, tokens, fed, slot]
+    step_no, slot = 0, 0
+    while queue or live:
+        while queue and len(live) < 4:
+            rid, toks = queue.pop(0)
+            live.append([rid, toks, 0, slot])
+            slot += 1
+        entries, ending = [], []
+        for item in live:
+            rid, toks, fed, sl = item
+            if (step_no + sl) % 5 == 4 and fed > 0:
+                continue                                   # left out of this step, goes on later
+            if fed < int(0.6 * len(toks)):
+                n = min(MIX_PORTIONS[(step_no + sl) % len(MIX_PORTIONS)], len(toks) - fed)
+            else:
+                n = 1
+            entries.append((rid, toks[fed:fed + n], True))
+            item[2] = fed + n
+            if item[2] == len(toks):
+                ending.append(rid)
+        need = max(need, sum(round64(it[2]) for it in live))
+        if entries:
+            tr.step(entries, end=ending)
+        live = [it for it in live if it[0] not in ending]
+        step_no += 1
+    return tr, seqs, need
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_replay_all_cuts(name, dtype, model_dirs, tmp_path):
+    cfg = TINY[name]
+    vocab = cfg["vocab_size"]
+    tr, seqs, need = build_trace(vocab, cfg["max_position_embeddings"])
+    got = run_trace(model_dirs[name], dtype, tr, tmp_path / "out", need, vocab)
+    refs = {}
+    for rid, toks in seqs.items():
+        key = tuple(toks)
+        if key not in refs:
+            refs[key] = plain_logits(model_dirs[name], toks, dtype)
+        lg = stack(got[rid])
+        assert lg.shape[0] == len(toks), f"{rid}: {lg.shape[0]} rows for {len(toks)} tokens"
+        check_logits(lg, refs[key], dtype, f"config {name} {dtype} request {rid}")
+    # the same tokens cut in different ways: beyond rounding nothing may differ, and in
+    # float32 every reduction runs in an order that does not depend on the cut
+    whole = stack(got["whole"])
+    for rid in ("tail", "cut", "mix0"):
+        other = stack(got[rid])
+        if dtype == "float32":
+            assert torch.equal(whole, other), f"float32: '{rid}' differs from 'whole' by {(whole - other).abs().max():.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_long_decode(dtype, model_dirs, tmp_path):
+    """A short prompt and then 560 tokens one by one: many pages, a long context."""
+    cfg = TINY["C"]
+    vocab = cfg["vocab_size"]
+    toks = random_tokens(600, vocab, 77)
+    tr = Trace()
+    tr.step([("long", toks[:40], True)])
+    for i in range(40, 600):
+        tr.step([("long", [toks[i]], True)], end=["long"] if i == 599 else [])
+    got = run_trace(model_dirs["C"], dtype, tr, tmp_path / "out", round64(600), vocab)
+    check_logits(stack(got["long"]), plain_logits(model_dirs["C"], toks, dtype), dtype, f"long decode {dtype}")
+
+
+def test_replay_without_graphs_matches(model_dirs, tmp_path):
+    """Captured decode steps and plainly launched ones give the same logits."""
+    cfg = TINY["A"]
+    vocab = cfg["vocab_size"]
+    toks = random_tokens(50, vocab, 5)
+    tr = Trace()
+    tr.step([("a", toks[:20], True)])
+    for i in range(20, 50):
+        tr.step([("a", [toks[i]], True)])
+    a = run_trace(model_dirs["A"], "bfloat16", tr, tmp_path / "g", 64, vocab)
+    b = run_trace(model_dirs["A"], "bfloat16", tr, tmp_path / "n", 64, vocab, extra=["--no-graphs"])
+    assert torch.equal(stack(a["a"]), stack(b["a"]))
