@@ -116,6 +116,7 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
         seq_of[lo] = s
         ctx[s] = 1
         slots[s] = manager.trash_slot
+        rows.append(lo)                      # padded items want a row too: the layout depends on S alone
     R = len(rows)
     need_blocks = max(-(-int(c) // page) for c in ctx)
     G = len(manager.groups)
