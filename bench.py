@@ -1,0 +1,374 @@
+"""Benchmark of the engine on one B200: decode tokens per second.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of the step function.  The default run has the layer
+sizes of the DeepSeek-R1-Distill-Qwen-1.5B shape (LitInfer's own benchmark
+model) with random weights, a batch of 8 sequences that each hold a 2,048-token
+prompt and decode on from there, 16-token pages, context capped at 4,096.
+One JSON line is printed:
+
+* ``value``: decoded tokens per second over exactly K steps, timed with CUDA
+  events on the device (metadata of every step staged on the device beforehand);
+* ``e2e``: the same through the Python entry point (``Qwen2.engine_*``): prompts
+  in as host lists, real prefill, and per step the host-to-device copy of the
+  step's metadata from pinned memory and the device-to-host read of the sampled
+  tokens inside the timed region;
+* ``prefill``: one 2,048-token prompt in one step;
+* ``roofline``: bytes a decode step has to read (every weight once and the cache
+  of the live requests) over its time, against the measured copy bandwidth;
+* ``points``: decode tokens per second at batch 1 and 64.
+
+Weights (3 GB) are larger than L2, so nothing stays cached between steps.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def load_peaks():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.is_file():
+        try:
+            d = json.loads(f.read_text())
+            hbm = float(d.get("hbm_gbs") or d.get("hbm_gb_s") or 0)
+            tf = float(d.get("bf16_tflops") or 0)
+            if hbm > 0 and tf > 0:
+                return {"hbm_gbs": hbm, "bf16_tflops": tf, "bf16_tflops_sustained": d.get("bf16_tflops_sustained"), "source": "measured"}
+        except (ValueError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+def bench_config():
+    """configs[2] of BASELINE.json: the 1.5B shape."""
+    return dict(
+        architectures=["Qwen2ForCausalLM"], torch_dtype="bfloat16", num_hidden_layers=28, hidden_size=1536,
+        num_attention_heads=12, num_key_value_heads=2, head_dim=128, intermediate_size=8960, vocab_size=151936,
+        rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096,
+        eos_token_id=None, use_sliding_window=False)
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 7:
+                self.rows.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def weight_bytes(model):
+    """Bytes of every matrix a decode step reads once: all blocks and the lm_head
+    (of the embedding only one row per token is read)."""
+    total = 0
+    for b in model.blocks:
+        for p in b.all_params():
+            n = 1
+            for s in p.shape:
+                n *= s
+            total += n * (model.embedding.element_size() if p.role == "matrix" else 4)
+    total += model.lm_head.numel() * model.lm_head.element_size()
+    return total
+
+
+def decode_flops_and_prefill_flops(cfg, T):
+    H, I, V, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"], cfg["num_hidden_layers"]
+    nh, nkv, dh = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_token_linear = 2 * (H * (nh + 2 * nkv) * dh + nh * dh * H + 3 * H * I) * L
+    attn = 2 * 2 * nh * dh * (T * (T + 1) // 2) * L          # causal q k^T and p v
+    return per_token_linear * T + attn + 2 * H * V
+
+
+def make_decode_state(model, batch, context, steps_total, seed=0):
+    """Cache manager and runner with ``batch`` requests that already hold ``context``
+    tokens (cache filled with random values: decode timing does not need a real prefill)."""
+    import torch
+
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.engine import ModelRunner
+
+    spec = model.spec
+    per_seq = -(-(context + steps_total + 1) // 16)
+    manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], per_seq * batch, 16, batch,
+                           model.dtype, model.device)
+    for g in manager.groups:
+        g.kv.normal_(0.0, 0.5)
+    runner = ModelRunner(model, manager, use_graphs=True, max_context=min(spec.max_position_embeddings, context + steps_total + 1))
+    reqs = []
+    for b in range(batch):
+        rc = manager.admit(b)
+        manager.extend(rc, context)
+        manager.commit(rc, context)
+        reqs.append(rc)
+    return manager, runner, reqs
+
+
+def time_decode(model, batch, context, steps, warmup):
+    """Device time of exactly ``steps`` decode steps (tokens per second, ms per step,
+    launches per step, mean context)."""
+    import numpy as np
+    import torch
+
+    from litinfer_b200 import kernels
+    from litinfer_b200.engine import StepItem
+    from litinfer_b200.engine.batch import pack_step
+
+    total = steps + warmup
+    manager, runner, reqs = make_decode_state(model, batch, context, total)
+    vocab = model.spec.vocab_size
+    g = torch.Generator().manual_seed(1)
+    toks = torch.randint(0, vocab, (total + 1, batch), generator=g).tolist()
+    # first step through the ordinary path: captures the graph for this batch size
+    for rc in reqs:
+        manager.extend(rc, rc.length + 1)
+    before = kernels.launches
+    runner.step([StepItem(rc, [toks[0][b]], (0,)) for b, rc in enumerate(reqs)])
+    graph = runner._graphs[runner._bucket(batch)]
+    # launches of one forward = those of the capture pass (two warm-ups and the capture itself ran the same sequence)
+    launches_per_step = (kernels.launches - before) // 3
+    out = torch.empty(batch, dtype=torch.int32, device=model.device)
+    max_blocks = graph.layout["max_blocks"]
+    staged = []
+    for k in range(total):
+        for rc in reqs:
+            manager.extend(rc, rc.length + 1)
+        buf, layout = pack_step([StepItem(rc, [toks[k + 1][b]], (0,)) for b, rc in enumerate(reqs)], manager, vocab,
+                                pad_seqs=runner._bucket(batch), max_blocks=max_blocks)
+        assert layout["fields"] == graph.layout["fields"]
+        staged.append(torch.from_numpy(buf))
+        for rc in reqs:
+            manager.commit(rc, rc.length + 1)
+    staged = torch.stack(staged).to(model.device)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    def run(k):
+        graph.meta_buf[:staged.shape[1]].copy_(staged[k], non_blocking=True)
+        graph.graph.replay()
+        kernels.argmax(graph.logits[:batch], out)
+
+    for k in range(warmup):
+        run(k)
+    torch.cuda.synchronize()
+    start.record()
+    for k in range(warmup, total):
+        run(k)
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    mean_ctx = context + 1 + warmup + (steps + 1) / 2
+    del staged, graph
+    return dict(tok_s=batch * steps / (ms / 1e3), ms_per_step=ms / steps, launches_per_step=launches_per_step + 1, mean_ctx=mean_ctx)
+
+
+def time_prefill(model, tokens, repeats=3):
+    import torch
+
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.engine import ModelRunner, StepItem
+
+    spec = model.spec
+    manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], -(-tokens // 16) + 1, 16, 1,
+                           model.dtype, model.device)
+    runner = ModelRunner(model, manager, use_graphs=False)
+    g = torch.Generator().manual_seed(2)
+    prompt = torch.randint(0, spec.vocab_size, (tokens,), generator=g).tolist()
+    times = []
+    for i in range(repeats + 2):
+        rc = manager.admit(i)
+        manager.extend(rc, tokens)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepItem(rc, prompt, (tokens - 1,))])
+        stop.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(start.elapsed_time(stop))
+        manager.release(rc)
+    return statistics.median(times)
+
+
+def time_e2e(model, cfg, batch, prompt_len, new_tokens, steps):
+    """Through the Python entry point: host token lists in, host token lists out."""
+    import torch
+
+    from litinfer_b200 import Qwen2
+
+    front = Qwen2(None, model=model, max_num_seqs=batch, max_tokens_per_step=4096, prefill_chunk=2048,
+                  num_pages=(-(-(prompt_len + new_tokens + 1) // 16)) * batch)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg["vocab_size"], (prompt_len,), generator=g).tolist() for _ in range(batch)]
+    front.engine_start()
+    ids = [front.engine_add_request(p, new_tokens) for p in prompts]
+    eng = front._eng()
+    # prefill and the first decode steps (graph capture) are outside the timed region
+    while any(r.num_cached < prompt_len for r in eng.scheduler.requests.values()):
+        front.engine_step()
+    for _ in range(4):
+        front.engine_step()
+    done_before = sum(len(front.engine_get_output(i)) for i in ids)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n = 0
+    while front.engine_has_unfinished() and n < steps:
+        front.engine_step()
+        n += 1
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    outs = [front.engine_get_output(i) for i in ids]
+    produced = sum(len(o) for o in outs) - done_before
+    h2d = eng.runner._graphs[eng.runner._bucket(batch)].meta_buf.numel() * 4
+    front.engine_stop()
+    return dict(value=produced / dt, steps=n, h2d=h2d, d2h=4 * batch)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
+    ap.add_argument("--skip-points", action="store_true")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "LitInfer installs offline only as its Python layer (its native library needs xmake, which is absent) "
+                          "and it has no GPU path; its CPU engine cannot run this configuration in bounded time"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+
+    from litinfer_b200 import kernels
+    from litinfer_b200.config import config_from_dict
+    from litinfer_b200.models import DecoderModel
+
+    cfg = bench_config()
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    peaks = load_peaks()
+    spec = config_from_dict(cfg).to_model_spec()
+    model = DecoderModel.from_random(spec, 0, "bfloat16", "cuda:0")
+    wbytes = weight_bytes(model)
+    kv_per_token = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+    clocks = ClockSampler()
+    clocks.start()
+    main_run = time_decode(model, args.batch, args.context, args.steps, warmup)
+    clock_info = clocks.stop()
+
+    step_bytes = wbytes + args.batch * main_run["mean_ctx"] * kv_per_token
+    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    prefill_tokens = 2048
+    pf_ms = time_prefill(model, prefill_tokens)
+    pf_flops = decode_flops_and_prefill_flops(cfg, prefill_tokens)
+    points = {}
+    if not args.skip_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = round(time_decode(model, b, args.context, min(args.steps, 64), warmup)["tok_s"], 1)
+    e2e = time_e2e(model, cfg, args.batch, args.context, 256, args.steps)
+
+    line = {
+        "metric": "decode tok/s @ batch 8 (1.5B shape, context 2048+)",
+        "value": round(main_run["tok_s"], 1),
+        "unit": "tokens/s",
+        "n_gpus": 1,
+        "steps": args.steps,
+        "warmup": warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "bf16",
+        "data": "synthetic: random-init weights N(0, 0.02), random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "DeepSeek-R1-Distill-Qwen-1.5B shape (Qwen2)", "layers": full_layers, "layers_run": cfg["num_hidden_layers"],
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "global_batch": args.batch, "seq_len": args.context, "new_tokens": args.steps + warmup, "context_cap": 4096,
+            "page_size": 16, "parallelism": "single GPU", "cache_refresh": "inputs larger than L2 (3 GB of weights per step)",
+            "peaks": peaks["source"],
+        },
+        "e2e": {"value": round(e2e["value"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                "steps": e2e["steps"]},
+        "gpu_launches": int(main_run["launches_per_step"] * args.steps),
+        "clocks": clock_info,
+        "prefill": {"value": round(prefill_tokens / (pf_ms / 1e3), 1), "tokens": prefill_tokens, "ms": round(pf_ms, 3),
+                    "frac": round(pf_flops / (pf_ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4)},
+        "points": points,
+        "kernel_library": kernels.library_file(),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -2,8 +2,10 @@
 
 Schedule entries whose mixers ask for the same :class:`PagedKV` (key heads,
 head size, window) form a *group*.  A group has one page-id space, one pool,
-one device tensor ``[entries, 2 (k|v), pages + 1, kv_heads, page_size, head_dim]``
-and, per request, one block table that is valid for all of its entries.
+one device tensor ``[entries, 2 (k|v), pages + 1, kv_heads, page_size * head_dim]``
+(keys of a page as ``[page_size, head_dim]``, values transposed as
+``[head_dim, page_size]``: the layout the attention kernels read without
+staging) and, per request, one block table that is valid for all of its entries.
 LitInfer has one pool, free list and block table per layer
 (src/llaisys/models/qwen2.hpp:76-79), all identical in practice.
 
@@ -38,7 +40,7 @@ class EntryCache:
     writes: bool = True
     group: int = -1
     k: Optional[torch.Tensor] = None        # [pages + 1, kv_heads, page_size, head_dim]
-    v: Optional[torch.Tensor] = None
+    v: Optional[torch.Tensor] = None        # [pages + 1, kv_heads, head_dim, page_size]
     state: Optional[torch.Tensor] = None    # [max_requests + 1, *shape]
 
 
@@ -90,7 +92,7 @@ class CacheManager:
                 self.groups[by_key[req]].entries.append(i)
         for g in self.groups:
             if allocate:
-                g.kv = torch.zeros((len(g.entries), 2, self.num_pages + 1, g.key.num_kv_heads, self.page_size, g.key.head_dim),
+                g.kv = torch.zeros((len(g.entries), 2, self.num_pages + 1, g.key.num_kv_heads, self.page_size * g.key.head_dim),
                                    dtype=dtype, device=self.device)
         for i, req in enumerate(requirements):
             src = cache_from[i]
@@ -101,8 +103,9 @@ class CacheManager:
                 gid = by_key[req]
                 g = self.groups[gid]
                 j = g.entries.index(i)
-                k = g.kv[j, 0] if g.kv is not None else None
-                v = g.kv[j, 1] if g.kv is not None else None
+                shape = (self.num_pages + 1, g.key.num_kv_heads)
+                k = g.kv[j, 0].view(*shape, self.page_size, g.key.head_dim) if g.kv is not None else None
+                v = g.kv[j, 1].view(*shape, g.key.head_dim, self.page_size) if g.kv is not None else None
                 self.entries.append(EntryCache("paged", True, gid, k, v))
             elif isinstance(req, FixedState):
                 st = torch.zeros((self.max_requests + 1,) + tuple(req.shape), dtype=req.dtype, device=self.device) if allocate else None

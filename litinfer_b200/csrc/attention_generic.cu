@@ -13,8 +13,9 @@
 // the keys and of the lanes' partial sums is fixed, so a token's output does
 // not depend on what else is in the batch or on how its sequence was cut.
 //
-// Cache layout: [page][kv_head][offset][head_dim]; page of key t of sequence s
-// is block_table[s][t / page_size].  Any head_dim up to 512.
+// Cache layout: keys [page][kv_head][offset][head_dim], values transposed
+// [page][kv_head][head_dim][offset]; the page of key t of sequence s is
+// block_table[s][t / page_size].  Any head_dim up to 512.
 #include "common.cuh"
 
 namespace {
@@ -53,7 +54,9 @@ attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T
         const int lb = key / page_size;
         int page = bt[lb];
         if (page < 0 || page >= num_pages) page = 0;      // host-validated; keep the read inside the cache
-        const size_t base = (((size_t)page * nkv + kvh) * page_size + (key - lb * page_size)) * dh;
+        const int off = key - lb * page_size;
+        const size_t base = (((size_t)page * nkv + kvh) * page_size + off) * dh;
+        const size_t vbase = ((size_t)page * nkv + kvh) * dh * page_size + off;
         float dot = 0.0f;
 #pragma unroll
         for (int i = 0; i < kMaxPerLane; ++i) {
@@ -68,7 +71,7 @@ attention_generic_kernel(const T* __restrict__ qkv, T* __restrict__ out, const T
 #pragma unroll
         for (int i = 0; i < kMaxPerLane; ++i) {
             const int d = lane + 32 * i;
-            if (i < per && d < dh) acc[i] = acc[i] * alpha + e * to_float(vcache[base + d]);
+            if (i < per && d < dh) acc[i] = acc[i] * alpha + e * to_float(vcache[vbase + (size_t)d * page_size]);
         }
         m = mn;
     }

@@ -1,4 +1,206 @@
+// out[M, N] = a[M, K] w[N, K]^T (+ bias) in bfloat16 for few rows of a
+// (decode: M = number of sequences): a kernel that is bound by reading every
+// weight once from HBM.
+//
+// Swap of the usual roles: 16 rows of the weight matrix are the M side of a
+// tensor-core tile (mma.sync m16n8k16, bfloat16 in, float accumulate), the
+// tokens are its N side (8 per tile, up to 8 tiles).  Both operands are read
+// with 16-byte loads straight from global memory into fragment registers: the
+// sum over k does not care about the order of k, so the 8 consecutive
+// elements a thread loads are taken as the k-pairs the fragment layout wants,
+// the same permutation on both operands.  Weights stream past L1 (ld.global.cs);
+// the activations (a few KB) stay in L1.
+//
+// A CTA of 4 warps owns 16 weight rows and a range of k; each warp a
+// contiguous sub-range.  Warps are summed through shared memory in fixed
+// order.  When 16-row tiles alone do not fill the GPU, k is split over
+// several CTAs (split count depends on N and K only, never on M): each writes
+// float partial sums to a workspace, and the CTA that arrives last (a counter
+// per tile) adds them in split order.  A token's result therefore does not
+// depend on how many other tokens are in the batch.
+//
+// Requires K % 8 == 0 and 16-byte aligned operands; M <= 64.
 #include "common.cuh"
-bool li_gemv_bf16_accepts(int M, int N, int K) { return false; }
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kMaxM = 64;
+constexpr size_t kWorkspaceFloats = 4u << 20;     // 16 MB of partial sums
+constexpr int kMaxTiles = 1 << 16;
+
+struct Workspace {
+    float* partial = nullptr;
+    unsigned* counters = nullptr;
+};
+Workspace g_ws[16];
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cs.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ uint4 ld_cached(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int NT, typename Tout>
+__global__ void __launch_bounds__(kWarps * 32)
+gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias, Tout* __restrict__ out,
+                 float* __restrict__ partial, unsigned* __restrict__ counters, int M, int N, int K, int ksplit) {
+    __shared__ float red[kWarps][NT * 128];
+    __shared__ int is_last;
+    const int tile = blockIdx.x, split = blockIdx.y;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = tile * 16;
+    const int chunks = (K + 31) >> 5;
+    const int c_begin = (int)((long long)split * chunks / ksplit), c_end = (int)((long long)(split + 1) * chunks / ksplit);
+    const int span = c_end - c_begin;
+    const int wb = c_begin + (int)((long long)warp * span / kWarps), we = c_begin + (int)((long long)(warp + 1) * span / kWarps);
+
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
+
+    const int r0 = n0 + g, r1 = n0 + g + 8;
+    const bool v0 = r0 < N, v1 = r1 < N;
+    const bf16* w0 = W + (size_t)(v0 ? r0 : 0) * K;
+    const bf16* w1 = W + (size_t)(v1 ? r1 : 0) * K;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+
+    constexpr int U = 4;
+    for (int c = wb; c < we; c += U) {
+        uint4 a[U], b[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = ((c + u) << 5) + t * 8;
+            const bool ok = (c + u) < we && k < K;
+            a[u] = (ok && v0) ? ld_stream(w0 + k) : zero;
+            b[u] = (ok && v1) ? ld_stream(w1 + k) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int k = ((c + u) << 5) + t * 8;
+            const bool ok = (c + u) < we && k < K;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const int tok = j * 8 + g;
+                const uint4 x = (ok && tok < M) ? ld_cached(X + (size_t)tok * K + k) : zero;
+                mma_bf16(acc[j], a[u].x, b[u].x, a[u].y, b[u].y, x.x, x.y);
+                mma_bf16(acc[j], a[u].z, b[u].z, a[u].w, b[u].w, x.z, x.w);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) red[warp][(j * 4 + i) * 32 + lane] = acc[j][i];
+    __syncthreads();
+
+    // element e = (j * 4 + i) * 32 + lane  ->  weight row n0 + g + 8 * (i >> 1), token j * 8 + 2 t + (i & 1)
+    const size_t pbase = ((size_t)split * gridDim.x + tile) * (NT * 128);
+    for (int e = threadIdx.x; e < NT * 128; e += kWarps * 32) {
+        float v = red[0][e];
+#pragma unroll
+        for (int w = 1; w < kWarps; ++w) v += red[w][e];
+        if (ksplit == 1) {
+            const int l = e & 31, ji = e >> 5, i = ji & 3, j = ji >> 2;
+            const int row = n0 + (l >> 2) + ((i >> 1) << 3), tok = j * 8 + ((l & 3) << 1) + (i & 1);
+            if (row < N && tok < M) out[(size_t)tok * N + row] = from_float<Tout>(bias ? v + bias[row] : v);
+        } else {
+            partial[pbase + e] = v;
+        }
+    }
+    if (ksplit == 1) return;
+
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(&counters[tile], 1u);
+        is_last = (prev == (unsigned)(ksplit - 1));
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int e = threadIdx.x; e < NT * 128; e += kWarps * 32) {
+        float v = 0.0f;
+        for (int s = 0; s < ksplit; ++s) v += __ldcg(&partial[((size_t)s * gridDim.x + tile) * (NT * 128) + e]);
+        const int l = e & 31, ji = e >> 5, i = ji & 3, j = ji >> 2;
+        const int row = n0 + (l >> 2) + ((i >> 1) << 3), tok = j * 8 + ((l & 3) << 1) + (i & 1);
+        if (row < N && tok < M) out[(size_t)tok * N + row] = from_float<Tout>(bias ? v + bias[row] : v);
+    }
+    if (threadIdx.x == 0) counters[tile] = 0;          // ready for the next launch on this stream
+}
+
+int ensure_workspace(Workspace** ws) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return li_fail("linear (gemv): cudaGetDevice: %s", cudaGetErrorString(e));
+    LI_REQUIRE(dev >= 0 && dev < 16, "linear (gemv): device index %d out of range", dev);
+    Workspace& w = g_ws[dev];
+    if (!w.partial) {
+        // first call on this device; must happen outside stream capture
+        e = cudaMalloc(&w.partial, kWorkspaceFloats * sizeof(float));
+        if (e != cudaSuccess) return li_fail("linear (gemv): cannot allocate the split-k workspace: %s", cudaGetErrorString(e));
+        e = cudaMalloc(&w.counters, kMaxTiles * sizeof(unsigned));
+        if (e == cudaSuccess) e = cudaMemset(w.counters, 0, kMaxTiles * sizeof(unsigned));
+        if (e != cudaSuccess) return li_fail("linear (gemv): cannot allocate the tile counters: %s", cudaGetErrorString(e));
+    }
+    *ws = &w;
+    return 0;
+}
+
+int choose_ksplit(int ntiles, int K, int nt) {
+    const int chunks = (K + 31) / 32;
+    int ksplit = 1;
+    if (ntiles < 296) {
+        ksplit = ceil_div(296, ntiles);
+        const int by_work = chunks / 16 > 0 ? chunks / 16 : 1;        // at least 512 k per split
+        if (ksplit > by_work) ksplit = by_work;
+    }
+    while (ksplit > 1 && (size_t)ksplit * ntiles * nt * 128 > kWorkspaceFloats) --ksplit;
+    return ksplit;
+}
+
+template <int NT, typename Tout>
+int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
+    const int ntiles = ceil_div(N, 16);
+    const int ksplit = choose_ksplit(ntiles, K, NT);
+    Workspace* ws = nullptr;
+    if (int rc = ensure_workspace(&ws)) return rc;
+    LI_REQUIRE(ntiles <= kMaxTiles || ksplit == 1, "linear (gemv): N=%d has too many tiles for split-k", N);
+    dim3 grid(ntiles, ksplit);
+    gemv_bf16_kernel<NT, Tout><<<grid, kWarps * 32, 0, stream>>>((const bf16*)a, (const bf16*)w, bias, (Tout*)out, ws->partial,
+                                                                 ws->counters, M, N, K, ksplit);
+    return li_check_launch("linear (gemv)");
+}
+
+template <typename Tout>
+int launch_nt(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
+    if (M <= 8) return launch<1, Tout>(a, w, bias, out, M, N, K, stream);
+    if (M <= 16) return launch<2, Tout>(a, w, bias, out, M, N, K, stream);
+    if (M <= 32) return launch<4, Tout>(a, w, bias, out, M, N, K, stream);
+    return launch<8, Tout>(a, w, bias, out, M, N, K, stream);
+}
+
+}  // namespace
+
+bool li_gemv_bf16_accepts(int M, int N, int K) { return M >= 1 && M <= kMaxM && K % 8 == 0 && N >= 1; }
+
 int li_linear_gemv_bf16(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
-                        cudaStream_t stream) { return li_fail("not built"); }
+                        cudaStream_t stream) {
+    LI_REQUIRE(li_gemv_bf16_accepts(M, N, K), "linear (gemv): refuses M=%d N=%d K=%d (M <= %d, K a multiple of 8)", M, N, K, kMaxM);
+    LI_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear (gemv): operands must be 16-byte aligned");
+    if (dtype_out == LI_BF16) return launch_nt<bf16>(a, w, bias, out, M, N, K, stream);
+    if (dtype_out == LI_F32) return launch_nt<float>(a, w, bias, out, M, N, K, stream);
+    return li_fail("linear (gemv): unsupported output dtype %d", dtype_out);
+}

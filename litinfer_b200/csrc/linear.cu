@@ -23,7 +23,8 @@ LI_EXPORT int li_linear(const void* a, const void* w, const float* bias, void* o
     LI_REQUIRE(M >= 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
     if (M == 0) return 0;
     if (dtype_in == LI_BF16) {
-        if (li_gemv_bf16_accepts(M, N, K)) return li_linear_gemv_bf16(a, w, bias, out, dtype_out, M, N, K, stream);
+        const bool aligned = ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
+        if (aligned && li_gemv_bf16_accepts(M, N, K)) return li_linear_gemv_bf16(a, w, bias, out, dtype_out, M, N, K, stream);
         if (li_tcgen05_accepts(a, w, out, dtype_out, M, N, K)) return li_linear_tcgen05(a, w, bias, out, dtype_out, M, N, K, stream);
     }
     return li_linear_simt(a, w, bias, out, dtype_in, dtype_out, M, N, K, stream);

@@ -6,8 +6,11 @@
 // (a, b) = (x[j], x[j + rotary_dim/2]), x'[j] = a cos - b sin,
 // x'[j + rotary_dim/2] = b cos + a sin, in float with sincosf.  q is rotated in
 // place inside the fused qkv row; k is rotated and stored, v stored as is, at
-// the token's slot: cache[page][kv_head][offset][:] with page = slot / page_size
-// (LitInfer caches k after rotation as well, src/llaisys/models/qwen2.cpp:626-673).
+// the token's slot (page = slot / page_size, offset = slot % page_size):
+// keys as kcache[page][kv_head][offset][:], values transposed as
+// vcache[page][kv_head][:][offset], which is how the tensor-core attention
+// kernels want to read them (LitInfer caches k after rotation as well,
+// src/llaisys/models/qwen2.cpp:626-673).
 #include "common.cuh"
 
 namespace {
@@ -57,7 +60,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict_
             }
         }
         kcache[dst] = from_float<T>(kv);
-        vcache[dst] = v[i];
+        vcache[((((size_t)page * nkv + h) * dh + d) * page_size) + off] = v[i];      // values are cached transposed
     }
 }
 

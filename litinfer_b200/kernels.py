@@ -178,7 +178,8 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torc
                   slot_mapping: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                   num_heads: int, num_kv_heads: int, head_dim: int, write: bool = True) -> None:
     """Rotate q (in place in ``qkv``) and k; store rotated k and plain v at each
-    token's slot of the caches ``[pages, kv_heads, page_size, head_dim]``.
+    token's slot of the caches: keys ``[pages, kv_heads, page_size, head_dim]``, values
+    transposed ``[pages, kv_heads, head_dim, page_size]``.
     With ``write`` false only q is rotated."""
     T = qkv.shape[0]
     _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
@@ -186,8 +187,8 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torc
     _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
     _need(slot_mapping, "slot mapping", torch.int32, (T,))
     _need(k_cache, "key cache", qkv.dtype)
-    _need(v_cache, "value cache", qkv.dtype, k_cache.shape)
     pages, nkv, page_size, dh = k_cache.shape
+    _need(v_cache, "value cache", qkv.dtype, (pages, nkv, dh, page_size))
     if nkv != num_kv_heads or dh != head_dim:
         raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
     _check(library().li_rope_kv_write(
@@ -216,7 +217,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
     _need(out, "attention output", qkv.dtype, (T, num_heads * head_dim))
     _need(k_cache, "key cache", qkv.dtype)
-    _need(v_cache, "value cache", qkv.dtype, k_cache.shape)
+    _need(v_cache, "value cache", qkv.dtype, (k_cache.shape[0], k_cache.shape[1], k_cache.shape[3], k_cache.shape[2]))
     _need(block_table, "block table", torch.int32)
     _need(q_start, "q_start", torch.int32, (S + 1,))
     _need(ctx_lens, "ctx_lens", torch.int32, (S,))

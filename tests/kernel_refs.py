@@ -79,7 +79,7 @@ def rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cach
     page = (slot_mapping // page_size).long()
     off = (slot_mapping % page_size).long()
     k_cache[page, :, off] = k
-    v_cache[page, :, off] = v
+    v_cache[page, :, :, off] = v         # values are cached transposed: [page, kv_head, head_dim, slot]
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
@@ -98,7 +98,7 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, 
         pages = block_table[s].long()[keys // page_size]
         offs = keys % page_size
         k = k_cache[pages, :, offs].float()          # [n, kv_heads, dh]
-        v = v_cache[pages, :, offs].float()
+        v = v_cache[pages, :, :, offs].float()
         for h in range(num_heads):
             sc = (k[:, h // group] @ q[t, h]) * scale
             pr = torch.softmax(sc, dim=0)

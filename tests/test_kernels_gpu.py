@@ -113,6 +113,52 @@ def test_linear(dtype, shape):
             close(out, ref, out_dtype, f"linear {shape} bias={bias is not None} out={out_dtype}", f32_tol=1e-5 * math.sqrt(Kd))
 
 
+GEMV_SHAPES = [(1, 64, 64), (8, 2048, 1536), (5, 100, 72), (16, 1536, 8960), (9, 389, 96), (33, 1000, 272), (64, 1536, 1536),
+               (3, 17920, 1536), (2, 151936, 1536), (40, 30, 40)]
+
+
+@pytest.mark.parametrize("shape", GEMV_SHAPES)
+def test_linear_weight_streaming_kernel(shape):
+    M, N, Kd = shape
+    a = rnd(M, Kd, dtype=torch.bfloat16, seed=16)
+    w = rnd(N, Kd, dtype=torch.bfloat16, seed=17, scale=0.05)
+    b = rnd(N, seed=18)
+    for bias in (None, b):
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.empty(M, N, dtype=out_dtype, device=dev())
+            ref = torch.empty_like(out)
+            K().linear_with("gemv", a, w, bias, out)
+            R.linear(a, w, bias, ref)
+            close(out, ref, out_dtype, f"gemv {shape} bias={bias is not None} out={out_dtype}", f32_tol=1e-5 * math.sqrt(Kd))
+    # a token's result does not depend on the batch it is in, nor on the call (split-k partial sums are added in fixed order)
+    full = torch.empty(M, N, dtype=torch.float32, device=dev())
+    K().linear_with("gemv", a, w, None, full)
+    one = torch.empty(1, N, dtype=torch.float32, device=dev())
+    K().linear_with("gemv", a[M - 1:M].contiguous(), w, None, one)
+    assert torch.equal(one[0], full[M - 1])
+
+
+TC_SHAPES = [(128, 128, 64), (128, 128, 512), (256, 384, 1536), (2048, 2048, 1536), (17, 100, 72), (130, 200, 272), (300, 136, 40),
+             (1000, 389, 96), (64, 1536, 8960), (2048, 1536, 8960), (5, 151936, 1536)]
+
+
+@pytest.mark.parametrize("shape", TC_SHAPES)
+def test_linear_tcgen05_kernel(shape):
+    M, N, Kd = shape
+    a = rnd(M, Kd, dtype=torch.bfloat16, seed=26)
+    w = rnd(N, Kd, dtype=torch.bfloat16, seed=27, scale=0.05)
+    b = rnd(N, seed=28)
+    for bias in (None, b):
+        for out_dtype in (torch.bfloat16, torch.float32):
+            out = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev())
+            ref = torch.empty_like(out)
+            K().linear_with("tcgen05", a, w, bias, out)
+            torch.cuda.synchronize()
+            assert K().library().li_tcgen05_status() == 0, "a wait inside the kernel ran out"
+            R.linear(a, w, bias, ref)
+            close(out, ref, out_dtype, f"tcgen05 {shape} bias={bias is not None} out={out_dtype}", f32_tol=1e-5 * math.sqrt(Kd))
+
+
 @pytest.mark.parametrize("shape", LINEAR_SHAPES)
 def test_linear_simt_rows_do_not_depend_on_batch(shape):
     """float32: a row's result is the same bits whether it runs alone or among others."""
@@ -138,7 +184,7 @@ def test_rope_kv_write(dtype, cfg):
     g = torch.Generator().manual_seed(10)
     slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32).to(dev())
     kc = torch.zeros(pages, nkv, page, dh, dtype=dtype, device=dev())
-    vc = torch.zeros_like(kc)
+    vc = torch.zeros(pages, nkv, dh, page, dtype=dtype, device=dev())
     kc2, vc2, qkv2 = kc.clone(), vc.clone(), qkv.clone()
     K().rope_kv_write(qkv, positions, denom, rot, slots, kc, vc, nh, nkv, dh, True)
     R.rope_kv_write(qkv2, positions, denom, rot, slots, kc2, vc2, nh, nkv, dh, True)
@@ -189,12 +235,12 @@ def run_attention_case(c, window, implementation=None):
     d = dev()
     page, nkv, dh = c["page"], c["nkv"], c["dh"]
     kc = torch.zeros(c["pages"], nkv, page, dh, dtype=c["dtype"])
-    vc = torch.zeros_like(kc)
+    vc = torch.zeros(c["pages"], nkv, dh, page, dtype=c["dtype"])
     for s in range(c["S"]):
         for t in range(c["ctx_lens"][s]):
             p = int(c["bt"][s, t // page])
             kc[p, :, t % page] = c["keys"][s][t]
-            vc[p, :, t % page] = c["vals"][s][t]
+            vc[p, :, :, t % page] = c["vals"][s][t]
     args = dict(
         qkv=c["qkv"].to(d), k_cache=kc.to(d), v_cache=vc.to(d), block_table=c["bt"].to(d),
         q_start=torch.tensor(c["q_start"], dtype=torch.int32, device=d), ctx_lens=torch.tensor(c["ctx_lens"], dtype=torch.int32, device=d),
@@ -236,6 +282,26 @@ def test_attention_decode_batch(dtype, heads):
     close(out, ref, dtype, f"decode attention heads={heads}")
     out, ref = run_attention_case(c, 100)
     close(out, ref, dtype, f"decode attention heads={heads} window=100")
+
+
+@pytest.mark.parametrize("heads", [(4, 2, 16), (3, 1, 32), (6, 2, 48), (12, 2, 128), (8, 8, 64), (14, 2, 80), (16, 1, 96), (28, 4, 128)])
+@pytest.mark.parametrize("page", [16, 64])
+def test_attention_decode_kernel_alone(heads, page):
+    nh, nkv, dh = heads
+    ctx_lens = [1, 16, 17, 300, 777, 64, 255, 256, 257, 1025]
+    c = make_attention_case([1] * len(ctx_lens), ctx_lens, nh, nkv, dh, page, torch.bfloat16, seed=31)
+    for window in (None, 100, 300):
+        out, ref = run_attention_case(c, window, implementation="decode")
+        close(out, ref, torch.bfloat16, f"decode kernel heads={heads} page={page} window={window}")
+    # alone or in the batch: the same bits
+    out_all, _ = run_attention_case(c, None, implementation="decode")
+    c1 = make_attention_case([1] * len(ctx_lens), ctx_lens, nh, nkv, dh, page, torch.bfloat16, seed=31)
+    for key in ("q_lens", "ctx_lens"):
+        c1[key] = c1[key][4:5]
+    c1.update(S=1, T=1, bt=c1["bt"][4:5], qkv=c1["qkv"][4:5], keys=c1["keys"][4:5], vals=c1["vals"][4:5], q_start=[0, 1], seq_of=[0],
+              pos=[ctx_lens[4] - 1])
+    out_one, _ = run_attention_case(c1, None, implementation="decode")
+    assert torch.equal(out_one[0], out_all[4])
 
 
 def _plant(c, s, h_kv, key_pos, q_token, strength=30.0):
