@@ -159,7 +159,7 @@ def make_decode_state(model, batch, context, steps_total, seed=0):
     return manager, runner, reqs
 
 
-def time_decode(model, batch, context, steps, warmup):
+def time_decode(model, batch, context, steps, warmup, graphs=True):
     """Device time of exactly ``steps`` decode steps (tokens per second, ms per step,
     launches per step, mean context)."""
     import numpy as np
@@ -174,6 +174,24 @@ def time_decode(model, batch, context, steps, warmup):
     vocab = model.spec.vocab_size
     g = torch.Generator().manual_seed(1)
     toks = torch.randint(0, vocab, (total + 1, batch), generator=g).tolist()
+    if not graphs:
+        # every kernel launched from the host, one by one: what a profiler can list
+        runner.use_graphs = False
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = 0
+        for k in range(total):
+            if k == warmup:
+                torch.cuda.synchronize()
+                before = kernels.launches
+                start.record()
+            for rc in reqs:
+                manager.extend(rc, rc.length + 1)
+            runner.step([StepItem(rc, [toks[k][b]], (0,)) for b, rc in enumerate(reqs)])
+        stop.record()
+        torch.cuda.synchronize()
+        ms = start.elapsed_time(stop)
+        return dict(tok_s=batch * steps / (ms / 1e3), ms_per_step=ms / steps, launches_per_step=(kernels.launches - before) // steps,
+                    mean_ctx=context + warmup + (steps + 1) / 2)
     # first step through the ordinary path: captures the graph for this batch size
     for rc in reqs:
         manager.extend(rc, rc.length + 1)
@@ -289,6 +307,10 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
+                    help="measure one part and print a short line (for profiling runs)")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (so that a profiler lists them)")
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -316,6 +338,18 @@ def main() -> int:
     model = DecoderModel.from_random(spec, 0, "bfloat16", "cuda:0")
     wbytes = weight_bytes(model)
     kv_per_token = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+
+    if args.only == "decode":
+        r = time_decode(model, args.batch, args.context, args.steps, warmup, graphs=not args.no_graphs)
+        print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context, "layers_run": cfg["num_hidden_layers"],
+                          "graphs": not args.no_graphs, **{k: round(v, 4) for k, v in r.items()}}))
+        return 0
+    if args.only == "prefill":
+        ms = time_prefill(model, args.prefill_tokens)
+        fl = decode_flops_and_prefill_flops(cfg, args.prefill_tokens)
+        print(json.dumps({"only": "prefill", "tokens": args.prefill_tokens, "layers_run": cfg["num_hidden_layers"], "ms": round(ms, 3),
+                          "tok_s": round(args.prefill_tokens / ms * 1e3, 1), "frac": round(fl / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}))
+        return 0
 
     clocks = ClockSampler()
     clocks.start()

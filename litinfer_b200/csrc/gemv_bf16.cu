@@ -28,6 +28,7 @@ constexpr int kWarps = 4;
 constexpr int kMaxM = 64;
 constexpr size_t kWorkspaceFloats = 4u << 20;     // 16 MB of partial sums
 constexpr int kMaxTiles = 1 << 16;
+constexpr int kTargetCtas = 1480;                 // about ten CTAs a multiprocessor keep enough loads in flight
 
 struct Workspace {
     float* partial = nullptr;
@@ -162,8 +163,8 @@ int ensure_workspace(Workspace** ws) {
 int choose_ksplit(int ntiles, int K, int nt) {
     const int chunks = (K + 31) / 32;
     int ksplit = 1;
-    if (ntiles < 296) {
-        ksplit = ceil_div(296, ntiles);
+    if (ntiles < kTargetCtas) {
+        ksplit = ceil_div(kTargetCtas, ntiles);
         const int by_work = chunks / 16 > 0 ? chunks / 16 : 1;        // at least 512 k per split
         if (ksplit > by_work) ksplit = by_work;
     }

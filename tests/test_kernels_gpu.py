@@ -304,6 +304,19 @@ def test_attention_decode_kernel_alone(heads, page):
     assert torch.equal(out_one[0], out_all[4])
 
 
+@pytest.mark.parametrize("heads", [(4, 2, 16), (3, 1, 32), (6, 2, 48), (12, 2, 128), (8, 8, 64), (14, 2, 80), (28, 4, 128)])
+@pytest.mark.parametrize("page", [16, 32])
+def test_attention_prefill_kernel_alone(heads, page):
+    nh, nkv, dh = heads
+    # whole prompts (one longer than a 64-token tile, one of 64 exactly), portions with history, single tokens, two tokens
+    q_lens = [37, 20, 1, 150, 2, 1, 64, 17]
+    ctx_lens = [37, 75, 33, 150, 130, 1, 64, 300]
+    c = make_attention_case(q_lens, ctx_lens, nh, nkv, dh, page, torch.bfloat16, seed=41)
+    for window in (None, 24, 100):
+        out, ref = run_attention_case(c, window, implementation="prefill")
+        close(out, ref, torch.bfloat16, f"prefill kernel heads={heads} page={page} window={window}")
+
+
 def _plant(c, s, h_kv, key_pos, q_token, strength=30.0):
     """Make key ``key_pos`` of sequence s point along the query of ``q_token`` (all heads
     of that key head), so that it takes nearly all the softmax weight if it is visible."""
