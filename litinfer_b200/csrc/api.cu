@@ -2,6 +2,7 @@
 // was built for.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <cstring>
 
 namespace {
@@ -20,6 +21,14 @@ int li_check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) return 0;
     return li_fail("%s: launch failed: %s", what, cudaGetErrorString(e));
+}
+
+bool li_pdl_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("LITINFER_B200_PDL");
+        return !(v && v[0] == '0');
+    }();
+    return on;
 }
 
 LI_EXPORT const char* li_last_error() { return g_error; }

@@ -1,8 +1,9 @@
 // Decode attention in bfloat16: one new token per sequence over its paged
 // cache, grouped-query, split along the context.
 //
-// Grid (split, kv head, sequence).  A CTA of 8 warps covers 256 keys at fixed
-// absolute positions [256 s, 256 s + 256), each warp 32 of them, for all query
+// Grid (split, kv head, sequence).  A CTA of 8 warps covers 128 keys at fixed
+// absolute positions [128 s, 128 s + 128), each warp 16 of them (all its loads
+// are in flight at once: one round trip to memory), for all query
 // heads of one key/value head at once (they share every K and V byte read;
 // heads are the 16 rows of a tensor-core tile).  Per 16 keys a warp computes
 // S = Q K^T and O += P V with mma.sync m16n8k16 (bfloat16 in, float
@@ -16,8 +17,9 @@
 //     one output column the 4 consecutive keys a thread needs are contiguous;
 //     the score tiles are computed with their key columns permuted to match
 //     (tile 0: keys 0,1,4,5,8,9,12,13 of the 16; tile 1: the others).
-// Warps are merged through shared memory, CTAs through a float workspace and a
-// small second kernel, both in fixed order: split boundaries depend on
+// Warps are merged through shared memory, CTAs through a float workspace by the
+// CTA that finishes last (a counter per sequence and kv head), both in fixed
+// order: split boundaries depend on
 // absolute key positions only, so a sequence's result does not depend on the
 // batch it is in.  Window: keys below p - window + 1 are masked, splits wholly
 // below it are skipped.
@@ -28,13 +30,15 @@
 
 namespace {
 
-constexpr int kSplit = 256;
+constexpr int kSplit = 128;
 constexpr int kWarps = 8;
 
 struct Workspace {
     float* buf = nullptr;
     size_t floats = 0;
+    unsigned* counters = nullptr;
 };
+constexpr size_t kCounters = 1u << 20;
 Workspace g_ws[16];
 
 using namespace attn;
@@ -47,12 +51,15 @@ __host__ __device__ inline void split_range(int ctx, int window, int* first, int
 }
 
 template <int DH>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
-                        float* __restrict__ part, int nh, int nkv, int page_size, int num_pages, float scale, int window,
-                        int nsplit) {
+                        float* __restrict__ part, unsigned* __restrict__ counters, bf16* __restrict__ out, int nh, int nkv,
+                        int page_size, int num_pages, float scale, int window, int nsplit) {
     extern __shared__ float sm[];
+    __shared__ int is_last;
+    pdl_launch_dependents();
+    pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
     const int ctx = ctx_lens[s];
     const int p = ctx - 1;
@@ -71,17 +78,19 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     st.init();
     const int lo2[2] = {lo, lo}, hi2[2] = {k_end - 1, k_end - 1};
     const int* bt = block_table + (size_t)s * max_blocks;
-    constexpr int kBlocksPerWarp = kSplit / 16 / kWarps;
-#pragma unroll 1
-    for (int b = 0; b < kBlocksPerWarp; ++b) {
-        const int key0 = k_begin + (warp * kBlocksPerWarp + b) * 16;
-        if (key0 >= k_end || key0 + 16 <= lo) continue;       // warp-uniform
-        int page = bt[key0 / page_size];
-        if (page < 0 || page >= num_pages) page = 0;
-        const int off = key0 % page_size;
-        const bf16* kbase = kcache + (((size_t)page * nkv + kvh) * page_size + off) * DH;
-        const bf16* vbase = vcache + ((size_t)page * nkv + kvh) * DH * page_size + off;
-        block16<DH, true>(st, qa, kbase, vbase, page_size, key0, lo2, hi2, scale, g, t);
+    static_assert(kSplit == 16 * kWarps, "one block of 16 keys per warp: one round trip to memory");
+    {
+        const int key0 = k_begin + warp * 16;
+        if (key0 < k_end && key0 + 16 > lo) {                  // warp-uniform
+            int page = bt[key0 / page_size];
+            if (page < 0 || page >= num_pages) page = 0;
+            const int off = key0 % page_size;
+            KFrag<DH> kf;
+            VFrag<DH> vf;
+            load_k<DH, true>(kf, kcache + (((size_t)page * nkv + kvh) * page_size + off) * DH, g, t);
+            load_v<DH, true>(vf, vcache + ((size_t)page * nkv + kvh) * DH * page_size + off, page_size, g, t);
+            compute16<DH>(st, qa, kf, vf, key0, lo2, hi2, scale, t);
+        }
     }
     const float m0 = st.m[0], m1 = st.m[1];
     const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
@@ -129,30 +138,61 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
             dst[DH + 1] = L;
         }
     }
-}
-
-template <int DH>
-__global__ void decode_combine_kernel(const float* __restrict__ part, const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nh,
-                                      int window, int nsplit) {
-    const int s = blockIdx.x / nh, h = blockIdx.x - s * nh;
+    // the CTA that finishes last for this (sequence, kv head) merges the splits, in split order
     int first, last;
-    split_range(ctx_lens[s], window, &first, &last);
-    const float* base = part + ((size_t)s * nh + h) * nsplit * (DH + 2);
-    float M = -INFINITY;
-    for (int sp = first; sp <= last; ++sp) M = fmaxf(M, base[(size_t)sp * (DH + 2) + DH]);
-    for (int d = threadIdx.x; d < DH; d += blockDim.x) {
-        float O = 0.0f, L = 0.0f;
-        for (int sp = first; sp <= last; ++sp) {
-            const float* q = base + (size_t)sp * (DH + 2);
-            const float f = expf(q[DH] - M);
-            O += q[d] * f;
-            L += q[DH + 1] * f;
-        }
-        out[((size_t)s * nh + h) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+    split_range(ctx, window, &first, &last);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(&counters[s * nkv + kvh], 1u);
+        is_last = (prev == (unsigned)(last - first));
     }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    // factors exp(m_split - M) and the denominators first (one round of loads), then the sums
+    // over splits with eight loads in flight at a time
+    const int nact = last - first + 1;
+    float* f_sm = sm;                                  // [G][nact] factors; reuses the warp-merge buffer
+    float* l_sm = sm + (size_t)G * nact;               // [G] denominators
+    __syncthreads();
+    for (int r = warp; r < G; r += kWarps) {
+        const float* base = part + ((size_t)s * nh + kvh * G + r) * nsplit * (DH + 2);
+        float M = -INFINITY;
+        for (int sp = first + lane; sp <= last; sp += 32) M = fmaxf(M, __ldcg(base + (size_t)sp * (DH + 2) + DH));
+        M = warp_max(M);
+        float L = 0.0f;
+        for (int sp0 = first; sp0 <= last; sp0 += 32) {        // ascending split order within each lane
+            const int sp = sp0 + lane;
+            if (sp <= last) {
+                const float f = expf(__ldcg(base + (size_t)sp * (DH + 2) + DH) - M);
+                f_sm[r * nact + sp - first] = f;
+                L += __ldcg(base + (size_t)sp * (DH + 2) + DH + 1) * f;
+            }
+        }
+        L = warp_sum(L);
+        if (lane == 0) l_sm[r] = L;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * DH; e += kWarps * 32) {
+        const int r = e / DH, d = e - r * DH;
+        const float* base = part + ((size_t)s * nh + kvh * G + r) * nsplit * (DH + 2) + d;
+        const float* f = f_sm + r * nact;
+        float O = 0.0f;
+        for (int i = 0; i < nact; i += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = (i + u < nact) ? __ldcg(base + (size_t)(first + i + u) * (DH + 2)) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) O += (i + u < nact) ? v[u] * f[i + u] : 0.0f;
+        }
+        const float L = l_sm[r];
+        out[((size_t)s * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+    }
+    if (threadIdx.x == 0) counters[s * nkv + kvh] = 0;          // ready for the next launch on this stream
 }
 
-int ensure_workspace(size_t floats, float** buf) {
+int ensure_workspace(size_t floats, float** buf, unsigned** counters) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return li_fail("attention (decode): cudaGetDevice: %s", cudaGetErrorString(e));
@@ -171,7 +211,13 @@ int ensure_workspace(size_t floats, float** buf) {
         w.buf = nb;
         w.floats = want;
     }
+    if (!w.counters) {
+        e = cudaMalloc(&w.counters, kCounters * sizeof(unsigned));
+        if (e == cudaSuccess) e = cudaMemset(w.counters, 0, kCounters * sizeof(unsigned));
+        if (e != cudaSuccess) return li_fail("attention (decode): cannot allocate the split counters: %s", cudaGetErrorString(e));
+    }
     *buf = w.buf;
+    *counters = w.counters;
     return 0;
 }
 
@@ -182,8 +228,12 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     const int nsplit = ceil_div(max_ctx_len > 0 ? max_ctx_len : 1, kSplit);
     const int G = nh / nkv;
     float* part = nullptr;
-    if (int rc = ensure_workspace((size_t)S * nh * nsplit * (DH + 2), &part)) return rc;
-    const size_t smem = (2 * kWarps * 16 + (size_t)kWarps * G * DH) * sizeof(float);
+    unsigned* counters = nullptr;
+    if (int rc = ensure_workspace((size_t)S * nh * nsplit * (DH + 2), &part, &counters)) return rc;
+    LI_REQUIRE((size_t)S * nkv <= kCounters, "attention (decode): batch %d x %d kv heads exceeds the split counters", S, nkv);
+    size_t smem_floats = 2 * kWarps * 16 + (size_t)kWarps * G * DH;
+    if (smem_floats < (size_t)G * (nsplit + 1)) smem_floats = (size_t)G * (nsplit + 1);      // the final merge reuses the buffer
+    const size_t smem = smem_floats * sizeof(float);
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -193,12 +243,10 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     LI_REQUIRE(smem <= 200 * 1024, "attention (decode): shared memory %zu too large", smem);
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     dim3 grid(nsplit, nkv, S);
-    decode_attention_kernel<DH><<<grid, kWarps * 32, smem, stream>>>((const bf16*)qkv, (const bf16*)kcache, (const bf16*)vcache,
-                                                                      block_table, max_blocks, ctx_lens, part, nh, nkv, page_size,
-                                                                      num_pages, scale, window, nsplit);
-    if (int rc = li_check_launch("attention (decode)")) return rc;
-    decode_combine_kernel<DH><<<S * nh, DH < 32 ? 32 : (DH > 128 ? 128 : DH), 0, stream>>>(part, ctx_lens, (bf16*)out, nh, window, nsplit);
-    return li_check_launch("attention (decode combine)");
+    li_launch_pdl(decode_attention_kernel<DH>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache, (const bf16*)vcache,
+                                                                      block_table, max_blocks, ctx_lens, part, counters, (bf16*)out,
+                                                                      nh, nkv, page_size, num_pages, scale, window, nsplit);
+    return li_check_launch("attention (decode)");
 }
 
 }  // namespace

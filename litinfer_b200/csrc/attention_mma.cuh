@@ -77,26 +77,46 @@ __device__ __forceinline__ void load_q(unsigned (&qa)[DH / 16][4], const bf16* r
     }
 }
 
-// One block of 16 keys starting at absolute key position key0.  kbase: the block's first key row
-// ([16][DH], rows DH apart); vbase: the block's first slot in the transposed values ([DH][page_size]).
-// A key is visible to row r iff lo[r] <= key <= hi[r].  kStream: the cache is read once (decode).
+// Fragments of one block of 16 keys.  kbase: the block's first key row ([16][DH], rows DH
+// apart); vbase: the block's first slot in the transposed values ([DH][page_size]).
+// kStream: the cache is read once (decode) and should not displace other data.
+template <int DH>
+struct KFrag {
+    uint2 t0[DH / 16], t1[DH / 16];      // score tile 0 / tile 1
+};
+template <int DH>
+struct VFrag {
+    uint2 v[DH / 8];
+};
+
 template <int DH, bool kStream>
-__device__ __forceinline__ void block16(RowState<DH>& st, const unsigned (&qa)[DH / 16][4], const bf16* kbase, const bf16* vbase,
-                                        int page_size, int key0, const int (&lo)[2], const int (&hi)[2], float scale, int g, int t) {
-    constexpr int KS = DH / 16, NT = DH / 8;
+__device__ __forceinline__ void load_k(KFrag<DH>& k, const bf16* kbase, int g, int t) {
     const int key_c0 = 4 * (g >> 1) + (g & 1);
     const bf16* k0 = kbase + (size_t)key_c0 * DH + t * 4;
     const bf16* k1 = k0 + 2 * DH;
-    const bf16* vcol = vbase + (size_t)g * page_size + 4 * t;
-    uint2 kb0[KS], kb1[KS], vb[NT];
 #pragma unroll
-    for (int s = 0; s < KS; ++s) {
-        kb0[s] = kStream ? ld8_stream(k0 + s * 16) : ld8_keep(k0 + s * 16);
-        kb1[s] = kStream ? ld8_stream(k1 + s * 16) : ld8_keep(k1 + s * 16);
+    for (int s = 0; s < DH / 16; ++s) {
+        k.t0[s] = kStream ? ld8_stream(k0 + s * 16) : ld8_keep(k0 + s * 16);
+        k.t1[s] = kStream ? ld8_stream(k1 + s * 16) : ld8_keep(k1 + s * 16);
     }
-#pragma unroll
-    for (int j = 0; j < NT; ++j) vb[j] = kStream ? ld8_stream(vcol + (size_t)j * 8 * page_size) : ld8_keep(vcol + (size_t)j * 8 * page_size);
+}
 
+template <int DH, bool kStream>
+__device__ __forceinline__ void load_v(VFrag<DH>& v, const bf16* vbase, int page_size, int g, int t) {
+    const bf16* vcol = vbase + (size_t)g * page_size + 4 * t;
+#pragma unroll
+    for (int j = 0; j < DH / 8; ++j) v.v[j] = kStream ? ld8_stream(vcol + (size_t)j * 8 * page_size) : ld8_keep(vcol + (size_t)j * 8 * page_size);
+}
+
+// 16 rows against the 16 keys whose fragments are given; key0 is the absolute position of the
+// block's first key.  A key is visible to row r iff lo[r] <= key <= hi[r].
+template <int DH>
+__device__ __forceinline__ void compute16(RowState<DH>& st, const unsigned (&qa)[DH / 16][4], const KFrag<DH>& kf, const VFrag<DH>& vf,
+                                          int key0, const int (&lo)[2], const int (&hi)[2], float scale, int t) {
+    constexpr int KS = DH / 16, NT = DH / 8;
+    const uint2* kb0 = kf.t0;
+    const uint2* kb1 = kf.t1;
+    const uint2* vb = vf.v;
     float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int s = 0; s < KS; ++s) {

@@ -55,14 +55,27 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
     const int key_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
 
     const int* bt = block_table + (size_t)s * max_blocks;
-#pragma unroll 1
-    for (int key0 = (key_lo / 16) * 16; key0 <= p_last; key0 += 16) {
+    auto page_of = [&](int key0) {
         int page = bt[key0 / page_size];
-        if (page < 0 || page >= num_pages) page = 0;
-        const int off = key0 % page_size;
-        const bf16* kbase = kcache + (((size_t)page * nkv + kvh) * page_size + off) * DH;
-        const bf16* vbase = vcache + ((size_t)page * nkv + kvh) * DH * page_size + off;
-        block16<DH, false>(st, qa, kbase, vbase, page_size, key0, lo, hi, scale, g, t);
+        return (page < 0 || page >= num_pages) ? 0 : page;
+    };
+    // keys of the next block are fetched while the current one is computed
+    int key0 = (key_lo / 16) * 16;
+    int page = page_of(key0);
+    KFrag<DH> kcur;
+    load_k<DH, false>(kcur, kcache + (((size_t)page * nkv + kvh) * page_size + key0 % page_size) * DH, g, t);
+#pragma unroll 1
+    for (; key0 <= p_last; key0 += 16) {
+        VFrag<DH> vf;
+        load_v<DH, false>(vf, vcache + ((size_t)page * nkv + kvh) * DH * page_size + key0 % page_size, page_size, g, t);
+        KFrag<DH> knext;
+        const int next0 = key0 + 16;
+        if (next0 <= p_last) {
+            page = page_of(next0);
+            load_k<DH, false>(knext, kcache + (((size_t)page * nkv + kvh) * page_size + next0 % page_size) * DH, g, t);
+        }
+        compute16<DH>(st, qa, kcur, vf, key0, lo, hi, scale, t);
+        kcur = knext;
     }
     const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
     const float inv0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, inv1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;

@@ -17,6 +17,8 @@
 #define LI_EXPORT extern "C" __attribute__((visibility("default")))
 
 enum LiDtype : int { LI_F32 = 0, LI_BF16 = 1 };
+// What a matrix product does to its result: nothing, or the SwiGLU of interleaved gate and up columns.
+enum LiEpilogue : int { LI_EPILOGUE_NONE = 0, LI_EPILOGUE_SWIGLU = 1 };
 
 int li_fail(const char* fmt, ...);            // stores the message, returns 1
 int li_check_launch(const char* what);        // cudaGetLastError -> message
@@ -59,6 +61,32 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
     float r = (lane < nwarps) ? scratch[lane] : 0.0f;
     r = warp_sum(r);
     return r;
+}
+
+// Programmatic dependent launch.  A kernel launched through li_launch_pdl may begin while
+// the kernel before it on the stream is still running; it must not touch memory that kernel
+// writes (or still reads and this one overwrites) before pdl_wait(), which returns once the
+// kernel before has finished and its writes are visible.  pdl_launch_dependents() lets the
+// kernel after this one start being scheduled.  Both are no-ops for a plain launch.  Used on
+// the decode path, where a step is a chain of short kernels and launch latency shows.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool li_pdl_enabled();      // LITINFER_B200_PDL=0 in the environment turns the overlap off (for measurements)
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t li_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = li_pdl_enabled() ? 1 : 0;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -14,6 +14,8 @@ constexpr int kRowThreads = 256;
 
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out, int H, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);          // ids are validated on the host; never read outside the table
@@ -27,6 +29,8 @@ template <typename T, bool kAdd>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
                                const float* __restrict__ w, float eps, T* __restrict__ out, int H, int T_rows) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     int src = rows ? rows[r] : r;
     if (src < 0 || src >= T_rows) src = 0;
@@ -46,8 +50,71 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delt
     for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = from_float<T>((w[j] * xr[j]) * rinv);
 }
 
+// The same for widths that are a multiple of 4 and fit 4 float4 a thread: the row stays in
+// registers between the sum of squares and the scaling, and all loads are 16 bytes wide.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x), b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<const unsigned*>(&a);
+    r.y = *reinterpret_cast<const unsigned*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+}
+
+constexpr int kVecPerThread = 4;
+
+template <typename T, bool kAdd>
+__global__ void rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
+                                   const float* __restrict__ w, float eps, T* __restrict__ out, int H, int T_rows) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    int src = rows ? rows[r] : r;
+    if (src < 0 || src >= T_rows) src = 0;
+    float* xr = x + (size_t)src * H;
+    const int nvec = H >> 2;
+    float4 v[kVecPerThread];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kVecPerThread; ++i) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < nvec) {
+            v[i] = load4(xr + 4 * q);
+            if (kAdd) {
+                const float4 d = load4(delta + (size_t)src * H + 4 * q);
+                v[i].x += d.x; v[i].y += d.y; v[i].z += d.z; v[i].w += d.w;
+                store4(xr + 4 * q, v[i]);
+            }
+            ss += v[i].x * v[i].x;
+            ss += v[i].y * v[i].y;
+            ss += v[i].z * v[i].z;
+            ss += v[i].w * v[i].w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r * H;
+#pragma unroll
+    for (int i = 0; i < kVecPerThread; ++i) {
+        const int q = threadIdx.x + i * blockDim.x;
+        if (q < nvec) {
+            const float4 ww = load4(w + 4 * q);
+            store4(o + 4 * q, make_float4((ww.x * v[i].x) * rinv, (ww.y * v[i].y) * rinv, (ww.z * v[i].z) * rinv, (ww.w * v[i].w) * rinv));
+        }
+    }
+}
+
 template <typename T>
 __global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ delta, long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; i < n; i += stride) x[i] += to_float(delta[i]);
@@ -55,6 +122,8 @@ __global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__
 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int I, long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; i < n; i += stride) {
@@ -78,9 +147,9 @@ LI_EXPORT int li_embedding(const void* table, int dtype, const int* ids, float* 
     LI_REQUIRE(T >= 0 && H > 0 && V > 0, "embedding: bad sizes T=%d H=%d V=%d", T, H, V);
     if (T == 0) return 0;
     if (dtype == LI_F32)
-        embedding_kernel<float><<<T, kRowThreads, 0, stream>>>((const float*)table, ids, out, H, V);
+        li_launch_pdl(embedding_kernel<float>, dim3(T), dim3(kRowThreads), 0, stream, (const float*)table, ids, out, H, V);
     else if (dtype == LI_BF16)
-        embedding_kernel<bf16><<<T, kRowThreads, 0, stream>>>((const bf16*)table, ids, out, H, V);
+        li_launch_pdl(embedding_kernel<bf16>, dim3(T), dim3(kRowThreads), 0, stream, (const bf16*)table, ids, out, H, V);
     else
         return li_fail("embedding: unknown dtype %d", dtype);
     return li_check_launch("embedding");
@@ -91,12 +160,22 @@ static int launch_norm(float* x, const void* delta, int dtype, const int* rows, 
                        int H, cudaStream_t stream, const char* what) {
     LI_REQUIRE(R >= 0 && H > 0, "%s: bad sizes rows=%d H=%d", what, R, H);
     if (R == 0) return 0;
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "%s: unknown dtype %d", what, dtype);
+    const bool aligned = ((uintptr_t)x % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)delta % 16 == 0);
+    if (H % 4 == 0 && H / 4 <= 1024 * kVecPerThread && aligned) {
+        int threads = ceil_div(H / 4, kVecPerThread);
+        threads = ceil_div(threads, 32) * 32;
+        if (threads < 64) threads = 64;
+        if (dtype == LI_F32)
+            li_launch_pdl(rmsnorm_vec_kernel<float, kAdd>, dim3(R), dim3(threads), 0, stream, x, (const float*)delta, rows, w, eps, (float*)out, H, T);
+        else
+            li_launch_pdl(rmsnorm_vec_kernel<bf16, kAdd>, dim3(R), dim3(threads), 0, stream, x, (const bf16*)delta, rows, w, eps, (bf16*)out, H, T);
+        return li_check_launch(what);
+    }
     if (dtype == LI_F32)
-        rmsnorm_kernel<float, kAdd><<<R, kRowThreads, 0, stream>>>(x, (const float*)delta, rows, w, eps, (float*)out, H, T);
-    else if (dtype == LI_BF16)
-        rmsnorm_kernel<bf16, kAdd><<<R, kRowThreads, 0, stream>>>(x, (const bf16*)delta, rows, w, eps, (bf16*)out, H, T);
+        li_launch_pdl(rmsnorm_kernel<float, kAdd>, dim3(R), dim3(kRowThreads), 0, stream, x, (const float*)delta, rows, w, eps, (float*)out, H, T);
     else
-        return li_fail("%s: unknown dtype %d", what, dtype);
+        li_launch_pdl(rmsnorm_kernel<bf16, kAdd>, dim3(R), dim3(kRowThreads), 0, stream, x, (const bf16*)delta, rows, w, eps, (bf16*)out, H, T);
     return li_check_launch(what);
 }
 

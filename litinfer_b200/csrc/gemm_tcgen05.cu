@@ -130,7 +130,7 @@ __device__ __forceinline__ void tmem_ld_32x32(unsigned taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-template <typename Tout>
+template <typename Tout, bool kSwiglu>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag) {
@@ -218,7 +218,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 float v[32];
                 tmem_ld_32x32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)c, v);
                 const int col0 = n0 + c;
-                if (row < M && col0 < N) {
+                if (kSwiglu) {
+                    // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 activations up * gate / (1 + exp(-gate))
+                    if (row < M && col0 < N) {
+                        const int half_n = N >> 1;
+                        Tout* dst = out + (size_t)row * half_n + (col0 >> 1);
+                        float a16[16];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float gate = v[16 * h + i], up = v[16 * h + 8 + i];
+                                a16[8 * h + i] = up * (gate / (1.0f + expf(-gate)));
+                            }
+                        if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0 && sizeof(Tout) == 2) {
+                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                            for (int i = 0; i < 2; ++i) {
+                                uint4 pk;
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(a16[8 * i + 0], a16[8 * i + 1]);
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(a16[8 * i + 2], a16[8 * i + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(a16[8 * i + 4], a16[8 * i + 5]);
+                                __nv_bfloat162 h3 = __floats2bfloat162_rn(a16[8 * i + 6], a16[8 * i + 7]);
+                                pk.x = *reinterpret_cast<unsigned*>(&h0);
+                                pk.y = *reinterpret_cast<unsigned*>(&h1);
+                                pk.z = *reinterpret_cast<unsigned*>(&h2);
+                                pk.w = *reinterpret_cast<unsigned*>(&h3);
+                                d4[i] = pk;
+                            }
+                        } else {
+                            for (int i = 0; i < 16; ++i) {
+                                const int src_col = col0 + 16 * (i >> 3) + (i & 7);      // the gate column of activation i
+                                if (src_col + 8 < N) dst[i] = from_float<Tout>(a16[i]);
+                            }
+                        }
+                    }
+                } else if (row < M && col0 < N) {
                     Tout* dst = out + (size_t)row * N + col0;
                     if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
                         if (bias) {
@@ -270,7 +305,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 EncodeTiledFn g_encode = nullptr;
 int* g_error_host = nullptr;       // mapped pinned memory: the kernel writes, the host reads without a sync
 int* g_error_dev = nullptr;
-bool g_attr_set[2] = {false, false};
+bool g_attr_set[3] = {false, false, false};
 
 int setup() {
     if (!g_encode) {
@@ -303,7 +338,7 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_row
     return 0;
 }
 
-template <typename Tout>
+template <typename Tout, bool kSwiglu>
 int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int which) {
     if (int rc = setup()) return rc;
     if (*g_error_host != 0)
@@ -313,13 +348,13 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     if (int rc = make_map(&map_w, w, N, K, BN)) return rc;
     const size_t smem = sizeof(SharedStorage) + 1024;
     if (!g_attr_set[which]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<Tout>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<Tout, kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         g_attr_set[which] = true;
     }
     dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
     LI_REQUIRE(grid.y <= 65535, "linear (tcgen05): M=%d is too large for one launch", M);
-    gemm_tcgen05_kernel<Tout><<<grid, kThreads, smem, stream>>>(map_a, map_w, bias, (Tout*)out, M, N, K, g_error_dev);
+    gemm_tcgen05_kernel<Tout, kSwiglu><<<grid, kThreads, smem, stream>>>(map_a, map_w, bias, (Tout*)out, M, N, K, g_error_dev);
     return li_check_launch("linear (tcgen05)");
 }
 
@@ -331,9 +366,14 @@ bool li_tcgen05_accepts(const void* a, const void* w, const void* out, int dtype
 }
 
 int li_linear_tcgen05(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
-                      cudaStream_t stream) {
-    if (dtype_out == LI_BF16) return launch<bf16>(a, w, bias, out, M, N, K, stream, 0);
-    if (dtype_out == LI_F32) return launch<float>(a, w, bias, out, M, N, K, stream, 1);
+                      int epilogue, cudaStream_t stream) {
+    if (epilogue == LI_EPILOGUE_SWIGLU) {
+        LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
+                   "linear (tcgen05): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
+        return launch<bf16, true>(a, w, bias, out, M, N, K, stream, 2);
+    }
+    if (dtype_out == LI_BF16) return launch<bf16, false>(a, w, bias, out, M, N, K, stream, 0);
+    if (dtype_out == LI_F32) return launch<float, false>(a, w, bias, out, M, N, K, stream, 1);
     return li_fail("linear (tcgen05): unsupported output dtype %d", dtype_out);
 }
 

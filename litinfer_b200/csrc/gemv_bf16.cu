@@ -11,7 +11,7 @@
 // the same permutation on both operands.  Weights stream past L1 (ld.global.cs);
 // the activations (a few KB) stay in L1.
 //
-// A CTA of 4 warps owns 16 weight rows and a range of k; each warp a
+// A CTA of 4, 8 or 16 warps owns 16 weight rows and a range of k; each warp a
 // contiguous sub-range.  Warps are summed through shared memory in fixed
 // order.  When 16-row tiles alone do not fill the GPU, k is split over
 // several CTAs (split count depends on N and K only, never on M): each writes
@@ -24,7 +24,6 @@
 
 namespace {
 
-constexpr int kWarps = 4;
 constexpr int kMaxM = 64;
 constexpr size_t kWorkspaceFloats = 4u << 20;     // 16 MB of partial sums
 constexpr int kMaxTiles = 1 << 16;
@@ -51,11 +50,39 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-template <int NT, typename Tout>
-__global__ void __launch_bounds__(kWarps * 32)
+// Epilogue of one reduced element.  e = (j * 4 + i) * 32 + lane stands for weight row
+// n0 + g + 8 (i >> 1) and token j * 8 + 2 t + (i & 1) with g = lane >> 2, t = lane & 3.
+// kSwiglu: the weight rows of a tile are 8 gate rows followed by the 8 up rows of the same
+// outputs; the element and its partner 64 places further on give one activation
+// up * gate / (1 + exp(-gate)) (src/ops/swiglu/op.cpp:17-23), stored at column n0 / 2 + g.
+template <int NT, typename Tout, bool kSwiglu, typename Get>
+__device__ __forceinline__ void store_elements(Get get, const float* __restrict__ bias, Tout* __restrict__ out, int n0, int M, int N,
+                                               int nthreads) {
+    if (!kSwiglu) {
+        for (int e = threadIdx.x; e < NT * 128; e += nthreads) {
+            const float v = get(e);
+            const int l = e & 31, ji = e >> 5, i = ji & 3, j = ji >> 2;
+            const int row = n0 + (l >> 2) + ((i >> 1) << 3), tok = j * 8 + ((l & 3) << 1) + (i & 1);
+            if (row < N && tok < M) out[(size_t)tok * N + row] = from_float<Tout>(bias ? v + bias[row] : v);
+        }
+    } else {
+        const int half_n = N >> 1;
+        for (int q = threadIdx.x; q < NT * 64; q += nthreads) {
+            const int l = q & 31, i = (q >> 5) & 1, j = q >> 6;
+            const int e = (j * 4 + i) * 32 + l;
+            const float gate = get(e), up = get(e + 64);
+            const int col = (n0 >> 1) + (l >> 2), tok = j * 8 + ((l & 3) << 1) + i;
+            if (col < half_n && tok < M) out[(size_t)tok * half_n + col] = from_float<Tout>(up * (gate / (1.0f + expf(-gate))));
+        }
+    }
+}
+
+template <int NT, int WARPS, typename Tout, bool kSwiglu>
+__global__ void __launch_bounds__(WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias, Tout* __restrict__ out,
                  float* __restrict__ partial, unsigned* __restrict__ counters, int M, int N, int K, int ksplit) {
-    __shared__ float red[kWarps][NT * 128];
+    extern __shared__ float red_raw[];                 // [WARPS][NT * 128]
+    float (*red)[NT * 128] = reinterpret_cast<float (*)[NT * 128]>(red_raw);
     __shared__ int is_last;
     const int tile = blockIdx.x, split = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -64,7 +91,7 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
     const int chunks = (K + 31) >> 5;
     const int c_begin = (int)((long long)split * chunks / ksplit), c_end = (int)((long long)(split + 1) * chunks / ksplit);
     const int span = c_end - c_begin;
-    const int wb = c_begin + (int)((long long)warp * span / kWarps), we = c_begin + (int)((long long)(warp + 1) * span / kWarps);
+    const int wb = c_begin + (int)((long long)warp * span / WARPS), we = c_begin + (int)((long long)(warp + 1) * span / WARPS);
 
     float acc[NT][4];
 #pragma unroll
@@ -78,16 +105,25 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
     const bf16* w1 = W + (size_t)(v1 ? r1 : 0) * K;
     const uint4 zero = make_uint4(0, 0, 0, 0);
 
+    // Weights do not depend on the kernel before this one: the first round of loads is issued
+    // before waiting for it (programmatic dependent launch), the activations after.  Later
+    // rounds are fetched one ahead of the round being multiplied.
     constexpr int U = 4;
-    for (int c = wb; c < we; c += U) {
-        uint4 a[U], b[U];
+    uint4 a[U], b[U], an[U], bn[U];
+    auto load_w = [&](uint4 (&wa)[U], uint4 (&wb2)[U], int c) {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = ((c + u) << 5) + t * 8;
             const bool ok = (c + u) < we && k < K;
-            a[u] = (ok && v0) ? ld_stream(w0 + k) : zero;
-            b[u] = (ok && v1) ? ld_stream(w1 + k) : zero;
+            wa[u] = (ok && v0) ? ld_stream(w0 + k) : zero;
+            wb2[u] = (ok && v1) ? ld_stream(w1 + k) : zero;
         }
+    };
+    pdl_launch_dependents();
+    load_w(a, b, wb);
+    pdl_wait();
+    for (int c = wb; c < we; c += U) {
+        if (c + U < we) load_w(an, bn, c + U);
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int k = ((c + u) << 5) + t * 8;
@@ -100,6 +136,11 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
                 mma_bf16(acc[j], a[u].z, b[u].z, a[u].w, b[u].w, x.z, x.w);
             }
         }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            a[u] = an[u];
+            b[u] = bn[u];
+        }
     }
 #pragma unroll
     for (int j = 0; j < NT; ++j)
@@ -107,22 +148,18 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
         for (int i = 0; i < 4; ++i) red[warp][(j * 4 + i) * 32 + lane] = acc[j][i];
     __syncthreads();
 
-    // element e = (j * 4 + i) * 32 + lane  ->  weight row n0 + g + 8 * (i >> 1), token j * 8 + 2 t + (i & 1)
-    const size_t pbase = ((size_t)split * gridDim.x + tile) * (NT * 128);
-    for (int e = threadIdx.x; e < NT * 128; e += kWarps * 32) {
+    auto warps_sum = [&](int e) {
         float v = red[0][e];
 #pragma unroll
-        for (int w = 1; w < kWarps; ++w) v += red[w][e];
-        if (ksplit == 1) {
-            const int l = e & 31, ji = e >> 5, i = ji & 3, j = ji >> 2;
-            const int row = n0 + (l >> 2) + ((i >> 1) << 3), tok = j * 8 + ((l & 3) << 1) + (i & 1);
-            if (row < N && tok < M) out[(size_t)tok * N + row] = from_float<Tout>(bias ? v + bias[row] : v);
-        } else {
-            partial[pbase + e] = v;
-        }
+        for (int w = 1; w < WARPS; ++w) v += red[w][e];
+        return v;
+    };
+    if (ksplit == 1) {
+        store_elements<NT, Tout, kSwiglu>(warps_sum, bias, out, n0, M, N, WARPS * 32);
+        return;
     }
-    if (ksplit == 1) return;
-
+    const size_t pbase = ((size_t)split * gridDim.x + tile) * (NT * 128);
+    for (int e = threadIdx.x; e < NT * 128; e += WARPS * 32) partial[pbase + e] = warps_sum(e);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -132,13 +169,13 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int e = threadIdx.x; e < NT * 128; e += kWarps * 32) {
+    const size_t tiles = gridDim.x;
+    auto splits_sum = [&](int e) {
         float v = 0.0f;
-        for (int s = 0; s < ksplit; ++s) v += __ldcg(&partial[((size_t)s * gridDim.x + tile) * (NT * 128) + e]);
-        const int l = e & 31, ji = e >> 5, i = ji & 3, j = ji >> 2;
-        const int row = n0 + (l >> 2) + ((i >> 1) << 3), tok = j * 8 + ((l & 3) << 1) + (i & 1);
-        if (row < N && tok < M) out[(size_t)tok * N + row] = from_float<Tout>(bias ? v + bias[row] : v);
-    }
+        for (int s = 0; s < ksplit; ++s) v += __ldcg(&partial[((size_t)s * tiles + tile) * (NT * 128) + e]);
+        return v;
+    };
+    store_elements<NT, Tout, kSwiglu>(splits_sum, bias, out, n0, M, N, WARPS * 32);
     if (threadIdx.x == 0) counters[tile] = 0;          // ready for the next launch on this stream
 }
 
@@ -160,37 +197,63 @@ int ensure_workspace(Workspace** ws) {
     return 0;
 }
 
-int choose_ksplit(int ntiles, int K, int nt) {
+// How a product is cut: warps per CTA (each warp should have about four 32-element chunks
+// of k per round of loads) and CTAs along k.  Depends on N and K only, never on M.
+void choose_shape(int ntiles, int K, int nt, int* warps, int* ksplit) {
     const int chunks = (K + 31) / 32;
-    int ksplit = 1;
-    if (ntiles < kTargetCtas) {
-        ksplit = ceil_div(kTargetCtas, ntiles);
-        const int by_work = chunks / 16 > 0 ? chunks / 16 : 1;        // at least 512 k per split
-        if (ksplit > by_work) ksplit = by_work;
+    int w = 4;
+    if (ntiles < kTargetCtas) w = chunks >= 48 ? 16 : (chunks >= 24 ? 8 : 4);
+    else if (ntiles < 4 * kTargetCtas && chunks >= 32) w = 8;
+    (void)nt;
+    int ks = 1;
+    const int ctas_wanted = kTargetCtas * 4 / w;
+    if (ntiles < ctas_wanted) {
+        ks = ceil_div(ctas_wanted, ntiles);
+        const int by_work = chunks / (w * 4) > 0 ? chunks / (w * 4) : 1;  // at least four chunks a warp
+        if (ks > by_work) ks = by_work;
     }
-    while (ksplit > 1 && (size_t)ksplit * ntiles * nt * 128 > kWorkspaceFloats) --ksplit;
-    return ksplit;
+    while (ks > 1 && (size_t)ks * ntiles * 8 * 128 > kWorkspaceFloats) --ks;      // sized for 64 tokens whatever M is
+    *warps = w;
+    *ksplit = ks;
 }
 
-template <int NT, typename Tout>
-int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
-    const int ntiles = ceil_div(N, 16);
-    const int ksplit = choose_ksplit(ntiles, K, NT);
-    Workspace* ws = nullptr;
-    if (int rc = ensure_workspace(&ws)) return rc;
-    LI_REQUIRE(ntiles <= kMaxTiles || ksplit == 1, "linear (gemv): N=%d has too many tiles for split-k", N);
-    dim3 grid(ntiles, ksplit);
-    gemv_bf16_kernel<NT, Tout><<<grid, kWarps * 32, 0, stream>>>((const bf16*)a, (const bf16*)w, bias, (Tout*)out, ws->partial,
-                                                                 ws->counters, M, N, K, ksplit);
+template <int NT, int WARPS, typename Tout, bool kSwiglu>
+int launch_kernel(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, int ksplit, Workspace* ws,
+                  cudaStream_t stream) {
+    dim3 grid(ceil_div(N, 16), ksplit);
+    constexpr size_t smem = (size_t)WARPS * NT * 128 * sizeof(float);
+    if (smem > 48 * 1024) {
+        static bool raised = false;
+        if (!raised) {
+            cudaError_t e = cudaFuncSetAttribute(gemv_bf16_kernel<NT, WARPS, Tout, kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return li_fail("linear (gemv): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+            raised = true;
+        }
+    }
+    li_launch_pdl(gemv_bf16_kernel<NT, WARPS, Tout, kSwiglu>, grid, dim3(WARPS * 32), smem, stream, (const bf16*)a, (const bf16*)w, bias,
+                  (Tout*)out, ws->partial, ws->counters, M, N, K, ksplit);
     return li_check_launch("linear (gemv)");
 }
 
-template <typename Tout>
+template <int NT, typename Tout, bool kSwiglu>
+int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
+    const int ntiles = ceil_div(N, 16);
+    int warps = 4, ksplit = 1;
+    choose_shape(ntiles, K, NT, &warps, &ksplit);
+    Workspace* ws = nullptr;
+    if (int rc = ensure_workspace(&ws)) return rc;
+    LI_REQUIRE(ntiles <= kMaxTiles || ksplit == 1, "linear (gemv): N=%d has too many tiles for split-k", N);
+    if (warps == 16) return launch_kernel<NT, 16, Tout, kSwiglu>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+    if (warps >= 8) return launch_kernel<NT, 8, Tout, kSwiglu>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+    return launch_kernel<NT, 4, Tout, kSwiglu>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+}
+
+template <typename Tout, bool kSwiglu>
 int launch_nt(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
-    if (M <= 8) return launch<1, Tout>(a, w, bias, out, M, N, K, stream);
-    if (M <= 16) return launch<2, Tout>(a, w, bias, out, M, N, K, stream);
-    if (M <= 32) return launch<4, Tout>(a, w, bias, out, M, N, K, stream);
-    return launch<8, Tout>(a, w, bias, out, M, N, K, stream);
+    if (M <= 8) return launch<1, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
+    if (M <= 16) return launch<2, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
+    if (M <= 32) return launch<4, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
+    return launch<8, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
 }
 
 }  // namespace
@@ -198,10 +261,15 @@ int launch_nt(const void* a, const void* w, const float* bias, void* out, int M,
 bool li_gemv_bf16_accepts(int M, int N, int K) { return M >= 1 && M <= kMaxM && K % 8 == 0 && N >= 1; }
 
 int li_linear_gemv_bf16(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
-                        cudaStream_t stream) {
+                        int epilogue, cudaStream_t stream) {
     LI_REQUIRE(li_gemv_bf16_accepts(M, N, K), "linear (gemv): refuses M=%d N=%d K=%d (M <= %d, K a multiple of 8)", M, N, K, kMaxM);
     LI_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear (gemv): operands must be 16-byte aligned");
-    if (dtype_out == LI_BF16) return launch_nt<bf16>(a, w, bias, out, M, N, K, stream);
-    if (dtype_out == LI_F32) return launch_nt<float>(a, w, bias, out, M, N, K, stream);
+    if (epilogue == LI_EPILOGUE_SWIGLU) {
+        LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
+                   "linear (gemv): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
+        return launch_nt<bf16, true>(a, w, bias, out, M, N, K, stream);
+    }
+    if (dtype_out == LI_BF16) return launch_nt<bf16, false>(a, w, bias, out, M, N, K, stream);
+    if (dtype_out == LI_F32) return launch_nt<float, false>(a, w, bias, out, M, N, K, stream);
     return li_fail("linear (gemv): unsupported output dtype %d", dtype_out);
 }

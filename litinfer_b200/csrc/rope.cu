@@ -15,53 +15,48 @@
 
 namespace {
 
+// One block per (token, head): query heads first, then key/value heads.  A thread owns the
+// pair (j, j + half) of its head, so sine and cosine are computed once per pair and nothing is
+// shared; blocks are small and many, which keeps the latency of a decode step's launch short.
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ denom,
                                      int rotary_dim, const int* __restrict__ slot_mapping, T* __restrict__ kcache,
                                      T* __restrict__ vcache, int nh, int nkv, int dh, int page_size, int num_pages, int write) {
-    extern __shared__ float cs[];                    // cos[half] | sin[half]
-    const int t = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, head = blockIdx.y;
     const int half = rotary_dim >> 1;
     const float pos = (float)positions[t];
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        float s, c;
-        sincosf(pos / denom[j], &s, &c);
-        cs[j] = c;
-        cs[half + j] = s;
-    }
-    __syncthreads();
-    const int row = (nh + 2 * nkv) * dh;
-    T* q = qkv + (size_t)t * row;
-    for (int i = threadIdx.x; i < nh * half; i += blockDim.x) {
-        const int h = i / half, j = i - h * half;
-        T* x = q + h * dh;
-        const float a = to_float(x[j]), b = to_float(x[j + half]);
-        x[j] = from_float<T>(a * cs[j] - b * cs[half + j]);
-        x[j + half] = from_float<T>(b * cs[j] + a * cs[half + j]);
+    T* row = qkv + (size_t)t * (nh + 2 * nkv) * dh;
+    if (head < nh) {
+        T* x = row + (size_t)head * dh;
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            float s, c;
+            sincosf(pos / denom[j], &s, &c);
+            const float a = to_float(x[j]), b = to_float(x[j + half]);
+            x[j] = from_float<T>(a * c - b * s);
+            x[j + half] = from_float<T>(b * c + a * s);
+        }
+        return;
     }
     if (!write) return;
+    const int h = head - nh;
     const int slot = slot_mapping[t];
     const int page = slot / page_size, off = slot - page * page_size;
     if (slot < 0 || page >= num_pages) return;       // validated on the host; never write outside the cache
-    const T* k = q + nh * dh;
-    const T* v = k + nkv * dh;
-    for (int i = threadIdx.x; i < nkv * dh; i += blockDim.x) {
-        const int h = i / dh, d = i - h * dh;
-        const size_t dst = (((size_t)page * nkv + h) * page_size + off) * dh + d;
-        float kv = to_float(k[i]);
-        if (d < rotary_dim) {
-            if (d < half) {
-                const float b = to_float(k[i + half]);
-                kv = kv * cs[d] - b * cs[half + d];
-            } else {
-                const int j = d - half;
-                const float a = to_float(k[i - half]);
-                kv = kv * cs[j] + a * cs[half + j];
-            }
-        }
-        kcache[dst] = from_float<T>(kv);
-        vcache[((((size_t)page * nkv + h) * dh + d) * page_size) + off] = v[i];      // values are cached transposed
+    const T* k = row + (size_t)(nh + h) * dh;
+    const T* v = row + (size_t)(nh + nkv + h) * dh;
+    T* kdst = kcache + (((size_t)page * nkv + h) * page_size + off) * dh;
+    T* vdst = vcache + ((size_t)page * nkv + h) * dh * page_size + off;      // values are cached transposed
+    for (int j = threadIdx.x; j < half; j += blockDim.x) {
+        float s, c;
+        sincosf(pos / denom[j], &s, &c);
+        const float a = to_float(k[j]), b = to_float(k[j + half]);
+        kdst[j] = from_float<T>(a * c - b * s);
+        kdst[j + half] = from_float<T>(b * c + a * s);
     }
+    for (int d = rotary_dim + threadIdx.x; d < dh; d += blockDim.x) kdst[d] = k[d];
+    for (int d = threadIdx.x; d < dh; d += blockDim.x) vdst[(size_t)d * page_size] = v[d];
 }
 
 }  // namespace
@@ -73,14 +68,15 @@ LI_EXPORT int li_rope_kv_write(void* qkv, int dtype, const int* positions, const
     LI_REQUIRE(rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= dh, "rope_kv_write: rotary_dim %d must be even and at most head_dim %d",
                rotary_dim, dh);
     if (T == 0) return 0;
-    const size_t smem = (size_t)rotary_dim * sizeof(float);
-    LI_REQUIRE(smem <= 48 * 1024, "rope_kv_write: rotary_dim %d is too large", rotary_dim);
-    const int threads = 128;
+    LI_REQUIRE(T <= 2147483647 && nh + nkv <= 65535, "rope_kv_write: too many heads for one launch");
+    const int threads = dh >= 128 ? 64 : 32;
+    const dim3 grid(T, nh + nkv);
+    const size_t smem = 0;
     if (dtype == LI_F32)
-        rope_kv_write_kernel<float><<<T, threads, smem, stream>>>((float*)qkv, positions, denom, rotary_dim, slot_mapping, (float*)kcache,
+        li_launch_pdl(rope_kv_write_kernel<float>, dim3(grid), dim3(threads), smem, stream, (float*)qkv, positions, denom, rotary_dim, slot_mapping, (float*)kcache,
                                                                    (float*)vcache, nh, nkv, dh, page_size, num_pages, write);
     else if (dtype == LI_BF16)
-        rope_kv_write_kernel<bf16><<<T, threads, smem, stream>>>((bf16*)qkv, positions, denom, rotary_dim, slot_mapping, (bf16*)kcache,
+        li_launch_pdl(rope_kv_write_kernel<bf16>, dim3(grid), dim3(threads), smem, stream, (bf16*)qkv, positions, denom, rotary_dim, slot_mapping, (bf16*)kcache,
                                                                   (bf16*)vcache, nh, nkv, dh, page_size, num_pages, write);
     else
         return li_fail("rope_kv_write: unknown dtype %d", dtype);

@@ -85,6 +85,8 @@ __device__ Best row_argmax(const float* row, int V, Best* scratch) {
 
 __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
     __shared__ Best scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const Best b = row_argmax(logits + (size_t)blockIdx.x * V, V, scratch);
     if (threadIdx.x == 0) out[blockIdx.x] = b.i;
 }
@@ -93,6 +95,8 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
                                                           int* __restrict__ out, int V) {
     __shared__ Best scratch[32];
     __shared__ float fscratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * V;
     const int* pr = params + r * 6;
@@ -160,7 +164,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
 LI_EXPORT int li_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream) {
     LI_REQUIRE(R >= 0 && V > 0, "argmax: bad sizes R=%d V=%d", R, V);
     if (R == 0) return 0;
-    argmax_kernel<<<R, kThreads, 0, stream>>>(logits, out, V);
+    li_launch_pdl(argmax_kernel, dim3(R), dim3(kThreads), 0, stream, logits, out, V);
     return li_check_launch("argmax");
 }
 
@@ -168,6 +172,6 @@ LI_EXPORT int li_sample(const float* logits, const int* params, int* out, int R,
     LI_REQUIRE(R >= 0 && V > 0, "sample: bad sizes R=%d V=%d", R, V);
     LI_REQUIRE(V < (1 << 24), "sample: vocabulary %d is too large", V);
     if (R == 0) return 0;
-    sample_kernel<<<R, kThreads, 0, stream>>>(logits, params, out, V);
+    li_launch_pdl(sample_kernel, dim3(R), dim3(kThreads), 0, stream, logits, params, out, V);
     return li_check_launch("sample");
 }

@@ -139,39 +139,57 @@ def residual_add(x32: torch.Tensor, delta: torch.Tensor) -> None:
     _check(library().li_residual_add(_p(x32), _p(delta), _i(_dt(delta)), _l(x32.numel()), _stream(x32)), "residual_add")
 
 
-def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
-    """out[M, N] = a[M, K] weight[N, K]^T (+ bias[N]); float32 accumulation;
-    out is in the run dtype or float32."""
+EPILOGUES = {None: 0, "swiglu": 1}
+
+
+def _linear_args(a, weight, bias, out, epilogue):
     M, Kd = a.shape
     N = weight.shape[0]
     _need(a, "linear input")
     _need(weight, "linear weight", a.dtype, (N, Kd))
     if bias is not None:
         _need(bias, "linear bias", torch.float32, (N,))
-    _need(out, "linear output", None, (M, N))
+    if epilogue not in EPILOGUES:
+        raise KernelError(f"linear: unknown epilogue {epilogue!r}")
+    _need(out, "linear output", None, (M, N // 2 if epilogue == "swiglu" else N))
     if out.dtype not in (a.dtype, torch.float32):
         raise KernelError(f"linear output must be {a.dtype} or float32, got {out.dtype}")
+    return M, N, Kd
+
+
+def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+           epilogue: Optional[str] = None) -> None:
+    """out[M, N] = a[M, K] weight[N, K]^T (+ bias[N]); float32 accumulation;
+    out is in the run dtype or float32.
+
+    ``epilogue="swiglu"`` (bfloat16 only): ``weight`` holds gate and up rows interleaved in
+    groups of 8 (see :func:`interleave_gate_up`) and out[M, N / 2] = up * gate / (1 + exp(-gate))."""
+    M, N, Kd = _linear_args(a, weight, bias, out, epilogue)
     if M == 0:
         return
-    _check(library().li_linear(_p(a), _p(weight), _p(bias), _p(out), _i(_dt(a)), _i(_dt(out)), _i(M), _i(N), _i(Kd), _stream(out)),
-           "linear")
+    _check(library().li_linear(_p(a), _p(weight), _p(bias), _p(out), _i(_dt(a)), _i(_dt(out)), _i(M), _i(N), _i(Kd),
+                               _i(EPILOGUES[epilogue]), _stream(out)), "linear")
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[I, K] gate and up rows as one [2 I, K] matrix in the order the swiglu epilogue reads:
+    8 gate rows, the 8 up rows of the same outputs, the next 8 gate rows, ... (I a multiple of 8)."""
+    I, Kd = gate.shape
+    if I % 8 or up.shape != gate.shape:
+        raise KernelError(f"interleave_gate_up: shapes {tuple(gate.shape)} / {tuple(up.shape)}, rows must be a multiple of 8")
+    return torch.stack((gate.view(I // 8, 8, Kd), up.view(I // 8, 8, Kd)), dim=1).reshape(2 * I, Kd).contiguous()
 
 
 LINEAR_IMPLEMENTATIONS = {"simt": 0, "gemv": 1, "tcgen05": 2}
 
 
-def linear_with(which: str, a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+def linear_with(which: str, a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                epilogue: Optional[str] = None) -> None:
     """:func:`linear` through one named kernel (``simt``, ``gemv``, ``tcgen05``); an error
     if that kernel refuses the sizes.  For tests and measurements of a kernel alone."""
-    M, Kd = a.shape
-    N = weight.shape[0]
-    _need(a, "linear input")
-    _need(weight, "linear weight", a.dtype, (N, Kd))
-    if bias is not None:
-        _need(bias, "linear bias", torch.float32, (N,))
-    _need(out, "linear output", None, (M, N))
+    M, N, Kd = _linear_args(a, weight, bias, out, epilogue)
     _check(library().li_linear_with(_i(LINEAR_IMPLEMENTATIONS[which]), _p(a), _p(weight), _p(bias), _p(out), _i(_dt(a)),
-                                    _i(_dt(out)), _i(M), _i(N), _i(Kd), _stream(out)), f"linear[{which}]")
+                                    _i(_dt(out)), _i(M), _i(N), _i(Kd), _i(EPILOGUES[epilogue]), _stream(out)), f"linear[{which}]")
 
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torch.Tensor, rotary_dim: int,

@@ -50,3 +50,31 @@ class FusedLinear:
         out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or self.dtype, device=x.device)
         K.linear(x, self.weight, self.bias, out)
         return out
+
+
+class GateUpLinear(FusedLinear):
+    """gate and up maps of a gated feed-forward.  In bfloat16, with sizes that are multiples of
+    8, the two matrices are interleaved in groups of 8 rows when bound and the product's
+    epilogue applies up * silu(gate), so the [tokens, 2 * intermediate] product never goes to
+    memory.  Otherwise (the 32-bit path) the fused product is followed by the swiglu kernel."""
+
+    def __init__(self, prefix, gate_name, up_name, in_features, intermediate, dtype, std=0.02):
+        super().__init__(prefix, [gate_name, up_name], in_features, [intermediate, intermediate], False, dtype, std)
+        self.intermediate = int(intermediate)
+        self.fused_activation = dtype == torch.bfloat16 and intermediate % 8 == 0 and in_features % 8 == 0
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        if not self.fused_activation:
+            return super().bind(tensors)
+        gate = tensors.pop(f"{self.prefix}{self.names[0]}.weight")
+        up = tensors.pop(f"{self.prefix}{self.names[1]}.weight")
+        self.weight = K.interleave_gate_up(gate, up)
+
+    def activation(self, x: torch.Tensor) -> torch.Tensor:
+        """up(x) * silu(gate(x)), [tokens, intermediate]."""
+        act = torch.empty((x.shape[0], self.intermediate), dtype=self.dtype, device=x.device)
+        if self.fused_activation:
+            K.linear(x, self.weight, None, act, epilogue="swiglu")
+        else:
+            K.swiglu(self(x), act)
+        return act

@@ -1,7 +1,7 @@
 """Dense SwiGLU feed-forward: down(up(h) * silu(gate(h))), no biases
 (src/llaisys/models/qwen2.cpp:744-759; src/ops/swiglu/op.cpp:17-23, silu as
 g / (1 + exp(-g))).  gate and up are one fused product; the activation is
-computed in float32 and rounded once."""
+computed in float32 and rounded once; in bfloat16 it is the epilogue of that product."""
 
 from __future__ import annotations
 
@@ -12,7 +12,7 @@ import torch
 from .. import kernels as K
 from ..weights.loader import ParamSpec
 from .base import FEED_FORWARDS, FeedForward
-from .linear import FusedLinear
+from .linear import FusedLinear, GateUpLinear
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -22,10 +22,9 @@ class SwiGLU(FeedForward):
         self.hidden = int(spec["hidden_size"])
         self.intermediate = int(spec["intermediate_size"])
         names = spec.get("names", {})
-        self.gate_up = FusedLinear(prefix, [names.get("gate", "gate_proj"), names.get("up", "up_proj")],
-                                   self.hidden, [self.intermediate, self.intermediate], bool(spec.get("bias", False)), dtype)
-        self.down = FusedLinear(prefix, [names.get("down", "down_proj")], self.intermediate, [self.hidden],
-                                bool(spec.get("bias", False)), dtype)
+        self.gate_up = GateUpLinear(prefix, names.get("gate", "gate_proj"), names.get("up", "up_proj"), self.hidden,
+                                    self.intermediate, dtype)
+        self.down = FusedLinear(prefix, [names.get("down", "down_proj")], self.intermediate, [self.hidden], False, dtype)
 
     def params(self) -> List[ParamSpec]:
         return self.gate_up.params() + self.down.params()
@@ -35,7 +34,4 @@ class SwiGLU(FeedForward):
         self.down.bind(tensors)
 
     def forward(self, h, ctx):
-        gu = self.gate_up(h)                                # [T, 2 * intermediate]: gate | up
-        act = torch.empty((h.shape[0], self.intermediate), dtype=self.dtype, device=h.device)
-        K.swiglu(gu, act)
-        return self.down(act)
+        return self.down(self.gate_up.activation(h))

@@ -47,11 +47,22 @@ def residual_add(x32, delta):
     x32.add_(delta.float())
 
 
-def linear(a, weight, bias, out):
+def linear(a, weight, bias, out, epilogue=None):
     y = a.float() @ weight.float().t()
     if bias is not None:
         y = y + bias
+    if epilogue == "swiglu":
+        # columns come as 8 gate, 8 up, 8 gate, 8 up, ...
+        M, N = y.shape
+        y = y.view(M, N // 16, 2, 8)
+        g, u = y[:, :, 0, :], y[:, :, 1, :]
+        y = (u * (g / (1.0 + torch.exp(-g)))).reshape(M, N // 2)
     _store(out, y)
+
+
+def interleave_gate_up(gate, up):
+    I, Kd = gate.shape
+    return torch.stack((gate.view(I // 8, 8, Kd), up.view(I // 8, 8, Kd)), dim=1).reshape(2 * I, Kd).contiguous()
 
 
 def rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cache, v_cache,
@@ -186,5 +197,5 @@ def sample(logits, params, out):
     out.copy_(torch.tensor(res, dtype=torch.int32))
 
 
-ALL = ["embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
+ALL = ["interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]

@@ -159,6 +159,28 @@ def test_linear_tcgen05_kernel(shape):
             close(out, ref, out_dtype, f"tcgen05 {shape} bias={bias is not None} out={out_dtype}", f32_tol=1e-5 * math.sqrt(Kd))
 
 
+@pytest.mark.parametrize("which,shape", [("gemv", (1, 256, 64)), ("gemv", (8, 17920, 1536)), ("gemv", (40, 544, 96)), ("gemv", (16, 352, 80)),
+                                         ("tcgen05", (128, 256, 64)), ("tcgen05", (300, 544, 96)), ("tcgen05", (2048, 17920, 1536)),
+                                         ("tcgen05", (77, 352, 80)), ("tcgen05", (65, 48, 40))])
+def test_linear_swiglu_epilogue(which, shape):
+    """gate and up rows interleaved in groups of 8; the product's epilogue applies up * silu(gate)."""
+    M, N, Kd = shape
+    I = N // 2
+    a = rnd(M, Kd, dtype=torch.bfloat16, seed=36)
+    gate = rnd(I, Kd, dtype=torch.bfloat16, seed=37, scale=0.1)
+    up = rnd(I, Kd, dtype=torch.bfloat16, seed=38, scale=0.1)
+    w = K().interleave_gate_up(gate, up)
+    assert torch.equal(w, R.interleave_gate_up(gate, up))
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=dev())
+    K().linear_with(which, a, w, None, out, epilogue="swiglu")
+    g, u = a.float() @ gate.float().t(), a.float() @ up.float().t()
+    ref = u * (g / (1 + torch.exp(-g)))
+    close(out, ref, torch.bfloat16, f"{which} swiglu {shape}")
+    ref2 = torch.empty_like(out)
+    R.linear(a, w, None, ref2, epilogue="swiglu")
+    close(out, ref2, torch.bfloat16, f"{which} swiglu {shape} against the reference of the fused call")
+
+
 @pytest.mark.parametrize("shape", LINEAR_SHAPES)
 def test_linear_simt_rows_do_not_depend_on_batch(shape):
     """float32: a row's result is the same bits whether it runs alone or among others."""
