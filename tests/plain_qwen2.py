@@ -105,8 +105,8 @@ def plain_rope(x, positions, theta):
     dh = x.shape[-1]
     half = dh // 2
     j = torch.arange(half, dtype=torch.float32)
-    inv = 1.0 / torch.pow(torch.tensor(float(theta), dtype=torch.float32), (2.0 * j) / dh)
-    phi = torch.as_tensor(positions, dtype=torch.float32)[:, None] * inv[None, :]
+    denom = torch.pow(torch.tensor(float(theta), dtype=torch.float32), (2.0 * j) / dh)
+    phi = torch.as_tensor(positions, dtype=torch.float32)[:, None] / denom[None, :]
     cos, sin = torch.cos(phi)[:, None, :], torch.sin(phi)[:, None, :]
     a, b = x[..., :half], x[..., half:]
     return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
