@@ -21,17 +21,16 @@
 // Every wait on an mbarrier is bounded.  A wait that runs out raises a flag in
 // mapped host memory (li_tcgen05_status() reads it), the CTA waits, again
 // bounded, for the copies it has in flight, frees its tensor memory and returns.
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;
+using namespace tc;
+
+constexpr int BM = 128, BN = 128;
 constexpr int kStages = 6;
 constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = BN * BK * 2;
 constexpr int kThreads = 192;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;      // two seconds: far beyond any legitimate wait
 
 struct __align__(1024) SharedStorage {
     unsigned char a[kStages][kStageBytesA];
@@ -42,93 +41,6 @@ struct __align__(1024) SharedStorage {
     unsigned tmem_base;
     int failed;
 };
-
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-// Bounded wait for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-    const unsigned addr = smem_u32(bar);
-    unsigned long long t0 = 0;
-    for (unsigned spin = 0;; ++spin) {
-        unsigned done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(addr), "r"(parity)
-            : "memory");
-        if (done) return true;
-        if ((spin & 255u) == 255u) {
-            unsigned long long now;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-            if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) return false;
-        }
-        if (spin > (1u << 30)) return false;
-    }
-}
-
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major tile of rows x 64 bfloat16 written by TMA
-// with the 128-byte swizzle; 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
-    const unsigned addr = smem_u32(tile);
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);         // start address
-    d |= (unsigned long long)0 << 16;                           // leading byte offset: unused with this swizzle
-    d |= (unsigned long long)(1024 >> 4) << 32;                 // stride byte offset
-    d |= (unsigned long long)1 << 46;                           // descriptor version of this architecture
-    d |= (unsigned long long)2 << 61;                           // 128-byte swizzle
-    return d;
-}
-
-// Instruction descriptor of kind::f16: bfloat16 a and b, float accumulator, both K-major.
-__host__ __device__ constexpr unsigned umma_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(unsigned long long* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld_32x32(unsigned taddr, float (&v)[32]) {
-    unsigned r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 template <typename Tout, bool kSwiglu>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -298,49 +210,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 // ---- host side -----------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn g_encode = nullptr;
-int* g_error_host = nullptr;       // mapped pinned memory: the kernel writes, the host reads without a sync
-int* g_error_dev = nullptr;
 bool g_attr_set[3] = {false, false, false};
-
-int setup() {
-    if (!g_encode) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
-            return li_fail("linear (tcgen05): the driver has no cuTensorMapEncodeTiled: %s", cudaGetErrorString(e));
-        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-    }
-    if (!g_error_host) {
-        cudaError_t e = cudaHostAlloc((void**)&g_error_host, sizeof(int), cudaHostAllocMapped);
-        if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot allocate the status word: %s", cudaGetErrorString(e));
-        *g_error_host = 0;
-        e = cudaHostGetDevicePointer((void**)&g_error_dev, g_error_host, 0);
-        if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot map the status word: %s", cudaGetErrorString(e));
-    }
-    return 0;
-}
-
-int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return li_fail("linear (tcgen05): cuTensorMapEncodeTiled failed with %d for a [%d, %d] tensor", (int)r, rows, cols);
-    return 0;
-}
 
 template <typename Tout, bool kSwiglu>
 int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int which) {
-    if (int rc = setup()) return rc;
+    EncodeTiledFn encode = nullptr;
+    int *g_error_host = nullptr, *g_error_dev = nullptr;
+    if (int rc = setup(&encode, &g_error_host, &g_error_dev)) return rc;
     if (*g_error_host != 0)
         return li_fail("linear (tcgen05): an earlier launch gave up waiting on a barrier (status %d); the results since then are invalid", *g_error_host);
     CUtensorMap map_a, map_w;
@@ -376,7 +252,3 @@ int li_linear_tcgen05(const void* a, const void* w, const float* bias, void* out
     if (dtype_out == LI_F32) return launch<float, false>(a, w, bias, out, M, N, K, stream, 1);
     return li_fail("linear (tcgen05): unsupported output dtype %d", dtype_out);
 }
-
-// 0 while no launch of the tcgen05 kernel has given up a wait; else which role did
-// (1 producer, 2 tensor-core issuer, 3 epilogue).  Meaningful after a synchronisation.
-LI_EXPORT int li_tcgen05_status() { return g_error_host ? *g_error_host : 0; }

@@ -1,0 +1,55 @@
+// Host side shared by the tcgen05 kernels: the driver entry point that encodes tensor maps
+// (resolved at run time, so the library does not link against the driver), the status word the
+// kernels raise when a bounded wait runs out, and the status query of the C interface.
+#include "tcgen05.cuh"
+
+namespace tc {
+
+static EncodeTiledFn g_encode = nullptr;
+static int* g_error_host = nullptr;       // mapped pinned memory: the kernels write, the host reads without a sync
+static int* g_error_dev = nullptr;
+
+int setup(EncodeTiledFn* encode, int** error_host, int** error_dev) {
+    if (!g_encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+            return li_fail("tcgen05: the driver has no cuTensorMapEncodeTiled: %s", cudaGetErrorString(e));
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    if (!g_error_host) {
+        cudaError_t e = cudaHostAlloc((void**)&g_error_host, sizeof(int), cudaHostAllocMapped);
+        if (e != cudaSuccess) return li_fail("tcgen05: cannot allocate the status word: %s", cudaGetErrorString(e));
+        *g_error_host = 0;
+        e = cudaHostGetDevicePointer((void**)&g_error_dev, g_error_host, 0);
+        if (e != cudaSuccess) return li_fail("tcgen05: cannot map the status word: %s", cudaGetErrorString(e));
+    }
+    *encode = g_encode;
+    *error_host = g_error_host;
+    *error_dev = g_error_dev;
+    return 0;
+}
+
+int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return li_fail("tcgen05: cuTensorMapEncodeTiled failed with %d for a [%d, %d] tensor", (int)r, rows, cols);
+    return 0;
+}
+
+}  // namespace tc
+
+// 0 while no launch of a tcgen05 kernel has given up a wait; else which role did
+// (1 producer, 2 tensor-core issuer, 3 epilogue).  Meaningful after a synchronisation.
+LI_EXPORT int li_tcgen05_status() {
+    tc::EncodeTiledFn f;
+    int *h = nullptr, *d = nullptr;
+    if (tc::setup(&f, &h, &d)) return -1;
+    return *h;
+}

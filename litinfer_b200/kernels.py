@@ -180,12 +180,12 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack((gate.view(I // 8, 8, Kd), up.view(I // 8, 8, Kd)), dim=1).reshape(2 * I, Kd).contiguous()
 
 
-LINEAR_IMPLEMENTATIONS = {"simt": 0, "gemv": 1, "tcgen05": 2}
+LINEAR_IMPLEMENTATIONS = {"simt": 0, "gemv": 1, "tcgen05": 2, "gemv_tcgen05": 3}
 
 
 def linear_with(which: str, a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
                 epilogue: Optional[str] = None) -> None:
-    """:func:`linear` through one named kernel (``simt``, ``gemv``, ``tcgen05``); an error
+    """:func:`linear` through one named kernel (``simt``, ``gemv``, ``tcgen05``, ``gemv_tcgen05``); an error
     if that kernel refuses the sizes.  For tests and measurements of a kernel alone."""
     M, N, Kd = _linear_args(a, weight, bias, out, epilogue)
     _check(library().li_linear_with(_i(LINEAR_IMPLEMENTATIONS[which]), _p(a), _p(weight), _p(bias), _p(out), _i(_dt(a)),

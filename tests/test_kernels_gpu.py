@@ -117,8 +117,9 @@ GEMV_SHAPES = [(1, 64, 64), (8, 2048, 1536), (5, 100, 72), (16, 1536, 8960), (9,
                (3, 17920, 1536), (2, 151936, 1536), (40, 30, 40)]
 
 
+@pytest.mark.parametrize("which", ["gemv", "gemv_tcgen05"])
 @pytest.mark.parametrize("shape", GEMV_SHAPES)
-def test_linear_weight_streaming_kernel(shape):
+def test_linear_weight_streaming_kernel(shape, which):
     M, N, Kd = shape
     a = rnd(M, Kd, dtype=torch.bfloat16, seed=16)
     w = rnd(N, Kd, dtype=torch.bfloat16, seed=17, scale=0.05)
@@ -127,15 +128,17 @@ def test_linear_weight_streaming_kernel(shape):
         for out_dtype in (torch.bfloat16, torch.float32):
             out = torch.empty(M, N, dtype=out_dtype, device=dev())
             ref = torch.empty_like(out)
-            K().linear_with("gemv", a, w, bias, out)
+            K().linear_with(which, a, w, bias, out)
             R.linear(a, w, bias, ref)
-            close(out, ref, out_dtype, f"gemv {shape} bias={bias is not None} out={out_dtype}", f32_tol=1e-5 * math.sqrt(Kd))
+            close(out, ref, out_dtype, f"{which} {shape} bias={bias is not None} out={out_dtype}", f32_tol=1e-5 * math.sqrt(Kd))
     # a token's result does not depend on the batch it is in, nor on the call (split-k partial sums are added in fixed order)
     full = torch.empty(M, N, dtype=torch.float32, device=dev())
-    K().linear_with("gemv", a, w, None, full)
+    K().linear_with(which, a, w, None, full)
     one = torch.empty(1, N, dtype=torch.float32, device=dev())
-    K().linear_with("gemv", a[M - 1:M].contiguous(), w, None, one)
+    K().linear_with(which, a[M - 1:M].contiguous(), w, None, one)
     assert torch.equal(one[0], full[M - 1])
+    torch.cuda.synchronize()
+    assert K().library().li_tcgen05_status() == 0, "a wait inside a tcgen05 kernel ran out"
 
 
 TC_SHAPES = [(128, 128, 64), (128, 128, 512), (256, 384, 1536), (2048, 2048, 1536), (17, 100, 72), (130, 200, 272), (300, 136, 40),
@@ -160,6 +163,8 @@ def test_linear_tcgen05_kernel(shape):
 
 
 @pytest.mark.parametrize("which,shape", [("gemv", (1, 256, 64)), ("gemv", (8, 17920, 1536)), ("gemv", (40, 544, 96)), ("gemv", (16, 352, 80)),
+                                         ("gemv_tcgen05", (1, 256, 64)), ("gemv_tcgen05", (8, 17920, 1536)), ("gemv_tcgen05", (40, 544, 96)),
+                                         ("gemv_tcgen05", (16, 352, 80)), ("gemv_tcgen05", (64, 3072, 8960)),
                                          ("tcgen05", (128, 256, 64)), ("tcgen05", (300, 544, 96)), ("tcgen05", (2048, 17920, 1536)),
                                          ("tcgen05", (77, 352, 80)), ("tcgen05", (65, 48, 40))])
 def test_linear_swiglu_epilogue(which, shape):
