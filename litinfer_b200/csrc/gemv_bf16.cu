@@ -21,6 +21,7 @@
 //
 // Requires K % 8 == 0 and 16-byte aligned operands; M <= 64.
 #include "common.cuh"
+#include "no_alloc.h"
 
 namespace {
 
@@ -272,4 +273,75 @@ int li_linear_gemv_bf16(const void* a, const void* w, const float* bias, void* o
     if (dtype_out == LI_BF16) return launch_nt<bf16, false>(a, w, bias, out, M, N, K, stream);
     if (dtype_out == LI_F32) return launch_nt<float, false>(a, w, bias, out, M, N, K, stream);
     return li_fail("linear (gemv): unsupported output dtype %d", dtype_out);
+}
+
+// ---- the entry point that allocates nothing (no_alloc.h) ---------------------------------
+
+namespace {
+
+// Scratch of li_linear_gemv_static.  In host code these names are stand-ins, not device
+// addresses: the addresses come from cudaGetSymbolAddress, once per device.
+static __device__ __align__(256) float g_static_partial[LI_STATIC_PARTIAL_FLOATS];
+static __device__ __align__(256) unsigned g_static_counters[LI_STATIC_TILES];
+
+Workspace g_static_ws[16];
+
+int static_workspace(Workspace** ws) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return li_fail("linear (gemv, static scratch): cudaGetDevice: %s", cudaGetErrorString(e));
+    LI_REQUIRE(dev >= 0 && dev < 16, "linear (gemv, static scratch): device index %d out of range", dev);
+    Workspace& w = g_static_ws[dev];
+    if (!w.partial) {
+        // first call on this device (it is the current one): ask where the arrays live on it
+        void *p = nullptr, *c = nullptr;
+        e = cudaGetSymbolAddress(&p, g_static_partial);
+        if (e != cudaSuccess) return li_fail("linear (gemv, static scratch): cudaGetSymbolAddress(partial): %s", cudaGetErrorString(e));
+        e = cudaGetSymbolAddress(&c, g_static_counters);
+        if (e != cudaSuccess) return li_fail("linear (gemv, static scratch): cudaGetSymbolAddress(counters): %s", cudaGetErrorString(e));
+        w.counters = static_cast<unsigned*>(c);
+        w.partial = static_cast<float*>(p);
+    }
+    *ws = &w;
+    return 0;
+}
+
+template <int NT, typename Tout>
+int launch_static(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
+    const int ntiles = ceil_div(N, 16);
+    int warps = 4, ksplit = 1;
+    choose_shape(ntiles, K, NT, &warps, &ksplit);
+    Workspace* ws = nullptr;
+    if (int rc = static_workspace(&ws)) return rc;
+    if (ksplit > 1) {
+        LI_REQUIRE(ntiles <= LI_STATIC_TILES && (size_t)ksplit * ntiles * NT * 128 <= LI_STATIC_PARTIAL_FLOATS,
+                   "linear (gemv, static scratch): M=%d N=%d K=%d needs %zu floats of partial sums and %d counters; the built-in scratch holds %u and %d",
+                   M, N, K, (size_t)ksplit * ntiles * NT * 128, ntiles, (unsigned)LI_STATIC_PARTIAL_FLOATS, LI_STATIC_TILES);
+        // the arrays keep what the last call left: the counters of this call's tiles start at zero
+        cudaError_t e = cudaMemsetAsync(ws->counters, 0, (size_t)ntiles * sizeof(unsigned), stream);
+        if (e != cudaSuccess) return li_fail("linear (gemv, static scratch): clearing the counters: %s", cudaGetErrorString(e));
+    }
+    if (warps == 16) return launch_kernel<NT, 16, Tout, false>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+    if (warps >= 8) return launch_kernel<NT, 8, Tout, false>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+    return launch_kernel<NT, 4, Tout, false>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+}
+
+template <typename Tout>
+int launch_static_nt(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
+    if (M <= 8) return launch_static<1, Tout>(a, w, bias, out, M, N, K, stream);
+    if (M <= 16) return launch_static<2, Tout>(a, w, bias, out, M, N, K, stream);
+    if (M <= 32) return launch_static<4, Tout>(a, w, bias, out, M, N, K, stream);
+    return launch_static<8, Tout>(a, w, bias, out, M, N, K, stream);
+}
+
+}  // namespace
+
+LI_EXPORT int li_linear_gemv_static(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
+                                    cudaStream_t stream) {
+    LI_REQUIRE(a && w && out, "linear (gemv, static scratch): null operand");
+    LI_REQUIRE(li_gemv_bf16_accepts(M, N, K), "linear (gemv, static scratch): refuses M=%d N=%d K=%d (1 <= M <= %d, K a multiple of 8)", M, N, K, kMaxM);
+    LI_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear (gemv, static scratch): operands must be 16-byte aligned");
+    if (dtype_out == LI_BF16) return launch_static_nt<bf16>(a, w, bias, out, M, N, K, stream);
+    if (dtype_out == LI_F32) return launch_static_nt<float>(a, w, bias, out, M, N, K, stream);
+    return li_fail("linear (gemv, static scratch): unsupported output dtype %d", dtype_out);
 }
