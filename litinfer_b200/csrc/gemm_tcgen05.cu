@@ -3,12 +3,18 @@
 // and the float accumulator in tensor memory.  The prefill path of every
 // projection (q|k|v, o, gate|up, down, lm_head).
 //
-// One CTA computes a 128 x BN tile (BN = 128).  Roles, by warp:
-//   warp 0   producer: one lane issues the TMA loads of a 128 x 64 tile of a and
+// One CTA computes a BM x BN tile: 128 x 128 with a ring of 6 stages, or 256 x 256
+// (two accumulators of 128 lanes x 256 columns: all of tensor memory) with 3
+// stages.  A multiprocessor takes in operand bytes at a limited rate (about
+// 90 GB/s measured here); a 128 x 128 tile needs 32 KB per 256 tensor-core
+// cycles and is bound by that, a 256 x 256 tile needs 64 KB per 1024 cycles.
+// The large tile is used where it still fills the GPU (wide products: gate|up,
+// lm_head of many rows).  Roles, by warp:
+//   warp 0   producer: one lane issues the TMA loads of a BM x 64 tile of a and
 //            a BN x 64 tile of w per k-block (64 bfloat16 = one 128-byte swizzle
 //            row) into a ring of stages, each guarded by a full/empty mbarrier pair;
-//   warp 1   allocates BN columns of tensor memory; one lane issues four
-//            tcgen05.mma (M 128, N BN, K 16) per k-block, commits the stage's
+//   warp 1   allocates tensor memory; one lane issues four tcgen05.mma (M 128,
+//            N BN, K 16) per k-block and 128 rows of a, commits the stage's
 //            empty barrier, and at the end the accumulator's barrier;
 //   warps 2-5 epilogue: tcgen05.ld of their quarter of the 128 lanes, bias in
 //            float, one rounding, stores to global memory.
@@ -27,27 +33,36 @@ namespace {
 
 using namespace tc;
 
-constexpr int BM = 128, BN = 128;
-constexpr int kStages = 6;
-constexpr int kStageBytesA = BM * BK * 2, kStageBytesB = BN * BK * 2;
 constexpr int kThreads = 192;
 
+template <int BM, int BN>
+struct Tile {
+    static constexpr int kStages = (BM + BN) <= 256 ? 6 : 3;
+    static constexpr int kBytesA = BM * BK * 2, kBytesB = BN * BK * 2;
+    static constexpr unsigned kCols = (BM / 128) * BN;          // tensor-memory columns: one accumulator per 128 rows
+};
+
+template <int BM, int BN>
 struct __align__(1024) SharedStorage {
-    unsigned char a[kStages][kStageBytesA];
-    unsigned char b[kStages][kStageBytesB];
-    unsigned long long full[kStages];
-    unsigned long long empty[kStages];
+    unsigned char a[Tile<BM, BN>::kStages][Tile<BM, BN>::kBytesA];
+    unsigned char b[Tile<BM, BN>::kStages][Tile<BM, BN>::kBytesB];
+    unsigned long long full[Tile<BM, BN>::kStages];
+    unsigned long long empty[Tile<BM, BN>::kStages];
     unsigned long long accum;
     unsigned tmem_base;
     int failed;
 };
 
-template <typename Tout, bool kSwiglu>
+template <int BM, int BN, typename Tout, bool kSwiglu>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag) {
     extern __shared__ unsigned char smem_raw[];
-    SharedStorage& sm = *reinterpret_cast<SharedStorage*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    using SS = SharedStorage<BM, BN>;
+    constexpr int kStages = Tile<BM, BN>::kStages;
+    constexpr int kStageBytesA = Tile<BM, BN>::kBytesA, kStageBytesB = Tile<BM, BN>::kBytesB;
+    constexpr unsigned kCols = Tile<BM, BN>::kCols;
+    SS& sm = *reinterpret_cast<SS*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int nkb = (K + BK - 1) / BK;
@@ -62,7 +77,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"((unsigned)BN)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kCols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -95,7 +110,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            const unsigned idesc = umma_idesc(BM, BN);
+            const unsigned idesc = umma_idesc(128, BN);
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % kStages;
@@ -106,7 +121,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const unsigned long long da = umma_desc(sm.a[s]), db = umma_desc(sm.b[s]);
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k)
-                    umma_bf16(tmem_acc, da + (unsigned long long)(k * 2), db + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
+#pragma unroll
+                    for (int half = 0; half < BM / 128; ++half)       // rows 128 half .. of the a tile: 128 rows x 128 bytes further on
+                        umma_bf16(tmem_acc + (unsigned)(half * BN), da + (unsigned long long)(k * 2 + half * (128 * 128 / 16)),
+                                  db + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
                 umma_commit(&sm.empty[s]);
             }
             if (ok) {
@@ -124,11 +142,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (lane == 0) atomicExch(error_flag, 3);
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
+            for (int hc = 0; hc < (BM / 128) * (BN / 32); ++hc) {
+                const int half = hc / (BN / 32), c = (hc - half * (BN / 32)) * 32;
+                const int row = m0 + half * 128 + quarter * 32 + lane;
                 float v[32];
-                tmem_ld_32x32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)c, v);
+                tmem_ld_32x32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)(half * BN + c), v);
                 const int col0 = n0 + c;
                 if (kSwiglu) {
                     // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 activations up * gate / (1 + exp(-gate))
@@ -204,16 +223,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((unsigned)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kCols) : "memory");
     }
 }
 
 // ---- host side -----------------------------------------------------------
 
-bool g_attr_set[3] = {false, false, false};
-
-template <typename Tout, bool kSwiglu>
-int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int which) {
+template <int BM, int BN, typename Tout, bool kSwiglu>
+int launch_tile(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
     EncodeTiledFn encode = nullptr;
     int *g_error_host = nullptr, *g_error_dev = nullptr;
     if (int rc = setup(&encode, &g_error_host, &g_error_dev)) return rc;
@@ -222,19 +239,35 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     CUtensorMap map_a, map_w;
     if (int rc = make_map(&map_a, a, M, K, BM)) return rc;
     if (int rc = make_map(&map_w, w, N, K, BN)) return rc;
-    const size_t smem = sizeof(SharedStorage) + 1024;
-    if (!g_attr_set[which]) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<Tout, kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = sizeof(SharedStorage<BM, BN>) + 1024;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
-        g_attr_set[which] = true;
+        raised = true;
     }
     dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
     LI_REQUIRE(grid.y <= 65535, "linear (tcgen05): M=%d is too large for one launch", M);
-    gemm_tcgen05_kernel<Tout, kSwiglu><<<grid, kThreads, smem, stream>>>(map_a, map_w, bias, (Tout*)out, M, N, K, g_error_dev);
+    gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu><<<grid, kThreads, smem, stream>>>(map_a, map_w, bias, (Tout*)out, M, N, K, g_error_dev);
     return li_check_launch("linear (tcgen05)");
 }
 
+// 256 x 256 tiles where they still fill most of the GPU (measured: better from about 120 CTAs on), else 128 x 128.
+// tile: 0 chooses, 1 forces the small tile, 2 the large one (for tests and measurements).
+template <typename Tout, bool kSwiglu>
+int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int tile) {
+    const long long big_ctas = (long long)ceil_div(M, 256) * ceil_div(N, 256);
+    const bool big = tile == 2 || (tile == 0 && big_ctas >= 120);
+    if (big) return launch_tile<256, 256, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
+    return launch_tile<128, 128, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
+}
+
+int g_forced_tile = 0;
+
 }  // namespace
+
+// 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always.  For tests and measurements.
+LI_EXPORT void li_tcgen05_force_tile(int tile) { g_forced_tile = tile; }
 
 bool li_tcgen05_accepts(const void* a, const void* w, const void* out, int dtype_out, int M, int N, int K) {
     return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0) &&
@@ -246,9 +279,9 @@ int li_linear_tcgen05(const void* a, const void* w, const float* bias, void* out
     if (epilogue == LI_EPILOGUE_SWIGLU) {
         LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
                    "linear (tcgen05): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
-        return launch<bf16, true>(a, w, bias, out, M, N, K, stream, 2);
+        return launch<bf16, true>(a, w, bias, out, M, N, K, stream, g_forced_tile);
     }
-    if (dtype_out == LI_BF16) return launch<bf16, false>(a, w, bias, out, M, N, K, stream, 0);
-    if (dtype_out == LI_F32) return launch<float, false>(a, w, bias, out, M, N, K, stream, 1);
+    if (dtype_out == LI_BF16) return launch<bf16, false>(a, w, bias, out, M, N, K, stream, g_forced_tile);
+    if (dtype_out == LI_F32) return launch<float, false>(a, w, bias, out, M, N, K, stream, g_forced_tile);
     return li_fail("linear (tcgen05): unsupported output dtype %d", dtype_out);
 }

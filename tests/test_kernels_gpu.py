@@ -145,8 +145,17 @@ TC_SHAPES = [(128, 128, 64), (128, 128, 512), (256, 384, 1536), (2048, 2048, 153
              (1000, 389, 96), (64, 1536, 8960), (2048, 1536, 8960), (5, 151936, 1536)]
 
 
+@pytest.fixture(params=[1, 2], ids=["tile128", "tile256"])
+def forced_tile(request):
+    """Both tile sizes of the tcgen05 kernel, whatever it would choose for the shape itself."""
+    lib = K().library()
+    lib.li_tcgen05_force_tile(request.param)
+    yield request.param
+    lib.li_tcgen05_force_tile(0)
+
+
 @pytest.mark.parametrize("shape", TC_SHAPES)
-def test_linear_tcgen05_kernel(shape):
+def test_linear_tcgen05_kernel(shape, forced_tile):
     M, N, Kd = shape
     a = rnd(M, Kd, dtype=torch.bfloat16, seed=26)
     w = rnd(N, Kd, dtype=torch.bfloat16, seed=27, scale=0.05)
@@ -167,8 +176,10 @@ def test_linear_tcgen05_kernel(shape):
                                          ("gemv_tcgen05", (16, 352, 80)), ("gemv_tcgen05", (64, 3072, 8960)),
                                          ("tcgen05", (128, 256, 64)), ("tcgen05", (300, 544, 96)), ("tcgen05", (2048, 17920, 1536)),
                                          ("tcgen05", (77, 352, 80)), ("tcgen05", (65, 48, 40))])
-def test_linear_swiglu_epilogue(which, shape):
+def test_linear_swiglu_epilogue(which, shape, forced_tile):
     """gate and up rows interleaved in groups of 8; the product's epilogue applies up * silu(gate)."""
+    if which != "tcgen05" and forced_tile == 2:
+        pytest.skip("tile size is a property of the tcgen05 kernel")
     M, N, Kd = shape
     I = N // 2
     a = rnd(M, Kd, dtype=torch.bfloat16, seed=36)
