@@ -76,6 +76,16 @@ class Request:
     def num_tokens(self) -> int:
         return len(self.prompt) + len(self.generated)
 
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """tokens[start:start + count] without building the whole list."""
+        n = len(self.prompt)
+        stop = start + count
+        if stop <= n:
+            return self.prompt[start:stop]
+        if start >= n:
+            return self.generated[start - n:stop - n]
+        return self.prompt[start:] + self.generated[:stop - n]
+
     @property
     def num_cached(self) -> int:
         return self.cache.length if self.cache is not None else 0
@@ -94,7 +104,7 @@ class ScheduledItem:
 
     @property
     def tokens(self) -> List[int]:
-        return self.request.tokens[self.start:self.start + self.count]
+        return self.request.token_slice(self.start, self.count)
 
 
 class RequestRefused(ValueError):
