@@ -187,11 +187,20 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     __threadfence();
 #pragma unroll
                     for (int j = 0; j < BT; ++j) v[j] = 0.0f;
-                    for (int s = 0; s < ksplit; ++s) {
-                        const float* src = partial + (((size_t)s * tiles + tile) * BT) * BR + r_in_tile;
+                    // several splits' loads in flight at once (64 values a thread), added in split order
+                    constexpr int SU = 64 / BT;
+                    for (int s0 = 0; s0 < ksplit; s0 += SU) {
+                        float p[SU][BT];
 #pragma unroll
-                        for (int j = 0; j < BT; ++j)
-                            if (j < M) v[j] += __ldcg(src + (size_t)j * BR);
+                        for (int u = 0; u < SU; ++u) {
+                            const float* src = partial + (((size_t)(s0 + u) * tiles + tile) * BT) * BR + r_in_tile;
+#pragma unroll
+                            for (int j = 0; j < BT; ++j) p[u][j] = (s0 + u < ksplit && j < M) ? __ldcg(src + (size_t)j * BR) : 0.0f;
+                        }
+#pragma unroll
+                        for (int u = 0; u < SU; ++u)
+#pragma unroll
+                            for (int j = 0; j < BT; ++j) v[j] += p[u][j];
                     }
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (warp == 2 && lane == 0) counters[tile] = 0;          // ready for the next launch on this stream

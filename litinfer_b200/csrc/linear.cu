@@ -31,9 +31,12 @@ LI_EXPORT int li_linear(const void* a, const void* w, const float* bias, void* o
     if (M == 0) return 0;
     if (dtype_in == LI_BF16) {
         const bool aligned = ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
-        // few rows (decode): wide matrices (at least 96 tiles of 128 rows: gate|up, lm_head) stream best through TMA and the
-        // swapped tcgen05 kernel; narrow ones would need a split of k there, which the register-fed kernel does with less latency
-        if (aligned && M <= 64 && (N + 127) / 128 >= 96 && li_gemv_tcgen05_accepts(a, w, M, N, K))
+        // few rows (decode): wide matrices (at least 96 tiles of 128 rows: gate|up, lm_head) and narrow ones with a long k
+        // (down) stream best through TMA and the swapped tcgen05 kernel; narrow and short ones (q|k|v, o) would be cut into
+        // splits of two or three k-blocks there, which the register-fed kernel does with less latency
+        const bool wide = (N + 127) / 128 >= 96;                   // fills the GPU without a split of k
+        const bool long_k = (K + 63) / 64 >= 64 && M <= 32;        // a split of k leaves every CTA enough to stream (measured: down projection)
+        if (aligned && M <= 64 && (wide || long_k) && li_gemv_tcgen05_accepts(a, w, M, N, K))
             return li_linear_gemv_tcgen05(a, w, bias, out, dtype_out, M, N, K, epilogue, stream);
         if (aligned && li_gemv_bf16_accepts(M, N, K)) return li_linear_gemv_bf16(a, w, bias, out, dtype_out, M, N, K, epilogue, stream);
         if (li_tcgen05_accepts(a, w, out, dtype_out, M, N, K)) return li_linear_tcgen05(a, w, bias, out, dtype_out, M, N, K, epilogue, stream);
