@@ -157,6 +157,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     float* l_sm = sm + (size_t)G * nact;               // [G] denominators
     __syncthreads();
     for (int r = warp; r < G; r += kWarps) {
+        // one warp per head: maxima and denominators of up to 32 splits per round of loads
         const float* base = part + ((size_t)s * nh + kvh * G + r) * nsplit * (DH + 2);
         float M = -INFINITY;
         for (int sp = first + lane; sp <= last; sp += 32) M = fmaxf(M, __ldcg(base + (size_t)sp * (DH + 2) + DH));
@@ -165,29 +166,51 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
         for (int sp0 = first; sp0 <= last; sp0 += 32) {        // ascending split order within each lane
             const int sp = sp0 + lane;
             if (sp <= last) {
-                const float f = expf(__ldcg(base + (size_t)sp * (DH + 2) + DH) - M);
+                const float m = __ldcg(base + (size_t)sp * (DH + 2) + DH), l = __ldcg(base + (size_t)sp * (DH + 2) + DH + 1);
+                const float f = expf(m - M);
                 f_sm[r * nact + sp - first] = f;
-                L += __ldcg(base + (size_t)sp * (DH + 2) + DH + 1) * f;
+                L += l * f;
             }
         }
         L = warp_sum(L);
         if (lane == 0) l_sm[r] = L;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e < G * DH; e += kWarps * 32) {
-        const int r = e / DH, d = e - r * DH;
-        const float* base = part + ((size_t)s * nh + kvh * G + r) * nsplit * (DH + 2) + d;
-        const float* f = f_sm + r * nact;
-        float O = 0.0f;
-        for (int i = 0; i < nact; i += 8) {
-            float v[8];
+    // the weighted sums: up to four outputs a thread at once, eight splits each, all their loads in flight together
+    constexpr int E = 4;
+    for (int e0 = threadIdx.x; e0 < G * DH; e0 += E * kWarps * 32) {
+        const float* src[E];
+        const float* fac[E];
+        float O[E];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = (i + u < nact) ? __ldcg(base + (size_t)(first + i + u) * (DH + 2)) : 0.0f;
-#pragma unroll
-            for (int u = 0; u < 8; ++u) O += (i + u < nact) ? v[u] * f[i + u] : 0.0f;
+        for (int q = 0; q < E; ++q) {
+            const int e = e0 + q * kWarps * 32;
+            const int r = e < G * DH ? e / DH : 0, d = e < G * DH ? e - r * DH : 0;
+            src[q] = part + ((size_t)s * nh + kvh * G + r) * nsplit * (DH + 2) + d;
+            fac[q] = f_sm + r * nact;
+            O[q] = 0.0f;
         }
-        const float L = l_sm[r];
-        out[((size_t)s * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+        for (int i = 0; i < nact; i += 8) {
+            float v[E][8];
+#pragma unroll
+            for (int q = 0; q < E; ++q)
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    v[q][u] = (i + u < nact && e0 + q * kWarps * 32 < G * DH) ? __ldcg(src[q] + (size_t)(first + i + u) * (DH + 2)) : 0.0f;
+#pragma unroll
+            for (int q = 0; q < E; ++q)
+#pragma unroll
+                for (int u = 0; u < 8; ++u) O[q] += (i + u < nact) ? v[q][u] * fac[q][i + u] : 0.0f;
+        }
+#pragma unroll
+        for (int q = 0; q < E; ++q) {
+            const int e = e0 + q * kWarps * 32;
+            if (e < G * DH) {
+                const int r = e / DH, d = e - r * DH;
+                const float L = l_sm[r];
+                out[((size_t)s * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O[q] / L : 0.0f);
+            }
+        }
     }
     if (threadIdx.x == 0) counters[s * nkv + kvh] = 0;          // ready for the next launch on this stream
 }
