@@ -51,6 +51,69 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Third epilogue: the product is the fused q|k|v projection and its epilogue is the rotary position
+// encoding plus the write of k and v into the paged cache (what rope.cu does as a kernel of its own).
+// For that the 16 rows of a tile are rows j .. j + 7 and j + head_dim / 2 .. j + head_dim / 2 + 7 of one
+// head: the two halves of a rotation pair end up as the element and its partner 64 places on.
+struct RopeArgs {
+    const int* positions;
+    const float* denom;
+    const int* slot_mapping;
+    bf16* kcache;
+    bf16* vcache;
+    int nh, nkv, dh, page_size, num_pages, write;
+};
+enum { kEpiNone = 0, kEpiSwiglu = 1, kEpiRope = 2 };
+
+template <int NT, typename Get>
+__device__ __forceinline__ void store_rope(Get get, const float* __restrict__ bias, bf16* __restrict__ out, int tile, int M, int N,
+                                           const RopeArgs& ra, int nthreads) {
+    const int tiles_per_head = ra.dh >> 4, half = ra.dh >> 1;
+    const int head = tile / tiles_per_head, jt = tile - head * tiles_per_head;
+    for (int q = threadIdx.x; q < NT * 64; q += nthreads) {
+        const int l = q & 31, i = (q >> 5) & 1, j = q >> 6;
+        const int e = (j * 4 + i) * 32 + l;
+        const int tok = j * 8 + ((l & 3) << 1) + i;
+        if (tok >= M) continue;
+        const int jj = jt * 8 + (l >> 2);                       // index of the pair within the head
+        const int r0 = head * ra.dh + jj, r1 = r0 + half;
+        float x0 = get(e), x1 = get(e + 64);
+        if (bias) {
+            x0 += bias[r0];
+            x1 += bias[r1];
+        }
+        float y0 = x0, y1 = x1;
+        if (head < ra.nh + ra.nkv) {
+            float sn, cs;
+            sincosf((float)ra.positions[tok] / ra.denom[jj], &sn, &cs);
+            // q and k are rounded to bfloat16 by the projection before they are rotated, as in the unfused path
+            x0 = __bfloat162float(__float2bfloat16_rn(x0));
+            x1 = __bfloat162float(__float2bfloat16_rn(x1));
+            y0 = x0 * cs - x1 * sn;
+            y1 = x1 * cs + x0 * sn;
+        }
+        if (head < ra.nh) {
+            out[(size_t)tok * N + r0] = __float2bfloat16_rn(y0);
+            out[(size_t)tok * N + r1] = __float2bfloat16_rn(y1);
+        } else if (ra.write) {
+            const int slot = ra.slot_mapping[tok];
+            const int page = slot / ra.page_size, off = slot - page * ra.page_size;
+            if (slot < 0 || page >= ra.num_pages) continue;        // validated on the host; never write outside the cache
+            if (head < ra.nh + ra.nkv) {
+                const int kvh = head - ra.nh;
+                bf16* dst = ra.kcache + (((size_t)page * ra.nkv + kvh) * ra.page_size + off) * ra.dh;
+                dst[jj] = __float2bfloat16_rn(y0);
+                dst[jj + half] = __float2bfloat16_rn(y1);
+            } else {
+                const int kvh = head - ra.nh - ra.nkv;
+                bf16* dst = ra.vcache + ((size_t)page * ra.nkv + kvh) * ra.dh * ra.page_size + off;      // values are cached transposed
+                dst[(size_t)jj * ra.page_size] = __float2bfloat16_rn(y0);
+                dst[(size_t)(jj + half) * ra.page_size] = __float2bfloat16_rn(y1);
+            }
+        }
+    }
+}
+
 // Epilogue of one reduced element.  e = (j * 4 + i) * 32 + lane stands for weight row
 // n0 + g + 8 (i >> 1) and token j * 8 + 2 t + (i & 1) with g = lane >> 2, t = lane & 3.
 // kSwiglu: the weight rows of a tile are 8 gate rows followed by the 8 up rows of the same
@@ -78,10 +141,11 @@ __device__ __forceinline__ void store_elements(Get get, const float* __restrict_
     }
 }
 
-template <int NT, int WARPS, typename Tout, bool kSwiglu>
+template <int NT, int WARPS, typename Tout, int kEpi>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias, Tout* __restrict__ out,
-                 float* __restrict__ partial, unsigned* __restrict__ counters, int M, int N, int K, int ksplit) {
+                 float* __restrict__ partial, unsigned* __restrict__ counters, int M, int N, int K, int ksplit, const RopeArgs rope) {
+    constexpr bool kSwiglu = kEpi == kEpiSwiglu;
     extern __shared__ float red_raw[];                 // [WARPS][NT * 128]
     float (*red)[NT * 128] = reinterpret_cast<float (*)[NT * 128]>(red_raw);
     __shared__ int is_last;
@@ -100,7 +164,13 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
 
-    const int r0 = n0 + g, r1 = n0 + g + 8;
+    int r0 = n0 + g, r1 = n0 + g + 8;
+    if (kEpi == kEpiRope) {
+        const int tiles_per_head = rope.dh >> 4;
+        const int head = tile / tiles_per_head, jt = tile - head * tiles_per_head;
+        r0 = head * rope.dh + jt * 8 + g;
+        r1 = r0 + (rope.dh >> 1);
+    }
     const bool v0 = r0 < N, v1 = r1 < N;
     const bf16* w0 = W + (size_t)(v0 ? r0 : 0) * K;
     const bf16* w1 = W + (size_t)(v1 ? r1 : 0) * K;
@@ -155,6 +225,10 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
         for (int w = 1; w < WARPS; ++w) v += red[w][e];
         return v;
     };
+    if (kEpi == kEpiRope) {
+        store_rope<NT>(warps_sum, bias, reinterpret_cast<bf16*>(out), tile, M, N, rope, WARPS * 32);       // never split along k
+        return;
+    }
     if (ksplit == 1) {
         store_elements<NT, Tout, kSwiglu>(warps_sum, bias, out, n0, M, N, WARPS * 32);
         return;
@@ -218,9 +292,10 @@ void choose_shape(int ntiles, int K, int nt, int* warps, int* ksplit) {
     *ksplit = ks;
 }
 
-template <int NT, int WARPS, typename Tout, bool kSwiglu>
+template <int NT, int WARPS, typename Tout, int kEpi>
 int launch_kernel(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, int ksplit, Workspace* ws,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
+    constexpr int kSwiglu = kEpi;
     dim3 grid(ceil_div(N, 16), ksplit);
     constexpr size_t smem = (size_t)WARPS * NT * 128 * sizeof(float);
     if (smem > 48 * 1024) {
@@ -232,7 +307,7 @@ int launch_kernel(const void* a, const void* w, const float* bias, void* out, in
         }
     }
     li_launch_pdl(gemv_bf16_kernel<NT, WARPS, Tout, kSwiglu>, grid, dim3(WARPS * 32), smem, stream, (const bf16*)a, (const bf16*)w, bias,
-                  (Tout*)out, ws->partial, ws->counters, M, N, K, ksplit);
+                  (Tout*)out, ws->partial, ws->counters, M, N, K, ksplit, rope);
     return li_check_launch("linear (gemv)");
 }
 
@@ -257,7 +332,36 @@ int launch_nt(const void* a, const void* w, const float* bias, void* out, int M,
     return launch<8, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
 }
 
+template <int NT>
+int launch_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const RopeArgs& rope, cudaStream_t stream) {
+    const int ntiles = ceil_div(N, 16);
+    int warps = 4, ksplit = 1;
+    choose_shape(ntiles, K, NT, &warps, &ksplit);
+    Workspace* ws = nullptr;
+    if (int rc = ensure_workspace(&ws)) return rc;
+    // the epilogue needs both halves of a pair in one CTA and the whole sum: no split along k
+    if (warps == 16) return launch_kernel<NT, 16, bf16, kEpiRope>(a, w, bias, out, M, N, K, 1, ws, stream, rope);
+    if (warps >= 8) return launch_kernel<NT, 8, bf16, kEpiRope>(a, w, bias, out, M, N, K, 1, ws, stream, rope);
+    return launch_kernel<NT, 4, bf16, kEpiRope>(a, w, bias, out, M, N, K, 1, ws, stream, rope);
+}
+
 }  // namespace
+
+// The fused q|k|v projection with rotary encoding and cache write in its epilogue, for few tokens.
+bool li_gemv_rope_accepts(const void* a, const void* w, int M, int N, int K, int nh, int nkv, int dh, int rotary_dim) {
+    return M >= 1 && M <= kMaxM && K % 8 == 0 && dh % 16 == 0 && rotary_dim == dh && N == (nh + 2 * nkv) * dh &&
+           ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);
+}
+
+int li_linear_gemv_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const int* positions,
+                        const float* denom, const int* slot_mapping, void* kcache, void* vcache, int nh, int nkv, int dh,
+                        int page_size, int num_pages, int write, cudaStream_t stream) {
+    RopeArgs ra{positions, denom, slot_mapping, (bf16*)kcache, (bf16*)vcache, nh, nkv, dh, page_size, num_pages, write};
+    if (M <= 8) return launch_rope<1>(a, w, bias, out, M, N, K, ra, stream);
+    if (M <= 16) return launch_rope<2>(a, w, bias, out, M, N, K, ra, stream);
+    if (M <= 32) return launch_rope<4>(a, w, bias, out, M, N, K, ra, stream);
+    return launch_rope<8>(a, w, bias, out, M, N, K, ra, stream);
+}
 
 bool li_gemv_bf16_accepts(int M, int N, int K) { return M >= 1 && M <= kMaxM && K % 8 == 0 && N >= 1; }
 

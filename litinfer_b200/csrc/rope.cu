@@ -82,3 +82,27 @@ LI_EXPORT int li_rope_kv_write(void* qkv, int dtype, const int* positions, const
         return li_fail("rope_kv_write: unknown dtype %d", dtype);
     return li_check_launch("rope_kv_write");
 }
+
+// The q|k|v projection followed by rope_kv_write.  For a few bfloat16 tokens (decode) both run as one
+// kernel: the weight-streaming product applies the rotation and writes the cache in its epilogue.
+// Otherwise: the product, then the kernel above.
+int li_linear_gemv_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const int* positions,
+                        const float* denom, const int* slot_mapping, void* kcache, void* vcache, int nh, int nkv, int dh,
+                        int page_size, int num_pages, int write, cudaStream_t stream);
+bool li_gemv_rope_accepts(const void* a, const void* w, int M, int N, int K, int nh, int nkv, int dh, int rotary_dim);
+extern "C" int li_linear(const void* a, const void* w, const float* bias, void* out, int dtype_in, int dtype_out, int M, int N, int K,
+                         int epilogue, cudaStream_t stream);
+
+LI_EXPORT int li_linear_rope_kv(const void* a, const void* w, const float* bias, void* qkv, int dtype, const int* positions,
+                                const float* denom, int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T,
+                                int K, int nh, int nkv, int dh, int page_size, int num_pages, int write, int allow_fused,
+                                cudaStream_t stream) {
+    const int N = (nh + 2 * nkv) * dh;
+    if (T == 0) return 0;
+    if (allow_fused && dtype == LI_BF16 && li_gemv_rope_accepts(a, w, T, N, K, nh, nkv, dh, rotary_dim))
+        return li_linear_gemv_rope(a, w, bias, qkv, T, N, K, positions, denom, slot_mapping, kcache, vcache, nh, nkv, dh, page_size,
+                                   num_pages, write, stream);
+    if (int rc = li_linear(a, w, bias, qkv, dtype, dtype, T, N, K, LI_EPILOGUE_NONE, stream)) return rc;
+    return li_rope_kv_write(qkv, dtype, positions, denom, rotary_dim, slot_mapping, kcache, vcache, T, nh, nkv, dh, page_size, num_pages,
+                            write, stream);
+}

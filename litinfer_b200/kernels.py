@@ -215,6 +215,35 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torc
         "rope_kv_write")
 
 
+def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], qkv: torch.Tensor,
+                   positions: torch.Tensor, denominators: torch.Tensor, rotary_dim: int, slot_mapping: torch.Tensor,
+                   k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                   write: bool = True, fused: bool = True) -> None:
+    """The fused q|k|v projection followed by :func:`rope_kv_write`: ``qkv = a weight^T + bias``, q rotated in
+    place, k rotated and v stored into the caches.  Keys and values are only guaranteed to be in the caches
+    afterwards, not in ``qkv``.  For a few bfloat16 tokens both steps run as one kernel (the rotation is the
+    product's epilogue); ``fused=False`` forces two kernels, for tests."""
+    T, Kd = a.shape
+    N = (num_heads + 2 * num_kv_heads) * head_dim
+    _need(a, "linear input")
+    _need(weight, "qkv weight", a.dtype, (N, Kd))
+    if bias is not None:
+        _need(bias, "qkv bias", torch.float32, (N,))
+    _need(qkv, "qkv", a.dtype, (T, N))
+    _need(positions, "positions", torch.int32, (T,))
+    _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
+    _need(slot_mapping, "slot mapping", torch.int32, (T,))
+    _need(k_cache, "key cache", a.dtype)
+    pages, nkv, page_size, dh = k_cache.shape
+    _need(v_cache, "value cache", a.dtype, (pages, nkv, dh, page_size))
+    if nkv != num_kv_heads or dh != head_dim:
+        raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
+    _check(library().li_linear_rope_kv(
+        _p(a), _p(weight), _p(bias), _p(qkv), _i(_dt(a)), _p(positions), _p(denominators), _i(rotary_dim), _p(slot_mapping),
+        _p(k_cache), _p(v_cache), _i(T), _i(Kd), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages),
+        _i(1 if write else 0), _i(1 if fused else 0), _stream(qkv)), "linear_rope_kv")
+
+
 ATTENTION_IMPLEMENTATIONS = {"general": 0, "decode": 1, "prefill": 2}
 
 

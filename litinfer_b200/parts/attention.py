@@ -57,12 +57,12 @@ class PagedAttention(Mixer):
         return PagedKV(self.num_kv_heads, self.head_dim, self.window)
 
     def forward(self, h, ctx, cache):
-        qkv = self.qkv(h)                                   # [T, (heads + 2 kv_heads) * head_dim]
         view = ctx.group(cache.group)
-        K.rope_kv_write(
-            qkv, ctx.positions, self.position.denominators, self.position.rotary_dim,
-            view.slot_mapping, cache.k, cache.v,
-            self.num_heads, self.num_kv_heads, self.head_dim, cache.writes)
+        qkv = torch.empty((h.shape[0], self.qkv.out_features), dtype=self.dtype, device=h.device)
+        # projection, position encoding of q and k, k and v into the cache: one call (and for few tokens one kernel)
+        K.linear_rope_kv(
+            h, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, self.position.denominators, self.position.rotary_dim,
+            view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, cache.writes)
         o = torch.empty((h.shape[0], self.q_dim), dtype=self.dtype, device=h.device)
         K.paged_attention(
             qkv, o, cache.k, cache.v, view.block_table, ctx.q_start, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,

@@ -93,6 +93,12 @@ def rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cach
     v_cache[page, :, :, off] = v         # values are cached transposed: [page, kv_head, head_dim, slot]
 
 
+def linear_rope_kv(a, weight, bias, qkv, positions, denominators, rotary_dim, slot_mapping, k_cache, v_cache,
+                   num_heads, num_kv_heads, head_dim, write=True, fused=True):
+    linear(a, weight, bias, qkv)
+    rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write)
+
+
 def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
                     num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None):
     T = qkv.shape[0]
@@ -197,5 +203,5 @@ def sample(logits, params, out):
     out.copy_(torch.tensor(res, dtype=torch.int32))
 
 
-ALL = ["interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
+ALL = ["linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]

@@ -236,6 +236,43 @@ def test_rope_kv_write(dtype, cfg):
     assert not kc3.any() and not vc3.any()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cfg", [(4, 2, 16, 64, 5), (12, 2, 128, 1536, 8), (3, 1, 32, 96, 1), (6, 2, 48, 80, 20), (14, 2, 80, 136, 64), (12, 2, 128, 1536, 70)])
+def test_linear_rope_kv_fused(dtype, cfg):
+    """Projection, rotation and cache write as one call; for few bfloat16 tokens one kernel, the rotation in the
+    product's epilogue.  Against the reference, and against the same call forced through separate kernels."""
+    nh, nkv, dh, H, T = cfg
+    N = (nh + 2 * nkv) * dh
+    pages, page = 9, 16
+    a = rnd(T, H, dtype=dtype, seed=51)
+    w = rnd(N, H, dtype=dtype, seed=52, scale=0.1)
+    b = rnd(N, seed=53, scale=0.5)
+    g = torch.Generator().manual_seed(54)
+    positions = torch.randint(0, 3000, (T,), generator=g).to(torch.int32).to(dev())
+    slots = torch.randperm(pages * page, generator=g)[:T].to(torch.int32).to(dev())
+    denom = torch.pow(torch.tensor(10000.0), torch.arange(dh // 2, dtype=torch.float32) * 2.0 / dh).to(dev())
+
+    def run(fn, **kw):
+        qkv = torch.zeros(T, N, dtype=dtype, device=dev())
+        kc = torch.zeros(pages, nkv, page, dh, dtype=dtype, device=dev())
+        vc = torch.zeros(pages, nkv, dh, page, dtype=dtype, device=dev())
+        fn(a, w, b, qkv, positions, denom, dh, slots, kc, vc, nh, nkv, dh, True, **kw)
+        return qkv[:, :nh * dh].clone(), kc, vc
+
+    q1, k1, v1 = run(K().linear_rope_kv)
+    q2, k2, v2 = run(K().linear_rope_kv, fused=False)
+    q3, k3, v3 = run(R.linear_rope_kv)
+    for got, ref, what in ((q1, q3, "q"), (k1, k3, "k cache"), (v1, v3, "v cache"), (q2, q3, "q unfused"), (k2, k3, "k unfused")):
+        close(got, ref, dtype, f"linear_rope_kv {what} {cfg}", f32_tol=5e-4)
+    # without writing: caches untouched
+    kc = torch.zeros(pages, nkv, page, dh, dtype=dtype, device=dev())
+    vc = torch.zeros(pages, nkv, dh, page, dtype=dtype, device=dev())
+    qkv = torch.zeros(T, N, dtype=dtype, device=dev())
+    K().linear_rope_kv(a, w, b, qkv, positions, denom, dh, slots, kc, vc, nh, nkv, dh, False)
+    assert not kc.any() and not vc.any()
+    close(qkv[:, :nh * dh], q3, dtype, "q without cache write", f32_tol=5e-4)
+
+
 # --------------------------------------------------------------------------
 # attention
 # --------------------------------------------------------------------------
