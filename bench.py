@@ -307,8 +307,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"],
-                    help="measure one part and print a short line (for profiling runs)")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels-decode", "kernels-prefill"],
+                    help="measure one part and print a short line (for profiling runs); kernels-*: a table of the "
+                         "kernels' device times from torch.profiler")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (so that a profiler lists them)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     args = ap.parse_args()
@@ -339,6 +340,21 @@ def main() -> int:
     wbytes = weight_bytes(model)
     kv_per_token = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
 
+    if args.only in ("kernels-decode", "kernels-prefill"):
+        from torch.profiler import ProfilerActivity, profile
+
+        if args.only == "kernels-decode":
+            time_decode(model, args.batch, args.context, 8, warmup)             # builds the graph, warms up
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                r = time_decode(model, args.batch, args.context, args.steps, warmup)
+            print(json.dumps({"only": args.only, "batch": args.batch, "steps": args.steps + warmup, **{k: round(v, 4) for k, v in r.items()}}))
+        else:
+            time_prefill(model, args.prefill_tokens, repeats=1)
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                ms = time_prefill(model, args.prefill_tokens, repeats=1)
+            print(json.dumps({"only": args.only, "tokens": args.prefill_tokens, "ms": round(ms, 3), "runs_in_table": 3}))
+        print(prof.key_averages().table(sort_by="cuda_time_total", row_limit=16, max_name_column_width=70))
+        return 0
     if args.only == "decode":
         r = time_decode(model, args.batch, args.context, args.steps, warmup, graphs=not args.no_graphs)
         print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context, "layers_run": cfg["num_hidden_layers"],

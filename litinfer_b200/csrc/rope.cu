@@ -15,48 +15,107 @@
 
 namespace {
 
-// One block per (token, head): query heads first, then key/value heads.  A thread owns the
-// pair (j, j + half) of its head, so sine and cosine are computed once per pair and nothing is
-// shared; blocks are small and many, which keeps the latency of a decode step's launch short.
+// A block takes one token and ``heads_per_block`` of its heads (query heads first, then key heads); a thread
+// owns pairs (j, j + half), so nothing is shared.  Few tokens (decode): one head a block, small and many
+// blocks, short latency.  Many tokens (prefill): all heads of a token in one block, fewer and fuller blocks.
 template <typename T>
 __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ denom,
                                      int rotary_dim, const int* __restrict__ slot_mapping, T* __restrict__ kcache,
-                                     T* __restrict__ vcache, int nh, int nkv, int dh, int page_size, int num_pages, int write) {
+                                     T* __restrict__ vcache, int nh, int nkv, int dh, int page_size, int num_pages, int write,
+                                     int write_v, int heads_per_block) {
     pdl_launch_dependents();
     pdl_wait();
-    const int t = blockIdx.x, head = blockIdx.y;
+    const int t = blockIdx.x;
     const int half = rotary_dim >> 1;
     const float pos = (float)positions[t];
     T* row = qkv + (size_t)t * (nh + 2 * nkv) * dh;
-    if (head < nh) {
-        T* x = row + (size_t)head * dh;
-        for (int j = threadIdx.x; j < half; j += blockDim.x) {
-            float s, c;
-            sincosf(pos / denom[j], &s, &c);
+    const int head_lo = blockIdx.y * heads_per_block;
+    const int head_hi = min(nh + nkv, head_lo + heads_per_block);
+    int page = 0, off = 0;
+    bool slot_ok = false;
+    if (write && head_hi > nh) {
+        const int slot = slot_mapping[t];
+        page = slot / page_size;
+        off = slot - page * page_size;
+        slot_ok = slot >= 0 && page < num_pages;       // validated on the host; never write outside the cache
+    }
+    // rotation pairs of the block's heads, spread over its threads
+    const int nheads = head_hi - head_lo;
+    for (int i = threadIdx.x; i < nheads * half; i += blockDim.x) {
+        const int hl = i / half, j = i - hl * half;
+        const int head = head_lo + hl;
+        float s, c;
+        sincosf(pos / denom[j], &s, &c);
+        if (head < nh) {
+            T* x = row + (size_t)head * dh;
             const float a = to_float(x[j]), b = to_float(x[j + half]);
             x[j] = from_float<T>(a * c - b * s);
             x[j + half] = from_float<T>(b * c + a * s);
+        } else if (slot_ok) {
+            const int h = head - nh;
+            const T* k = row + (size_t)head * dh;
+            T* kdst = kcache + (((size_t)page * nkv + h) * page_size + off) * dh;
+            const float a = to_float(k[j]), b = to_float(k[j + half]);
+            kdst[j] = from_float<T>(a * c - b * s);
+            kdst[j + half] = from_float<T>(b * c + a * s);
         }
-        return;
     }
-    if (!write) return;
-    const int h = head - nh;
-    const int slot = slot_mapping[t];
-    const int page = slot / page_size, off = slot - page * page_size;
-    if (slot < 0 || page >= num_pages) return;       // validated on the host; never write outside the cache
-    const T* k = row + (size_t)(nh + h) * dh;
-    const T* v = row + (size_t)(nh + nkv + h) * dh;
-    T* kdst = kcache + (((size_t)page * nkv + h) * page_size + off) * dh;
-    T* vdst = vcache + ((size_t)page * nkv + h) * dh * page_size + off;      // values are cached transposed
-    for (int j = threadIdx.x; j < half; j += blockDim.x) {
-        float s, c;
-        sincosf(pos / denom[j], &s, &c);
-        const float a = to_float(k[j]), b = to_float(k[j + half]);
-        kdst[j] = from_float<T>(a * c - b * s);
-        kdst[j + half] = from_float<T>(b * c + a * s);
+    if (!slot_ok) return;
+    for (int head = max(head_lo, nh); head < head_hi; ++head) {
+        const int h = head - nh;
+        const T* k = row + (size_t)head * dh;
+        const T* v = row + (size_t)(nh + nkv + h) * dh;
+        T* kdst = kcache + (((size_t)page * nkv + h) * page_size + off) * dh;
+        T* vdst = vcache + ((size_t)page * nkv + h) * dh * page_size + off;      // values are cached transposed
+        for (int d = rotary_dim + threadIdx.x; d < dh; d += blockDim.x) kdst[d] = k[d];
+        if (write_v)
+            for (int d = threadIdx.x; d < dh; d += blockDim.x) vdst[(size_t)d * page_size] = v[d];
     }
-    for (int d = rotary_dim + threadIdx.x; d < dh; d += blockDim.x) kdst[d] = k[d];
-    for (int d = threadIdx.x; d < dh; d += blockDim.x) vdst[(size_t)d * page_size] = v[d];
+}
+
+// The values of many tokens (prefill) into the transposed cache, 16 tokens and one key/value head per block:
+// the tile goes through shared memory, so that each output column's 16 slots are written as one 32-byte
+// piece when the 16 tokens sit in consecutive slots of one page (the usual case), instead of 16 scattered
+// two-byte writes.  Tokens whose slots are not such a run are written one by one.
+template <typename T>
+__global__ void v_cache_write_kernel(const T* __restrict__ qkv, const int* __restrict__ slot_mapping, T* __restrict__ vcache,
+                                     int total, int nh, int nkv, int dh, int page_size, int num_pages) {
+    extern __shared__ __align__(16) unsigned char vt_raw[];
+    T* vt = reinterpret_cast<T*>(vt_raw);              // [dh][16 + 2]: padded against bank conflicts
+    __shared__ int slots[16];
+    constexpr int LD = 18;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * 16, h = blockIdx.y;
+    const int n = min(16, total - t0);
+    const int row = (nh + 2 * nkv) * dh;
+    if (threadIdx.x < 16) slots[threadIdx.x] = threadIdx.x < n ? slot_mapping[t0 + threadIdx.x] : -1;
+    for (int i = threadIdx.x; i < n * dh; i += blockDim.x) {
+        const int tk = i / dh, d = i - tk * dh;
+        vt[d * LD + tk] = qkv[(size_t)(t0 + tk) * row + (size_t)(nh + nkv + h) * dh + d];
+    }
+    __syncthreads();
+    const int s0 = slots[0];
+    bool run = n == 16 && s0 >= 0 && (s0 % 16) == 0 && (s0 / page_size) < num_pages && (s0 % page_size) + 16 <= page_size;
+    if (run)
+        for (int i = 1; i < 16; ++i) run = run && slots[i] == s0 + i;
+    if (run) {
+        const int page = s0 / page_size, off = s0 - page * page_size;
+        T* dst = vcache + ((size_t)page * nkv + h) * dh * page_size + off;
+        for (int d = threadIdx.x; d < dh; d += blockDim.x) {
+            T* o = dst + (size_t)d * page_size;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = vt[d * LD + i];
+        }
+    } else {
+        for (int i = threadIdx.x; i < n * dh; i += blockDim.x) {
+            const int tk = i / dh, d = i - tk * dh;
+            const int slot = slots[tk];
+            const int page = slot / page_size, off = slot - page * page_size;
+            if (slot < 0 || page >= num_pages) continue;
+            vcache[(((size_t)page * nkv + h) * dh + d) * page_size + off] = vt[d * LD + tk];
+        }
+    }
 }
 
 }  // namespace
@@ -69,18 +128,34 @@ LI_EXPORT int li_rope_kv_write(void* qkv, int dtype, const int* positions, const
                rotary_dim, dh);
     if (T == 0) return 0;
     LI_REQUIRE(T <= 2147483647 && nh + nkv <= 65535, "rope_kv_write: too many heads for one launch");
-    const int threads = dh >= 128 ? 64 : 32;
-    const dim3 grid(T, nh + nkv);
+    const int heads_per_block = T >= 64 ? nh + nkv : 1;
+    const int threads = T >= 64 ? 256 : (dh >= 128 ? 64 : 32);
+    const dim3 grid(T, ceil_div(nh + nkv, heads_per_block));
     const size_t smem = 0;
+    LI_REQUIRE(dtype == LI_F32 || dtype == LI_BF16, "rope_kv_write: unknown dtype %d", dtype);
+    // many tokens: the values go through a kernel of their own that writes the transposed cache in 32-byte pieces
+    const bool v_separate = write && T >= 64;
+    const int write_v = v_separate ? 0 : 1;
     if (dtype == LI_F32)
-        li_launch_pdl(rope_kv_write_kernel<float>, dim3(grid), dim3(threads), smem, stream, (float*)qkv, positions, denom, rotary_dim, slot_mapping, (float*)kcache,
-                                                                   (float*)vcache, nh, nkv, dh, page_size, num_pages, write);
-    else if (dtype == LI_BF16)
-        li_launch_pdl(rope_kv_write_kernel<bf16>, dim3(grid), dim3(threads), smem, stream, (bf16*)qkv, positions, denom, rotary_dim, slot_mapping, (bf16*)kcache,
-                                                                  (bf16*)vcache, nh, nkv, dh, page_size, num_pages, write);
+        li_launch_pdl(rope_kv_write_kernel<float>, dim3(grid), dim3(threads), smem, stream, (float*)qkv, positions, denom, rotary_dim,
+                      slot_mapping, (float*)kcache, (float*)vcache, nh, nkv, dh, page_size, num_pages, write, write_v, heads_per_block);
     else
-        return li_fail("rope_kv_write: unknown dtype %d", dtype);
-    return li_check_launch("rope_kv_write");
+        li_launch_pdl(rope_kv_write_kernel<bf16>, dim3(grid), dim3(threads), smem, stream, (bf16*)qkv, positions, denom, rotary_dim,
+                      slot_mapping, (bf16*)kcache, (bf16*)vcache, nh, nkv, dh, page_size, num_pages, write, write_v, heads_per_block);
+    if (int rc = li_check_launch("rope_kv_write")) return rc;
+    if (v_separate) {
+        const dim3 vgrid(ceil_div(T, 16), nkv);
+        const size_t vsmem = (size_t)dh * 18 * (dtype == LI_F32 ? 4 : 2);
+        LI_REQUIRE(vsmem <= 48 * 1024, "rope_kv_write: head_dim %d is too large", dh);
+        if (dtype == LI_F32)
+            li_launch_pdl(v_cache_write_kernel<float>, vgrid, dim3(128), vsmem, stream, (const float*)qkv, slot_mapping, (float*)vcache, T, nh,
+                          nkv, dh, page_size, num_pages);
+        else
+            li_launch_pdl(v_cache_write_kernel<bf16>, vgrid, dim3(128), vsmem, stream, (const bf16*)qkv, slot_mapping, (bf16*)vcache, T, nh,
+                          nkv, dh, page_size, num_pages);
+        return li_check_launch("rope_kv_write (values)");
+    }
+    return 0;
 }
 
 // The q|k|v projection followed by rope_kv_write.  For a few bfloat16 tokens (decode) both run as one

@@ -74,9 +74,20 @@ __device__ Best block_best(Best x, Best* scratch /* 32 */) {
 
 __device__ Best row_argmax(const float* row, int V, Best* scratch) {
     Best b{-INFINITY, 0x7fffffff};
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    // eight loads in flight per thread: the row comes from L2 and one load at a time would wait out its latency each time
+    constexpr int U = 8;
+    int i = threadIdx.x;
+    for (; i + (U - 1) * (int)blockDim.x < V; i += U * blockDim.x) {
+        float v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = row[i + u * blockDim.x];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (v[u] > b.v) b = Best{v[u], i + u * (int)blockDim.x};      // ascending index per thread: the first maximum stays
+    }
+    for (; i < V; i += blockDim.x) {
         const float v = row[i];
-        if (v > b.v) b = Best{v, i};            // ascending i per thread: the first maximum stays
+        if (v > b.v) b = Best{v, i};
     }
     b = block_best(b, scratch);
     if (b.i == 0x7fffffff) b.i = 0;             // a row of NaN or -inf

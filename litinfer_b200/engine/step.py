@@ -40,6 +40,7 @@ class _DecodeGraph:
 
 class ModelRunner:
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+    GRAPH_CONTEXT_CAP = 8192            # a captured step covers contexts up to this; longer ones are launched plainly
 
     def __init__(self, model: DecoderModel, manager: CacheManager, use_graphs: bool = False,
                  max_context: Optional[int] = None) -> None:
@@ -47,7 +48,9 @@ class ModelRunner:
         self.manager = manager
         self.device = model.device
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
-        self.max_context = int(max_context or model.spec.max_position_embeddings)
+        # a captured attention launch has to cover the longest context it may meet (its grid and workspace
+        # are sized for it), so that length is capped; steps with a longer context run without a graph
+        self.max_context = min(int(max_context or model.spec.max_position_embeddings), self.GRAPH_CONTEXT_CAP)
         self._graphs: Dict[int, _DecodeGraph] = {}
         self._pinned: Optional[torch.Tensor] = None
         self._copy_done = None
@@ -84,7 +87,8 @@ class ModelRunner:
         """Float32 logits ``[wanted, vocab]`` in the order of the items and of their ``want``."""
         items = list(items)
         decode_only = all(len(it.tokens) == 1 for it in items)
-        if self.use_graphs and decode_only and len(items) <= self.GRAPH_BUCKETS[-1]:
+        fits = decode_only and max(it.cache.length for it in items) + 1 <= self.max_context
+        if self.use_graphs and fits and len(items) <= self.GRAPH_BUCKETS[-1]:
             logits = self._step_graph(items)
         else:
             buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size)

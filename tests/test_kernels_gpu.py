@@ -237,6 +237,40 @@ def test_rope_kv_write(dtype, cfg):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("cfg", [(4, 2, 16), (12, 2, 128), (6, 2, 48)])
+@pytest.mark.parametrize("page", [16, 64])
+def test_rope_kv_write_many_tokens(dtype, cfg, page):
+    """Prefill sizes: values take the path that writes the transposed cache page-wise.  Runs of 16 tokens in
+    consecutive slots of one page (in scrambled page order), a run that starts in the middle of a page, and
+    tokens scattered one by one."""
+    nh, nkv, dh = cfg
+    pages = 640 // page + 6
+    T = 16 * 6 + 16 + 13
+    qkv = rnd(T, (nh + 2 * nkv) * dh, dtype=dtype, seed=61)
+    positions = torch.arange(T, dtype=torch.int32, device=dev()) + 7
+    g = torch.Generator().manual_seed(62)
+    free16 = torch.randperm(pages * page // 16, generator=g).tolist()          # 16-slot pieces of the cache, in scrambled order
+    slots = []
+    for i in range(6):
+        slots += [free16[i] * 16 + j for j in range(16)]
+    base = free16[6] * 16 + 8                                                   # starts at slot 8 of a piece: crosses into the next one
+    slots += [base + j for j in range(8)] + [free16[7] * 16 + j for j in range(8)]
+    rest = [free16[8 + i] * 16 + (3 * i) % 16 for i in range(13)]
+    slots += rest
+    assert len(set(slots)) == T
+    slots = torch.tensor(slots, dtype=torch.int32, device=dev())
+    denom = torch.pow(torch.tensor(10000.0), torch.arange(dh // 2, dtype=torch.float32) * 2.0 / dh).to(dev())
+    kc = torch.zeros(pages, nkv, page, dh, dtype=dtype, device=dev())
+    vc = torch.zeros(pages, nkv, dh, page, dtype=dtype, device=dev())
+    kc2, vc2, qkv2 = kc.clone(), vc.clone(), qkv.clone()
+    K().rope_kv_write(qkv, positions, denom, dh, slots, kc, vc, nh, nkv, dh, True)
+    R.rope_kv_write(qkv2, positions, denom, dh, slots, kc2, vc2, nh, nkv, dh, True)
+    close(qkv, qkv2, dtype, "rope q", f32_tol=5e-5)
+    close(kc, kc2, dtype, "rope k cache", f32_tol=5e-5)
+    assert torch.equal(vc, vc2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("cfg", [(4, 2, 16, 64, 5), (12, 2, 128, 1536, 8), (3, 1, 32, 96, 1), (6, 2, 48, 80, 20), (14, 2, 80, 136, 64), (12, 2, 128, 1536, 70)])
 def test_linear_rope_kv_fused(dtype, cfg):
     """Projection, rotation and cache write as one call; for few bfloat16 tokens one kernel, the rotation in the
