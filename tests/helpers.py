@@ -18,7 +18,8 @@ ROOT = Path(__file__).resolve().parent.parent
 
 # Float32: two independent float32 implementations of these tiny models differ by a few
 # 1e-7 in the logits (measured between LitInfer's ops and a plain forward); 1e-4 leaves
-# room for longer sums and is still far below any real fault (a wrong key moves logits by 1e-2).
+# room for the longer sums of real layer sizes (rows of 8,960 products) and is still far
+# below any real fault (a wrong key moves logits by 1e-2).
 F32_ATOL = 1e-4
 # bfloat16 against the plain model in float32 on the same (bfloat16-rounded) weights:
 # activations are rounded to 8 bits of mantissa (relative step 2^-8) at roughly ten places

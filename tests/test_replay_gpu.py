@@ -135,3 +135,42 @@ def test_replay_without_graphs_matches(model_dirs, tmp_path):
     a = run_trace(model_dirs["A"], "bfloat16", tr, tmp_path / "g", 64, vocab)
     b = run_trace(model_dirs["A"], "bfloat16", tr, tmp_path / "n", 64, vocab, extra=["--no-graphs"])
     assert torch.equal(stack(a["a"]), stack(b["a"]))
+
+
+REAL_SIZES = dict(
+    architectures=["Qwen2ForCausalLM"], torch_dtype="float32", num_hidden_layers=2, hidden_size=1536,
+    num_attention_heads=12, num_key_value_heads=2, head_dim=128, intermediate_size=8960, vocab_size=32000,
+    rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=4096,
+    eos_token_id=None, use_sliding_window=False)
+
+
+@pytest.fixture(scope="module")
+def real_size_dir(tmp_path_factory):
+    """Two layers with the layer sizes of the 1.5B shape (the vocabulary cut to 32,000 to keep the file small)."""
+    from litinfer_b200.weights import write_model_folder
+
+    d = tmp_path_factory.mktemp("real_sizes")
+    write_model_folder(d, dict(REAL_SIZES), seed=99, store_dtype="float32")
+    return d
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_real_layer_sizes(dtype, real_size_dir, tmp_path):
+    """The kernels at the sizes they are built for: a 300-token prompt whole, then decoded on while a second
+    request comes in portions beside it."""
+    vocab = REAL_SIZES["vocab_size"]
+    a = random_tokens(324, vocab, 201)
+    b = random_tokens(160, vocab, 202)
+    tr = Trace()
+    tr.step([("a", a[:300], list(range(280, 300)))])
+    tr.step([("a", [a[300]], True), ("b", b[:100], [99])])
+    tr.step([("a", [a[301]], True), ("b", b[100:137], [0, 36])])
+    tr.step([("a", [a[302]], True), ("b", b[137:139], True)])
+    for i in range(303, 324):
+        tr.step([("a", [a[i]], True), ("b", [b[139 + i - 303]], True)])
+    got = run_trace(real_size_dir, dtype, tr, tmp_path / "out", 384 + 192, vocab)
+    ref_a = plain_logits(real_size_dir, a, dtype)
+    ref_b = plain_logits(real_size_dir, b[:139 + 21], dtype)
+    for rid, ref in (("a", ref_a), ("b", ref_b)):
+        rows = sorted(got[rid])
+        check_logits(stack(got[rid]), ref[rows], dtype, f"real layer sizes {dtype} request {rid}")
