@@ -35,6 +35,8 @@ using namespace tc;
 
 constexpr int kThreads = 192;
 
+int g_forced_ksplit = 0;         // > 0: split k this many ways whatever the shape (tests and measurements)
+
 template <int BM, int BN>
 struct Tile {
     static constexpr int kStages = (BM + BN) <= 256 ? 6 : 3;
@@ -51,12 +53,14 @@ struct __align__(1024) SharedStorage {
     unsigned long long accum;
     unsigned tmem_base;
     int failed;
+    int is_last;
 };
 
 template <int BM, int BN, typename Tout, bool kSwiglu>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag) {
+                    const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag,
+                    float* __restrict__ partial, unsigned* __restrict__ counters, int ksplit) {
     extern __shared__ unsigned char smem_raw[];
     using SS = SharedStorage<BM, BN>;
     constexpr int kStages = Tile<BM, BN>::kStages;
@@ -65,7 +69,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     SS& sm = *reinterpret_cast<SS*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-    const int nkb = (K + BK - 1) / BK;
+    const int nkb_total = (K + BK - 1) / BK;
+    const int split = blockIdx.z;
+    const int kb_first = (int)((long long)split * nkb_total / ksplit);
+    const int nkb = (int)((long long)(split + 1) * nkb_total / ksplit) - kb_first;       // this CTA's k-blocks
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) {
@@ -96,8 +103,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 ok = mbar_wait(&sm.empty[s], phase ^ 1);
                 if (!ok) break;
                 mbar_expect_tx(&sm.full[s], kStageBytesA + kStageBytesB);
-                tma_load_2d(sm.a[s], &map_a, kb * BK, m0, &sm.full[s]);
-                tma_load_2d(sm.b[s], &map_w, kb * BK, n0, &sm.full[s]);
+                tma_load_2d(sm.a[s], &map_a, (kb_first + kb) * BK, m0, &sm.full[s]);
+                tma_load_2d(sm.b[s], &map_w, (kb_first + kb) * BK, n0, &sm.full[s]);
                 issued = kb + 1;
             }
             if (!ok) {
@@ -142,78 +149,126 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (lane == 0) atomicExch(error_flag, 3);
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-            for (int hc = 0; hc < (BM / 128) * (BN / 32); ++hc) {
-                const int half = hc / (BN / 32), c = (hc - half * (BN / 32)) * 32;
-                const int row = m0 + half * 128 + quarter * 32 + lane;
-                float v[32];
-                tmem_ld_32x32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)(half * BN + c), v);
+            // one 32-column piece of a row: bias or SwiGLU, one rounding, store
+            auto emit = [&](int row, int c, float (&v)[32]) {
                 const int col0 = n0 + c;
-                if (kSwiglu) {
-                    // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 activations up * gate / (1 + exp(-gate))
-                    if (row < M && col0 < N) {
-                        const int half_n = N >> 1;
-                        Tout* dst = out + (size_t)row * half_n + (col0 >> 1);
-                        float a16[16];
+                    if (kSwiglu) {
+                        // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 activations up * gate / (1 + exp(-gate))
+                        if (row < M && col0 < N) {
+                            const int half_n = N >> 1;
+                            Tout* dst = out + (size_t)row * half_n + (col0 >> 1);
+                            float a16[16];
 #pragma unroll
-                        for (int h = 0; h < 2; ++h)
+                            for (int h = 0; h < 2; ++h)
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const float gate = v[16 * h + i], up = v[16 * h + 8 + i];
-                                a16[8 * h + i] = up * (gate / (1.0f + expf(-gate)));
+                                for (int i = 0; i < 8; ++i) {
+                                    const float gate = v[16 * h + i], up = v[16 * h + 8 + i];
+                                    a16[8 * h + i] = up * (gate / (1.0f + expf(-gate)));
+                                }
+                            if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0 && sizeof(Tout) == 2) {
+                                uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                                for (int i = 0; i < 2; ++i) {
+                                    uint4 pk;
+                                    __nv_bfloat162 h0 = __floats2bfloat162_rn(a16[8 * i + 0], a16[8 * i + 1]);
+                                    __nv_bfloat162 h1 = __floats2bfloat162_rn(a16[8 * i + 2], a16[8 * i + 3]);
+                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(a16[8 * i + 4], a16[8 * i + 5]);
+                                    __nv_bfloat162 h3 = __floats2bfloat162_rn(a16[8 * i + 6], a16[8 * i + 7]);
+                                    pk.x = *reinterpret_cast<unsigned*>(&h0);
+                                    pk.y = *reinterpret_cast<unsigned*>(&h1);
+                                    pk.z = *reinterpret_cast<unsigned*>(&h2);
+                                    pk.w = *reinterpret_cast<unsigned*>(&h3);
+                                    d4[i] = pk;
+                                }
+                            } else {
+                                for (int i = 0; i < 16; ++i) {
+                                    const int src_col = col0 + 16 * (i >> 3) + (i & 7);      // the gate column of activation i
+                                    if (src_col + 8 < N) dst[i] = from_float<Tout>(a16[i]);
+                                }
                             }
-                        if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0 && sizeof(Tout) == 2) {
-                            uint4* d4 = reinterpret_cast<uint4*>(dst);
+                        }
+                    } else if (row < M && col0 < N) {
+                        Tout* dst = out + (size_t)row * N + col0;
+                        if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
+                            if (bias) {
 #pragma unroll
-                            for (int i = 0; i < 2; ++i) {
-                                uint4 pk;
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(a16[8 * i + 0], a16[8 * i + 1]);
-                                __nv_bfloat162 h1 = __floats2bfloat162_rn(a16[8 * i + 2], a16[8 * i + 3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(a16[8 * i + 4], a16[8 * i + 5]);
-                                __nv_bfloat162 h3 = __floats2bfloat162_rn(a16[8 * i + 6], a16[8 * i + 7]);
-                                pk.x = *reinterpret_cast<unsigned*>(&h0);
-                                pk.y = *reinterpret_cast<unsigned*>(&h1);
-                                pk.z = *reinterpret_cast<unsigned*>(&h2);
-                                pk.w = *reinterpret_cast<unsigned*>(&h3);
-                                d4[i] = pk;
+                                for (int i = 0; i < 32; ++i) v[i] += bias[col0 + i];
+                            }
+                            if (sizeof(Tout) == 2) {
+                                uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    uint4 pk;
+                                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
+                                    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+                                    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+                                    pk.x = *reinterpret_cast<unsigned*>(&h0);
+                                    pk.y = *reinterpret_cast<unsigned*>(&h1);
+                                    pk.z = *reinterpret_cast<unsigned*>(&h2);
+                                    pk.w = *reinterpret_cast<unsigned*>(&h3);
+                                    d4[i] = pk;
+                                }
+                            } else {
+                                float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                             }
                         } else {
-                            for (int i = 0; i < 16; ++i) {
-                                const int src_col = col0 + 16 * (i >> 3) + (i & 7);      // the gate column of activation i
-                                if (src_col + 8 < N) dst[i] = from_float<Tout>(a16[i]);
-                            }
+                            for (int i = 0; i < 32 && col0 + i < N; ++i) dst[i] = from_float<Tout>(bias ? v[i] + bias[col0 + i] : v[i]);
                         }
                     }
-                } else if (row < M && col0 < N) {
-                    Tout* dst = out + (size_t)row * N + col0;
-                    if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
-                        if (bias) {
+            };
+            const size_t tile_id = (size_t)blockIdx.y * gridDim.x + blockIdx.x, tiles = (size_t)gridDim.x * gridDim.y;
+            if (ksplit == 1) {
+#pragma unroll 1
+                for (int hc = 0; hc < (BM / 128) * (BN / 32); ++hc) {
+                    const int half = hc / (BN / 32), c = (hc - half * (BN / 32)) * 32;
+                    float v[32];
+                    tmem_ld_32x32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)(half * BN + c), v);
+                    emit(m0 + half * 128 + quarter * 32 + lane, c, v);
+                }
+            } else {
+                // k is split over several CTAs: each leaves its float tile in the workspace; the one that
+                // arrives last (a counter per tile) adds the tiles in split order and finishes
+#pragma unroll 1
+                for (int hc = 0; hc < (BM / 128) * (BN / 32); ++hc) {
+                    const int half = hc / (BN / 32), c = (hc - half * (BN / 32)) * 32;
+                    float v[32];
+                    tmem_ld_32x32(tmem_acc + ((unsigned)(quarter * 32) << 16) + (unsigned)(half * BN + c), v);
+                    if (nkb == 0) {                       // more splits than k-blocks: this one adds nothing (its accumulator was never written)
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] += bias[col0 + i];
-                        }
-                        if (sizeof(Tout) == 2) {
-                            uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                uint4 pk;
-                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
-                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
-                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
-                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
-                                pk.x = *reinterpret_cast<unsigned*>(&h0);
-                                pk.y = *reinterpret_cast<unsigned*>(&h1);
-                                pk.z = *reinterpret_cast<unsigned*>(&h2);
-                                pk.w = *reinterpret_cast<unsigned*>(&h3);
-                                d4[i] = pk;
-                            }
-                        } else {
-                            float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-                            for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                        }
-                    } else {
-                        for (int i = 0; i < 32 && col0 + i < N; ++i) dst[i] = from_float<Tout>(bias ? v[i] + bias[col0 + i] : v[i]);
+                        for (int i = 0; i < 32; ++i) v[i] = 0.0f;
                     }
+                    // layout [split][tile][piece hc][column i][128 rows]: the 32 lanes of a warp write 32 consecutive floats
+                    float* dst = partial + ((((size_t)split * tiles + tile_id) * ((BM / 128) * (BN / 32)) + hc) * 32) * 128 + quarter * 32 + lane;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) dst[(size_t)i * 128] = v[i];
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (warp == 2 && lane == 0) {
+                    const unsigned prev = atomicAdd(&counters[tile_id], 1u);
+                    sm.is_last = (prev == (unsigned)(ksplit - 1)) ? 1 : 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (sm.is_last) {
+                    __threadfence();
+#pragma unroll 1
+                    for (int hc = 0; hc < (BM / 128) * (BN / 32); ++hc) {
+                        const int half = hc / (BN / 32), c = (hc - half * (BN / 32)) * 32;
+                        float v[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                        for (int sp = 0; sp < ksplit; ++sp) {
+                            const float* src = partial + ((((size_t)sp * tiles + tile_id) * ((BM / 128) * (BN / 32)) + hc) * 32) * 128 + quarter * 32 + lane;
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] += __ldcg(src + (size_t)i * 128);
+                        }
+                        emit(m0 + half * 128 + quarter * 32 + lane, c, v);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (warp == 2 && lane == 0) counters[tile_id] = 0;          // ready for the next launch
                 }
             }
         }
@@ -229,8 +284,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 // ---- host side -----------------------------------------------------------
 
+struct SplitWorkspace {
+    float* partial = nullptr;
+    size_t floats = 0;
+    unsigned* counters = nullptr;
+};
+SplitWorkspace g_split_ws[16];
+constexpr int kSplitCounters = 1 << 16;
+
+// Workspace of the k-splits (prefill only: it may grow, so the first call of a size must not be under stream capture).
+int split_workspace(size_t floats, SplitWorkspace** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return li_fail("linear (tcgen05): cudaGetDevice: %s", cudaGetErrorString(e));
+    LI_REQUIRE(dev >= 0 && dev < 16, "linear (tcgen05): device index %d out of range", dev);
+    SplitWorkspace& w = g_split_ws[dev];
+    if (!w.counters) {
+        e = cudaMalloc(&w.counters, kSplitCounters * sizeof(unsigned));
+        if (e == cudaSuccess) e = cudaMemset(w.counters, 0, kSplitCounters * sizeof(unsigned));
+        if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot allocate the tile counters: %s", cudaGetErrorString(e));
+    }
+    if (w.floats < floats) {
+        float* nb = nullptr;
+        e = cudaMalloc(&nb, floats * sizeof(float));
+        if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot allocate %zu bytes for the k-splits: %s", floats * sizeof(float), cudaGetErrorString(e));
+        if (w.partial) cudaFree(w.partial);
+        w.partial = nb;
+        w.floats = floats;
+    }
+    *out = &w;
+    return 0;
+}
+
 template <int BM, int BN, typename Tout, bool kSwiglu>
-int launch_tile(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
+int launch_tile(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int ksplit = 1) {
     EncodeTiledFn encode = nullptr;
     int *g_error_host = nullptr, *g_error_dev = nullptr;
     if (int rc = setup(&encode, &g_error_host, &g_error_dev)) return rc;
@@ -246,9 +333,15 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
         if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
-    dim3 grid(ceil_div(N, BN), ceil_div(M, BM));
+    dim3 grid(ceil_div(N, BN), ceil_div(M, BM), ksplit);
     LI_REQUIRE(grid.y <= 65535, "linear (tcgen05): M=%d is too large for one launch", M);
-    gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu><<<grid, kThreads, smem, stream>>>(map_a, map_w, bias, (Tout*)out, M, N, K, g_error_dev);
+    SplitWorkspace none, *ws = &none;
+    if (ksplit > 1) {
+        LI_REQUIRE((size_t)grid.x * grid.y <= (size_t)kSplitCounters, "linear (tcgen05): too many tiles for a split of k");
+        if (int rc = split_workspace((size_t)ksplit * grid.x * grid.y * BM * BN, &ws)) return rc;
+    }
+    gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu><<<grid, kThreads, smem, stream>>>(map_a, map_w, bias, (Tout*)out, M, N, K, g_error_dev,
+                                                                                 ws->partial, ws->counters, ksplit);
     return li_check_launch("linear (tcgen05)");
 }
 
@@ -257,9 +350,18 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
 template <typename Tout, bool kSwiglu>
 int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int tile) {
     const long long big_ctas = (long long)ceil_div(M, 256) * ceil_div(N, 256);
-    const bool big = tile == 2 || (tile == 0 && big_ctas >= 120);
-    if (big) return launch_tile<256, 256, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
-    return launch_tile<128, 128, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
+    const int nkb = ceil_div(K, BK);
+    // few large tiles and a long k: split k so that the large tiles fill the GPU
+    int ksplit = 1;
+    if (big_ctas < 120 && big_ctas >= 24) {
+        ksplit = (int)(148 / big_ctas);
+        if (ksplit > nkb / 32) ksplit = nkb / 32;          // measured: worth it from about 32 k-blocks a split (down projection), not for k = 1536
+        if (ksplit < 1) ksplit = 1;
+    }
+    if (g_forced_ksplit > 0) ksplit = g_forced_ksplit;
+    const bool big = tile == 2 || (tile == 0 && (big_ctas >= 120 || ksplit > 1));
+    if (big) return launch_tile<256, 256, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, ksplit);
+    return launch_tile<128, 128, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
 }
 
 int g_forced_tile = 0;
@@ -268,6 +370,9 @@ int g_forced_tile = 0;
 
 // 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always.  For tests and measurements.
 LI_EXPORT void li_tcgen05_force_tile(int tile) { g_forced_tile = tile; }
+
+// 0: splits of k by shape; n > 0: n splits always.  For tests and measurements.
+LI_EXPORT void li_tcgen05_force_ksplit(int n) { g_forced_ksplit = n; }
 
 bool li_tcgen05_accepts(const void* a, const void* w, const void* out, int dtype_out, int M, int N, int K) {
     return M >= 1 && N >= 1 && K >= 8 && K % 8 == 0 && ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0) &&

@@ -154,8 +154,17 @@ def forced_tile(request):
     lib.li_tcgen05_force_tile(0)
 
 
+@pytest.fixture(params=[0, 3], ids=["ksplit_by_shape", "ksplit3"])
+def forced_ksplit(request):
+    """The tcgen05 kernel with k split over three CTAs a tile, whatever it would choose for the shape itself."""
+    lib = K().library()
+    lib.li_tcgen05_force_ksplit(request.param)
+    yield request.param
+    lib.li_tcgen05_force_ksplit(0)
+
+
 @pytest.mark.parametrize("shape", TC_SHAPES)
-def test_linear_tcgen05_kernel(shape, forced_tile):
+def test_linear_tcgen05_kernel(shape, forced_tile, forced_ksplit):
     M, N, Kd = shape
     a = rnd(M, Kd, dtype=torch.bfloat16, seed=26)
     w = rnd(N, Kd, dtype=torch.bfloat16, seed=27, scale=0.05)
@@ -176,10 +185,10 @@ def test_linear_tcgen05_kernel(shape, forced_tile):
                                          ("gemv_tcgen05", (16, 352, 80)), ("gemv_tcgen05", (64, 3072, 8960)),
                                          ("tcgen05", (128, 256, 64)), ("tcgen05", (300, 544, 96)), ("tcgen05", (2048, 17920, 1536)),
                                          ("tcgen05", (77, 352, 80)), ("tcgen05", (65, 48, 40))])
-def test_linear_swiglu_epilogue(which, shape, forced_tile):
+def test_linear_swiglu_epilogue(which, shape, forced_tile, forced_ksplit):
     """gate and up rows interleaved in groups of 8; the product's epilogue applies up * silu(gate)."""
-    if which != "tcgen05" and forced_tile == 2:
-        pytest.skip("tile size is a property of the tcgen05 kernel")
+    if which != "tcgen05" and (forced_tile == 2 or forced_ksplit):
+        pytest.skip("tile size and forced splits are properties of the tcgen05 kernel")
     M, N, Kd = shape
     I = N // 2
     a = rnd(M, Kd, dtype=torch.bfloat16, seed=36)
