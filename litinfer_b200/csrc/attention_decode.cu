@@ -31,6 +31,7 @@
 namespace {
 
 constexpr int kSplit = 128;
+constexpr int kWholeFrom = 120;        // (sequences x kv heads) from which a CTA takes a whole context
 constexpr int kWarps = 8;
 
 struct Workspace {
@@ -215,6 +216,83 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     if (threadIdx.x == 0) counters[s * nkv + kvh] = 0;          // ready for the next launch on this stream
 }
 
+// Many sequences at once: with one CTA per (sequence, kv head) the GPU is already full, and splitting the
+// context over CTAs would only add partial results to write, merge and wait for.  Each of the CTA's warps
+// walks every WARPS-th block of 16 keys with a running softmax; the warps are merged through shared memory in
+// warp order at the end.  The assignment of blocks to warps depends on the sequence alone.
+template <int DH, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 1)
+decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
+                              bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages, float scale, int window) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int kvh = blockIdx.x, s = blockIdx.y;
+    const int ctx = ctx_lens[s];
+    const int p = ctx - 1;
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int G = nh / nkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const bf16* qrow = qkv + (size_t)s * (nh + 2 * nkv) * DH + (size_t)kvh * G * DH;
+    unsigned qa[DH / 16][4];
+    load_q<DH>(qa, g < G ? qrow + (size_t)g * DH : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * DH : nullptr, t);
+    RowState<DH> st;
+    st.init();
+    const int lo2[2] = {lo, lo}, hi2[2] = {p, p};
+    const int* bt = block_table + (size_t)s * max_blocks;
+    const int b_first = lo / 16, b_last = p / 16;
+#pragma unroll 1
+    for (int b = b_first + warp; b <= b_last; b += WARPS) {
+        const int key0 = b * 16;
+        int page = bt[key0 / page_size];
+        if (page < 0 || page >= num_pages) page = 0;
+        const int off = key0 % page_size;
+        KFrag<DH> kf;
+        VFrag<DH> vf;
+        load_k<DH, true>(kf, kcache + (((size_t)page * nkv + kvh) * page_size + off) * DH, g, t);
+        load_v<DH, true>(vf, vcache + ((size_t)page * nkv + kvh) * DH * page_size + off, page_size, g, t);
+        compute16<DH>(st, qa, kf, vf, key0, lo2, hi2, scale, t);
+    }
+    const float m0 = st.m[0], m1 = st.m[1];
+    const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
+    float* sm_m = sm;
+    float* sm_l = sm + WARPS * 16;
+    float* sm_o = sm + 2 * WARPS * 16;
+    if (t == 0) {
+        sm_m[warp * 16 + g] = m0; sm_m[warp * 16 + g + 8] = m1;
+        sm_l[warp * 16 + g] = l0; sm_l[warp * 16 + g + 8] = l1;
+    }
+#pragma unroll
+    for (int j = 0; j < DH / 8; ++j) {
+        const int col = j * 8 + 2 * t;
+        if (g < G) {
+            sm_o[((size_t)warp * G + g) * DH + col] = st.o[j][0];
+            sm_o[((size_t)warp * G + g) * DH + col + 1] = st.o[j][1];
+        }
+        if (g + 8 < G) {
+            sm_o[((size_t)warp * G + g + 8) * DH + col] = st.o[j][2];
+            sm_o[((size_t)warp * G + g + 8) * DH + col + 1] = st.o[j][3];
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < G * DH; e += WARPS * 32) {
+        const int r = e / DH, d = e - r * DH;
+        float M = sm_m[r];
+#pragma unroll
+        for (int w = 1; w < WARPS; ++w) M = fmaxf(M, sm_m[w * 16 + r]);
+        float O = 0.0f, L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float f = (sm_m[w * 16 + r] == -INFINITY) ? 0.0f : expf(sm_m[w * 16 + r] - M);
+            O += sm_o[((size_t)w * G + r) * DH + d] * f;
+            L += sm_l[w * 16 + r] * f;
+        }
+        out[((size_t)s * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+    }
+}
+
 int ensure_workspace(size_t floats, float** buf, unsigned** counters) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -248,8 +326,25 @@ template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
            const int* ctx_lens, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window, int max_ctx_len,
            cudaStream_t stream) {
-    const int nsplit = ceil_div(max_ctx_len > 0 ? max_ctx_len : 1, kSplit);
     const int G = nh / nkv;
+    LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
+    if ((long long)S * nkv >= kWholeFrom) {
+        // one CTA per (sequence, kv head) fills the GPU: no split of the context
+        constexpr int W = 16;
+        const size_t wsmem = (2 * W * 16 + (size_t)W * G * DH) * sizeof(float);
+        if (wsmem <= 200 * 1024) {
+            static bool raised = false;
+            if (!raised && wsmem > 48 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(decode_attention_whole_kernel<DH, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+                if (e != cudaSuccess) return li_fail("attention (decode): cannot raise shared memory: %s", cudaGetErrorString(e));
+                raised = true;
+            }
+            li_launch_pdl(decode_attention_whole_kernel<DH, W>, dim3(nkv, S), dim3(W * 32), wsmem, stream, (const bf16*)qkv, (const bf16*)kcache,
+                          (const bf16*)vcache, block_table, max_blocks, ctx_lens, (bf16*)out, nh, nkv, page_size, num_pages, scale, window);
+            return li_check_launch("attention (decode, whole context)");
+        }
+    }
+    const int nsplit = ceil_div(max_ctx_len > 0 ? max_ctx_len : 1, kSplit);
     float* part = nullptr;
     unsigned* counters = nullptr;
     if (int rc = ensure_workspace((size_t)S * nh * nsplit * (DH + 2), &part, &counters)) return rc;

@@ -150,4 +150,127 @@ __device__ __forceinline__ void compute16(RowState<DH>& st, const unsigned (&qa)
     }
 }
 
+// ---- the same step on 32 keys with 16-byte loads (decode: half as many memory requests per byte) ----
+//
+// Thread t of a quad owns keys 8t .. 8t+7 of the block: a 16-byte load of a value column gives it both
+// k-steps of P V (keys 8t..8t+3 and 8t+4..8t+7), and score tile 2s+h carries in column n the key
+// 8 (n >> 1) + 4 s + 2 h + (n & 1).  Along head_dim a 16-byte load of a key row (8 elements) serves two
+// k-steps of Q K^T; the query fragments are permuted the same way (load_q32).  head_dim = 32 F + 16 R.
+
+template <int DH>
+struct KFrag32 {
+    uint4 k[4][DH / 32 > 0 ? DH / 32 : 1];
+    uint2 tail[4];
+};
+template <int DH>
+struct VFrag32 {
+    uint4 v[DH / 8];
+};
+
+template <int DH>
+__device__ __forceinline__ void load_q32(unsigned (&qa)[DH / 16][4], const bf16* row_lo, const bf16* row_hi, int t) {
+    constexpr int F = DH / 32, R = (DH % 32) / 16;
+#pragma unroll
+    for (int f = 0; f < F; ++f) {
+        const uint4 a = row_lo ? *reinterpret_cast<const uint4*>(row_lo + f * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+        const uint4 b = row_hi ? *reinterpret_cast<const uint4*>(row_hi + f * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+        qa[2 * f][0] = a.x; qa[2 * f][1] = b.x; qa[2 * f][2] = a.y; qa[2 * f][3] = b.y;
+        qa[2 * f + 1][0] = a.z; qa[2 * f + 1][1] = b.z; qa[2 * f + 1][2] = a.w; qa[2 * f + 1][3] = b.w;
+    }
+    if (R) {
+        const uint2 a = row_lo ? ld8(row_lo + F * 32 + t * 4) : make_uint2(0, 0);
+        const uint2 b = row_hi ? ld8(row_hi + F * 32 + t * 4) : make_uint2(0, 0);
+        qa[DH / 16 - 1][0] = a.x; qa[DH / 16 - 1][1] = b.x; qa[DH / 16 - 1][2] = a.y; qa[DH / 16 - 1][3] = b.y;
+    }
+}
+
+__device__ __forceinline__ uint4 ld16_stream(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.cs.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// kgroup: the first of the 8 key rows [8 (g >> 1), 8 (g >> 1) + 8) of the block, which lie in one page
+// ([8][DH], rows DH apart).  This thread's rows in the four score tiles are (g & 1) + {0, 2, 4, 6} of them.
+template <int DH>
+__device__ __forceinline__ void load_k32(KFrag32<DH>& kf, const bf16* kgroup, int g, int t) {
+    constexpr int F = DH / 32, R = (DH % 32) / 16;
+#pragma unroll
+    for (int tau = 0; tau < 4; ++tau) {
+        const bf16* row = kgroup + (size_t)((g & 1) + 4 * (tau >> 1) + 2 * (tau & 1)) * DH;
+#pragma unroll
+        for (int f = 0; f < F; ++f) kf.k[tau][f] = ld16_stream(row + f * 32 + t * 8);
+        if (R) kf.tail[tau] = ld8_stream(row + F * 32 + t * 4);
+    }
+}
+
+// vkeys: slot of key 8 t of the block in the transposed values of its page ([DH][page_size]), for this thread's t.
+template <int DH>
+__device__ __forceinline__ void load_v32(VFrag32<DH>& vf, const bf16* vkeys, int page_size, int g) {
+#pragma unroll
+    for (int j = 0; j < DH / 8; ++j) vf.v[j] = ld16_stream(vkeys + (size_t)(j * 8 + g) * page_size);
+}
+
+template <int DH>
+__device__ __forceinline__ void compute32(RowState<DH>& st, const unsigned (&qa)[DH / 16][4], const KFrag32<DH>& kf, const VFrag32<DH>& vf,
+                                          int key0, const int (&lo)[2], const int (&hi)[2], float scale, int t) {
+    constexpr int F = DH / 32, R = (DH % 32) / 16, NT = DH / 8;
+    float sc[4][4];
+#pragma unroll
+    for (int tau = 0; tau < 4; ++tau) {
+        sc[tau][0] = sc[tau][1] = sc[tau][2] = sc[tau][3] = 0.0f;
+#pragma unroll
+        for (int f = 0; f < F; ++f) {
+            mma_bf16(sc[tau], qa[2 * f][0], qa[2 * f][1], qa[2 * f][2], qa[2 * f][3], kf.k[tau][f].x, kf.k[tau][f].y);
+            mma_bf16(sc[tau], qa[2 * f + 1][0], qa[2 * f + 1][1], qa[2 * f + 1][2], qa[2 * f + 1][3], kf.k[tau][f].z, kf.k[tau][f].w);
+        }
+        if (R) mma_bf16(sc[tau], qa[DH / 16 - 1][0], qa[DH / 16 - 1][1], qa[DH / 16 - 1][2], qa[DH / 16 - 1][3], kf.tail[tau].x, kf.tail[tau].y);
+    }
+    float alpha[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int tau = 0; tau < 4; ++tau) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key0 + 8 * t + 4 * (tau >> 1) + 2 * (tau & 1) + e;
+                float& v = sc[tau][2 * r + e];
+                v = (key >= lo[r] && key <= hi[r]) ? v * scale : -INFINITY;
+                mx = fmaxf(mx, v);
+            }
+        }
+        mx = quad_max(mx);
+        const float mn = fmaxf(st.m[r], mx);
+        const float ms = (mn == -INFINITY) ? 0.0f : mn;
+        alpha[r] = expf(st.m[r] - ms);
+        float sum = 0.0f;
+#pragma unroll
+        for (int tau = 0; tau < 4; ++tau) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float& v = sc[tau][2 * r + e];
+                v = expf(v - ms);
+                sum += v;
+            }
+        }
+        st.l[r] = st.l[r] * alpha[r] + sum;
+        st.m[r] = mn;
+    }
+    unsigned pa[2][4];
+#pragma unroll
+    for (int s2 = 0; s2 < 2; ++s2) {
+        pa[s2][0] = pack_bf16(sc[2 * s2][0], sc[2 * s2][1]);
+        pa[s2][1] = pack_bf16(sc[2 * s2][2], sc[2 * s2][3]);
+        pa[s2][2] = pack_bf16(sc[2 * s2 + 1][0], sc[2 * s2 + 1][1]);
+        pa[s2][3] = pack_bf16(sc[2 * s2 + 1][2], sc[2 * s2 + 1][3]);
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        st.o[j][0] *= alpha[0]; st.o[j][1] *= alpha[0]; st.o[j][2] *= alpha[1]; st.o[j][3] *= alpha[1];
+        mma_bf16(st.o[j], pa[0][0], pa[0][1], pa[0][2], pa[0][3], vf.v[j].x, vf.v[j].y);
+        mma_bf16(st.o[j], pa[1][0], pa[1][1], pa[1][2], pa[1][3], vf.v[j].z, vf.v[j].w);
+    }
+}
+
 }  // namespace attn

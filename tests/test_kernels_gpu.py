@@ -435,6 +435,28 @@ def test_attention_prefill_kernel_alone(heads, page):
         close(out, ref, torch.bfloat16, f"prefill kernel heads={heads} page={page} window={window}")
 
 
+@pytest.mark.parametrize("heads", [(12, 2, 128), (4, 2, 16), (6, 2, 48), (8, 8, 64)])
+def test_attention_decode_large_batch(heads):
+    """From 120 (sequence, kv head) pairs on, a CTA takes a whole context instead of a 128-key split."""
+    nh, nkv, dh = heads
+    S = 128 // nkv + 3
+    g = torch.Generator().manual_seed(5)
+    ctx_lens = torch.randint(1, 700, (S,), generator=g).tolist()
+    ctx_lens[:6] = [1, 16, 17, 255, 256, 257]
+    c = make_attention_case([1] * S, ctx_lens, nh, nkv, dh, 16, torch.bfloat16, seed=33)
+    for window in (None, 100):
+        out, ref = run_attention_case(c, window, implementation="decode")
+        close(out, ref, torch.bfloat16, f"decode, large batch, heads={heads} window={window}")
+    # one far key carries the answer
+    c = make_attention_case([1] * S, [650] * S, nh, nkv, dh, 16, torch.bfloat16, seed=34)
+    _plant(c, 7, nkv - 1, 3, 7)
+    out, ref = run_attention_case(c, None, implementation="decode")
+    close(out, ref, torch.bfloat16, "decode, large batch, far key")
+    v = c["vals"][7][3, nkv - 1].float().to(out.device)
+    got = out[7].float().view(nh, dh)[(nkv - 1) * (nh // nkv)]
+    assert (got - v).abs().max() < 0.1 * v.abs().max() + 0.05
+
+
 def _plant(c, s, h_kv, key_pos, q_token, strength=30.0):
     """Make key ``key_pos`` of sequence s point along the query of ``q_token`` (all heads
     of that key head), so that it takes nearly all the softmax weight if it is visible."""
