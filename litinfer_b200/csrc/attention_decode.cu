@@ -1,28 +1,32 @@
 // Decode attention in bfloat16: one new token per sequence over its paged
-// cache, grouped-query, split along the context.
+// cache, grouped-query.
 //
-// Grid (split, kv head, sequence).  A CTA of 8 warps covers 128 keys at fixed
-// absolute positions [128 s, 128 s + 128), each warp 16 of them (all its loads
-// are in flight at once: one round trip to memory), for all query
-// heads of one key/value head at once (they share every K and V byte read;
-// heads are the 16 rows of a tensor-core tile).  Per 16 keys a warp computes
-// S = Q K^T and O += P V with mma.sync m16n8k16 (bfloat16 in, float
-// accumulate), softmax online in float as in LitInfer's kernel
-// (src/ops/paged_attention/op.cpp:194-234).  All operands go from global
-// memory straight into fragment registers with 8-byte loads:
-//   * the sum over head_dim does not depend on its order, so the 4 consecutive
+// Two kernels share one inner step.  Few sequences: grid (split, kv head,
+// sequence); a CTA of 8 warps covers 256 keys at fixed absolute positions
+// [256 s, 256 s + 256), each warp 32 of them (all its loads are in flight at
+// once: one round trip to memory).  Many sequences (sequences x kv heads >= 120):
+// one CTA per (sequence, kv head) whose warps walk every 8th block of 32 keys;
+// nothing to merge across CTAs.  Either way a warp works for all query heads of
+// one key/value head at once (they share every K and V byte read; heads are the
+// 16 rows of a tensor-core tile).  Per block a warp computes S = Q K^T and
+// O += P V with mma.sync m16n8k16 (bfloat16 in, float accumulate), softmax
+// online in float as in LitInfer's kernel (src/ops/paged_attention/op.cpp:194-234).
+// All operands go from global memory straight into fragment registers with
+// 16-byte loads (8-byte loads and blocks of 16 keys for head_dim 256, where
+// registers are short):
+//   * the sum over head_dim does not depend on its order, so the 8 consecutive
 //     elements a thread loads from a q row and from a key row are used as the
-//     element pairs the fragment layout asks for, the same way on both sides;
+//     element pairs the fragment layout asks for in two k-steps, the same way
+//     on both sides;
 //   * values are cached transposed, [page][kv_head][head_dim][slot], so that for
-//     one output column the 4 consecutive keys a thread needs are contiguous;
-//     the score tiles are computed with their key columns permuted to match
-//     (tile 0: keys 0,1,4,5,8,9,12,13 of the 16; tile 1: the others).
+//     one output column the 8 consecutive keys a thread needs are contiguous;
+//     the score tiles are computed with their key columns permuted to match.
 // Warps are merged through shared memory, CTAs through a float workspace by the
 // CTA that finishes last (a counter per sequence and kv head), both in fixed
-// order: split boundaries depend on
-// absolute key positions only, so a sequence's result does not depend on the
-// batch it is in.  Window: keys below p - window + 1 are masked, splits wholly
-// below it are skipped.
+// order: which keys a warp or a CTA takes depends on absolute key positions
+// only, so a sequence's result does not depend on the batch it is in, as long
+// as the same kernel runs (the choice depends on the number of sequences).
+// Window: keys below p - window + 1 are masked, blocks wholly below it skipped.
 //
 // Requires head_dim in {16, 32, ..., 128, 256}, at most 16 query heads per
 // key/value head, page_size a multiple of 16.
@@ -30,7 +34,6 @@
 
 namespace {
 
-constexpr int kSplit = 128;
 constexpr int kWholeFrom = 120;        // (sequences x kv heads) from which a CTA takes a whole context
 constexpr int kWarps = 8;
 
@@ -44,14 +47,45 @@ Workspace g_ws[16];
 
 using namespace attn;
 
-__host__ __device__ inline void split_range(int ctx, int window, int* first, int* last) {
+__host__ __device__ inline void split_range(int ctx, int window, int kSplit, int* first, int* last) {
     const int p = ctx - 1;
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     *first = lo / kSplit;
     *last = (ctx - 1) / kSplit;
 }
 
-template <int DH>
+// One block of KB keys (16: 8-byte loads; 32: 16-byte loads, half as many requests per byte) from the pages of a
+// sequence into the running softmax of a warp.  All loads of the block are issued before the first use.
+template <int DH, int KB>
+__device__ __forceinline__ void block_step(RowState<DH>& st, const unsigned (&qa)[DH / 16][4], const bf16* __restrict__ kcache,
+                                           const bf16* __restrict__ vcache, const int* __restrict__ bt, int key0, int kvh, int nkv,
+                                           int page_size, int num_pages, const int (&lo2)[2], const int (&hi2)[2], float scale, int g, int t) {
+    if constexpr (KB == 16) {
+        int page = bt[key0 / page_size];
+        if (page < 0 || page >= num_pages) page = 0;
+        const int off = key0 % page_size;
+        KFrag<DH> kf;
+        VFrag<DH> vf;
+        load_k<DH, true>(kf, kcache + (((size_t)page * nkv + kvh) * page_size + off) * DH, g, t);
+        load_v<DH, true>(vf, vcache + ((size_t)page * nkv + kvh) * DH * page_size + off, page_size, g, t);
+        compute16<DH>(st, qa, kf, vf, key0, lo2, hi2, scale, t);
+    } else {
+        // keys of this thread's key rows: the group of 8 at 8 (g >> 1); of its value columns: the 8 at 8 t.
+        // A group of 8 aligned keys lies in one page (pages hold a multiple of 16); groups wholly past the
+        // context may have no page yet: they read page 0 and are masked.
+        const int kk = key0 + 8 * (g >> 1), vk = key0 + 8 * t;
+        int kpage = kk <= hi2[0] ? bt[kk / page_size] : 0, vpage = vk <= hi2[0] ? bt[vk / page_size] : 0;
+        if (kpage < 0 || kpage >= num_pages) kpage = 0;
+        if (vpage < 0 || vpage >= num_pages) vpage = 0;
+        KFrag32<DH> kf;
+        VFrag32<DH> vf;
+        load_k32<DH>(kf, kcache + (((size_t)kpage * nkv + kvh) * page_size + kk % page_size) * DH, g, t);
+        load_v32<DH>(vf, vcache + ((size_t)vpage * nkv + kvh) * DH * page_size + vk % page_size, page_size, g);
+        compute32<DH>(st, qa, kf, vf, key0, lo2, hi2, scale, t);
+    }
+}
+
+template <int DH, int KB>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
@@ -61,6 +95,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     __shared__ int is_last;
     pdl_launch_dependents();
     pdl_wait();
+    constexpr int kSplit = KB * kWarps;                // one block of KB keys per warp: one round trip to memory
     const int split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
     const int ctx = ctx_lens[s];
     const int p = ctx - 1;
@@ -74,24 +109,18 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     // query fragments: rows g and g + 8 are heads kvh * G + g (+ 8)
     const bf16* qrow = qkv + (size_t)s * (nh + 2 * nkv) * DH + (size_t)kvh * G * DH;
     unsigned qa[DH / 16][4];
-    load_q<DH>(qa, g < G ? qrow + (size_t)g * DH : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * DH : nullptr, t);
+    const bf16* q_lo = g < G ? qrow + (size_t)g * DH : nullptr;
+    const bf16* q_hi = g + 8 < G ? qrow + (size_t)(g + 8) * DH : nullptr;
+    if constexpr (KB == 16) load_q<DH>(qa, q_lo, q_hi, t);
+    else load_q32<DH>(qa, q_lo, q_hi, t);
     RowState<DH> st;
     st.init();
     const int lo2[2] = {lo, lo}, hi2[2] = {k_end - 1, k_end - 1};
     const int* bt = block_table + (size_t)s * max_blocks;
-    static_assert(kSplit == 16 * kWarps, "one block of 16 keys per warp: one round trip to memory");
     {
-        const int key0 = k_begin + warp * 16;
-        if (key0 < k_end && key0 + 16 > lo) {                  // warp-uniform
-            int page = bt[key0 / page_size];
-            if (page < 0 || page >= num_pages) page = 0;
-            const int off = key0 % page_size;
-            KFrag<DH> kf;
-            VFrag<DH> vf;
-            load_k<DH, true>(kf, kcache + (((size_t)page * nkv + kvh) * page_size + off) * DH, g, t);
-            load_v<DH, true>(vf, vcache + ((size_t)page * nkv + kvh) * DH * page_size + off, page_size, g, t);
-            compute16<DH>(st, qa, kf, vf, key0, lo2, hi2, scale, t);
-        }
+        const int key0 = k_begin + warp * KB;
+        if (key0 < k_end && key0 + KB > lo)                  // warp-uniform
+            block_step<DH, KB>(st, qa, kcache, vcache, bt, key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t);
     }
     const float m0 = st.m[0], m1 = st.m[1];
     const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
@@ -141,7 +170,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     }
     // the CTA that finishes last for this (sequence, kv head) merges the splits, in split order
     int first, last;
-    split_range(ctx, window, &first, &last);
+    split_range(ctx, window, kSplit, &first, &last);
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -220,7 +249,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
 // context over CTAs would only add partial results to write, merge and wait for.  Each of the CTA's warps
 // walks every WARPS-th block of 16 keys with a running softmax; the warps are merged through shared memory in
 // warp order at the end.  The assignment of blocks to warps depends on the sequence alone.
-template <int DH, int WARPS>
+template <int DH, int WARPS, int KB>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                               const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
@@ -237,24 +266,18 @@ decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restri
     const int g = lane >> 2, t = lane & 3;
     const bf16* qrow = qkv + (size_t)s * (nh + 2 * nkv) * DH + (size_t)kvh * G * DH;
     unsigned qa[DH / 16][4];
-    load_q<DH>(qa, g < G ? qrow + (size_t)g * DH : nullptr, g + 8 < G ? qrow + (size_t)(g + 8) * DH : nullptr, t);
+    const bf16* q_lo = g < G ? qrow + (size_t)g * DH : nullptr;
+    const bf16* q_hi = g + 8 < G ? qrow + (size_t)(g + 8) * DH : nullptr;
+    if constexpr (KB == 16) load_q<DH>(qa, q_lo, q_hi, t);
+    else load_q32<DH>(qa, q_lo, q_hi, t);
     RowState<DH> st;
     st.init();
     const int lo2[2] = {lo, lo}, hi2[2] = {p, p};
     const int* bt = block_table + (size_t)s * max_blocks;
-    const int b_first = lo / 16, b_last = p / 16;
+    const int b_first = lo / KB, b_last = p / KB;
 #pragma unroll 1
-    for (int b = b_first + warp; b <= b_last; b += WARPS) {
-        const int key0 = b * 16;
-        int page = bt[key0 / page_size];
-        if (page < 0 || page >= num_pages) page = 0;
-        const int off = key0 % page_size;
-        KFrag<DH> kf;
-        VFrag<DH> vf;
-        load_k<DH, true>(kf, kcache + (((size_t)page * nkv + kvh) * page_size + off) * DH, g, t);
-        load_v<DH, true>(vf, vcache + ((size_t)page * nkv + kvh) * DH * page_size + off, page_size, g, t);
-        compute16<DH>(st, qa, kf, vf, key0, lo2, hi2, scale, t);
-    }
+    for (int b = b_first + warp; b <= b_last; b += WARPS)
+        block_step<DH, KB>(st, qa, kcache, vcache, bt, b * KB, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t);
     const float m0 = st.m[0], m1 = st.m[1];
     const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
     float* sm_m = sm;
@@ -330,20 +353,22 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     if ((long long)S * nkv >= kWholeFrom) {
         // one CTA per (sequence, kv head) fills the GPU: no split of the context
-        constexpr int W = 16;
+        constexpr int W = 8, KB = DH <= 128 ? 32 : 16;
         const size_t wsmem = (2 * W * 16 + (size_t)W * G * DH) * sizeof(float);
         if (wsmem <= 200 * 1024) {
             static bool raised = false;
             if (!raised && wsmem > 48 * 1024) {
-                cudaError_t e = cudaFuncSetAttribute(decode_attention_whole_kernel<DH, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+                cudaError_t e = cudaFuncSetAttribute(decode_attention_whole_kernel<DH, W, KB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
                 if (e != cudaSuccess) return li_fail("attention (decode): cannot raise shared memory: %s", cudaGetErrorString(e));
                 raised = true;
             }
-            li_launch_pdl(decode_attention_whole_kernel<DH, W>, dim3(nkv, S), dim3(W * 32), wsmem, stream, (const bf16*)qkv, (const bf16*)kcache,
+            li_launch_pdl(decode_attention_whole_kernel<DH, W, KB>, dim3(nkv, S), dim3(W * 32), wsmem, stream, (const bf16*)qkv, (const bf16*)kcache,
                           (const bf16*)vcache, block_table, max_blocks, ctx_lens, (bf16*)out, nh, nkv, page_size, num_pages, scale, window);
             return li_check_launch("attention (decode, whole context)");
         }
     }
+    constexpr int KBS = DH <= 128 ? 32 : 16;
+    constexpr int kSplit = KBS * kWarps;
     const int nsplit = ceil_div(max_ctx_len > 0 ? max_ctx_len : 1, kSplit);
     float* part = nullptr;
     unsigned* counters = nullptr;
@@ -354,14 +379,14 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     const size_t smem = smem_floats * sizeof(float);
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<DH, KBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return li_fail("attention (decode): cannot raise shared memory: %s", cudaGetErrorString(e));
         attr_set = true;
     }
     LI_REQUIRE(smem <= 200 * 1024, "attention (decode): shared memory %zu too large", smem);
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     dim3 grid(nsplit, nkv, S);
-    li_launch_pdl(decode_attention_kernel<DH>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache, (const bf16*)vcache,
+    li_launch_pdl(decode_attention_kernel<DH, KBS>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache, (const bf16*)vcache,
                                                                       block_table, max_blocks, ctx_lens, part, counters, (bf16*)out,
                                                                       nh, nkv, page_size, num_pages, scale, window, nsplit);
     return li_check_launch("attention (decode)");
