@@ -216,3 +216,32 @@ LI_EXPORT int li_swiglu(const void* gate_up, void* out, int dtype, int T, int I,
         return li_fail("swiglu: unknown dtype %d", dtype);
     return li_check_launch("swiglu");
 }
+
+// out[tok, :] = hprime[tok, :] / sqrt(sum of ssq[:, tok] / width + eps): the normalised activation itself, for a
+// consumer that cannot take the factor into its own product (row_scale.cuh).  bfloat16.
+namespace {
+__global__ void apply_row_scale_kernel(const bf16* __restrict__ hprime, const float* __restrict__ ssq, int nparts, float width, float eps,
+                                       bf16* __restrict__ out, int M, int H) {
+    __shared__ float factor;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tok = blockIdx.x;
+    if (threadIdx.x < 32) {
+        float s = 0.0f;
+        for (int p = threadIdx.x; p < nparts; p += 32) s += ssq[(size_t)tok * nparts + p];
+        s = warp_sum(s);
+        if (threadIdx.x == 0) factor = 1.0f / sqrtf(s / width + eps);
+    }
+    __syncthreads();
+    const float f = factor;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) out[(size_t)tok * H + j] = __float2bfloat16_rn(__bfloat162float(hprime[(size_t)tok * H + j]) * f);
+}
+}  // namespace
+
+LI_EXPORT int li_apply_row_scale(const void* hprime, const float* ssq, int nparts, int width, float eps, void* out, int M, int H,
+                                 cudaStream_t stream) {
+    LI_REQUIRE(M >= 0 && H > 0 && nparts >= 1 && width >= 1, "apply_row_scale: bad sizes M=%d H=%d parts=%d width=%d", M, H, nparts, width);
+    if (M == 0) return 0;
+    li_launch_pdl(apply_row_scale_kernel, dim3(M), dim3(256), 0, stream, (const bf16*)hprime, ssq, nparts, (float)width, eps, (bf16*)out, M, H);
+    return li_check_launch("apply_row_scale");
+}

@@ -22,6 +22,7 @@
 // Requires K % 8 == 0 and 16-byte aligned operands; M <= 64.
 #include "common.cuh"
 #include "no_alloc.h"
+#include "row_scale.cuh"
 
 namespace {
 
@@ -63,11 +64,11 @@ struct RopeArgs {
     bf16* vcache;
     int nh, nkv, dh, page_size, num_pages, write;
 };
-enum { kEpiNone = 0, kEpiSwiglu = 1, kEpiRope = 2 };
+enum { kEpiNone = 0, kEpiSwiglu = 1, kEpiRope = 2, kEpiAddScaled = 3 };
 
 template <int NT, typename Get>
 __device__ __forceinline__ void store_rope(Get get, const float* __restrict__ bias, bf16* __restrict__ out, int tile, int M, int N,
-                                           const RopeArgs& ra, int nthreads) {
+                                           const RopeArgs& ra, int nthreads, const float* rs_sm) {
     const int tiles_per_head = ra.dh >> 4, half = ra.dh >> 1;
     const int head = tile / tiles_per_head, jt = tile - head * tiles_per_head;
     for (int q = threadIdx.x; q < NT * 64; q += nthreads) {
@@ -78,6 +79,10 @@ __device__ __forceinline__ void store_rope(Get get, const float* __restrict__ bi
         const int jj = jt * 8 + (l >> 2);                       // index of the pair within the head
         const int r0 = head * ra.dh + jj, r1 = r0 + half;
         float x0 = get(e), x1 = get(e + 64);
+        if (rs_sm) {
+            x0 *= rs_sm[tok];
+            x1 *= rs_sm[tok];
+        }
         if (bias) {
             x0 += bias[r0];
             x1 += bias[r1];
@@ -121,12 +126,14 @@ __device__ __forceinline__ void store_rope(Get get, const float* __restrict__ bi
 // up * gate / (1 + exp(-gate)) (src/ops/swiglu/op.cpp:17-23), stored at column n0 / 2 + g.
 template <int NT, typename Tout, bool kSwiglu, typename Get>
 __device__ __forceinline__ void store_elements(Get get, const float* __restrict__ bias, Tout* __restrict__ out, int n0, int M, int N,
-                                               int nthreads) {
+                                               int nthreads, const float* rs_sm) {
+    // rs_sm: a factor per token (the reciprocal root of an RMSNorm whose weights are already in the input), or nullptr
     if (!kSwiglu) {
         for (int e = threadIdx.x; e < NT * 128; e += nthreads) {
-            const float v = get(e);
+            float v = get(e);
             const int l = e & 31, ji = e >> 5, i = ji & 3, j = ji >> 2;
             const int row = n0 + (l >> 2) + ((i >> 1) << 3), tok = j * 8 + ((l & 3) << 1) + (i & 1);
+            if (rs_sm) v *= rs_sm[tok];
             if (row < N && tok < M) out[(size_t)tok * N + row] = from_float<Tout>(bias ? v + bias[row] : v);
         }
     } else {
@@ -134,21 +141,59 @@ __device__ __forceinline__ void store_elements(Get get, const float* __restrict_
         for (int q = threadIdx.x; q < NT * 64; q += nthreads) {
             const int l = q & 31, i = (q >> 5) & 1, j = q >> 6;
             const int e = (j * 4 + i) * 32 + l;
-            const float gate = get(e), up = get(e + 64);
+            float gate = get(e), up = get(e + 64);
             const int col = (n0 >> 1) + (l >> 2), tok = j * 8 + ((l & 3) << 1) + i;
+            if (rs_sm) {
+                gate *= rs_sm[tok];
+                up *= rs_sm[tok];
+            }
             if (col < half_n && tok < M) out[(size_t)tok * half_n + col] = from_float<Tout>(up * (gate / (1.0f + expf(-gate))));
         }
+    }
+}
+
+// Fourth epilogue (row_scale.cuh): the product is added to the float32 residual stream, this CTA's 16 columns of
+// it; the sums also leave as bfloat16(norm_weight * x) for the next product, with their squares added up per token.
+// xpre: the stream's old values of this thread's elements, loaded while the weights were streaming.
+template <int NT, int XP, typename Get>
+__device__ __forceinline__ void store_add_scaled(Get get, const float* __restrict__ bias, const AddScaled& add, const float (&xpre)[XP],
+                                                 int tile, int M, int N, int nthreads, float* tile_sm) {
+    const int n0 = tile * 16;
+#pragma unroll
+    for (int q = 0; q < XP; ++q) {
+        const int e = threadIdx.x + q * nthreads;
+        if (e < NT * 128) {
+            const int l = e & 31, ji = e >> 5, i = ji & 3, j = ji >> 2;
+            const int r = (l >> 2) + ((i >> 1) << 3), row = n0 + r, tok = j * 8 + ((l & 3) << 1) + (i & 1);
+            float x = 0.0f;
+            if (row < N && tok < M) {
+                const float v = get(e);
+                x = xpre[q] + (bias ? v + bias[row] : v);
+                __stcg(add.x32 + (size_t)tok * N + row, x);              // other CTAs own the rest of the line: past L1
+                add.hprime[(size_t)tok * N + row] = __float2bfloat16_rn(add.norm_weight[row] * x);
+            }
+            tile_sm[tok * 16 + r] = x;
+        }
+    }
+    __syncthreads();
+    for (int tok = threadIdx.x; tok < M; tok += nthreads) {
+        float s = 0.0f;
+#pragma unroll
+        for (int r = 0; r < 16; ++r) s += tile_sm[tok * 16 + r] * tile_sm[tok * 16 + r];
+        add.ssq_out[(size_t)tok * gridDim.x + tile] = s;
     }
 }
 
 template <int NT, int WARPS, typename Tout, int kEpi>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const float* __restrict__ bias, Tout* __restrict__ out,
-                 float* __restrict__ partial, unsigned* __restrict__ counters, int M, int N, int K, int ksplit, const RopeArgs rope) {
+                 float* __restrict__ partial, unsigned* __restrict__ counters, int M, int N, int K, int ksplit, const RopeArgs rope,
+                 const RowScale rs, const AddScaled add) {
     constexpr bool kSwiglu = kEpi == kEpiSwiglu;
     extern __shared__ float red_raw[];                 // [WARPS][NT * 128]
     float (*red)[NT * 128] = reinterpret_cast<float (*)[NT * 128]>(red_raw);
     __shared__ int is_last;
+    __shared__ float rs_sm[NT * 8];
     const int tile = blockIdx.x, split = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -193,6 +238,45 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
     pdl_launch_dependents();
     load_w(a, b, wb);
     pdl_wait();
+    // What the epilogue needs from memory is asked for now and used after the weights have streamed past: the partial
+    // sums of squares for the tokens' factors (when a lane has at most kPre parts per token), and the old values of
+    // the residual stream.
+    constexpr int kPre = 4;                                          // parts a lane holds per token: up to 128 parts
+    constexpr int kTok = NT * 8 > WARPS ? NT * 8 / WARPS : 1;        // tokens a warp computes the factor of
+    float pre[kTok][kPre];
+    const bool pre_fits = rs.ssq != nullptr && rs.nparts <= 32 * kPre;
+#pragma unroll
+    for (int ti = 0; ti < kTok; ++ti) {
+        const int tok = warp + ti * WARPS;
+#pragma unroll
+        for (int q = 0; q < kPre; ++q) {
+            const int p = lane + 32 * q;
+            pre[ti][q] = (pre_fits && tok < M && p < rs.nparts) ? __ldcg(rs.ssq + (size_t)tok * rs.nparts + p) : 0.0f;
+        }
+    }
+    // Many tokens: registers are short, so the factors are finished here, behind one round trip that the first weights
+    // (already on their way) cover; few tokens: after the loop.
+    constexpr bool kFactorsFirst = NT >= 4;
+    auto finish_factors = [&]() {
+#pragma unroll
+        for (int ti = 0; ti < kTok; ++ti) {
+            const int tok = warp + ti * WARPS;
+            const float ssum = warp_sum(((pre[ti][0] + pre[ti][1]) + pre[ti][2]) + pre[ti][3]);
+            if (lane == 0 && tok < M) rs_sm[tok] = 1.0f / sqrtf(ssum / rs.width + rs.eps);
+        }
+    };
+    if (kFactorsFirst && pre_fits) finish_factors();
+    constexpr int kXPre = kEpi == kEpiAddScaled ? (NT * 128 + WARPS * 32 - 1) / (WARPS * 32) : 1;
+    float xpre[kXPre];
+    if constexpr (kEpi == kEpiAddScaled) {
+#pragma unroll
+        for (int q = 0; q < kXPre; ++q) {
+            const int e = threadIdx.x + q * WARPS * 32;
+            const int l = e & 31, ji = e >> 5, i = ji & 3, j = ji >> 2;
+            const int row = n0 + (l >> 2) + ((i >> 1) << 3), tok = j * 8 + ((l & 3) << 1) + (i & 1);
+            xpre[q] = (e < NT * 128 && row < N && tok < M) ? __ldcg(add.x32 + (size_t)tok * N + row) : 0.0f;
+        }
+    }
     for (int c = wb; c < we; c += U) {
         if (c + U < we) load_w(an, bn, c + U);
 #pragma unroll
@@ -217,6 +301,15 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
     for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) red[warp][(j * 4 + i) * 32 + lane] = acc[j][i];
+    if (rs.ssq) {
+        // the tokens' factors; the same order of summation either way (a lane's parts ascending, then the butterfly)
+        if (pre_fits) {
+            if (!kFactorsFirst) finish_factors();
+        } else {
+            row_scales_of_warp<1>(rs, M, warp, WARPS, lane, rs_sm);
+        }
+    }
+    const float* factors = rs.ssq ? rs_sm : nullptr;
     __syncthreads();
 
     auto warps_sum = [&](int e) {
@@ -226,11 +319,19 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
         return v;
     };
     if (kEpi == kEpiRope) {
-        store_rope<NT>(warps_sum, bias, reinterpret_cast<bf16*>(out), tile, M, N, rope, WARPS * 32);       // never split along k
+        store_rope<NT>(warps_sum, bias, reinterpret_cast<bf16*>(out), tile, M, N, rope, WARPS * 32, factors);       // never split along k
         return;
     }
+    auto finish = [&](auto get) {
+        if constexpr (kEpi == kEpiAddScaled) {
+            __shared__ float tile_sm[NT * 8 * 16];
+            store_add_scaled<NT>(get, bias, add, xpre, tile, M, N, WARPS * 32, tile_sm);
+        } else {
+            store_elements<NT, Tout, kSwiglu>(get, bias, out, n0, M, N, WARPS * 32, factors);
+        }
+    };
     if (ksplit == 1) {
-        store_elements<NT, Tout, kSwiglu>(warps_sum, bias, out, n0, M, N, WARPS * 32);
+        finish(warps_sum);
         return;
     }
     const size_t pbase = ((size_t)split * gridDim.x + tile) * (NT * 128);
@@ -250,8 +351,8 @@ gemv_bf16_kernel(const bf16* __restrict__ X, const bf16* __restrict__ W, const f
         for (int s = 0; s < ksplit; ++s) v += __ldcg(&partial[((size_t)s * tiles + tile) * (NT * 128) + e]);
         return v;
     };
-    store_elements<NT, Tout, kSwiglu>(splits_sum, bias, out, n0, M, N, WARPS * 32);
     if (threadIdx.x == 0) counters[tile] = 0;          // ready for the next launch on this stream
+    finish(splits_sum);
 }
 
 int ensure_workspace(Workspace** ws) {
@@ -294,7 +395,7 @@ void choose_shape(int ntiles, int K, int nt, int* warps, int* ksplit) {
 
 template <int NT, int WARPS, typename Tout, int kEpi>
 int launch_kernel(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, int ksplit, Workspace* ws,
-                  cudaStream_t stream, const RopeArgs& rope = RopeArgs{}) {
+                  cudaStream_t stream, const RopeArgs& rope = RopeArgs{}, const RowScale& rs = RowScale{}, const AddScaled& add = AddScaled{}) {
     constexpr int kSwiglu = kEpi;
     dim3 grid(ceil_div(N, 16), ksplit);
     constexpr size_t smem = (size_t)WARPS * NT * 128 * sizeof(float);
@@ -307,42 +408,45 @@ int launch_kernel(const void* a, const void* w, const float* bias, void* out, in
         }
     }
     li_launch_pdl(gemv_bf16_kernel<NT, WARPS, Tout, kSwiglu>, grid, dim3(WARPS * 32), smem, stream, (const bf16*)a, (const bf16*)w, bias,
-                  (Tout*)out, ws->partial, ws->counters, M, N, K, ksplit, rope);
+                  (Tout*)out, ws->partial, ws->counters, M, N, K, ksplit, rope, rs, add);
     return li_check_launch("linear (gemv)");
 }
 
-template <int NT, typename Tout, bool kSwiglu>
-int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
+template <int NT, typename Tout, int kEpi>
+int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, const RowScale& rs,
+           const AddScaled& add = AddScaled{}) {
     const int ntiles = ceil_div(N, 16);
     int warps = 4, ksplit = 1;
     choose_shape(ntiles, K, NT, &warps, &ksplit);
     Workspace* ws = nullptr;
     if (int rc = ensure_workspace(&ws)) return rc;
     LI_REQUIRE(ntiles <= kMaxTiles || ksplit == 1, "linear (gemv): N=%d has too many tiles for split-k", N);
-    if (warps == 16) return launch_kernel<NT, 16, Tout, kSwiglu>(a, w, bias, out, M, N, K, ksplit, ws, stream);
-    if (warps >= 8) return launch_kernel<NT, 8, Tout, kSwiglu>(a, w, bias, out, M, N, K, ksplit, ws, stream);
-    return launch_kernel<NT, 4, Tout, kSwiglu>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+    if (warps == 16) return launch_kernel<NT, 16, Tout, kEpi>(a, w, bias, out, M, N, K, ksplit, ws, stream, RopeArgs{}, rs, add);
+    if (warps >= 8) return launch_kernel<NT, 8, Tout, kEpi>(a, w, bias, out, M, N, K, ksplit, ws, stream, RopeArgs{}, rs, add);
+    return launch_kernel<NT, 4, Tout, kEpi>(a, w, bias, out, M, N, K, ksplit, ws, stream, RopeArgs{}, rs, add);
 }
 
-template <typename Tout, bool kSwiglu>
-int launch_nt(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
-    if (M <= 8) return launch<1, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
-    if (M <= 16) return launch<2, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
-    if (M <= 32) return launch<4, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
-    return launch<8, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
+template <typename Tout, int kEpi>
+int launch_nt(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, const RowScale& rs,
+              const AddScaled& add = AddScaled{}) {
+    if (M <= 8) return launch<1, Tout, kEpi>(a, w, bias, out, M, N, K, stream, rs, add);
+    if (M <= 16) return launch<2, Tout, kEpi>(a, w, bias, out, M, N, K, stream, rs, add);
+    if (M <= 32) return launch<4, Tout, kEpi>(a, w, bias, out, M, N, K, stream, rs, add);
+    return launch<8, Tout, kEpi>(a, w, bias, out, M, N, K, stream, rs, add);
 }
 
 template <int NT>
-int launch_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const RopeArgs& rope, cudaStream_t stream) {
+int launch_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const RopeArgs& rope, const RowScale& rs,
+                cudaStream_t stream) {
     const int ntiles = ceil_div(N, 16);
     int warps = 4, ksplit = 1;
     choose_shape(ntiles, K, NT, &warps, &ksplit);
     Workspace* ws = nullptr;
     if (int rc = ensure_workspace(&ws)) return rc;
     // the epilogue needs both halves of a pair in one CTA and the whole sum: no split along k
-    if (warps == 16) return launch_kernel<NT, 16, bf16, kEpiRope>(a, w, bias, out, M, N, K, 1, ws, stream, rope);
-    if (warps >= 8) return launch_kernel<NT, 8, bf16, kEpiRope>(a, w, bias, out, M, N, K, 1, ws, stream, rope);
-    return launch_kernel<NT, 4, bf16, kEpiRope>(a, w, bias, out, M, N, K, 1, ws, stream, rope);
+    if (warps == 16) return launch_kernel<NT, 16, bf16, kEpiRope>(a, w, bias, out, M, N, K, 1, ws, stream, rope, rs);
+    if (warps >= 8) return launch_kernel<NT, 8, bf16, kEpiRope>(a, w, bias, out, M, N, K, 1, ws, stream, rope, rs);
+    return launch_kernel<NT, 4, bf16, kEpiRope>(a, w, bias, out, M, N, K, 1, ws, stream, rope, rs);
 }
 
 }  // namespace
@@ -355,28 +459,38 @@ bool li_gemv_rope_accepts(const void* a, const void* w, int M, int N, int K, int
 
 int li_linear_gemv_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const int* positions,
                         const float* denom, const int* slot_mapping, void* kcache, void* vcache, int nh, int nkv, int dh,
-                        int page_size, int num_pages, int write, cudaStream_t stream) {
+                        int page_size, int num_pages, int write, const RowScale& rs, cudaStream_t stream) {
     RopeArgs ra{positions, denom, slot_mapping, (bf16*)kcache, (bf16*)vcache, nh, nkv, dh, page_size, num_pages, write};
-    if (M <= 8) return launch_rope<1>(a, w, bias, out, M, N, K, ra, stream);
-    if (M <= 16) return launch_rope<2>(a, w, bias, out, M, N, K, ra, stream);
-    if (M <= 32) return launch_rope<4>(a, w, bias, out, M, N, K, ra, stream);
-    return launch_rope<8>(a, w, bias, out, M, N, K, ra, stream);
+    if (M <= 8) return launch_rope<1>(a, w, bias, out, M, N, K, ra, rs, stream);
+    if (M <= 16) return launch_rope<2>(a, w, bias, out, M, N, K, ra, rs, stream);
+    if (M <= 32) return launch_rope<4>(a, w, bias, out, M, N, K, ra, rs, stream);
+    return launch_rope<8>(a, w, bias, out, M, N, K, ra, rs, stream);
 }
 
 bool li_gemv_bf16_accepts(int M, int N, int K) { return M >= 1 && M <= kMaxM && K % 8 == 0 && N >= 1; }
 
 int li_linear_gemv_bf16(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
-                        int epilogue, cudaStream_t stream) {
+                        int epilogue, cudaStream_t stream, const RowScale& rs) {
     LI_REQUIRE(li_gemv_bf16_accepts(M, N, K), "linear (gemv): refuses M=%d N=%d K=%d (M <= %d, K a multiple of 8)", M, N, K, kMaxM);
     LI_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear (gemv): operands must be 16-byte aligned");
     if (epilogue == LI_EPILOGUE_SWIGLU) {
         LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
                    "linear (gemv): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
-        return launch_nt<bf16, true>(a, w, bias, out, M, N, K, stream);
+        return launch_nt<bf16, kEpiSwiglu>(a, w, bias, out, M, N, K, stream, rs);
     }
-    if (dtype_out == LI_BF16) return launch_nt<bf16, false>(a, w, bias, out, M, N, K, stream);
-    if (dtype_out == LI_F32) return launch_nt<float, false>(a, w, bias, out, M, N, K, stream);
+    if (dtype_out == LI_BF16) return launch_nt<bf16, kEpiNone>(a, w, bias, out, M, N, K, stream, rs);
+    if (dtype_out == LI_F32) return launch_nt<float, kEpiNone>(a, w, bias, out, M, N, K, stream, rs);
     return li_fail("linear (gemv): unsupported output dtype %d", dtype_out);
+}
+
+// x32 += a w^T (+ bias), hprime = bfloat16(norm_weight * x32), ssq_out[token, tile] = sums of squares (row_scale.cuh).
+int li_gemv_bf16_tiles(int N) { return ceil_div(N, 16); }
+
+int li_linear_gemv_bf16_add_scaled(const void* a, const void* w, const float* bias, int M, int N, int K, const AddScaled& add,
+                                   cudaStream_t stream) {
+    LI_REQUIRE(li_gemv_bf16_accepts(M, N, K), "linear + add (gemv): refuses M=%d N=%d K=%d (M <= %d, K a multiple of 8)", M, N, K, kMaxM);
+    LI_REQUIRE(((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0), "linear + add (gemv): operands must be 16-byte aligned");
+    return launch_nt<bf16, kEpiAddScaled>(a, w, bias, add.hprime, M, N, K, stream, RowScale{}, add);
 }
 
 // ---- the entry point that allocates nothing (no_alloc.h) ---------------------------------
@@ -425,9 +539,9 @@ int launch_static(const void* a, const void* w, const float* bias, void* out, in
         cudaError_t e = cudaMemsetAsync(ws->counters, 0, (size_t)ntiles * sizeof(unsigned), stream);
         if (e != cudaSuccess) return li_fail("linear (gemv, static scratch): clearing the counters: %s", cudaGetErrorString(e));
     }
-    if (warps == 16) return launch_kernel<NT, 16, Tout, false>(a, w, bias, out, M, N, K, ksplit, ws, stream);
-    if (warps >= 8) return launch_kernel<NT, 8, Tout, false>(a, w, bias, out, M, N, K, ksplit, ws, stream);
-    return launch_kernel<NT, 4, Tout, false>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+    if (warps == 16) return launch_kernel<NT, 16, Tout, kEpiNone>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+    if (warps >= 8) return launch_kernel<NT, 8, Tout, kEpiNone>(a, w, bias, out, M, N, K, ksplit, ws, stream);
+    return launch_kernel<NT, 4, Tout, kEpiNone>(a, w, bias, out, M, N, K, ksplit, ws, stream);
 }
 
 template <typename Tout>

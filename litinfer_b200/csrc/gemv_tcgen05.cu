@@ -17,6 +17,7 @@
 // (up * gate / (1 + exp(-gate)), src/ops/swiglu/op.cpp:17-23).
 //
 // K a multiple of 8; waits bounded as in the other tcgen05 kernel.
+#include "row_scale.cuh"
 #include "tcgen05.cuh"
 
 namespace {
@@ -39,6 +40,8 @@ struct __align__(1024) Smem {
     unsigned long long accum;
     unsigned tmem_base;
     int is_last;
+    float factor[64];                // per token: the reciprocal root of the norm before this product
+    float squares[4][64];            // per epilogue warp and token: sums of squares of the new residual values
 };
 
 struct Workspace {
@@ -78,11 +81,15 @@ __device__ __forceinline__ void tmem_ld<64>(unsigned taddr, float (&v)[64]) {
     }
 }
 
-template <int BT, typename Tout, bool kSwiglu>
+enum { kEpiNone = 0, kEpiSwiglu = 1, kEpiAddScaled = 2 };
+
+template <int BT, typename Tout, int kEpi>
 __global__ void __launch_bounds__(kThreads)
 gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const float* __restrict__ bias, Tout* __restrict__ out, float* __restrict__ partial,
-                    unsigned* __restrict__ counters, int M, int N, int K, int ksplit, int* __restrict__ error_flag) {
+                    unsigned* __restrict__ counters, int M, int N, int K, int ksplit, int* __restrict__ error_flag, const RowScale rs,
+                    const AddScaled add) {
+    constexpr bool kSwiglu = kEpi == kEpiSwiglu, kAdd = kEpi == kEpiAddScaled;
     extern __shared__ unsigned char smem_raw[];
     Smem<BT>& sm = *reinterpret_cast<Smem<BT>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -161,6 +168,18 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         const int quarter = warp & 3;
         const int r_in_tile = quarter * 32 + lane;
         const int row = n0 + r_in_tile;
+        // while the weights stream: the tokens' factors from the partial sums of squares, and the old values of
+        // the residual stream that the product will be added to (row_scale.cuh)
+        if (rs.ssq) {
+            // a warp takes every fourth token, eight tokens' loads in flight at once
+            row_scales_of_warp<8>(rs, M, warp - 2, 4, lane, sm.factor);
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        float xold[kAdd ? BT : 1];
+        if constexpr (kAdd) {
+#pragma unroll
+            for (int j = 0; j < BT; ++j) xold[j] = (j < M && row < N) ? __ldcg(add.x32 + (size_t)j * N + row) : 0.0f;
+        }
         const bool ok = mbar_wait(&sm.accum, 0);
         if (!ok) {
             if (lane == 0) atomicExch(error_flag, 3);
@@ -206,8 +225,33 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     if (warp == 2 && lane == 0) counters[tile] = 0;          // ready for the next launch on this stream
                 }
             }
+            if (write && rs.ssq) {
+#pragma unroll
+                for (int j = 0; j < BT; ++j)
+                    if (j < M) v[j] *= sm.factor[j];
+            }
             if (write) {
-                if (!kSwiglu) {
+                if constexpr (kAdd) {
+                    // into the residual stream, and on to the next product as bfloat16(norm_weight * x) with the sums of x^2
+                    const float b = (bias && row < N) ? bias[row] : 0.0f;
+                    const float nw = row < N ? add.norm_weight[row] : 0.0f;
+#pragma unroll
+                    for (int j = 0; j < BT; ++j) {
+                        if (j < M) {                                       // uniform
+                            const float x = row < N ? xold[j] + (v[j] + b) : 0.0f;
+                            if (row < N) {
+                                __stcg(add.x32 + (size_t)j * N + row, x);
+                                add.hprime[(size_t)j * N + row] = __float2bfloat16_rn(nw * x);
+                            }
+                            const float sq = warp_sum(x * x);
+                            if (lane == 0) sm.squares[quarter][j] = sq;
+                        }
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    const int tid = (int)threadIdx.x - 64;
+                    if (tid < M)
+                        add.ssq_out[(size_t)tid * gridDim.x + tile] = ((sm.squares[0][tid] + sm.squares[1][tid]) + sm.squares[2][tid]) + sm.squares[3][tid];
+                } else if constexpr (!kSwiglu) {
                     const float b = (bias && row < N) ? bias[row] : 0.0f;
 #pragma unroll
                     for (int j = 0; j < BT; ++j)
@@ -265,8 +309,9 @@ int choose_ksplit(int N, int K) {
     return ks;
 }
 
-template <int BT, typename Tout, bool kSwiglu>
-int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
+template <int BT, typename Tout, int kEpi>
+int launch(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, const RowScale& rs,
+           const AddScaled& add) {
     EncodeTiledFn encode = nullptr;
     int *err_host = nullptr, *err_dev = nullptr;
     if (int rc = setup(&encode, &err_host, &err_dev)) return rc;
@@ -283,20 +328,21 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     const size_t smem = sizeof(Smem<BT>) + 1024;
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_tcgen05_kernel<BT, Tout, kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemv_tcgen05_kernel<BT, Tout, kEpi>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return li_fail("linear (tcgen05 gemv): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
-    li_launch_pdl(gemv_tcgen05_kernel<BT, Tout, kSwiglu>, dim3(tiles, ksplit), dim3(kThreads), smem, stream, map_w, map_x, bias, (Tout*)out,
-                  ws->partial, ws->counters, M, N, K, ksplit, err_dev);
+    li_launch_pdl(gemv_tcgen05_kernel<BT, Tout, kEpi>, dim3(tiles, ksplit), dim3(kThreads), smem, stream, map_w, map_x, bias, (Tout*)out,
+                  ws->partial, ws->counters, M, N, K, ksplit, err_dev, rs, add);
     return li_check_launch("linear (tcgen05 gemv)");
 }
 
-template <typename Tout, bool kSwiglu>
-int launch_bt(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream) {
-    if (M <= 16) return launch<16, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
-    if (M <= 32) return launch<32, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
-    return launch<64, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream);
+template <typename Tout, int kEpi>
+int launch_bt(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, const RowScale& rs,
+              const AddScaled& add = AddScaled{}) {
+    if (M <= 16) return launch<16, Tout, kEpi>(a, w, bias, out, M, N, K, stream, rs, add);
+    if (M <= 32) return launch<32, Tout, kEpi>(a, w, bias, out, M, N, K, stream, rs, add);
+    return launch<64, Tout, kEpi>(a, w, bias, out, M, N, K, stream, rs, add);
 }
 
 }  // namespace
@@ -306,14 +352,23 @@ bool li_gemv_tcgen05_accepts(const void* a, const void* w, int M, int N, int K) 
 }
 
 int li_linear_gemv_tcgen05(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
-                           int epilogue, cudaStream_t stream) {
+                           int epilogue, cudaStream_t stream, const RowScale& rs) {
     LI_REQUIRE(li_gemv_tcgen05_accepts(a, w, M, N, K), "linear (tcgen05 gemv): refuses M=%d N=%d K=%d (M <= 64, K a multiple of 8, 16-byte aligned operands)", M, N, K);
     if (epilogue == LI_EPILOGUE_SWIGLU) {
         LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
                    "linear (tcgen05 gemv): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
-        return launch_bt<bf16, true>(a, w, bias, out, M, N, K, stream);
+        return launch_bt<bf16, kEpiSwiglu>(a, w, bias, out, M, N, K, stream, rs);
     }
-    if (dtype_out == LI_BF16) return launch_bt<bf16, false>(a, w, bias, out, M, N, K, stream);
-    if (dtype_out == LI_F32) return launch_bt<float, false>(a, w, bias, out, M, N, K, stream);
+    if (dtype_out == LI_BF16) return launch_bt<bf16, kEpiNone>(a, w, bias, out, M, N, K, stream, rs);
+    if (dtype_out == LI_F32) return launch_bt<float, kEpiNone>(a, w, bias, out, M, N, K, stream, rs);
     return li_fail("linear (tcgen05 gemv): unsupported output dtype %d", dtype_out);
+}
+
+// x32 += a w^T (+ bias), hprime = bfloat16(norm_weight * x32), ssq_out[token, tile] = sums of squares (row_scale.cuh).
+int li_gemv_tcgen05_tiles(int N) { return ceil_div(N, BR); }
+
+int li_linear_gemv_tcgen05_add_scaled(const void* a, const void* w, const float* bias, int M, int N, int K, const AddScaled& add,
+                                      cudaStream_t stream) {
+    LI_REQUIRE(li_gemv_tcgen05_accepts(a, w, M, N, K), "linear + add (tcgen05 gemv): refuses M=%d N=%d K=%d", M, N, K);
+    return launch_bt<bf16, kEpiAddScaled>(a, w, bias, add.hprime, M, N, K, stream, RowScale{}, add);
 }

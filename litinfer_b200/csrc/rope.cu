@@ -12,6 +12,7 @@
 // kernels want to read them (LitInfer caches k after rotation as well,
 // src/llaisys/models/qwen2.cpp:626-673).
 #include "common.cuh"
+#include "row_scale.cuh"
 
 namespace {
 
@@ -163,21 +164,34 @@ LI_EXPORT int li_rope_kv_write(void* qkv, int dtype, const int* positions, const
 // Otherwise: the product, then the kernel above.
 int li_linear_gemv_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const int* positions,
                         const float* denom, const int* slot_mapping, void* kcache, void* vcache, int nh, int nkv, int dh,
-                        int page_size, int num_pages, int write, cudaStream_t stream);
+                        int page_size, int num_pages, int write, const RowScale& rs, cudaStream_t stream);
 bool li_gemv_rope_accepts(const void* a, const void* w, int M, int N, int K, int nh, int nkv, int dh, int rotary_dim);
 extern "C" int li_linear(const void* a, const void* w, const float* bias, void* out, int dtype_in, int dtype_out, int M, int N, int K,
                          int epilogue, cudaStream_t stream);
+extern "C" int li_linear_scaled(const void* a, const void* w, const float* bias, void* out, int dtype_in, int dtype_out, int M, int N,
+                                int K, int epilogue, const float* ssq, int nparts, int width, float eps, cudaStream_t stream);
 
 LI_EXPORT int li_linear_rope_kv(const void* a, const void* w, const float* bias, void* qkv, int dtype, const int* positions,
                                 const float* denom, int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T,
                                 int K, int nh, int nkv, int dh, int page_size, int num_pages, int write, int allow_fused,
-                                cudaStream_t stream) {
+                                const float* ssq, int nparts, int width, float eps, cudaStream_t stream) {
+    // ssq (or nullptr): partial sums of squares for a factor per token on the product, as in li_linear_scaled
     const int N = (nh + 2 * nkv) * dh;
     if (T == 0) return 0;
+    RowScale rs;
+    if (ssq) {
+        LI_REQUIRE(nparts >= 1 && width >= 1, "linear_rope_kv: bad partial sums (%d parts, width %d)", nparts, width);
+        rs.ssq = ssq;
+        rs.nparts = nparts;
+        rs.width = (float)width;
+        rs.eps = eps;
+    }
     if (allow_fused && dtype == LI_BF16 && li_gemv_rope_accepts(a, w, T, N, K, nh, nkv, dh, rotary_dim))
         return li_linear_gemv_rope(a, w, bias, qkv, T, N, K, positions, denom, slot_mapping, kcache, vcache, nh, nkv, dh, page_size,
-                                   num_pages, write, stream);
-    if (int rc = li_linear(a, w, bias, qkv, dtype, dtype, T, N, K, LI_EPILOGUE_NONE, stream)) return rc;
+                                   num_pages, write, rs, stream);
+    if (ssq) {
+        if (int rc = li_linear_scaled(a, w, bias, qkv, dtype, dtype, T, N, K, LI_EPILOGUE_NONE, ssq, nparts, width, eps, stream)) return rc;
+    } else if (int rc = li_linear(a, w, bias, qkv, dtype, dtype, T, N, K, LI_EPILOGUE_NONE, stream)) return rc;
     return li_rope_kv_write(qkv, dtype, positions, denom, rotary_dim, slot_mapping, kcache, vcache, T, nh, nkv, dh, page_size, num_pages,
                             write, stream);
 }

@@ -158,17 +158,78 @@ def _linear_args(a, weight, bias, out, epilogue):
 
 
 def linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
-           epilogue: Optional[str] = None) -> None:
+           epilogue: Optional[str] = None, row_scale=None) -> None:
     """out[M, N] = a[M, K] weight[N, K]^T (+ bias[N]); float32 accumulation;
     out is in the run dtype or float32.
+
+    ``row_scale=(ssq, width, eps)``: every token's row of the product is multiplied by
+    ``1 / sqrt(sum_p ssq[t, p] / width + eps)`` before bias and epilogue (see :func:`linear_add_scaled`); an error
+    unless :func:`linear_scaled_accepts`.
 
     ``epilogue="swiglu"`` (bfloat16 only): ``weight`` holds gate and up rows interleaved in
     groups of 8 (see :func:`interleave_gate_up`) and out[M, N / 2] = up * gate / (1 + exp(-gate))."""
     M, N, Kd = _linear_args(a, weight, bias, out, epilogue)
     if M == 0:
         return
+    if row_scale is not None:
+        _check(library().li_linear_scaled(_p(a), _p(weight), _p(bias), _p(out), _i(_dt(a)), _i(_dt(out)), _i(M), _i(N), _i(Kd),
+                                          _i(EPILOGUES[epilogue]), *_row_scale_args(row_scale, M), _stream(out)), "linear (scaled)")
+        return
     _check(library().li_linear(_p(a), _p(weight), _p(bias), _p(out), _i(_dt(a)), _i(_dt(out)), _i(M), _i(N), _i(Kd),
                                _i(EPILOGUES[epilogue]), _stream(out)), "linear")
+
+
+def _row_scale_args(row_scale, M: int):
+    ssq, width, eps = row_scale
+    _need(ssq, "partial sums of squares", torch.float32)
+    if ssq.dim() != 2 or ssq.shape[0] != M:
+        raise KernelError(f"partial sums of squares of shape {tuple(ssq.shape)} for {M} tokens")
+    return _p(ssq), _i(ssq.shape[1]), _i(int(width)), _f(float(eps))
+
+
+def linear_scaled_accepts(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> bool:
+    """Whether :func:`linear` takes ``row_scale`` for these operands (bfloat16, at most 64 tokens)."""
+    M, Kd = a.shape
+    return bool(library().li_linear_scaled_accepts(_p(a), _p(weight), _p(out), _i(_dt(a)), _i(M), _i(weight.shape[0]), _i(Kd)))
+
+
+def linear_add_scaled_parts(a: torch.Tensor, weight: torch.Tensor, x32: torch.Tensor, hprime: torch.Tensor) -> int:
+    """How many partial sums per token :func:`linear_add_scaled` writes for these operands; 0 if no kernel takes them."""
+    M, Kd = a.shape
+    return int(library().li_linear_add_scaled_parts(_p(a), _p(weight), _p(x32), _p(hprime), _i(_dt(a)), _i(M), _i(weight.shape[0]), _i(Kd)))
+
+
+def linear_add_scaled(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], x32: torch.Tensor,
+                      norm_weight: torch.Tensor, hprime: torch.Tensor, ssq: torch.Tensor) -> None:
+    """The product into the residual stream with the next RMSNorm half done, as one kernel (few bfloat16 tokens):
+    ``x32 += a weight^T (+ bias)``; ``hprime = bfloat16(norm_weight * x32)``; ``ssq[t, p]`` = the sum of the new
+    ``x32[t]^2`` over the columns of the product's tile p.  The normalised activation is
+    ``hprime[t] / sqrt(sum_p ssq[t, p] / N + eps)``; :func:`linear` applies that factor to its own result
+    (``row_scale``), :func:`apply_row_scale` to hprime itself."""
+    M, Kd = a.shape
+    N = weight.shape[0]
+    _need(a, "linear input", torch.bfloat16)
+    _need(weight, "linear weight", a.dtype, (N, Kd))
+    if bias is not None:
+        _need(bias, "linear bias", torch.float32, (N,))
+    _need(x32, "residual stream", torch.float32, (M, N))
+    _need(norm_weight, "rmsnorm weight", torch.float32, (N,))
+    _need(hprime, "weighted sum", a.dtype, (M, N))
+    parts = linear_add_scaled_parts(a, weight, x32, hprime)
+    if parts == 0:
+        raise KernelError(f"linear_add_scaled: no kernel for {M} tokens, N={N}, K={Kd}")
+    _need(ssq, "partial sums of squares", torch.float32, (M, parts))
+    _check(library().li_linear_add_scaled(_p(a), _p(weight), _p(bias), _p(x32), _p(norm_weight), _p(hprime), _p(ssq), _i(_dt(a)),
+                                          _i(M), _i(N), _i(Kd), _stream(hprime)), "linear_add_scaled")
+
+
+def apply_row_scale(hprime: torch.Tensor, ssq: torch.Tensor, width: int, eps: float, out: torch.Tensor) -> None:
+    """``out[t] = hprime[t] / sqrt(sum_p ssq[t, p] / width + eps)`` (bfloat16)."""
+    M, H = hprime.shape
+    _need(hprime, "weighted sum", torch.bfloat16)
+    _need(out, "normalised output", torch.bfloat16, (M, H))
+    p_ssq, nparts, w, e = _row_scale_args((ssq, width, eps), M)
+    _check(library().li_apply_row_scale(_p(hprime), p_ssq, nparts, w, e, _p(out), _i(M), _i(H), _stream(out)), "apply_row_scale")
 
 
 def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
@@ -218,11 +279,11 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torc
 def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], qkv: torch.Tensor,
                    positions: torch.Tensor, denominators: torch.Tensor, rotary_dim: int, slot_mapping: torch.Tensor,
                    k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                   write: bool = True, fused: bool = True) -> None:
+                   write: bool = True, fused: bool = True, row_scale=None) -> None:
     """The fused q|k|v projection followed by :func:`rope_kv_write`: ``qkv = a weight^T + bias``, q rotated in
     place, k rotated and v stored into the caches.  Keys and values are only guaranteed to be in the caches
     afterwards, not in ``qkv``.  For a few bfloat16 tokens both steps run as one kernel (the rotation is the
-    product's epilogue); ``fused=False`` forces two kernels, for tests."""
+    product's epilogue); ``fused=False`` forces two kernels, for tests.  ``row_scale`` as in :func:`linear`."""
     T, Kd = a.shape
     N = (num_heads + 2 * num_kv_heads) * head_dim
     _need(a, "linear input")
@@ -241,7 +302,8 @@ def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
     _check(library().li_linear_rope_kv(
         _p(a), _p(weight), _p(bias), _p(qkv), _i(_dt(a)), _p(positions), _p(denominators), _i(rotary_dim), _p(slot_mapping),
         _p(k_cache), _p(v_cache), _i(T), _i(Kd), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages),
-        _i(1 if write else 0), _i(1 if fused else 0), _stream(qkv)), "linear_rope_kv")
+        _i(1 if write else 0), _i(1 if fused else 0),
+        *(_row_scale_args(row_scale, T) if row_scale is not None else (_p(None), _i(0), _i(0), _f(0.0))), _stream(qkv)), "linear_rope_kv")
 
 
 ATTENTION_IMPLEMENTATIONS = {"general": 0, "decode": 1, "prefill": 2}

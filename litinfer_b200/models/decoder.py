@@ -98,11 +98,14 @@ class DecoderModel:
         s = self.spec
         x32 = torch.empty((ctx.num_tokens, s.hidden_size), dtype=torch.float32, device=self.device)
         K.embedding(self.embedding, ctx.token_ids, x32)
-        pending = None
+        carry = None
+        last = len(s.schedule) - 1
         for i, e in enumerate(s.schedule):
-            x32, pending = self.blocks[e.block].forward(x32, ctx, caches[i], pending)
-        if pending is not None:
-            K.residual_add(x32, pending)
+            # a block is told the first norm of the block that runs next, so that it can apply it in its own tail
+            next_entry = self.blocks[s.schedule[i + 1].block].entry() if i < last else None
+            x32, carry = self.blocks[e.block].forward(x32, ctx, caches[i], carry, next_entry)
+        if carry is not None and carry.delta is not None:
+            K.residual_add(x32, carry.delta)
         R = ctx.num_logit_rows
         logits = torch.empty((R, s.vocab_size), dtype=torch.float32, device=self.device)
         if R:

@@ -19,11 +19,13 @@ import torch
 from .. import kernels as K
 from ..weights.loader import ParamSpec
 from .base import MIXERS, POSITIONS, Mixer, PagedKV
-from .linear import FusedLinear
+from .linear import FusedLinear, undefer
 
 
 @MIXERS.register("attention")
 class PagedAttention(Mixer):
+    takes_deferred = True            # the q|k|v product applies the factor
+
     def __init__(self, spec, prefix, dtype, device):
         super().__init__(spec, prefix, dtype, device)
         self.hidden = int(spec["hidden_size"])
@@ -57,15 +59,23 @@ class PagedAttention(Mixer):
         return PagedKV(self.num_kv_heads, self.head_dim, self.window)
 
     def forward(self, h, ctx, cache):
+        return self.out(self._attend(h, ctx, cache))
+
+    def forward_into(self, h, ctx, cache, tail):
+        return tail.apply_linear(self.out, self._attend(h, ctx, cache))
+
+    def _attend(self, h, ctx, cache):
+        """Everything before the output projection: [tokens, heads * head_dim]."""
         view = ctx.group(cache.group)
+        h, row_scale = undefer(h, self.qkv.weight)
         qkv = torch.empty((h.shape[0], self.qkv.out_features), dtype=self.dtype, device=h.device)
         # projection, position encoding of q and k, k and v into the cache: one call (and for few tokens one kernel)
         K.linear_rope_kv(
             h, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, self.position.denominators, self.position.rotary_dim,
-            view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, cache.writes)
+            view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, cache.writes, row_scale=row_scale)
         o = torch.empty((h.shape[0], self.q_dim), dtype=self.dtype, device=h.device)
         K.paged_attention(
             qkv, o, cache.k, cache.v, view.block_table, ctx.q_start, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,
             self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
             ctx.max_q_len, ctx.max_ctx_len)
-        return self.out(o)
+        return o

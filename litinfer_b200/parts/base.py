@@ -14,11 +14,24 @@ the package is all it takes to make a new kind available to configurations.
 Interfaces:
 
 * norm:          ``forward(x32) -> y``; ``add_forward(x32, delta) -> y`` (x32 += delta first);
-                 ``gather_forward(x32, rows) -> y[rows]``
+                 ``gather_forward(x32, rows) -> y[rows]``; ``after_linear(linear, a, x32) -> y``
+                 (x32 += linear(a) first; a norm may run it as one kernel with the product)
 * position:      owns what the mixer needs to encode positions (tables, constants)
-* mixer:         ``forward(h, ctx, cache) -> y``; ``cache_requirement()``
-* feed-forward:  ``forward(h, ctx) -> y``
-* block:         ``forward(x32, ctx, cache, pending) -> (x32, pending)``
+* mixer:         ``forward(h, ctx, cache) -> y``; ``cache_requirement()``;
+                 optionally ``forward_into(h, ctx, cache, tail) -> h'``
+* feed-forward:  ``forward(h, ctx) -> y``; optionally ``forward_into(h, ctx, tail) -> h'``
+* block:         ``forward(x32, ctx, cache, carry, next_norm) -> (x32, carry)``; ``first_norm``
+
+A :class:`Tail` says what follows a part's output: it is added to the residual stream and the
+sum is normalised for the next part.  ``forward_into`` does all of that and returns the
+normalised sum; the default calls ``forward`` and then the norm's ``add_forward``, and a part
+whose last step is a product may hand it to the norm's ``after_linear`` instead.  If the part
+that comes next says ``takes_deferred``, the norm may return a :class:`Deferred` activation:
+the weighted sum with the reciprocal root still to be applied, which that part's first product
+applies to its own result (``FusedLinear`` does), so that the norm costs no kernel.  A
+:class:`Carry` is what a block hands to the next one: its last output not yet added to the
+stream (``delta``), or, when it was told the next block's entry, the stream already
+updated and normalised by that block's first norm (``normed``).
 
 ``x32`` is the residual stream, always float32 ``[tokens, hidden]``; ``h`` and
 ``y`` are activations in the run dtype.  ``ctx`` is the step's
@@ -92,7 +105,63 @@ class Part:
             p.bind_all(tensors)
 
 
+@dataclass
+class Deferred:
+    """A normalised activation not yet multiplied out: ``h[t] / sqrt(sum_p ssq[t, p] / width + eps)``.
+
+    ``h`` already holds the norm's weights.  A product applies the factor to its rows
+    (``kernels.linear(..., row_scale=d.row_scale)``); :meth:`materialize` gives the activation itself."""
+
+    h: torch.Tensor
+    ssq: torch.Tensor
+    width: int
+    eps: float
+
+    @property
+    def row_scale(self):
+        return (self.ssq, self.width, self.eps)
+
+    @property
+    def shape(self):
+        return self.h.shape
+
+    def materialize(self) -> torch.Tensor:
+        from .. import kernels as K
+
+        out = torch.empty_like(self.h)
+        K.apply_row_scale(self.h, self.ssq, self.width, self.eps, out)
+        return out
+
+
+@dataclass
+class Tail:
+    """What follows a part's output y: ``x32 += y``, then ``norm`` of the sum feeds the next part, which may
+    (``defer``) be given a :class:`Deferred` activation."""
+
+    x32: torch.Tensor
+    norm: "Norm"
+    defer: bool = False
+
+    def apply(self, y: torch.Tensor) -> torch.Tensor:
+        return self.norm.add_forward(self.x32, y)
+
+    def apply_linear(self, linear, a: torch.Tensor):
+        """The same for y = linear(a), which the norm may fuse with the product."""
+        return self.norm.after_linear(linear, a, self.x32, defer=self.defer)
+
+
+@dataclass
+class Carry:
+    """From one block to the next: ``delta`` is still to be added to the residual stream;
+    ``normed`` is the next block's first norm of the stream, which already holds everything."""
+
+    delta: Optional[torch.Tensor] = None
+    normed: Optional[torch.Tensor] = None
+
+
 class Mixer(Part):
+    takes_deferred = False           # whether forward accepts a Deferred activation as h
+
     def cache_requirement(self):
         """PagedKV, FixedState or None."""
         return None
@@ -100,10 +169,18 @@ class Mixer(Part):
     def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
         raise NotImplementedError
 
+    def forward_into(self, h: torch.Tensor, ctx, cache, tail: Tail) -> torch.Tensor:
+        return tail.apply(self.forward(h, ctx, cache))
+
 
 class FeedForward(Part):
+    takes_deferred = False
+
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
+
+    def forward_into(self, h: torch.Tensor, ctx, tail: Tail) -> torch.Tensor:
+        return tail.apply(self.forward(h, ctx))
 
 
 class Norm(Part):
@@ -116,13 +193,23 @@ class Norm(Part):
     def gather_forward(self, x32: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
+    def after_linear(self, linear, a: torch.Tensor, x32: torch.Tensor, defer: bool = False):
+        """``x32 += linear(a)``; the norm of the sum, which may be :class:`Deferred` if ``defer``.
+        ``linear`` is a :class:`~litinfer_b200.parts.linear.FusedLinear`."""
+        return self.add_forward(x32, linear(a))
+
 
 class Position(Part):
     pass
 
 
 class Block(Part):
-    def forward(self, x32, ctx, cache, pending):
+    def entry(self) -> Optional[Tail]:
+        """The norm this block applies to the residual stream first, and whether its consumer takes a deferred
+        activation, as a Tail without a stream; None if the block before may not apply it in this block's place."""
+        return None
+
+    def forward(self, x32, ctx, cache, carry: Optional[Carry], next_entry: Optional[Tail] = None):
         raise NotImplementedError
 
 

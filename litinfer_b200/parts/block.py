@@ -1,17 +1,19 @@
 """Arrangement of a layer's parts.  ``prenorm``: x += Mixer(norm(x));
 x += FeedForward(norm(x)) (src/llaisys/models/qwen2.cpp:272-316).
 
-The residual stream x is float32.  A block hands the output of its
-feed-forward back as ``pending`` instead of adding it, so that the next block
-(or the model's tail) adds it inside its first norm kernel: one pass over x
-for add and norm together.
+The residual stream x is float32.  A block does not add the output of its
+feed-forward itself: told the next block's entry (its first norm), it lets the feed-forward
+add, and normalise for the next block, in the tail of its last product
+(``Carry.normed``); otherwise it hands the output on (``Carry.delta``) and the next
+block, or the model's tail, adds it inside its first norm kernel.  Either way
+add and norm are one pass over x.
 """
 
 from __future__ import annotations
 
 from typing import List
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Carry, Tail
 
 
 @BLOCKS.register("prenorm")
@@ -31,8 +33,17 @@ class PreNormBlock(Block):
     def parts(self) -> List:
         return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
 
-    def forward(self, x32, ctx, cache, pending):
-        h = self.mixer_norm.forward(x32) if pending is None else self.mixer_norm.add_forward(x32, pending)
-        a = self.mixer.forward(h, ctx, cache)
-        h = self.feed_forward_norm.add_forward(x32, a)
-        return x32, self.feed_forward.forward(h, ctx)
+    def entry(self):
+        return Tail(None, self.mixer_norm, self.mixer.takes_deferred)
+
+    def forward(self, x32, ctx, cache, carry, next_entry=None):
+        if carry is None:
+            h = self.mixer_norm.forward(x32)
+        elif carry.normed is not None:
+            h = carry.normed                               # the block before applied this block's first norm
+        else:
+            h = self.mixer_norm.add_forward(x32, carry.delta)
+        h = self.mixer.forward_into(h, ctx, cache, Tail(x32, self.feed_forward_norm, self.feed_forward.takes_deferred))
+        if next_entry is None:
+            return x32, Carry(delta=self.feed_forward.forward(h, ctx))
+        return x32, Carry(normed=self.feed_forward.forward_into(h, ctx, Tail(x32, next_entry.norm, next_entry.defer)))

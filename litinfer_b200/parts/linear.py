@@ -12,6 +12,17 @@ import torch
 
 from .. import kernels as K
 from ..weights.loader import ParamSpec
+from .base import Deferred
+
+
+def undefer(x, weight: torch.Tensor):
+    """(input tensor, row_scale) for a product over ``x``: a deferred activation keeps its factor for the product if
+    the product's kernel takes one, else it is multiplied out first."""
+    if not isinstance(x, Deferred):
+        return x, None
+    if K.linear_scaled_accepts(x.h, weight, x.h):
+        return x.h, x.row_scale
+    return x.materialize(), None
 
 
 class FusedLinear:
@@ -46,9 +57,11 @@ class FusedLinear:
             bs = [tensors.pop(f"{self.prefix}{n}.bias") for n in self.names]
             self.bias = bs[0] if len(bs) == 1 else torch.cat(bs, dim=0).contiguous()
 
-    def __call__(self, x: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def __call__(self, x, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``x`` may be a :class:`~litinfer_b200.parts.base.Deferred` activation: its factor per token goes on the product."""
+        x, row_scale = undefer(x, self.weight)
         out = torch.empty((x.shape[0], self.out_features), dtype=out_dtype or self.dtype, device=x.device)
-        K.linear(x, self.weight, self.bias, out)
+        K.linear(x, self.weight, self.bias, out, row_scale=row_scale)
         return out
 
 
@@ -72,9 +85,11 @@ class GateUpLinear(FusedLinear):
 
     def activation(self, x: torch.Tensor) -> torch.Tensor:
         """up(x) * silu(gate(x)), [tokens, intermediate]."""
-        act = torch.empty((x.shape[0], self.intermediate), dtype=self.dtype, device=x.device)
         if self.fused_activation:
-            K.linear(x, self.weight, None, act, epilogue="swiglu")
+            x, row_scale = undefer(x, self.weight)
+            act = torch.empty((x.shape[0], self.intermediate), dtype=self.dtype, device=x.device)
+            K.linear(x, self.weight, None, act, epilogue="swiglu", row_scale=row_scale)
         else:
+            act = torch.empty((x.shape[0], self.intermediate), dtype=self.dtype, device=x.device)
             K.swiglu(self(x), act)
         return act

@@ -17,6 +17,8 @@ from .linear import FusedLinear, GateUpLinear
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
+    takes_deferred = True            # the gate|up product applies the factor
+
     def __init__(self, spec, prefix, dtype, device):
         super().__init__(spec, prefix, dtype, device)
         self.hidden = int(spec["hidden_size"])
@@ -35,3 +37,6 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, ctx):
         return self.down(self.gate_up.activation(h))
+
+    def forward_into(self, h, ctx, tail):
+        return tail.apply_linear(self.down, self.gate_up.activation(h))

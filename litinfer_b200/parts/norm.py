@@ -10,7 +10,12 @@ import torch
 
 from .. import kernels as K
 from ..weights.loader import ParamSpec
-from .base import NORMS, Norm
+from .base import NORMS, Deferred, Norm
+
+
+# Up to this many tokens a step the norm between two products rides on them (measured: with more tokens the products'
+# registers are too short for the extra work, and a norm kernel of its own is cheaper).
+DEFER_MAX_TOKENS = 16
 
 
 @NORMS.register("rmsnorm")
@@ -36,6 +41,18 @@ class RMSNorm(Norm):
         out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
         K.add_rmsnorm(x32, delta, self.weight, self.eps, out)
         return out
+
+    def after_linear(self, linear, a, x32, defer=False):
+        # Few bfloat16 tokens and a consumer that applies the reciprocal root itself: the product adds to the stream and
+        # leaves weight * x with the sums of squares, all in its epilogue; this norm has no kernel of its own.
+        if defer and self.dtype == torch.bfloat16 and not isinstance(a, Deferred) and 0 < a.shape[0] <= DEFER_MAX_TOKENS:
+            h = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
+            parts = K.linear_add_scaled_parts(a, linear.weight, x32, h)
+            if parts:
+                ssq = torch.empty((x32.shape[0], parts), dtype=torch.float32, device=x32.device)
+                K.linear_add_scaled(a, linear.weight, linear.bias, x32, self.weight, h, ssq)
+                return Deferred(h, ssq, self.size, self.eps)
+        return self.add_forward(x32, linear(a))
 
     def gather_forward(self, x32, rows):
         out = torch.empty((rows.shape[0], x32.shape[1]), dtype=self.dtype, device=x32.device)

@@ -47,8 +47,10 @@ def residual_add(x32, delta):
     x32.add_(delta.float())
 
 
-def linear(a, weight, bias, out, epilogue=None):
+def linear(a, weight, bias, out, epilogue=None, row_scale=None):
     y = a.float() @ weight.float().t()
+    if row_scale is not None:
+        y = y * _factor(row_scale)
     if bias is not None:
         y = y + bias
     if epilogue == "swiglu":
@@ -58,6 +60,34 @@ def linear(a, weight, bias, out, epilogue=None):
         g, u = y[:, :, 0, :], y[:, :, 1, :]
         y = (u * (g / (1.0 + torch.exp(-g)))).reshape(M, N // 2)
     _store(out, y)
+
+
+def _factor(row_scale):
+    ssq, width, eps = row_scale
+    return (1.0 / torch.sqrt(ssq.sum(1) / width + eps)).unsqueeze(1)
+
+
+def linear_scaled_accepts(a, weight, out):
+    return True
+
+
+def linear_add_scaled_parts(a, weight, x32, hprime):
+    return 3
+
+
+def linear_add_scaled(a, weight, bias, x32, norm_weight, hprime, ssq):
+    y = a.float() @ weight.float().t()
+    if bias is not None:
+        y = y + bias
+    x32.add_(y)
+    _store(hprime, norm_weight * x32)
+    # any split of the columns into parts gives the same sums; here: everything in part 0
+    ssq.zero_()
+    ssq[:, 0] = (x32 * x32).sum(-1)
+
+
+def apply_row_scale(hprime, ssq, width, eps, out):
+    _store(out, hprime.float() * _factor((ssq, width, eps)))
 
 
 def interleave_gate_up(gate, up):
@@ -94,8 +124,8 @@ def rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cach
 
 
 def linear_rope_kv(a, weight, bias, qkv, positions, denominators, rotary_dim, slot_mapping, k_cache, v_cache,
-                   num_heads, num_kv_heads, head_dim, write=True, fused=True):
-    linear(a, weight, bias, qkv)
+                   num_heads, num_kv_heads, head_dim, write=True, fused=True, row_scale=None):
+    linear(a, weight, bias, qkv, row_scale=row_scale)
     rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write)
 
 
@@ -203,5 +233,5 @@ def sample(logits, params, out):
     out.copy_(torch.tensor(res, dtype=torch.int32))
 
 
-ALL = ["linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
+ALL = ["linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]

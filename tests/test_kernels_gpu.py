@@ -307,6 +307,13 @@ def test_linear_rope_kv_fused(dtype, cfg):
     q3, k3, v3 = run(R.linear_rope_kv)
     for got, ref, what in ((q1, q3, "q"), (k1, k3, "k cache"), (v1, v3, "v cache"), (q2, q3, "q unfused"), (k2, k3, "k unfused")):
         close(got, ref, dtype, f"linear_rope_kv {what} {cfg}", f32_tol=5e-4)
+    # with a factor per token on the product
+    if dtype == torch.bfloat16 and T <= 64:
+        rs = ((rnd(T, 7, seed=55).abs() * 30.0 + 1.0).contiguous(), H, 1e-5)
+        q4, k4, v4 = run(K().linear_rope_kv, row_scale=rs)
+        q5, k5, v5 = run(R.linear_rope_kv, row_scale=rs)
+        for got, ref, what in ((q4, q5, "q"), (k4, k5, "k cache"), (v4, v5, "v cache")):
+            close(got, ref, dtype, f"linear_rope_kv scaled {what} {cfg}")
     # without writing: caches untouched
     kc = torch.zeros(pages, nkv, page, dh, dtype=dtype, device=dev())
     vc = torch.zeros(pages, nkv, dh, page, dtype=dtype, device=dev())
@@ -314,6 +321,89 @@ def test_linear_rope_kv_fused(dtype, cfg):
     K().linear_rope_kv(a, w, b, qkv, positions, denom, dh, slots, kc, vc, nh, nkv, dh, False)
     assert not kc.any() and not vc.any()
     close(qkv[:, :nh * dh], q3, dtype, "q without cache write", f32_tol=5e-4)
+
+
+ADD_SCALED = [(1, 1536, 1536, False), (8, 1536, 1536, True), (8, 1536, 8960, False), (16, 1536, 8960, False), (3, 136, 200, True),
+              (5, 4100, 264, False), (13, 12288, 1536, False), (33, 1536, 1536, True), (64, 1536, 8960, False), (40, 264, 4608, True),
+              (8, 1532, 4096, True)]
+
+
+@pytest.mark.parametrize("cfg", ADD_SCALED)
+def test_linear_add_scaled(cfg):
+    """The product into the residual stream with the next norm half done: x32 += a w^T (+ b), h' = bfloat16(w_norm x32)
+    and partial sums of x32^2, through whichever of the two weight-streaming kernels the sizes choose; then the factor
+    per token, applied to h' itself.  Against product, add and norm as separate references; twice in a row, since the
+    split of k leaves counters behind."""
+    M, N, Kd, with_bias = cfg
+    dtype = torch.bfloat16
+    a = rnd(M, Kd, dtype=dtype, seed=61)
+    w = rnd(N, Kd, dtype=dtype, seed=62, scale=0.05)
+    b = rnd(N, seed=63, scale=0.5) if with_bias else None
+    x0 = rnd(M, N, seed=64)
+    nw = (1.0 + 0.1 * rnd(N, seed=65)).contiguous()
+    eps = 3e-6
+    x_ref = x0.clone()
+    o_ref = torch.zeros(M, N, dtype=dtype, device=dev())
+    delta = torch.zeros(M, N, dtype=torch.float32, device=dev())
+    R.linear(a, w, b, delta)
+    R.add_rmsnorm(x_ref, delta, nw, eps, o_ref)
+    for rep in range(2):
+        x = x0.clone()
+        h = torch.zeros(M, N, dtype=dtype, device=dev())
+        parts = K().linear_add_scaled_parts(a, w, x, h)
+        assert parts > 0, f"no kernel for {cfg}"
+        ssq = torch.full((M, parts), float("nan"), dtype=torch.float32, device=dev())
+        K().linear_add_scaled(a, w, b, x, nw, h, ssq)
+        close(x, x_ref, dtype, f"stream {cfg} run {rep}")
+        close(ssq.sum(1), (x_ref * x_ref).sum(-1), torch.float32, f"sums of squares {cfg}", f32_tol=1e-4)
+        out = torch.zeros(M, N, dtype=dtype, device=dev())
+        K().apply_row_scale(h, ssq, N, eps, out)
+        close(out, o_ref, dtype, f"normalised {cfg} run {rep}")
+    # a token's results do not depend on the others in the batch
+    if M >= 2:
+        x1 = x0[:1].clone()
+        h1 = torch.zeros(1, N, dtype=dtype, device=dev())
+        ssq1 = torch.zeros(1, K().linear_add_scaled_parts(a[:1].contiguous(), w, x1, h1), dtype=torch.float32, device=dev())
+        K().linear_add_scaled(a[:1].contiguous(), w, b, x1, nw, h1, ssq1)
+        if M <= 32:                       # the same kernel for 1 and for M tokens
+            assert torch.equal(x1[0], x[0]) and torch.equal(h1[0], h[0]) and torch.equal(ssq1[0], ssq[0])
+
+
+@pytest.mark.parametrize("epilogue", [None, "swiglu"])
+@pytest.mark.parametrize("cfg", [(1, 2048, 1536, 12, True), (8, 2048, 1536, 96, True), (8, 17920, 1536, 12, False), (16, 17920, 1536, 96, False),
+                                 (5, 272, 200, 1, True), (40, 1536, 8960, 140, False), (64, 4608, 264, 33, True), (9, 640, 4096, 200, False)])
+def test_linear_row_scale(cfg, epilogue):
+    """A factor per token, from partial sums of squares, on the rows of the product before bias and epilogue."""
+    M, N, Kd, parts, with_bias = cfg
+    dtype = torch.bfloat16
+    a = rnd(M, Kd, dtype=dtype, seed=71)
+    w = rnd(N, Kd, dtype=dtype, seed=72, scale=0.05)
+    b = rnd(N, seed=73, scale=0.5) if (with_bias and epilogue is None) else None
+    ssq = (rnd(M, parts, seed=74).abs() * 50.0 + 1.0).contiguous()
+    width, eps = 777, 2e-5
+    if epilogue == "swiglu":
+        w = K().interleave_gate_up(w[:N // 2].contiguous(), w[N // 2:].contiguous())
+    n_out = N // 2 if epilogue else N
+    out = torch.zeros(M, n_out, dtype=dtype, device=dev())
+    ref = torch.zeros(M, n_out, dtype=dtype, device=dev())
+    assert K().linear_scaled_accepts(a, w, out)
+    K().linear(a, w, b, out, epilogue=epilogue, row_scale=(ssq, width, eps))
+    R.linear(a, w, b, ref, epilogue=epilogue, row_scale=(ssq, width, eps))
+    close(out, ref, dtype, f"scaled product {cfg} {epilogue}")
+    if M >= 2 and M <= 8:
+        one = torch.zeros(1, n_out, dtype=dtype, device=dev())
+        K().linear(a[:1].contiguous(), w, b, one, epilogue=epilogue, row_scale=(ssq[:1].contiguous(), width, eps))
+        assert torch.equal(one[0], out[0])
+
+
+def test_linear_row_scale_refused():
+    """Products that no weight-streaming kernel takes cannot apply the factor: said, not ignored."""
+    a = rnd(100, 64, dtype=torch.bfloat16, seed=1)
+    w = rnd(32, 64, dtype=torch.bfloat16, seed=2)
+    out = torch.zeros(100, 32, dtype=torch.bfloat16, device=dev())
+    assert not K().linear_scaled_accepts(a, w, out)
+    with pytest.raises(Exception, match="at most 64"):
+        K().linear(a, w, None, out, row_scale=(torch.ones(100, 1, device=dev()), 64, 1e-6))
 
 
 # --------------------------------------------------------------------------

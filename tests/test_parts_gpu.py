@@ -158,7 +158,8 @@ def test_block_and_head(dtype, model_dirs):
     ctx = step_context(manager, [(rc, T)], cfg["vocab_size"])
     x = torch.randn(T, cfg["hidden_size"])
     xd = x.to(DEV).clone()
-    xd, pending = model.blocks[1].forward(xd, ctx, manager.entries[1], None)
+    xd, carry = model.blocks[1].forward(xd, ctx, manager.entries[1], None)
+    pending = carry.delta
     ref, _ = P.plain_block(x, w, cfg, 1, torch.arange(T), None)
     check(xd + pending.float(), ref, dtype, "block")
     # the head on three wanted rows of a made-up residual stream
