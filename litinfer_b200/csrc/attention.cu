@@ -3,7 +3,9 @@
 //
 //   float32                          -> general kernel (attention_generic.cu)
 //   bfloat16, every item one token   -> split-context decode kernel (attention_decode.cu)
-//   bfloat16, portions of prompts    -> tiled tensor-core kernel (attention_prefill.cu);
+//   bfloat16, long portions          -> tcgen05 kernel (attention_tcgen05.cu): head_dim 64 or 128, a portion of
+//                                       at least 64 tokens in the batch
+//   bfloat16, other portions         -> tiled mma.sync kernel (attention_prefill.cu);
 //                                       single tokens in the same batch are portions of length one
 //   sizes those refuse               -> general kernel
 #include "common.cuh"
@@ -19,6 +21,11 @@ bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size,
                          int num_pages, float scale, int window, int max_q_len, cudaStream_t stream);
+
+bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const void* vcache, int nh, int nkv, int dh, int page_size);
+int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
+                         const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
+                         float scale, int window, int max_q_len, cudaStream_t stream);
 
 static int validate(int T, int S, int nh, int nkv, int dh, int page_size, int window) {
     LI_REQUIRE(T >= 0 && S > 0, "attention: bad batch T=%d S=%d", T, S);
@@ -40,6 +47,9 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
         if (max_q_len == 1 && T == S && li_attention_decode_accepts(nh, nkv, dh, page_size))
             return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, S, nh, nkv, dh, page_size,
                                        num_pages, scale, window, max_ctx_len, stream);
+        if (max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size))
+            return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
+                                        num_pages, scale, window, max_q_len, stream);
         if (li_attention_prefill_accepts(nh, nkv, dh, page_size))
             return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh,
                                         page_size, num_pages, scale, window, max_q_len, stream);
@@ -48,7 +58,7 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
                                 page_size, num_pages, scale, window, stream);
 }
 
-// Force one implementation, for tests of each kernel alone: 0 general, 1 decode, 2 prefill.
+// Force one implementation, for tests of each kernel alone: 0 general, 1 decode, 2 prefill (mma.sync), 3 prefill (tcgen05).
 LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, const void* kcache, const void* vcache, int dtype,
                                       const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens,
                                       const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
@@ -69,6 +79,11 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
     if (which == 2) {
         LI_REQUIRE(li_attention_prefill_accepts(nh, nkv, dh, page_size), "attention: the prefill kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
         return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
+                                    num_pages, scale, window, max_q_len, stream);
+    }
+    if (which == 3) {
+        LI_REQUIRE(li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size), "attention: the tcgen05 kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
+        return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                     num_pages, scale, window, max_q_len, stream);
     }
     return li_fail("attention: unknown implementation %d", which);

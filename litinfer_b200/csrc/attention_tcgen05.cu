@@ -1,0 +1,323 @@
+// Prefill attention on the fifth-generation tensor cores: long portions of prompts over the paged cache,
+// causal, grouped-query, bfloat16.
+//
+// Grid (tile of 128 tokens, query head, sequence).  A CTA of six warps works on 128 consecutive tokens of a
+// portion for one head, against tiles of 128 keys:
+//   warp 0     one thread brings Q (once) and, two tiles ahead, K and V of each tile into shared memory with
+//              TMA, page by page through the block table: a page of keys is 16 rows of the K operand
+//              ([keys, head_dim], 128-byte swizzle), a page of values (cached transposed, [head_dim, 16 slots])
+//              is the V operand of one k-step ([head_dim, 16 keys], 32-byte swizzle);
+//   warp 1     one thread issues the products with tcgen05.mma, accumulators in tensor memory:
+//              S = Q K^T (128 x 128) and, once the probabilities are in shared memory, PV = P V (128 x head_dim);
+//   warps 2-5  one thread per token: reads its row of S from tensor memory, applies scale and mask, keeps the
+//              running maximum and sum of the online softmax in float (src/ops/paged_attention/op.cpp:194-234),
+//              writes P as bfloat16 in the operand layout, then adds PV to its output row in registers,
+//              O = O alpha + PV.
+// Keys and values of the portion itself are already in the cache (the rope kernel ran before).  Token i of a
+// portion of n tokens in a context of c sits at position p = c - n + i and sees keys max(0, p - window + 1) .. p.
+// Keys of a tile that lie past the context are read from whatever page the table names (page 0 if none) and get
+// probability zero; the cache holds finite numbers only.
+//
+// Every wait on a barrier is bounded; a wait that runs out raises the status word of the tcgen05 kernels and the
+// CTA leaves, freeing its tensor memory.
+//
+// Requires head_dim 64 or 128 and page_size a multiple of 16.
+#include "tcgen05.cuh"
+
+namespace tc {
+int make_map_ex(CUtensorMap* map, const void* base, unsigned long long rows, unsigned long long cols, unsigned box_cols, unsigned box_rows,
+                int swizzle_bytes);
+}
+
+namespace {
+
+using namespace tc;
+
+constexpr int kRows = 128;          // tokens per CTA
+constexpr int kKeys = 128;          // keys per tile
+constexpr int kThreads = 192;
+constexpr int kBuffers = 2;
+
+template <int DH>
+struct __align__(1024) Smem {
+    unsigned char q[kRows * DH * 2];                 // DH / 64 panels of [128 rows][64] (128-byte swizzle)
+    unsigned char k[kBuffers][kKeys * DH * 2];       // the same for keys
+    unsigned char v[kBuffers][kKeys * DH * 2];       // 8 pages of [DH rows][16 keys] (32-byte swizzle)
+    unsigned char p[kRows * kKeys * 2];              // 2 panels of [128 rows][64 keys] (128-byte swizzle)
+    unsigned long long q_full, s_full, p_full, pv_full;
+    unsigned long long kv_full[kBuffers], kv_empty[kBuffers];
+    unsigned tmem_base;
+};
+
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory descriptor of a K-major tile of rows x 16 bfloat16 written by TMA with the 32-byte swizzle: 8-row
+// groups are 256 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc_sw32(const void* tile) {
+    const unsigned addr = smem_u32(tile);
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)(256 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)6 << 61;
+    return d;
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int DH>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
+                            int max_blocks, const int* __restrict__ q_start, const int* __restrict__ ctx_lens, int nh, int nkv,
+                            int page_size, int num_pages, float scale, int window, int* __restrict__ error_flag) {
+    extern __shared__ unsigned char smem_raw[];
+    Smem<DH>& sm = *reinterpret_cast<Smem<DH>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr int kPanels = DH / 64;
+    constexpr unsigned kTmemCols = 256;              // S: 128 columns, PV: up to 128
+    const int s = blockIdx.z, h = blockIdx.y;
+    const int tok0 = q_start[s], n = q_start[s + 1] - tok0;
+    const int cta_i0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kRows;       // the last tiles see the most keys: first
+    if (cta_i0 >= n) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ctx = ctx_lens[s];
+    const int kvh = h / (nh / nkv);
+    const int cta_rows = min(kRows, n - cta_i0);
+    const int p_first = ctx - n + cta_i0, p_last = p_first + cta_rows - 1;
+    const int key_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
+    const int kt_first = key_lo / kKeys, kt_last = p_last / kKeys;
+    const int ntiles = kt_last - kt_first + 1;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.p_full, 128);
+        mbar_init(&sm.pv_full, 1);
+        for (int b = 0; b < kBuffers; ++b) {
+            mbar_init(&sm.kv_full[b], 1);
+            mbar_init(&sm.kv_empty[b], 1);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_s = sm.tmem_base, tmem_pv = sm.tmem_base + 128;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(&sm.q_full, kRows * DH * 2);
+#pragma unroll
+            for (int pn = 0; pn < kPanels; ++pn) tma_load_2d(sm.q + pn * (kRows * 128), &map_q, h * DH + pn * 64, tok0 + cta_i0, &sm.q_full);
+            const int* bt = block_table + (size_t)s * max_blocks;
+            bool ok = true;
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int b = j % kBuffers;
+                ok = mbar_wait(&sm.kv_empty[b], ((j / kBuffers) & 1) ^ 1);
+                if (!ok) break;
+                mbar_expect_tx(&sm.kv_full[b], 2 * kKeys * DH * 2);
+                const int key0 = (kt_first + j) * kKeys;
+#pragma unroll 1
+                for (int pg = 0; pg < kKeys / 16; ++pg) {
+                    const int key = key0 + pg * 16;
+                    int idx = key / page_size;
+                    int page = (key < ctx && idx < max_blocks) ? bt[idx] : 0;
+                    if (page < 0 || page >= num_pages) page = 0;
+                    const int off = key % page_size;
+#pragma unroll
+                    for (int pn = 0; pn < kPanels; ++pn)
+                        tma_load_2d(sm.k[b] + pn * (kKeys * 128) + pg * 2048, &map_k, pn * 64, (page * nkv + kvh) * page_size + off, &sm.kv_full[b]);
+                    tma_load_2d(sm.v[b] + pg * (DH * 32), &map_v, off, (page * nkv + kvh) * DH, &sm.kv_full[b]);
+                }
+            }
+            if (!ok) atomicExch(error_flag, 11);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr unsigned idesc_s = umma_idesc(kRows, kKeys), idesc_pv = umma_idesc(kRows, DH);
+            bool ok = mbar_wait(&sm.q_full, 0);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int b = j % kBuffers;
+                ok = mbar_wait(&sm.kv_full[b], (j / kBuffers) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int k = 0; k < DH / 16; ++k) {
+                    const unsigned long long da = umma_desc(sm.q + (k >> 2) * (kRows * 128)) + (unsigned long long)((k & 3) * 2);
+                    const unsigned long long db = umma_desc(sm.k[b] + (k >> 2) * (kKeys * 128)) + (unsigned long long)((k & 3) * 2);
+                    umma_bf16(tmem_s, da, db, idesc_s, k ? 1u : 0u);
+                }
+                umma_commit(&sm.s_full);
+                ok = mbar_wait(&sm.p_full, j & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int k = 0; k < kKeys / 16; ++k) {
+                    const unsigned long long da = umma_desc(sm.p + (k >> 2) * (kRows * 128)) + (unsigned long long)((k & 3) * 2);
+                    const unsigned long long db = umma_desc_sw32(sm.v[b] + k * (DH * 32));
+                    umma_bf16(tmem_pv, da, db, idesc_pv, k ? 1u : 0u);
+                }
+                umma_commit(&sm.pv_full);
+                umma_commit(&sm.kv_empty[b]);
+            }
+            if (!ok) atomicExch(error_flag, 12);
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                       // this thread's token within the tile = its lane of tensor memory
+        const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+        const bool valid = cta_i0 + r < n;
+        const int p = valid ? p_first + r : -1;                  // its position; no key is visible to an unused row
+        const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+        const float scale_log2 = scale * 1.4426950408889634f;
+        float o[DH];
+#pragma unroll
+        for (int d = 0; d < DH; ++d) o[d] = 0.0f;
+        float m = -INFINITY, l = 0.0f;
+        unsigned char* prow = sm.p + (r >> 3) * 1024 + (r & 7) * 128;
+        bool ok = true;
+        for (int j = 0; j < ntiles; ++j) {
+            const int key0 = (kt_first + j) * kKeys;
+            ok = mbar_wait(&sm.s_full, j & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // first pass: the row's maximum over this tile
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c = 0; c < kKeys / 32; ++c) {
+                float v[32];
+                tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int key = key0 + c * 32 + i;
+                    if (key >= lo && key <= p) mx = fmaxf(mx, v[i]);
+                }
+            }
+            const float m_new = fmaxf(m, mx * scale_log2);           // scale > 0: the order is the same
+            const float ms = (m_new == -INFINITY) ? 0.0f : m_new;
+            const float alpha = fast_exp2(m - ms);
+            // second pass: probabilities, rounded to bfloat16, into the operand tile
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < kKeys / 32; ++c) {
+                float v[32];
+                tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
+                unsigned pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const int key = key0 + c * 32 + i;
+                    const float e0 = (key >= lo && key <= p) ? fast_exp2(v[i] * scale_log2 - ms) : 0.0f;
+                    const float e1 = (key + 1 >= lo && key + 1 <= p) ? fast_exp2(v[i + 1] * scale_log2 - ms) : 0.0f;
+                    sum += e0 + e1;
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(e0, e1);
+                    pk[i >> 1] = *reinterpret_cast<unsigned*>(&t2);
+                }
+                // 32 keys = four 16-byte chunks of panel c / 2, chunks 4 (c & 1) .. + 3 of the row, swizzled by the row
+                unsigned char* panel = prow + (c >> 1) * (kRows * 128);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int ch = ((c & 1) * 4 + q) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(panel + ch * 16) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+                }
+            }
+            l = l * alpha + sum;
+            m = m_new;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(&sm.p_full);
+            ok = mbar_wait(&sm.pv_full, j & 1);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < DH / 32; ++c) {
+                float v[32];
+                tmem_ld_32x32(tmem_pv + lane_addr + c * 32, v);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + v[i];
+            }
+        }
+        if (!ok) {
+            if (lane == 0) atomicExch(error_flag, 13);
+        } else if (valid) {
+            const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+            bf16* dst = out + ((size_t)(tok0 + cta_i0 + r) * nh + h) * DH;
+#pragma unroll
+            for (int d = 0; d < DH; d += 8) {
+                unsigned pk[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(o[d + 2 * i] * inv, o[d + 2 * i + 1] * inv);
+                    pk[i] = *reinterpret_cast<unsigned*>(&t2);
+                }
+                *reinterpret_cast<uint4*>(dst + d) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
+    }
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(sm.tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+template <int DH>
+int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks, const int* q_start,
+           const int* ctx_lens, int T, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window, int max_q_len,
+           cudaStream_t stream) {
+    EncodeTiledFn encode = nullptr;
+    int *err_host = nullptr, *err_dev = nullptr;
+    if (int rc = setup(&encode, &err_host, &err_dev)) return rc;
+    if (*err_host != 0)
+        return li_fail("attention (tcgen05): an earlier launch gave up waiting on a barrier (status %d); the results since then are invalid", *err_host);
+    CUtensorMap map_q, map_k, map_v;
+    const unsigned long long row_elems = (unsigned long long)(nh + 2 * nkv) * DH;
+    if (int rc = make_map_ex(&map_q, qkv, (unsigned long long)T, row_elems, 64, kRows, 128)) return rc;
+    if (int rc = make_map_ex(&map_k, kcache, (unsigned long long)num_pages * nkv * page_size, DH, 64, 16, 128)) return rc;
+    if (int rc = make_map_ex(&map_v, vcache, (unsigned long long)num_pages * nkv * DH, (unsigned long long)page_size, 16, DH, 32)) return rc;
+    const size_t smem = sizeof(Smem<DH>) + 1024;
+    static bool raised = false;
+    if (!raised) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return li_fail("attention (tcgen05): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
+        raised = true;
+    }
+    LI_REQUIRE(S <= 65535 && nh <= 65535, "attention (tcgen05): batch %d or heads %d too large for one launch", S, nh);
+    dim3 grid(ceil_div(max_q_len, kRows), nh, S);
+    li_launch_pdl(prefill_attention_tc_kernel<DH>, grid, dim3(kThreads), smem, stream, map_q, map_k, map_v, (bf16*)out, block_table, max_blocks,
+                  q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, err_dev);
+    return li_check_launch("attention (tcgen05)");
+}
+
+}  // namespace
+
+bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const void* vcache, int nh, int nkv, int dh, int page_size) {
+    const bool aligned = ((uintptr_t)qkv % 16 == 0) && ((uintptr_t)kcache % 16 == 0) && ((uintptr_t)vcache % 16 == 0);
+    return aligned && (dh == 64 || dh == 128) && nh % nkv == 0 && page_size % 16 == 0 && page_size <= 256;
+}
+
+int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
+                         const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
+                         float scale, int window, int max_q_len, cudaStream_t stream) {
+    LI_REQUIRE(li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size),
+               "attention (tcgen05): refuses heads=%d/%d head_dim=%d page=%d (head_dim 64 or 128, pages a multiple of 16)", nh, nkv, dh, page_size);
+    LI_REQUIRE(scale > 0.0f, "attention (tcgen05): the scale must be positive");
+    if (dh == 64)
+        return launch<64>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
+                          window, max_q_len, stream);
+    return launch<128>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
+                       window, max_q_len, stream);
+}

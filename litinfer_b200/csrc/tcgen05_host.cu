@@ -43,10 +43,30 @@ int make_map(CUtensorMap* map, const void* base, int rows, int cols, int box_row
     return 0;
 }
 
+// The general form: a row-major [rows, cols] bfloat16 matrix in boxes of box_rows x box_cols with the 32-, 64- or
+// 128-byte swizzle (box_cols * 2 bytes must not exceed the swizzle width), zero fill outside.
+int make_map_ex(CUtensorMap* map, const void* base, unsigned long long rows, unsigned long long cols, unsigned box_cols, unsigned box_rows,
+                int swizzle_bytes) {
+    LI_REQUIRE(g_encode != nullptr, "tcgen05: make_map_ex before setup");
+    LI_REQUIRE(box_rows >= 1 && box_rows <= 256 && box_cols >= 8 && box_cols * 2 <= (unsigned)swizzle_bytes && (cols * 2) % 16 == 0,
+               "tcgen05: bad tensor map (box %u x %u, swizzle %d, %llu columns)", box_rows, box_cols, swizzle_bytes, cols);
+    const CUtensorMapSwizzle sw = swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                  : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return li_fail("tcgen05: cuTensorMapEncodeTiled failed with %d for a [%llu, %llu] tensor in boxes of %u x %u", (int)r, rows, cols, box_rows, box_cols);
+    return 0;
+}
+
 }  // namespace tc
 
 // 0 while no launch of a tcgen05 kernel has given up a wait; else which role did
-// (1 producer, 2 tensor-core issuer, 3 epilogue).  Meaningful after a synchronisation.
+// (products: 1 producer, 2 tensor-core issuer, 3 epilogue; attention: 11, 12, 13 likewise).  Meaningful after a synchronisation.
 LI_EXPORT int li_tcgen05_status() {
     tc::EncodeTiledFn f;
     int *h = nullptr, *d = nullptr;

@@ -306,7 +306,7 @@ def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
         *(_row_scale_args(row_scale, T) if row_scale is not None else (_p(None), _i(0), _i(0), _f(0.0))), _stream(qkv)), "linear_rope_kv")
 
 
-ATTENTION_IMPLEMENTATIONS = {"general": 0, "decode": 1, "prefill": 2}
+ATTENTION_IMPLEMENTATIONS = {"general": 0, "decode": 1, "prefill": 2, "prefill_tcgen05": 3}
 
 
 def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -319,7 +319,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     Queries are the first ``num_heads * head_dim`` columns of ``qkv`` (already
     rotated).  The token at position p of sequence s sees the cached keys
     ``max(0, p - window + 1) .. p`` of s, found through ``block_table[s]``.
-    ``implementation`` (``general``, ``decode``, ``prefill``) forces one kernel, for
+    ``implementation`` (``general``, ``decode``, ``prefill``, ``prefill_tcgen05``) forces one kernel, for
     tests and measurements; it is an error if that kernel refuses the sizes."""
     T = qkv.shape[0]
     S = ctx_lens.shape[0]

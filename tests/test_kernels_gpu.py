@@ -525,6 +525,45 @@ def test_attention_prefill_kernel_alone(heads, page):
         close(out, ref, torch.bfloat16, f"prefill kernel heads={heads} page={page} window={window}")
 
 
+@pytest.mark.parametrize("heads", [(12, 2, 128), (8, 8, 64), (28, 4, 128), (3, 1, 64)])
+@pytest.mark.parametrize("page", [16, 32])
+def test_attention_tcgen05_kernel_alone(heads, page):
+    """The prefill kernel on tcgen05 (128 tokens x 128 keys a tile): whole prompts shorter and longer than a tile and of
+    exactly one and two tiles, portions with history (ending inside a key tile and on its edge), single tokens, windows."""
+    nh, nkv, dh = heads
+    q_lens = [37, 300, 1, 128, 2, 256, 64, 17, 129]
+    ctx_lens = [37, 300, 33, 128, 130, 256, 384, 300, 513]
+    c = make_attention_case(q_lens, ctx_lens, nh, nkv, dh, page, torch.bfloat16, seed=43)
+    for window in (None, 24, 100, 200):
+        out, ref = run_attention_case(c, window, implementation="prefill_tcgen05")
+        close(out, ref, torch.bfloat16, f"tcgen05 prefill kernel heads={heads} page={page} window={window}")
+    assert K().library().li_tcgen05_status() == 0
+
+
+def test_attention_tcgen05_far_key_and_window_edge():
+    """One key far back carries the answer (a lost page or a wrong tile would change everything); the key at
+    p - window + 1 is the oldest one seen, the one at p - window is not."""
+    nh, nkv, dh = 12, 2, 128
+    for far in (0, 15, 16, 127, 128, 255, 256, 383):
+        c = make_attention_case([200], [600], nh, nkv, dh, 16, torch.bfloat16, seed=far)
+        _plant(c, 0, 1, far, 199)
+        out, ref = run_attention_case(c, None, implementation="prefill_tcgen05")
+        close(out, ref, torch.bfloat16, f"far key {far}")
+        v = c["vals"][0][far, 1].float().to(out.device)
+        got = out[199].float().view(nh, dh)[6]
+        assert (got - v).abs().max() < 0.1 * v.abs().max() + 0.05
+    W = 140
+    for key_pos, visible in ((599 - W + 1, True), (599 - W, False)):
+        c = make_attention_case([200], [600], nh, nkv, dh, 16, torch.bfloat16, seed=key_pos)
+        _plant(c, 0, 0, key_pos, 199)
+        out, ref = run_attention_case(c, W, implementation="prefill_tcgen05")
+        close(out, ref, torch.bfloat16, f"window edge key {key_pos}")
+        v = c["vals"][0][key_pos, 0].float().to(out.device)
+        got = out[199].float().view(nh, dh)[0]
+        near = (got - v).abs().max() < 0.1 * v.abs().max() + 0.05
+        assert bool(near) == visible, f"key {key_pos} should be {'visible' if visible else 'hidden'}"
+
+
 @pytest.mark.parametrize("heads", [(12, 2, 128), (4, 2, 16), (6, 2, 48), (8, 8, 64)])
 def test_attention_decode_large_batch(heads):
     """From 120 (sequence, kv head) pairs on, a CTA takes a whole context instead of a 128-key split."""
