@@ -44,8 +44,9 @@ struct __align__(1024) Smem {
     unsigned char k[kBuffers][kKeys * DH * 2];       // the same for keys
     unsigned char v[kBuffers][kKeys * DH * 2];       // 8 pages of [DH rows][16 keys] (32-byte swizzle)
     unsigned char p[kRows * kKeys * 2];              // 2 panels of [128 rows][64 keys] (128-byte swizzle)
-    unsigned long long q_full, s_full, p_full, pv_full;
-    unsigned long long kv_full[kBuffers], kv_empty[kBuffers];
+    unsigned long long q_full, p_full, pv_full;
+    unsigned long long s_full[2];
+    unsigned long long k_full[kBuffers], k_empty[kBuffers], v_full[kBuffers], v_empty[kBuffers];
     unsigned tmem_base;
 };
 
@@ -80,7 +81,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     extern __shared__ unsigned char smem_raw[];
     Smem<DH>& sm = *reinterpret_cast<Smem<DH>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int kPanels = DH / 64;
-    constexpr unsigned kTmemCols = 256;              // S: 128 columns, PV: up to 128
+    constexpr unsigned kTmemCols = 512;              // S of two tiles: 128 columns each; PV: up to 128
     const int s = blockIdx.z, h = blockIdx.y;
     const int tok0 = q_start[s], n = q_start[s + 1] - tok0;
     const int cta_i0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kRows;       // the last tiles see the most keys: first
@@ -96,12 +97,15 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.q_full, 1);
-        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.s_full[0], 1);
+        mbar_init(&sm.s_full[1], 1);
         mbar_init(&sm.p_full, 128);
         mbar_init(&sm.pv_full, 1);
         for (int b = 0; b < kBuffers; ++b) {
-            mbar_init(&sm.kv_full[b], 1);
-            mbar_init(&sm.kv_empty[b], 1);
+            mbar_init(&sm.k_full[b], 1);
+            mbar_init(&sm.k_empty[b], 1);
+            mbar_init(&sm.v_full[b], 1);
+            mbar_init(&sm.v_empty[b], 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -112,7 +116,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const unsigned tmem_s = sm.tmem_base, tmem_pv = sm.tmem_base + 128;
+    const unsigned tmem_s = sm.tmem_base, tmem_pv = sm.tmem_base + 256;      // S of tile j at tmem_s + 128 (j & 1)
     pdl_launch_dependents();
     pdl_wait();
 
@@ -123,24 +127,35 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int pn = 0; pn < kPanels; ++pn) tma_load_2d(sm.q + pn * (kRows * 128), &map_q, h * DH + pn * 64, tok0 + cta_i0, &sm.q_full);
             const int* bt = block_table + (size_t)s * max_blocks;
             bool ok = true;
+            // keys of a tile as soon as the product S two tiles back has read its buffer, values once P V has
             for (int j = 0; j < ntiles && ok; ++j) {
                 const int b = j % kBuffers;
-                ok = mbar_wait(&sm.kv_empty[b], ((j / kBuffers) & 1) ^ 1);
-                if (!ok) break;
-                mbar_expect_tx(&sm.kv_full[b], 2 * kKeys * DH * 2);
+                const unsigned free_parity = ((j / kBuffers) & 1) ^ 1;
                 const int key0 = (kt_first + j) * kKeys;
-#pragma unroll 1
+                int pages[kKeys / 16], offs[kKeys / 16];
+#pragma unroll
                 for (int pg = 0; pg < kKeys / 16; ++pg) {
                     const int key = key0 + pg * 16;
-                    int idx = key / page_size;
+                    const int idx = key / page_size;
                     int page = (key < ctx && idx < max_blocks) ? bt[idx] : 0;
                     if (page < 0 || page >= num_pages) page = 0;
-                    const int off = key % page_size;
+                    pages[pg] = page;
+                    offs[pg] = key % page_size;
+                }
+                ok = mbar_wait(&sm.k_empty[b], free_parity);
+                if (!ok) break;
+                mbar_expect_tx(&sm.k_full[b], kKeys * DH * 2);
+#pragma unroll
+                for (int pg = 0; pg < kKeys / 16; ++pg)
 #pragma unroll
                     for (int pn = 0; pn < kPanels; ++pn)
-                        tma_load_2d(sm.k[b] + pn * (kKeys * 128) + pg * 2048, &map_k, pn * 64, (page * nkv + kvh) * page_size + off, &sm.kv_full[b]);
-                    tma_load_2d(sm.v[b] + pg * (DH * 32), &map_v, off, (page * nkv + kvh) * DH, &sm.kv_full[b]);
-                }
+                        tma_load_2d(sm.k[b] + pn * (kKeys * 128) + pg * 2048, &map_k, pn * 64, (pages[pg] * nkv + kvh) * page_size + offs[pg], &sm.k_full[b]);
+                ok = mbar_wait(&sm.v_empty[b], free_parity);
+                if (!ok) break;
+                mbar_expect_tx(&sm.v_full[b], kKeys * DH * 2);
+#pragma unroll
+                for (int pg = 0; pg < kKeys / 16; ++pg)
+                    tma_load_2d(sm.v[b] + pg * (DH * 32), &map_v, offs[pg], (pages[pg] * nkv + kvh) * DH, &sm.v_full[b]);
             }
             if (!ok) atomicExch(error_flag, 11);
         }
@@ -148,18 +163,30 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0) {
             constexpr unsigned idesc_s = umma_idesc(kRows, kKeys), idesc_pv = umma_idesc(kRows, DH);
             bool ok = mbar_wait(&sm.q_full, 0);
-            for (int j = 0; j < ntiles && ok; ++j) {
+            // S of tile j + 1 is issued before P V of tile j: the tensor cores work on it while the softmax of tile j runs
+            auto issue_s = [&](int j) {
                 const int b = j % kBuffers;
-                ok = mbar_wait(&sm.kv_full[b], (j / kBuffers) & 1);
-                if (!ok) break;
+                if (!mbar_wait(&sm.k_full[b], (j / kBuffers) & 1)) return false;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
                     const unsigned long long da = umma_desc(sm.q + (k >> 2) * (kRows * 128)) + (unsigned long long)((k & 3) * 2);
                     const unsigned long long db = umma_desc(sm.k[b] + (k >> 2) * (kKeys * 128)) + (unsigned long long)((k & 3) * 2);
-                    umma_bf16(tmem_s, da, db, idesc_s, k ? 1u : 0u);
+                    umma_bf16(tmem_s + 128 * (j & 1), da, db, idesc_s, k ? 1u : 0u);
                 }
-                umma_commit(&sm.s_full);
+                umma_commit(&sm.s_full[j & 1]);
+                umma_commit(&sm.k_empty[b]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; j < ntiles && ok; ++j) {
+                const int b = j % kBuffers;
+                if (j + 1 < ntiles) {
+                    ok = issue_s(j + 1);
+                    if (!ok) break;
+                }
+                ok = mbar_wait(&sm.v_full[b], (j / kBuffers) & 1);
+                if (!ok) break;
                 ok = mbar_wait(&sm.p_full, j & 1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -170,7 +197,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     umma_bf16(tmem_pv, da, db, idesc_pv, k ? 1u : 0u);
                 }
                 umma_commit(&sm.pv_full);
-                umma_commit(&sm.kv_empty[b]);
+                umma_commit(&sm.v_empty[b]);
             }
             if (!ok) atomicExch(error_flag, 12);
         }
@@ -188,23 +215,35 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         float m = -INFINITY, l = 0.0f;
         unsigned char* prow = sm.p + (r >> 3) * 1024 + (r & 7) * 128;
         bool ok = true;
-        for (int j = 0; j < ntiles; ++j) {
+        // the row's maximum over tile j (first pass over its scores); a tile that the row sees whole needs no mask
+        auto tile_max = [&](int j, float& mx) {
             const int key0 = (kt_first + j) * kKeys;
-            ok = mbar_wait(&sm.s_full, j & 1);
-            if (!ok) break;
+            if (!mbar_wait(&sm.s_full[j & 1], (j >> 1) & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // first pass: the row's maximum over this tile
-            float mx = -INFINITY;
+            const bool whole = key0 >= lo && key0 + kKeys - 1 <= p;
+            mx = -INFINITY;
 #pragma unroll 1
             for (int c = 0; c < kKeys / 32; ++c) {
                 float v[32];
-                tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
+                tmem_ld_32x32(tmem_s + 128 * (j & 1) + lane_addr + c * 32, v);
+                if (whole) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int key = key0 + c * 32 + i;
-                    if (key >= lo && key <= p) mx = fmaxf(mx, v[i]);
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + c * 32 + i;
+                        if (key >= lo && key <= p) mx = fmaxf(mx, v[i]);
+                    }
                 }
             }
+            return true;
+        };
+        float mx = -INFINITY;
+        ok = tile_max(0, mx);
+        for (int j = 0; j < ntiles && ok; ++j) {
+            const int key0 = (kt_first + j) * kKeys;
+            const bool whole = key0 >= lo && key0 + kKeys - 1 <= p;
             const float m_new = fmaxf(m, mx * scale_log2);           // scale > 0: the order is the same
             const float ms = (m_new == -INFINITY) ? 0.0f : m_new;
             const float alpha = fast_exp2(m - ms);
@@ -213,16 +252,26 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll 1
             for (int c = 0; c < kKeys / 32; ++c) {
                 float v[32];
-                tmem_ld_32x32(tmem_s + lane_addr + c * 32, v);
+                tmem_ld_32x32(tmem_s + 128 * (j & 1) + lane_addr + c * 32, v);
                 unsigned pk[16];
+                if (whole) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    const int key = key0 + c * 32 + i;
-                    const float e0 = (key >= lo && key <= p) ? fast_exp2(v[i] * scale_log2 - ms) : 0.0f;
-                    const float e1 = (key + 1 >= lo && key + 1 <= p) ? fast_exp2(v[i + 1] * scale_log2 - ms) : 0.0f;
-                    sum += e0 + e1;
-                    __nv_bfloat162 t2 = __floats2bfloat162_rn(e0, e1);
-                    pk[i >> 1] = *reinterpret_cast<unsigned*>(&t2);
+                    for (int i = 0; i < 32; i += 2) {
+                        const float e0 = fast_exp2(fmaf(v[i], scale_log2, -ms)), e1 = fast_exp2(fmaf(v[i + 1], scale_log2, -ms));
+                        sum += e0 + e1;
+                        __nv_bfloat162 t2 = __floats2bfloat162_rn(e0, e1);
+                        pk[i >> 1] = *reinterpret_cast<unsigned*>(&t2);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        const int key = key0 + c * 32 + i;
+                        const float e0 = (key >= lo && key <= p) ? fast_exp2(fmaf(v[i], scale_log2, -ms)) : 0.0f;
+                        const float e1 = (key + 1 >= lo && key + 1 <= p) ? fast_exp2(fmaf(v[i + 1], scale_log2, -ms)) : 0.0f;
+                        sum += e0 + e1;
+                        __nv_bfloat162 t2 = __floats2bfloat162_rn(e0, e1);
+                        pk[i >> 1] = *reinterpret_cast<unsigned*>(&t2);
+                    }
                 }
                 // 32 keys = four 16-byte chunks of panel c / 2, chunks 4 (c & 1) .. + 3 of the row, swizzled by the row
                 unsigned char* panel = prow + (c >> 1) * (kRows * 128);
@@ -237,6 +286,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&sm.p_full);
+            // while the tensor cores multiply P V: the maximum of the next tile, whose scores are ready by now
+            if (j + 1 < ntiles) {
+                ok = tile_max(j + 1, mx);
+                if (!ok) break;
+            }
             ok = mbar_wait(&sm.pv_full, j & 1);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
