@@ -9,10 +9,12 @@
 //              is the V operand of one k-step ([head_dim, 16 keys], 32-byte swizzle);
 //   warp 1     one thread issues the products with tcgen05.mma, accumulators in tensor memory:
 //              S = Q K^T (128 x 128) and, once the probabilities are in shared memory, PV = P V (128 x head_dim);
-//   warps 2-5  one thread per token: reads its row of S from tensor memory, applies scale and mask, keeps the
-//              running maximum and sum of the online softmax in float (src/ops/paged_attention/op.cpp:194-234),
-//              writes P as bfloat16 in the operand layout, then adds PV to its output row in registers,
-//              O = O alpha + PV.
+//   warps 2-9  two threads per token, each with half of a tile's keys and half of the output columns: they read
+//              their part of the token's row of S from tensor memory, apply scale and mask, keep the running
+//              maximum (exchanged between the two) and sum of the online softmax in float
+//              (src/ops/paged_attention/op.cpp:194-234), write P as bfloat16 in the operand layout, then add
+//              PV to the output row in registers, O = O alpha + PV.  The maximum of tile j + 1 is taken while
+//              the tensor cores multiply P V of tile j, and S of tile j + 1 was issued before that.
 // Keys and values of the portion itself are already in the cache (the rope kernel ran before).  Token i of a
 // portion of n tokens in a context of c sits at position p = c - n + i and sees keys max(0, p - window + 1) .. p.
 // Keys of a tile that lie past the context are read from whatever page the table names (page 0 if none) and get
@@ -35,7 +37,7 @@ using namespace tc;
 
 constexpr int kRows = 128;          // tokens per CTA
 constexpr int kKeys = 128;          // keys per tile
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;        // producer warp, tensor-core warp, eight softmax warps
 constexpr int kBuffers = 2;
 
 template <int DH>
@@ -45,7 +47,8 @@ struct __align__(1024) Smem {
     unsigned char v[kBuffers][kKeys * DH * 2];       // 8 pages of [DH rows][16 keys] (32-byte swizzle)
     unsigned char p[kRows * kKeys * 2];              // 2 panels of [128 rows][64 keys] (128-byte swizzle)
     unsigned long long q_full, p_full, pv_full;
-    unsigned long long s_full[2];
+    unsigned long long s_full[2], mx_full[2];
+    float mx[2][2][kRows];                           // [tile parity][half of the keys][row]: maxima, exchanged between a row's two threads
     unsigned long long k_full[kBuffers], k_empty[kBuffers], v_full[kBuffers], v_empty[kBuffers];
     unsigned tmem_base;
 };
@@ -99,7 +102,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(&sm.q_full, 1);
         mbar_init(&sm.s_full[0], 1);
         mbar_init(&sm.s_full[1], 1);
-        mbar_init(&sm.p_full, 128);
+        mbar_init(&sm.p_full, 256);
+        mbar_init(&sm.mx_full[0], 256);
+        mbar_init(&sm.mx_full[1], 256);
         mbar_init(&sm.pv_full, 1);
         for (int b = 0; b < kBuffers; ++b) {
             mbar_init(&sm.k_full[b], 1);
@@ -202,57 +207,64 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!ok) atomicExch(error_flag, 12);
         }
     } else {
-        const int quarter = warp & 3;
+        // Two threads a token (warps w and w + 4 reach the same lanes of tensor memory): each takes half of a tile's
+        // keys and half of the output columns; they exchange their maxima through shared memory.
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;                       // this thread's token within the tile = its lane of tensor memory
         const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+        constexpr int HK = kKeys / 2, HD = DH / 2;
         const bool valid = cta_i0 + r < n;
         const int p = valid ? p_first + r : -1;                  // its position; no key is visible to an unused row
         const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
         const float scale_log2 = scale * 1.4426950408889634f;
-        float o[DH];
+        float o[HD];
 #pragma unroll
-        for (int d = 0; d < DH; ++d) o[d] = 0.0f;
+        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
         float m = -INFINITY, l = 0.0f;
-        unsigned char* prow = sm.p + (r >> 3) * 1024 + (r & 7) * 128;
+        unsigned char* prow = sm.p + half * (kRows * 128) + (r >> 3) * 1024 + (r & 7) * 128;      // panel `half` holds this thread's 64 keys
         bool ok = true;
-        // the row's maximum over tile j (first pass over its scores); a tile that the row sees whole needs no mask
+        // the row's maximum over tile j (first pass over the scores); keys that the row sees whole need no mask
         auto tile_max = [&](int j, float& mx) {
-            const int key0 = (kt_first + j) * kKeys;
+            const int key0 = (kt_first + j) * kKeys + half * HK;
             if (!mbar_wait(&sm.s_full[j & 1], (j >> 1) & 1)) return false;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const bool whole = key0 >= lo && key0 + kKeys - 1 <= p;
-            mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < kKeys / 32; ++c) {
+            const bool whole = key0 >= lo && key0 + HK - 1 <= p;
+            float mine = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < HK / 32; ++c) {
                 float v[32];
-                tmem_ld_32x32(tmem_s + 128 * (j & 1) + lane_addr + c * 32, v);
+                tmem_ld_32x32(tmem_s + 128 * (j & 1) + lane_addr + half * HK + c * 32, v);
                 if (whole) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, v[i]);
+                    for (int i = 0; i < 32; ++i) mine = fmaxf(mine, v[i]);
                 } else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const int key = key0 + c * 32 + i;
-                        if (key >= lo && key <= p) mx = fmaxf(mx, v[i]);
+                        if (key >= lo && key <= p) mine = fmaxf(mine, v[i]);
                     }
                 }
             }
+            sm.mx[j & 1][half][r] = mine;
+            mbar_arrive(&sm.mx_full[j & 1]);
+            if (!mbar_wait(&sm.mx_full[j & 1], (j >> 1) & 1)) return false;
+            mx = fmaxf(mine, sm.mx[j & 1][half ^ 1][r]);
             return true;
         };
         float mx = -INFINITY;
         ok = tile_max(0, mx);
         for (int j = 0; j < ntiles && ok; ++j) {
-            const int key0 = (kt_first + j) * kKeys;
-            const bool whole = key0 >= lo && key0 + kKeys - 1 <= p;
+            const int key0 = (kt_first + j) * kKeys + half * HK;
+            const bool whole = key0 >= lo && key0 + HK - 1 <= p;
             const float m_new = fmaxf(m, mx * scale_log2);           // scale > 0: the order is the same
             const float ms = (m_new == -INFINITY) ? 0.0f : m_new;
             const float alpha = fast_exp2(m - ms);
             // second pass: probabilities, rounded to bfloat16, into the operand tile
             float sum = 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < kKeys / 32; ++c) {
+#pragma unroll
+            for (int c = 0; c < HK / 32; ++c) {
                 float v[32];
-                tmem_ld_32x32(tmem_s + 128 * (j & 1) + lane_addr + c * 32, v);
+                tmem_ld_32x32(tmem_s + 128 * (j & 1) + lane_addr + half * HK + c * 32, v);
                 unsigned pk[16];
                 if (whole) {
 #pragma unroll
@@ -273,12 +285,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         pk[i >> 1] = *reinterpret_cast<unsigned*>(&t2);
                     }
                 }
-                // 32 keys = four 16-byte chunks of panel c / 2, chunks 4 (c & 1) .. + 3 of the row, swizzled by the row
-                unsigned char* panel = prow + (c >> 1) * (kRows * 128);
+                // 32 keys = four 16-byte chunks of the row, chunks 4 c .. 4 c + 3, swizzled by the row
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    const int ch = ((c & 1) * 4 + q) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(panel + ch * 16) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+                    const int ch = (c * 4 + q) ^ (r & 7);
+                    *reinterpret_cast<uint4*>(prow + ch * 16) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
                 }
             }
             l = l * alpha + sum;
@@ -295,20 +306,28 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int c = 0; c < DH / 32; ++c) {
+            for (int c = 0; c < HD / 32; ++c) {
                 float v[32];
-                tmem_ld_32x32(tmem_pv + lane_addr + c * 32, v);
+                tmem_ld_32x32(tmem_pv + lane_addr + half * HD + c * 32, v);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + v[i];
             }
+        }
+        // the row's denominator: the sums of its two threads (both ran with the same maxima)
+        if (ok) {
+            const int jx = ntiles;                               // one more use of the exchange buffers
+            sm.mx[jx & 1][half][r] = l;
+            mbar_arrive(&sm.mx_full[jx & 1]);
+            ok = mbar_wait(&sm.mx_full[jx & 1], (jx >> 1) & 1);
+            if (ok) l = sm.mx[jx & 1][0][r] + sm.mx[jx & 1][1][r];
         }
         if (!ok) {
             if (lane == 0) atomicExch(error_flag, 13);
         } else if (valid) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
-            bf16* dst = out + ((size_t)(tok0 + cta_i0 + r) * nh + h) * DH;
+            bf16* dst = out + ((size_t)(tok0 + cta_i0 + r) * nh + h) * DH + half * HD;
 #pragma unroll
-            for (int d = 0; d < DH; d += 8) {
+            for (int d = 0; d < HD; d += 8) {
                 unsigned pk[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {

@@ -3,13 +3,15 @@
 // and the float accumulator in tensor memory.  The prefill path of every
 // projection (q|k|v, o, gate|up, down, lm_head).
 //
-// One CTA computes a BM x BN tile: 128 x 128 with a ring of 6 stages, or 256 x 256
-// (two accumulators of 128 lanes x 256 columns: all of tensor memory) with 3
-// stages.  A multiprocessor takes in operand bytes at a limited rate (about
-// 90 GB/s measured here); a 128 x 128 tile needs 32 KB per 256 tensor-core
-// cycles and is bound by that, a 256 x 256 tile needs 64 KB per 1024 cycles.
-// The large tile is used where it still fills the GPU (wide products: gate|up,
-// lm_head of many rows).  Roles, by warp:
+// One CTA computes a BM x BN tile: 128 x 128 with a ring of 6 stages, 256 x 128
+// with 4, or 256 x 256 (two accumulators of 128 lanes x 256 columns: all of
+// tensor memory) with 3 stages.  A multiprocessor takes in operand bytes from
+// L2 at a limited rate (about 55 GB/s measured here, 8 TB/s over the GPU); a
+// 128 x 128 tile needs 32 KB per 256 tensor-core cycles and is bound by that,
+// a 256 x 256 tile needs 64 KB per 1024 cycles.  The large tile is used where it
+// still fills the GPU (wide products: gate|up, lm_head of many rows; with a
+// split of k: down), the middle one for narrow products with a short k
+// (q|k|v, o).  Roles, by warp:
 //   warp 0   producer: one lane issues the TMA loads of a BM x 64 tile of a and
 //            a BN x 64 tile of w per k-block (64 bfloat16 = one 128-byte swizzle
 //            row) into a ring of stages, each guarded by a full/empty mbarrier pair;
@@ -21,8 +23,7 @@
 // Both operands are K-major ([rows, K] row-major), which is how activations and
 // LitInfer-style [out, in] weights (src/ops/linear/cpu/linear_cpu.cpp:45-60)
 // lie in memory; TMA zero-fills rows and columns beyond the tensor, so any M,
-// N and any K that is a multiple of 8 (16-byte rows) work.  No cluster
-// multicast is used.
+// N and any K that is a multiple of 8 (16-byte rows) work.
 //
 // Every wait on an mbarrier is bounded.  A wait that runs out raises a flag in
 // mapped host memory (li_tcgen05_status() reads it), the CTA waits, again
@@ -39,7 +40,7 @@ int g_forced_ksplit = 0;         // > 0: split k this many ways whatever the sha
 
 template <int BM, int BN>
 struct Tile {
-    static constexpr int kStages = (BM + BN) <= 256 ? 6 : 3;
+    static constexpr int kStages = (BM + BN) <= 256 ? 6 : ((BM + BN) <= 384 ? 4 : 3);
     static constexpr int kBytesA = BM * BK * 2, kBytesB = BN * BK * 2;
     static constexpr unsigned kCols = (BM / 128) * BN;          // tensor-memory columns: one accumulator per 128 rows
 };
@@ -361,6 +362,11 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     if (g_forced_ksplit > 0) ksplit = g_forced_ksplit;
     const bool big = tile == 2 || (tile == 0 && (big_ctas >= 120 || ksplit > 1));
     if (big) return launch_tile<256, 256, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, ksplit);
+    // narrow products with a short k (q|k|v, o): 256 x 128 tiles take in a quarter less per flop than 128 x 128, and
+    // there are still enough of them to occupy most of the GPU
+    const long long mid_ctas = (long long)ceil_div(M, 256) * ceil_div(N, 128);
+    if (tile == 3 || (tile == 0 && mid_ctas >= 74))
+        return launch_tile<256, 128, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
     return launch_tile<128, 128, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
 }
 
@@ -368,7 +374,7 @@ int g_forced_tile = 0;
 
 }  // namespace
 
-// 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always.  For tests and measurements.
+// 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always; 3: 256 x 128 always.  For tests and measurements.
 LI_EXPORT void li_tcgen05_force_tile(int tile) { g_forced_tile = tile; }
 
 // 0: splits of k by shape; n > 0: n splits always.  For tests and measurements.

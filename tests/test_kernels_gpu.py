@@ -145,9 +145,9 @@ TC_SHAPES = [(128, 128, 64), (128, 128, 512), (256, 384, 1536), (2048, 2048, 153
              (1000, 389, 96), (64, 1536, 8960), (2048, 1536, 8960), (5, 151936, 1536)]
 
 
-@pytest.fixture(params=[1, 2], ids=["tile128", "tile256"])
+@pytest.fixture(params=[1, 2, 3], ids=["tile128", "tile256", "tile256x128"])
 def forced_tile(request):
-    """Both tile sizes of the tcgen05 kernel, whatever it would choose for the shape itself."""
+    """Every tile size of the tcgen05 kernel, whatever it would choose for the shape itself."""
     lib = K().library()
     lib.li_tcgen05_force_tile(request.param)
     yield request.param
@@ -187,7 +187,7 @@ def test_linear_tcgen05_kernel(shape, forced_tile, forced_ksplit):
                                          ("tcgen05", (77, 352, 80)), ("tcgen05", (65, 48, 40))])
 def test_linear_swiglu_epilogue(which, shape, forced_tile, forced_ksplit):
     """gate and up rows interleaved in groups of 8; the product's epilogue applies up * silu(gate)."""
-    if which != "tcgen05" and (forced_tile == 2 or forced_ksplit):
+    if which != "tcgen05" and (forced_tile != 1 or forced_ksplit):
         pytest.skip("tile size and forced splits are properties of the tcgen05 kernel")
     M, N, Kd = shape
     I = N // 2
