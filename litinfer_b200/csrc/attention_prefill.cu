@@ -2,7 +2,7 @@
 // without history in the cache) over the paged cache, causal, grouped-query.
 // Single tokens in the same batch are portions of length one.
 //
-// Grid (tile of 64 tokens, query head, sequence); a CTA has 4 warps, each owns
+// Grid (query head, tile of 64 tokens, sequence); a CTA has 4 warps, each owns
 // 16 consecutive tokens of the portion for one head.  The keys and values the
 // CTA needs are brought into shared memory in tiles of 64 keys with cp.async,
 // two tiles in flight (the next one loads while the current one is used), and
@@ -82,10 +82,10 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
     constexpr int F = DH / 32, R = (DH % 32) / 16;  // 32-wide groups of head_dim (16-byte fragment loads), 16-wide tail (8-byte loads)
     constexpr int KS = DH / 16, NT = DH / 8;
 
-    const int s = blockIdx.z, h = blockIdx.y;
+    const int s = blockIdx.z, h = blockIdx.x;
     const int tok0 = q_start[s], n = q_start[s + 1] - tok0;
     // the last tiles of a portion see the most keys: they are started first
-    const int cta_i0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTile;
+    const int cta_i0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * kTile;       // CTAs start in the order x, y, z: all heads of the heaviest tile first
     if (cta_i0 >= n) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -277,7 +277,7 @@ template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
            const int* q_start, const int* ctx_lens, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window,
            int max_q_len, cudaStream_t stream) {
-    LI_REQUIRE(S <= 65535 && nh <= 65535, "attention (prefill): batch %d or heads %d too large for one launch", S, nh);
+    LI_REQUIRE(S <= 65535 && ceil_div(max_q_len > 0 ? max_q_len : 1, kTile) <= 65535, "attention (prefill): batch %d or portions of %d tokens too large for one launch", S, max_q_len);
     constexpr size_t smem = 2 * (size_t)(kKeys * DH * 2 + DH * kKeys * 2);
     static bool raised = false;
     if (!raised && smem > 48 * 1024) {
@@ -285,7 +285,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
         if (e != cudaSuccess) return li_fail("attention (prefill): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
-    dim3 grid(ceil_div(max_q_len > 0 ? max_q_len : 1, kTile), nh, S);
+    dim3 grid(nh, ceil_div(max_q_len > 0 ? max_q_len : 1, kTile), S);
     prefill_attention_kernel<DH><<<grid, kWarps * 32, smem, stream>>>((const bf16*)qkv, (bf16*)out, (const bf16*)kcache,
                                                                       (const bf16*)vcache, block_table, max_blocks, q_start, ctx_lens,
                                                                       nh, nkv, page_size, num_pages, scale, window);

@@ -1,7 +1,7 @@
 // Prefill attention on the fifth-generation tensor cores: long portions of prompts over the paged cache,
 // causal, grouped-query, bfloat16.
 //
-// Grid (tile of 128 tokens, query head, sequence).  A CTA of six warps works on 128 consecutive tokens of a
+// Grid (query head, tile of 128 tokens, sequence).  A CTA of six warps works on 128 consecutive tokens of a
 // portion for one head, against tiles of 128 keys:
 //   warp 0     one thread brings Q (once) and, two tiles ahead, K and V of each tile into shared memory with
 //              TMA, page by page through the block table: a page of keys is 16 rows of the K operand
@@ -85,9 +85,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     Smem<DH>& sm = *reinterpret_cast<Smem<DH>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int kPanels = DH / 64;
     constexpr unsigned kTmemCols = 512;              // S of two tiles: 128 columns each; PV: up to 128
-    const int s = blockIdx.z, h = blockIdx.y;
+    // CTAs start in the order x, y, z: all heads of a sequence's last tile of tokens (which sees the most keys) first, then
+    // all heads of the tile before it, and so on, so that the long CTAs do not start late
+    const int s = blockIdx.z, h = blockIdx.x;
     const int tok0 = q_start[s], n = q_start[s + 1] - tok0;
-    const int cta_i0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kRows;       // the last tiles see the most keys: first
+    const int cta_i0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * kRows;
     if (cta_i0 >= n) return;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ctx = ctx_lens[s];
@@ -368,8 +370,8 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
         if (e != cudaSuccess) return li_fail("attention (tcgen05): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
-    LI_REQUIRE(S <= 65535 && nh <= 65535, "attention (tcgen05): batch %d or heads %d too large for one launch", S, nh);
-    dim3 grid(ceil_div(max_q_len, kRows), nh, S);
+    LI_REQUIRE(S <= 65535 && ceil_div(max_q_len, kRows) <= 65535, "attention (tcgen05): batch %d or portions of %d tokens too large for one launch", S, max_q_len);
+    dim3 grid(nh, ceil_div(max_q_len, kRows), S);
     li_launch_pdl(prefill_attention_tc_kernel<DH>, grid, dim3(kThreads), smem, stream, map_q, map_k, map_v, (bf16*)out, block_table, max_blocks,
                   q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, err_dev);
     return li_check_launch("attention (tcgen05)");
