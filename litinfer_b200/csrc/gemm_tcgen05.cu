@@ -93,11 +93,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_acc = sm.tmem_base;
+    // programmatic dependent launch: everything up to here overlapped the end of the kernel before this one; what reads
+    // its results (the producer) or writes over memory it may still read (the epilogue) waits for it
+    pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
             int issued = 0;
             bool ok = true;
+            pdl_wait();
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % kStages;
                 const unsigned phase = (kb / kStages) & 1;
@@ -150,6 +154,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (lane == 0) atomicExch(error_flag, 3);
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            pdl_wait();
             // one 32-column piece of a row: bias or SwiGLU, one rounding, store
             auto emit = [&](int row, int c, float (&v)[32]) {
                 const int col0 = n0 + c;
@@ -341,8 +346,8 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
         LI_REQUIRE((size_t)grid.x * grid.y <= (size_t)kSplitCounters, "linear (tcgen05): too many tiles for a split of k");
         if (int rc = split_workspace((size_t)ksplit * grid.x * grid.y * BM * BN, &ws)) return rc;
     }
-    gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu><<<grid, kThreads, smem, stream>>>(map_a, map_w, bias, (Tout*)out, M, N, K, g_error_dev,
-                                                                                 ws->partial, ws->counters, ksplit);
+    li_launch_pdl(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu>, grid, dim3(kThreads), smem, stream, map_a, map_w, bias, (Tout*)out, M, N, K,
+                  g_error_dev, ws->partial, ws->counters, ksplit);
     return li_check_launch("linear (tcgen05)");
 }
 
