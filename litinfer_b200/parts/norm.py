@@ -13,9 +13,12 @@ from ..weights.loader import ParamSpec
 from .base import NORMS, Deferred, Norm
 
 
-# Up to this many tokens a step the norm between two products rides on them (measured: with more tokens the products'
-# registers are too short for the extra work, and a norm kernel of its own is cheaper).
-DEFER_MAX_TOKENS = 16
+def defers(tokens: int) -> bool:
+    """Whether the norm between two products rides on them for a step of this many tokens.  Measured: up to 16 tokens it
+    saves two kernels a layer; with more, the weight-streaming kernels' registers are too short for the extra work.  (Tried
+    in the tensor-memory GEMM of prefill too: there the residual stream read and written by the epilogue's threads, a row
+    each, cost more than the norm kernels it replaced.)"""
+    return 0 < tokens <= 16
 
 
 @NORMS.register("rmsnorm")
@@ -43,9 +46,9 @@ class RMSNorm(Norm):
         return out
 
     def after_linear(self, linear, a, x32, defer=False):
-        # Few bfloat16 tokens and a consumer that applies the reciprocal root itself: the product adds to the stream and
-        # leaves weight * x with the sums of squares, all in its epilogue; this norm has no kernel of its own.
-        if defer and self.dtype == torch.bfloat16 and not isinstance(a, Deferred) and 0 < a.shape[0] <= DEFER_MAX_TOKENS:
+        # bfloat16 and a consumer that applies the reciprocal root itself: the product adds to the stream and leaves
+        # weight * x with the sums of squares, all in its epilogue; this norm has no kernel of its own.
+        if defer and self.dtype == torch.bfloat16 and not isinstance(a, Deferred) and defers(a.shape[0]):
             h = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
             parts = K.linear_add_scaled_parts(a, linear.weight, x32, h)
             if parts:
