@@ -38,38 +38,84 @@ constexpr int kThreads = 192;
 
 int g_forced_ksplit = 0;         // > 0: split k this many ways whatever the shape (tests and measurements)
 
-template <int BM, int BN>
+// kPair: two CTAs of a cluster (multiprocessors of one pair) work as one on a tile of 2 BM x BN with tcgen05.mma
+// cta_group::2: each brings its own BM rows of a and half of the BN rows of w, the tensor cores of both read both halves
+// of w, and each keeps the accumulator of its own rows.  A CTA then takes in a quarter less per flop (BM = BN = 256).
+template <int BM, int BN, bool kPair = false>
 struct Tile {
-    static constexpr int kStages = (BM + BN) <= 256 ? 6 : ((BM + BN) <= 384 ? 4 : 3);
-    static constexpr int kBytesA = BM * BK * 2, kBytesB = BN * BK * 2;
+    static constexpr int kRowsB = kPair ? BN / 2 : BN;
+    static constexpr int kBytesA = BM * BK * 2, kBytesB = kRowsB * BK * 2;
+    static constexpr int kStages = (kBytesA + kBytesB) <= 32768 ? 6 : ((kBytesA + kBytesB) <= 49152 ? 4 : 3);
     static constexpr unsigned kCols = (BM / 128) * BN;          // tensor-memory columns: one accumulator per 128 rows
 };
 
-template <int BM, int BN>
+template <int BM, int BN, bool kPair = false>
 struct __align__(1024) SharedStorage {
-    unsigned char a[Tile<BM, BN>::kStages][Tile<BM, BN>::kBytesA];
-    unsigned char b[Tile<BM, BN>::kStages][Tile<BM, BN>::kBytesB];
-    unsigned long long full[Tile<BM, BN>::kStages];
-    unsigned long long empty[Tile<BM, BN>::kStages];
+    unsigned char a[Tile<BM, BN, kPair>::kStages][Tile<BM, BN, kPair>::kBytesA];
+    unsigned char b[Tile<BM, BN, kPair>::kStages][Tile<BM, BN, kPair>::kBytesB];
+    unsigned long long full[Tile<BM, BN, kPair>::kStages];
+    unsigned long long empty[Tile<BM, BN, kPair>::kStages];
     unsigned long long accum;
     unsigned tmem_base;
     int failed;
     int is_last;
 };
 
-template <int BM, int BN, typename Tout, bool kSwiglu>
+// ---- forms for a pair of CTAs (cta_group::2) ----
+
+__device__ __forceinline__ unsigned cluster_cta_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// A tile load whose bytes are counted on the barrier of the pair's first CTA (the same offset in its shared memory: in
+// the cluster's address space the two CTAs of a pair differ in bit 24), whichever of the two issues it.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
+    const unsigned z = 0;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(z)
+        : "memory");
+}
+
+// arrives on the barrier at this offset in both CTAs of the pair once the products issued so far are done
+__device__ __forceinline__ void umma_commit_pair(unsigned long long* bar) {
+    const unsigned short mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
+}
+
+template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag,
                     float* __restrict__ partial, unsigned* __restrict__ counters, int ksplit) {
     extern __shared__ unsigned char smem_raw[];
-    using SS = SharedStorage<BM, BN>;
-    constexpr int kStages = Tile<BM, BN>::kStages;
-    constexpr int kStageBytesA = Tile<BM, BN>::kBytesA, kStageBytesB = Tile<BM, BN>::kBytesB;
-    constexpr unsigned kCols = Tile<BM, BN>::kCols;
+    using SS = SharedStorage<BM, BN, kPair>;
+    constexpr int kStages = Tile<BM, BN, kPair>::kStages;
+    constexpr int kStageBytesA = Tile<BM, BN, kPair>::kBytesA, kStageBytesB = Tile<BM, BN, kPair>::kBytesB;
+    constexpr unsigned kCols = Tile<BM, BN, kPair>::kCols;
+    const unsigned pair_rank = kPair ? cluster_cta_rank() : 0u;
     SS& sm = *reinterpret_cast<SS*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    // a pair is two neighbours along x (the hardware pairs CTAs of consecutive rank): they share the tile's columns and
+    // take consecutive tiles of rows
+    const int m0 = kPair ? ((int)blockIdx.y * 2 + (int)(blockIdx.x & 1)) * BM : (int)blockIdx.y * BM;
+    const int n0 = kPair ? (int)(blockIdx.x >> 1) * BN : (int)blockIdx.x * BN;
     const int nkb_total = (K + BK - 1) / BK;
     const int split = blockIdx.z;
     const int kb_first = (int)((long long)split * nkb_total / ksplit);
@@ -85,12 +131,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kCols)
-                     : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if constexpr (kPair) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kCols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kCols)
+                         : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();          // the other CTA's barriers are set up before anything arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_acc = sm.tmem_base;
     // programmatic dependent launch: everything up to here overlapped the end of the kernel before this one; what reads
@@ -107,22 +160,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const unsigned phase = (kb / kStages) & 1;
                 ok = mbar_wait(&sm.empty[s], phase ^ 1);
                 if (!ok) break;
-                mbar_expect_tx(&sm.full[s], kStageBytesA + kStageBytesB);
-                tma_load_2d(sm.a[s], &map_a, (kb_first + kb) * BK, m0, &sm.full[s]);
-                tma_load_2d(sm.b[s], &map_w, (kb_first + kb) * BK, n0, &sm.full[s]);
+                if constexpr (kPair) {
+                    // both CTAs' tiles are counted on the first CTA's barrier, which expects the bytes of both
+                    if (pair_rank == 0) mbar_expect_tx(&sm.full[s], 2 * (kStageBytesA + kStageBytesB));
+                    tma_load_2d_pair(sm.a[s], &map_a, (kb_first + kb) * BK, m0, &sm.full[s]);
+                    tma_load_2d_pair(sm.b[s], &map_w, (kb_first + kb) * BK, n0 + (int)pair_rank * (BN / 2), &sm.full[s]);
+                } else {
+                    mbar_expect_tx(&sm.full[s], kStageBytesA + kStageBytesB);
+                    tma_load_2d(sm.a[s], &map_a, (kb_first + kb) * BK, m0, &sm.full[s]);
+                    tma_load_2d(sm.b[s], &map_w, (kb_first + kb) * BK, n0, &sm.full[s]);
+                }
                 issued = kb + 1;
             }
             if (!ok) {
                 sm.failed = 1;
                 atomicExch(error_flag, 1);
-                // the copies already issued must land before the CTA may leave
-                for (int kb = (issued > kStages ? issued - kStages : 0); kb < issued; ++kb)
-                    mbar_wait(&sm.full[kb % kStages], (kb / kStages) & 1);
+                // the copies already issued must land before the CTA may leave (in a pair only the first CTA can tell)
+                if (!kPair || pair_rank == 0)
+                    for (int kb = (issued > kStages ? issued - kStages : 0); kb < issued; ++kb)
+                        mbar_wait(&sm.full[kb % kStages], (kb / kStages) & 1);
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            const unsigned idesc = umma_idesc(128, BN);
+        if (lane == 0 && pair_rank == 0) {                 // in a pair the first CTA issues the products of both
+            const unsigned idesc = umma_idesc(kPair ? 256 : 128, BN);
             bool ok = true;
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % kStages;
@@ -134,13 +195,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                 for (int k = 0; k < BK / 16; ++k)
 #pragma unroll
-                    for (int half = 0; half < BM / 128; ++half)       // rows 128 half .. of the a tile: 128 rows x 128 bytes further on
-                        umma_bf16(tmem_acc + (unsigned)(half * BN), da + (unsigned long long)(k * 2 + half * (128 * 128 / 16)),
-                                  db + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
-                umma_commit(&sm.empty[s]);
+                    for (int half = 0; half < BM / 128; ++half) {     // rows 128 half .. of the a tile: 128 rows x 128 bytes further on
+                        if constexpr (kPair)
+                            umma_bf16_pair(tmem_acc + (unsigned)(half * BN), da + (unsigned long long)(k * 2 + half * (128 * 128 / 16)),
+                                           db + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
+                        else
+                            umma_bf16(tmem_acc + (unsigned)(half * BN), da + (unsigned long long)(k * 2 + half * (128 * 128 / 16)),
+                                      db + (unsigned long long)(k * 2), idesc, (kb | k) ? 1u : 0u);
+                    }
+                if constexpr (kPair) umma_commit_pair(&sm.empty[s]);
+                else umma_commit(&sm.empty[s]);
             }
             if (ok) {
-                umma_commit(&sm.accum);
+                if constexpr (kPair) umma_commit_pair(&sm.accum);
+                else umma_commit(&sm.accum);
             } else {
                 sm.failed = 1;
                 atomicExch(error_flag, 2);
@@ -282,9 +350,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     __syncwarp();                    // the lanes that had no role wait for the one that had
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if constexpr (kPair) cluster_sync_all();          // neither CTA frees tensor memory or leaves while the other may still use it
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kCols) : "memory");
+        if constexpr (kPair) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kCols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kCols) : "memory");
     }
 }
 
@@ -322,7 +392,7 @@ int split_workspace(size_t floats, SplitWorkspace** out) {
     return 0;
 }
 
-template <int BM, int BN, typename Tout, bool kSwiglu>
+template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false>
 int launch_tile(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int ksplit = 1) {
     EncodeTiledFn encode = nullptr;
     int *g_error_host = nullptr, *g_error_dev = nullptr;
@@ -331,23 +401,27 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
         return li_fail("linear (tcgen05): an earlier launch gave up waiting on a barrier (status %d); the results since then are invalid", *g_error_host);
     CUtensorMap map_a, map_w;
     if (int rc = make_map(&map_a, a, M, K, BM)) return rc;
-    if (int rc = make_map(&map_w, w, N, K, BN)) return rc;
-    const size_t smem = sizeof(SharedStorage<BM, BN>) + 1024;
+    if (int rc = make_map(&map_w, w, N, K, Tile<BM, BN, kPair>::kRowsB)) return rc;
+    const size_t smem = sizeof(SharedStorage<BM, BN, kPair>) + 1024;
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
     dim3 grid(ceil_div(N, BN), ceil_div(M, BM), ksplit);
+    if (kPair) {                                           // pairs along x; a tile of rows past the matrix reads zeros and stores nothing
+        grid.x *= 2;
+        grid.y = (grid.y + 1) / 2;
+    }
     LI_REQUIRE(grid.y <= 65535, "linear (tcgen05): M=%d is too large for one launch", M);
     SplitWorkspace none, *ws = &none;
     if (ksplit > 1) {
         LI_REQUIRE((size_t)grid.x * grid.y <= (size_t)kSplitCounters, "linear (tcgen05): too many tiles for a split of k");
         if (int rc = split_workspace((size_t)ksplit * grid.x * grid.y * BM * BN, &ws)) return rc;
     }
-    li_launch_pdl(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu>, grid, dim3(kThreads), smem, stream, map_a, map_w, bias, (Tout*)out, M, N, K,
-                  g_error_dev, ws->partial, ws->counters, ksplit);
+    li_launch_pdl(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu, kPair>, grid, dim3(kThreads), smem, stream, dim3(kPair ? 2 : 1, 1, 1), map_a, map_w,
+                  bias, (Tout*)out, M, N, K, g_error_dev, ws->partial, ws->counters, ksplit);
     return li_check_launch("linear (tcgen05)");
 }
 
@@ -365,7 +439,13 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
         if (ksplit < 1) ksplit = 1;
     }
     if (g_forced_ksplit > 0) ksplit = g_forced_ksplit;
-    const bool big = tile == 2 || (tile == 0 && (big_ctas >= 120 || ksplit > 1));
+    // narrow products with a long k (down): pairs of CTAs on 256 x 256 (128 rows each, one accumulator) fill the GPU without
+    // a split of k and its merge (measured: 56 us against 73 us with the split)
+    const long long pair_ctas = (long long)((ceil_div(M, 128) + 1) & ~1) * ceil_div(N, 256);
+    if (tile == 5 || (tile == 0 && ksplit > 1 && g_forced_ksplit == 0 && pair_ctas >= 74 && pair_ctas <= 148))
+        return launch_tile<128, 256, Tout, kSwiglu, true>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
+    const bool big = tile == 2 || tile == 4 || (tile == 0 && (big_ctas >= 120 || ksplit > 1));
+    if (big && tile == 4) return launch_tile<256, 256, Tout, kSwiglu, true>(a, w, bias, out, M, N, K, stream, ksplit);
     if (big) return launch_tile<256, 256, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, ksplit);
     // narrow products with a short k (q|k|v, o): 256 x 128 tiles take in a quarter less per flop than 128 x 128, and
     // there are still enough of them to occupy most of the GPU
@@ -379,7 +459,8 @@ int g_forced_tile = 0;
 
 }  // namespace
 
-// 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always; 3: 256 x 128 always.  For tests and measurements.
+// 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always, one CTA a tile; 3: 256 x 128 always; 4: pairs of CTAs on
+// 512 x 256 (two accumulators each); 5: pairs of CTAs on 256 x 256 (one accumulator each).  For tests and measurements.
 LI_EXPORT void li_tcgen05_force_tile(int tile) { g_forced_tile = tile; }
 
 // 0: splits of k by shape; n > 0: n splits always.  For tests and measurements.
