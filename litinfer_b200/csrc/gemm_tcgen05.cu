@@ -28,6 +28,7 @@
 // Every wait on an mbarrier is bounded.  A wait that runs out raises a flag in
 // mapped host memory (li_tcgen05_status() reads it), the CTA waits, again
 // bounded, for the copies it has in flight, frees its tensor memory and returns.
+#include "gemm_epilogue.cuh"
 #include "tcgen05.cuh"
 
 namespace {
@@ -60,44 +61,6 @@ struct __align__(1024) SharedStorage {
     int failed;
     int is_last;
 };
-
-// ---- forms for a pair of CTAs (cta_group::2) ----
-
-__device__ __forceinline__ unsigned cluster_cta_rank() {
-    unsigned r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// A tile load whose bytes are counted on the barrier of the pair's first CTA (the same offset in its shared memory: in
-// the cluster's address space the two CTAs of a pair differ in bit 24), whichever of the two issues it.
-__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1, unsigned long long* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar) & 0xFEFFFFFFu), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_bf16_pair(unsigned tmem_d, unsigned long long da, unsigned long long db, unsigned idesc, unsigned accumulate) {
-    const unsigned z = 0;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(z)
-        : "memory");
-}
-
-// arrives on the barrier at this offset in both CTAs of the pair once the products issued so far are done
-__device__ __forceinline__ void umma_commit_pair(unsigned long long* bar) {
-    const unsigned short mask = 3;
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-                 ::"r"(smem_u32(bar)), "h"(mask) : "memory");
-}
 
 template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -224,75 +187,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             pdl_wait();
             // one 32-column piece of a row: bias or SwiGLU, one rounding, store
-            auto emit = [&](int row, int c, float (&v)[32]) {
-                const int col0 = n0 + c;
-                    if (kSwiglu) {
-                        // columns come as 8 gate, 8 up, 8 gate, 8 up: 16 activations up * gate / (1 + exp(-gate))
-                        if (row < M && col0 < N) {
-                            const int half_n = N >> 1;
-                            Tout* dst = out + (size_t)row * half_n + (col0 >> 1);
-                            float a16[16];
-#pragma unroll
-                            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) {
-                                    const float gate = v[16 * h + i], up = v[16 * h + 8 + i];
-                                    a16[8 * h + i] = up * (gate / (1.0f + expf(-gate)));
-                                }
-                            if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0 && sizeof(Tout) == 2) {
-                                uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-                                for (int i = 0; i < 2; ++i) {
-                                    uint4 pk;
-                                    __nv_bfloat162 h0 = __floats2bfloat162_rn(a16[8 * i + 0], a16[8 * i + 1]);
-                                    __nv_bfloat162 h1 = __floats2bfloat162_rn(a16[8 * i + 2], a16[8 * i + 3]);
-                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(a16[8 * i + 4], a16[8 * i + 5]);
-                                    __nv_bfloat162 h3 = __floats2bfloat162_rn(a16[8 * i + 6], a16[8 * i + 7]);
-                                    pk.x = *reinterpret_cast<unsigned*>(&h0);
-                                    pk.y = *reinterpret_cast<unsigned*>(&h1);
-                                    pk.z = *reinterpret_cast<unsigned*>(&h2);
-                                    pk.w = *reinterpret_cast<unsigned*>(&h3);
-                                    d4[i] = pk;
-                                }
-                            } else {
-                                for (int i = 0; i < 16; ++i) {
-                                    const int src_col = col0 + 16 * (i >> 3) + (i & 7);      // the gate column of activation i
-                                    if (src_col + 8 < N) dst[i] = from_float<Tout>(a16[i]);
-                                }
-                            }
-                        }
-                    } else if (row < M && col0 < N) {
-                        Tout* dst = out + (size_t)row * N + col0;
-                        if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0) {
-                            if (bias) {
-#pragma unroll
-                                for (int i = 0; i < 32; ++i) v[i] += bias[col0 + i];
-                            }
-                            if (sizeof(Tout) == 2) {
-                                uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    uint4 pk;
-                                    __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
-                                    __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
-                                    __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
-                                    __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
-                                    pk.x = *reinterpret_cast<unsigned*>(&h0);
-                                    pk.y = *reinterpret_cast<unsigned*>(&h1);
-                                    pk.z = *reinterpret_cast<unsigned*>(&h2);
-                                    pk.w = *reinterpret_cast<unsigned*>(&h3);
-                                    d4[i] = pk;
-                                }
-                            } else {
-                                float4* d4 = reinterpret_cast<float4*>(dst);
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) d4[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                            }
-                        } else {
-                            for (int i = 0; i < 32 && col0 + i < N; ++i) dst[i] = from_float<Tout>(bias ? v[i] + bias[col0 + i] : v[i]);
-                        }
-                    }
-            };
+            auto emit = [&](int row, int c, float (&v)[32]) { gemm_store_piece<Tout, kSwiglu>(row, n0 + c, v, bias, out, M, N); };
             const size_t tile_id = (size_t)blockIdx.y * gridDim.x + blockIdx.x, tiles = (size_t)gridDim.x * gridDim.y;
             if (ksplit == 1) {
 #pragma unroll 1
@@ -460,7 +355,8 @@ int g_forced_tile = 0;
 }  // namespace
 
 // 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always, one CTA a tile; 3: 256 x 128 always; 4: pairs of CTAs on
-// 512 x 256 (two accumulators each); 5: pairs of CTAs on 256 x 256 (one accumulator each).  For tests and measurements.
+// 512 x 256 (two accumulators each); 5: pairs of CTAs on 256 x 256 (one accumulator each); 6: the persistent kernel
+// (gemm_tcgen05_persistent.cu).  For tests and measurements.
 LI_EXPORT void li_tcgen05_force_tile(int tile) { g_forced_tile = tile; }
 
 // 0: splits of k by shape; n > 0: n splits always.  For tests and measurements.
@@ -471,8 +367,15 @@ bool li_tcgen05_accepts(const void* a, const void* w, const void* out, int dtype
            (dtype_out == LI_BF16 || dtype_out == LI_F32);
 }
 
+bool li_tcgen05_persistent_wanted(int M, int N, int K);
+int li_linear_tcgen05_persistent(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K, int epilogue,
+                                 cudaStream_t stream);
+
 int li_linear_tcgen05(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K,
                       int epilogue, cudaStream_t stream) {
+    // wide products with a short k (gate|up): the persistent kernel, whose epilogue overlaps the next tile's products
+    if (g_forced_tile == 6 || (g_forced_tile == 0 && g_forced_ksplit == 0 && li_tcgen05_persistent_wanted(M, N, K)))
+        return li_linear_tcgen05_persistent(a, w, bias, out, dtype_out, M, N, K, epilogue, stream);
     if (epilogue == LI_EPILOGUE_SWIGLU) {
         LI_REQUIRE(N % 16 == 0 && bias == nullptr && dtype_out == LI_BF16,
                    "linear (tcgen05): the swiglu epilogue needs N a multiple of 16, no bias and bfloat16 output");
