@@ -334,10 +334,11 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
         if (ksplit < 1) ksplit = 1;
     }
     if (g_forced_ksplit > 0) ksplit = g_forced_ksplit;
-    // narrow products with a long k (down): pairs of CTAs on 256 x 256 (128 rows each, one accumulator) fill the GPU without
-    // a split of k and its merge (measured: 56 us against 73 us with the split)
+    // narrow products (q|k|v, o, down of a long step): pairs of CTAs on 256 x 256 (128 rows each, one accumulator) fill the GPU
+    // in one wave without a split of k and its merge (measured at 2,048 rows: down 56 us against 73 us with the split,
+    // q|k|v 17 us against 19 us on 256 x 128 tiles)
     const long long pair_ctas = (long long)((ceil_div(M, 128) + 1) & ~1) * ceil_div(N, 256);
-    if (tile == 5 || (tile == 0 && ksplit > 1 && g_forced_ksplit == 0 && pair_ctas >= 74 && pair_ctas <= 148))
+    if (tile == 5 || (tile == 0 && big_ctas < 120 && g_forced_ksplit == 0 && pair_ctas >= 74 && pair_ctas <= 148))
         return launch_tile<128, 256, Tout, kSwiglu, true>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
     const bool big = tile == 2 || tile == 4 || (tile == 0 && (big_ctas >= 120 || ksplit > 1));
     if (big && tile == 4) return launch_tile<256, 256, Tout, kSwiglu, true>(a, w, bias, out, M, N, K, stream, ksplit);
@@ -347,7 +348,15 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     const long long mid_ctas = (long long)ceil_div(M, 256) * ceil_div(N, 128);
     if (tile == 3 || (tile == 0 && mid_ctas >= 74))
         return launch_tile<256, 128, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
-    return launch_tile<128, 128, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
+    // few small tiles and a long k (down of a short step): split k so that they fill the GPU, at least 16 k-blocks a split
+    int small_split = 1;
+    const long long small_ctas = (long long)ceil_div(M, 128) * ceil_div(N, 128);
+    if (small_ctas < 74 && nkb >= 32) {
+        small_split = (int)(148 / small_ctas);
+        if (small_split > nkb / 16) small_split = nkb / 16;
+        if (small_split < 1) small_split = 1;
+    }
+    return launch_tile<128, 128, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : small_split);
 }
 
 int g_forced_tile = 0;

@@ -194,10 +194,11 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
 
 }  // namespace
 
-// Worth it when every pair of multiprocessors gets several tiles and k is short enough for the epilogue to matter.
+// Worth it when a pair of multiprocessors gets more than one tile and k is short enough for the epilogue to matter
+// (measured: gate|up of 512 rows, 140 tiles: 29 us against 33 us; of 2,048 rows: 94 us against 138 us).
 bool li_tcgen05_persistent_wanted(int M, int N, int K) {
     const long long total = (long long)((ceil_div(M, kRows) + 1) / 2) * ceil_div(N, BN);
-    return total >= 3 * 74 && ceil_div(K, BK) <= 64;
+    return total >= 120 && ceil_div(K, BK) <= 64;
 }
 
 int li_linear_tcgen05_persistent(const void* a, const void* w, const float* bias, void* out, int dtype_out, int M, int N, int K, int epilogue,
