@@ -40,7 +40,8 @@ class Qwen2:
 
     def __init__(self, model_path, device="cuda:0", quantize=None, dtype: Optional[str] = None,
                  num_pages: Optional[int] = None, max_num_seqs: int = 64, max_tokens_per_step: int = 2048,
-                 prefill_chunk: int = 512, use_graphs: bool = True, model: Optional[DecoderModel] = None) -> None:
+                 prefill_chunk: int = 512, use_graphs: bool = True, run_ahead: bool = False,
+                 model: Optional[DecoderModel] = None) -> None:
         if quantize is not None:
             raise ValueError("quantized weights are not supported by this engine")
         dev = torch.device(device)
@@ -53,7 +54,7 @@ class Qwen2:
         self.spec = model.spec
         self.device = model.device
         self._engine_options = dict(max_num_seqs=max_num_seqs, max_tokens_per_step=max_tokens_per_step,
-                                    prefill_chunk=prefill_chunk, use_graphs=use_graphs)
+                                    prefill_chunk=prefill_chunk, use_graphs=use_graphs, run_ahead=run_ahead)
         self._num_pages = num_pages
         self._engine: Optional[Engine] = None
         self._single: Optional[Engine] = None
@@ -84,7 +85,7 @@ class Qwen2:
         has_state = any(getattr(r, "shape", None) is not None for r in self.model.cache_requirements())
         cfg = EngineConfig(num_pages=pages, page_size=16, max_num_seqs=opts["max_num_seqs"],
                            max_tokens_per_step=opts["max_tokens_per_step"], prefill_chunk=opts["prefill_chunk"],
-                           use_graphs=opts["use_graphs"] and not has_state)
+                           use_graphs=opts["use_graphs"] and not has_state, run_ahead=bool(opts.get("run_ahead", False)))
         return Engine(self.model, cfg)
 
     # ------------------------------------------------------------------
@@ -144,6 +145,7 @@ class Qwen2:
                     yield out[sent]
                     sent += 1
         finally:
+            eng.drain()                          # a step launched ahead is read before the request goes
             eng.scheduler.abort(rid)             # frees pages if the caller stopped early; no-op when finished
             eng.scheduler.forget(rid)
 

@@ -83,16 +83,25 @@ class ModelRunner:
         return into
 
     # ------------------------------------------------------------------
-    def step(self, items: Sequence[StepItem]) -> torch.Tensor:
-        """Float32 logits ``[wanted, vocab]`` in the order of the items and of their ``want``."""
+    def step(self, items: Sequence[StepItem], token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Float32 logits ``[wanted, vocab]`` in the order of the items and of their ``want``.
+
+        ``token_source`` (int32 on the device, one entry per item; every item a single token): the token ids come
+        from there instead of from the items, whose own ids are placeholders: they are copied over the uploaded
+        ones on the device, so that a step can be fed by the sampler's output of the step before without a round
+        trip through the host."""
         items = list(items)
         decode_only = all(len(it.tokens) == 1 for it in items)
+        if token_source is not None and (not decode_only or token_source.numel() != len(items)):
+            raise ValueError("token_source needs one token per item and items of one token each")
         fits = decode_only and max(it.cache.length for it in items) + 1 <= self.max_context
         if self.use_graphs and fits and len(items) <= self.GRAPH_BUCKETS[-1]:
-            logits = self._step_graph(items)
+            logits = self._step_graph(items, token_source)
         else:
             buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size)
             ctx = context_from(self._upload(buf), layout, self.manager.page_size)
+            if token_source is not None:
+                ctx.token_ids[:len(items)].copy_(token_source)
             logits = self.model.forward(ctx, self.manager.entries)
         for it in items:
             self.manager.commit(it.cache, it.cache.length + len(it.tokens))
@@ -106,7 +115,7 @@ class ModelRunner:
                 return b
         raise ValueError(n)
 
-    def _step_graph(self, items: List[StepItem]) -> torch.Tensor:
+    def _step_graph(self, items: List[StepItem], token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Decode-only step through a captured graph.  Every item wants its one token's
         logits in the captured layout; rows of items that want nothing are dropped after."""
         B = self._bucket(len(items))
@@ -125,6 +134,9 @@ class ModelRunner:
         g.last_key = tuple(it.cache.request_id for it in items)
         g.last_lengths = [it.cache.length for it in items]
         self._upload(buf, g.meta_buf)
+        if token_source is not None:
+            o_tok = g.layout["fields"]["token_ids"][0]
+            g.meta_buf[o_tok:o_tok + len(items)].copy_(token_source)
         g.graph.replay()
         self.graph_replays += 1
         rows = [i for i, w in enumerate(wanted) if w]

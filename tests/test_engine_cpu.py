@@ -94,6 +94,51 @@ def test_engine_greedy_matches_plain(model_dirs, cpu_kernels):
             assert eng.get_output(rid) == ref, f"config {name}, prompt of {len(p)}"
 
 
+def test_engine_run_ahead_gives_the_same_tokens(model_dirs, cpu_kernels):
+    """Steps launched before the tokens of the step before them are read: the same outputs as step by step, with requests
+    of different lengths (some end by length while others go on), with an end-of-sequence token that cuts requests short
+    (the token computed ahead for them is dropped), with too few pages for everybody, and with sampling."""
+    from litinfer_b200.engine import Engine, EngineConfig
+    from litinfer_b200.models import DecoderModel
+    from litinfer_b200.sampling.sampler import SamplingParams
+
+    cfg, w = P.read_model_folder(model_dirs["A"])
+    model = DecoderModel.from_dir(model_dirs["A"], "float32", "cpu")
+    prompts = [random_tokens(n, cfg["vocab_size"], 300 + n) for n in (5, 11, 17, 3)]
+    new = [9, 14, 6, 20]
+
+    def run(run_ahead, eos, pages, params):
+        eng = Engine(model, EngineConfig(num_pages=pages, max_num_seqs=4, max_tokens_per_step=24, prefill_chunk=16, use_graphs=False,
+                                         run_ahead=run_ahead))
+        eng.scheduler.eos = set(eos)
+        ids = [eng.add_request(p, n, params) for p, n in zip(prompts, new)]
+        steps = 0
+        while eng.has_unfinished():
+            eng.step()
+            steps += 1
+            assert steps < 500
+        assert eng.drain() == []
+        eng.manager.check()
+        assert eng.manager.num_free_pages(0) == pages and eng.manager.num_free_slots() == 4
+        return [(eng.get_output(i), eng.finish_reason(i)) for i in ids], eng.scheduler.num_preemptions
+
+    plain, _ = run(False, (), 12, None)
+    assert [len(o) for o, _ in plain] == new
+    # an end-of-sequence token: one that some request produces in the middle of its output
+    eos = plain[1][0][5]
+    preempted = 0
+    for params in (None, SamplingParams(temperature=0.8, top_k=20, top_p=0.9, seed=7)):
+        for e in ((), (eos,)):
+            for pages in (12, 5, 4, 3):
+                a, pre_a = run(False, e, pages, params)
+                b, pre_b = run(True, e, pages, params)
+                assert a == b, f"run_ahead changes the outputs (eos {e}, pages {pages}, params {params})"
+                if e and params is None:
+                    assert any(r == "eos" for _, r in a)
+                preempted += min(pre_a, pre_b)
+    assert preempted > 0, "the small pools were meant to force preemptions in both modes"
+
+
 def test_toy_mixer_with_state_on_cpu_references(model_dirs, cpu_kernels):
     from test_engine_gpu import run_toy_mixer
 

@@ -85,6 +85,52 @@ def test_engine_sampling_is_reproducible_and_batch_independent(model_dirs):
         assert alone == ref, f"request {i}: differs from the plain model with the same draws"
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_engine_run_ahead_on_the_device(dtype, model_dirs):
+    """Decode steps launched ahead (captured graphs, token ids passed from the sampler's output on the device): the same
+    tokens as step by step, greedy and sampled, with requests that end at different lengths and on an end-of-sequence
+    token; and through the entry point."""
+    from litinfer_b200 import Qwen2
+
+    cfg, _ = P.read_model_folder(model_dirs["B"])
+    prompts = [random_tokens(n, cfg["vocab_size"], 500 + n) for n in (5, 40, 17, 3, 64)]
+    new = [30, 12, 45, 7, 20]
+
+    def run(run_ahead, eos, sampled):
+        front = Qwen2(str(model_dirs["B"]), dtype=dtype, max_num_seqs=8, run_ahead=run_ahead)
+        front.engine_start()
+        front._eng().scheduler.eos = set(eos)
+        ids = [front.engine_add_request(p, n, **(dict(top_k=30, top_p=0.9, temperature=0.7, seed=11 + i) if sampled else {}))
+               for i, (p, n) in enumerate(zip(prompts, new))]
+        steps = 0
+        while front.engine_has_unfinished():
+            front.engine_step()
+            steps += 1
+            assert steps < 1000
+        outs = [front.engine_get_output(i) for i in ids]
+        eng = front._eng()
+        eng.manager.check()
+        assert eng.manager.num_free_slots() == 8
+        replays = eng.runner.graph_replays
+        front.engine_stop()
+        return outs, replays
+
+    plain, _ = run(False, (), False)
+    assert [len(o) for o in plain] == new
+    eos = plain[2][20]
+    for sampled in (False, True):
+        for e in ((), (eos,)):
+            a, _ = run(False, e, sampled)
+            b, replays = run(True, e, sampled)
+            assert a == b, f"run_ahead changes the outputs (eos {e}, sampled {sampled})"
+            assert replays > 20, "decode steps were meant to run through captured graphs"
+    # through the entry point, a request alone (in bfloat16 a request alone and in a batch may differ by rounding: other kernels)
+    ahead, plainly = Qwen2(str(model_dirs["B"]), dtype=dtype, run_ahead=True), Qwen2(str(model_dirs["B"]), dtype=dtype)
+    for i in (2, 0, 4):                                                       # the engine of generate is used again
+        assert ahead.generate(prompts[i], max_new_tokens=new[i]) == plainly.generate(prompts[i], max_new_tokens=new[i])
+    assert list(ahead.generate_stream(prompts[1], max_new_tokens=5))[:3] == plainly.generate(prompts[1], max_new_tokens=5)[:3]
+
+
 def test_engine_preempts_and_recomputes_when_pages_run_out(model_dirs):
     from litinfer_b200 import DecoderModel, Engine, EngineConfig
 
