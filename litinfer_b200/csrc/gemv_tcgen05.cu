@@ -299,10 +299,15 @@ int ensure_workspace(Workspace** ws) {
     return 0;
 }
 
-int choose_ksplit(int N, int K) {
+int g_forced_ksplit = 0;          // > 0: this many splits of k whatever the shape (measurements)
+
+// Splits of k: a function of N, K and the token tile (16, 32 or 64 columns), never of the number of tokens itself.
+int choose_ksplit(int N, int K, int bt) {
     const int tiles = ceil_div(N, BR), nkb = ceil_div(K, BK);
+    if (g_forced_ksplit > 0) return g_forced_ksplit < nkb ? g_forced_ksplit : nkb;
     int ks = kTargetCtas / tiles;
     if (ks < 1) ks = 1;
+    if (bt == 64 && ks > 8) ks = 8;                                   // 32 KB of partial sums a split: the merge by one CTA grows with them (measured)
     const int by_work = nkb / 2 > 0 ? nkb / 2 : 1;                    // at least two k-blocks a CTA
     if (ks > by_work) ks = by_work;
     while (ks > 1 && (size_t)ks * tiles * 64 * BR > kWorkspaceFloats) --ks;      // sized for 64 tokens whatever M is
@@ -320,7 +325,7 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     Workspace* ws = nullptr;
     if (int rc = ensure_workspace(&ws)) return rc;
     const int tiles = ceil_div(N, BR);
-    const int ksplit = choose_ksplit(N, K);
+    const int ksplit = choose_ksplit(N, K, BT);
     LI_REQUIRE(tiles <= kMaxTiles, "linear (tcgen05 gemv): N=%d has too many tiles", N);
     CUtensorMap map_w, map_x;
     if (int rc = make_map(&map_w, w, N, K, BR)) return rc;
@@ -346,6 +351,9 @@ int launch_bt(const void* a, const void* w, const float* bias, void* out, int M,
 }
 
 }  // namespace
+
+// 0: splits of k by shape; n > 0: n splits always.  For measurements.
+LI_EXPORT void li_gemv_tcgen05_force_ksplit(int n) { g_forced_ksplit = n; }
 
 bool li_gemv_tcgen05_accepts(const void* a, const void* w, int M, int N, int K) {
     return M >= 1 && M <= 64 && N >= 1 && K >= 8 && K % 8 == 0 && ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0);

@@ -40,7 +40,7 @@ int few_rows_kernel(const void* a, const void* w, const void* out, int M, int N,
     const bool aligned = ((uintptr_t)a % 16 == 0) && ((uintptr_t)w % 16 == 0) && ((uintptr_t)out % 16 == 0);
     if (!aligned || M > 64) return 0;
     const bool wide = (N + 127) / 128 >= 96;                   // fills the GPU without a split of k
-    const bool long_k = (K + 63) / 64 >= 64 && M <= 32;        // a split of k leaves every CTA enough to stream (measured: down projection)
+    const bool long_k = (K + 63) / 64 >= 64;                   // a split of k leaves every CTA enough to stream (measured: down projection)
     if ((wide || long_k) && li_gemv_tcgen05_accepts(a, w, M, N, K)) return 3;
     if (li_gemv_bf16_accepts(M, N, K)) return 1;
     return 0;
