@@ -29,7 +29,11 @@
 // mapped host memory (li_tcgen05_status() reads it), the CTA waits, again
 // bounded, for the copies it has in flight, frees its tensor memory and returns.
 #include "gemm_epilogue.cuh"
+#include "rope_epilogue.cuh"
 #include "tcgen05.cuh"
+
+bool li_tcgen05_persistent_wanted(int M, int N, int K);
+bool li_tcgen05_accepts(const void* a, const void* w, const void* out, int dtype_out, int M, int N, int K);
 
 namespace {
 
@@ -62,11 +66,81 @@ struct __align__(1024) SharedStorage {
     int is_last;
 };
 
-template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false>
+// One head (128 columns at `col0` of the accumulator row of token `row`) of the q|k|v product: bias, rotation of q and k
+// by the step's table, q into the output row, k into the paged cache, v into it transposed (rope_epilogue.cuh).
+// Called by whole warps (the loads from tensor memory are warp-wide); `valid`: this thread's row is a row of the product.
+__device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_tile, int row, bool valid, int head, const float* __restrict__ bias,
+                                                bf16* __restrict__ out, int N, const RopeEpilogue& re) {
+    const int slot = valid ? re.slot_mapping[row] : -1;
+    const int page = slot / re.page_size, off = slot - page * re.page_size;
+    const bool cache_ok = valid && re.write && slot >= 0 && page < re.num_pages;       // validated on the host; never write outside the cache
+    if (head < re.nh + re.nkv) {                                   // the same for the whole warp
+        const bool is_q = head < re.nh;
+        const bool store = is_q ? valid : cache_ok;
+        bf16* dst = !store ? nullptr
+                    : (is_q ? out + (size_t)row * N + (size_t)head * 128
+                            : re.kcache + (((size_t)page * re.nkv + (head - re.nh)) * re.page_size + off) * 128);
+        const float2* cs = reinterpret_cast<const float2*>(re.cos_sin) + (size_t)(valid ? row : 0) * 64;
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+            float lo[32], hi[32];
+            tc::tmem_ld_32x32(tmem_row + (unsigned)(col_in_tile + c * 32), lo);
+            tc::tmem_ld_32x32(tmem_row + (unsigned)(col_in_tile + c * 32 + 64), hi);
+            unsigned plo[16], phi[16];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                float y[4];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int j = c * 32 + i + e;
+                    float a = lo[i + e], b = hi[i + e];
+                    if (bias) {
+                        a += bias[head * 128 + j];
+                        b += bias[head * 128 + j + 64];
+                    }
+                    // q and k are rounded to bfloat16 by the projection before they are rotated, as in the unfused path
+                    a = __bfloat162float(__float2bfloat16_rn(a));
+                    b = __bfloat162float(__float2bfloat16_rn(b));
+                    const float2 t2 = __ldg(cs + j);
+                    y[e] = a * t2.x - b * t2.y;
+                    y[2 + e] = b * t2.x + a * t2.y;
+                }
+                __nv_bfloat162 l2 = __floats2bfloat162_rn(y[0], y[1]), h2 = __floats2bfloat162_rn(y[2], y[3]);
+                plo[i >> 1] = *reinterpret_cast<unsigned*>(&l2);
+                phi[i >> 1] = *reinterpret_cast<unsigned*>(&h2);
+            }
+            if (store) {
+                uint4* dl = reinterpret_cast<uint4*>(dst + c * 32);
+                uint4* dh = reinterpret_cast<uint4*>(dst + c * 32 + 64);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    dl[q] = make_uint4(plo[4 * q], plo[4 * q + 1], plo[4 * q + 2], plo[4 * q + 3]);
+                    dh[q] = make_uint4(phi[4 * q], phi[4 * q + 1], phi[4 * q + 2], phi[4 * q + 3]);
+                }
+            }
+        }
+    } else {
+        bf16* dst = cache_ok ? re.vcache + ((size_t)page * re.nkv + (head - re.nh - re.nkv)) * 128 * re.page_size + off : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+            float v[32];
+            tc::tmem_ld_32x32(tmem_row + (unsigned)(col_in_tile + c * 32), v);
+            if (cache_ok) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int d = c * 32 + i;
+                    dst[(size_t)d * re.page_size] = __float2bfloat16_rn(bias ? v[i] + bias[head * 128 + d] : v[i]);
+                }
+            }
+        }
+    }
+}
+
+template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false, bool kRope = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag,
-                    float* __restrict__ partial, unsigned* __restrict__ counters, int ksplit) {
+                    float* __restrict__ partial, unsigned* __restrict__ counters, int ksplit, const RopeEpilogue rope) {
     extern __shared__ unsigned char smem_raw[];
     using SS = SharedStorage<BM, BN, kPair>;
     constexpr int kStages = Tile<BM, BN, kPair>::kStages;
@@ -189,7 +263,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             // one 32-column piece of a row: bias or SwiGLU, one rounding, store
             auto emit = [&](int row, int c, float (&v)[32]) { gemm_store_piece<Tout, kSwiglu>(row, n0 + c, v, bias, out, M, N); };
             const size_t tile_id = (size_t)blockIdx.y * gridDim.x + blockIdx.x, tiles = (size_t)gridDim.x * gridDim.y;
-            if (ksplit == 1) {
+            if constexpr (kRope) {
+                // the q|k|v product of a prefill step: a tile of 256 columns is two heads of 128; never split along k
+                static_assert(!kRope || (BM == 128 && BN == 256 && sizeof(Tout) == 2 && !kSwiglu), "the rope epilogue is for 128 x 256 bfloat16 tiles");
+                const int row = m0 + quarter * 32 + lane;
+#pragma unroll 1
+                for (int hl = 0; hl < BN / 128; ++hl) {
+                    const int head = n0 / 128 + hl;
+                    if (head * 128 < N)                            // the same for the whole CTA
+                        rope_store_head(tmem_acc + ((unsigned)(quarter * 32) << 16), hl * 128, row, row < M, head, bias, reinterpret_cast<bf16*>(out), N, rope);
+                }
+            } else if (ksplit == 1) {
 #pragma unroll 1
                 for (int hc = 0; hc < (BM / 128) * (BN / 32); ++hc) {
                     const int half = hc / (BN / 32), c = (hc - half * (BN / 32)) * 32;
@@ -287,8 +371,9 @@ int split_workspace(size_t floats, SplitWorkspace** out) {
     return 0;
 }
 
-template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false>
-int launch_tile(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int ksplit = 1) {
+template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false, bool kRope = false>
+int launch_tile(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, cudaStream_t stream, int ksplit = 1,
+                const RopeEpilogue& rope = RopeEpilogue{}) {
     EncodeTiledFn encode = nullptr;
     int *g_error_host = nullptr, *g_error_dev = nullptr;
     if (int rc = setup(&encode, &g_error_host, &g_error_dev)) return rc;
@@ -300,7 +385,7 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
     const size_t smem = sizeof(SharedStorage<BM, BN, kPair>) + 1024;
     static bool raised = false;
     if (!raised) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu, kPair, kRope>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot raise shared memory to %zu: %s", smem, cudaGetErrorString(e));
         raised = true;
     }
@@ -315,8 +400,8 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
         LI_REQUIRE((size_t)grid.x * grid.y <= (size_t)kSplitCounters, "linear (tcgen05): too many tiles for a split of k");
         if (int rc = split_workspace((size_t)ksplit * grid.x * grid.y * BM * BN, &ws)) return rc;
     }
-    li_launch_pdl(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu, kPair>, grid, dim3(kThreads), smem, stream, dim3(kPair ? 2 : 1, 1, 1), map_a, map_w,
-                  bias, (Tout*)out, M, N, K, g_error_dev, ws->partial, ws->counters, ksplit);
+    li_launch_pdl(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu, kPair, kRope>, grid, dim3(kThreads), smem, stream, dim3(kPair ? 2 : 1, 1, 1), map_a, map_w,
+                  bias, (Tout*)out, M, N, K, g_error_dev, ws->partial, ws->counters, ksplit, rope);
     return li_check_launch("linear (tcgen05)");
 }
 
@@ -361,7 +446,30 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
 
 int g_forced_tile = 0;
 
+// whether `launch` would take the paired 256 x 256 tiles (one accumulator a CTA) for this shape by itself
+bool pair_tiles_chosen(int M, int N, int K) {
+    const long long big_ctas = (long long)ceil_div(M, 256) * ceil_div(N, 256);
+    const long long pair_ctas = (long long)((ceil_div(M, 128) + 1) & ~1) * ceil_div(N, 256);
+    (void)K;
+    return g_forced_tile == 0 && g_forced_ksplit == 0 && big_ctas < 120 && pair_ctas >= 74 && pair_ctas <= 148;
+}
+
 }  // namespace
+
+// The q|k|v product with rotary encoding and the cache writes as its epilogue (rope_epilogue.cuh): where the shape takes
+// the paired tiles anyway.
+bool li_tcgen05_rope_wanted(const void* a, const void* w, const void* out, int M, int N, int K) {
+    return li_tcgen05_accepts(a, w, out, LI_BF16, M, N, K) && N % 128 == 0 && pair_tiles_chosen(M, N, K) &&
+           !li_tcgen05_persistent_wanted(M, N, K);
+}
+
+int li_linear_tcgen05_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const RopeEpilogue& rope,
+                           cudaStream_t stream) {
+    LI_REQUIRE(li_tcgen05_rope_wanted(a, w, out, M, N, K), "linear + rope (tcgen05): refuses M=%d N=%d K=%d", M, N, K);
+    LI_REQUIRE(N == (rope.nh + 2 * rope.nkv) * 128 && rope.cos_sin && rope.slot_mapping && rope.kcache && rope.vcache,
+               "linear + rope (tcgen05): N=%d does not match %d + 2 x %d heads of 128, or a null operand", N, rope.nh, rope.nkv);
+    return launch_tile<128, 256, bf16, false, true, true>(a, w, bias, out, M, N, K, stream, 1, rope);
+}
 
 // 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always, one CTA a tile; 3: 256 x 128 always; 4: pairs of CTAs on
 // 512 x 256 (two accumulators each); 5: pairs of CTAs on 256 x 256 (one accumulator each); 6: the persistent kernel

@@ -12,6 +12,7 @@
 // kernels want to read them (LitInfer caches k after rotation as well,
 // src/llaisys/models/qwen2.cpp:626-673).
 #include "common.cuh"
+#include "rope_epilogue.cuh"
 #include "row_scale.cuh"
 
 namespace {
@@ -119,7 +120,29 @@ __global__ void v_cache_write_kernel(const T* __restrict__ qkv, const int* __res
     }
 }
 
+// cos and sin of every (token, pair) of a step, for kernels that rotate as an epilogue: out[t][j] = (cos, sin)(pos_t / denom_j)
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ denom, int half, float2* __restrict__ out, int total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int t = i / half, j = i - t * half;
+    float sn, cs;
+    sincosf((float)positions[t] / denom[j], &sn, &cs);
+    out[i] = make_float2(cs, sn);
+}
+
 }  // namespace
+
+LI_EXPORT int li_rope_table(const int* positions, const float* denom, int half, float* out, int T, cudaStream_t stream) {
+    LI_REQUIRE(T >= 0 && half > 0, "rope_table: bad sizes T=%d half=%d", T, half);
+    if (T == 0) return 0;
+    const long long total = (long long)T * half;
+    LI_REQUIRE(total <= 2147483647LL, "rope_table: too many entries");
+    li_launch_pdl(rope_table_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, positions, denom, half,
+                  reinterpret_cast<float2*>(out), (int)total);
+    return li_check_launch("rope_table");
+}
 
 LI_EXPORT int li_rope_kv_write(void* qkv, int dtype, const int* positions, const float* denom, int rotary_dim,
                                const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh, int page_size,
@@ -166,6 +189,9 @@ int li_linear_gemv_rope(const void* a, const void* w, const float* bias, void* o
                         const float* denom, const int* slot_mapping, void* kcache, void* vcache, int nh, int nkv, int dh,
                         int page_size, int num_pages, int write, const RowScale& rs, cudaStream_t stream);
 bool li_gemv_rope_accepts(const void* a, const void* w, int M, int N, int K, int nh, int nkv, int dh, int rotary_dim);
+bool li_tcgen05_rope_wanted(const void* a, const void* w, const void* out, int M, int N, int K);
+int li_linear_tcgen05_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const RopeEpilogue& rope,
+                           cudaStream_t stream);
 extern "C" int li_linear(const void* a, const void* w, const float* bias, void* out, int dtype_in, int dtype_out, int M, int N, int K,
                          int epilogue, cudaStream_t stream);
 extern "C" int li_linear_scaled(const void* a, const void* w, const float* bias, void* out, int dtype_in, int dtype_out, int M, int N,
@@ -174,10 +200,26 @@ extern "C" int li_linear_scaled(const void* a, const void* w, const float* bias,
 LI_EXPORT int li_linear_rope_kv(const void* a, const void* w, const float* bias, void* qkv, int dtype, const int* positions,
                                 const float* denom, int rotary_dim, const int* slot_mapping, void* kcache, void* vcache, int T,
                                 int K, int nh, int nkv, int dh, int page_size, int num_pages, int write, int allow_fused,
-                                const float* ssq, int nparts, int width, float eps, cudaStream_t stream) {
+                                const float* ssq, int nparts, int width, float eps, const float* cos_sin, cudaStream_t stream) {
     // ssq (or nullptr): partial sums of squares for a factor per token on the product, as in li_linear_scaled
+    // cos_sin (or nullptr): the step's table from li_rope_table; with it a long bfloat16 step rotates and writes the cache
+    // in the epilogue of the tensor-memory product (head_dim 128)
     const int N = (nh + 2 * nkv) * dh;
     if (T == 0) return 0;
+    if (allow_fused && cos_sin && !ssq && dtype == LI_BF16 && T > 64 && dh == 128 && rotary_dim == 128 && page_size % 16 == 0 &&
+        li_tcgen05_rope_wanted(a, w, qkv, T, N, K)) {
+        RopeEpilogue re;
+        re.cos_sin = cos_sin;
+        re.slot_mapping = slot_mapping;
+        re.kcache = (bf16*)kcache;
+        re.vcache = (bf16*)vcache;
+        re.nh = nh;
+        re.nkv = nkv;
+        re.page_size = page_size;
+        re.num_pages = num_pages;
+        re.write = write;
+        return li_linear_tcgen05_rope(a, w, bias, qkv, T, N, K, re, stream);
+    }
     RowScale rs;
     if (ssq) {
         LI_REQUIRE(nparts >= 1 && width >= 1, "linear_rope_kv: bad partial sums (%d parts, width %d)", nparts, width);

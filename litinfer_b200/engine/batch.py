@@ -59,6 +59,8 @@ class StepContext:
     host_q_start: List[int] = field(default_factory=list)
     host_ctx_lens: List[int] = field(default_factory=list)
     host_state_slots: List[int] = field(default_factory=list)
+    # what parts make once per step and share between the layers (keyed by the part), e.g. a table of rotation angles
+    scratch: dict = field(default_factory=dict)
 
     def group(self, gid: int) -> GroupView:
         return self.groups[gid]

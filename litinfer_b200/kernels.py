@@ -279,11 +279,13 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torc
 def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], qkv: torch.Tensor,
                    positions: torch.Tensor, denominators: torch.Tensor, rotary_dim: int, slot_mapping: torch.Tensor,
                    k_cache: torch.Tensor, v_cache: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                   write: bool = True, fused: bool = True, row_scale=None) -> None:
+                   write: bool = True, fused: bool = True, row_scale=None, cos_sin: Optional[torch.Tensor] = None) -> None:
     """The fused q|k|v projection followed by :func:`rope_kv_write`: ``qkv = a weight^T + bias``, q rotated in
     place, k rotated and v stored into the caches.  Keys and values are only guaranteed to be in the caches
     afterwards, not in ``qkv``.  For a few bfloat16 tokens both steps run as one kernel (the rotation is the
-    product's epilogue); ``fused=False`` forces two kernels, for tests.  ``row_scale`` as in :func:`linear`."""
+    product's epilogue); ``fused=False`` forces two kernels, for tests.  ``row_scale`` as in :func:`linear`.
+    ``cos_sin``: the step's table from :func:`rope_table`; with it a long bfloat16 step (head_dim 128) rotates and
+    writes the cache in the epilogue of the tensor-memory product too."""
     T, Kd = a.shape
     N = (num_heads + 2 * num_kv_heads) * head_dim
     _need(a, "linear input")
@@ -294,6 +296,8 @@ def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
     _need(positions, "positions", torch.int32, (T,))
     _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
     _need(slot_mapping, "slot mapping", torch.int32, (T,))
+    if cos_sin is not None:
+        _need(cos_sin, "rope table", torch.float32, (T, rotary_dim // 2, 2))
     _need(k_cache, "key cache", a.dtype)
     pages, nkv, page_size, dh = k_cache.shape
     _need(v_cache, "value cache", a.dtype, (pages, nkv, dh, page_size))
@@ -303,7 +307,19 @@ def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
         _p(a), _p(weight), _p(bias), _p(qkv), _i(_dt(a)), _p(positions), _p(denominators), _i(rotary_dim), _p(slot_mapping),
         _p(k_cache), _p(v_cache), _i(T), _i(Kd), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages),
         _i(1 if write else 0), _i(1 if fused else 0),
-        *(_row_scale_args(row_scale, T) if row_scale is not None else (_p(None), _i(0), _i(0), _f(0.0))), _stream(qkv)), "linear_rope_kv")
+        *(_row_scale_args(row_scale, T) if row_scale is not None else (_p(None), _i(0), _i(0), _f(0.0))), _p(cos_sin), _stream(qkv)),
+        "linear_rope_kv")
+
+
+def rope_table(positions: torch.Tensor, denominators: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t, j] = (cos, sin)(float(positions[t]) / denominators[j])``: the angles of a step, for products that rotate in
+    their epilogue (:func:`linear_rope_kv`)."""
+    T = positions.shape[0]
+    half = denominators.shape[0]
+    _need(positions, "positions", torch.int32, (T,))
+    _need(denominators, "rope denominators", torch.float32, (half,))
+    _need(out, "rope table", torch.float32, (T, half, 2))
+    _check(library().li_rope_table(_p(positions), _p(denominators), _i(half), _p(out), _i(T), _stream(out)), "rope_table")
 
 
 ATTENTION_IMPLEMENTATIONS = {"general": 0, "decode": 1, "prefill": 2, "prefill_tcgen05": 3}

@@ -72,7 +72,8 @@ class PagedAttention(Mixer):
         # projection, position encoding of q and k, k and v into the cache: one call (and for few tokens one kernel)
         K.linear_rope_kv(
             h, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, self.position.denominators, self.position.rotary_dim,
-            view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, cache.writes, row_scale=row_scale)
+            view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, cache.writes, row_scale=row_scale,
+            cos_sin=self.position.table(ctx) if hasattr(self.position, "table") else None)
         o = torch.empty((h.shape[0], self.q_dim), dtype=self.dtype, device=h.device)
         K.paged_attention(
             qkv, o, cache.k, cache.v, view.block_table, ctx.q_start, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,

@@ -29,3 +29,21 @@ class RotaryEmbedding(Position):
         j = torch.arange(self.rotary_dim // 2, dtype=torch.float32)
         denom = torch.pow(torch.tensor(self.theta, dtype=torch.float32), (2.0 * j) / float(self.rotary_dim))
         self.denominators = denom.to(self.device)
+
+    # Steps of more tokens than this get a table of cosines and sines, made once and shared by the layers (products that
+    # rotate in their epilogue read it); shorter steps compute the angles where they rotate.
+    TABLE_FROM_TOKENS = 65
+
+    def table(self, ctx):
+        """``[tokens, rotary_dim / 2, 2]`` float32 cos and sin of this step's positions, or None for a short step."""
+        if ctx.num_tokens < self.TABLE_FROM_TOKENS or self.dtype != torch.bfloat16:
+            return None
+        key = ("rope_table", self.theta, self.rotary_dim)
+        t = ctx.scratch.get(key)
+        if t is None:
+            from .. import kernels as K
+
+            t = torch.empty((ctx.num_tokens, self.rotary_dim // 2, 2), dtype=torch.float32, device=ctx.positions.device)
+            K.rope_table(ctx.positions, self.denominators, t)
+            ctx.scratch[key] = t
+        return t

@@ -124,9 +124,15 @@ def rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cach
 
 
 def linear_rope_kv(a, weight, bias, qkv, positions, denominators, rotary_dim, slot_mapping, k_cache, v_cache,
-                   num_heads, num_kv_heads, head_dim, write=True, fused=True, row_scale=None):
+                   num_heads, num_kv_heads, head_dim, write=True, fused=True, row_scale=None, cos_sin=None):
     linear(a, weight, bias, qkv, row_scale=row_scale)
     rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cache, v_cache, num_heads, num_kv_heads, head_dim, write)
+
+
+def rope_table(positions, denominators, out):
+    phi = positions.float().unsqueeze(1) / denominators.unsqueeze(0)
+    out[..., 0] = torch.cos(phi)
+    out[..., 1] = torch.sin(phi)
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
@@ -233,5 +239,5 @@ def sample(logits, params, out):
     out.copy_(torch.tensor(res, dtype=torch.int32))
 
 
-ALL = ["linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
+ALL = ["rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]

@@ -282,13 +282,14 @@ def test_rope_kv_write_many_tokens(dtype, cfg, page):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("cfg", [(4, 2, 16, 64, 5), (12, 2, 128, 1536, 8), (3, 1, 32, 96, 1), (6, 2, 48, 80, 20), (14, 2, 80, 136, 64), (12, 2, 128, 1536, 70)])
+@pytest.mark.parametrize("cfg", [(4, 2, 16, 64, 5), (12, 2, 128, 1536, 8), (3, 1, 32, 96, 1), (6, 2, 48, 80, 20), (14, 2, 80, 136, 64), (12, 2, 128, 1536, 70),
+                                 (12, 2, 128, 1536, 2048), (12, 2, 128, 1536, 1111), (28, 4, 128, 264, 600), (12, 2, 128, 1536, 300)])
 def test_linear_rope_kv_fused(dtype, cfg):
     """Projection, rotation and cache write as one call; for few bfloat16 tokens one kernel, the rotation in the
     product's epilogue.  Against the reference, and against the same call forced through separate kernels."""
     nh, nkv, dh, H, T = cfg
     N = (nh + 2 * nkv) * dh
-    pages, page = 9, 16
+    pages, page = max(9, -(-T // 16) + 2), 16
     a = rnd(T, H, dtype=dtype, seed=51)
     w = rnd(N, H, dtype=dtype, seed=52, scale=0.1)
     b = rnd(N, seed=53, scale=0.5)
@@ -304,7 +305,15 @@ def test_linear_rope_kv_fused(dtype, cfg):
         fn(a, w, b, qkv, positions, denom, dh, slots, kc, vc, nh, nkv, dh, True, **kw)
         return qkv[:, :nh * dh].clone(), kc, vc
 
-    q1, k1, v1 = run(K().linear_rope_kv)
+    # long steps: with the step's table of angles the tensor-memory product rotates and writes the cache in its epilogue
+    table = None
+    if T > 64:
+        table = torch.empty(T, dh // 2, 2, dtype=torch.float32, device=dev())
+        K().rope_table(positions, denom, table)
+        ref_table = torch.empty_like(table)
+        R.rope_table(positions, denom, ref_table)
+        close(table, ref_table, torch.float32, "rope table", f32_tol=2e-3)      # sincosf of angles up to 3000 rad
+    q1, k1, v1 = run(K().linear_rope_kv, cos_sin=table)
     q2, k2, v2 = run(K().linear_rope_kv, fused=False)
     q3, k3, v3 = run(R.linear_rope_kv)
     for got, ref, what in ((q1, q3, "q"), (k1, k3, "k cache"), (v1, v3, "v cache"), (q2, q3, "q unfused"), (k2, k3, "k unfused")):
@@ -320,7 +329,7 @@ def test_linear_rope_kv_fused(dtype, cfg):
     kc = torch.zeros(pages, nkv, page, dh, dtype=dtype, device=dev())
     vc = torch.zeros(pages, nkv, dh, page, dtype=dtype, device=dev())
     qkv = torch.zeros(T, N, dtype=dtype, device=dev())
-    K().linear_rope_kv(a, w, b, qkv, positions, denom, dh, slots, kc, vc, nh, nkv, dh, False)
+    K().linear_rope_kv(a, w, b, qkv, positions, denom, dh, slots, kc, vc, nh, nkv, dh, False, cos_sin=table)
     assert not kc.any() and not vc.any()
     close(qkv[:, :nh * dh], q3, dtype, "q without cache write", f32_tol=5e-4)
 
