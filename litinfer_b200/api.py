@@ -40,7 +40,7 @@ class Qwen2:
 
     def __init__(self, model_path, device="cuda:0", quantize=None, dtype: Optional[str] = None,
                  num_pages: Optional[int] = None, max_num_seqs: int = 64, max_tokens_per_step: int = 2048,
-                 prefill_chunk: int = 512, use_graphs: bool = True, run_ahead: bool = False,
+                 prefill_chunk: int = 2048, use_graphs: bool = True, run_ahead: bool = False,
                  model: Optional[DecoderModel] = None) -> None:
         if quantize is not None:
             raise ValueError("quantized weights are not supported by this engine")

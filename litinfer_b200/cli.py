@@ -44,7 +44,7 @@ def main(argv=None) -> int:
     ap.add_argument("--batch", action="store_true", help="run all prompts together through the continuous-batching engine")
     ap.add_argument("--num-pages", type=int, default=None, help="pages of 16 tokens in the cache pool (LLAISYS_NUM_BLOCKS also works)")
     ap.add_argument("--max-tokens-per-step", type=int, default=2048)
-    ap.add_argument("--prefill-chunk", type=int, default=512)
+    ap.add_argument("--prefill-chunk", type=int, default=2048)
     ap.add_argument("--output", help="write the results as JSON here as well")
     args = ap.parse_args(argv)
 

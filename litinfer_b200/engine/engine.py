@@ -41,7 +41,7 @@ class EngineConfig:
     page_size: int = 16                  # src/llaisys/kv_cache/block_kv_cache.hpp:11
     max_num_seqs: int = 64
     max_tokens_per_step: int = 2048
-    prefill_chunk: int = 512
+    prefill_chunk: int = 2048
     use_graphs: bool = True
     max_context: Optional[int] = None    # longest context a captured decode step must cover
     run_ahead: bool = False              # launch a decode step before the tokens of the one before it are read

@@ -47,7 +47,7 @@ DEFAULT_MAX_NEW_TOKENS = 512        # src/llaisys/models/qwen2.cpp:795
 class SchedulerConfig:
     max_num_seqs: int = 64
     max_tokens_per_step: int = 2048
-    prefill_chunk: int = 512
+    prefill_chunk: int = 2048            # a portion of a prompt per step: the step's whole budget (the tensor-memory kernels are at their best from about 2,000 rows)
 
     def __post_init__(self):
         for k in ("max_num_seqs", "max_tokens_per_step", "prefill_chunk"):

@@ -23,6 +23,15 @@ def pytest_configure(config):
 
 def pytest_collection_modifyitems(config, items):
     if torch.cuda.is_available():
+        # no GPU test takes more than seconds; one that sits for minutes ends the run (a thread ends the process: a
+        # signal would not get through a call that waits for the device)
+        try:
+            import pytest_timeout  # noqa: F401
+        except ImportError:
+            return
+        for item in items:
+            if "gpu" in item.keywords and item.get_closest_marker("timeout") is None:
+                item.add_marker(pytest.mark.timeout(300, method="thread"))
         return
     skip = pytest.mark.skip(reason="no CUDA device")
     for item in items:
