@@ -85,6 +85,19 @@ __device__ __forceinline__ void block_step(RowState<DH>& st, const unsigned (&qa
     }
 }
 
+// The two halves of block_step for blocks of 32 keys, so that the loads can be issued before the queries exist.
+template <int DH>
+__device__ __forceinline__ void block_load32(KFrag32<DH>& kf, VFrag32<DH>& vf, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
+                                             const int* __restrict__ bt, int key0, int last_key, int kvh, int nkv, int page_size, int num_pages,
+                                             int g, int t) {
+    const int kk = key0 + 8 * (g >> 1), vk = key0 + 8 * t;
+    int kpage = kk <= last_key ? bt[kk / page_size] : 0, vpage = vk <= last_key ? bt[vk / page_size] : 0;
+    if (kpage < 0 || kpage >= num_pages) kpage = 0;
+    if (vpage < 0 || vpage >= num_pages) vpage = 0;
+    load_k32<DH>(kf, kcache + (((size_t)kpage * nkv + kvh) * page_size + kk % page_size) * DH, g, t);
+    load_v32<DH>(vf, vcache + ((size_t)vpage * nkv + kvh) * DH * page_size + vk % page_size, page_size, g);
+}
+
 template <int DH, int KB>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
@@ -94,18 +107,33 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     extern __shared__ float sm[];
     __shared__ int is_last;
     pdl_launch_dependents();
-    pdl_wait();
     constexpr int kSplit = KB * kWarps;                // one block of KB keys per warp: one round trip to memory
     const int split = blockIdx.x, kvh = blockIdx.y, s = blockIdx.z;
-    const int ctx = ctx_lens[s];
+    const int ctx = ctx_lens[s];                       // the step's metadata is in place before its first kernel starts
     const int p = ctx - 1;
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int k_begin = split * kSplit;
     const int k_end = min(ctx, k_begin + kSplit);
-    if (k_begin >= ctx || k_end <= lo) return;
+    if (k_begin >= ctx || k_end <= lo) {
+        pdl_wait();                                    // a CTA leaves only after the kernel before it has finished: the chain of dependent kernels stays ordered
+        return;
+    }
     const int G = nh / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
+    const int* bt = block_table + (size_t)s * max_blocks;
+    const int my_key0 = k_begin + warp * KB;
+    const bool my_block = my_key0 < k_end && my_key0 + KB > lo;           // warp-uniform
+    // The kernel before this one (the q|k|v product) writes the keys and values of position p only.  A warp whose block
+    // does not hold p asks for its keys and values now, while that kernel is still running, and waits afterwards.
+    [[maybe_unused]] KFrag32<DH> kf_early;
+    [[maybe_unused]] VFrag32<DH> vf_early;
+    bool early = false;
+    if constexpr (KB == 32) {
+        early = my_block && !(p >= my_key0 && p < my_key0 + KB);
+        if (early) block_load32<DH>(kf_early, vf_early, kcache, vcache, bt, my_key0, k_end - 1, kvh, nkv, page_size, num_pages, g, t);
+    }
+    pdl_wait();
     // query fragments: rows g and g + 8 are heads kvh * G + g (+ 8)
     const bf16* qrow = qkv + (size_t)s * (nh + 2 * nkv) * DH + (size_t)kvh * G * DH;
     unsigned qa[DH / 16][4];
@@ -116,11 +144,13 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     RowState<DH> st;
     st.init();
     const int lo2[2] = {lo, lo}, hi2[2] = {k_end - 1, k_end - 1};
-    const int* bt = block_table + (size_t)s * max_blocks;
-    {
-        const int key0 = k_begin + warp * KB;
-        if (key0 < k_end && key0 + KB > lo)                  // warp-uniform
-            block_step<DH, KB>(st, qa, kcache, vcache, bt, key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t);
+    if (my_block) {
+        if constexpr (KB == 32) {
+            if (!early) block_load32<DH>(kf_early, vf_early, kcache, vcache, bt, my_key0, k_end - 1, kvh, nkv, page_size, num_pages, g, t);
+            compute32<DH>(st, qa, kf_early, vf_early, my_key0, lo2, hi2, scale, t);
+        } else {
+            block_step<DH, KB>(st, qa, kcache, vcache, bt, my_key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t);
+        }
     }
     const float m0 = st.m[0], m1 = st.m[1];
     const float l0 = quad_sum(st.l[0]), l1 = quad_sum(st.l[1]);
