@@ -143,3 +143,10 @@ def test_toy_mixer_with_state_on_cpu_references(model_dirs, cpu_kernels):
     from test_engine_gpu import run_toy_mixer
 
     run_toy_mixer(model_dirs, "cpu")
+
+
+def test_toy_routed_feed_forward_and_positions_on_cpu_references(model_dirs, cpu_kernels):
+    from test_engine_gpu import run_toy_feed_forward_and_positions
+
+    run_toy_feed_forward_and_positions(model_dirs, "cpu", "float32")
+

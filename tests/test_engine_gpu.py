@@ -227,3 +227,137 @@ def run_toy_mixer(model_dirs, device):
         assert (whole[5:] - whole[:-5]).abs().max() > 1e-3
     finally:
         MIXERS.unregister("toy_ema")
+
+
+# --------------------------------------------------------------------------
+# a toy feed-forward with routing and a toy position encoding
+# --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_routed_feed_forward_and_toy_positions(dtype, model_dirs):
+    run_toy_feed_forward_and_positions(model_dirs, "cuda:0", dtype)
+
+
+def run_toy_feed_forward_and_positions(model_dirs, device, dtype):
+    """Two more kinds of parts registered from outside the package and chosen per layer by a spec.
+
+    A feed-forward with routing: the router's logits (float32) pick one of four small gated experts per token.
+    A position encoding: rotary with the positions stretched by a factor (it owns its table of denominators, which is
+    all the attention kernels ask of it).  Checked: the parts alone against plain formulas; a model built from them
+    whole, in portions and token by token; and that each of them changes the logits."""
+    from dataclasses import replace
+
+    from litinfer_b200 import DecoderModel, StepItem
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.config import PartSpec, load_config
+    from litinfer_b200.engine import ModelRunner
+    from litinfer_b200.parts import FEED_FORWARDS, POSITIONS, FeedForward, FusedLinear, Position
+    from litinfer_b200.weights.loader import ParamSpec
+
+    class RoutedFF(FeedForward):
+        def __init__(self, spec, prefix, dtype, device):
+            super().__init__(spec, prefix, dtype, device)
+            self.hidden, self.inner, self.experts = int(spec["hidden_size"]), int(spec["expert_size"]), int(spec["experts"])
+            self.up = [FusedLinear(prefix, [f"experts.{e}.up"], self.hidden, [self.inner], False, dtype) for e in range(self.experts)]
+            self.gate = [FusedLinear(prefix, [f"experts.{e}.gate"], self.hidden, [self.inner], False, dtype) for e in range(self.experts)]
+            self.down = [FusedLinear(prefix, [f"experts.{e}.down"], self.inner, [self.hidden], False, dtype) for e in range(self.experts)]
+            self.router = None
+
+        def params(self):
+            out = [ParamSpec(self.prefix + "router.weight", (self.experts, self.hidden), role="keep", std=0.5)]
+            for group in (self.up, self.gate, self.down):
+                for lin in group:
+                    out += lin.params()
+            return out
+
+        def bind(self, tensors):
+            self.router = tensors.pop(self.prefix + "router.weight").float()
+            for group in (self.up, self.gate, self.down):
+                for lin in group:
+                    lin.bind(tensors)
+
+        def forward(self, h, ctx):
+            logits = h.float() @ self.router.t()                      # routing in float32
+            choice = logits.argmax(-1)
+            weight = torch.softmax(logits, -1).gather(1, choice[:, None])
+            y = torch.zeros(h.shape[0], self.hidden, dtype=torch.float32, device=h.device)
+            for e in range(self.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    x = h[rows].contiguous()
+                    g, u = self.gate[e](x).float(), self.up[e](x).float()
+                    y[rows] = self.down[e]((u * (g / (1 + torch.exp(-g)))).to(self.dtype)).float()
+            return (y * weight).to(self.dtype)
+
+    class StretchedRope(Position):
+        def __init__(self, spec, prefix, dtype, device, head_dim=None):
+            super().__init__(spec, prefix, dtype, device)
+            self.rotary_dim = int(head_dim)
+            j = torch.arange(self.rotary_dim // 2, dtype=torch.float32)
+            self.denominators = (float(spec["stretch"]) * torch.pow(torch.tensor(float(spec["theta"])), 2.0 * j / self.rotary_dim)).to(self.device)
+
+    FEED_FORWARDS.register("toy_routed", RoutedFF)
+    POSITIONS.register("toy_stretched_rope", StretchedRope)
+    try:
+        base = load_config(model_dirs["A"]).to_model_spec()
+        H = base.hidden_size
+        tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+        # the routed part alone against the plain formula
+        ff = RoutedFF(PartSpec("toy_routed", {"hidden_size": H, "expert_size": 48, "experts": 4}), "ff.", tdt, device)
+        g = torch.Generator().manual_seed(3)
+        tensors = {p.name: (torch.randn(p.shape, generator=g) * (p.std or 0.1)).to(device) for p in ff.params()}
+        plain = {k: v.float().cpu() if "router" in k else v.to(tdt).float().cpu() for k, v in tensors.items()}
+        ff.bind({k: (v if "router" in k else v.to(tdt)) for k, v in tensors.items()})
+        h = (torch.randn(23, H, generator=g)).to(tdt)
+        got = ff.forward(h.to(device), None).float().cpu()
+        logits = h.float() @ plain["ff.router.weight"].t()
+        choice, prob = logits.argmax(-1), torch.softmax(logits, -1).max(-1).values
+        assert len(set(choice.tolist())) >= 3, "the test wants several experts in use"
+        ref = torch.zeros(23, H)
+        for t in range(23):
+            e = int(choice[t])
+            gate, up = h[t].float() @ plain[f"ff.experts.{e}.gate.weight"].t(), h[t].float() @ plain[f"ff.experts.{e}.up.weight"].t()
+            act = up * (gate / (1 + torch.exp(-gate)))
+            ref[t] = prob[t] * (act.to(tdt).float() @ plain[f"ff.experts.{e}.down.weight"].t())
+        tol = 1e-5 if dtype == "float32" else 0.02
+        assert (got - ref).abs().max() <= tol * max(1.0, float(ref.abs().max())), f"routed feed-forward: {(got - ref).abs().max()}"
+
+        # a model with both toy parts in its second layer
+        blocks = list(base.blocks)
+        routed = PartSpec("toy_routed", {"hidden_size": H, "expert_size": 48, "experts": 4})
+
+        def with_stretch(stretch):
+            mixer = blocks[1].mixer
+            pos = PartSpec("toy_stretched_rope", {"theta": mixer["position"]["theta"], "stretch": stretch})
+            params = dict(mixer.params)
+            params["position"] = pos
+            return replace(blocks[1], mixer=PartSpec(mixer.kind, params), feed_forward=routed)
+
+        def logits_of(stretch, cuts):
+            spec = replace(base, blocks=(blocks[0], with_stretch(stretch)) + tuple(blocks[2:]))
+            model = DecoderModel.from_random(spec, 5, dtype, device)
+            manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], 16, 16, 2, model.dtype, model.device)
+            runner = ModelRunner(model, manager)
+            toks = random_tokens(50, spec.vocab_size, 9)
+            rc = manager.admit(1)
+            outs, pos = [], 0
+            for n in cuts:
+                manager.extend(rc, pos + n)
+                outs.append(runner.step([StepItem(rc, toks[pos:pos + n], list(range(n)))]).clone())
+                pos += n
+            manager.release(rc)
+            return torch.cat(outs)
+
+        whole = logits_of(2.0, [50])
+        cut = logits_of(2.0, [7, 2, 16, 1, 1, 13, 1, 1, 1, 7])
+        assert torch.isfinite(whole).all()
+        scale = float(whole.abs().max())
+        assert (whole - cut).abs().max() <= (1e-4 if dtype == "float32" else 0.03 * scale)
+        other = logits_of(1.0, [50])
+        # with random weights attention is nearly uniform and positions move the logits little: measurable in float32,
+        # within rounding in bfloat16 (there only: not the same numbers)
+        assert (whole[10:] - other[10:]).abs().max() > (1e-3 if dtype == "float32" else 0.0), "the stretch of the positions must matter"
+    finally:
+        FEED_FORWARDS.unregister("toy_routed")
+        POSITIONS.unregister("toy_stretched_rope")
+
