@@ -62,14 +62,6 @@ __device__ __forceinline__ int tile_key(int tau, int n) {
     return 8 * (n >> 1) + 4 * (s & 1) + 32 * (s >> 1) + 2 * h + (n & 1);
 }
 
-// 2^x by the hardware approximation (about two units in the last place): the probabilities are rounded to
-// bfloat16 right after, and the running sums stay in float
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 template <int DH>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, const bf16* __restrict__ kcache,

@@ -53,28 +53,6 @@ struct __align__(1024) Smem {
     unsigned tmem_base;
 };
 
-__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-// Shared-memory descriptor of a K-major tile of rows x 16 bfloat16 written by TMA with the 32-byte swizzle: 8-row
-// groups are 256 bytes apart.
-__device__ __forceinline__ unsigned long long umma_desc_sw32(const void* tile) {
-    const unsigned addr = smem_u32(tile);
-    unsigned long long d = 0;
-    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
-    d |= (unsigned long long)(256 >> 4) << 32;
-    d |= (unsigned long long)1 << 46;
-    d |= (unsigned long long)6 << 61;
-    return d;
-}
-
-__device__ __forceinline__ float fast_exp2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 template <int DH>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,

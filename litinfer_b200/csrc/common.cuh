@@ -63,6 +63,14 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floa
     return r;
 }
 
+// 2^x by the hardware approximation (about two units in the last place): used where the result is rounded to bfloat16
+// right after (attention probabilities) while the running sums stay in float.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Programmatic dependent launch.  A kernel launched through li_launch_pdl may begin while
 // the kernel before it on the stream is still running; it must not touch memory that kernel
 // writes (or still reads and this one overwrites) before pdl_wait(), which returns once the

@@ -39,13 +39,6 @@ struct __align__(1024) Smem {
     unsigned tmem_base;
 };
 
-// arrive on the barrier at the same offset in the shared memory of the cluster's CTA `rank`
-__device__ __forceinline__ void mbar_arrive_remote(unsigned long long* bar, unsigned rank) {
-    unsigned remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(rank));
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
-}
-
 template <typename Tout, bool kSwiglu>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,

@@ -23,6 +23,10 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // Bounded wait for the phase with the given parity; false if the limit ran out.
 __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
     const unsigned addr = smem_u32(bar);
@@ -64,6 +68,18 @@ __device__ __forceinline__ unsigned long long umma_desc(const void* tile) {
     d |= (unsigned long long)(1024 >> 4) << 32;                 // stride byte offset
     d |= (unsigned long long)1 << 46;                           // descriptor version of this architecture
     d |= (unsigned long long)2 << 61;                           // 128-byte swizzle
+    return d;
+}
+
+// Shared-memory descriptor of a K-major tile of rows x 16 bfloat16 written by TMA with the 32-byte swizzle: 8-row
+// groups are 256 bytes apart.
+__device__ __forceinline__ unsigned long long umma_desc_sw32(const void* tile) {
+    const unsigned addr = smem_u32(tile);
+    unsigned long long d = 0;
+    d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+    d |= (unsigned long long)(256 >> 4) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)6 << 61;
     return d;
 }
 
@@ -112,6 +128,13 @@ __device__ __forceinline__ unsigned cluster_cta_rank() {
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// arrive on the barrier at the same offset in the shared memory of the cluster's CTA `rank`
+__device__ __forceinline__ void mbar_arrive_remote(unsigned long long* bar, unsigned rank) {
+    unsigned remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(bar)), "r"(rank));
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
 }
 
 // A tile load whose bytes are counted on the barrier of the pair's first CTA (the same offset in its shared memory: in
