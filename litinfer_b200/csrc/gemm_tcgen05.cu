@@ -51,7 +51,8 @@ struct Tile {
     static constexpr int kRowsB = kPair ? BN / 2 : BN;
     static constexpr int kBytesA = BM * BK * 2, kBytesB = kRowsB * BK * 2;
     static constexpr int kStages = (kBytesA + kBytesB) <= 32768 ? 6 : ((kBytesA + kBytesB) <= 49152 ? 4 : 3);
-    static constexpr unsigned kCols = (BM / 128) * BN;          // tensor-memory columns: one accumulator per 128 rows
+    static constexpr unsigned kAccCols = (BM / 128) * BN;       // tensor-memory columns: one accumulator per 128 rows
+    static constexpr unsigned kCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;   // allocated: a power of two
 };
 
 template <int BM, int BN, bool kPair = false>
@@ -422,8 +423,16 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     // narrow products (q|k|v, o, down of a long step): pairs of CTAs on 256 x 256 (128 rows each, one accumulator) fill the GPU
     // in one wave without a split of k and its merge (measured at 2,048 rows: down 56 us against 73 us with the split,
     // q|k|v 17 us against 19 us on 256 x 128 tiles)
-    const long long pair_ctas = (long long)((ceil_div(M, 128) + 1) & ~1) * ceil_div(N, 256);
-    if (tile == 5 || (tile == 0 && big_ctas < 120 && g_forced_ksplit == 0 && pair_ctas >= 74 && pair_ctas <= 148))
+    const long long pair_rows = (ceil_div(M, 128) + 1) & ~1;
+    const long long pair_ctas = pair_rows * ceil_div(N, 256), pair_ctas_192 = pair_rows * ceil_div(N, 192);
+    // 192 columns a tile instead of 256 where that fills the waves of 148 CTAs clearly better (N = 1536: 8 column tiles
+    // instead of 6; measured at 2,048 rows: down 52 us against 55 us, o 16 us against 18 us)
+    auto wave_fill = [](long long ctas) { return (double)ctas / (double)(((ctas + 147) / 148) * 148); };
+    const bool narrow = N % 192 == 0 && wave_fill(pair_ctas_192) > 1.1 * wave_fill(pair_ctas);
+    const bool pairs = tile == 0 && big_ctas < 120 && g_forced_ksplit == 0 && pair_ctas >= 74;
+    if (tile == 7 || (pairs && narrow))
+        return launch_tile<128, 192, Tout, kSwiglu, true>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
+    if (tile == 5 || pairs)
         return launch_tile<128, 256, Tout, kSwiglu, true>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
     // half as many of them and a long k (down of about 1,000 rows): the same tiles with k split two or three ways
     // (measured at 1,024 rows: 39 us against 69 us on 256 x 256 tiles with four splits)
@@ -450,12 +459,12 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
 
 int g_forced_tile = 0;
 
-// whether `launch` would take the paired 256 x 256 tiles (one accumulator a CTA) for this shape by itself
+// whether `launch` takes paired tiles (one accumulator a CTA) for this shape by itself
 bool pair_tiles_chosen(int M, int N, int K) {
     const long long big_ctas = (long long)ceil_div(M, 256) * ceil_div(N, 256);
     const long long pair_ctas = (long long)((ceil_div(M, 128) + 1) & ~1) * ceil_div(N, 256);
     (void)K;
-    return g_forced_tile == 0 && g_forced_ksplit == 0 && big_ctas < 120 && pair_ctas >= 74 && pair_ctas <= 148;
+    return g_forced_tile == 0 && g_forced_ksplit == 0 && big_ctas < 120 && pair_ctas >= 74;
 }
 
 }  // namespace
@@ -477,7 +486,7 @@ int li_linear_tcgen05_rope(const void* a, const void* w, const float* bias, void
 
 // 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always, one CTA a tile; 3: 256 x 128 always; 4: pairs of CTAs on
 // 512 x 256 (two accumulators each); 5: pairs of CTAs on 256 x 256 (one accumulator each); 6: the persistent kernel
-// (gemm_tcgen05_persistent.cu).  For tests and measurements.
+// (gemm_tcgen05_persistent.cu); 7: pairs of CTAs on 256 x 192.  For tests and measurements.
 LI_EXPORT void li_tcgen05_force_tile(int tile) { g_forced_tile = tile; }
 
 // 0: splits of k by shape; n > 0: n splits always.  For tests and measurements.

@@ -147,7 +147,7 @@ TC_SHAPES = [(128, 128, 64), (128, 128, 512), (256, 384, 1536), (2048, 2048, 153
              (1000, 389, 96), (64, 1536, 8960), (2048, 1536, 8960), (5, 151936, 1536)]
 
 
-@pytest.fixture(params=[1, 2, 3, 4, 5, 6], ids=["tile128", "tile256", "tile256x128", "tile512pair", "tile256pair", "persistent"])
+@pytest.fixture(params=[1, 2, 3, 4, 5, 6, 7], ids=["tile128", "tile256", "tile256x128", "tile512pair", "tile256pair", "persistent", "tile256x192pair"])
 def forced_tile(request):
     """Every tile size of the tcgen05 kernel, whatever it would choose for the shape itself."""
     lib = K().library()
