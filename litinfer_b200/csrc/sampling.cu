@@ -102,6 +102,46 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const float* __restric
     if (threadIdx.x == 0) out[blockIdx.x] = b.i;
 }
 
+// Few rows of a large vocabulary (decode): one CTA a row would read its 600 KB alone while the rest of the GPU waits.  A row
+// is cut into kChunks pieces; the CTA that finishes a row last (a counter per row) picks the best of the pieces, the
+// first maximum again: pieces are compared in ascending order of their indices.
+constexpr int kChunks = 16;
+constexpr int kChunkRows = 1024;                 // rows the static scratch below holds
+__device__ Best g_chunk_best[kChunkRows * kChunks];
+__device__ unsigned g_chunk_done[kChunkRows];    // zero between launches
+
+__global__ void __launch_bounds__(256) argmax_chunks_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+    __shared__ Best scratch[32];
+    __shared__ int is_last;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const int per = (((V + kChunks - 1) / kChunks) + 3) & ~3;
+    const int lo = chunk * per, hi = min(V, lo + per);
+    Best b{-INFINITY, 0x7fffffff};
+    if (lo < hi) {
+        b = row_argmax(logits + (size_t)row * V + lo, hi - lo, scratch);
+        // a chunk without a finite maximum (all NaN or -inf) must not win with a made-up index
+        if (!(b.v > -INFINITY)) b = Best{-INFINITY, 0x7fffffff};
+        else b.i += lo;
+    }
+    if (threadIdx.x == 0) {
+        g_chunk_best[row * kChunks + chunk] = b;
+        __threadfence();
+        is_last = atomicAdd(&g_chunk_done[row], 1u) == (unsigned)(kChunks - 1);
+    }
+    __syncthreads();
+    if (!is_last || threadIdx.x != 0) return;
+    __threadfence();
+    Best r{-INFINITY, 0x7fffffff};
+    for (int c = 0; c < kChunks; ++c) {
+        const volatile Best* p = &g_chunk_best[row * kChunks + c];
+        r = better(r, Best{p->v, p->i});
+    }
+    out[row] = r.i == 0x7fffffff ? 0 : r.i;      // a row of NaN or -inf
+    g_chunk_done[row] = 0;                       // ready for the next launch on this stream
+}
+
 __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restrict__ logits, const int* __restrict__ params,
                                                           int* __restrict__ out, int V) {
     __shared__ Best scratch[32];
@@ -175,6 +215,10 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const float* __restric
 LI_EXPORT int li_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream) {
     LI_REQUIRE(R >= 0 && V > 0, "argmax: bad sizes R=%d V=%d", R, V);
     if (R == 0) return 0;
+    if (R <= 64 && R <= kChunkRows && V >= 16384) {
+        li_launch_pdl(argmax_chunks_kernel, dim3(kChunks, R), dim3(256), 0, stream, logits, out, V);
+        return li_check_launch("argmax (chunks)");
+    }
     li_launch_pdl(argmax_kernel, dim3(R), dim3(kThreads), 0, stream, logits, out, V);
     return li_check_launch("argmax");
 }

@@ -662,6 +662,21 @@ def test_argmax_first_maximum():
     out = torch.empty(3, dtype=torch.int32, device=dev())
     K().argmax(big, out)
     assert out.tolist() == big.argmax(dim=1).tolist()
+    # few rows of a large vocabulary are cut into pieces: ties across pieces (the first wins), a maximum in the last,
+    # ragged piece, a row without any finite value; twice, since a counter per row stays behind
+    for V in (151936, 16384, 50001):
+        lg = rnd(8, V, seed=13)
+        lg[0, 5] = lg[0, V - 1] = lg[0, V // 2] = 70.0
+        lg[1, V - 1] = 70.0
+        lg[2, V // 16 + 3] = lg[2, V // 16 - 3] = 70.0
+        lg[3, :] = float("-inf")
+        lg[4, V - 7:] = 70.0
+        for _ in range(2):
+            out = torch.full((8,), -1, dtype=torch.int32, device=dev())
+            K().argmax(lg, out)
+            want = lg.argmax(dim=1).tolist()
+            want[0], want[2], want[3], want[4] = 5, V // 16 - 3, 0, V - 7
+            assert out.tolist() == want, f"V={V}: {out.tolist()} vs {want}"
 
 
 def _params(rows):
