@@ -23,6 +23,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import List, Sequence
 
+import numpy as np
 import torch
 
 from .. import kernels as K
@@ -58,17 +59,16 @@ class Sampler:
             K.argmax(logits, out)
             return out
         # rows that are greedy get temperature 0, which the kernel reads as argmax
-        host = torch.empty((R, 6), dtype=torch.int32)
-        f = host.view(torch.float32)
-        for r, (p, idx) in enumerate(zip(params, output_index)):
-            f[r, 0] = 0.0 if p.greedy else float(p.temperature)
-            host[r, 1] = int(p.top_k)
-            f[r, 2] = float(p.top_p)
-            seed = int(p.seed) & 0xFFFF_FFFF_FFFF_FFFF
-            host[r, 3] = _as_i32(seed & 0xFFFF_FFFF)
-            host[r, 4] = _as_i32(seed >> 32)
-            host[r, 5] = int(idx)
-        K.sample(logits, host.to(logits.device), out)
+        packed = np.empty((R, 6), dtype=np.int32)
+        as_float = packed.view(np.float32)
+        as_float[:, 0] = [0.0 if p.greedy else float(p.temperature) for p in params]
+        packed[:, 1] = [min(max(int(p.top_k), -1), 2**31 - 1) for p in params]
+        as_float[:, 2] = [float(p.top_p) for p in params]
+        seeds = np.array([int(p.seed) & 0xFFFF_FFFF_FFFF_FFFF for p in params], dtype=np.uint64)
+        packed[:, 3] = (seeds & np.uint64(0xFFFF_FFFF)).astype(np.uint32).view(np.int32)
+        packed[:, 4] = (seeds >> np.uint64(32)).astype(np.uint32).view(np.int32)
+        packed[:, 5] = [int(i) for i in output_index]
+        K.sample(logits, torch.from_numpy(packed).to(logits.device), out)
         return out
 
 

@@ -708,6 +708,30 @@ def test_sample_matches_reference_and_is_batch_independent():
         assert one.item() == out[r].item()
 
 
+@pytest.mark.parametrize("V", [4097, 20011])
+def test_sample_large_vocabulary_matches_reference(V):
+    # (20,011 tokens also take the path that cuts a row with temperature alone over many CTAs)
+    """Above 4,096 tokens the thresholds come from a radix selection and the rest happens on the gathered candidates in
+    shared memory: top-k alone, top-p alone (peaked: the gathered tokens hold the mass; flat: they do not, and the row
+    is bisected), both, ties at the k-th value, k larger than fits."""
+    g = torch.Generator().manual_seed(V)
+    peaked = (torch.randn(V, generator=g) * 4.0)
+    flat = (torch.randn(V, generator=g) * 0.05)
+    ties = peaked.clone()
+    ties[torch.randperm(V, generator=g)[:300]] = float(peaked.topk(40).values[-1])         # 300 copies of the 40th largest value
+    cases = [(peaked, 0.8, 50, 1.0), (peaked, 1.0, 0, 0.9), (peaked, 0.7, 40, 0.8), (flat, 1.0, 0, 0.9), (flat, 1.0, 64, 0.5),
+             (ties, 1.0, 40, 1.0), (ties, 0.9, 40, 0.7), (peaked, 1.0, 5000, 0.95), (peaked, 1.3, 3, 0.999), (peaked, 0.5, 0, 0.3),
+             (peaked, 0.9, 0, 1.0), (flat, 1.4, 0, 1.0), (peaked, 0.0, 0, 1.0), (flat, 1.0, 1, 0.5)]
+    lg = torch.stack([c[0] for c in cases]).to(dev())
+    for rep in range(2):
+        rows = [(t, k, p, 77 + i, rep * 5 + i) for i, (_, t, k, p) in enumerate(cases)]
+        out = torch.empty(len(cases), dtype=torch.int32, device=dev())
+        K().sample(lg, _params(rows), out)
+        for i, (temp, k, p, seed, idx) in enumerate(rows):
+            tok, kept = R.sample_row(lg[i], temp, k, p, seed, idx)
+            assert out[i].item() == tok, f"case {i} {cases[i][1:]}: {out[i].item()} vs {tok} ({len(kept)} candidates)"
+
+
 def test_sample_stays_in_candidates_and_follows_distribution():
     V = 50
     lg = rnd(1, V, seed=14, scale=1.5)
