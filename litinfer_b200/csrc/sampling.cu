@@ -4,12 +4,16 @@
 // Candidates as LitInfer's sampler keeps them (src/llaisys/models/qwen2.cpp:890-920):
 // z = logits / temperature; the top_k largest if 0 < k < V; softmax over
 // those; the shortest prefix, in descending order, whose cumulative
-// probability reaches top_p if 0 < p < 1.  Instead of sorting, the two
-// thresholds are found by bisection over the order-preserving integer image
-// of a float (32 steps each, every step one pass over the row):
+// probability reaches top_p if 0 < p < 1.  Instead of sorting, two thresholds
+// over the order-preserving integer image of a float decide who stays:
 //   t_k = smallest t with  #{z_i > t} < k                  (the k-th largest value)
 //   t_p = smallest t with  sum_{z_i > t} prob_i < top_p    (a token stays iff the
 //         probability mass of strictly larger candidates is below top_p)
+// t_k comes from radix selection (three passes over the row with a histogram
+// in shared memory); the values at or above it are gathered into shared
+// memory in a fixed order, and t_p and the draw are found there.  Rows whose
+// candidates do not fit (a flat distribution with top_p alone) and small
+// vocabularies take bisection over the whole row, 32 passes a threshold.
 // Equal values stay or go together.  The draw is Gumbel-max over the
 // candidates, argmax(z_i + g_i), g_i = -log(-log(u_i)), with u_i a hash of
 // (seed, index of the output token, i): exact sampling from the candidates'
