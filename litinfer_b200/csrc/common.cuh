@@ -71,6 +71,15 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// up * gate / (1 + exp(-gate)) (src/ops/swiglu/op.cpp:17-23) in float.  For an output that is rounded to 16 bits the
+// exponential and the quotient come from the fast units (errors near 2^-21, far below that rounding): an epilogue in which
+// one warp works through its row alone is bound by the length of this chain of instructions.
+template <typename Tout>
+__device__ __forceinline__ float swiglu_of(float gate, float up) {
+    if constexpr (sizeof(Tout) == 2) return up * __fdividef(gate, 1.0f + fast_exp2(-1.4426950408889634f * gate));
+    else return up * (gate / (1.0f + expf(-gate)));
+}
+
 // Programmatic dependent launch.  A kernel launched through li_launch_pdl may begin while
 // the kernel before it on the stream is still running; it must not touch memory that kernel
 // writes (or still reads and this one overwrites) before pdl_wait(), which returns once the

@@ -131,7 +131,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
         const int j = (int)(i - t * I);
         const float g = to_float(gate_up[t * 2 * I + j]);
         const float u = to_float(gate_up[t * 2 * I + I + j]);
-        out[i] = from_float<T>(u * (g / (1.0f + expf(-g))));
+        out[i] = from_float<T>(swiglu_of<T>(g, u));
     }
 }
 

@@ -20,7 +20,7 @@ __device__ __forceinline__ void gemm_store_piece(int row, int col0, float (&v)[3
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float gate = v[16 * h + i], up = v[16 * h + 8 + i];
-                    a16[8 * h + i] = up * (gate / (1.0f + expf(-gate)));
+                    a16[8 * h + i] = swiglu_of<Tout>(gate, up);
                 }
             if (col0 + 32 <= N && (((uintptr_t)dst) & 15) == 0 && sizeof(Tout) == 2) {
                 uint4* d4 = reinterpret_cast<uint4*>(dst);

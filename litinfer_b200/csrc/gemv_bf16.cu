@@ -147,7 +147,7 @@ __device__ __forceinline__ void store_elements(Get get, const float* __restrict_
                 gate *= rs_sm[tok];
                 up *= rs_sm[tok];
             }
-            if (col < half_n && tok < M) out[(size_t)tok * half_n + col] = from_float<Tout>(up * (gate / (1.0f + expf(-gate))));
+            if (col < half_n && tok < M) out[(size_t)tok * half_n + col] = from_float<Tout>(swiglu_of<Tout>(gate, up));
         }
     }
 }

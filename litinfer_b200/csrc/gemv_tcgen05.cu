@@ -265,7 +265,7 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                         const float up = __shfl_down_sync(0xffffffffu, v[j], 8);
                         if (j < M && (lane & 8) == 0 && row + 8 < N) {
                             const float gate = v[j];
-                            out[(size_t)j * half_n + col] = from_float<Tout>(up * (gate / (1.0f + expf(-gate))));
+                            out[(size_t)j * half_n + col] = from_float<Tout>(swiglu_of<Tout>(gate, up));
                         }
                     }
                 }
