@@ -60,13 +60,13 @@ def _dt(t: torch.Tensor) -> int:
 def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
     if not isinstance(t, torch.Tensor):
         raise KernelError(f"{name}: expected a tensor, got {type(t).__name__}")
-    if t.device.type != "cuda":
+    if not t.is_cuda:
         raise KernelError(f"{name}: the kernels run on CUDA devices only, tensor is on '{t.device}'")
     if not t.is_contiguous():
         raise KernelError(f"{name}: tensor must be contiguous")
     if dtype is not None and t.dtype != dtype:
         raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
-    if shape is not None and tuple(t.shape) != tuple(shape):
+    if shape is not None and t.shape != tuple(shape):
         raise KernelError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
 
 
@@ -74,7 +74,14 @@ def _p(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+# the current stream's handle without building a Stream object (a few hundred launches a step ask for it)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(t: torch.Tensor):
+    if _raw_stream is not None:
+        index = t.device.index
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device() if index is None else index))
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
