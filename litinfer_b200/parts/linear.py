@@ -90,6 +90,7 @@ class GateUpLinear(FusedLinear):
             act = torch.empty((x.shape[0], self.intermediate), dtype=self.dtype, device=x.device)
             K.linear(x, self.weight, None, act, epilogue="swiglu", row_scale=row_scale)
         else:
-            act = torch.empty((x.shape[0], self.intermediate), dtype=self.dtype, device=x.device)
-            K.swiglu(self(x), act)
+            both = self(x)                                 # x may be deferred: the product multiplies its factor out
+            act = torch.empty((both.shape[0], self.intermediate), dtype=self.dtype, device=both.device)
+            K.swiglu(both, act)
         return act

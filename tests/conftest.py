@@ -64,6 +64,26 @@ TINY_C = dict(
 TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
 
 
+def _qwen2(layers, hidden, heads, kv_heads, head_dim, intermediate, vocab, theta=10000.0, eps=1e-6, tie=False, window=None,
+           max_window_layers=0):
+    cfg = dict(architectures=["Qwen2ForCausalLM"], torch_dtype="float32", num_hidden_layers=layers, hidden_size=hidden,
+               num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=head_dim, intermediate_size=intermediate,
+               vocab_size=vocab, rope_theta=theta, rms_norm_eps=eps, tie_word_embeddings=tie, max_position_embeddings=512,
+               eos_token_id=None, use_sliding_window=window is not None)
+    if window is not None:
+        cfg.update(sliding_window=window, max_window_layers=max_window_layers)
+    return cfg
+
+
+# Still small, but with the head sizes of real checkpoints (the engine takes other kernels for them), and one whose widths
+# are no multiple of 8.
+MID = {
+    "head128": _qwen2(2, 256, 2, 1, 128, 512, 1000),
+    "head64_window": _qwen2(2, 512, 8, 2, 64, 1376, 3001, theta=1e6, eps=1e-5, window=100, max_window_layers=1),
+    "odd_widths": _qwen2(1, 100, 5, 1, 20, 250, 333),
+}
+
+
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
     """Model folders of the tiny configurations with random float32 weights."""

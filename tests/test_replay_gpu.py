@@ -12,7 +12,7 @@ from __future__ import annotations
 import pytest
 import torch
 
-from conftest import TINY
+from conftest import MID, TINY
 from helpers import Trace, check_logits, plain_logits, random_tokens, run_trace, stack
 
 pytestmark = pytest.mark.gpu
@@ -25,10 +25,10 @@ def round64(n):
     return -(-n // 64) * 64
 
 
-def build_trace(vocab: int, max_pos: int):
+def build_trace(vocab: int, max_pos: int, main_len: int = 100, portions=PORTIONS, mix_portions=MIX_PORTIONS, mix_lens=None):
     tr = Trace()
     seqs = {}
-    main_len = min(100, max_pos - 4)
+    main_len = min(main_len, max_pos - 4)
     main = random_tokens(main_len, vocab, 11)
     # whole
     seqs["whole"] = main
@@ -42,7 +42,7 @@ def build_trace(vocab: int, max_pos: int):
     seqs["cut"] = main
     pos, i = 0, 0
     while pos < main_len:
-        n = min(PORTIONS[i % len(PORTIONS)], main_len - pos)
+        n = min(portions[i % len(portions)], main_len - pos)
         last = pos + n == main_len
         tr.step([("cut", main[pos:pos + n], True)], end=["cut"] if last else [])
         pos += n
@@ -53,7 +53,7 @@ def build_trace(vocab: int, max_pos: int):
         tr.step([(f"first{n}", seqs[f"first{n}"], True)], end=[f"first{n}"])
     need = round64(main_len)
     # mixed: up to four live requests
-    lens = [main_len, 60, min(90, max_pos - 2), 40, 75, 50, 33]
+    lens = [main_len] + list(mix_lens or [60, min(90, max_pos - 2), 40, 75, 50, 33])
     queue = [(f"mix{j}", main if j == 0 else random_tokens(n, vocab, 40 + j)) for j, n in enumerate(lens)]
     for rid, toks in queue:
         seqs[rid] = toks
@@ -70,7 +70,7 @@ def build_trace(vocab: int, max_pos: int):
             if (step_no + sl) % 5 == 4 and fed > 0:
                 continue                                   # left out of this step, goes on later
             if fed < int(0.6 * len(toks)):
-                n = min(MIX_PORTIONS[(step_no + sl) % len(MIX_PORTIONS)], len(toks) - fed)
+                n = min(mix_portions[(step_no + sl) % len(mix_portions)], len(toks) - fed)
             else:
                 n = 1
             entries.append((rid, toks[fed:fed + n], True))
@@ -107,6 +107,34 @@ def test_replay_all_cuts(name, dtype, model_dirs, tmp_path):
         other = stack(got[rid])
         if dtype == "float32":
             assert torch.equal(whole, other), f"float32: '{rid}' differs from 'whole' by {(whole - other).abs().max():.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(MID))
+def test_replay_other_sizes(name, dtype, tmp_path):
+    """Sizes at which the engine takes other kernels than at the tiny ones: head sizes of 128 and 64 with portions of 64
+    tokens and more (tensor-core attention and products, rotary encoding in the product's epilogue), a window of 100 keys,
+    and widths that are no multiple of 8 (no fused activation, no 16-byte loads)."""
+    from litinfer_b200.weights import write_model_folder
+
+    cfg = MID[name]
+    vocab = cfg["vocab_size"]
+    write_model_folder(tmp_path / "model", dict(cfg), seed=4321 + len(name), store_dtype="float32")
+    tr, seqs, need = build_trace(vocab, cfg["max_position_embeddings"], main_len=300, portions=[70, 2, 130, 5, 64, 17, 3, 9, 66],
+                                 mix_portions=[65, 2, 100, 9, 33, 128, 2, 71], mix_lens=[150, 210, 90, 170, 120])
+    got = run_trace(tmp_path / "model", dtype, tr, tmp_path / "out", need, vocab)
+    refs = {}
+    for rid, toks in seqs.items():
+        key = tuple(toks)
+        if key not in refs:
+            refs[key] = plain_logits(tmp_path / "model", toks, dtype)
+        lg = stack(got[rid])
+        assert lg.shape[0] == len(toks), f"{rid}: {lg.shape[0]} rows for {len(toks)} tokens"
+        check_logits(lg, refs[key], dtype, f"config {name} {dtype} request {rid}")
+    if dtype == "float32":
+        whole = stack(got["whole"])
+        for rid in ("tail", "cut", "mix0"):
+            assert torch.equal(whole, stack(got[rid])), f"float32: '{rid}' differs from 'whole'"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
