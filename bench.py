@@ -299,6 +299,28 @@ def time_e2e(model, cfg, batch, prompt_len, new_tokens, steps):
     return dict(value=produced / dt, steps=n, h2d=h2d, d2h=4 * batch, run_ahead=True)
 
 
+def time_first_token(model, cfg, prompt_len=16, repeats=7):
+    """Milliseconds from ``Qwen2.generate(prompt, 1)`` with a short prompt to its token on the host: LitInfer's own
+    headline figure (TTFT of prompts of 10-17 tokens, README.md:69-76, scripts/benchmark_cpu.py:202-253)."""
+    import torch
+
+    from litinfer_b200 import Qwen2
+
+    front = Qwen2(None, model=model, max_num_seqs=1, num_pages=16)
+    g = torch.Generator().manual_seed(5)
+    times = []
+    for i in range(repeats + 3):
+        prompt = torch.randint(0, cfg["vocab_size"], (prompt_len,), generator=g).tolist()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        out = front.generate(prompt, max_new_tokens=1)
+        dt = time.perf_counter() - t0
+        assert len(out) == 1
+        if i >= 3:
+            times.append(dt * 1e3)
+    return statistics.median(times)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -383,6 +405,7 @@ def main() -> int:
     if not args.skip_points:
         for b in (1, 64):
             points[f"decode_b{b}"] = round(time_decode(model, b, args.context, min(args.steps, 64), warmup)["tok_s"], 1)
+        points["first_token_ms_prompt16"] = round(time_first_token(model, cfg), 3)
     e2e = time_e2e(model, cfg, args.batch, args.context, 256, args.steps)
 
     line = {

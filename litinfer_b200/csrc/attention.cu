@@ -15,7 +15,7 @@ int li_attention_generic(const void* qkv, void* out, const void* kcache, const v
                          int page_size, int num_pages, float scale, int window, cudaStream_t stream);
 bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
-                        const int* ctx_lens, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window,
+                        const int* ctx_lens, const int* old_lens, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window,
                         int max_ctx_len, cudaStream_t stream);
 bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
@@ -40,12 +40,12 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
                                  const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens,
                                  const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
                                  int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
-                                 cudaStream_t stream) {
+                                 const int* old_lens, cudaStream_t stream) {
     if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
     if (T == 0) return 0;
     if (dtype == LI_BF16) {
         if (max_q_len == 1 && T == S && li_attention_decode_accepts(nh, nkv, dh, page_size))
-            return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, S, nh, nkv, dh, page_size,
+            return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, S, nh, nkv, dh, page_size,
                                        num_pages, scale, window, max_ctx_len, stream);
         if (max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size))
             return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
@@ -58,12 +58,16 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
                                 page_size, num_pages, scale, window, stream);
 }
 
+// old_lens (may be null): how many keys of each sequence were in the cache before this step.  Null means all but the
+// last one, which is so when every sequence of the step is a request of its own.  The decode kernel may read those
+// keys while the kernel that writes the step's keys is still running.
+//
 // Force one implementation, for tests of each kernel alone: 0 general, 1 decode, 2 prefill (mma.sync), 3 prefill (tcgen05).
 LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, const void* kcache, const void* vcache, int dtype,
                                       const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens,
                                       const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
                                       int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
-                                      cudaStream_t stream) {
+                                      const int* old_lens, cudaStream_t stream) {
     if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
     if (T == 0) return 0;
     if (which == 0)
@@ -73,7 +77,7 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
     if (which == 1) {
         LI_REQUIRE(max_q_len == 1 && T == S, "attention: the decode kernel takes one token per sequence");
         LI_REQUIRE(li_attention_decode_accepts(nh, nkv, dh, page_size), "attention: the decode kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
-        return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, S, nh, nkv, dh, page_size, num_pages,
+        return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, S, nh, nkv, dh, page_size, num_pages,
                                    scale, window, max_ctx_len, stream);
     }
     if (which == 2) {

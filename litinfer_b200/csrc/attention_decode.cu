@@ -102,8 +102,8 @@ template <int DH, int KB>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
-                        float* __restrict__ part, unsigned* __restrict__ counters, bf16* __restrict__ out, int nh, int nkv,
-                        int page_size, int num_pages, float scale, int window, int nsplit) {
+                        const int* __restrict__ old_lens, float* __restrict__ part, unsigned* __restrict__ counters,
+                        bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages, float scale, int window, int nsplit) {
     extern __shared__ float sm[];
     __shared__ int is_last;
     pdl_launch_dependents();
@@ -124,13 +124,16 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     const int* bt = block_table + (size_t)s * max_blocks;
     const int my_key0 = k_begin + warp * KB;
     const bool my_block = my_key0 < k_end && my_key0 + KB > lo;           // warp-uniform
-    // The kernel before this one (the q|k|v product) writes the keys and values of position p only.  A warp whose block
-    // does not hold p asks for its keys and values now, while that kernel is still running, and waits afterwards.
+    // The kernel before this one (the q|k|v product) writes the keys and values of the step's tokens: of position p
+    // only, or, when several sequences of the step are tokens of one request, of the positions from old_lens[s] on.  A
+    // warp whose block lies below them asks for its keys and values now, while that kernel is still running, and
+    // waits afterwards.
+    const int old = old_lens ? old_lens[s] : p;
     [[maybe_unused]] KFrag32<DH> kf_early;
     [[maybe_unused]] VFrag32<DH> vf_early;
     bool early = false;
     if constexpr (KB == 32) {
-        early = my_block && !(p >= my_key0 && p < my_key0 + KB);
+        early = my_block && my_key0 + KB <= old;
         if (early) block_load32<DH>(kf_early, vf_early, kcache, vcache, bt, my_key0, k_end - 1, kvh, nkv, page_size, num_pages, g, t);
     }
     pdl_wait();
@@ -377,8 +380,8 @@ int ensure_workspace(size_t floats, float** buf, unsigned** counters) {
 
 template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
-           const int* ctx_lens, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window, int max_ctx_len,
-           cudaStream_t stream) {
+           const int* ctx_lens, const int* old_lens, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window,
+           int max_ctx_len, cudaStream_t stream) {
     const int G = nh / nkv;
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     if ((long long)S * nkv >= kWholeFrom) {
@@ -417,7 +420,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     dim3 grid(nsplit, nkv, S);
     li_launch_pdl(decode_attention_kernel<DH, KBS>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache, (const bf16*)vcache,
-                                                                      block_table, max_blocks, ctx_lens, part, counters, (bf16*)out,
+                                                                      block_table, max_blocks, ctx_lens, old_lens, part, counters, (bf16*)out,
                                                                       nh, nkv, page_size, num_pages, scale, window, nsplit);
     return li_check_launch("attention (decode)");
 }
@@ -430,11 +433,11 @@ bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size) {
 }
 
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
-                        const int* ctx_lens, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window,
+                        const int* ctx_lens, const int* old_lens, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window,
                         int max_ctx_len, cudaStream_t stream) {
 #define LI_CASE(D)                                                                                                             \
     case D:                                                                                                                    \
-        return launch<D>(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, S, nh, nkv, page_size, num_pages, scale, \
+        return launch<D>(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, S, nh, nkv, page_size, num_pages, scale, \
                          window, max_ctx_len, stream);
     switch (dh) {
         LI_CASE(16) LI_CASE(32) LI_CASE(48) LI_CASE(64) LI_CASE(80) LI_CASE(96) LI_CASE(112) LI_CASE(128) LI_CASE(256)

@@ -8,8 +8,8 @@ copy; LitInfer rebuilds and uploads its block table per layer
 (src/llaisys/models/qwen2.cpp:993-1007).
 
 Layout of the packed buffer (all int32): token_ids[T] | positions[T] |
-seq_of_token[T] | q_start[S+1] | ctx_lens[S] | state_slots[S] | logit_rows[R] |
-per group: slot_mapping[T] | block_table[S * max_blocks].  With ``pad_seqs``
+seq_of_token[T] | q_start[S+1] | ctx_lens[S] | old_lens[S] | state_slots[S] |
+logit_rows[R] | per group: slot_mapping[T] | block_table[S * max_blocks].  With ``pad_seqs``
 the batch is padded to that many one-token items that write to the sink page
 and whose results nobody reads (a captured decode step has a fixed size).
 """
@@ -59,6 +59,9 @@ class StepContext:
     host_q_start: List[int] = field(default_factory=list)
     host_ctx_lens: List[int] = field(default_factory=list)
     host_state_slots: List[int] = field(default_factory=list)
+    # [S] int32: how many keys of each sequence were in the cache before this step (a sequence's own tokens of this step
+    # come after them; where a step's sequences are the tokens of one request, so do that request's earlier tokens)
+    old_lens: Optional[torch.Tensor] = None
     # what parts make once per step and share between the layers (keyed by the part), e.g. a table of rotation angles
     scratch: dict = field(default_factory=dict)
 
@@ -70,12 +73,45 @@ def _round_up(x: int, m: int) -> int:
     return -(-x // m) * m
 
 
+class _TokenOf:
+    """One token of an item, seen as a sequence of its own: the request's cache as far as this token."""
+
+    __slots__ = ("request_id", "length", "old_length", "slot", "tables")
+
+    def __init__(self, rc, offset: int) -> None:
+        self.request_id = rc.request_id
+        self.length = rc.length + offset
+        self.old_length = rc.length
+        self.slot = rc.slot
+        self.tables = rc.tables
+
+
+def split_into_tokens(items: Sequence[StepItem]) -> List[StepItem]:
+    """Every token of every item as an item of one token that wants its logits.  A portion of a prompt is the same work
+    as that many decoded tokens whose contexts end one after the other: each token's keys and values are in the cache
+    before any attention of the step runs.  Only for mixers without state of their own per request."""
+    seen = set()
+    out = []
+    for it in items:
+        if it.cache.request_id in seen:
+            raise ValueError(f"request {it.cache.request_id} appears twice in one step")
+        seen.add(it.cache.request_id)
+        if len(it.tokens) == 0:
+            raise ValueError("an item without tokens")
+        for w in it.want:
+            if not 0 <= w < len(it.tokens):
+                raise IndexError(f"request {it.cache.request_id}: wanted place {w} is outside its {len(it.tokens)} tokens")
+        out.extend(StepItem(_TokenOf(it.cache, j), (t,), (0,)) for j, t in enumerate(it.tokens))
+    return out
+
+
 def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int, pad_seqs: int = 0,
-              max_blocks: Optional[int] = None):
+              max_blocks: Optional[int] = None, tokens_of_one_request: bool = False):
     """Host side: validate the items and fill the packed int32 array.
 
     Returns (array, layout) where layout maps field name -> (offset, length) and
     carries the scalar sizes.  Pages for all tokens must already be allocated.
+    ``tokens_of_one_request``: the items come from :func:`split_into_tokens`, several may belong to one request.
     """
     S_real = len(items)
     if S_real == 0:
@@ -89,6 +125,7 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
     q_start = np.zeros(S + 1, dtype=np.int32)
     np.cumsum(q_lens, out=q_start[1:])
     ctx = np.empty(S, dtype=np.int32)
+    old = np.zeros(S, dtype=np.int32)
     slots = np.empty(S, dtype=np.int32)
     token_ids = np.zeros(T, dtype=np.int32)
     positions = np.zeros(T, dtype=np.int32)
@@ -97,7 +134,7 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
     seen = set()
     for s, it in enumerate(items):
         rc = it.cache
-        if rc.request_id in seen:
+        if rc.request_id in seen and not tokens_of_one_request:
             raise ValueError(f"request {rc.request_id} appears twice in one step")
         seen.add(rc.request_id)
         n, lo = q_lens[s], int(q_start[s])
@@ -108,6 +145,7 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
         positions[lo:lo + n] = np.arange(rc.length, rc.length + n)
         seq_of[lo:lo + n] = s
         ctx[s] = rc.length + n
+        old[s] = getattr(rc, "old_length", rc.length)
         slots[s] = rc.slot
         for w in it.want:
             if not 0 <= w < n:
@@ -132,7 +170,7 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
         off += _round_up(max(n, 1), 4)       # 16-byte aligned starts
 
     for name, n in (("token_ids", T), ("positions", T), ("seq_of_token", T), ("q_start", S + 1),
-                    ("ctx_lens", S), ("state_slots", S), ("logit_rows", R)):
+                    ("ctx_lens", S), ("old_lens", S), ("state_slots", S), ("logit_rows", R)):
         place(name, n)
     for gid in range(G):
         place(f"slot_mapping{gid}", T)
@@ -148,6 +186,7 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
     put("seq_of_token", seq_of)
     put("q_start", q_start)
     put("ctx_lens", ctx)
+    put("old_lens", old)
     put("state_slots", slots)
     put("logit_rows", np.asarray(rows, dtype=np.int32))
     trash = manager.trash_page
@@ -189,7 +228,7 @@ def context_from(device_buf: torch.Tensor, layout, page_size: int) -> StepContex
     return StepContext(
         num_tokens=layout["T"], num_seqs=S, num_logit_rows=layout["R"],
         token_ids=view("token_ids"), positions=view("positions"), seq_of_token=view("seq_of_token"),
-        q_start=view("q_start"), ctx_lens=view("ctx_lens"), state_slots=view("state_slots"),
+        q_start=view("q_start"), ctx_lens=view("ctx_lens"), state_slots=view("state_slots"), old_lens=view("old_lens"),
         logit_rows=view("logit_rows"), groups=groups,
         max_q_len=layout["max_q_len"], max_ctx_len=layout["max_ctx_len"],
         host_q_start=layout["q_start"], host_ctx_lens=layout["ctx_lens"], host_state_slots=layout["state_slots"])

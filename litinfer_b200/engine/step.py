@@ -22,7 +22,8 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..models.decoder import DecoderModel
-from .batch import StepContext, StepItem, context_from, pack_step
+from ..parts.base import FixedState
+from .batch import StepContext, StepItem, context_from, pack_step, split_into_tokens
 
 
 class _DecodeGraph:
@@ -41,6 +42,11 @@ class _DecodeGraph:
 class ModelRunner:
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
     GRAPH_CONTEXT_CAP = 8192            # a captured step covers contexts up to this; longer ones are launched plainly
+    # A step of few tokens that holds portions of prompts runs through the captured decode step too, every token an item
+    # of its own (batch.split_into_tokens): launched plainly, a step costs the host about 250 launches (3 ms), more than
+    # the device needs for it.  Every token then reads its context by itself, so the contexts together are bounded.
+    SPLIT_TOKENS = 64
+    SPLIT_CONTEXT_SUM = 32768
 
     def __init__(self, model: DecoderModel, manager: CacheManager, use_graphs: bool = False,
                  max_context: Optional[int] = None) -> None:
@@ -52,6 +58,8 @@ class ModelRunner:
         # are sized for it), so that length is capped; steps with a longer context run without a graph
         self.max_context = min(int(max_context or model.spec.max_position_embeddings), self.GRAPH_CONTEXT_CAP)
         self._graphs: Dict[int, _DecodeGraph] = {}
+        # a mixer with state of its own takes a request's tokens in order: its portions are never split
+        self._may_split = not any(isinstance(r, FixedState) for r in model.cache_requirements())
         self._pinned: Optional[torch.Tensor] = None
         self._copy_done = None
         self.steps_run = 0
@@ -97,6 +105,12 @@ class ModelRunner:
         fits = decode_only and max(it.cache.length for it in items) + 1 <= self.max_context
         if self.use_graphs and fits and len(items) <= self.GRAPH_BUCKETS[-1]:
             logits = self._step_graph(items, token_source)
+        elif self.use_graphs and not decode_only and self._splits(items):
+            rows, base = [], 0
+            for it in items:
+                rows.extend(base + int(w) for w in it.want)
+                base += len(it.tokens)
+            logits = self._step_graph(split_into_tokens(items), None, rows)
         else:
             buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size)
             ctx = context_from(self._upload(buf), layout, self.manager.page_size)
@@ -115,23 +129,37 @@ class ModelRunner:
                 return b
         raise ValueError(n)
 
-    def _step_graph(self, items: List[StepItem], token_source: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Decode-only step through a captured graph.  Every item wants its one token's
-        logits in the captured layout; rows of items that want nothing are dropped after."""
+    def _splits(self, items: Sequence[StepItem]) -> bool:
+        """Whether a step with portions of prompts is run as single tokens through the captured decode step."""
+        if not self._may_split or sum(len(it.tokens) for it in items) > self.SPLIT_TOKENS:
+            return False
+        if max(it.cache.length + len(it.tokens) for it in items) > self.max_context:
+            return False
+        # token j of a portion reads length + j + 1 keys
+        reads = sum(len(it.tokens) * it.cache.length + len(it.tokens) * (len(it.tokens) + 1) // 2 for it in items)
+        return reads <= self.SPLIT_CONTEXT_SUM
+
+    def _step_graph(self, items: List[StepItem], token_source: Optional[torch.Tensor] = None,
+                    rows: Optional[List[int]] = None) -> torch.Tensor:
+        """A step of single tokens through a captured graph.  Every item gets its token's logits in the captured
+        layout; rows that nobody wants are dropped after.  ``rows``: the items are the tokens of a step with portions
+        of prompts (split_into_tokens) and these are the wanted places among them, in the order of the answer."""
         B = self._bucket(len(items))
         max_blocks = -(-self.max_context // self.manager.page_size)
+        split = rows is not None
         wanted = [bool(len(it.want)) for it in items]
         g = self._graphs.get(B)
-        buf = self._advance(g, items) if g is not None else None
+        buf = self._advance(g, items) if g is not None and not split else None
         if buf is None:
             full = [StepItem(it.cache, it.tokens, (0,)) for it in items]
-            buf, layout = pack_step(full, self.manager, self.model.spec.vocab_size, pad_seqs=B, max_blocks=max_blocks)
+            buf, layout = pack_step(full, self.manager, self.model.spec.vocab_size, pad_seqs=B, max_blocks=max_blocks,
+                                    tokens_of_one_request=split)
             if g is None:
                 g = self._capture(B, max_blocks, buf, layout)
             if layout["fields"] != g.layout["fields"]:
                 raise RuntimeError("decode graph: metadata layout changed between capture and replay")
             g.last_buf = buf
-        g.last_key = tuple(it.cache.request_id for it in items)
+        g.last_key = None if split else tuple(it.cache.request_id for it in items)
         g.last_lengths = [it.cache.length for it in items]
         self._upload(buf, g.meta_buf)
         if token_source is not None:
@@ -139,8 +167,9 @@ class ModelRunner:
             g.meta_buf[o_tok:o_tok + len(items)].copy_(token_source)
         g.graph.replay()
         self.graph_replays += 1
-        rows = [i for i, w in enumerate(wanted) if w]
-        if len(rows) == len(items) == B:
+        if rows is None:
+            rows = [i for i, w in enumerate(wanted) if w]
+        if rows == list(range(B)):
             return g.logits
         return g.logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else g.logits[:0]
 
@@ -159,7 +188,7 @@ class ModelRunner:
         page = mgr.page_size
         buf, f = g.last_buf, g.layout["fields"]
         mb = g.layout["max_blocks"]
-        o_tok, o_pos, o_ctx = f["token_ids"][0], f["positions"][0], f["ctx_lens"][0]
+        o_tok, o_pos, o_ctx, o_old = f["token_ids"][0], f["positions"][0], f["ctx_lens"][0], f["old_lens"][0]
         for i, it in enumerate(items):
             rc = it.cache
             if rc.length != g.last_lengths[i] + 1:
@@ -173,6 +202,7 @@ class ModelRunner:
             buf[o_tok + i] = tok
             buf[o_pos + i] = pos
             buf[o_ctx + i] = pos + 1
+            buf[o_old + i] = pos
             for gid in range(len(mgr.groups)):
                 table = rc.tables[gid]
                 if len(table) <= pos // page:

@@ -336,14 +336,17 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                     block_table: torch.Tensor, q_start: torch.Tensor, ctx_lens: torch.Tensor,
                     seq_of_token: torch.Tensor, positions: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-                    max_q_len: int, max_ctx_len: int, implementation: Optional[str] = None) -> None:
+                    max_q_len: int, max_ctx_len: int, implementation: Optional[str] = None,
+                    old_lens: Optional[torch.Tensor] = None) -> None:
     """Causal grouped-query attention of the step's tokens over the paged cache.
 
     Queries are the first ``num_heads * head_dim`` columns of ``qkv`` (already
     rotated).  The token at position p of sequence s sees the cached keys
     ``max(0, p - window + 1) .. p`` of s, found through ``block_table[s]``.
     ``implementation`` (``general``, ``decode``, ``prefill``, ``prefill_tcgen05``) forces one kernel, for
-    tests and measurements; it is an error if that kernel refuses the sizes."""
+    tests and measurements; it is an error if that kernel refuses the sizes.
+    ``old_lens`` (int32 ``[S]``): how many keys of each sequence were in the cache before this step; needed when
+    several sequences of the step are tokens of one request (None: all but each sequence's last key)."""
     T = qkv.shape[0]
     S = ctx_lens.shape[0]
     _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
@@ -362,10 +365,12 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
     if block_table.shape[1] * page_size < max_ctx_len:
         raise KernelError(f"block table of {block_table.shape[1]} pages cannot cover a context of {max_ctx_len}")
+    if old_lens is not None:
+        _need(old_lens, "old_lens", torch.int32, (S,))
     args = (_p(qkv), _p(out), _p(k_cache), _p(v_cache), _i(_dt(qkv)), _p(block_table), _i(block_table.shape[1]),
             _p(q_start), _p(ctx_lens), _p(seq_of_token), _p(positions), _i(T), _i(S),
             _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _f(scale),
-            _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _stream(out))
+            _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _p(old_lens), _stream(out))
     if implementation is None:
         _check(library().li_paged_attention(*args), "paged_attention")
     else:

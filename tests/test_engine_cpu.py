@@ -150,3 +150,48 @@ def test_toy_routed_feed_forward_and_positions_on_cpu_references(model_dirs, cpu
 
     run_toy_feed_forward_and_positions(model_dirs, "cpu", "float32")
 
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_portions_as_single_tokens_are_the_same_step(name, model_dirs, cpu_kernels):
+    """A step with portions of prompts, packed with every token as an item of its own (as the captured decode step
+    takes it), asks for the same work: same logits at the wanted places, in the order of the items and their wants."""
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.engine import ModelRunner, StepItem
+    from litinfer_b200.engine.batch import context_from, pack_step, split_into_tokens
+    from litinfer_b200.models import DecoderModel
+
+    cfg = TINY[name]
+    vocab = cfg["vocab_size"]
+    model = DecoderModel.from_dir(model_dirs[name], "float32", "cpu")
+    spec = model.spec
+    manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], 24, 16, 4, model.dtype, model.device)
+    runner = ModelRunner(model, manager)
+    a, b, c = random_tokens(60, vocab, 1), random_tokens(30, vocab, 2), random_tokens(9, vocab, 3)
+    ra, rb, rc = manager.admit(1), manager.admit(2), manager.admit(3)
+    manager.extend(ra, 41)
+    manager.extend(rb, 29)
+    runner.step([StepItem(ra, a[:41], ()), StepItem(rb, b[:29], ())])
+    # a: a portion over a page's edge, far enough for the window of configuration B; b: one token; c: a whole short prompt
+    manager.extend(ra, 60)
+    manager.extend(rb, 30)
+    manager.extend(rc, 9)
+    items = [StepItem(ra, a[41:], (18, 0, 7)), StepItem(rb, b[29:], (0,)), StepItem(rc, c, (8,))]
+    buf, layout = pack_step(items, manager, vocab)
+    whole = model.forward(context_from(torch.from_numpy(buf), layout, manager.page_size), manager.entries)
+    singles = split_into_tokens(items)
+    assert [len(it.tokens) for it in singles] == [1] * 29
+    buf, layout = pack_step(singles, manager, vocab, pad_seqs=32, tokens_of_one_request=True)
+    assert layout["S"] == 32 and layout["max_q_len"] == 1
+    f = layout["fields"]
+    old = buf[f["old_lens"][0]:f["old_lens"][0] + 29].tolist()
+    assert old == [41] * 19 + [29] + [0] * 9                      # the keys that were there before the step
+    ctx_lens = buf[f["ctx_lens"][0]:f["ctx_lens"][0] + 29].tolist()
+    assert ctx_lens == list(range(42, 61)) + [30] + list(range(1, 10))
+    split = model.forward(context_from(torch.from_numpy(buf), layout, manager.page_size), manager.entries)
+    rows = [18, 0, 7, 19, 20 + 8]
+    assert torch.allclose(split[rows], whole, atol=1e-6, rtol=0)
+    with pytest.raises(ValueError):
+        pack_step(singles, manager, vocab)                        # one request twice, unless said so
+    with pytest.raises(IndexError):
+        split_into_tokens([StepItem(rc, c, (9,))])

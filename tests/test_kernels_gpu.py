@@ -450,7 +450,7 @@ def make_attention_case(q_lens, ctx_lens, nh, nkv, dh, page, dtype, seed=0, extr
                 ctx_lens=list(ctx_lens), q_lens=list(q_lens), nh=nh, nkv=nkv, dh=dh, dtype=dtype)
 
 
-def run_attention_case(c, window, implementation=None):
+def run_attention_case(c, window, implementation=None, old_lens=None):
     d = dev()
     page, nkv, dh = c["page"], c["nkv"], c["dh"]
     kc = torch.zeros(c["pages"], nkv, page, dh, dtype=c["dtype"])
@@ -469,7 +469,8 @@ def run_attention_case(c, window, implementation=None):
     scale = 1.0 / math.sqrt(dh)
     tail = (c["nh"], nkv, dh, scale, window, max(c["q_lens"]), max(c["ctx_lens"]))
     K().paged_attention(args["qkv"], out, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
-                        args["seq_of_token"], args["positions"], *tail, implementation=implementation)
+                        args["seq_of_token"], args["positions"], *tail, implementation=implementation,
+                        old_lens=None if old_lens is None else torch.tensor(old_lens, dtype=torch.int32, device=d))
     R.paged_attention(args["qkv"], ref, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
                       args["seq_of_token"], args["positions"], *tail)
     return out, ref
@@ -521,6 +522,25 @@ def test_attention_decode_kernel_alone(heads, page):
               pos=[ctx_lens[4] - 1])
     out_one, _ = run_attention_case(c1, None, implementation="decode")
     assert torch.equal(out_one[0], out_all[4])
+
+
+@pytest.mark.parametrize("heads", [(4, 2, 16), (12, 2, 128)])
+def test_attention_decode_kernel_tokens_of_one_request(heads):
+    """A portion of a prompt as single tokens: sequences that share one block table and end one key after the other,
+    with the count of keys that were cached before the step (old_lens) given."""
+    nh, nkv, dh = heads
+    first, n = 283, 40                                   # keys before the portion, tokens of the portion
+    c = make_attention_case([1] * n, [first + n] * n, nh, nkv, dh, 16, torch.bfloat16, seed=7)
+    c["bt"] = c["bt"][:1].repeat(n, 1)
+    c["keys"] = [c["keys"][0]] * n
+    c["vals"] = [c["vals"][0]] * n
+    c["ctx_lens"] = [first + j + 1 for j in range(n)]
+    c["pos"] = [first + j for j in range(n)]
+    for window in (None, 100):
+        out, ref = run_attention_case(c, window, implementation="decode", old_lens=[first] * n)
+        close(out, ref, torch.bfloat16, f"decode kernel, tokens of one request, heads={heads} window={window}")
+        again, _ = run_attention_case(c, window, implementation="decode")
+        assert torch.equal(out, again)
 
 
 @pytest.mark.parametrize("heads", [(4, 2, 16), (3, 1, 32), (6, 2, 48), (12, 2, 128), (8, 8, 64), (14, 2, 80), (28, 4, 128)])
