@@ -356,7 +356,8 @@ int ensure_workspace(size_t floats, float** buf, unsigned** counters) {
     LI_REQUIRE(dev >= 0 && dev < 16, "attention (decode): device index %d out of range", dev);
     Workspace& w = g_ws[dev];
     if (w.floats < floats) {
-        // grows on demand; the first call of a given size must come before stream capture
+        // grows on demand; the first call of a given size must come before stream capture.  The buffer that was
+        // outgrown is kept until the process ends: a captured graph may still hold its address.
         size_t want = floats < (8u << 20) ? (8u << 20) : floats + floats / 2;
         float* nb = nullptr;
         e = cudaMalloc(&nb, want * sizeof(float));
@@ -364,7 +365,6 @@ int ensure_workspace(size_t floats, float** buf, unsigned** counters) {
             return li_fail("attention (decode): cannot allocate %zu bytes of workspace: %s (a first call of this size inside a stream capture cannot allocate)",
                            want * sizeof(float), cudaGetErrorString(e));
         }
-        if (w.buf) cudaFree(w.buf);
         w.buf = nb;
         w.floats = want;
     }

@@ -50,7 +50,7 @@ template <int BM, int BN, bool kPair = false>
 struct Tile {
     static constexpr int kRowsB = kPair ? BN / 2 : BN;
     static constexpr int kBytesA = BM * BK * 2, kBytesB = kRowsB * BK * 2;
-    static constexpr int kStages = (kBytesA + kBytesB) <= 32768 ? 6 : ((kBytesA + kBytesB) <= 49152 ? 4 : 3);
+    static constexpr int kStages = (kBytesA + kBytesB) <= 24576 ? 8 : (kBytesA + kBytesB) <= 32768 ? 6 : ((kBytesA + kBytesB) <= 49152 ? 4 : 3);
     static constexpr unsigned kAccCols = (BM / 128) * BN;       // tensor-memory columns: one accumulator per 128 rows
     static constexpr unsigned kCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;   // allocated: a power of two
 };
@@ -265,8 +265,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             auto emit = [&](int row, int c, float (&v)[32]) { gemm_store_piece<Tout, kSwiglu>(row, n0 + c, v, bias, out, M, N); };
             const size_t tile_id = (size_t)blockIdx.y * gridDim.x + blockIdx.x, tiles = (size_t)gridDim.x * gridDim.y;
             if constexpr (kRope) {
-                // the q|k|v product of a prefill step: a tile of 256 columns is two heads of 128; never split along k
-                static_assert(!kRope || (BM == 128 && BN == 256 && sizeof(Tout) == 2 && !kSwiglu), "the rope epilogue is for 128 x 256 bfloat16 tiles");
+                // the q|k|v product of a prefill step: a tile of 128 or 256 columns is one or two heads of 128; never split along k
+                static_assert(!kRope || (BM == 128 && BN % 128 == 0 && sizeof(Tout) == 2 && !kSwiglu), "the rope epilogue is for tiles of whole heads of 128 in bfloat16");
                 const int row = m0 + quarter * 32 + lane;
 #pragma unroll 1
                 for (int hl = 0; hl < BN / 128; ++hl) {
@@ -349,6 +349,7 @@ SplitWorkspace g_split_ws[16];
 constexpr int kSplitCounters = 1 << 16;
 
 // Workspace of the k-splits (prefill only: it may grow, so the first call of a size must not be under stream capture).
+// A buffer that was outgrown is kept until the process ends: a captured graph may still hold its address.
 int split_workspace(size_t floats, SplitWorkspace** out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -362,11 +363,11 @@ int split_workspace(size_t floats, SplitWorkspace** out) {
     }
     if (w.floats < floats) {
         float* nb = nullptr;
-        e = cudaMalloc(&nb, floats * sizeof(float));
-        if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot allocate %zu bytes for the k-splits: %s", floats * sizeof(float), cudaGetErrorString(e));
-        if (w.partial) cudaFree(w.partial);
+        size_t want = floats < (4u << 20) ? (4u << 20) : floats + floats / 2;
+        e = cudaMalloc(&nb, want * sizeof(float));
+        if (e != cudaSuccess) return li_fail("linear (tcgen05): cannot allocate %zu bytes for the k-splits: %s", want * sizeof(float), cudaGetErrorString(e));
         w.partial = nb;
-        w.floats = floats;
+        w.floats = want;
     }
     *out = &w;
     return 0;
@@ -438,13 +439,42 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     // (measured at 1,024 rows: 39 us against 69 us on 256 x 256 tiles with four splits)
     if (tile == 0 && big_ctas < 120 && g_forced_ksplit == 0 && pair_ctas >= 40 && pair_ctas < 74 && nkb >= 64)
         return launch_tile<128, 256, Tout, kSwiglu, true>(a, w, bias, out, M, N, K, stream, (int)(148 / pair_ctas));
+    if (tile == 8) return launch_tile<128, 64, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
+    if (tile == 9) return launch_tile<128, 32, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
     const bool big = tile == 2 || tile == 4 || (tile == 0 && (big_ctas >= 120 || ksplit > 1));
     if (big && tile == 4) return launch_tile<256, 256, Tout, kSwiglu, true>(a, w, bias, out, M, N, K, stream, ksplit);
     if (big) return launch_tile<256, 256, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, ksplit);
+    // few tiles of rows (a step of up to about 500 tokens) and a narrow product: the weights are the traffic, and 128 x 128
+    // tiles are too few CTAs to stream them (q|k|v at 128 rows: 16).  Narrower column tiles, and a split of k where there
+    // is room left, bring the count near one wave (measured at 128 / 256 / 512 rows, 40 launches in a graph: q|k|v 11.1 ->
+    // 8.7, 11.4 -> 9.4, 11.7 -> 10.2 us; o 11.8 -> 8.0, 11.8 -> 9.5, 12.1 -> 10.7 us; down 25.3 -> 18.0, 25.5 -> 21.9 us
+    // and unchanged from 384 rows on, where 128 x 128 tiles with four splits stay ahead)
+    if (tile == 0 && g_forced_ksplit == 0) {
+        const long long rows = ceil_div(M, 128);
+        if (nkb < 32) {
+            for (int bn = 32; bn <= 64; bn *= 2) {
+                const long long ctas = rows * ceil_div(N, bn);
+                if (ctas > 148) continue;
+                int ks = (int)(148 / ctas);
+                if (ks > nkb / 8) ks = nkb / 8;
+                if (ks < 1) ks = 1;
+                if (bn == 32) return launch_tile<128, 32, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, ks);
+                return launch_tile<128, 64, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, ks);
+            }
+        } else if (rows <= 2) {
+            const long long ctas = rows * ceil_div(N, 64);
+            if (ctas * 2 <= 148) {
+                int ks = (int)(148 / ctas);
+                if (ks > nkb / 16) ks = nkb / 16;
+                if (ks < 1) ks = 1;
+                return launch_tile<128, 64, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, ks);
+            }
+        }
+    }
     // narrow products with a short k (q|k|v, o): 256 x 128 tiles take in a quarter less per flop than 128 x 128, and
-    // there are still enough of them to occupy most of the GPU
+    // there are still enough of them to occupy most of the GPU; with no more than 128 rows their second half would be empty
     const long long mid_ctas = (long long)ceil_div(M, 256) * ceil_div(N, 128);
-    if (tile == 3 || (tile == 0 && mid_ctas >= 74))
+    if (tile == 3 || (tile == 0 && mid_ctas >= 74 && M > 128))
         return launch_tile<256, 128, Tout, kSwiglu>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
     // few small tiles and a long k (down of a short step): split k so that they fill the GPU, at least 16 k-blocks a split
     int small_split = 1;
@@ -470,10 +500,11 @@ bool pair_tiles_chosen(int M, int N, int K) {
 }  // namespace
 
 // The q|k|v product with rotary encoding and the cache writes as its epilogue (rope_epilogue.cuh): where the shape takes
-// the paired tiles anyway.
+// the paired tiles anyway, and on single 128 x 128 tiles (a head each) for steps too short for those: there the two
+// kernels that would rotate and write the cache cost more than the narrower column tiles of the plain product gain.
 bool li_tcgen05_rope_wanted(const void* a, const void* w, const void* out, int M, int N, int K) {
-    return li_tcgen05_accepts(a, w, out, LI_BF16, M, N, K) && N % 128 == 0 && pair_tiles_chosen(M, N, K) &&
-           !li_tcgen05_persistent_wanted(M, N, K);
+    if (!li_tcgen05_accepts(a, w, out, LI_BF16, M, N, K) || N % 128 != 0 || li_tcgen05_persistent_wanted(M, N, K)) return false;
+    return g_forced_tile == 0 && g_forced_ksplit == 0;
 }
 
 int li_linear_tcgen05_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const RopeEpilogue& rope,
@@ -481,12 +512,13 @@ int li_linear_tcgen05_rope(const void* a, const void* w, const float* bias, void
     LI_REQUIRE(li_tcgen05_rope_wanted(a, w, out, M, N, K), "linear + rope (tcgen05): refuses M=%d N=%d K=%d", M, N, K);
     LI_REQUIRE(N == (rope.nh + 2 * rope.nkv) * 128 && rope.cos_sin && rope.slot_mapping && rope.kcache && rope.vcache,
                "linear + rope (tcgen05): N=%d does not match %d + 2 x %d heads of 128, or a null operand", N, rope.nh, rope.nkv);
-    return launch_tile<128, 256, bf16, false, true, true>(a, w, bias, out, M, N, K, stream, 1, rope);
+    if (pair_tiles_chosen(M, N, K)) return launch_tile<128, 256, bf16, false, true, true>(a, w, bias, out, M, N, K, stream, 1, rope);
+    return launch_tile<128, 128, bf16, false, false, true>(a, w, bias, out, M, N, K, stream, 1, rope);
 }
 
 // 0: tile size by shape; 1: 128 x 128 always; 2: 256 x 256 always, one CTA a tile; 3: 256 x 128 always; 4: pairs of CTAs on
 // 512 x 256 (two accumulators each); 5: pairs of CTAs on 256 x 256 (one accumulator each); 6: the persistent kernel
-// (gemm_tcgen05_persistent.cu); 7: pairs of CTAs on 256 x 192.  For tests and measurements.
+// (gemm_tcgen05_persistent.cu); 7: pairs of CTAs on 256 x 192; 8: 128 x 64; 9: 128 x 32.  For tests and measurements.
 LI_EXPORT void li_tcgen05_force_tile(int tile) { g_forced_tile = tile; }
 
 // 0: splits of k by shape; n > 0: n splits always.  For tests and measurements.

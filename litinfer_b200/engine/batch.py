@@ -106,20 +106,33 @@ def split_into_tokens(items: Sequence[StepItem]) -> List[StepItem]:
 
 
 def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int, pad_seqs: int = 0,
-              max_blocks: Optional[int] = None, tokens_of_one_request: bool = False):
+              max_blocks: Optional[int] = None, tokens_of_one_request: bool = False, pad_tokens: int = 0,
+              pad_rows: int = 0):
     """Host side: validate the items and fill the packed int32 array.
 
     Returns (array, layout) where layout maps field name -> (offset, length) and
     carries the scalar sizes.  Pages for all tokens must already be allocated.
     ``tokens_of_one_request``: the items come from :func:`split_into_tokens`, several may belong to one request.
+    ``pad_tokens`` (with ``pad_seqs`` and ``pad_rows``): the step is padded to exactly that many tokens, sequences
+    and logit rows, for a captured step of a fixed shape: the padding sequences are empty but the last, which takes
+    the padding tokens; it starts at position 0, writes to the sink page and sees nothing else; the real rows come
+    first among the logit rows, and ``layout["R_real"]`` says how many they are.
     """
     S_real = len(items)
     if S_real == 0:
         raise ValueError("a step needs at least one item")
     S = max(S_real, pad_seqs)
-    q_lens = [len(it.tokens) for it in items] + [1] * (S - S_real)
+    q_lens = [len(it.tokens) for it in items]
     if min(q_lens) <= 0:
         raise ValueError("an item without tokens")
+    if pad_tokens:
+        rest = pad_tokens - sum(q_lens)
+        if rest < 0 or (rest > 0 and S == S_real):
+            raise ValueError(f"{sum(q_lens)} tokens in {S_real} sequences cannot be padded to {pad_tokens} tokens in {S}")
+        q_lens += [0] * (S - S_real)
+        q_lens[-1] += rest
+    else:
+        q_lens += [1] * (S - S_real)
     T = sum(q_lens)
     page = manager.page_size
     q_start = np.zeros(S + 1, dtype=np.int32)
@@ -151,12 +164,19 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
             if not 0 <= w < n:
                 raise IndexError(f"request {rc.request_id}: wanted place {w} is outside its {n} tokens")
             rows.append(lo + int(w))
+    R_real = len(rows)
     for s in range(S_real, S):
-        lo = int(q_start[s])
-        seq_of[lo] = s
-        ctx[s] = 1
+        lo, n = int(q_start[s]), q_lens[s]
+        seq_of[lo:lo + n] = s
+        positions[lo:lo + n] = np.arange(n)
+        ctx[s] = n
         slots[s] = manager.trash_slot
-        rows.append(lo)                      # padded items want a row too: the layout depends on S alone
+        if not pad_tokens:
+            rows.append(lo)                  # padded items want a row too: the layout depends on S alone
+    if pad_tokens:
+        if len(rows) > pad_rows:
+            raise ValueError(f"{len(rows)} wanted rows do not fit the {pad_rows} of the padded step")
+        rows.extend([T - 1] * (pad_rows - len(rows)))
     R = len(rows)
     need_blocks = max(-(-int(c) // page) for c in ctx)
     G = len(manager.groups)
@@ -192,7 +212,7 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
     trash = manager.trash_page
     for gid in range(G):
         bt = np.full((S, mb), trash, dtype=np.int32)
-        sm = np.full(T, trash * page, dtype=np.int32)
+        sm = trash * page + positions % page             # padding tokens: the sink page, the slot of their position
         for s, it in enumerate(items):
             rc = it.cache
             table = rc.tables[gid]
@@ -210,7 +230,7 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
             sm[lo:lo + n] = pages * page + pos % page
         put(f"block_table{gid}", bt.reshape(-1))
         put(f"slot_mapping{gid}", sm)
-    layout = dict(fields=fields, T=T, S=S, R=R, G=G, max_blocks=mb, max_q_len=max(q_lens), max_ctx_len=int(ctx.max()),
+    layout = dict(fields=fields, T=T, S=S, R=R, R_real=R_real, G=G, max_blocks=mb, max_q_len=max(q_lens), max_ctx_len=int(ctx.max()),
                   q_start=q_start.tolist(), ctx_lens=ctx.tolist(), state_slots=slots.tolist())
     return buf, layout
 

@@ -23,7 +23,8 @@ from .step import ModelRunner
 
 
 class Replayer:
-    def __init__(self, model: DecoderModel, max_tokens: int, page_size: int = 16, max_live: int = 8, use_graphs: bool = True) -> None:
+    def __init__(self, model: DecoderModel, max_tokens: int, page_size: int = 16, max_live: int = 8, use_graphs: bool = True,
+                 step_graph_after: int = 1) -> None:
         spec = model.spec
         self.model = model
         num_pages = max(1, -(-int(max_tokens) // page_size))
@@ -32,7 +33,8 @@ class Replayer:
         has_state = any(e.kind == "state" for e in self.manager.entries)
         max_context = min(spec.max_position_embeddings, num_pages * page_size)
         # a captured step is warmed up by running it, which a mixer with state of its own would not survive
-        self.runner = ModelRunner(model, self.manager, use_graphs=use_graphs and not has_state, max_context=max_context)
+        self.runner = ModelRunner(model, self.manager, use_graphs=use_graphs and not has_state, max_context=max_context,
+                                  step_graph_after=step_graph_after)
         self.live: Dict[str, RequestCache] = {}
         self._next_id = 0
 
@@ -60,11 +62,11 @@ class Replayer:
 
 
 def replay(model: DecoderModel, lines: Iterable[str], out_dir, max_tokens: int, page_size: int = 16, max_live: int = 8,
-           use_graphs: bool = True, report: Optional[IO[str]] = None) -> None:
+           use_graphs: bool = True, report: Optional[IO[str]] = None, step_graph_after: int = 1) -> None:
     """Feed the step records in ``lines``; write ``<step>.f32`` files; print ``done <step>`` to ``report``."""
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
-    rp = Replayer(model, max_tokens, page_size, max_live, use_graphs)
+    rp = Replayer(model, max_tokens, page_size, max_live, use_graphs, step_graph_after)
     for line in lines:
         line = line.strip()
         if not line:

@@ -10,7 +10,10 @@ schedules, samples and frees; here those live in the scheduler above.
 
 Steps that consist of single tokens only can be replayed from a captured CUDA
 graph per batch-size bucket: the launch sequence of a decode step is fixed, so
-one graph launch replaces a few hundred kernel launches.
+one graph launch replaces a few hundred kernel launches.  Steps with portions
+of prompts are captured too, per shape (tokens, sequences and logit rows, each
+rounded up and padded), once a shape has come back: launched plainly, a step
+of a few hundred tokens is bound by the host's launches, not by the device.
 """
 
 from __future__ import annotations
@@ -47,9 +50,16 @@ class ModelRunner:
     # the device needs for it.  Every token then reads its context by itself, so the contexts together are bounded.
     SPLIT_TOKENS = 64
     SPLIT_CONTEXT_SUM = 32768
+    # Larger steps with portions of prompts: a captured graph per shape.  Tokens are rounded up in steps of 64, 128 and
+    # 256 (at most an eighth of padding from 512 tokens on), sequences to the decode buckets (the padding sequences are
+    # empty but the last, which takes the padding tokens), logit rows to the sequences or, if more are wanted, to the
+    # tokens.
+    STEP_GRAPH_TOKENS = 2048
+    STEP_GRAPH_LIMIT = 48               # captured shapes kept; further shapes are launched plainly
+    STEP_GRAPH_LOGITS = 1 << 26         # logits (floats) a captured shape may hold
 
     def __init__(self, model: DecoderModel, manager: CacheManager, use_graphs: bool = False,
-                 max_context: Optional[int] = None) -> None:
+                 max_context: Optional[int] = None, step_graph_after: int = 1) -> None:
         self.model = model
         self.manager = manager
         self.device = model.device
@@ -58,6 +68,12 @@ class ModelRunner:
         # are sized for it), so that length is capped; steps with a longer context run without a graph
         self.max_context = min(int(max_context or model.spec.max_position_embeddings), self.GRAPH_CONTEXT_CAP)
         self._graphs: Dict[int, _DecodeGraph] = {}
+        # shapes of steps with portions of prompts: how often each came, and the captured ones; a shape is captured
+        # when it comes for the (step_graph_after + 1)-th time, since a capture costs three plain runs
+        self.step_graph_after = int(step_graph_after)
+        self._shape_seen: Dict[tuple, int] = {}
+        self._step_graphs: Dict[tuple, _DecodeGraph] = {}
+        self._step_pool = None
         # a mixer with state of its own takes a request's tokens in order: its portions are never split
         self._may_split = not any(isinstance(r, FixedState) for r in model.cache_requirements())
         self._pinned: Optional[torch.Tensor] = None
@@ -111,6 +127,8 @@ class ModelRunner:
                 rows.extend(base + int(w) for w in it.want)
                 base += len(it.tokens)
             logits = self._step_graph(split_into_tokens(items), None, rows)
+        elif self.use_graphs and not decode_only and (shape := self._step_shape(items)) is not None:
+            logits = self._step_shape_graph(items, shape)
         else:
             buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size)
             ctx = context_from(self._upload(buf), layout, self.manager.page_size)
@@ -138,6 +156,51 @@ class ModelRunner:
         # token j of a portion reads length + j + 1 keys
         reads = sum(len(it.tokens) * it.cache.length + len(it.tokens) * (len(it.tokens) + 1) // 2 for it in items)
         return reads <= self.SPLIT_CONTEXT_SUM
+
+    def _step_shape(self, items: Sequence[StepItem]) -> Optional[tuple]:
+        """The padded shape (tokens, sequences, logit rows) under which a step with portions of prompts is replayed from
+        a captured graph, or None if it is launched plainly: too large, a context beyond the captured attention's,
+        a shape that has not come back yet, or a mixer with state of its own."""
+        if not self._may_split:
+            return None
+        T = sum(len(it.tokens) for it in items)
+        S = len(items)
+        if T > self.STEP_GRAPH_TOKENS or S >= self.GRAPH_BUCKETS[-1]:
+            return None
+        if max(it.cache.length + len(it.tokens) for it in items) > self.max_context:
+            return None
+        step = 64 if T <= 512 else 128 if T <= 1024 else 256
+        Tp = -(-T // step) * step
+        Sp = self._bucket(S if Tp == T else S + 1)          # padding tokens need a sequence to be in
+        R = sum(len(it.want) for it in items)
+        if R > Sp and Tp * self.model.spec.vocab_size > self.STEP_GRAPH_LOGITS:
+            return None                                     # logits of every token of a large step: not kept per shape
+        shape = (Tp, Sp, Sp if R <= Sp else Tp)
+        if shape in self._step_graphs:
+            return shape
+        seen = self._shape_seen.get(shape, 0)
+        self._shape_seen[shape] = seen + 1
+        if seen < self.step_graph_after or len(self._step_graphs) >= self.STEP_GRAPH_LIMIT:
+            return None
+        return shape
+
+    def _step_shape_graph(self, items: List[StepItem], shape: tuple) -> torch.Tensor:
+        """A step with portions of prompts through the captured graph of its padded shape."""
+        Tp, Sp, Rp = shape
+        max_blocks = -(-self.max_context // self.manager.page_size)
+        buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size, pad_seqs=Sp, max_blocks=max_blocks,
+                                pad_tokens=Tp, pad_rows=Rp)
+        g = self._step_graphs.get(shape)
+        if g is None:
+            # the attention launch is sized for the longest portion and the longest context the shape may hold
+            g = self._capture(None, max_blocks, buf, layout, max_q_len=Tp)
+            self._step_graphs[shape] = g
+        if layout["fields"] != g.layout["fields"]:
+            raise RuntimeError("step graph: metadata layout changed between capture and replay")
+        self._upload(buf, g.meta_buf)
+        g.graph.replay()
+        self.graph_replays += 1
+        return g.logits[:layout["R_real"]]
 
     def _step_graph(self, items: List[StepItem], token_source: Optional[torch.Tensor] = None,
                     rows: Optional[List[int]] = None) -> torch.Tensor:
@@ -212,24 +275,34 @@ class ModelRunner:
                 buf[f[f"slot_mapping{gid}"][0] + i] = p * page + pos % page
         return buf
 
-    def _capture(self, B: int, max_blocks: int, buf: np.ndarray, layout) -> _DecodeGraph:
+    def _capture(self, B: Optional[int], max_blocks: int, buf: np.ndarray, layout, max_q_len: int = 1) -> _DecodeGraph:
+        """Capture the model's forward pass over the packed step.  ``B``: the decode bucket it is kept under (None: the
+        caller keeps it).  Graphs of padded steps share one memory pool: they run one after the other on one stream, and
+        a step's logits are read before the next step starts."""
         meta = torch.zeros(buf.shape[0], dtype=torch.int32, device=self.device)
         self._upload(buf, meta)
         lay = dict(layout)
         # a captured attention launch must cover any context up to the maximum
         lay["max_ctx_len"] = self.max_context
-        lay["max_q_len"] = 1
+        lay["max_q_len"] = max_q_len
         ctx = context_from(meta, lay, self.manager.page_size)
         stream = torch.cuda.Stream(self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(stream):
             for _ in range(2):                    # warm-up outside capture (first-call set-up, allocator)
+                ctx.scratch.clear()
                 self.model.forward(ctx, self.manager.entries)
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        if B is None and self._step_pool is None:
+            self._step_pool = torch.cuda.graph_pool_handle()
+        # what the parts make once per step (a table of rotation angles) is made inside the capture, from the step's
+        # metadata, not taken over from the warm-up runs
+        ctx.scratch.clear()
+        with torch.cuda.graph(graph, pool=None if B is not None else self._step_pool):
             logits = self.model.forward(ctx, self.manager.entries)
         g = _DecodeGraph(graph, meta, logits, lay)
-        self._graphs[B] = g
+        if B is not None:
+            self._graphs[B] = g
         return g

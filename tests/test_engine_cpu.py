@@ -195,3 +195,45 @@ def test_portions_as_single_tokens_are_the_same_step(name, model_dirs, cpu_kerne
         pack_step(singles, manager, vocab)                        # one request twice, unless said so
     with pytest.raises(IndexError):
         split_into_tokens([StepItem(rc, c, (9,))])
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_a_step_padded_to_a_fixed_shape_is_the_same_step(name, model_dirs, cpu_kernels):
+    """A step with portions of prompts, padded to a fixed count of tokens, sequences and logit rows (as a captured step
+    takes it): the padding writes to the sink page only, and the real rows come first and are unchanged."""
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.engine import ModelRunner, StepItem
+    from litinfer_b200.engine.batch import context_from, pack_step
+    from litinfer_b200.models import DecoderModel
+
+    cfg = TINY[name]
+    vocab = cfg["vocab_size"]
+    model = DecoderModel.from_dir(model_dirs[name], "float32", "cpu")
+    spec = model.spec
+    manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], 24, 16, 4, model.dtype, model.device)
+    runner = ModelRunner(model, manager)
+    a, b = random_tokens(70, vocab, 1), random_tokens(30, vocab, 2)
+    ra, rb = manager.admit(1), manager.admit(2)
+    manager.extend(ra, 21)
+    manager.extend(rb, 29)
+    runner.step([StepItem(ra, a[:21], ()), StepItem(rb, b[:29], ())])
+    manager.extend(ra, 70)
+    manager.extend(rb, 30)
+    items = [StepItem(ra, a[21:], (48, 3)), StepItem(rb, b[29:], (0,))]
+    buf, layout = pack_step(items, manager, vocab)
+    plain = model.forward(context_from(torch.from_numpy(buf), layout, manager.page_size), manager.entries)
+    buf, layout = pack_step(items, manager, vocab, pad_seqs=4, max_blocks=8, pad_tokens=64, pad_rows=4)
+    assert (layout["T"], layout["S"], layout["R"], layout["R_real"]) == (64, 4, 4, 3)
+    f = layout["fields"]
+    q_start = buf[f["q_start"][0]:f["q_start"][0] + 5].tolist()
+    assert q_start == [0, 49, 50, 50, 64]                         # an empty padding sequence, and one with the padding tokens
+    sm = buf[f["slot_mapping0"][0]:f["slot_mapping0"][0] + 64]
+    trash = manager.trash_page
+    assert (sm[50:] // 16 == trash).all() and (sm[:50] // 16 != trash).all()
+    padded = model.forward(context_from(torch.from_numpy(buf), layout, manager.page_size), manager.entries)
+    assert padded.shape[0] == 4
+    assert torch.equal(padded[:3], plain)
+    with pytest.raises(ValueError):
+        pack_step(items, manager, vocab, pad_seqs=2, pad_tokens=64, pad_rows=4)     # no sequence for the padding tokens
+    with pytest.raises(ValueError):
+        pack_step(items, manager, vocab, pad_seqs=4, pad_tokens=64, pad_rows=2)     # three rows wanted

@@ -147,7 +147,8 @@ TC_SHAPES = [(128, 128, 64), (128, 128, 512), (256, 384, 1536), (2048, 2048, 153
              (1000, 389, 96), (64, 1536, 8960), (2048, 1536, 8960), (5, 151936, 1536)]
 
 
-@pytest.fixture(params=[1, 2, 3, 4, 5, 6, 7], ids=["tile128", "tile256", "tile256x128", "tile512pair", "tile256pair", "persistent", "tile256x192pair"])
+@pytest.fixture(params=[1, 2, 3, 4, 5, 6, 7, 8, 9], ids=["tile128", "tile256", "tile256x128", "tile512pair", "tile256pair", "persistent", "tile256x192pair",
+                                                   "tile128x64", "tile128x32"])
 def forced_tile(request):
     """Every tile size of the tcgen05 kernel, whatever it would choose for the shape itself."""
     lib = K().library()
@@ -283,7 +284,8 @@ def test_rope_kv_write_many_tokens(dtype, cfg, page):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("cfg", [(4, 2, 16, 64, 5), (12, 2, 128, 1536, 8), (3, 1, 32, 96, 1), (6, 2, 48, 80, 20), (14, 2, 80, 136, 64), (12, 2, 128, 1536, 70),
-                                 (12, 2, 128, 1536, 2048), (12, 2, 128, 1536, 1111), (28, 4, 128, 264, 600), (12, 2, 128, 1536, 300)])
+                                 (12, 2, 128, 1536, 2048), (12, 2, 128, 1536, 1111), (28, 4, 128, 264, 600), (12, 2, 128, 1536, 300),
+                                 (12, 2, 128, 1536, 130), (28, 4, 128, 264, 200)])
 def test_linear_rope_kv_fused(dtype, cfg):
     """Projection, rotation and cache write as one call; for few bfloat16 tokens one kernel, the rotation in the
     product's epilogue.  Against the reference, and against the same call forced through separate kernels."""

@@ -202,3 +202,95 @@ def test_replay_real_layer_sizes(dtype, real_size_dir, tmp_path):
     for rid, ref in (("a", ref_a), ("b", ref_b)):
         rows = sorted(got[rid])
         check_logits(stack(got[rid]), ref[rows], dtype, f"real layer sizes {dtype} request {rid}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["head128", "head64_window", "B"])
+def test_steps_with_portions_through_captured_shapes(name, dtype, model_dirs, tmp_path):
+    """Steps with portions of prompts replayed from graphs of their padded shapes (captured at first sight here) give
+    what the same steps give when launched plainly: padding tokens, padding sequences and padding rows change nothing,
+    a captured shape serves other requests at other places of the cache, and two shapes share their memory."""
+    from litinfer_b200.engine.replay import Replayer
+    from litinfer_b200.models import DecoderModel
+    from litinfer_b200.weights import write_model_folder
+
+    if name in MID:
+        cfg = MID[name]
+        folder = tmp_path / "model"
+        write_model_folder(folder, dict(cfg), seed=77, store_dtype="float32")
+    else:
+        cfg, folder = TINY[name], model_dirs[name]
+    vocab = cfg["vocab_size"]
+    lens = dict(a=230, b=152, c=90, d=203, e=80)
+    lens = {k: min(v, cfg["max_position_embeddings"] - 2) for k, v in lens.items()}
+    toks = {k: random_tokens(n, vocab, 500 + i) for i, (k, n) in enumerate(lens.items())}
+    a, b, c, d, e = (toks[k] for k in "abcde")
+    nd = len(d)
+    records = [
+        dict(entries=[dict(id="a", tokens=a[:130], want=[129])]),
+        dict(entries=[dict(id="a", tokens=a[130:200], want=[0, 69]), dict(id="b", tokens=b[:70], want=[69])]),
+        dict(entries=[dict(id="a", tokens=a[200:201], want=[0]), dict(id="b", tokens=b[70:150], want=[79]),
+                      dict(id="c", tokens=c, want=[3, len(c) - 1])]),
+        dict(entries=[dict(id="a", tokens=a[201:202], want=[0]), dict(id="b", tokens=b[150:151], want=[0]),
+                      dict(id="d", tokens=d[:100], want=[99])], end=["c"]),
+        # the same shape again, with other requests' tokens and a page that c gave back
+        dict(entries=[dict(id="b", tokens=b[151:152], want=[0]), dict(id="a", tokens=a[202:203], want=[0]),
+                      dict(id="d", tokens=d[100:nd], want=[nd - 101])], end=["b"]),
+        # the logits of every token: rows padded to the tokens
+        dict(entries=[dict(id="e", tokens=e, want=list(range(len(e))))], end=["e"]),
+        dict(entries=[dict(id="a", tokens=a[203:], want=[len(a) - 204])], end=["a", "d"]),
+    ]
+    where = [[("a", 129)], [("a", 130), ("a", 199), ("b", 69)], [("a", 200), ("b", 149), ("c", 3), ("c", len(c) - 1)],
+             [("a", 201), ("b", 150), ("d", 99)], [("b", 151), ("a", 202), ("d", nd - 1)], [("e", i) for i in range(len(e))],
+             [("a", len(a) - 1)]]
+    model = DecoderModel.from_dir(folder, dtype, torch.device("cuda:0"))
+    need = sum(round64(n) for n in lens.values())
+    plainly = Replayer(model, need, use_graphs=False)
+    captured = Replayer(model, need, use_graphs=True, step_graph_after=0)
+    refs = {k: plain_logits(folder, toks[k], dtype) for k in toks}
+    for i, rec in enumerate(records):
+        rec = dict(rec, step=i)
+        x = plainly.step(rec).clone()
+        y = captured.step(rec).clone()
+        ref = torch.stack([refs[k][p] for k, p in where[i]])
+        check_logits(x.cpu(), ref, dtype, f"{name} {dtype} step {i} launched plainly")
+        check_logits(y.cpu(), ref, dtype, f"{name} {dtype} step {i} from a captured shape")
+        if dtype == "float32":
+            assert torch.equal(x, y), f"float32: step {i} differs between a captured shape and plain launches"
+    r = captured.runner
+    assert r.graph_replays == len(records)
+    assert 4 <= len(r._step_graphs) <= 6 and plainly.runner.graph_replays == 0
+    # a shape that has not come back yet is launched plainly by default
+    later = Replayer(model, need, use_graphs=True)
+    later.step(dict(records[0], step=0))
+    assert later.runner.graph_replays == 0 and not later.runner._step_graphs
+
+
+def test_captured_decode_step_of_many_requests(tmp_path):
+    """Seventy requests decoding together (a captured step of 128 single tokens, where the products take the tensor-memory
+    kernel and the rotation angles come from the step's table): the same logits as launched plainly, step after step."""
+    from litinfer_b200.engine.replay import Replayer
+    from litinfer_b200.models import DecoderModel
+    from litinfer_b200.weights import write_model_folder
+
+    cfg = MID["head128"]
+    folder = tmp_path / "model"
+    write_model_folder(folder, dict(cfg), seed=78, store_dtype="float32")
+    vocab = cfg["vocab_size"]
+    n = 70
+    prompts = [random_tokens(5 + (i * 7) % 23, vocab, 900 + i) for i in range(n)]
+    model = DecoderModel.from_dir(folder, "bfloat16", torch.device("cuda:0"))
+    plainly = Replayer(model, 64 * n, max_live=n, use_graphs=False)
+    captured = Replayer(model, 64 * n, max_live=n, use_graphs=True)
+    refs = [plain_logits(folder, p, "bfloat16") for p in prompts]
+    first = dict(step=0, entries=[dict(id=str(i), tokens=p[:-4], want=[]) for i, p in enumerate(prompts)])
+    plainly.step(first)
+    captured.step(first)
+    for j in range(4, 0, -1):
+        rec = dict(step=5 - j, entries=[dict(id=str(i), tokens=[p[-j]], want=[0]) for i, p in enumerate(prompts)])
+        x = plainly.step(rec).clone()
+        y = captured.step(rec).clone()
+        ref = torch.stack([r[len(p) - j] for r, p in zip(refs, prompts)])
+        check_logits(x.cpu(), ref, "bfloat16", f"70 requests, token -{j}, launched plainly")
+        check_logits(y.cpu(), ref, "bfloat16", f"70 requests, token -{j}, from the captured step")
+    assert captured.runner.graph_replays == 4
