@@ -430,7 +430,7 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     // instead of 6; measured at 2,048 rows: down 52 us against 55 us, o 16 us against 18 us)
     auto wave_fill = [](long long ctas) { return (double)ctas / (double)(((ctas + 147) / 148) * 148); };
     const bool narrow = N % 192 == 0 && wave_fill(pair_ctas_192) > 1.1 * wave_fill(pair_ctas);
-    const bool pairs = tile == 0 && big_ctas < 120 && g_forced_ksplit == 0 && pair_ctas >= 74;
+    const bool pairs = tile == 0 && big_ctas < 120 && g_forced_ksplit == 0 && pair_ctas >= 74 && M > 128;     // up to 128 rows the second CTA of a pair would have none
     if (tile == 7 || (pairs && narrow))
         return launch_tile<128, 192, Tout, kSwiglu, true>(a, w, bias, out, M, N, K, stream, g_forced_ksplit > 0 ? g_forced_ksplit : 1);
     if (tile == 5 || pairs)
@@ -494,7 +494,7 @@ bool pair_tiles_chosen(int M, int N, int K) {
     const long long big_ctas = (long long)ceil_div(M, 256) * ceil_div(N, 256);
     const long long pair_ctas = (long long)((ceil_div(M, 128) + 1) & ~1) * ceil_div(N, 256);
     (void)K;
-    return g_forced_tile == 0 && g_forced_ksplit == 0 && big_ctas < 120 && pair_ctas >= 74;
+    return g_forced_tile == 0 && g_forced_ksplit == 0 && big_ctas < 120 && pair_ctas >= 74 && M > 128;
 }
 
 }  // namespace
@@ -502,9 +502,12 @@ bool pair_tiles_chosen(int M, int N, int K) {
 // The q|k|v product with rotary encoding and the cache writes as its epilogue (rope_epilogue.cuh): where the shape takes
 // the paired tiles anyway, and on single 128 x 128 tiles (a head each) for steps too short for those: there the two
 // kernels that would rotate and write the cache cost more than the narrower column tiles of the plain product gain.
+int g_rope_single_tiles = 1;      // 0: the rope epilogue only on paired tiles (measurements)
+LI_EXPORT void li_tcgen05_rope_single_tiles(int on) { g_rope_single_tiles = on; }
+
 bool li_tcgen05_rope_wanted(const void* a, const void* w, const void* out, int M, int N, int K) {
     if (!li_tcgen05_accepts(a, w, out, LI_BF16, M, N, K) || N % 128 != 0 || li_tcgen05_persistent_wanted(M, N, K)) return false;
-    return g_forced_tile == 0 && g_forced_ksplit == 0;
+    return g_forced_tile == 0 && g_forced_ksplit == 0 && (g_rope_single_tiles || pair_tiles_chosen(M, N, K));
 }
 
 int li_linear_tcgen05_rope(const void* a, const void* w, const float* bias, void* out, int M, int N, int K, const RopeEpilogue& rope,
