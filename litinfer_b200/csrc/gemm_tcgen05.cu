@@ -190,10 +190,26 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
             bool ok = true;
+            // the weight tiles of the first stages at once (weights do not depend on the kernel before this one); the
+            // tiles of a once that kernel has finished
+            const int first = nkb < kStages ? nkb : kStages;
+            for (int kb = 0; kb < first; ++kb) {
+                if constexpr (kPair) {
+                    if (pair_rank == 0) mbar_expect_tx(&sm.full[kb], 2 * (kStageBytesA + kStageBytesB));
+                    tma_load_2d_pair(sm.b[kb], &map_w, (kb_first + kb) * BK, n0 + (int)pair_rank * (BN / 2), &sm.full[kb]);
+                } else {
+                    mbar_expect_tx(&sm.full[kb], kStageBytesA + kStageBytesB);
+                    tma_load_2d(sm.b[kb], &map_w, (kb_first + kb) * BK, n0, &sm.full[kb]);
+                }
+            }
             pdl_wait();
-            for (int kb = 0; kb < nkb && ok; ++kb) {
+            for (int kb = 0; kb < first; ++kb) {
+                if constexpr (kPair) tma_load_2d_pair(sm.a[kb], &map_a, (kb_first + kb) * BK, m0, &sm.full[kb]);
+                else tma_load_2d(sm.a[kb], &map_a, (kb_first + kb) * BK, m0, &sm.full[kb]);
+            }
+            int issued = first;
+            for (int kb = first; kb < nkb && ok; ++kb) {
                 const int s = kb % kStages;
                 const unsigned phase = (kb / kStages) & 1;
                 ok = mbar_wait(&sm.empty[s], phase ^ 1);
