@@ -5,8 +5,11 @@
 //   bfloat16, every item one token   -> split-context decode kernel (attention_decode.cu)
 //   bfloat16, long portions          -> tcgen05 kernel (attention_tcgen05.cu): head_dim 64 or 128, a portion of
 //                                       at least 64 tokens in the batch
-//   bfloat16, other portions         -> tiled mma.sync kernel (attention_prefill.cu);
-//                                       single tokens in the same batch are portions of length one
+//   bfloat16, other portions         -> tiled mma.sync kernel (attention_prefill.cu)
+//   bfloat16, portions beside single tokens (`singles` != 0) -> two launches: the decode kernel takes the sequences of
+//                                       one token (it finds them by q_start), the kernel for portions skips them.  A
+//                                       single token as a portion of length one would occupy a whole tile of 64 or 128
+//                                       query rows for each head and read its keys once per query head.
 //   sizes those refuse               -> general kernel
 #include "common.cuh"
 
@@ -15,17 +18,17 @@ int li_attention_generic(const void* qkv, void* out, const void* kcache, const v
                          int page_size, int num_pages, float scale, int window, cudaStream_t stream);
 bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
-                        const int* ctx_lens, const int* old_lens, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window,
-                        int max_ctx_len, cudaStream_t stream);
+                        const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int dh, int page_size, int num_pages,
+                        float scale, int window, int max_ctx_len, cudaStream_t stream);
 bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size,
-                         int num_pages, float scale, int window, int max_q_len, cudaStream_t stream);
+                         int num_pages, float scale, int window, int max_q_len, int skip_single, cudaStream_t stream);
 
 bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const void* vcache, int nh, int nkv, int dh, int page_size);
 int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                         float scale, int window, int max_q_len, cudaStream_t stream);
+                         float scale, int window, int max_q_len, int skip_single, cudaStream_t stream);
 
 static int validate(int T, int S, int nh, int nkv, int dh, int page_size, int window) {
     LI_REQUIRE(T >= 0 && S > 0, "attention: bad batch T=%d S=%d", T, S);
@@ -36,23 +39,44 @@ static int validate(int T, int S, int nh, int nkv, int dh, int page_size, int wi
     return 0;
 }
 
+// The kernels for a step of bfloat16 tokens that are not all single: portions on tcgen05 or mma.sync tiles; with
+// `singles` the sequences of one token first, on the decode kernel.
+static int attention_portions(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
+                              const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
+                              float scale, int window, int max_q_len, int max_ctx_len, const int* old_lens, int singles, bool* done,
+                              cudaStream_t stream) {
+    *done = false;
+    const bool tc = max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size);
+    if (!tc && !li_attention_prefill_accepts(nh, nkv, dh, page_size)) return 0;
+    const int split = (singles != 0 && max_q_len > 1 && li_attention_decode_accepts(nh, nkv, dh, page_size)) ? 1 : 0;
+    if (split)
+        if (int rc = li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, dh,
+                                         page_size, num_pages, scale, window, max_ctx_len, stream))
+            return rc;
+    *done = true;
+    if (tc)
+        return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
+                                    num_pages, scale, window, max_q_len, split, stream);
+    return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
+                                num_pages, scale, window, max_q_len, split, stream);
+}
+
+// singles: how many sequences of the step have one token beside longer ones (0: none; negative: not known, there may be).
 LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype,
                                  const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens,
                                  const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
                                  int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
-                                 const int* old_lens, cudaStream_t stream) {
+                                 const int* old_lens, int singles, cudaStream_t stream) {
     if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
     if (T == 0) return 0;
     if (dtype == LI_BF16) {
         if (max_q_len == 1 && T == S && li_attention_decode_accepts(nh, nkv, dh, page_size))
-            return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, S, nh, nkv, dh, page_size,
+            return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, nullptr, S, nh, nkv, dh, page_size,
                                        num_pages, scale, window, max_ctx_len, stream);
-        if (max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size))
-            return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                        num_pages, scale, window, max_q_len, stream);
-        if (li_attention_prefill_accepts(nh, nkv, dh, page_size))
-            return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh,
-                                        page_size, num_pages, scale, window, max_q_len, stream);
+        bool done = false;
+        const int rc = attention_portions(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
+                                          num_pages, scale, window, max_q_len, max_ctx_len, old_lens, singles, &done, stream);
+        if (rc || done) return rc;
     }
     return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv, dh,
                                 page_size, num_pages, scale, window, stream);
@@ -63,11 +87,12 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
 // keys while the kernel that writes the step's keys is still running.
 //
 // Force one implementation, for tests of each kernel alone: 0 general, 1 decode, 2 prefill (mma.sync), 3 prefill (tcgen05).
+// With `singles` 2 and 3 leave the sequences of one token to the decode kernel, as li_paged_attention does.
 LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, const void* kcache, const void* vcache, int dtype,
                                       const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens,
                                       const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
                                       int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
-                                      const int* old_lens, cudaStream_t stream) {
+                                      const int* old_lens, int singles, cudaStream_t stream) {
     if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
     if (T == 0) return 0;
     if (which == 0)
@@ -77,18 +102,25 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
     if (which == 1) {
         LI_REQUIRE(max_q_len == 1 && T == S, "attention: the decode kernel takes one token per sequence");
         LI_REQUIRE(li_attention_decode_accepts(nh, nkv, dh, page_size), "attention: the decode kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
-        return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, S, nh, nkv, dh, page_size, num_pages,
+        return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, nullptr, S, nh, nkv, dh, page_size, num_pages,
                                    scale, window, max_ctx_len, stream);
     }
-    if (which == 2) {
-        LI_REQUIRE(li_attention_prefill_accepts(nh, nkv, dh, page_size), "attention: the prefill kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
-        return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                    num_pages, scale, window, max_q_len, stream);
-    }
-    if (which == 3) {
-        LI_REQUIRE(li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size), "attention: the tcgen05 kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
+    if (which == 2 || which == 3) {
+        if (which == 2) {
+            LI_REQUIRE(li_attention_prefill_accepts(nh, nkv, dh, page_size), "attention: the prefill kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
+        } else {
+            LI_REQUIRE(li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size), "attention: the tcgen05 kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
+        }
+        const int split = (singles != 0 && max_q_len > 1 && li_attention_decode_accepts(nh, nkv, dh, page_size)) ? 1 : 0;
+        if (split)
+            if (int rc = li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, dh,
+                                             page_size, num_pages, scale, window, max_ctx_len, stream))
+                return rc;
+        if (which == 2)
+            return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
+                                        num_pages, scale, window, max_q_len, split, stream);
         return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                    num_pages, scale, window, max_q_len, stream);
+                                    num_pages, scale, window, max_q_len, split, stream);
     }
     return li_fail("attention: unknown implementation %d", which);
 }

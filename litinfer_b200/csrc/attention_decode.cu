@@ -102,8 +102,9 @@ template <int DH, int KB>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
-                        const int* __restrict__ old_lens, float* __restrict__ part, unsigned* __restrict__ counters,
-                        bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages, float scale, int window, int nsplit) {
+                        const int* __restrict__ old_lens, const int* __restrict__ q_start, float* __restrict__ part,
+                        unsigned* __restrict__ counters, bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages,
+                        float scale, int window, int nsplit) {
     extern __shared__ float sm[];
     __shared__ int is_last;
     pdl_launch_dependents();
@@ -114,7 +115,11 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int k_begin = split * kSplit;
     const int k_end = min(ctx, k_begin + kSplit);
-    if (k_begin >= ctx || k_end <= lo) {
+    // q_start (a step that also holds portions of prompts): the sequence's token is row q_start[s], and only the
+    // sequences of one token are this kernel's; without it sequence s is row s
+    const int tok = q_start ? q_start[s] : s;
+    const bool mine = !q_start || q_start[s + 1] - tok == 1;
+    if (!mine || k_begin >= ctx || k_end <= lo) {
         pdl_wait();                                    // a CTA leaves only after the kernel before it has finished: the chain of dependent kernels stays ordered
         return;
     }
@@ -138,7 +143,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
     }
     pdl_wait();
     // query fragments: rows g and g + 8 are heads kvh * G + g (+ 8)
-    const bf16* qrow = qkv + (size_t)s * (nh + 2 * nkv) * DH + (size_t)kvh * G * DH;
+    const bf16* qrow = qkv + (size_t)tok * (nh + 2 * nkv) * DH + (size_t)kvh * G * DH;
     unsigned qa[DH / 16][4];
     const bf16* q_lo = g < G ? qrow + (size_t)g * DH : nullptr;
     const bf16* q_hi = g + 8 < G ? qrow + (size_t)(g + 8) * DH : nullptr;
@@ -271,7 +276,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k
             if (e < G * DH) {
                 const int r = e / DH, d = e - r * DH;
                 const float L = l_sm[r];
-                out[((size_t)s * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O[q] / L : 0.0f);
+                out[((size_t)tok * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O[q] / L : 0.0f);
             }
         }
     }
@@ -286,18 +291,21 @@ template <int DH, int WARPS, int KB>
 __global__ void __launch_bounds__(WARPS * 32, 1)
 decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                               const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
-                              bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages, float scale, int window) {
+                              const int* __restrict__ q_start, bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages,
+                              float scale, int window) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
     const int kvh = blockIdx.x, s = blockIdx.y;
+    const int tok = q_start ? q_start[s] : s;          // as in the kernel above
+    if (q_start && q_start[s + 1] - tok != 1) return;
     const int ctx = ctx_lens[s];
     const int p = ctx - 1;
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int G = nh / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const bf16* qrow = qkv + (size_t)s * (nh + 2 * nkv) * DH + (size_t)kvh * G * DH;
+    const bf16* qrow = qkv + (size_t)tok * (nh + 2 * nkv) * DH + (size_t)kvh * G * DH;
     unsigned qa[DH / 16][4];
     const bf16* q_lo = g < G ? qrow + (size_t)g * DH : nullptr;
     const bf16* q_hi = g + 8 < G ? qrow + (size_t)(g + 8) * DH : nullptr;
@@ -345,7 +353,7 @@ decode_attention_whole_kernel(const bf16* __restrict__ qkv, const bf16* __restri
             O += sm_o[((size_t)w * G + r) * DH + d] * f;
             L += sm_l[w * 16 + r] * f;
         }
-        out[((size_t)s * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
+        out[((size_t)tok * nh + kvh * G + r) * DH + d] = __float2bfloat16_rn(L > 0.0f ? O / L : 0.0f);
     }
 }
 
@@ -380,8 +388,8 @@ int ensure_workspace(size_t floats, float** buf, unsigned** counters) {
 
 template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
-           const int* ctx_lens, const int* old_lens, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window,
-           int max_ctx_len, cudaStream_t stream) {
+           const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int page_size, int num_pages, float scale,
+           int window, int max_ctx_len, cudaStream_t stream) {
     const int G = nh / nkv;
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     if ((long long)S * nkv >= kWholeFrom) {
@@ -396,7 +404,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
                 raised = true;
             }
             li_launch_pdl(decode_attention_whole_kernel<DH, W, KB>, dim3(nkv, S), dim3(W * 32), wsmem, stream, (const bf16*)qkv, (const bf16*)kcache,
-                          (const bf16*)vcache, block_table, max_blocks, ctx_lens, (bf16*)out, nh, nkv, page_size, num_pages, scale, window);
+                          (const bf16*)vcache, block_table, max_blocks, ctx_lens, q_start, (bf16*)out, nh, nkv, page_size, num_pages, scale, window);
             return li_check_launch("attention (decode, whole context)");
         }
     }
@@ -420,7 +428,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     dim3 grid(nsplit, nkv, S);
     li_launch_pdl(decode_attention_kernel<DH, KBS>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache, (const bf16*)vcache,
-                                                                      block_table, max_blocks, ctx_lens, old_lens, part, counters, (bf16*)out,
+                                                                      block_table, max_blocks, ctx_lens, old_lens, q_start, part, counters, (bf16*)out,
                                                                       nh, nkv, page_size, num_pages, scale, window, nsplit);
     return li_check_launch("attention (decode)");
 }
@@ -433,11 +441,11 @@ bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size) {
 }
 
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
-                        const int* ctx_lens, const int* old_lens, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window,
-                        int max_ctx_len, cudaStream_t stream) {
+                        const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int dh, int page_size, int num_pages,
+                        float scale, int window, int max_ctx_len, cudaStream_t stream) {
 #define LI_CASE(D)                                                                                                             \
     case D:                                                                                                                    \
-        return launch<D>(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, S, nh, nkv, page_size, num_pages, scale, \
+        return launch<D>(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, page_size, num_pages, scale, \
                          window, max_ctx_len, stream);
     switch (dh) {
         LI_CASE(16) LI_CASE(32) LI_CASE(48) LI_CASE(64) LI_CASE(80) LI_CASE(96) LI_CASE(112) LI_CASE(128) LI_CASE(256)

@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(kWarps * 32, 2)
 prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, const bf16* __restrict__ kcache,
                          const bf16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ q_start, const int* __restrict__ ctx_lens, int nh, int nkv, int page_size,
-                         int num_pages, float scale, int window) {
+                         int num_pages, float scale, int window, int skip_single) {
     extern __shared__ __align__(16) unsigned char smem[];
     constexpr int KCH = DH / 8;                     // 16-byte chunks in a key row
     constexpr int kKBytes = kKeys * DH * 2, kVBytes = DH * kKeys * 2;
@@ -78,7 +78,7 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
     const int tok0 = q_start[s], n = q_start[s + 1] - tok0;
     // the last tiles of a portion see the most keys: they are started first
     const int cta_i0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * kTile;       // CTAs start in the order x, y, z: all heads of the heaviest tile first
-    if (cta_i0 >= n) return;
+    if (cta_i0 >= n || (skip_single && n == 1)) return;          // skip_single: sequences of one token are another kernel's
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int ctx = ctx_lens[s];
@@ -268,7 +268,7 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ out, c
 template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
            const int* q_start, const int* ctx_lens, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window,
-           int max_q_len, cudaStream_t stream) {
+           int max_q_len, int skip_single, cudaStream_t stream) {
     LI_REQUIRE(S <= 65535 && ceil_div(max_q_len > 0 ? max_q_len : 1, kTile) <= 65535, "attention (prefill): batch %d or portions of %d tokens too large for one launch", S, max_q_len);
     constexpr size_t smem = 2 * (size_t)(kKeys * DH * 2 + DH * kKeys * 2);
     static bool raised = false;
@@ -280,7 +280,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     dim3 grid(nh, ceil_div(max_q_len > 0 ? max_q_len : 1, kTile), S);
     prefill_attention_kernel<DH><<<grid, kWarps * 32, smem, stream>>>((const bf16*)qkv, (bf16*)out, (const bf16*)kcache,
                                                                       (const bf16*)vcache, block_table, max_blocks, q_start, ctx_lens,
-                                                                      nh, nkv, page_size, num_pages, scale, window);
+                                                                      nh, nkv, page_size, num_pages, scale, window, skip_single);
     return li_check_launch("attention (prefill)");
 }
 
@@ -293,13 +293,13 @@ bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size) {
 
 int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size,
-                         int num_pages, float scale, int window, int max_q_len, cudaStream_t stream) {
+                         int num_pages, float scale, int window, int max_q_len, int skip_single, cudaStream_t stream) {
     (void)T;
     LI_REQUIRE(scale > 0.0f, "attention (prefill): the scale must be positive, got %g", (double)scale);
 #define LI_CASE(D)                                                                                                                  \
     case D:                                                                                                                         \
         return launch<D>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, S, nh, nkv, page_size, num_pages, scale, \
-                         window, max_q_len, stream);
+                         window, max_q_len, skip_single, stream);
     switch (dh) {
         LI_CASE(16) LI_CASE(32) LI_CASE(48) LI_CASE(64) LI_CASE(80) LI_CASE(96) LI_CASE(112) LI_CASE(128) LI_CASE(256)
         default:

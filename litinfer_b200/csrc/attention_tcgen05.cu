@@ -58,7 +58,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
                             int max_blocks, const int* __restrict__ q_start, const int* __restrict__ ctx_lens, int nh, int nkv,
-                            int page_size, int num_pages, float scale, int window, int* __restrict__ error_flag) {
+                            int page_size, int num_pages, float scale, int window, int skip_single, int* __restrict__ error_flag) {
     extern __shared__ unsigned char smem_raw[];
     Smem<DH>& sm = *reinterpret_cast<Smem<DH>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr int kPanels = DH / 64;
@@ -68,7 +68,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int s = blockIdx.z, h = blockIdx.x;
     const int tok0 = q_start[s], n = q_start[s + 1] - tok0;
     const int cta_i0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * kRows;
-    if (cta_i0 >= n) return;
+    if (cta_i0 >= n || (skip_single && n == 1)) return;          // skip_single: sequences of one token are another kernel's
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ctx = ctx_lens[s];
     const int kvh = h / (nh / nkv);
@@ -330,7 +330,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks, const int* q_start,
            const int* ctx_lens, int T, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window, int max_q_len,
-           cudaStream_t stream) {
+           int skip_single, cudaStream_t stream) {
     EncodeTiledFn encode = nullptr;
     int *err_host = nullptr, *err_dev = nullptr;
     if (int rc = setup(&encode, &err_host, &err_dev)) return rc;
@@ -351,7 +351,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     LI_REQUIRE(S <= 65535 && ceil_div(max_q_len, kRows) <= 65535, "attention (tcgen05): batch %d or portions of %d tokens too large for one launch", S, max_q_len);
     dim3 grid(nh, ceil_div(max_q_len, kRows), S);
     li_launch_pdl(prefill_attention_tc_kernel<DH>, grid, dim3(kThreads), smem, stream, map_q, map_k, map_v, (bf16*)out, block_table, max_blocks,
-                  q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, err_dev);
+                  q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, skip_single, err_dev);
     return li_check_launch("attention (tcgen05)");
 }
 
@@ -364,13 +364,13 @@ bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const voi
 
 int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                         float scale, int window, int max_q_len, cudaStream_t stream) {
+                         float scale, int window, int max_q_len, int skip_single, cudaStream_t stream) {
     LI_REQUIRE(li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size),
                "attention (tcgen05): refuses heads=%d/%d head_dim=%d page=%d (head_dim 64 or 128, pages a multiple of 16)", nh, nkv, dh, page_size);
     LI_REQUIRE(scale > 0.0f, "attention (tcgen05): the scale must be positive");
     if (dh == 64)
         return launch<64>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
-                          window, max_q_len, stream);
+                          window, max_q_len, skip_single, stream);
     return launch<128>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
-                       window, max_q_len, stream);
+                       window, max_q_len, skip_single, stream);
 }

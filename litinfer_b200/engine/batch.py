@@ -62,6 +62,9 @@ class StepContext:
     # [S] int32: how many keys of each sequence were in the cache before this step (a sequence's own tokens of this step
     # come after them; where a step's sequences are the tokens of one request, so do that request's earlier tokens)
     old_lens: Optional[torch.Tensor] = None
+    # how many sequences of a step with longer portions have one token (they can go to a decode kernel); negative: not
+    # known (a captured step that may hold any)
+    num_single: int = 0
     # what parts make once per step and share between the layers (keyed by the part), e.g. a table of rotation angles
     scratch: dict = field(default_factory=dict)
 
@@ -230,7 +233,8 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
             sm[lo:lo + n] = pages * page + pos % page
         put(f"block_table{gid}", bt.reshape(-1))
         put(f"slot_mapping{gid}", sm)
-    layout = dict(fields=fields, T=T, S=S, R=R, R_real=R_real, G=G, max_blocks=mb, max_q_len=max(q_lens), max_ctx_len=int(ctx.max()),
+    singles = sum(1 for q in q_lens[:S_real] if q == 1) if max(q_lens) > 1 else 0
+    layout = dict(fields=fields, T=T, S=S, R=R, R_real=R_real, G=G, max_blocks=mb, singles=singles, max_q_len=max(q_lens), max_ctx_len=int(ctx.max()),
                   q_start=q_start.tolist(), ctx_lens=ctx.tolist(), state_slots=slots.tolist())
     return buf, layout
 
@@ -250,5 +254,5 @@ def context_from(device_buf: torch.Tensor, layout, page_size: int) -> StepContex
         token_ids=view("token_ids"), positions=view("positions"), seq_of_token=view("seq_of_token"),
         q_start=view("q_start"), ctx_lens=view("ctx_lens"), state_slots=view("state_slots"), old_lens=view("old_lens"),
         logit_rows=view("logit_rows"), groups=groups,
-        max_q_len=layout["max_q_len"], max_ctx_len=layout["max_ctx_len"],
+        max_q_len=layout["max_q_len"], max_ctx_len=layout["max_ctx_len"], num_single=layout.get("singles", 0),
         host_q_start=layout["q_start"], host_ctx_lens=layout["ctx_lens"], host_state_slots=layout["state_slots"])

@@ -175,7 +175,9 @@ class ModelRunner:
         R = sum(len(it.want) for it in items)
         if R > Sp and Tp * self.model.spec.vocab_size > self.STEP_GRAPH_LOGITS:
             return None                                     # logits of every token of a large step: not kept per shape
-        shape = (Tp, Sp, Sp if R <= Sp else Tp)
+        # sequences of one token beside the portions go to the decode kernel: a captured shape has that launch or not
+        singles = any(len(it.tokens) == 1 for it in items)
+        shape = (Tp, Sp, Sp if R <= Sp else Tp, singles)
         if shape in self._step_graphs:
             return shape
         seen = self._shape_seen.get(shape, 0)
@@ -186,14 +188,14 @@ class ModelRunner:
 
     def _step_shape_graph(self, items: List[StepItem], shape: tuple) -> torch.Tensor:
         """A step with portions of prompts through the captured graph of its padded shape."""
-        Tp, Sp, Rp = shape
+        Tp, Sp, Rp, singles = shape
         max_blocks = -(-self.max_context // self.manager.page_size)
         buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size, pad_seqs=Sp, max_blocks=max_blocks,
                                 pad_tokens=Tp, pad_rows=Rp)
         g = self._step_graphs.get(shape)
         if g is None:
             # the attention launch is sized for the longest portion and the longest context the shape may hold
-            g = self._capture(None, max_blocks, buf, layout, max_q_len=Tp)
+            g = self._capture(None, max_blocks, buf, layout, max_q_len=Tp, singles=-1 if singles else 0)
             self._step_graphs[shape] = g
         if layout["fields"] != g.layout["fields"]:
             raise RuntimeError("step graph: metadata layout changed between capture and replay")
@@ -275,7 +277,7 @@ class ModelRunner:
                 buf[f[f"slot_mapping{gid}"][0] + i] = p * page + pos % page
         return buf
 
-    def _capture(self, B: Optional[int], max_blocks: int, buf: np.ndarray, layout, max_q_len: int = 1) -> _DecodeGraph:
+    def _capture(self, B: Optional[int], max_blocks: int, buf: np.ndarray, layout, max_q_len: int = 1, singles: int = 0) -> _DecodeGraph:
         """Capture the model's forward pass over the packed step.  ``B``: the decode bucket it is kept under (None: the
         caller keeps it).  Graphs of padded steps share one memory pool: they run one after the other on one stream, and
         a step's logits are read before the next step starts."""
@@ -285,6 +287,7 @@ class ModelRunner:
         # a captured attention launch must cover any context up to the maximum
         lay["max_ctx_len"] = self.max_context
         lay["max_q_len"] = max_q_len
+        lay["singles"] = singles
         ctx = context_from(meta, lay, self.manager.page_size)
         stream = torch.cuda.Stream(self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))

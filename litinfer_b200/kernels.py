@@ -337,7 +337,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                     seq_of_token: torch.Tensor, positions: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                     max_q_len: int, max_ctx_len: int, implementation: Optional[str] = None,
-                    old_lens: Optional[torch.Tensor] = None) -> None:
+                    old_lens: Optional[torch.Tensor] = None, singles: int = 0) -> None:
     """Causal grouped-query attention of the step's tokens over the paged cache.
 
     Queries are the first ``num_heads * head_dim`` columns of ``qkv`` (already
@@ -346,7 +346,9 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     ``implementation`` (``general``, ``decode``, ``prefill``, ``prefill_tcgen05``) forces one kernel, for
     tests and measurements; it is an error if that kernel refuses the sizes.
     ``old_lens`` (int32 ``[S]``): how many keys of each sequence were in the cache before this step; needed when
-    several sequences of the step are tokens of one request (None: all but each sequence's last key)."""
+    several sequences of the step are tokens of one request (None: all but each sequence's last key).
+    ``singles``: how many sequences of a step with longer portions have one token (negative: not known).  They then
+    go to the decode kernel, the rest to the kernel for portions (bfloat16)."""
     T = qkv.shape[0]
     S = ctx_lens.shape[0]
     _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
@@ -370,7 +372,7 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     args = (_p(qkv), _p(out), _p(k_cache), _p(v_cache), _i(_dt(qkv)), _p(block_table), _i(block_table.shape[1]),
             _p(q_start), _p(ctx_lens), _p(seq_of_token), _p(positions), _i(T), _i(S),
             _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _f(scale),
-            _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _p(old_lens), _stream(out))
+            _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _p(old_lens), _i(int(singles)), _stream(out))
     if implementation is None:
         _check(library().li_paged_attention(*args), "paged_attention")
     else:

@@ -78,5 +78,5 @@ class PagedAttention(Mixer):
         K.paged_attention(
             qkv, o, cache.k, cache.v, view.block_table, ctx.q_start, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,
             self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
-            ctx.max_q_len, ctx.max_ctx_len, old_lens=ctx.old_lens)
+            ctx.max_q_len, ctx.max_ctx_len, old_lens=ctx.old_lens, singles=ctx.num_single)
         return o

@@ -136,8 +136,9 @@ def rope_table(positions, denominators, out):
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
-                    num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None):
-    # old_lens only tells a kernel which keys it may read early; the result does not depend on it
+                    num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None, singles=0):
+    # old_lens only tells a kernel which keys it may read early, singles which kernel takes which sequence; the result
+    # does not depend on them
     T = qkv.shape[0]
     page_size = k_cache.shape[2]
     group = num_heads // num_kv_heads

@@ -224,6 +224,7 @@ def test_a_step_padded_to_a_fixed_shape_is_the_same_step(name, model_dirs, cpu_k
     plain = model.forward(context_from(torch.from_numpy(buf), layout, manager.page_size), manager.entries)
     buf, layout = pack_step(items, manager, vocab, pad_seqs=4, max_blocks=8, pad_tokens=64, pad_rows=4)
     assert (layout["T"], layout["S"], layout["R"], layout["R_real"]) == (64, 4, 4, 3)
+    assert layout["singles"] == 1                                 # b's one token beside a's portion
     f = layout["fields"]
     q_start = buf[f["q_start"][0]:f["q_start"][0] + 5].tolist()
     assert q_start == [0, 49, 50, 50, 64]                         # an empty padding sequence, and one with the padding tokens

@@ -452,7 +452,7 @@ def make_attention_case(q_lens, ctx_lens, nh, nkv, dh, page, dtype, seed=0, extr
                 ctx_lens=list(ctx_lens), q_lens=list(q_lens), nh=nh, nkv=nkv, dh=dh, dtype=dtype)
 
 
-def run_attention_case(c, window, implementation=None, old_lens=None):
+def run_attention_case(c, window, implementation=None, old_lens=None, singles=0):
     d = dev()
     page, nkv, dh = c["page"], c["nkv"], c["dh"]
     kc = torch.zeros(c["pages"], nkv, page, dh, dtype=c["dtype"])
@@ -472,7 +472,7 @@ def run_attention_case(c, window, implementation=None, old_lens=None):
     tail = (c["nh"], nkv, dh, scale, window, max(c["q_lens"]), max(c["ctx_lens"]))
     K().paged_attention(args["qkv"], out, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
                         args["seq_of_token"], args["positions"], *tail, implementation=implementation,
-                        old_lens=None if old_lens is None else torch.tensor(old_lens, dtype=torch.int32, device=d))
+                        old_lens=None if old_lens is None else torch.tensor(old_lens, dtype=torch.int32, device=d), singles=singles)
     R.paged_attention(args["qkv"], ref, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
                       args["seq_of_token"], args["positions"], *tail)
     return out, ref
@@ -543,6 +543,40 @@ def test_attention_decode_kernel_tokens_of_one_request(heads):
         close(out, ref, torch.bfloat16, f"decode kernel, tokens of one request, heads={heads} window={window}")
         again, _ = run_attention_case(c, window, implementation="decode")
         assert torch.equal(out, again)
+
+
+@pytest.mark.parametrize("heads", [(4, 2, 16), (6, 2, 48), (12, 2, 128), (8, 8, 64), (28, 4, 128)])
+@pytest.mark.parametrize("many", [False, True])
+def test_attention_single_tokens_beside_portions(heads, many):
+    """A step of portions and single tokens in two launches: the decode kernel finds the sequences of one token by
+    q_start wherever they stand in the batch, the kernel for portions leaves them out.  `many`: enough sequences for the
+    decode kernel that walks a whole context per CTA."""
+    nh, nkv, dh = heads
+    if many:
+        q_lens = [1] * 33 + [80, 1, 2, 5] + [1] * 30 + [64]
+        ctx_lens = [17 + 23 * i for i in range(33)] + [200, 1, 130, 5] + [300 - 7 * i for i in range(30)] + [64]
+    else:
+        q_lens = [1, 1, 37, 1, 70, 1, 2, 1]
+        ctx_lens = [300, 17, 37, 1, 200, 256, 130, 777]
+    c = make_attention_case(q_lens, ctx_lens, nh, nkv, dh, 16, torch.bfloat16, seed=nh + dh)
+    n1 = sum(1 for q in q_lens if q == 1)
+    for window in (None, 24, 100):
+        for count in (n1, -1):
+            out, ref = run_attention_case(c, window, singles=count)
+            close(out, ref, torch.bfloat16, f"attention, single tokens beside portions, heads={heads} window={window} singles={count}")
+        out, ref = run_attention_case(c, window, implementation="prefill", singles=n1)
+        close(out, ref, torch.bfloat16, f"attention, single tokens beside portions (mma.sync tiles), heads={heads} window={window}")
+        if dh in (64, 128):
+            out, ref = run_attention_case(c, window, implementation="prefill_tcgen05", singles=n1)
+            close(out, ref, torch.bfloat16, f"attention, single tokens beside portions (tcgen05 tiles), heads={heads} window={window}")
+    # a single token alone in a step of singles, or beside portions: the same kernel, the same bits
+    alone = make_attention_case([1] * len(q_lens), ctx_lens, nh, nkv, dh, 16, torch.bfloat16, seed=nh + dh)
+    tok0 = c["q_start"][0]
+    alone["qkv"][0] = c["qkv"][tok0]
+    alone["keys"], alone["vals"], alone["bt"] = c["keys"], c["vals"], c["bt"]
+    out_alone, _ = run_attention_case(alone, None, implementation="decode")
+    out_mixed, _ = run_attention_case(c, None, singles=n1)
+    assert torch.equal(out_alone[0], out_mixed[tok0])
 
 
 @pytest.mark.parametrize("heads", [(4, 2, 16), (3, 1, 32), (6, 2, 48), (12, 2, 128), (8, 8, 64), (14, 2, 80), (28, 4, 128)])
