@@ -233,7 +233,9 @@ def logit_sequences(cfg):
 
 
 def main():
-    src = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py /path/to/LitInfer")
+    src = Path(sys.argv[1])
     out = {}
     with tempfile.TemporaryDirectory() as tmp:
         pkg = build_reference(src, Path(tmp))
