@@ -238,3 +238,62 @@ def test_a_step_padded_to_a_fixed_shape_is_the_same_step(name, model_dirs, cpu_k
         pack_step(items, manager, vocab, pad_seqs=2, pad_tokens=64, pad_rows=4)     # no sequence for the padding tokens
     with pytest.raises(ValueError):
         pack_step(items, manager, vocab, pad_seqs=4, pad_tokens=64, pad_rows=2)     # three rows wanted
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_padded_steps_keep_their_invariants_under_random_batches(seed, model_dirs, cpu_kernels):
+    """Random batches of portions and single tokens, padded to the shape the runner would capture them under: the real
+    tokens, sequences and rows come first and unchanged, the padding sits on the sink page, and the shape only grows."""
+    import random
+
+    import numpy as np
+
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.engine import ModelRunner, StepItem
+    from litinfer_b200.engine.batch import pack_step
+    from litinfer_b200.models import DecoderModel
+
+    rnd = random.Random(seed)
+    cfg = TINY["C"]
+    vocab = cfg["vocab_size"]
+    model = DecoderModel.from_dir(model_dirs["C"], "float32", "cpu")
+    manager = CacheManager(model.cache_requirements(), [e.cache_from for e in model.spec.schedule], 400, 16, 40, model.dtype, model.device)
+    runner = ModelRunner(model, manager)
+    runner.step_graph_after = 0
+    for _ in range(8):
+        n = rnd.randint(1, 20)
+        items = []
+        for i in range(n):
+            rc = manager.admit(i)
+            had = rnd.choice([0, 0, 5, 16, 33])
+            if had:
+                manager.extend(rc, had)
+                manager.commit(rc, had)
+            q = rnd.choice([1, 1, 1, 2, 7, 64, 100])
+            manager.extend(rc, had + q)
+            want = tuple(sorted(rnd.sample(range(q), rnd.randint(0, min(q, 2)))))
+            items.append(StepItem(rc, random_tokens(q, vocab, seed * 100 + i), want))
+        T, S, R = sum(len(it.tokens) for it in items), len(items), sum(len(it.want) for it in items)
+        shape = runner._step_shape(items)
+        if all(len(it.tokens) == 1 for it in items):
+            shape = None                                            # a step of single tokens is the decode graph's
+        if shape is not None:
+            Tp, Sp, Rp, singles = shape
+            assert Tp >= T and Sp >= S and Rp >= R and Tp - T < max(64, T // 4) and (Tp == T or Sp > S)
+            assert singles == any(len(it.tokens) == 1 for it in items)
+            plain, _ = pack_step(items, manager, vocab)
+            buf, lay = pack_step(items, manager, vocab, pad_seqs=Sp, max_blocks=64, pad_tokens=Tp, pad_rows=Rp)
+            f = lay["fields"]
+            get = lambda name, n: buf[f[name][0]:f[name][0] + n]
+            assert (lay["T"], lay["S"], lay["R"], lay["R_real"]) == (Tp, Sp, Rp, R)
+            q_start = get("q_start", Sp + 1)
+            assert q_start[S] == T and q_start[Sp] == Tp and (np.diff(q_start) >= 0).all()
+            assert (np.diff(q_start)[S:Sp - 1] == 0).all() if Sp - S > 1 else True
+            assert (get("slot_mapping0", Tp)[T:] // 16 == manager.trash_page).all()
+            assert (get("block_table0", Sp * 64).reshape(Sp, 64)[S:] == manager.trash_page).all()
+            assert (get("logit_rows", Rp)[R:] == Tp - 1).all() and (get("logit_rows", Rp)[:R] < T).all()
+            assert (get("ctx_lens", Sp)[S:] == np.diff(q_start)[S:]).all()
+            assert lay["singles"] == sum(1 for it in items if len(it.tokens) == 1)
+        for it in items:
+            manager.release(it.cache)
+        manager.check()

@@ -361,3 +361,33 @@ def run_toy_feed_forward_and_positions(model_dirs, device, dtype):
         FEED_FORWARDS.unregister("toy_routed")
         POSITIONS.unregister("toy_stretched_rope")
 
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_that_come_back_run_from_captured_shapes(dtype, model_dirs):
+    """The same longer prompt again and again through the entry point, and a batch of requests in portions under a
+    small token budget: from the second time on a step's shape is replayed from its captured graph, and the tokens stay
+    what the plain model generates."""
+    from litinfer_b200 import Qwen2
+
+    cfg, w = P.read_model_folder(model_dirs["C"])
+    if dtype == "bfloat16":
+        w = bf16_round(w)
+    front = Qwen2(str(model_dirs["C"]), dtype=dtype, max_num_seqs=4, max_tokens_per_step=96, prefill_chunk=80)
+    prompt = random_tokens(150, cfg["vocab_size"], 321)
+    ref, margin = plain_generate(cfg, w, prompt, 6)
+    for _ in range(3):
+        got = front.generate(prompt, max_new_tokens=6)
+        assert got == ref or (dtype == "bfloat16" and margin < 0.05), f"{got} vs {ref} (margin {margin})"
+    assert len(front._single.runner._step_graphs) >= 1, "the portions of 80 and 70 tokens came back and were meant to be captured"
+    prompts = [random_tokens(n, cfg["vocab_size"], 700 + n) for n in (150, 97, 130, 66)]
+    front.engine_start()
+    ids = [front.engine_add_request(p, 5) for p in prompts]
+    while front.engine_has_unfinished():
+        front.engine_step()
+    outs = [front.engine_get_output(i) for i in ids]
+    assert front._eng().runner.graph_replays > 0
+    front.engine_stop()
+    for p, o in zip(prompts, outs):
+        r, m = plain_generate(cfg, w, p, 5)
+        assert o == r or (dtype == "bfloat16" and m < 0.05), f"prompt of {len(p)}: {o} vs {r} (margin {m})"
