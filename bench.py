@@ -324,6 +324,51 @@ def time_first_token(model, cfg, prompt_len=16, repeats=7):
     return statistics.median(times)
 
 
+def time_mixed(model, batch, context, portion, repeats=4):
+    """Median device time of a step that holds ``batch`` requests decoding at about ``context`` tokens beside a portion of
+    ``portion`` prompt tokens of another request (what a continuous-batching engine runs while a prompt comes in): as the
+    engine runs it, from the captured graph of its shape once that has come back."""
+    import torch
+
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.engine import ModelRunner, StepItem
+
+    spec = model.spec
+    pages = (batch * (context + 64) + 2 * portion + 4096) // 16
+    manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], pages, 16, batch + 2, model.dtype, model.device)
+    runner = ModelRunner(model, manager, use_graphs=True)
+    g = torch.Generator().manual_seed(4)
+    live = []
+    for i in range(batch):
+        rc = manager.admit(i)
+        manager.extend(rc, context)
+        toks = torch.randint(0, spec.vocab_size, (context,), generator=g).tolist()
+        for lo in range(0, context, 2048):
+            runner.step([StepItem(rc, toks[lo:lo + 2048], ())])
+        live.append(rc)
+    incoming, next_id = manager.admit(batch), batch + 1
+    times = []
+    for it in range(repeats + 3):
+        items = []
+        for rc in live:
+            manager.extend(rc, rc.length + 1)
+            items.append(StepItem(rc, [5], (0,)))
+        if incoming.length + portion > min(4000, spec.max_position_embeddings - 1):
+            manager.release(incoming)
+            incoming, next_id = manager.admit(next_id), next_id + 1
+        manager.extend(incoming, incoming.length + portion)
+        items.append(StepItem(incoming, torch.randint(0, spec.vocab_size, (portion,), generator=g).tolist(), (portion - 1,)))
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step(items)
+        stop.record()
+        torch.cuda.synchronize()
+        if it >= 3:
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -334,9 +379,10 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "kernels-decode", "kernels-prefill"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "mixed", "kernels-decode", "kernels-prefill"],
                     help="measure one part and print a short line (for profiling runs); kernels-*: a table of the "
-                         "kernels' device times from torch.profiler")
+                         "kernels' device times from torch.profiler; mixed: --batch requests decoding at --context beside "
+                         "a portion of --prefill-tokens prompt tokens")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (so that a profiler lists them)")
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     args = ap.parse_args()
@@ -386,6 +432,12 @@ def main() -> int:
         r = time_decode(model, args.batch, args.context, args.steps, warmup, graphs=not args.no_graphs)
         print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context, "layers_run": cfg["num_hidden_layers"],
                           "graphs": not args.no_graphs, **{k: round(v, 4) for k, v in r.items()}}))
+        return 0
+    if args.only == "mixed":
+        ms = time_mixed(model, args.batch, args.context, args.prefill_tokens)
+        print(json.dumps({"only": "mixed", "decoding": args.batch, "context": args.context, "portion": args.prefill_tokens,
+                          "layers_run": cfg["num_hidden_layers"], "ms": round(ms, 3),
+                          "tok_s": round((args.batch + args.prefill_tokens) / ms * 1e3, 1)}))
         return 0
     if args.only == "prefill":
         ms = time_prefill(model, args.prefill_tokens, graphs=not args.no_graphs)
