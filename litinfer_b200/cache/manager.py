@@ -28,8 +28,11 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
+import ctypes
+
 from ..parts.base import FixedState, PagedKV
-from .pool import OutOfPages, PagePool, PoolError
+from . import native
+from .pool import OutOfPages, PoolError, PoolView
 
 
 @dataclass
@@ -48,21 +51,31 @@ class EntryCache:
 class Group:
     key: PagedKV
     entries: List[int]
-    pool: PagePool
+    pool: Optional[PoolView]
     kv: Optional[torch.Tensor]
 
 
-@dataclass
 class RequestCache:
-    """What one live request holds."""
+    """What one live request holds.  The block tables are the host runtime's; ``tables`` reads them out."""
 
-    request_id: int
-    slot: int
-    length: int = 0                         # tokens whose keys and values are cached
-    tables: List[List[int]] = field(default_factory=list)   # per group: logical page -> page id, -1 once given back
+    __slots__ = ("request_id", "slot", "length", "_manager")
+
+    def __init__(self, request_id: int, slot: int, manager: "CacheManager") -> None:
+        self.request_id = request_id
+        self.slot = slot
+        self.length = 0                     # tokens whose keys and values are cached
+        self._manager = manager
+
+    @property
+    def tables(self) -> List[List[int]]:
+        """Per group: logical page -> page id, -1 once given back (a copy)."""
+        return [self._manager.table(self, gid) for gid in range(len(self._manager.groups))]
+
+    def num_blocks(self, group: int) -> int:
+        return self._manager.table_length(self, group)
 
     def pages_held(self, group: int) -> List[int]:
-        return [p for p in self.tables[group] if p >= 0]
+        return [p for p in self._manager.table(self, group) if p >= 0]
 
 
 class CacheManager:
@@ -79,7 +92,6 @@ class CacheManager:
         self.device = torch.device(device)
         self.groups: List[Group] = []
         self.entries: List[EntryCache] = []
-        self.slots = PagePool(self.max_requests, "state slot")
         self.live: Dict[int, RequestCache] = {}
         by_key: Dict[PagedKV, int] = {}
         for i, req in enumerate(requirements):
@@ -88,8 +100,19 @@ class CacheManager:
             if isinstance(req, PagedKV):
                 if req not in by_key:
                     by_key[req] = len(self.groups)
-                    self.groups.append(Group(req, [], PagePool(self.num_pages), None))
+                    self.groups.append(Group(req, [], None, None))
                 self.groups[by_key[req]].entries.append(i)
+        if self.num_pages <= 0 or self.max_requests <= 0:
+            raise ValueError("a cache needs at least one page and one request slot")
+        # pools, block tables and the step packer live in the host runtime (csrc/host/runtime.cpp)
+        self._lib = native.library()
+        windows = (ctypes.c_int * max(len(self.groups), 1))(*[int(g.key.window or 0) for g in self.groups])
+        self._h = self._lib.li_cm_create(len(self.groups), windows, self.num_pages, self.page_size, self.max_requests)
+        if not self._h:
+            raise PoolError("the host runtime could not create the cache manager")
+        self.slots = PoolView(self, -1, self.max_requests)
+        for gid, g in enumerate(self.groups):
+            g.pool = PoolView(self, gid, self.num_pages)
         for g in self.groups:
             if allocate:
                 g.kv = torch.zeros((len(g.entries), 2, self.num_pages + 1, g.key.num_kv_heads, self.page_size * g.key.head_dim),
@@ -129,96 +152,79 @@ class CacheManager:
         esize = torch.empty((), dtype=self.dtype).element_size()
         return sum(len(g.entries) * 2 * g.key.num_kv_heads * self.page_size * g.key.head_dim * esize for g in self.groups)
 
+    def __del__(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.li_cm_destroy(h)
+
     def num_free_pages(self, group: int = 0) -> int:
-        return self.groups[group].pool.num_free
+        return self._lib.li_cm_num_free(self._h, group)
 
     def num_free_slots(self) -> int:
-        return self.slots.num_free
+        return self._lib.li_cm_num_free(self._h, -1)
 
     # ------------------------------------------------------------------
     def admit(self, request_id: int) -> RequestCache:
-        if request_id in self.live:
-            raise PoolError(f"request {request_id} is already admitted")
-        slot = self.slots.alloc(request_id)
+        slot = ctypes.c_int(0)
+        native.check(self._lib.li_cm_admit(self._h, int(request_id), ctypes.byref(slot)))
         for e in self.entries:
             if e.kind == "state" and e.writes and e.state is not None:
-                e.state[slot].zero_()
-        rc = RequestCache(request_id, slot, 0, [[] for _ in self.groups])
-        self.live[request_id] = rc
+                e.state[slot.value].zero_()
+        rc = RequestCache(int(request_id), slot.value, self)
+        self.live[rc.request_id] = rc
         return rc
 
-    def _first_needed_page(self, g: Group, length: int) -> int:
-        """First logical page that a query at position >= ``length`` can still read."""
-        if g.key.window is None:
-            return 0
-        first_key = max(0, length - g.key.window + 1)
-        return first_key // self.page_size
+    def table_length(self, rc: RequestCache, group: int) -> int:
+        n = self._lib.li_cm_table(self._h, rc.request_id, group, None, 0)
+        if n < 0:
+            raise PoolError(f"request {rc.request_id} is not live")
+        return n
+
+    def table(self, rc: RequestCache, group: int) -> List[int]:
+        """A copy of the request's block table in a group: logical page -> page id, -1 once given back."""
+        n = self._lib.li_cm_table(self._h, rc.request_id, group, None, 0)
+        if n < 0:
+            return []
+        out = (ctypes.c_int * max(n, 1))()
+        self._lib.li_cm_table(self._h, rc.request_id, group, out, n)
+        return list(out[:n])
 
     def pages_needed(self, rc: RequestCache, new_length: int) -> List[int]:
-        want = -(-new_length // self.page_size)
-        return [max(0, want - len(rc.tables[gid])) for gid in range(len(self.groups))]
+        need = (ctypes.c_int * max(len(self.groups), 1))()
+        native.check(self._lib.li_cm_pages_needed(self._h, rc.request_id, int(new_length), need))
+        return list(need[:len(self.groups)])
 
     def can_extend(self, rc: RequestCache, new_length: int, reserve: int = 0) -> bool:
         need = self.pages_needed(rc, new_length)
-        return all(n + reserve <= g.pool.num_free or n == 0 for n, g in zip(need, self.groups))
+        return all(n + reserve <= self.num_free_pages(gid) or n == 0 for gid, n in enumerate(need))
 
     def extend(self, rc: RequestCache, new_length: int) -> None:
         """Pages for positions up to ``new_length`` in every group; all or nothing."""
-        need = self.pages_needed(rc, new_length)
-        for n, g in zip(need, self.groups):
-            if n > g.pool.num_free:
-                raise OutOfPages(f"request {rc.request_id} needs {n} pages, {g.pool.num_free} are free")
-        for gid, (n, g) in enumerate(zip(need, self.groups)):
-            for _ in range(n):
-                rc.tables[gid].append(g.pool.alloc(rc.request_id))
+        native.check(self._lib.li_cm_extend(self._h, rc.request_id, int(new_length)))
 
     def commit(self, rc: RequestCache, new_length: int) -> None:
         """The step has written positions below ``new_length``.  Give back the
         pages of windowed groups that no further query can read."""
-        if new_length < rc.length:
-            raise PoolError("a request's length never shrinks")
-        rc.length = new_length
-        for gid, g in enumerate(self.groups):
-            if g.key.window is None:
-                continue
-            table = rc.tables[gid]
-            for lp in range(min(self._first_needed_page(g, new_length), len(table))):
-                if table[lp] != self.RELEASED:
-                    g.pool.free(table[lp], rc.request_id)
-                    table[lp] = self.RELEASED
+        native.check(self._lib.li_cm_commit(self._h, rc.request_id, int(new_length)))
+        rc.length = int(new_length)
 
     def release(self, rc: RequestCache) -> None:
         if self.live.get(rc.request_id) is not rc:
             raise PoolError(f"request {rc.request_id} is not live")
-        for gid, g in enumerate(self.groups):
-            # last page first, so that a request admitted next gets them in ascending order
-            for p in reversed(rc.tables[gid]):
-                if p != self.RELEASED:
-                    g.pool.free(p, rc.request_id)
-            rc.tables[gid] = []
-        self.slots.free(rc.slot, rc.request_id)
+        native.check(self._lib.li_cm_release(self._h, rc.request_id))
         rc.length = 0
         del self.live[rc.request_id]
 
     def slot_of(self, rc: RequestCache, group: int, position: int) -> int:
         """Flat index (page * page_size + offset) of a position in a group's pages."""
-        page = rc.tables[group][position // self.page_size]
+        page = self.table(rc, group)[position // self.page_size]
         if page == self.RELEASED:
             raise PoolError(f"position {position} of request {rc.request_id} lies on a page that was given back")
         return page * self.page_size + position % self.page_size
 
     def check(self) -> None:
         """Invariants, for tests: no page lost, held twice, or held by a dead request."""
-        self.slots.check()
-        for gid, g in enumerate(self.groups):
-            g.pool.check()
-            held = {}
-            for rc in self.live.values():
-                for p in rc.pages_held(gid):
-                    if p in held:
-                        raise PoolError(f"page {p} of group {gid} is held by requests {held[p]} and {rc.request_id}")
-                    held[p] = rc.request_id
-                    if g.pool.owner_of(p) != rc.request_id:
-                        raise PoolError(f"page {p} of group {gid}: table of {rc.request_id}, pool says {g.pool.owner_of(p)}")
-            if len(held) != g.pool.num_used:
-                raise PoolError(f"group {gid}: {g.pool.num_used} pages in use, {len(held)} in block tables")
+        native.check(self._lib.li_cm_check(self._h))
+        for rc in self.live.values():
+            if self._lib.li_cm_length(self._h, rc.request_id) != rc.length:
+                raise PoolError(f"request {rc.request_id}: length {rc.length} here, {self._lib.li_cm_length(self._h, rc.request_id)} in the host runtime")

@@ -1,5 +1,5 @@
 """Host-side bookkeeping of one pool of pages (or slots): a LIFO free list with
-ownership checks.
+ownership checks, kept by the host runtime (``csrc/host/runtime.cpp``).
 
 LitInfer keeps one such list per layer and checks only the range of a freed
 id (src/llaisys/kv_cache/block_kv_cache.hpp:34-59).  Here one list serves a
@@ -10,15 +10,12 @@ can neither be freed twice nor by a request that does not hold it.
 
 from __future__ import annotations
 
-from typing import List
+import ctypes
 
+from . import native
+from .native import OutOfPages, PoolError
 
-class PoolError(RuntimeError):
-    pass
-
-
-class OutOfPages(PoolError):
-    pass
+__all__ = ["OutOfPages", "PagePool", "PoolError"]
 
 
 class PagePool:
@@ -29,49 +26,58 @@ class PagePool:
             raise ValueError(f"a pool needs at least one {what}")
         self.num_pages = int(num_pages)
         self.what = what
-        self._free: List[int] = list(range(self.num_pages - 1, -1, -1))
-        self._owner: List[int] = [self.FREE] * self.num_pages
+        self._lib = native.library()
+        self._h = self._lib.li_pool_create(self.num_pages, what.encode())
+        if not self._h:
+            raise PoolError(f"cannot create a pool of {num_pages} {what}s")
+
+    def __del__(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.li_pool_destroy(h)
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._lib.li_pool_num_free(self._h)
 
     @property
     def num_used(self) -> int:
-        return self.num_pages - len(self._free)
+        return self.num_pages - self.num_free
 
     def owner_of(self, page: int) -> int:
-        return self._owner[page]
+        return self._lib.li_pool_owner(self._h, int(page))
 
     def alloc(self, owner: int) -> int:
-        if owner < 0:
-            raise PoolError("owner ids are non-negative")
-        if not self._free:
-            raise OutOfPages(f"no free {self.what} (all {self.num_pages} in use)")
-        page = self._free.pop()
-        self._owner[page] = owner
-        return page
+        page = ctypes.c_int(0)
+        native.check(self._lib.li_pool_alloc(self._h, int(owner), ctypes.byref(page)))
+        return page.value
 
     def free(self, page: int, owner: int) -> None:
-        if not 0 <= page < self.num_pages:
-            raise PoolError(f"{self.what} {page} is outside the pool of {self.num_pages}")
-        held_by = self._owner[page]
-        if held_by == self.FREE:
-            raise PoolError(f"{self.what} {page} freed twice")
-        if held_by != owner:
-            raise PoolError(f"{self.what} {page} is held by {held_by}, not by {owner}")
-        self._owner[page] = self.FREE
-        self._free.append(page)
+        native.check(self._lib.li_pool_free(self._h, int(page), int(owner)))
 
     def check(self) -> None:
         """Every page is either free exactly once or owned, never both."""
-        seen = set()
-        for p in self._free:
-            if p in seen:
-                raise PoolError(f"{self.what} {p} is on the free list twice")
-            if self._owner[p] != self.FREE:
-                raise PoolError(f"{self.what} {p} is free and owned by {self._owner[p]}")
-            seen.add(p)
-        for p, o in enumerate(self._owner):
-            if o == self.FREE and p not in seen:
-                raise PoolError(f"{self.what} {p} is lost: neither free nor owned")
+        native.check(self._lib.li_pool_check(self._h))
+
+
+class PoolView:
+    """One of a manager's pools (a group's pages, or the state slots), seen from outside: counts and ownership."""
+
+    def __init__(self, manager, which: int, num_pages: int) -> None:
+        self._m = manager
+        self._which = which
+        self.num_pages = num_pages
+
+    @property
+    def num_free(self) -> int:
+        return self._m._lib.li_cm_num_free(self._m._h, self._which)
+
+    @property
+    def num_used(self) -> int:
+        return self.num_pages - self.num_free
+
+    def owner_of(self, page: int) -> int:
+        return self._m._lib.li_cm_owner(self._m._h, self._which, int(page))
+
+    def check(self) -> None:
+        native.check(self._m._lib.li_cm_pool_check(self._m._h, self._which))

@@ -139,5 +139,54 @@ def ensure_built(verbose: bool = True, extra_flags: Optional[List[str]] = None) 
     return target
 
 
+# ---------------------------------------------------------------------------
+# the host runtime (csrc/host/*.cpp): plain C++, built with g++ into a library of its own, so that the engine's
+# bookkeeping also runs (and is tested) where there is neither a GPU nor nvcc
+# ---------------------------------------------------------------------------
+
+HOST_DIR = CSRC / "host"
+HOST_STEM = "liblitinfer_host"
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-Wall"]
+
+
+def _host_fingerprint() -> str:
+    h = hashlib.sha256()
+    for f in sorted(list(HOST_DIR.glob("*.cpp")) + list(HOST_DIR.glob("*.h"))):
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(HOST_FLAGS).encode())
+    return h.hexdigest()[:16]
+
+
+def ensure_host_built(verbose: bool = True) -> Path:
+    """Path of the up-to-date host runtime library, compiling it first if need be (a second or two)."""
+    name = f"{HOST_STEM}_{_host_fingerprint()}.so"
+    for d in _build_dirs():
+        if (d / name).is_file():
+            return d / name
+    cxx = next((c for c in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")) if c), None)
+    if cxx is None:
+        raise BuildError("no C++ compiler found (set CXX or install g++); the host runtime cannot be built")
+    srcs = sorted(HOST_DIR.glob("*.cpp"))
+    if not srcs:
+        raise BuildError(f"no .cpp sources in {HOST_DIR}")
+    out_dir = _writable_dir()
+    target = out_dir / name
+    tmp = out_dir / f".{name}.{os.getpid()}.tmp"
+    _say(f"compiling the host runtime ({len(srcs)} C++ file{'s' if len(srcs) > 1 else ''}) into {out_dir}", verbose)
+    r = subprocess.run([cxx, *HOST_FLAGS, "-I", str(HOST_DIR), *[str(s) for s in srcs], "-o", str(tmp)], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"{cxx} failed on the host runtime:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, target)
+    for old in out_dir.glob(f"{HOST_STEM}_*.so"):
+        if old != target:
+            try:
+                old.unlink()
+            except OSError:
+                pass
+    return target
+
+
 if __name__ == "__main__":
+    print(ensure_host_built())
     print(ensure_built())

@@ -1,0 +1,408 @@
+// The host side of the engine's memory: pools of pages and slots, the block tables of the live requests, and the
+// packer that turns a step's items into the one int32 buffer the kernels read.  Plain C++17 behind a C interface
+// (no CUDA, no Python): it is compiled with g++ into a library of its own, so that it also runs where there is no GPU.
+//
+// LitInfer keeps the same bookkeeping in C++, per layer: a free list and a block table for every layer
+// (src/llaisys/kv_cache/block_kv_cache.hpp:34-81) and a block table rebuilt and uploaded per layer and step
+// (src/llaisys/models/qwen2.cpp:993-1007).  Here a group of layers with equal needs shares one page-id space, a page
+// cannot be freed twice or by a request that does not hold it, and a step's metadata is packed once.
+//
+// Every function returns 0 or an error class (LI_HOST_* below) and leaves the message for li_host_last_error().
+#include <algorithm>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <unordered_map>
+#include <unordered_set>
+#include <vector>
+
+#define LI_HOST_EXPORT extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+enum { LI_HOST_OK = 0, LI_HOST_POOL = 1, LI_HOST_OUT_OF_PAGES = 2, LI_HOST_VALUE = 3, LI_HOST_INDEX = 4, LI_HOST_RUNTIME = 5 };
+
+thread_local char g_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+constexpr int kFree = -1;          // owner of a page nobody holds
+constexpr int kReleased = -1;      // block-table entry of a page that was given back behind a window
+
+// A LIFO free list with ownership: page 0 comes out first, a page just given back is the next one handed out.
+struct Pool {
+    int n = 0;
+    std::string what;
+    std::vector<int> free_list;
+    std::vector<int> owner;
+
+    Pool(int pages, const char* name) : n(pages), what(name), owner((size_t)pages, kFree) {
+        free_list.reserve((size_t)pages);
+        for (int p = pages - 1; p >= 0; --p) free_list.push_back(p);
+    }
+    int num_free() const { return (int)free_list.size(); }
+    int alloc(int who, int* page) {
+        if (who < 0) return fail(LI_HOST_POOL, "owner ids are non-negative");
+        if (free_list.empty()) return fail(LI_HOST_OUT_OF_PAGES, "no free %s (all %d in use)", what.c_str(), n);
+        *page = free_list.back();
+        free_list.pop_back();
+        owner[(size_t)*page] = who;
+        return LI_HOST_OK;
+    }
+    int release(int page, int who) {
+        if (page < 0 || page >= n) return fail(LI_HOST_POOL, "%s %d is outside the pool of %d", what.c_str(), page, n);
+        const int held_by = owner[(size_t)page];
+        if (held_by == kFree) return fail(LI_HOST_POOL, "%s %d freed twice", what.c_str(), page);
+        if (held_by != who) return fail(LI_HOST_POOL, "%s %d is held by %d, not by %d", what.c_str(), page, held_by, who);
+        owner[(size_t)page] = kFree;
+        free_list.push_back(page);
+        return LI_HOST_OK;
+    }
+    // every page is either free exactly once or owned, never both
+    int check() const {
+        std::vector<char> seen((size_t)n, 0);
+        for (int p : free_list) {
+            if (seen[(size_t)p]) return fail(LI_HOST_POOL, "%s %d is on the free list twice", what.c_str(), p);
+            if (owner[(size_t)p] != kFree) return fail(LI_HOST_POOL, "%s %d is free and owned by %d", what.c_str(), p, owner[(size_t)p]);
+            seen[(size_t)p] = 1;
+        }
+        for (int p = 0; p < n; ++p)
+            if (owner[(size_t)p] == kFree && !seen[(size_t)p]) return fail(LI_HOST_POOL, "%s %d is lost: neither free nor owned", what.c_str(), p);
+        return LI_HOST_OK;
+    }
+};
+
+struct Request {
+    int id = 0, slot = 0, length = 0;
+    std::vector<std::vector<int>> tables;          // per group: logical page -> page id, kReleased once given back
+};
+
+struct Manager {
+    int page_size, num_pages, max_requests;
+    std::vector<int> windows;                      // per group: keys a query still reads, 0 = all of them
+    std::vector<Pool> pools;
+    Pool slots;
+    std::unordered_map<int, Request> live;
+
+    Manager(int groups, const int* win, int pages, int page, int requests)
+        : page_size(page), num_pages(pages), max_requests(requests), windows(win, win + groups), slots(requests, "state slot") {
+        for (int g = 0; g < groups; ++g) pools.emplace_back(pages, "page");
+    }
+    Request* find(int id) {
+        auto it = live.find(id);
+        return it == live.end() ? nullptr : &it->second;
+    }
+    int blocks(int tokens) const { return (tokens + page_size - 1) / page_size; }
+    // first logical page that a query at a position >= length can still read
+    int first_needed_page(int g, int length) const {
+        if (windows[(size_t)g] <= 0) return 0;
+        const int first_key = length - windows[(size_t)g] + 1;
+        return first_key > 0 ? first_key / page_size : 0;
+    }
+};
+
+#define FIND(m, r, id)                                                                \
+    Request* r = (m)->find(id);                                                       \
+    if (!r) return fail(LI_HOST_POOL, "request %d is not live", id)
+
+}  // namespace
+
+LI_HOST_EXPORT const char* li_host_last_error() { return g_error; }
+
+// ---- a pool by itself ---------------------------------------------------------------------------------------------
+
+LI_HOST_EXPORT void* li_pool_create(int pages, const char* what) { return pages > 0 ? new Pool(pages, what ? what : "page") : nullptr; }
+LI_HOST_EXPORT void li_pool_destroy(void* p) { delete static_cast<Pool*>(p); }
+LI_HOST_EXPORT int li_pool_alloc(void* p, int owner, int* page) { return static_cast<Pool*>(p)->alloc(owner, page); }
+LI_HOST_EXPORT int li_pool_free(void* p, int page, int owner) { return static_cast<Pool*>(p)->release(page, owner); }
+LI_HOST_EXPORT int li_pool_num_free(void* p) { return static_cast<Pool*>(p)->num_free(); }
+LI_HOST_EXPORT int li_pool_owner(void* p, int page) {
+    Pool* pool = static_cast<Pool*>(p);
+    return page >= 0 && page < pool->n ? pool->owner[(size_t)page] : -2;
+}
+LI_HOST_EXPORT int li_pool_check(void* p) { return static_cast<Pool*>(p)->check(); }
+
+// ---- the manager ----------------------------------------------------------------------------------------------------
+
+// windows[g] <= 0: the group keeps every key
+LI_HOST_EXPORT void* li_cm_create(int groups, const int* windows, int num_pages, int page_size, int max_requests) {
+    if (groups < 0 || num_pages <= 0 || max_requests <= 0 || page_size < 1) return nullptr;
+    return new Manager(groups, windows, num_pages, page_size, max_requests);
+}
+LI_HOST_EXPORT void li_cm_destroy(void* h) { delete static_cast<Manager*>(h); }
+
+// which: -1 the state slots, else a group's pages
+static Pool* pool_of(Manager* m, int which) {
+    if (which < 0) return &m->slots;
+    return which < (int)m->pools.size() ? &m->pools[(size_t)which] : nullptr;
+}
+LI_HOST_EXPORT int li_cm_num_free(void* h, int which) {
+    Pool* p = pool_of(static_cast<Manager*>(h), which);
+    return p ? p->num_free() : -1;
+}
+LI_HOST_EXPORT int li_cm_owner(void* h, int which, int page) {
+    Pool* p = pool_of(static_cast<Manager*>(h), which);
+    return p && page >= 0 && page < p->n ? p->owner[(size_t)page] : -2;
+}
+LI_HOST_EXPORT int li_cm_pool_check(void* h, int which) {
+    Pool* p = pool_of(static_cast<Manager*>(h), which);
+    return p ? p->check() : fail(LI_HOST_POOL, "no pool %d", which);
+}
+
+LI_HOST_EXPORT int li_cm_admit(void* h, int id, int* slot) {
+    Manager* m = static_cast<Manager*>(h);
+    if (m->find(id)) return fail(LI_HOST_POOL, "request %d is already admitted", id);
+    if (int rc = m->slots.alloc(id, slot)) return rc;
+    Request r;
+    r.id = id;
+    r.slot = *slot;
+    r.tables.resize(m->pools.size());
+    m->live.emplace(id, std::move(r));
+    return LI_HOST_OK;
+}
+
+// pages each group lacks for positions up to new_length
+LI_HOST_EXPORT int li_cm_pages_needed(void* h, int id, int new_length, int* need) {
+    Manager* m = static_cast<Manager*>(h);
+    FIND(m, r, id);
+    const int want = m->blocks(new_length);
+    for (size_t g = 0; g < m->pools.size(); ++g) {
+        const int have = (int)r->tables[g].size();
+        need[g] = want > have ? want - have : 0;
+    }
+    return LI_HOST_OK;
+}
+
+// pages for positions up to new_length in every group; all or nothing
+LI_HOST_EXPORT int li_cm_extend(void* h, int id, int new_length) {
+    Manager* m = static_cast<Manager*>(h);
+    FIND(m, r, id);
+    const int want = m->blocks(new_length);
+    for (size_t g = 0; g < m->pools.size(); ++g) {
+        const int n = want - (int)r->tables[g].size();
+        if (n > m->pools[g].num_free())
+            return fail(LI_HOST_OUT_OF_PAGES, "request %d needs %d pages, %d are free", id, n, m->pools[g].num_free());
+    }
+    for (size_t g = 0; g < m->pools.size(); ++g)
+        while ((int)r->tables[g].size() < want) {
+            int page = 0;
+            if (int rc = m->pools[g].alloc(id, &page)) return rc;
+            r->tables[g].push_back(page);
+        }
+    return LI_HOST_OK;
+}
+
+// the step has written positions below new_length: pages of windowed groups that no further query can read go back
+LI_HOST_EXPORT int li_cm_commit(void* h, int id, int new_length) {
+    Manager* m = static_cast<Manager*>(h);
+    FIND(m, r, id);
+    if (new_length < r->length) return fail(LI_HOST_POOL, "a request's length never shrinks");
+    r->length = new_length;
+    for (size_t g = 0; g < m->pools.size(); ++g) {
+        if (m->windows[g] <= 0) continue;
+        std::vector<int>& t = r->tables[g];
+        const int upto = std::min(m->first_needed_page((int)g, new_length), (int)t.size());
+        for (int lp = 0; lp < upto; ++lp)
+            if (t[(size_t)lp] != kReleased) {
+                if (int rc = m->pools[g].release(t[(size_t)lp], id)) return rc;
+                t[(size_t)lp] = kReleased;
+            }
+    }
+    return LI_HOST_OK;
+}
+
+LI_HOST_EXPORT int li_cm_release(void* h, int id) {
+    Manager* m = static_cast<Manager*>(h);
+    FIND(m, r, id);
+    for (size_t g = 0; g < m->pools.size(); ++g) {
+        // last page first, so that a request admitted next gets them in ascending order
+        std::vector<int>& t = r->tables[g];
+        for (size_t i = t.size(); i-- > 0;)
+            if (t[i] != kReleased)
+                if (int rc = m->pools[g].release(t[i], id)) return rc;
+        t.clear();
+    }
+    if (int rc = m->slots.release(r->slot, id)) return rc;
+    m->live.erase(id);
+    return LI_HOST_OK;
+}
+
+LI_HOST_EXPORT int li_cm_length(void* h, int id) {
+    Request* r = static_cast<Manager*>(h)->find(id);
+    return r ? r->length : -1;
+}
+
+// a request's block table of one group: its length, and up to cap entries into out
+LI_HOST_EXPORT int li_cm_table(void* h, int id, int group, int* out, int cap) {
+    Manager* m = static_cast<Manager*>(h);
+    Request* r = m->find(id);
+    if (!r || group < 0 || group >= (int)m->pools.size()) return -1;
+    const std::vector<int>& t = r->tables[(size_t)group];
+    const int n = (int)t.size();
+    if (out && cap > 0) std::memcpy(out, t.data(), sizeof(int) * (size_t)std::min(n, cap));
+    return n;
+}
+
+// no page lost, held twice, or held by a request that is not live
+LI_HOST_EXPORT int li_cm_check(void* h) {
+    Manager* m = static_cast<Manager*>(h);
+    if (int rc = m->slots.check()) return rc;
+    for (size_t g = 0; g < m->pools.size(); ++g) {
+        if (int rc = m->pools[g].check()) return rc;
+        std::unordered_map<int, int> held;
+        for (const auto& kv : m->live)
+            for (int p : kv.second.tables[g]) {
+                if (p == kReleased) continue;
+                auto it = held.find(p);
+                if (it != held.end()) return fail(LI_HOST_POOL, "page %d of group %d is held by requests %d and %d", p, (int)g, it->second, kv.first);
+                held.emplace(p, kv.first);
+                if (m->pools[g].owner[(size_t)p] != kv.first)
+                    return fail(LI_HOST_POOL, "page %d of group %d: table of %d, pool says %d", p, (int)g, kv.first, m->pools[g].owner[(size_t)p]);
+            }
+        const int used = m->num_pages - m->pools[g].num_free();
+        if ((int)held.size() != used) return fail(LI_HOST_POOL, "group %d: %d pages in use, %d in block tables", (int)g, used, (int)held.size());
+    }
+    return LI_HOST_OK;
+}
+
+// ---- the packer -----------------------------------------------------------------------------------------------------
+//
+// Fills the packed int32 buffer of a step (engine/batch.py describes the layout; `offsets` gives where each field
+// starts: token_ids, positions, seq_of_token, q_start, ctx_lens, old_lens, state_slots, logit_rows, then per group
+// slot_mapping and block_table).  Items: request ids, token counts, tokens and wanted places, flattened.
+// starts[i] / olds[i] (or -1: the request's cached length): the position of the item's first token, and how many of the
+// request's keys were cached before the step; they differ from the cached length when a portion is given as single
+// tokens.  The batch is padded to S sequences, T tokens and R rows (their meaning as in batch.py: with pad_tokens the
+// padding sequences are empty but the last, else they hold one token each and want its row).  The buffer must be
+// zeroed and sized by the caller; T, S, R and the width of the block tables are the caller's too, checked here.
+LI_HOST_EXPORT int li_cm_pack_step(void* h, int n_items, const int* request_ids, const int* q_lens, const int* starts, const int* olds,
+                                   const int* tokens, const int* want_counts, const int* wants, int vocab, int S, int T, int R,
+                                   int pad_tokens, int max_blocks, int allow_repeat, int trash_page, int trash_slot, const int* offsets,
+                                   int* buf, long long buf_len, int* info /* R_real, max_q_len, max_ctx_len, singles */) {
+    Manager* m = static_cast<Manager*>(h);
+    const int G = (int)m->pools.size(), page = m->page_size;
+    if (n_items <= 0) return fail(LI_HOST_VALUE, "a step needs at least one item");
+    if (S < n_items) return fail(LI_HOST_VALUE, "%d items do not fit %d sequences", n_items, S);
+    long long t_real = 0, r_real = 0;
+    for (int i = 0; i < n_items; ++i) {
+        if (q_lens[i] <= 0) return fail(LI_HOST_VALUE, "an item without tokens");
+        t_real += q_lens[i];
+        r_real += want_counts[i];
+    }
+    const int pad_seq = S - n_items;
+    long long t_pad = 0;                                // tokens of the padding sequences
+    if (pad_tokens) {
+        t_pad = (long long)T - t_real;
+        if (t_pad < 0 || (t_pad > 0 && pad_seq == 0))
+            return fail(LI_HOST_VALUE, "%lld tokens in %d sequences cannot be padded to %d tokens in %d", t_real, n_items, T, S);
+        if (r_real > R) return fail(LI_HOST_VALUE, "%lld wanted rows do not fit the %d of the padded step", r_real, R);
+    } else {
+        t_pad = pad_seq;
+        if (t_real + t_pad != T || r_real + pad_seq != R) return fail(LI_HOST_VALUE, "the step's sizes do not match its items");
+    }
+    // the fields must fit the buffer
+    const int n_fields = 8 + 2 * G;
+    const long long sizes[8] = {T, T, T, (long long)S + 1, S, S, S, R};
+    for (int f = 0; f < n_fields; ++f) {
+        const long long len = f < 8 ? sizes[f] : ((f - 8) % 2 == 0 ? (long long)T : (long long)S * max_blocks);
+        if (offsets[f] < 0 || offsets[f] + len > buf_len) return fail(LI_HOST_VALUE, "field %d does not fit the step's buffer", f);
+    }
+    int* token_ids = buf + offsets[0];
+    int* positions = buf + offsets[1];
+    int* seq_of = buf + offsets[2];
+    int* q_start = buf + offsets[3];
+    int* ctx_lens = buf + offsets[4];
+    int* old_lens = buf + offsets[5];
+    int* state_slots = buf + offsets[6];
+    int* logit_rows = buf + offsets[7];
+
+    std::unordered_set<int> seen;
+    int tok = 0, row = 0, max_q = 0, max_ctx = 0, singles = 0, tok_in = 0, want_in = 0;
+    q_start[0] = 0;
+    for (int s = 0; s < n_items; ++s) {
+        const int id = request_ids[s], n = q_lens[s];
+        FIND(m, r, id);
+        if (!seen.insert(id).second && !allow_repeat) return fail(LI_HOST_VALUE, "request %d appears twice in one step", id);
+        const int start = starts && starts[s] >= 0 ? starts[s] : r->length;
+        const int old = olds && olds[s] >= 0 ? olds[s] : r->length;
+        for (int j = 0; j < n; ++j) {
+            const int t = tokens[tok_in + j];
+            if (t < 0 || t >= vocab) return fail(LI_HOST_INDEX, "request %d: token id outside [0, %d)", id, vocab);
+            token_ids[tok + j] = t;
+            positions[tok + j] = start + j;
+            seq_of[tok + j] = s;
+        }
+        for (int w = 0; w < want_counts[s]; ++w) {
+            const int place = wants[want_in + w];
+            if (place < 0 || place >= n) return fail(LI_HOST_INDEX, "request %d: wanted place %d is outside its %d tokens", id, place, n);
+            logit_rows[row++] = tok + place;
+        }
+        const int ctx = start + n;
+        ctx_lens[s] = ctx;
+        old_lens[s] = old;
+        state_slots[s] = r->slot;
+        const int nb = m->blocks(ctx);
+        if (nb > max_blocks) return fail(LI_HOST_VALUE, "request %d: %d pages do not fit block tables of %d", id, nb, max_blocks);
+        for (int g = 0; g < G; ++g) {
+            const std::vector<int>& table = r->tables[(size_t)g];
+            if ((int)table.size() < nb)
+                return fail(LI_HOST_RUNTIME, "request %d: pages for %d tokens are not allocated (group %d)", id, ctx, g);
+            int* bt = buf + offsets[8 + 2 * g + 1] + (size_t)s * max_blocks;
+            for (int b = 0; b < nb; ++b) bt[b] = table[(size_t)b] == kReleased ? trash_page : table[(size_t)b];
+            for (int b = nb; b < max_blocks; ++b) bt[b] = trash_page;
+            int* sm = buf + offsets[8 + 2 * g] + tok;
+            for (int j = 0; j < n; ++j) {
+                const int pos = start + j, pg = table[(size_t)(pos / page)];
+                if (pg == kReleased) return fail(LI_HOST_RUNTIME, "request %d: a new token falls on a page that was given back (group %d)", id, g);
+                sm[j] = pg * page + pos % page;
+            }
+        }
+        if (n > max_q) max_q = n;
+        if (ctx > max_ctx) max_ctx = ctx;
+        if (n == 1) ++singles;
+        tok += n;
+        tok_in += n;
+        want_in += want_counts[s];
+        q_start[s + 1] = tok;
+    }
+    const int r_real_i = row;
+    // padding: sequences at position 0 on the sink page
+    for (int s = n_items; s < S; ++s) {
+        int n = pad_tokens ? 0 : 1;
+        if (pad_tokens && s == S - 1) n = (int)t_pad;
+        for (int j = 0; j < n; ++j) {
+            token_ids[tok + j] = 0;
+            positions[tok + j] = j;
+            seq_of[tok + j] = s;
+            for (int g = 0; g < G; ++g) buf[offsets[8 + 2 * g] + tok + j] = trash_page * page + j % page;
+        }
+        ctx_lens[s] = n;
+        old_lens[s] = 0;
+        state_slots[s] = trash_slot;
+        for (int g = 0; g < G; ++g) {
+            int* bt = buf + offsets[8 + 2 * g + 1] + (size_t)s * max_blocks;
+            for (int b = 0; b < max_blocks; ++b) bt[b] = trash_page;
+        }
+        if (!pad_tokens) logit_rows[row++] = tok;       // padded items want a row too: the layout depends on S alone
+        if (n > max_q) max_q = n;
+        if (n > max_ctx) max_ctx = n;
+        tok += n;
+        q_start[s + 1] = tok;
+    }
+    if (pad_tokens)
+        while (row < R) logit_rows[row++] = T - 1;
+    if (tok != T || row != R) return fail(LI_HOST_VALUE, "the step's sizes do not match its items (%d tokens, %d rows)", tok, row);
+    info[0] = r_real_i;
+    info[1] = max_q;
+    info[2] = max_ctx;
+    info[3] = max_q > 1 ? singles : 0;
+    return LI_HOST_OK;
+}

@@ -16,12 +16,15 @@ and whose results nobody reads (a captured decode step has a fixed size).
 
 from __future__ import annotations
 
+import functools
+import itertools
 from dataclasses import dataclass, field
 from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
 
+from ..cache import native
 from ..cache.manager import CacheManager, RequestCache
 
 
@@ -79,14 +82,13 @@ def _round_up(x: int, m: int) -> int:
 class _TokenOf:
     """One token of an item, seen as a sequence of its own: the request's cache as far as this token."""
 
-    __slots__ = ("request_id", "length", "old_length", "slot", "tables")
+    __slots__ = ("request_id", "length", "old_length", "slot")
 
     def __init__(self, rc, offset: int) -> None:
         self.request_id = rc.request_id
         self.length = rc.length + offset
         self.old_length = rc.length
         self.slot = rc.slot
-        self.tables = rc.tables
 
 
 def split_into_tokens(items: Sequence[StepItem]) -> List[StepItem]:
@@ -108,10 +110,35 @@ def split_into_tokens(items: Sequence[StepItem]) -> List[StepItem]:
     return out
 
 
+_FIELDS = ("token_ids", "positions", "seq_of_token", "q_start", "ctx_lens", "old_lens", "state_slots", "logit_rows")
+
+
+@functools.lru_cache(maxsize=512)
+def _fields(T: int, S: int, R: int, G: int, mb: int):
+    """Where each field starts in the packed buffer (16-byte aligned starts), the buffer's length, and the starts as
+    the array the host runtime takes."""
+    fields = {}
+    off = 0
+    for name, n in zip(_FIELDS, (T, T, T, S + 1, S, S, S, R)):
+        fields[name] = (off, n)
+        off += _round_up(max(n, 1), 4)
+    for gid in range(G):
+        fields[f"slot_mapping{gid}"] = (off, T)
+        off += _round_up(max(T, 1), 4)
+        fields[f"block_table{gid}"] = (off, S * mb)
+        off += _round_up(max(S * mb, 1), 4)
+    starts = np.asarray([o for o, _ in fields.values()], dtype=np.int32)
+    return fields, off, starts
+
+
+def _ints(values) -> np.ndarray:
+    return np.asarray(values, dtype=np.int32) if len(values) else np.zeros(1, dtype=np.int32)
+
+
 def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int, pad_seqs: int = 0,
               max_blocks: Optional[int] = None, tokens_of_one_request: bool = False, pad_tokens: int = 0,
               pad_rows: int = 0):
-    """Host side: validate the items and fill the packed int32 array.
+    """Host side: validate the items and fill the packed int32 array (the host runtime does both, in C++).
 
     Returns (array, layout) where layout maps field name -> (offset, length) and
     carries the scalar sizes.  Pages for all tokens must already be allocated.
@@ -119,123 +146,56 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
     ``pad_tokens`` (with ``pad_seqs`` and ``pad_rows``): the step is padded to exactly that many tokens, sequences
     and logit rows, for a captured step of a fixed shape: the padding sequences are empty but the last, which takes
     the padding tokens; it starts at position 0, writes to the sink page and sees nothing else; the real rows come
-    first among the logit rows, and ``layout["R_real"]`` says how many they are.
+    first among the logit rows, and ``layout["R_real"]`` says how many they are.  Without ``pad_tokens`` the padding
+    sequences hold one token each and want its row.
     """
     S_real = len(items)
     if S_real == 0:
         raise ValueError("a step needs at least one item")
-    S = max(S_real, pad_seqs)
+    caches = [it.cache for it in items]
     q_lens = [len(it.tokens) for it in items]
     if min(q_lens) <= 0:
         raise ValueError("an item without tokens")
-    if pad_tokens:
-        rest = pad_tokens - sum(q_lens)
-        if rest < 0 or (rest > 0 and S == S_real):
-            raise ValueError(f"{sum(q_lens)} tokens in {S_real} sequences cannot be padded to {pad_tokens} tokens in {S}")
-        q_lens += [0] * (S - S_real)
-        q_lens[-1] += rest
-    else:
-        q_lens += [1] * (S - S_real)
-    T = sum(q_lens)
+    starts = [c.length for c in caches]
+    olds = [c.old_length for c in caches] if tokens_of_one_request else starts
+    counts = [len(it.want) for it in items]
+    S = max(S_real, pad_seqs)
+    T_real, R_real = sum(q_lens), sum(counts)
     page = manager.page_size
-    q_start = np.zeros(S + 1, dtype=np.int32)
-    np.cumsum(q_lens, out=q_start[1:])
-    ctx = np.empty(S, dtype=np.int32)
-    old = np.zeros(S, dtype=np.int32)
-    slots = np.empty(S, dtype=np.int32)
-    token_ids = np.zeros(T, dtype=np.int32)
-    positions = np.zeros(T, dtype=np.int32)
-    seq_of = np.empty(T, dtype=np.int32)
-    rows: List[int] = []
-    seen = set()
-    for s, it in enumerate(items):
-        rc = it.cache
-        if rc.request_id in seen and not tokens_of_one_request:
-            raise ValueError(f"request {rc.request_id} appears twice in one step")
-        seen.add(rc.request_id)
-        n, lo = q_lens[s], int(q_start[s])
-        toks = np.asarray(it.tokens, dtype=np.int64)
-        if toks.min() < 0 or toks.max() >= vocab_size:
-            raise IndexError(f"request {rc.request_id}: token id outside [0, {vocab_size})")
-        token_ids[lo:lo + n] = toks
-        positions[lo:lo + n] = np.arange(rc.length, rc.length + n)
-        seq_of[lo:lo + n] = s
-        ctx[s] = rc.length + n
-        old[s] = getattr(rc, "old_length", rc.length)
-        slots[s] = rc.slot
-        for w in it.want:
-            if not 0 <= w < n:
-                raise IndexError(f"request {rc.request_id}: wanted place {w} is outside its {n} tokens")
-            rows.append(lo + int(w))
-    R_real = len(rows)
-    for s in range(S_real, S):
-        lo, n = int(q_start[s]), q_lens[s]
-        seq_of[lo:lo + n] = s
-        positions[lo:lo + n] = np.arange(n)
-        ctx[s] = n
-        slots[s] = manager.trash_slot
-        if not pad_tokens:
-            rows.append(lo)                  # padded items want a row too: the layout depends on S alone
+    need_blocks = max(-(-(st + n) // page) for st, n in zip(starts, q_lens))
     if pad_tokens:
-        if len(rows) > pad_rows:
-            raise ValueError(f"{len(rows)} wanted rows do not fit the {pad_rows} of the padded step")
-        rows.extend([T - 1] * (pad_rows - len(rows)))
-    R = len(rows)
-    need_blocks = max(-(-int(c) // page) for c in ctx)
+        rest = pad_tokens - T_real
+        if rest < 0 or (rest > 0 and S == S_real):
+            raise ValueError(f"{T_real} tokens in {S_real} sequences cannot be padded to {pad_tokens} tokens in {S}")
+        if R_real > pad_rows:
+            raise ValueError(f"{R_real} wanted rows do not fit the {pad_rows} of the padded step")
+        T, R = int(pad_tokens), int(pad_rows)
+        need_blocks = max(need_blocks, -(-rest // page))
+    else:
+        T, R = T_real + S - S_real, R_real + S - S_real
     G = len(manager.groups)
     mb = max(need_blocks, max_blocks or 0, 1)
-    fields = {}
-    off = 0
+    fields, total, offsets = _fields(T, S, R, G, mb)
+    buf = np.zeros(total, dtype=np.int32)
+    if T_real == S_real:
+        tokens = _ints([it.tokens[0] for it in items])
+    else:
+        tokens = _ints(list(itertools.chain.from_iterable(it.tokens for it in items)))
+    wants = _ints(list(itertools.chain.from_iterable(it.want for it in items))) if R_real else _ints(())
+    ids, lens, first, old, cnt = _ints([c.request_id for c in caches]), _ints(q_lens), _ints(starts), _ints(olds), _ints(counts)
+    info = np.zeros(4, dtype=np.int32)
+    native.check(manager._lib.li_cm_pack_step(
+        manager._h, S_real, ids.ctypes.data, lens.ctypes.data, first.ctypes.data, old.ctypes.data, tokens.ctypes.data,
+        cnt.ctypes.data, wants.ctypes.data, int(vocab_size), S, T, R, int(pad_tokens), mb, 1 if tokens_of_one_request else 0,
+        manager.trash_page, manager.trash_slot, offsets.ctypes.data, buf.ctypes.data, total, info.ctypes.data))
 
-    def place(name, n):
-        nonlocal off
-        fields[name] = (off, n)
-        off += _round_up(max(n, 1), 4)       # 16-byte aligned starts
-
-    for name, n in (("token_ids", T), ("positions", T), ("seq_of_token", T), ("q_start", S + 1),
-                    ("ctx_lens", S), ("old_lens", S), ("state_slots", S), ("logit_rows", R)):
-        place(name, n)
-    for gid in range(G):
-        place(f"slot_mapping{gid}", T)
-        place(f"block_table{gid}", S * mb)
-    buf = np.zeros(off, dtype=np.int32)
-
-    def put(name, arr):
+    def host(name):
         o, n = fields[name]
-        buf[o:o + n] = arr
+        return buf[o:o + n].tolist()
 
-    put("token_ids", token_ids)
-    put("positions", positions)
-    put("seq_of_token", seq_of)
-    put("q_start", q_start)
-    put("ctx_lens", ctx)
-    put("old_lens", old)
-    put("state_slots", slots)
-    put("logit_rows", np.asarray(rows, dtype=np.int32))
-    trash = manager.trash_page
-    for gid in range(G):
-        bt = np.full((S, mb), trash, dtype=np.int32)
-        sm = trash * page + positions % page             # padding tokens: the sink page, the slot of their position
-        for s, it in enumerate(items):
-            rc = it.cache
-            table = rc.tables[gid]
-            nb = -(-int(ctx[s]) // page)
-            if len(table) < nb:
-                raise RuntimeError(f"request {rc.request_id}: pages for {int(ctx[s])} tokens are not allocated (group {gid})")
-            row = np.asarray(table[:nb], dtype=np.int32)
-            row = np.where(row < 0, trash, row)
-            bt[s, :nb] = row
-            lo, n = int(q_start[s]), q_lens[s]
-            pos = positions[lo:lo + n]
-            pages = row[pos // page]
-            if (pages == trash).any():
-                raise RuntimeError(f"request {rc.request_id}: a new token falls on a page that was given back (group {gid})")
-            sm[lo:lo + n] = pages * page + pos % page
-        put(f"block_table{gid}", bt.reshape(-1))
-        put(f"slot_mapping{gid}", sm)
-    singles = sum(1 for q in q_lens[:S_real] if q == 1) if max(q_lens) > 1 else 0
-    layout = dict(fields=fields, T=T, S=S, R=R, R_real=R_real, G=G, max_blocks=mb, singles=singles, max_q_len=max(q_lens), max_ctx_len=int(ctx.max()),
-                  q_start=q_start.tolist(), ctx_lens=ctx.tolist(), state_slots=slots.tolist())
+    layout = dict(fields=fields, T=T, S=S, R=R, R_real=int(info[0]), G=G, max_blocks=mb, singles=int(info[3]),
+                  max_q_len=int(info[1]), max_ctx_len=int(info[2]),
+                  q_start=host("q_start"), ctx_lens=host("ctx_lens"), state_slots=host("state_slots"))
     return buf, layout
 
 

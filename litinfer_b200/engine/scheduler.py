@@ -187,7 +187,7 @@ class Scheduler:
         page = self.manager.page_size
         most = want
         for gid, g in enumerate(self.manager.groups):
-            have = len(rc.tables[gid]) * page - rc.length
+            have = rc.num_blocks(gid) * page - rc.length
             most = min(most, have + g.pool.num_free * page)
         return max(0, most)
 

@@ -35,11 +35,6 @@ class _DecodeGraph:
         self.meta_buf = meta_buf
         self.logits = logits
         self.layout = layout
-        # the packed metadata of the last step through this graph, to be advanced in place
-        # when the same requests come back with one more token each
-        self.last_key = None
-        self.last_lengths = None
-        self.last_buf = None
 
 
 class ModelRunner:
@@ -214,18 +209,13 @@ class ModelRunner:
         split = rows is not None
         wanted = [bool(len(it.want)) for it in items]
         g = self._graphs.get(B)
-        buf = self._advance(g, items) if g is not None and not split else None
-        if buf is None:
-            full = [StepItem(it.cache, it.tokens, (0,)) for it in items]
-            buf, layout = pack_step(full, self.manager, self.model.spec.vocab_size, pad_seqs=B, max_blocks=max_blocks,
-                                    tokens_of_one_request=split)
-            if g is None:
-                g = self._capture(B, max_blocks, buf, layout)
-            if layout["fields"] != g.layout["fields"]:
-                raise RuntimeError("decode graph: metadata layout changed between capture and replay")
-            g.last_buf = buf
-        g.last_key = None if split else tuple(it.cache.request_id for it in items)
-        g.last_lengths = [it.cache.length for it in items]
+        full = [StepItem(it.cache, it.tokens, (0,)) for it in items]
+        buf, layout = pack_step(full, self.manager, self.model.spec.vocab_size, pad_seqs=B, max_blocks=max_blocks,
+                                tokens_of_one_request=split)
+        if g is None:
+            g = self._capture(B, max_blocks, buf, layout)
+        if layout["fields"] != g.layout["fields"]:
+            raise RuntimeError("decode graph: metadata layout changed between capture and replay")
         self._upload(buf, g.meta_buf)
         if token_source is not None:
             o_tok = g.layout["fields"]["token_ids"][0]
@@ -237,45 +227,6 @@ class ModelRunner:
         if rows == list(range(B)):
             return g.logits
         return g.logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else g.logits[:0]
-
-    def _advance(self, g: _DecodeGraph, items: List[StepItem]) -> Optional[np.ndarray]:
-        """The common case of decoding: the requests of the last step through this graph, in
-        the same order, each one token further.  Then only token ids, positions, context
-        lengths, the new tokens' slots and (at a page's first slot) one block-table entry
-        change; they are patched into the last packed buffer instead of packing afresh.
-        Returns None when the step is anything else."""
-        if g.last_buf is None or g.last_key != tuple(it.cache.request_id for it in items):
-            return None
-        mgr = self.manager
-        if any(grp.key.window is not None for grp in mgr.groups):
-            return None                                   # pages behind a window leave the table: pack afresh
-        vocab = self.model.spec.vocab_size
-        page = mgr.page_size
-        buf, f = g.last_buf, g.layout["fields"]
-        mb = g.layout["max_blocks"]
-        o_tok, o_pos, o_ctx, o_old = f["token_ids"][0], f["positions"][0], f["ctx_lens"][0], f["old_lens"][0]
-        for i, it in enumerate(items):
-            rc = it.cache
-            if rc.length != g.last_lengths[i] + 1:
-                return None
-            tok = int(it.tokens[0])
-            if not 0 <= tok < vocab:
-                raise IndexError(f"request {rc.request_id}: token id outside [0, {vocab})")
-            pos = rc.length
-            if pos // page >= mb:
-                return None
-            buf[o_tok + i] = tok
-            buf[o_pos + i] = pos
-            buf[o_ctx + i] = pos + 1
-            buf[o_old + i] = pos
-            for gid in range(len(mgr.groups)):
-                table = rc.tables[gid]
-                if len(table) <= pos // page:
-                    raise RuntimeError(f"request {rc.request_id}: pages for {pos + 1} tokens are not allocated (group {gid})")
-                p = table[pos // page]
-                buf[f[f"block_table{gid}"][0] + i * mb + pos // page] = p
-                buf[f[f"slot_mapping{gid}"][0] + i] = p * page + pos % page
-        return buf
 
     def _capture(self, B: Optional[int], max_blocks: int, buf: np.ndarray, layout, max_q_len: int = 1, singles: int = 0) -> _DecodeGraph:
         """Capture the model's forward pass over the packed step.  ``B``: the decode bucket it is kept under (None: the

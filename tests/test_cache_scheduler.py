@@ -240,3 +240,83 @@ def test_sampling_params_greedy_rule():
     assert SamplingParams().greedy                                     # top_k = 1 by default (qwen2.py:305-311)
     assert SamplingParams(temperature=0.0, top_k=50).greedy            # temperature <= 0 (qwen2.cpp:893-895)
     assert not SamplingParams(temperature=0.8, top_k=0).greedy
+
+
+# --------------------------------------------------------------------------
+# the packer of a step's metadata (host runtime) against the plain one
+# --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("window", [None, 20])
+def test_packed_steps_equal_the_plain_packer(seed, window):
+    """Random batches (portions, single tokens, requests with pages behind a window given back) packed by the host
+    runtime and by the plain numpy packer of the tests: the same buffer and the same layout, plainly, padded to a decode
+    bucket, padded to a captured shape, and as single tokens of one request."""
+    import numpy as np
+
+    import plain_pack
+    from litinfer_b200.engine import StepItem
+    from litinfer_b200.engine.batch import pack_step, split_into_tokens
+
+    rnd = random.Random(seed)
+    m = manager(num_pages=200, max_requests=24, window=window, two_groups=True)
+    vocab = 500
+    for _ in range(12):
+        items = []
+        for i in range(rnd.randint(1, 12)):
+            rc = m.admit(i)
+            had = rnd.choice([0, 0, 7, 16, 40, 65])
+            if had:
+                m.extend(rc, had)
+                m.commit(rc, had)
+            q = rnd.choice([1, 1, 1, 2, 9, 33])
+            m.extend(rc, had + q)
+            items.append(StepItem(rc, [rnd.randrange(vocab) for _ in range(q)], tuple(sorted(rnd.sample(range(q), rnd.randint(0, min(q, 3)))))))
+        T, S, R = sum(len(it.tokens) for it in items), len(items), sum(len(it.want) for it in items)
+        cases = [dict(), dict(max_blocks=16)]
+        if all(len(it.tokens) == 1 for it in items):
+            cases.append(dict(pad_seqs=16, max_blocks=16))
+        cases.append(dict(pad_seqs=S + 2, max_blocks=16, pad_tokens=T + 21, pad_rows=max(R, S + 2)))
+        cases.append(dict(pad_seqs=S, max_blocks=16, pad_tokens=T, pad_rows=R + 1))
+        for kw in cases:
+            a, la = pack_step(items, m, vocab, **kw)
+            b, lb = plain_pack.pack_step(items, m, vocab, **kw)
+            assert np.array_equal(a, b), f"buffers differ for {kw}"
+            assert la == lb, f"layouts differ for {kw}"
+        singles = split_into_tokens([StepItem(it.cache, it.tokens, ()) for it in items])
+        a, la = pack_step(singles, m, vocab, pad_seqs=len(singles) + 3, max_blocks=16, tokens_of_one_request=True)
+        b, lb = plain_pack.pack_step(singles, m, vocab, pad_seqs=len(singles) + 3, max_blocks=16, tokens_of_one_request=True)
+        assert np.array_equal(a, b) and la == lb
+        for it in items:
+            m.release(it.cache)
+        m.check()
+
+
+def test_the_packer_refuses_what_the_plain_one_refuses():
+    from litinfer_b200.engine import StepItem
+    from litinfer_b200.engine.batch import pack_step
+
+    m = manager(num_pages=8, window=20)
+    a, b = m.admit(0), m.admit(1)
+    m.extend(a, 40)
+    m.commit(a, 37)
+    m.extend(b, 5)
+    with pytest.raises(ValueError, match="at least one item"):
+        pack_step([], m, 100)
+    with pytest.raises(ValueError, match="without tokens"):
+        pack_step([StepItem(a, [], ())], m, 100)
+    with pytest.raises(ValueError, match="twice"):
+        pack_step([StepItem(a, [1], ()), StepItem(a, [2], ())], m, 100)
+    with pytest.raises(IndexError, match="token id"):
+        pack_step([StepItem(a, [100], ())], m, 100)
+    with pytest.raises(IndexError, match="wanted place"):
+        pack_step([StepItem(a, [1, 2], (2,))], m, 100)
+    with pytest.raises(RuntimeError, match="not allocated"):
+        pack_step([StepItem(a, [1] * 12, ())], m, 100)                # 37 + 12 tokens need a fourth page
+    with pytest.raises(ValueError, match="cannot be padded"):
+        pack_step([StepItem(b, [1, 2], ())], m, 100, pad_seqs=1, pad_tokens=8, pad_rows=1)
+    with pytest.raises(ValueError, match="wanted rows"):
+        pack_step([StepItem(b, [1, 2], (0, 1))], m, 100, pad_seqs=2, pad_tokens=8, pad_rows=1)
+    m.release(a)
+    with pytest.raises(PoolError, match="not live"):
+        pack_step([StepItem(a, [1], ())], m, 100)
