@@ -174,6 +174,21 @@ class CacheManager:
         self.live[rc.request_id] = rc
         return rc
 
+    def adopt(self, request_id: int, slot: int) -> RequestCache:
+        """The host runtime admitted a request by itself (its scheduler does): the picture of it here."""
+        for e in self.entries:
+            if e.kind == "state" and e.writes and e.state is not None:
+                e.state[slot].zero_()
+        rc = RequestCache(int(request_id), int(slot), self)
+        self.live[rc.request_id] = rc
+        return rc
+
+    def dropped(self, rc: RequestCache) -> None:
+        """The host runtime gave a request's pages and slot back by itself: forget the picture of it here."""
+        if self.live.get(rc.request_id) is rc:
+            del self.live[rc.request_id]
+        rc.length = 0
+
     def table_length(self, rc: RequestCache, group: int) -> int:
         n = self._lib.li_cm_table(self._h, rc.request_id, group, None, 0)
         if n < 0:

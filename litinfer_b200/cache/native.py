@@ -46,6 +46,15 @@ _SIGNATURES = {
     "li_cm_length": (I, [P, I]),
     "li_cm_table": (I, [P, I, I, IP, I]),
     "li_cm_check": (I, [P]),
+    "li_sched_create": (P, [P, I, I, I, I]),
+    "li_sched_destroy": (None, [P]),
+    "li_sched_set_eos": (I, [P, P, I]),
+    "li_sched_add": (I, [P, I, I, I]),
+    "li_sched_counts": (I, [P, IP, IP, IP]),
+    "li_sched_schedule": (I, [P, P, I, IP, P, I, IP]),
+    "li_sched_update": (I, [P, I, P, P, P, P]),
+    "li_sched_abort": (I, [P, I, IP]),
+    "li_sched_forget": (I, [P, I]),
     "li_cm_pack_step": (I, [P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, ctypes.c_longlong, P]),
 }
 

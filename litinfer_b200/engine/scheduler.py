@@ -26,18 +26,22 @@ here instead:
   exactly ``max_new_tokens`` tokens (``<= 0`` means 512, qwen2.cpp:795).
   Pages are given back at once.
 
-The scheduler is host-only logic over the cache manager's bookkeeping; it
-needs no device.
+The decisions are taken in the host runtime (``csrc/host/scheduler.cpp``, C++)
+over the cache manager's bookkeeping; this module holds the requests' tokens
+and outputs and mirrors what the runtime did.  Host-only logic: no device.
 """
 
 from __future__ import annotations
 
+import ctypes
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, List, Optional, Sequence, Tuple
+from typing import Deque, Dict, List, Optional, Sequence
 
+import numpy as np
+
+from ..cache import native
 from ..cache.manager import CacheManager, RequestCache
-from ..cache.pool import OutOfPages
 from ..sampling.sampler import SamplingParams
 
 DEFAULT_MAX_NEW_TOKENS = 512        # src/llaisys/models/qwen2.cpp:795
@@ -112,17 +116,50 @@ class RequestRefused(ValueError):
 
 
 class Scheduler:
+    """The Python face of the scheduler in the host runtime (``csrc/host/scheduler.cpp``): the decisions are taken
+    there, over the cache manager's bookkeeping; the requests' tokens, sampling parameters and outputs live here."""
+
+    _REASONS = {1: "eos", 2: "length", 3: "max_positions"}
+
     def __init__(self, manager: CacheManager, config: SchedulerConfig, max_positions: int, eos_token_ids: Sequence[int] = ()) -> None:
         self.manager = manager
         self.config = config
         self.max_positions = int(max_positions)
-        self.eos = set(int(e) for e in eos_token_ids)
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self.requests: Dict[int, Request] = {}
         self._next_id = 0
         self._clock = 0
-        self.num_preemptions = 0
+        self._lib = native.library()
+        self._h = self._lib.li_sched_create(manager._h, config.max_num_seqs, config.max_tokens_per_step, config.prefill_chunk,
+                                            self.max_positions)
+        if not self._h:
+            raise RuntimeError("the host runtime could not create the scheduler")
+        cap = 4 * config.max_num_seqs + 64
+        self._items = np.zeros(4 * cap, dtype=np.int32)
+        self._events = np.zeros(3 * 8 * cap, dtype=np.int32)
+        self.eos = eos_token_ids
+
+    def __del__(self) -> None:
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.li_sched_destroy(h)
+
+    @property
+    def eos(self):
+        return self._eos
+
+    @eos.setter
+    def eos(self, ids) -> None:
+        self._eos = set(int(e) for e in ids)
+        arr = np.asarray(sorted(self._eos) or [0], dtype=np.int32)
+        native.check(self._lib.li_sched_set_eos(self._h, arr.ctypes.data, len(self._eos)))
+
+    @property
+    def num_preemptions(self) -> int:
+        w, r, p = ctypes.c_int(0), ctypes.c_int(0), ctypes.c_int(0)
+        self._lib.li_sched_counts(self._h, ctypes.byref(w), ctypes.byref(r), ctypes.byref(p))
+        return p.value
 
     # ------------------------------------------------------------------
     def add_request(self, prompt: Sequence[int], max_new_tokens: int = 128, params: Optional[SamplingParams] = None) -> int:
@@ -142,6 +179,7 @@ class Scheduler:
                 f"the request may hold {most} tokens ({pages} pages), the cache has {self.manager.num_pages} pages")
         rid = self._next_id
         self._next_id += 1
+        native.check(self._lib.li_sched_add(self._h, rid, len(prompt), int(max_new_tokens)))
         req = Request(rid, prompt, int(max_new_tokens), params or SamplingParams())
         self.requests[rid] = req
         self.waiting.append(req)
@@ -154,9 +192,11 @@ class Scheduler:
         req = self.requests[rid]
         if req.finished:
             return
+        was_running = ctypes.c_int(0)
+        native.check(self._lib.li_sched_abort(self._h, rid, ctypes.byref(was_running)))
         if req.status == "running":
             self.running.remove(req)
-            self._give_back(req)
+            self._dropped(req)
         else:
             self.waiting.remove(req)
         req.status, req.finish_reason = "finished", "aborted"
@@ -165,121 +205,76 @@ class Scheduler:
         """Drop a finished request's record (LitInfer keeps them forever, qwen2.cpp:797-798)."""
         if not self.requests[rid].finished:
             raise ValueError(f"request {rid} is not finished")
+        native.check(self._lib.li_sched_forget(self._h, rid))
         del self.requests[rid]
 
     # ------------------------------------------------------------------
-    def _give_back(self, req: Request) -> None:
+    def _dropped(self, req: Request) -> None:
+        """The host runtime gave the request's pages and slot back: forget its cache here too."""
         if req.cache is not None:
-            self.manager.release(req.cache)
+            self.manager.dropped(req.cache)
             req.cache = None
 
-    def _preempt(self, req: Request) -> None:
-        self.running.remove(req)
-        self._give_back(req)
-        req.status = "waiting"
-        req.preemptions += 1
-        self.num_preemptions += 1
-        self.waiting.appendleft(req)
-
-    def _fit(self, req: Request, want: int) -> int:
-        """How many of the next ``want`` tokens fit into the free pages of every group."""
-        rc = req.cache
-        page = self.manager.page_size
-        most = want
-        for gid, g in enumerate(self.manager.groups):
-            have = rc.num_blocks(gid) * page - rc.length
-            most = min(most, have + g.pool.num_free * page)
-        return max(0, most)
-
-    def schedule(self) -> List[ScheduledItem]:
-        """Pick the next step's items and allocate their pages."""
-        cfg = self.config
-        preempted_before = self.num_preemptions
-        while True:
-            budget = cfg.max_tokens_per_step
-            items: List[ScheduledItem] = []
-            picked = set()
-            # 1. decoding requests, oldest first; preempt the youngest when a page is missing
-            for req in list(self.running):
-                if req.status != "running" or budget <= 0:
-                    continue
-                if req.num_tokens - req.num_cached != 1:
-                    continue
-                while True:
-                    try:
-                        self.manager.extend(req.cache, req.num_cached + 1)
-                        break
-                    except OutOfPages:
-                        victim = self.running[-1]
-                        self._preempt(victim)
-                        if victim is req:
-                            break
-                if req.status != "running":
-                    continue
-                items.append(ScheduledItem(req, req.num_cached, 1, True))
-                picked.add(req.id)
-                budget -= 1
-            # 2. prompt portions of running requests
-            for req in self.running:
-                if budget <= 0:
-                    break
-                if req.id in picked:
-                    continue
-                left = req.num_tokens - req.num_cached
-                n = self._fit(req, min(left, cfg.prefill_chunk, budget))
-                if n <= 0:
-                    continue
-                self.manager.extend(req.cache, req.num_cached + n)
-                items.append(ScheduledItem(req, req.num_cached, n, n == left))
-                picked.add(req.id)
-                budget -= n
-            # 3. admit waiting requests, in order
-            while self.waiting and budget > 0 and len(self.running) < cfg.max_num_seqs and self.manager.num_free_slots() > 0:
-                if self.num_preemptions != preempted_before:
-                    break                   # a request was just preempted for lack of pages: admit nobody this step
-                req = self.waiting[0]
-                req.cache = self.manager.admit(req.id)
-                n = self._fit(req, min(req.num_tokens, cfg.prefill_chunk, budget))
-                if n <= 0:
-                    self._give_back(req)
-                    break
-                self.waiting.popleft()
+    def _apply(self, n_events: int) -> None:
+        """What the host runtime did to the requests while it scheduled, in order."""
+        ev = self._events
+        for i in range(n_events):
+            kind, rid, arg = int(ev[3 * i]), int(ev[3 * i + 1]), int(ev[3 * i + 2])
+            req = self.requests[rid]
+            if kind == 1:                                   # admitted, with its state slot
+                self._dropped(req)
+                req.cache = self.manager.adopt(rid, arg)
+                self.waiting.remove(req)
                 req.status = "running"
                 req.admitted_at = self._clock
                 self._clock += 1
                 self.running.append(req)
-                self.manager.extend(req.cache, n)
-                items.append(ScheduledItem(req, 0, n, n == req.num_tokens))
-                picked.add(req.id)
-                budget -= n
-            if items or not self.running:
-                return items
-            # nothing can run although requests are live: free the youngest one's pages
-            self._preempt(self.running[-1])
+            elif kind == 2:                                 # preempted: back to the head of the queue, to be recomputed
+                self.running.remove(req)
+                self._dropped(req)
+                req.status = "waiting"
+                req.preemptions += 1
+                self.waiting.appendleft(req)
+            else:
+                raise RuntimeError(f"unknown scheduler event {kind}")
+
+    def schedule(self) -> List[ScheduledItem]:
+        """Pick the next step's items and allocate their pages."""
+        n_items, n_events = ctypes.c_int(0), ctypes.c_int(0)
+        rc = self._lib.li_sched_schedule(self._h, self._items.ctypes.data, self._items.size // 4, ctypes.byref(n_items),
+                                         self._events.ctypes.data, self._events.size // 3, ctypes.byref(n_events))
+        self._apply(min(n_events.value, self._events.size // 3))
+        native.check(rc)
+        it = self._items
+        return [ScheduledItem(self.requests[int(it[4 * i])], int(it[4 * i + 1]), int(it[4 * i + 2]), bool(it[4 * i + 3]))
+                for i in range(n_items.value)]
 
     # ------------------------------------------------------------------
     def update(self, items: Sequence[ScheduledItem], sampled: Sequence[Optional[int]]) -> List[Request]:
         """After the step: ``sampled[i]`` is the token drawn for ``items[i]`` (None if it
         wanted no logits).  Returns the requests that finished."""
-        done = []
+        wanting, toks = [], []
         for it, tok in zip(items, sampled):
-            req = it.request
             if not it.wants_logits:
                 continue
             if tok is None:
-                raise ValueError(f"request {req.id} wanted a token and got none")
-            tok = int(tok)
-            if tok in self.eos:
-                req.finish_reason = "eos"                       # the token is dropped (qwen2.cpp:1060-1062)
-            else:
-                req.generated.append(tok)
-                if len(req.generated) >= req.max_new_tokens:
-                    req.finish_reason = "length"
-                elif req.num_tokens > self.max_positions:
-                    req.finish_reason = "max_positions"
-            if req.finish_reason is not None:
+                raise ValueError(f"request {it.request.id} wanted a token and got none")
+            wanting.append(it.request)
+            toks.append(int(tok))
+        if not wanting:
+            return []
+        n = len(wanting)
+        ids, tk = np.asarray([r.id for r in wanting], dtype=np.int32), np.asarray(toks, dtype=np.int32)
+        outcome, reason = np.zeros(n, dtype=np.int32), np.zeros(n, dtype=np.int32)
+        native.check(self._lib.li_sched_update(self._h, n, ids.ctypes.data, tk.ctypes.data, outcome.ctypes.data, reason.ctypes.data))
+        done = []
+        for req, tok, kept, why in zip(wanting, toks, outcome.tolist(), reason.tolist()):
+            if kept:
+                req.generated.append(tok)                   # an end-of-sequence token is dropped (qwen2.cpp:1060-1062)
+            if why:
+                req.finish_reason = self._REASONS[why]
                 self.running.remove(req)
-                self._give_back(req)
+                self._dropped(req)
                 req.status = "finished"
                 done.append(req)
         return done

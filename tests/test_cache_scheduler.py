@@ -320,3 +320,66 @@ def test_the_packer_refuses_what_the_plain_one_refuses():
     m.release(a)
     with pytest.raises(PoolError, match="not live"):
         pack_step([StepItem(a, [1], ())], m, 100)
+
+
+@pytest.mark.parametrize("seed", range(10))
+@pytest.mark.parametrize("window", [None, 24])
+def test_the_scheduler_decides_like_the_plain_one(seed, window):
+    """Random streams of requests (arrivals while others run, small pools so that requests are preempted, budgets that
+    cut prompts into portions, end-of-sequence tokens, aborts) through the scheduler of the host runtime and through
+    the plain Python one of the tests, each over a cache manager of its own: the same items every step, the same
+    outputs, reasons and preemptions."""
+    import plain_scheduler
+
+    rnd = random.Random(1000 + seed)
+    pages, slots = rnd.choice([6, 8, 14]), rnd.choice([2, 4, 6])
+    cfg = dict(max_num_seqs=rnd.choice([2, 3, 8]), max_tokens_per_step=rnd.choice([8, 24, 64]), prefill_chunk=rnd.choice([5, 16, 64]))
+    pair = []
+    for mod in (None, plain_scheduler):
+        m = manager(num_pages=pages, max_requests=slots, window=window, two_groups=True)
+        if mod is None:
+            s = Scheduler(m, SchedulerConfig(**cfg), 200, eos_token_ids=[7])
+        else:
+            s = mod.Scheduler(m, mod.SchedulerConfig(**cfg), 200, eos_token_ids=[7])
+        pair.append((m, s))
+    ids = []
+    for step in range(300):
+        if rnd.random() < 0.25 and len(ids) < 25:
+            n, new = rnd.randint(1, 40), rnd.choice([1, 3, 20, 45, 45])
+            got = []
+            for m, s in pair:
+                try:
+                    got.append(s.add_request(list(range(n)), new))
+                except ValueError as e:                         # refused by both, for the same reason
+                    got.append(str(e))
+            assert got[0] == got[1]
+            if isinstance(got[0], int):
+                ids.append(got[0])
+        if ids and rnd.random() < 0.03:
+            victim = rnd.choice(ids)
+            for m, s in pair:
+                s.abort(victim)
+        draws = {}
+        logs = []
+        for m, s in pair:
+            items = s.schedule()
+            logs.append([(it.request.id, it.start, it.count, it.wants_logits) for it in items])
+            for it in items:
+                m.commit(it.request.cache, it.start + it.count)
+            toks = []
+            for it in items:
+                if it.wants_logits and it.request.id not in draws:
+                    draws[it.request.id] = rnd.choice([1, 2, 3, 7]) if rnd.random() < 0.3 else 1
+                toks.append(draws.get(it.request.id) if it.wants_logits else None)
+            done = s.update(items, toks)
+            logs.append(sorted(r.id for r in done))
+            m.check()
+        assert logs[0] == logs[2] and logs[1] == logs[3], f"step {step}: {logs}"
+        a, b = pair[0][1], pair[1][1]
+        assert [r.id for r in a.running] == [r.id for r in b.running] and [r.id for r in a.waiting] == [r.id for r in b.waiting]
+        assert a.num_preemptions == b.num_preemptions
+        assert all(pair[0][0].num_free_pages(g) == pair[1][0].num_free_pages(g) for g in range(len(pair[0][0].groups)))
+    a, b = pair[0][1], pair[1][1]
+    for rid in ids:
+        ra, rb = a.requests[rid], b.requests[rid]
+        assert (ra.generated, ra.finish_reason, ra.status, ra.preemptions) == (rb.generated, rb.finish_reason, rb.status, rb.preemptions)
