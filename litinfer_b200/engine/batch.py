@@ -11,7 +11,10 @@ Layout of the packed buffer (all int32): token_ids[T] | positions[T] |
 seq_of_token[T] | q_start[S+1] | ctx_lens[S] | old_lens[S] | state_slots[S] |
 logit_rows[R] | per group: slot_mapping[T] | block_table[S * max_blocks].  With ``pad_seqs``
 the batch is padded to that many one-token items that write to the sink page
-and whose results nobody reads (a captured decode step has a fixed size).
+and whose results nobody reads (a captured decode step has a fixed size); with
+``pad_tokens`` to a fixed count of tokens, sequences and rows (a captured step
+with portions of prompts).  The buffer is filled by the host runtime
+(``li_cm_pack_step`` in ``csrc/host/runtime.cpp``), which holds the block tables.
 """
 
 from __future__ import annotations

@@ -153,9 +153,10 @@ class ModelRunner:
         return reads <= self.SPLIT_CONTEXT_SUM
 
     def _step_shape(self, items: Sequence[StepItem]) -> Optional[tuple]:
-        """The padded shape (tokens, sequences, logit rows) under which a step with portions of prompts is replayed from
-        a captured graph, or None if it is launched plainly: too large, a context beyond the captured attention's,
-        a shape that has not come back yet, or a mixer with state of its own."""
+        """The padded shape (tokens, sequences, logit rows, whether single tokens stand beside the portions) under which
+        a step with portions of prompts is replayed from a captured graph, or None if it is launched plainly: too large,
+        a context beyond the captured attention's, a shape that has not come back yet, or a mixer with state of its
+        own."""
         if not self._may_split:
             return None
         T = sum(len(it.tokens) for it in items)
