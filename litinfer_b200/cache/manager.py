@@ -223,6 +223,15 @@ class CacheManager:
         native.check(self._lib.li_cm_commit(self._h, rc.request_id, int(new_length)))
         rc.length = int(new_length)
 
+    def commit_many(self, caches: Sequence[RequestCache], new_lengths: Sequence[int]) -> None:
+        """:meth:`commit` for the requests of a step at once."""
+        n = len(caches)
+        ids = (ctypes.c_int * n)(*[rc.request_id for rc in caches])
+        lens = (ctypes.c_int * n)(*[int(x) for x in new_lengths])
+        native.check(self._lib.li_cm_commit_many(self._h, n, ids, lens))
+        for rc, x in zip(caches, new_lengths):
+            rc.length = int(x)
+
     def release(self, rc: RequestCache) -> None:
         if self.live.get(rc.request_id) is not rc:
             raise PoolError(f"request {rc.request_id} is not live")

@@ -42,6 +42,7 @@ _SIGNATURES = {
     "li_cm_pages_needed": (I, [P, I, I, IP]),
     "li_cm_extend": (I, [P, I, I]),
     "li_cm_commit": (I, [P, I, I]),
+    "li_cm_commit_many": (I, [P, I, P, P]),
     "li_cm_release": (I, [P, I]),
     "li_cm_length": (I, [P, I]),
     "li_cm_table": (I, [P, I, I, IP, I]),

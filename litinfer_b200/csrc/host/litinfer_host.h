@@ -57,6 +57,9 @@ int li_cm_pages_needed(void* h, int id, int new_length, int* need);
 /* The step has written positions below new_length: pages of windowed groups that no further query can read go back */
 int li_cm_commit(void* h, int id, int new_length);
 
+/* li_cm_commit for the requests of a step at once. */
+int li_cm_commit_many(void* h, int n, const int* ids, const int* new_lengths);
+
 /* A new live request: takes a state slot. */
 int li_cm_admit(void* h, int id, int* slot);
 

@@ -130,6 +130,13 @@ LI_HOST_EXPORT int li_cm_commit(void* h, int id, int new_length) {
     return LI_HOST_OK;
 }
 
+// li_cm_commit for the requests of a step at once
+LI_HOST_EXPORT int li_cm_commit_many(void* h, int n, const int* ids, const int* new_lengths) {
+    for (int i = 0; i < n; ++i)
+        if (int rc = li_cm_commit(h, ids[i], new_lengths[i])) return rc;
+    return LI_HOST_OK;
+}
+
 int li_host::cm_release(Manager* m, int id) {
     FIND(m, r, id);
     for (size_t g = 0; g < m->pools.size(); ++g) {

@@ -130,8 +130,7 @@ class ModelRunner:
             if token_source is not None:
                 ctx.token_ids[:len(items)].copy_(token_source)
             logits = self.model.forward(ctx, self.manager.entries)
-        for it in items:
-            self.manager.commit(it.cache, it.cache.length + len(it.tokens))
+        self.manager.commit_many([it.cache for it in items], [it.cache.length + len(it.tokens) for it in items])
         self.steps_run += 1
         return logits
 
