@@ -20,6 +20,10 @@ One JSON line is printed:
 * ``points``: decode tokens per second at batch 1 and 64.
 
 Weights (3 GB) are larger than L2, so nothing stays cached between steps.
+
+``--only decode|prefill|mixed|kernels-decode|kernels-prefill`` measures one part and prints a short line (for
+profiling runs and the summaries under ``profiles/``); ``mixed`` is a step of ``--batch`` requests decoding at
+``--context`` beside a portion of ``--prefill-tokens`` prompt tokens.
 """
 
 from __future__ import annotations
