@@ -297,3 +297,42 @@ def test_padded_steps_keep_their_invariants_under_random_batches(seed, model_dir
         for it in items:
             manager.release(it.cache)
         manager.check()
+
+
+def test_which_steps_are_captured_and_under_which_shape(model_dirs, cpu_kernels):
+    """The runner's rule for steps with portions of prompts: a shape is captured when it comes back, the shape rounds
+    tokens, sequences and rows up, and what does not fit a captured shape is launched plainly."""
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.engine import ModelRunner, StepItem
+    from litinfer_b200.models import DecoderModel
+
+    model = DecoderModel.from_dir(model_dirs["C"], "float32", "cpu")
+    manager = CacheManager(model.cache_requirements(), [e.cache_from for e in model.spec.schedule], 8, 16, 4, model.dtype, model.device)
+    runner = ModelRunner(model, manager)
+
+    class Cache:
+        def __init__(self, length):
+            self.length = length
+
+    def items(*portions):
+        return [StepItem(Cache(had), [0] * n, want) for had, n, want in portions]
+
+    step = items((0, 130, (129,)))
+    assert runner._step_shape(step) is None                          # first sight: launched plainly
+    assert runner._step_shape(step) == (192, 2, 2, False)            # it came back
+    runner._step_graphs[(192, 2, 2, False)] = object()
+    assert runner._step_shape(items((40, 150, (149,)))) == (192, 2, 2, False)      # another step of the same shape
+    runner.step_graph_after = 0
+    assert runner._step_shape(items((0, 512, (511,)))) == (512, 1, 1, False)       # nothing to pad: no padding sequence
+    assert runner._step_shape(items((0, 500, (499,)), *[(700, 1, (0,))] * 12)) == (512, 16, 16, True)
+    assert runner._step_shape(items((0, 544, (543,)))) == (640, 2, 2, False)       # steps of 128 beyond 512 tokens
+    assert runner._step_shape(items((0, 80, tuple(range(80))))) == (128, 2, 128, False)    # every token's logits: rows padded to the tokens
+    assert runner._step_shape(items((0, 2049, (0,)))) is None                       # too many tokens
+    assert runner._step_shape(items((runner.max_context - 50, 100, (0,)))) is None  # beyond the captured attention's context
+    runner.STEP_GRAPH_LOGITS = 1000
+    assert runner._step_shape(items((0, 80, tuple(range(80))))) is None             # too many logits to keep per shape
+    runner.STEP_GRAPH_LOGITS = ModelRunner.STEP_GRAPH_LOGITS
+    runner._step_graphs.update({i: None for i in range(ModelRunner.STEP_GRAPH_LIMIT)})
+    assert runner._step_shape(items((0, 300, (299,)))) is None                      # enough shapes are kept already
+    runner._may_split = False
+    assert runner._step_shape(step) is None                                         # a mixer with state of its own
