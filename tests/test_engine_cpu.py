@@ -336,3 +336,52 @@ def test_which_steps_are_captured_and_under_which_shape(model_dirs, cpu_kernels)
     assert runner._step_shape(items((0, 300, (299,)))) is None                      # enough shapes are kept already
     runner._may_split = False
     assert runner._step_shape(step) is None                                         # a mixer with state of its own
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_captured_paths_of_the_runner_with_the_capture_emulated(name, model_dirs, tmp_path, cpu_kernels):
+    """Everything the runner does around a captured graph, on the CPU: single-token steps padded to a bucket, small
+    steps with portions as single tokens of one request, larger ones padded to a shape, the rows picked out of the
+    captured layout.  The capture itself is emulated (replaying runs the forward pass on the captured metadata
+    buffer again), so that the packed, padded metadata and the bookkeeping are checked against the plain model."""
+    from litinfer_b200.engine import step as step_module
+    from litinfer_b200.engine.batch import context_from
+    from litinfer_b200.engine.replay import Replayer
+    from litinfer_b200.models import DecoderModel
+
+    class Emulated(step_module.ModelRunner):
+        def _capture(self, B, max_blocks, buf, layout, max_q_len=1, singles=0):
+            meta = torch.zeros(buf.shape[0], dtype=torch.int32)
+            self._upload(buf, meta)
+            lay = dict(layout, max_ctx_len=self.max_context, max_q_len=max_q_len, singles=singles)
+            ctx = context_from(meta, lay, self.manager.page_size)
+            runner = self
+
+            class Graph:
+                def replay(self):
+                    ctx.scratch.clear()
+                    g.logits.copy_(runner.model.forward(ctx, runner.manager.entries))
+
+            g = step_module._DecodeGraph(Graph(), meta, self.model.forward(ctx, self.manager.entries).clone(), lay)
+            if B is not None:
+                self._graphs[B] = g
+            return g
+
+    cfg = TINY[name]
+    vocab = cfg["vocab_size"]
+    tr, seqs, need = build_trace(vocab, cfg["max_position_embeddings"])
+    model = DecoderModel.from_dir(model_dirs[name], "float32", "cpu")
+    rp = Replayer(model, need, use_graphs=False)
+    rp.runner = Emulated(model, rp.manager, max_context=rp.runner.max_context, step_graph_after=0)
+    rp.runner.use_graphs = True
+    got = {}
+    for i, line in enumerate(tr.lines().splitlines()):
+        logits = rp.step(json.loads(line)).clone()
+        for (rid, pos), row in zip(tr.where[i], logits):
+            got.setdefault(rid, {})[pos] = row
+    for rid, toks in seqs.items():
+        check_logits(stack(got[rid]), plain_logits(model_dirs[name], toks, "float32"), "float32", f"{name} {rid} through emulated captures")
+    r = rp.runner
+    assert r.graph_replays == len(tr.steps), "every step of the trace fits a captured path"
+    assert len(r._graphs) >= 2 and len(r._step_graphs) >= 1
+    rp.manager.check()
