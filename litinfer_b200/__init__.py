@@ -6,7 +6,7 @@
 
 __version__ = "0.1.0"
 
-from .api import Qwen2, load_model
+from .api import CausalLM, Qwen2, load_model
 from .config import Qwen2Config, register_architecture
 from .engine import Engine, EngineConfig, StepItem
 from .models import DecoderModel
@@ -16,6 +16,7 @@ __all__ = [
     "DecoderModel",
     "Engine",
     "EngineConfig",
+    "CausalLM",
     "Qwen2",
     "Qwen2Config",
     "SamplingParams",

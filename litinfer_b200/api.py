@@ -35,8 +35,9 @@ def _default_dtype(config) -> str:
     return "float32" if getattr(config, "torch_dtype", "bfloat16") in ("float32", "fp32") else "bfloat16"
 
 
-class Qwen2:
-    """A model folder (config.json + safetensors) ready to generate on one GPU."""
+class CausalLM:
+    """A model folder (config.json + safetensors) of any registered architecture, ready to generate on one GPU.
+    :data:`Qwen2` is this class under LitInfer's name for it."""
 
     def __init__(self, model_path, device="cuda:0", quantize=None, dtype: Optional[str] = None,
                  num_pages: Optional[int] = None, max_num_seqs: int = 64, max_tokens_per_step: int = 2048,
@@ -82,10 +83,9 @@ class Qwen2:
         opts = dict(self._engine_options)
         opts.update(overrides)
         pages = self._default_pages(opts["max_num_seqs"])
-        has_state = any(getattr(r, "shape", None) is not None for r in self.model.cache_requirements())
         cfg = EngineConfig(num_pages=pages, page_size=16, max_num_seqs=opts["max_num_seqs"],
                            max_tokens_per_step=opts["max_tokens_per_step"], prefill_chunk=opts["prefill_chunk"],
-                           use_graphs=opts["use_graphs"] and not has_state, run_ahead=bool(opts.get("run_ahead", False)))
+                           use_graphs=opts["use_graphs"], run_ahead=bool(opts.get("run_ahead", False)))
         return Engine(self.model, cfg)
 
     # ------------------------------------------------------------------
@@ -145,8 +145,7 @@ class Qwen2:
                     yield out[sent]
                     sent += 1
         finally:
-            eng.drain()                          # a step launched ahead is read before the request goes
-            eng.scheduler.abort(rid)             # frees pages if the caller stopped early; no-op when finished
+            eng.abort(rid)                       # reads a step launched ahead, then frees pages if the caller stopped early; no-op when finished
             eng.scheduler.forget(rid)
 
     # ------------------------------------------------------------------
@@ -184,6 +183,9 @@ class Qwen2:
         self._engine = None
 
 
-def load_model(model_path, **kwargs) -> Qwen2:
+Qwen2 = CausalLM            # LitInfer's name (python/llaisys/models/qwen2.py:23); the class itself serves any registered architecture
+
+
+def load_model(model_path, **kwargs) -> CausalLM:
     """The front end for whatever registered architecture config.json names."""
-    return Qwen2(model_path, **kwargs)
+    return CausalLM(model_path, **kwargs)

@@ -47,7 +47,7 @@ class Qwen2Config:
     rms_norm_eps: float
     rope_theta: float
     tie_word_embeddings: bool
-    attention_bias: bool
+    attention_bias: Optional[bool]
     use_sliding_window: bool
     sliding_window: Optional[int]
     max_window_layers: int
@@ -115,7 +115,9 @@ class Qwen2Config:
             rms_norm_eps=eps,
             rope_theta=theta,
             tie_word_embeddings=bool(d.get("tie_word_embeddings", False)),
-            attention_bias=bool(d.get("attention_bias", True)),
+            # Qwen2's config.json has no such key: the q/k/v biases then follow the file, as in LitInfer, whose
+            # loader does not require them (python/llaisys/models/qwen2.py:220-230)
+            attention_bias=None if d.get("attention_bias") is None else bool(d["attention_bias"]),
             use_sliding_window=use_win,
             sliding_window=window if use_win else None,
             max_window_layers=mwl,
@@ -141,6 +143,8 @@ class Qwen2Config:
         d["eos_token_id"] = eos[0] if len(eos) == 1 else (eos if eos else None)
         d["hidden_act"] = "silu"
         d["model_type"] = "qwen2"
+        if d["attention_bias"] is None:
+            d.pop("attention_bias")
         return d
 
     # ------------------------------------------------------------------
@@ -173,7 +177,8 @@ class Qwen2Config:
                     "position": rope,
                 },
             )
-            blocks.append(BlockSpec("prenorm", f"model.layers.{i}.", mixer, ffn, norm, norm))
+            blocks.append(BlockSpec.of("prenorm", f"model.layers.{i}.", mixer=mixer, feed_forward=ffn, mixer_norm=norm,
+                                       feed_forward_norm=norm))
         return ModelSpec(
             architecture=self.ARCHITECTURE,
             vocab_size=self.vocab_size,
@@ -184,4 +189,10 @@ class Qwen2Config:
             tie_word_embeddings=self.tie_word_embeddings,
             max_position_embeddings=self.max_position_embeddings,
             eos_token_ids=self.eos_token_ids,
+            # the other names LitInfer's loader takes (python/llaisys/models/qwen2.py:139-149)
+            aliases={
+                "model.embed_tokens.weight": ("transformer.wte.weight",),
+                "lm_head.weight": ("model.lm_head.weight",),
+                "model.norm.weight": ("transformer.ln_f.weight",),
+            },
         )

@@ -204,6 +204,37 @@ LI_EXPORT int li_residual_add(float* x, const void* delta, int dtype, long long 
     return li_check_launch("residual_add");
 }
 
+// x *= factor (an embedding scale) and x = cap * tanh(x / cap) (a cap on the logits), in place on float32.
+namespace {
+__global__ void scale_kernel(float* __restrict__ x, long long n, float factor) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= factor;
+}
+__global__ void logit_cap_kernel(float* __restrict__ x, long long n, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+}  // namespace
+
+LI_EXPORT int li_scale_inplace(float* x, long long n, float factor, cudaStream_t stream) {
+    LI_REQUIRE(n >= 0 && n <= (1LL << 40), "scale: bad size %lld", n);
+    if (n == 0) return 0;
+    li_launch_pdl(scale_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, factor);
+    return li_check_launch("scale");
+}
+
+LI_EXPORT int li_logit_cap(float* x, long long n, float cap, cudaStream_t stream) {
+    LI_REQUIRE(n >= 0 && n <= (1LL << 40), "logit_cap: bad size %lld", n);
+    LI_REQUIRE(cap > 0.0f, "logit_cap: the cap must be positive, got %g", (double)cap);
+    if (n == 0) return 0;
+    li_launch_pdl(logit_cap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, x, n, cap);
+    return li_check_launch("logit_cap");
+}
+
 LI_EXPORT int li_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
     LI_REQUIRE(T >= 0 && I > 0, "swiglu: bad sizes T=%d I=%d", T, I);
     const long long n = (long long)T * I;

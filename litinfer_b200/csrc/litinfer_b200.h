@@ -54,6 +54,12 @@ int li_gather_rmsnorm(const float* x, const int* rows, const float* w, float eps
 /* x += delta over n elements. */
 int li_residual_add(float* x, const void* delta, int dtype, long long n, cudaStream_t stream);
 
+/* x *= factor over n floats (an embedding scale). */
+int li_scale_inplace(float* x, long long n, float factor, cudaStream_t stream);
+
+/* x = cap * tanh(x / cap) over n floats (a cap on the logits). */
+int li_logit_cap(float* x, long long n, float cap, cudaStream_t stream);
+
 /* out[t, i] = up * gate / (1 + exp(-gate)), gate_up [T, 2 I] as gate | up. */
 int li_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream);
 

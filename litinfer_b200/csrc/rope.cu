@@ -148,8 +148,10 @@ LI_EXPORT int li_rope_kv_write(void* qkv, int dtype, const int* positions, const
                                const int* slot_mapping, void* kcache, void* vcache, int T, int nh, int nkv, int dh, int page_size,
                                int num_pages, int write, cudaStream_t stream) {
     LI_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && dh > 0 && page_size > 0, "rope_kv_write: bad sizes");
-    LI_REQUIRE(rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= dh, "rope_kv_write: rotary_dim %d must be even and at most head_dim %d",
+    // rotary_dim 0: nothing is rotated (a model without rotary positions); keys and values are stored as they are
+    LI_REQUIRE(rotary_dim >= 0 && rotary_dim % 2 == 0 && rotary_dim <= dh, "rope_kv_write: rotary_dim %d must be even and at most head_dim %d",
                rotary_dim, dh);
+    LI_REQUIRE(rotary_dim == 0 || denom != nullptr, "rope_kv_write: rotary_dim %d without denominators", rotary_dim);
     if (T == 0) return 0;
     LI_REQUIRE(T <= 2147483647 && nh + nkv <= 65535, "rope_kv_write: too many heads for one launch");
     const int heads_per_block = T >= 64 ? nh + nkv : 1;

@@ -138,6 +138,13 @@ class Engine:
         self._ahead = following
         return done
 
+    def abort(self, rid: int) -> List[Request]:
+        """End request ``rid`` now and give back what it holds.  A step launched ahead is read first, so that the
+        tokens it computed for the other requests count; returns the requests whose end became known by that."""
+        done = self.drain()
+        self.scheduler.abort(rid)
+        return done
+
     def drain(self) -> List[Request]:
         """Read the tokens of a step that was launched ahead, if there is one."""
         ahead, self._ahead = self._ahead, None
@@ -187,8 +194,10 @@ class Engine:
                 if it.wants_logits:
                     sampled[i] = host[j]
                     j += 1
-        if launched.void:
-            keep = [i for i, it in enumerate(items) if it.request.id not in launched.void]
+        # requests that ended before this step's token could count: on an end-of-sequence token of the step before
+        # (void), or aborted through the scheduler while the step was in flight (no longer running)
+        if launched.void or any(it.request.status != "running" for it in items):
+            keep = [i for i, it in enumerate(items) if it.request.id not in launched.void and it.request.status == "running"]
             items = [items[i] for i in keep]
             sampled = [sampled[i] for i in keep]
         return self.scheduler.update(items, sampled)

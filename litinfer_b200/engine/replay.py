@@ -30,10 +30,9 @@ class Replayer:
         num_pages = max(1, -(-int(max_tokens) // page_size))
         self.manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], num_pages, page_size,
                                     max_live, model.dtype, model.device)
-        has_state = any(e.kind == "state" for e in self.manager.entries)
         max_context = min(spec.max_position_embeddings, num_pages * page_size)
-        # a captured step is warmed up by running it, which a mixer with state of its own would not survive
-        self.runner = ModelRunner(model, self.manager, use_graphs=use_graphs and not has_state, max_context=max_context,
+        # (the runner captures nothing for a model with a mixer that has state of its own)
+        self.runner = ModelRunner(model, self.manager, use_graphs=use_graphs, max_context=max_context,
                                   step_graph_after=step_graph_after)
         self.live: Dict[str, RequestCache] = {}
         self._next_id = 0

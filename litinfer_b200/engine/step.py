@@ -58,7 +58,11 @@ class ModelRunner:
         self.model = model
         self.manager = manager
         self.device = model.device
-        self.use_graphs = bool(use_graphs) and self.device.type == "cuda"
+        # a mixer with state of its own takes a request's tokens in order and advances its state every time the step
+        # runs: its portions are never split, and nothing of such a model is captured (capturing runs the step for
+        # warm-up, and a captured step would freeze which slots it updates)
+        self._may_split = not any(isinstance(r, FixedState) for r in model.cache_requirements())
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and self._may_split
         # a captured attention launch has to cover the longest context it may meet (its grid and workspace
         # are sized for it), so that length is capped; steps with a longer context run without a graph
         self.max_context = min(int(max_context or model.spec.max_position_embeddings), self.GRAPH_CONTEXT_CAP)
@@ -69,8 +73,6 @@ class ModelRunner:
         self._shape_seen: Dict[tuple, int] = {}
         self._step_graphs: Dict[tuple, _DecodeGraph] = {}
         self._step_pool = None
-        # a mixer with state of its own takes a request's tokens in order: its portions are never split
-        self._may_split = not any(isinstance(r, FixedState) for r in model.cache_requirements())
         self._pinned: Optional[torch.Tensor] = None
         self._copy_done = None
         self.steps_run = 0

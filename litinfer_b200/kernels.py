@@ -146,6 +146,18 @@ def residual_add(x32: torch.Tensor, delta: torch.Tensor) -> None:
     _check(library().li_residual_add(_p(x32), _p(delta), _i(_dt(delta)), _l(x32.numel()), _stream(x32)), "residual_add")
 
 
+def scale_inplace(x32: torch.Tensor, factor: float) -> None:
+    """x32 *= factor (float32, in place)."""
+    _need(x32, "scale operand", torch.float32)
+    _check(library().li_scale_inplace(_p(x32), _l(x32.numel()), _f(factor), _stream(x32)), "scale")
+
+
+def logit_cap(logits: torch.Tensor, cap: float) -> None:
+    """logits = cap * tanh(logits / cap) (float32, in place)."""
+    _need(logits, "logits", torch.float32)
+    _check(library().li_logit_cap(_p(logits), _l(logits.numel()), _f(cap), _stream(logits)), "logit_cap")
+
+
 EPILOGUES = {None: 0, "swiglu": 1}
 
 
@@ -266,11 +278,13 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torc
     """Rotate q (in place in ``qkv``) and k; store rotated k and plain v at each
     token's slot of the caches: keys ``[pages, kv_heads, page_size, head_dim]``, values
     transposed ``[pages, kv_heads, head_dim, page_size]``.
-    With ``write`` false only q is rotated."""
+    With ``write`` false only q is rotated.  ``rotary_dim`` 0 (``denominators`` may be None): nothing is
+    rotated, keys and values are stored as they are."""
     T = qkv.shape[0]
     _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
     _need(positions, "positions", torch.int32, (T,))
-    _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
+    if rotary_dim:
+        _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
     _need(slot_mapping, "slot mapping", torch.int32, (T,))
     _need(k_cache, "key cache", qkv.dtype)
     pages, nkv, page_size, dh = k_cache.shape
@@ -278,7 +292,7 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, denominators: torc
     if nkv != num_kv_heads or dh != head_dim:
         raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
     _check(library().li_rope_kv_write(
-        _p(qkv), _i(_dt(qkv)), _p(positions), _p(denominators), _i(rotary_dim), _p(slot_mapping), _p(k_cache), _p(v_cache),
+        _p(qkv), _i(_dt(qkv)), _p(positions), _p(denominators if rotary_dim else None), _i(rotary_dim), _p(slot_mapping), _p(k_cache), _p(v_cache),
         _i(T), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _i(1 if write else 0), _stream(qkv)),
         "rope_kv_write")
 
@@ -292,7 +306,8 @@ def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
     afterwards, not in ``qkv``.  For a few bfloat16 tokens both steps run as one kernel (the rotation is the
     product's epilogue); ``fused=False`` forces two kernels, for tests.  ``row_scale`` as in :func:`linear`.
     ``cos_sin``: the step's table from :func:`rope_table`; with it a long bfloat16 step (head_dim 128) rotates and
-    writes the cache in the epilogue of the tensor-memory product too."""
+    writes the cache in the epilogue of the tensor-memory product too.  ``rotary_dim`` 0 (``denominators`` may be
+    None): no rotation, as in :func:`rope_kv_write`."""
     T, Kd = a.shape
     N = (num_heads + 2 * num_kv_heads) * head_dim
     _need(a, "linear input")
@@ -301,7 +316,8 @@ def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
         _need(bias, "qkv bias", torch.float32, (N,))
     _need(qkv, "qkv", a.dtype, (T, N))
     _need(positions, "positions", torch.int32, (T,))
-    _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
+    if rotary_dim:
+        _need(denominators, "rope denominators", torch.float32, (rotary_dim // 2,))
     _need(slot_mapping, "slot mapping", torch.int32, (T,))
     if cos_sin is not None:
         _need(cos_sin, "rope table", torch.float32, (T, rotary_dim // 2, 2))
@@ -311,7 +327,7 @@ def linear_rope_kv(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.T
     if nkv != num_kv_heads or dh != head_dim:
         raise KernelError(f"cache of {nkv} heads x {dh} does not match {num_kv_heads} x {head_dim}")
     _check(library().li_linear_rope_kv(
-        _p(a), _p(weight), _p(bias), _p(qkv), _i(_dt(a)), _p(positions), _p(denominators), _i(rotary_dim), _p(slot_mapping),
+        _p(a), _p(weight), _p(bias), _p(qkv), _i(_dt(a)), _p(positions), _p(denominators if rotary_dim else None), _i(rotary_dim), _p(slot_mapping),
         _p(k_cache), _p(v_cache), _i(T), _i(Kd), _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages),
         _i(1 if write else 0), _i(1 if fused else 0),
         *(_row_scale_args(row_scale, T) if row_scale is not None else (_p(None), _i(0), _i(0), _f(0.0))), _p(cos_sin), _stream(qkv)),

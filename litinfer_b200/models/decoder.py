@@ -1,8 +1,12 @@
 """The one model class: a decoder assembled from a ModelSpec.
 
-embedding -> blocks in the order of the schedule -> final norm and lm_head on
-the wanted rows only (LitInfer computes logits for every row and uses one,
-src/llaisys/models/qwen2.cpp:331-350).  Which architecture a ModelSpec came
+embedding (-> the model's own position encoding, if the spec names one) ->
+blocks in the order of the schedule -> final norm and lm_head on the wanted
+rows only (LitInfer computes logits for every row and uses one,
+src/llaisys/models/qwen2.cpp:331-350).  The lm_head follows the file, as in
+LitInfer (python/llaisys/models/qwen2.py:143-146, 196-199): a stored one is
+used, a missing one is the embedding table, whatever config.json says; the
+spec's ``tie_word_embeddings`` only decides what random-weights mode makes.  Which architecture a ModelSpec came
 from does not matter here; the architecture registry supplies the spec and
 the part registries supply the parts.
 """
@@ -10,13 +14,14 @@ the part registries supply the parts.
 from __future__ import annotations
 
 from pathlib import Path
+from dataclasses import replace
 from typing import Dict, List, Optional
 
 import torch
 
 from .. import kernels as K
 from ..config import ModelSpec, load_config, validate_schedule
-from ..parts import BLOCKS, NORMS
+from ..parts import BLOCKS, NORMS, POSITIONS
 from ..parts.base import FixedState, PagedKV
 from ..weights.loader import ParamSpec, load_tensors
 from ..weights.random_init import random_tensors
@@ -46,28 +51,41 @@ class DecoderModel:
         self.device = torch.device(device)
         self.blocks = [BLOCKS.build(b, b.prefix, self.dtype, self.device) for b in spec.blocks]
         self.final_norm = NORMS.build(spec.final_norm, spec.final_norm_prefix, self.dtype, self.device)
+        self.position = (POSITIONS.build(spec.position, spec.position_prefix, self.dtype, self.device)
+                         if spec.position is not None else None)
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
+        self.head_is_tied = False
 
     # ------------------------------------------------------------------
     def params(self) -> List[ParamSpec]:
         s = self.spec
         out = [ParamSpec(s.embedding_name, (s.vocab_size, s.hidden_size), role="matrix")]
+        if self.position is not None:
+            out.extend(self.position.all_params())
         for b in self.blocks:
             out.extend(b.all_params())
         out.extend(self.final_norm.all_params())
-        if not s.tie_word_embeddings:
-            out.append(ParamSpec(s.lm_head_name, (s.vocab_size, s.hidden_size), role="matrix"))
+        # optional either way: the file decides (see bind); random-weights mode makes one unless the spec ties
+        out.append(ParamSpec(s.lm_head_name, (s.vocab_size, s.hidden_size), role="matrix", optional=True,
+                             draw=not s.tie_word_embeddings))
+        if s.aliases:
+            out = [replace(p, aliases=p.aliases + tuple(s.aliases[p.name])) if p.name in s.aliases else p for p in out]
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
         self.embedding = tensors.pop(s.embedding_name)
+        if self.position is not None:
+            self.position.bind_all(tensors)
         for b in self.blocks:
             b.bind_all(tensors)
         self.final_norm.bind_all(tensors)
-        # tied: the embedding table itself (python/llaisys/models/qwen2.py:196-199)
-        self.lm_head = self.embedding if s.tie_word_embeddings else tensors.pop(s.lm_head_name)
+        # a stored head is used; without one the head is the embedding table itself
+        # (python/llaisys/models/qwen2.py:196-199: ``if not w.out_embed and w.in_embed``)
+        head = tensors.pop(s.lm_head_name, None)
+        self.head_is_tied = head is None
+        self.lm_head = self.embedding if head is None else head
         if tensors:
             raise RuntimeError("tensors left unbound: " + ", ".join(sorted(tensors)))
 
@@ -75,7 +93,7 @@ class DecoderModel:
         """For each schedule entry: PagedKV, FixedState or None (entries that read another's cache: None)."""
         out = []
         for e in self.spec.schedule:
-            out.append(self.blocks[e.block].mixer.cache_requirement() if e.cache_from is None else None)
+            out.append(self.blocks[e.block].cache_requirement() if e.cache_from is None else None)
         return out
 
     # ------------------------------------------------------------------
@@ -98,6 +116,10 @@ class DecoderModel:
         s = self.spec
         x32 = torch.empty((ctx.num_tokens, s.hidden_size), dtype=torch.float32, device=self.device)
         K.embedding(self.embedding, ctx.token_ids, x32)
+        if s.embedding_scale is not None:
+            K.scale_inplace(x32, float(s.embedding_scale))
+        if self.position is not None:
+            self.position.add_to_stream(x32, ctx)
         carry = None
         last = len(s.schedule) - 1
         for i, e in enumerate(s.schedule):
@@ -111,6 +133,8 @@ class DecoderModel:
         if R:
             y = self.final_norm.gather_forward(x32, ctx.logit_rows)
             K.linear(y, self.lm_head, None, logits)
+            if s.logit_cap is not None:
+                K.logit_cap(logits, float(s.logit_cap))
         return logits
 
 

@@ -7,7 +7,10 @@ head ``i`` reads key head ``i // (heads / kv_heads)``; the query at position p
 sees keys 0..p, or with a window only those with p - t < window;
 scores * scale, softmax in float32, weighted sum of v; output map without
 bias unless the spec says so.  Sizes, scale, window and bias flags are
-parameters of the spec; the position encoding is a part of its own.
+parameters of the spec; the position encoding is a part of its own, named by the spec
+(``position``; None: none) and asked only through :meth:`~litinfer_b200.parts.base.Position.rotary`.
+``qkv_bias`` may be ``None``: the biases then follow the file, each on its own
+(LitInfer's linear takes a missing bias as none, src/llaisys/ops.cc:27-29).
 """
 
 from __future__ import annotations
@@ -41,15 +44,16 @@ class PagedAttention(Mixer):
         self.kv_dim = self.num_kv_heads * self.head_dim
         self.qkv = FusedLinear(
             prefix, [names.get("q", "q_proj"), names.get("k", "k_proj"), names.get("v", "v_proj")],
-            self.hidden, [self.q_dim, self.kv_dim, self.kv_dim], bool(spec.get("qkv_bias", False)), dtype)
+            self.hidden, [self.q_dim, self.kv_dim, self.kv_dim], spec.get("qkv_bias", False), dtype)
         self.out = FusedLinear(prefix, [names.get("o", "o_proj")], self.q_dim, [self.hidden], bool(spec.get("out_bias", False)), dtype)
-        self.position = POSITIONS.build(spec["position"], prefix, dtype, device, head_dim=self.head_dim)
+        position = spec.get("position")
+        self.position = POSITIONS.build(position, prefix, dtype, device, head_dim=self.head_dim) if position is not None else None
 
     def params(self) -> List[ParamSpec]:
         return self.qkv.params() + self.out.params()
 
     def parts(self):
-        return [self.position]
+        return [self.position] if self.position is not None else []
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.qkv.bind(tensors)
@@ -70,10 +74,11 @@ class PagedAttention(Mixer):
         h, row_scale = undefer(h, self.qkv.weight)
         qkv = torch.empty((h.shape[0], self.qkv.out_features), dtype=self.dtype, device=h.device)
         # projection, position encoding of q and k, k and v into the cache: one call (and for few tokens one kernel)
+        rot = self.position.rotary(ctx) if self.position is not None else None
         K.linear_rope_kv(
-            h, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, self.position.denominators, self.position.rotary_dim,
+            h, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, rot.denominators if rot else None, rot.rotary_dim if rot else 0,
             view.slot_mapping, cache.k, cache.v, self.num_heads, self.num_kv_heads, self.head_dim, cache.writes, row_scale=row_scale,
-            cos_sin=self.position.table(ctx) if hasattr(self.position, "table") else None)
+            cos_sin=rot.table if rot else None)
         o = torch.empty((h.shape[0], self.q_dim), dtype=self.dtype, device=h.device)
         K.paged_attention(
             qkv, o, cache.k, cache.v, view.block_table, ctx.q_start, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,

@@ -199,11 +199,54 @@ class Norm(Part):
         return self.add_forward(x32, linear(a))
 
 
+@dataclass
+class Rotary:
+    """What a mixer's kernels need to rotate queries and keys of this step: pair ``j`` of the first ``rotary_dim``
+    elements of a head turns by ``position / denominators[j]``; ``table`` (or None) holds the cosines and sines
+    of the step's tokens, ``[tokens, rotary_dim / 2, 2]`` float32, for kernels that rotate in an epilogue."""
+
+    denominators: torch.Tensor
+    rotary_dim: int
+    table: Optional[torch.Tensor] = None
+
+
 class Position(Part):
-    pass
+    """A position encoding.  It serves a mixer (``PartSpec`` of the mixer names it) or the whole model
+    (``ModelSpec.position``), and says what it does through these methods; the defaults do nothing, so a
+    part overrides only what it is.
+
+    * :meth:`rotary`: for encodings that rotate queries and keys (the mixer hands the answer to its kernels);
+      ``None`` means "rotate nothing": keys and values still go into the cache.
+    * :meth:`add_to_stream`: for encodings that are added to the residual stream after the embedding
+      (learned absolute positions); only called on the model's own position part.
+    """
+
+    def rotary(self, ctx) -> Optional[Rotary]:
+        return None
+
+    def add_to_stream(self, x32: torch.Tensor, ctx) -> None:
+        return None
 
 
 class Block(Part):
+    """``spec`` is a :class:`~litinfer_b200.config.spec.BlockSpec`: parts by role."""
+
+    def build(self, registry: "Registry", role: str, required: bool = True, **extra):
+        """The part under ``role`` of this block's spec, built from ``registry``; None if the spec has none and it
+        is not required."""
+        part = self.spec.part(role)
+        if part is None:
+            if required:
+                raise ValueError(f"block '{self.spec.kind}' at {self.spec.prefix!r} needs a part under the role '{role}'; "
+                                 f"the spec has: {', '.join(sorted(self.spec.parts)) or 'none'}")
+            return None
+        return registry.build(part, self.spec.prefix_of(role), self.dtype, self.device, **extra)
+
+    def cache_requirement(self):
+        """What this block's schedule entry needs from the cache manager: by default its mixer's."""
+        mixer = getattr(self, "mixer", None)
+        return mixer.cache_requirement() if mixer is not None else None
+
     def entry(self) -> Optional[Tail]:
         """The norm this block applies to the residual stream first, and whether its consumer takes a deferred
         activation, as a Tail without a stream; None if the block before may not apply it in this block's place."""

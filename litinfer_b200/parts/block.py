@@ -2,11 +2,15 @@
 x += FeedForward(norm(x)) (src/llaisys/models/qwen2.cpp:272-316).
 
 The residual stream x is float32.  A block does not add the output of its
-feed-forward itself: told the next block's entry (its first norm), it lets the feed-forward
+last part itself: told the next block's entry (its first norm), it lets that part
 add, and normalise for the next block, in the tail of its last product
 (``Carry.normed``); otherwise it hands the output on (``Carry.delta``) and the next
 block, or the model's tail, adds it inside its first norm kernel.  Either way
 add and norm are one pass over x.
+
+A block takes its parts from the roles of its :class:`~litinfer_b200.config.spec.BlockSpec`
+(:meth:`Block.build`); ``prenorm`` wants ``mixer`` and ``mixer_norm`` and, unless the layer has
+no feed-forward, ``feed_forward`` and ``feed_forward_norm``.
 """
 
 from __future__ import annotations
@@ -19,19 +23,14 @@ from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Carry, Tail
 @BLOCKS.register("prenorm")
 class PreNormBlock(Block):
     def __init__(self, spec, prefix, dtype, device):
-        # ``spec`` is a BlockSpec here
-        self.spec = spec
-        self.prefix = prefix
-        self.dtype = dtype
-        self.device = device
-        p = spec.prefix
-        self.mixer_norm = NORMS.build(spec.mixer_norm, p + spec.mixer_norm_prefix, dtype, device)
-        self.mixer = MIXERS.build(spec.mixer, p + spec.mixer_prefix, dtype, device)
-        self.feed_forward_norm = NORMS.build(spec.feed_forward_norm, p + spec.feed_forward_norm_prefix, dtype, device)
-        self.feed_forward = FEED_FORWARDS.build(spec.feed_forward, p + spec.feed_forward_prefix, dtype, device)
+        super().__init__(spec, prefix, dtype, device)
+        self.mixer_norm = self.build(NORMS, "mixer_norm")
+        self.mixer = self.build(MIXERS, "mixer")
+        self.feed_forward = self.build(FEED_FORWARDS, "feed_forward", required=False)
+        self.feed_forward_norm = self.build(NORMS, "feed_forward_norm", required=self.feed_forward is not None)
 
     def parts(self) -> List:
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [p for p in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if p is not None]
 
     def entry(self):
         return Tail(None, self.mixer_norm, self.mixer.takes_deferred)
@@ -43,6 +42,10 @@ class PreNormBlock(Block):
             h = carry.normed                               # the block before applied this block's first norm
         else:
             h = self.mixer_norm.add_forward(x32, carry.delta)
+        if self.feed_forward is None:
+            if next_entry is None:
+                return x32, Carry(delta=self.mixer.forward(h, ctx, cache))
+            return x32, Carry(normed=self.mixer.forward_into(h, ctx, cache, Tail(x32, next_entry.norm, next_entry.defer)))
         h = self.mixer.forward_into(h, ctx, cache, Tail(x32, self.feed_forward_norm, self.feed_forward.takes_deferred))
         if next_entry is None:
             return x32, Carry(delta=self.feed_forward.forward(h, ctx))

@@ -26,16 +26,19 @@ def undefer(x, weight: torch.Tensor):
 
 
 class FusedLinear:
-    """``names``: tensor-name stems (without .weight / .bias); ``outs``: their output sizes."""
+    """``names``: tensor-name stems (without .weight / .bias); ``outs``: their output sizes.
+    ``bias``: True (each map has one), False (none), or None: the biases follow the file, each map on
+    its own; a map without one counts as zeros when another has one."""
 
-    def __init__(self, prefix: str, names: Sequence[str], in_features: int, outs: Sequence[int], bias: bool,
+    def __init__(self, prefix: str, names: Sequence[str], in_features: int, outs: Sequence[int], bias: Optional[bool],
                  dtype: torch.dtype, std: float = 0.02) -> None:
         self.prefix = prefix
         self.names = list(names)
         self.in_features = int(in_features)
         self.outs = [int(o) for o in outs]
         self.out_features = sum(self.outs)
-        self.has_bias = bool(bias)
+        self.has_bias = bool(bias) or bias is None          # declared; with None the file decides when bound
+        self.bias_optional = bias is None
         self.dtype = dtype
         self.std = std
         self.weight: Optional[torch.Tensor] = None
@@ -46,7 +49,7 @@ class FusedLinear:
         for n, o in zip(self.names, self.outs):
             out.append(ParamSpec(f"{self.prefix}{n}.weight", (o, self.in_features), role="matrix", std=self.std))
             if self.has_bias:
-                out.append(ParamSpec(f"{self.prefix}{n}.bias", (o,), role="vector", std=self.std))
+                out.append(ParamSpec(f"{self.prefix}{n}.bias", (o,), role="vector", std=self.std, optional=self.bias_optional))
         return out
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -54,8 +57,14 @@ class FusedLinear:
         self.weight = ws[0] if len(ws) == 1 else torch.cat(ws, dim=0).contiguous()
         del ws
         if self.has_bias:
-            bs = [tensors.pop(f"{self.prefix}{n}.bias") for n in self.names]
-            self.bias = bs[0] if len(bs) == 1 else torch.cat(bs, dim=0).contiguous()
+            bs = [tensors.pop(f"{self.prefix}{n}.bias", None) if self.bias_optional else tensors.pop(f"{self.prefix}{n}.bias")
+                  for n in self.names]
+            if all(b is None for b in bs):
+                self.bias = None
+            else:
+                like = next(b for b in bs if b is not None)
+                bs = [b if b is not None else torch.zeros(o, dtype=like.dtype, device=like.device) for b, o in zip(bs, self.outs)]
+                self.bias = bs[0] if len(bs) == 1 else torch.cat(bs, dim=0).contiguous()
 
     def __call__(self, x, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """``x`` may be a :class:`~litinfer_b200.parts.base.Deferred` activation: its factor per token goes on the product."""

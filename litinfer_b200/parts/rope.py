@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import POSITIONS, Position
+from .base import POSITIONS, Position, Rotary
 
 
 @POSITIONS.register("rope")
@@ -33,6 +33,9 @@ class RotaryEmbedding(Position):
     # Steps of more tokens than this get a table of cosines and sines, made once and shared by the layers (products that
     # rotate in their epilogue read it); shorter steps compute the angles where they rotate.
     TABLE_FROM_TOKENS = 65
+
+    def rotary(self, ctx) -> Rotary:
+        return Rotary(self.denominators, self.rotary_dim, self.table(ctx))
 
     def table(self, ctx):
         """``[tokens, rotary_dim / 2, 2]`` float32 cos and sin of this step's positions, or None for a short step."""

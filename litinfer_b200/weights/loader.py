@@ -62,8 +62,9 @@ class ParamSpec:
     role: str = "matrix"            # matrix | vector | table | keep
     init: str = "normal"            # normal | ones_normal | zeros | randint
     std: float = 0.02
-    optional: bool = False
-    aliases: Tuple[str, ...] = ()
+    optional: bool = False          # the file may lack it (the part then does without)
+    aliases: Tuple[str, ...] = ()   # other names it may be stored under, tried in order after ``name``
+    draw: bool = True               # whether random-weights mode makes one (an optional tensor may say no)
 
     def device_dtype(self, run_dtype: torch.dtype, stored: Optional[torch.dtype] = None) -> torch.dtype:
         if self.role == "matrix":

@@ -55,8 +55,8 @@ def random_tensor(p: ParamSpec, seed: int, device="cpu", dtype: torch.dtype = to
 
 
 def random_tensors(params: Sequence[ParamSpec], seed: int, run_dtype: torch.dtype, device) -> Dict[str, torch.Tensor]:
-    """Every declared (non-optional or not) tensor, drawn on ``device`` in its device dtype."""
-    return {p.name: random_tensor(p, seed, device, p.device_dtype(run_dtype)) for p in params}
+    """Every declared tensor that random mode draws (``ParamSpec.draw``), on ``device`` in its device dtype."""
+    return {p.name: random_tensor(p, seed, device, p.device_dtype(run_dtype)) for p in params if p.draw}
 
 
 def write_model_folder(path, config, seed: int, store_dtype: str = "float32") -> Path:
@@ -79,6 +79,8 @@ def write_model_folder(path, config, seed: int, store_dtype: str = "float32") ->
     params = declared_params(config.to_model_spec())
     tensors = {}
     for p in params:
+        if not p.draw:
+            continue
         t = random_tensor(p, seed, "cpu", torch.float32)
         if p.role == "table":
             tensors[p.name] = t.to(torch.int32)

@@ -99,12 +99,15 @@ def rope_kv_write(qkv, positions, denominators, rotary_dim, slot_mapping, k_cach
                   num_heads, num_kv_heads, head_dim, write=True):
     T = qkv.shape[0]
     q_dim, kv_dim = num_heads * head_dim, num_kv_heads * head_dim
-    phi = positions.float()[:, None] / denominators[None, :]
-    cos, sin = torch.cos(phi)[:, None, :], torch.sin(phi)[:, None, :]
     half = rotary_dim // 2
+    if rotary_dim:
+        phi = positions.float()[:, None] / denominators[None, :]
+        cos, sin = torch.cos(phi)[:, None, :], torch.sin(phi)[:, None, :]
 
     def rot(x):
         x = x.float().clone()
+        if not rotary_dim:
+            return x
         a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
         x[..., :half] = a * cos - b * sin
         x[..., half:rotary_dim] = b * cos + a * sin
@@ -159,6 +162,14 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, 
             pr = torch.softmax(sc, dim=0)
             res[t, h] = pr @ v[:, h // group]
     _store(out, res.reshape(T, num_heads * head_dim))
+
+
+def scale_inplace(x32, factor):
+    x32.mul_(factor)
+
+
+def logit_cap(logits, cap):
+    logits.copy_(cap * torch.tanh(logits / cap))
 
 
 def swiglu(gate_up, out):
@@ -241,5 +252,5 @@ def sample(logits, params, out):
     out.copy_(torch.tensor(res, dtype=torch.int32))
 
 
-ALL = ["rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
+ALL = ["scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]

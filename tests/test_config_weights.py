@@ -38,15 +38,15 @@ def test_every_size_comes_from_the_configuration():
         c = config_from_dict(cfg)
         spec = c.to_model_spec()
         assert len(spec.blocks) == cfg["num_hidden_layers"] and spec.vocab_size == cfg["vocab_size"]
-        m = spec.blocks[0].mixer
+        m = spec.blocks[0].part("mixer")
         assert (m["num_heads"], m["num_kv_heads"], m["head_dim"]) == (cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"])
         assert m["position"]["theta"] == cfg["rope_theta"]
-        assert spec.blocks[0].mixer_norm["eps"] == cfg["rms_norm_eps"]
-        assert spec.blocks[0].feed_forward["intermediate_size"] == cfg["intermediate_size"]
+        assert spec.blocks[0].part("mixer_norm")["eps"] == cfg["rms_norm_eps"]
+        assert spec.blocks[0].part("feed_forward")["intermediate_size"] == cfg["intermediate_size"]
         assert spec.tie_word_embeddings == cfg["tie_word_embeddings"]
     # the window applies from max_window_layers on
     spec = config_from_dict(TINY["B"]).to_model_spec()
-    assert [b.mixer["window"] for b in spec.blocks] == [None, 24, 24]
+    assert [b.part("mixer")["window"] for b in spec.blocks] == [None, 24, 24]
 
 
 @pytest.mark.parametrize("change,fragment", [
@@ -131,7 +131,7 @@ def test_corrupt_containers_are_refused(tmp_path):
 # --------------------------------------------------------------------------
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
-    d = write_model_folder(tmp_path / "m", dict(TINY["B"]), seed=3)
+    d = write_model_folder(tmp_path / "m", dict(TINY["B"], attention_bias=True), seed=3)     # the key given: biases are required
     tensors = dict(iter_tensors(d / "model.safetensors"))
     del tensors["model.layers.1.self_attn.k_proj.bias"]
     del tensors["model.norm.weight"]
@@ -151,16 +151,74 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert part in msg
 
 
-def test_tied_head_is_checked_against_the_file(tmp_path):
-    cfg = dict(TINY["A"])                                  # tied: the file must not hold an lm_head
+def test_the_head_follows_the_file(tmp_path):
+    """LitInfer uses a stored lm_head and ties to the embedding when there is none, whatever config.json says
+    (python/llaisys/models/qwen2.py:143-146, 196-199)."""
+    cfg = dict(TINY["A"])                                  # tied: random mode writes no lm_head
     d = write_model_folder(tmp_path / "m", cfg, seed=3)
-    names = [n for n, _ in iter_tensors(d / "model.safetensors")]
-    assert "lm_head.weight" not in names
+    tensors = dict(iter_tensors(d / "model.safetensors"))
+    assert "lm_head.weight" not in tensors
     m = DecoderModel.from_dir(d, "float32", "cpu")
-    assert m.lm_head is m.embedding                        # the table itself (python/llaisys/models/qwen2.py:196-199)
+    assert m.lm_head is m.embedding and m.head_is_tied     # the table itself
+    # a config that says "untied" over a file without a head: tied all the same
     cfg["tie_word_embeddings"] = False
     (d / "config.json").write_text(json.dumps(cfg))
-    with pytest.raises(WeightError, match="missing tensors.*lm_head.weight"):
+    m = DecoderModel.from_dir(d, "float32", "cpu")
+    assert m.lm_head is m.embedding and m.head_is_tied
+    # a tied config over a file that stores a head: the stored one is used
+    cfg["tie_word_embeddings"] = True
+    (d / "config.json").write_text(json.dumps(cfg))
+    head = torch.randn(cfg["vocab_size"], cfg["hidden_size"])
+    write_file(d / "model.safetensors", dict(tensors, **{"lm_head.weight": head}))
+    m = DecoderModel.from_dir(d, "float32", "cpu")
+    assert torch.equal(m.lm_head, head) and not m.head_is_tied
+    # a head of the wrong shape is still an error
+    write_file(d / "model.safetensors", dict(tensors, **{"lm_head.weight": head[:, :5].contiguous()}))
+    with pytest.raises(WeightError, match="wrong shapes.*lm_head.weight"):
+        DecoderModel.from_dir(d, "float32", "cpu")
+
+
+def test_the_other_names_of_litinfers_loader_are_accepted(tmp_path):
+    """transformer.wte.weight, model.lm_head.weight, transformer.ln_f.weight (python/llaisys/models/qwen2.py:139-149)."""
+    d = write_model_folder(tmp_path / "m", dict(TINY["B"]), seed=3)
+    tensors = dict(iter_tensors(d / "model.safetensors"))
+    want = DecoderModel.from_dir(d, "float32", "cpu")
+    renamed = {"model.embed_tokens.weight": "transformer.wte.weight", "lm_head.weight": "model.lm_head.weight",
+               "model.norm.weight": "transformer.ln_f.weight"}
+    write_file(d / "model.safetensors", {renamed.get(k, k): v for k, v in tensors.items()})
+    got = DecoderModel.from_dir(d, "float32", "cpu")
+    assert torch.equal(got.embedding, want.embedding) and torch.equal(got.lm_head, want.lm_head)
+    assert torch.equal(got.final_norm.weight, want.final_norm.weight)
+    # both names of one tensor at once: the second is unexpected
+    write_file(d / "model.safetensors", dict(tensors, **{"transformer.wte.weight": tensors["model.embed_tokens.weight"]}))
+    with pytest.raises(WeightError, match="unexpected tensors.*transformer.wte.weight"):
+        DecoderModel.from_dir(d, "float32", "cpu")
+
+
+def test_biases_follow_the_file_when_the_config_does_not_say(tmp_path):
+    """Qwen2's config.json has no attention_bias key and LitInfer's loader does not require the q/k/v biases
+    (python/llaisys/models/qwen2.py:220-230); a missing bias is none (src/llaisys/ops.cc:27-29)."""
+    cfg = dict(TINY["B"])
+    assert "attention_bias" not in cfg
+    d = write_model_folder(tmp_path / "m", cfg, seed=3)
+    tensors = dict(iter_tensors(d / "model.safetensors"))
+    assert "model.layers.1.self_attn.k_proj.bias" in tensors                  # random mode makes them
+    full = DecoderModel.from_dir(d, "float32", "cpu")
+    nh, nkv, dh = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    # one bias gone: zeros in its place, the others kept
+    write_file(d / "model.safetensors", {k: v for k, v in tensors.items() if k != "model.layers.1.self_attn.k_proj.bias"})
+    m = DecoderModel.from_dir(d, "float32", "cpu")
+    b = m.blocks[1].mixer.qkv.bias
+    assert torch.equal(b[:nh * dh], full.blocks[1].mixer.qkv.bias[:nh * dh])
+    assert torch.count_nonzero(b[nh * dh:(nh + nkv) * dh]) == 0
+    # all gone: no bias at all
+    write_file(d / "model.safetensors", {k: v for k, v in tensors.items() if not k.endswith("_proj.bias")})
+    m = DecoderModel.from_dir(d, "float32", "cpu")
+    assert all(blk.mixer.qkv.bias is None for blk in m.blocks)
+    # attention_bias false in the config: a stored bias is unexpected
+    (d / "config.json").write_text(json.dumps(dict(cfg, attention_bias=False)))
+    write_file(d / "model.safetensors", tensors)
+    with pytest.raises(WeightError, match="unexpected tensors"):
         DecoderModel.from_dir(d, "float32", "cpu")
 
 

@@ -139,6 +139,43 @@ def test_engine_run_ahead_gives_the_same_tokens(model_dirs, cpu_kernels):
     assert preempted > 0, "the small pools were meant to force preemptions in both modes"
 
 
+def test_abort_while_a_step_is_in_flight(model_dirs, cpu_kernels):
+    """With run_ahead a step is unread between calls.  Ending a request then, through the engine or straight through the
+    scheduler, must not cost the other requests of that step their tokens."""
+    from litinfer_b200.engine import Engine, EngineConfig
+    from litinfer_b200.models import DecoderModel
+
+    cfg, _ = P.read_model_folder(model_dirs["A"])
+    model = DecoderModel.from_dir(model_dirs["A"], "float32", "cpu")
+    prompts = [random_tokens(n, cfg["vocab_size"], 400 + n) for n in (5, 9, 12)]
+
+    def run(abort_how):
+        eng = Engine(model, EngineConfig(num_pages=16, max_num_seqs=4, max_tokens_per_step=32, use_graphs=False, run_ahead=True))
+        ids = [eng.add_request(p, 10) for p in prompts]
+        calls = 0
+        while eng.has_unfinished():
+            eng.step()
+            calls += 1
+            if calls == 5 and abort_how:
+                assert eng._ahead is not None, "the test wants a step in flight here"
+                if abort_how == "engine":
+                    eng.abort(ids[1])
+                else:
+                    eng.scheduler.abort(ids[1])
+            assert calls < 200
+        eng.drain()
+        eng.manager.check()
+        assert eng.manager.num_free_pages(0) == 16 and eng.manager.num_free_slots() == 4
+        return [eng.get_output(i) for i in ids], [eng.finish_reason(i) for i in ids]
+
+    whole, _ = run(None)
+    for how in ("engine", "scheduler"):
+        outs, reasons = run(how)
+        assert reasons[1] == "aborted" and reasons[0] == reasons[2] == "length"
+        assert outs[0] == whole[0] and outs[2] == whole[2], how
+        assert outs[1] == whole[1][:len(outs[1])] and len(outs[1]) < 10
+
+
 def test_toy_mixer_with_state_on_cpu_references(model_dirs, cpu_kernels):
     from test_engine_gpu import run_toy_mixer
 
@@ -385,3 +422,15 @@ def test_captured_paths_of_the_runner_with_the_capture_emulated(name, model_dirs
     assert r.graph_replays == len(tr.steps), "every step of the trace fits a captured path"
     assert len(r._graphs) >= 2 and len(r._step_graphs) >= 1
     rp.manager.check()
+
+
+def test_toy_mixer_with_state_through_the_engine_on_cpu_references(model_dirs, cpu_kernels):
+    from test_engine_gpu import run_toy_mixer_through_engine
+
+    run_toy_mixer_through_engine(model_dirs, "cpu")
+
+
+def test_toy_positions_and_block_arrangements_on_cpu_references(model_dirs, cpu_kernels):
+    from test_engine_gpu import run_toy_positions_and_blocks
+
+    run_toy_positions_and_blocks(model_dirs, "cpu", "float32")

@@ -169,39 +169,12 @@ def run_toy_mixer(model_dirs, device):
     from litinfer_b200.config import PartSpec
     from dataclasses import replace
 
-    class EmaMixer(Mixer):
-        def __init__(self, spec, prefix, dtype, device):
-            super().__init__(spec, prefix, dtype, device)
-            self.hidden = int(spec["hidden_size"])
-            self.decay = float(spec["decay"])
-            self.proj = FusedLinear(prefix, ["in_proj"], self.hidden, [self.hidden], False, dtype)
-
-        def params(self):
-            return self.proj.params()
-
-        def bind(self, tensors):
-            self.proj.bind(tensors)
-
-        def cache_requirement(self):
-            return FixedState((self.hidden,), torch.float32)
-
-        def forward(self, h, ctx, cache):
-            u = self.proj(h).float()
-            y = torch.empty_like(u)
-            for s in range(ctx.num_seqs):
-                lo, hi = ctx.host_q_start[s], ctx.host_q_start[s + 1]
-                st = cache.state[ctx.host_state_slots[s]]
-                for t in range(lo, hi):
-                    st.mul_(self.decay).add_((1 - self.decay) * u[t])
-                    y[t] = st
-            return y.to(self.dtype)
-
-    MIXERS.register("toy_ema", EmaMixer)
+    MIXERS.register("toy_ema", _ema_mixer_class())
     try:
         base = load_config(model_dirs["A"]).to_model_spec()
         blocks = list(base.blocks)
         toy = PartSpec("toy_ema", {"hidden_size": base.hidden_size, "decay": 0.75})
-        blocks[1] = replace(blocks[1], mixer=toy, mixer_prefix="ema.")
+        blocks[1] = blocks[1].with_part("mixer", toy, "ema.")
         spec = replace(base, blocks=tuple(blocks))
         model = DecoderModel.from_random(spec, 5, "float32", device)
         manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], 16, 16, 3, model.dtype, model.device)
@@ -229,6 +202,230 @@ def run_toy_mixer(model_dirs, device):
         MIXERS.unregister("toy_ema")
 
 
+def _ema_mixer_class():
+    """The toy mixer with state of its own (see run_toy_mixer), as a class to register."""
+    from litinfer_b200.parts import FixedState, FusedLinear, Mixer
+
+    class EmaMixer(Mixer):
+        def __init__(self, spec, prefix, dtype, device):
+            super().__init__(spec, prefix, dtype, device)
+            self.hidden = int(spec["hidden_size"])
+            self.decay = float(spec["decay"])
+            self.proj = FusedLinear(prefix, ["in_proj"], self.hidden, [self.hidden], False, dtype)
+
+        def params(self):
+            return self.proj.params()
+
+        def bind(self, tensors):
+            self.proj.bind(tensors)
+
+        def cache_requirement(self):
+            return FixedState((self.hidden,), torch.float32)
+
+        def forward(self, h, ctx, cache):
+            u = self.proj(h).float()
+            y = torch.empty_like(u)
+            for s in range(ctx.num_seqs):
+                lo, hi = ctx.host_q_start[s], ctx.host_q_start[s + 1]
+                st = cache.state[ctx.host_state_slots[s]]
+                for t in range(lo, hi):
+                    st.mul_(self.decay).add_((1 - self.decay) * u[t])
+                    y[t] = st
+            return y.to(self.dtype)
+
+    return EmaMixer
+
+
+def test_toy_mixer_with_state_through_the_engine_and_the_entry_point(model_dirs):
+    run_toy_mixer_through_engine(model_dirs, "cuda:0")
+
+
+def run_toy_mixer_through_engine(model_dirs, device):
+    """The mixer with state of its own under the scheduler: default engine options (graphs asked for: the runner must
+    not capture anything for such a model), several requests decoding together, a pool so small that a request is
+    preempted and recomputed (its slot is cleared when it is admitted again), and the entry point's generate.  Every
+    request's tokens equal those of the same request run alone."""
+    from dataclasses import replace
+
+    from litinfer_b200 import CausalLM, DecoderModel, Engine, EngineConfig
+    from litinfer_b200.config import PartSpec, load_config
+    from litinfer_b200.parts import MIXERS
+
+    MIXERS.register("toy_ema", _ema_mixer_class())
+    try:
+        base = load_config(model_dirs["A"]).to_model_spec()
+        blocks = list(base.blocks)
+        blocks[1] = blocks[1].with_part("mixer", PartSpec("toy_ema", {"hidden_size": base.hidden_size, "decay": 0.75}), "ema.")
+        spec = replace(base, blocks=tuple(blocks))
+        model = DecoderModel.from_random(spec, 5, "float32", device)
+        prompts = [random_tokens(n, spec.vocab_size, 900 + n) for n in (30, 28, 27)]
+
+        alone = []
+        for p in prompts:
+            eng = Engine(model, EngineConfig(num_pages=16, max_num_seqs=1))          # use_graphs is on by default
+            assert not eng.runner.use_graphs, "nothing of a model with state of its own may be captured"
+            rid = eng.add_request(p, 24)
+            eng.run_to_completion()
+            alone.append(eng.get_output(rid))
+        assert len({tuple(a) for a in alone}) == 3
+
+        for run_ahead in (False, True):
+            eng = Engine(model, EngineConfig(num_pages=7, max_num_seqs=4, max_tokens_per_step=64, prefill_chunk=16, run_ahead=run_ahead))
+            ids = [eng.add_request(p, 24) for p in prompts]
+            eng.run_to_completion()
+            assert eng.scheduler.num_preemptions > 0, "the pool was meant to be too small for all three"
+            eng.manager.check()
+            assert eng.manager.num_free_pages(0) == 7 and eng.manager.num_free_slots() == 4
+            assert eng.runner.graph_replays == 0
+            for rid, a in zip(ids, alone):
+                assert eng.get_output(rid) == a, f"request {rid} (run_ahead {run_ahead}): tokens differ from the request run alone"
+
+        front = CausalLM(None, device=device, model=model, num_pages=16)
+        for p, a in zip(prompts, alone):
+            assert front.generate(p, max_new_tokens=24) == a
+    finally:
+        MIXERS.unregister("toy_ema")
+
+
+# --------------------------------------------------------------------------
+# toy position encodings that are no rotation, and a block of another shape
+# --------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_positions_and_block_arrangements(dtype, model_dirs):
+    run_toy_positions_and_blocks(model_dirs, "cuda:0", dtype)
+
+
+def run_toy_positions_and_blocks(model_dirs, device, dtype):
+    """Registered from here, with no change to the package: learned absolute positions (a table added to the residual
+    stream after the embedding: the model's own position part), attention without any position encoding, a block with
+    four norms (one before and one after each of mixer and feed-forward), a block without a feed-forward, a factor on
+    the embedding and a cap on the logits.  Each model whole, in portions and token by token: bitwise equal in float32."""
+    from dataclasses import replace
+
+    from litinfer_b200 import DecoderModel, StepItem
+    from litinfer_b200 import kernels as K
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.config import PartSpec, load_config
+    from litinfer_b200.engine import ModelRunner
+    from litinfer_b200.parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, Block, Position
+    from litinfer_b200.weights.loader import ParamSpec
+
+    class LearnedPositions(Position):
+        def __init__(self, spec, prefix, dtype, device):
+            super().__init__(spec, prefix, dtype, device)
+            self.size, self.positions = int(spec["size"]), int(spec["positions"])
+            self.table = None
+
+        def params(self):
+            return [ParamSpec(self.prefix + "positions.weight", (self.positions, self.size), role="keep", std=0.5)]
+
+        def bind(self, tensors):
+            self.table = tensors.pop(self.prefix + "positions.weight").float()
+
+        def add_to_stream(self, x32, ctx):
+            x32.add_(self.table[ctx.positions.long()])
+
+    class SandwichBlock(Block):
+        """x += post_norm(Mixer(pre_norm(x))); x += post_norm(FeedForward(pre_norm(x)))."""
+
+        def __init__(self, spec, prefix, dtype, device):
+            super().__init__(spec, prefix, dtype, device)
+            self.mixer_norm = self.build(NORMS, "mixer_norm")
+            self.mixer = self.build(MIXERS, "mixer")
+            self.mixer_post_norm = self.build(NORMS, "mixer_post_norm")
+            self.feed_forward_norm = self.build(NORMS, "feed_forward_norm")
+            self.feed_forward = self.build(FEED_FORWARDS, "feed_forward")
+            self.feed_forward_post_norm = self.build(NORMS, "feed_forward_post_norm")
+
+        def parts(self):
+            return [self.mixer_norm, self.mixer, self.mixer_post_norm, self.feed_forward_norm, self.feed_forward, self.feed_forward_post_norm]
+
+        def forward(self, x32, ctx, cache, carry, next_entry=None):
+            if carry is not None and carry.delta is not None:
+                K.residual_add(x32, carry.delta)
+            y = self.mixer.forward(self.mixer_norm.forward(x32), ctx, cache)
+            K.residual_add(x32, self.mixer_post_norm.forward(y.float()))
+            y = self.feed_forward.forward(self.feed_forward_norm.forward(x32), ctx)
+            K.residual_add(x32, self.feed_forward_post_norm.forward(y.float()))
+            return x32, None
+
+    POSITIONS.register("toy_learned", LearnedPositions)
+    BLOCKS.register("toy_sandwich", SandwichBlock)
+    try:
+        base = load_config(model_dirs["A"]).to_model_spec()
+        H = base.hidden_size
+        norm = base.blocks[0].part("mixer_norm")
+        toks = random_tokens(50, base.vocab_size, 9)
+        cuts_list = ([50], [7, 2, 16, 1, 1, 13, 1, 1, 1, 7], [1] * 50)
+
+        def logits_of(spec, cuts):
+            model = DecoderModel.from_random(spec, 5, dtype, device)
+            manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], 16, 16, 2, model.dtype, model.device)
+            runner = ModelRunner(model, manager)
+            rc = manager.admit(1)
+            outs, pos = [], 0
+            for n in cuts:
+                manager.extend(rc, pos + n)
+                outs.append(runner.step([StepItem(rc, toks[pos:pos + n], list(range(n)))]).clone())
+                pos += n
+            manager.release(rc)
+            return torch.cat(outs)
+
+        def all_cuts_agree(spec, what):
+            whole = logits_of(spec, cuts_list[0])
+            assert torch.isfinite(whole).all(), what
+            for cuts in cuts_list[1:]:
+                cut = logits_of(spec, cuts)
+                if dtype == "float32" and str(device).startswith("cuda"):
+                    assert torch.equal(whole, cut), f"{what}: float32 logits differ between cuts by {(whole - cut).abs().max()}"
+                elif dtype == "float32":                   # the plain references under the CPU twin of this test sum in other orders
+                    assert (whole - cut).abs().max() <= 1e-5, what
+                else:
+                    assert (whole - cut).abs().max() <= 0.03 * float(whole.abs().max()), what
+            return whole
+
+        reference = all_cuts_agree(base, "the unchanged model")
+
+        # attention without positions: the same keys in another order give the same logits at the last token
+        bare = tuple(b.with_part("mixer", b.part("mixer").replace(position=None)) for b in base.blocks)
+        no_pos = replace(base, blocks=bare)
+        got = all_cuts_agree(no_pos, "no positions")
+        assert (got - reference).abs().max() > 1e-3, "dropping the rotation must matter"
+
+        # learned absolute positions on top of it, as the model's own position part
+        learned = replace(no_pos, position=PartSpec("toy_learned", {"size": H, "positions": base.max_position_embeddings}))
+        got_learned = all_cuts_agree(learned, "learned positions")
+        assert (got_learned - got).abs().max() > 1e-2, "the table of positions must matter"
+        names = [p.name for p in DecoderModel(learned, "float32", "meta").params()]
+        assert "model.positions.weight" in names
+
+        # a block with four norms in the second layer, under tensor names of its own
+        sandwich = base.blocks[1].with_kind("toy_sandwich").with_part("mixer_post_norm", norm).with_part("feed_forward_post_norm", norm, "post_ffn_norm.")
+        spec4 = replace(base, blocks=(base.blocks[0], sandwich))
+        got4 = all_cuts_agree(spec4, "a block with four norms")
+        assert (got4 - reference).abs().max() > 1e-3
+        names = [p.name for p in DecoderModel(spec4, "float32", "meta").params()]
+        assert "model.layers.1.mixer_post_norm.weight" in names and "model.layers.1.post_ffn_norm.weight" in names
+
+        # a layer without a feed-forward, first and last
+        for where in (0, 1):
+            blocks = list(base.blocks)
+            blocks[where] = blocks[where].with_part("feed_forward", None).with_part("feed_forward_norm", None)
+            got = all_cuts_agree(replace(base, blocks=tuple(blocks)), f"layer {where} without a feed-forward")
+            assert (got - reference).abs().max() > 1e-3
+
+        # a factor on the embedding and a cap on the logits
+        scaled = all_cuts_agree(replace(base, embedding_scale=3.0, logit_cap=2.0), "embedding scale and logit cap")
+        assert float(scaled.abs().max()) <= 2.0 and (scaled - reference).abs().max() > 1e-3
+        capped = all_cuts_agree(replace(base, logit_cap=0.5), "logit cap")
+        want = 0.5 * torch.tanh(reference / 0.5)
+        assert (capped - want).abs().max() <= (1e-5 if dtype == "float32" else 0.02)
+    finally:
+        POSITIONS.unregister("toy_learned")
+        BLOCKS.unregister("toy_sandwich")
+
+
 # --------------------------------------------------------------------------
 # a toy feed-forward with routing and a toy position encoding
 # --------------------------------------------------------------------------
@@ -251,7 +448,7 @@ def run_toy_feed_forward_and_positions(model_dirs, device, dtype):
     from litinfer_b200.cache import CacheManager
     from litinfer_b200.config import PartSpec, load_config
     from litinfer_b200.engine import ModelRunner
-    from litinfer_b200.parts import FEED_FORWARDS, POSITIONS, FeedForward, FusedLinear, Position
+    from litinfer_b200.parts import FEED_FORWARDS, POSITIONS, FeedForward, FusedLinear, Position, Rotary
     from litinfer_b200.weights.loader import ParamSpec
 
     class RoutedFF(FeedForward):
@@ -296,6 +493,9 @@ def run_toy_feed_forward_and_positions(model_dirs, device, dtype):
             j = torch.arange(self.rotary_dim // 2, dtype=torch.float32)
             self.denominators = (float(spec["stretch"]) * torch.pow(torch.tensor(float(spec["theta"])), 2.0 * j / self.rotary_dim)).to(self.device)
 
+        def rotary(self, ctx):
+            return Rotary(self.denominators, self.rotary_dim)
+
     FEED_FORWARDS.register("toy_routed", RoutedFF)
     POSITIONS.register("toy_stretched_rope", StretchedRope)
     try:
@@ -327,11 +527,9 @@ def run_toy_feed_forward_and_positions(model_dirs, device, dtype):
         routed = PartSpec("toy_routed", {"hidden_size": H, "expert_size": 48, "experts": 4})
 
         def with_stretch(stretch):
-            mixer = blocks[1].mixer
+            mixer = blocks[1].part("mixer")
             pos = PartSpec("toy_stretched_rope", {"theta": mixer["position"]["theta"], "stretch": stretch})
-            params = dict(mixer.params)
-            params["position"] = pos
-            return replace(blocks[1], mixer=PartSpec(mixer.kind, params), feed_forward=routed)
+            return blocks[1].with_part("mixer", mixer.replace(position=pos)).with_part("feed_forward", routed)
 
         def logits_of(stretch, cuts):
             spec = replace(base, blocks=(blocks[0], with_stretch(stretch)) + tuple(blocks[2:]))
