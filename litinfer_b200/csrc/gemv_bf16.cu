@@ -24,6 +24,8 @@
 #include "no_alloc.h"
 #include "row_scale.cuh"
 
+#include <mutex>
+
 namespace {
 
 constexpr int kMaxM = 64;
@@ -503,8 +505,10 @@ static __device__ __align__(256) float g_static_partial[LI_STATIC_PARTIAL_FLOATS
 static __device__ __align__(256) unsigned g_static_counters[LI_STATIC_TILES];
 
 Workspace g_static_ws[16];
+std::mutex g_static_lock;
 
 int static_workspace(Workspace** ws) {
+    std::lock_guard<std::mutex> guard(g_static_lock);      // two host threads may make their first call together
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return li_fail("linear (gemv, static scratch): cudaGetDevice: %s", cudaGetErrorString(e));

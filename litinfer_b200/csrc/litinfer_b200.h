@@ -136,9 +136,21 @@ int li_argmax(const float* logits, int* out, int R, int V, cudaStream_t stream);
  * max with a counter-based generator, independent of the batch. */
 int li_sample(const float* logits, const int* params, int* out, int R, int V, cudaStream_t stream);
 
+/* ---- fill_random.cu ---- */
+/* out[i] = mean + std * n(key, i), n standard normal from a counter-based generator (a pure function of key and i). */
+int li_fill_normal(void* out, int dtype, long long n, unsigned long long key, float mean, float std, cudaStream_t stream);
+
+/* out[i] = an integer in [0, range) from (key, i). */
+int li_fill_randint(int* out, long long n, unsigned long long key, int range, cudaStream_t stream);
+
 /* ---- tcgen05_host.cu ---- */
 /* 0, or the status a tcgen05 kernel left when one of its bounded waits ran out. */
 int li_tcgen05_status();
+
+/* Tests: clear the status word; make a bounded wait run out on purpose (one thread, a barrier nobody arrives on,
+ * a limit in microseconds): the status then reads 99. */
+void li_tcgen05_clear_status();
+int li_tcgen05_wait_selftest(int limit_us, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -6,9 +6,8 @@
  *
  * Who needs it: a host program that owns all device memory itself and forbids
  * cudaMalloc inside libraries (an inference server with a fixed arena, a plugin
- * loaded into another runtime), code on a latency-critical path where an
- * allocation would synchronise the device, and code that runs while a stream is
- * being captured, where allocation calls are not allowed.  The ordinary entry
+ * loaded into another runtime) and code on a latency-critical path where an
+ * allocation would synchronise the device.  The ordinary entry
  * point (li_linear) allocates a split-k workspace with cudaMalloc the first time
  * it runs on a device; this one never calls cudaMalloc, cudaFree or any other
  * allocating routine.
@@ -24,7 +23,9 @@
  *
  * The first call on a device looks up the arrays' device addresses
  * (cudaGetSymbolAddress, with that device current).  Make that first call before
- * any stream capture.
+ * any stream capture.  The look-up is guarded by a lock, so host threads may make
+ * their first calls at the same time; the calls themselves are ordered by the
+ * caller (next paragraph).
  *
  * All calls share the arrays, and the arrays keep what the last call left: each
  * call clears the counters it is going to use (an asynchronous memset on the

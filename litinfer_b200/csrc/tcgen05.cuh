@@ -27,8 +27,8 @@ __device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// Bounded wait for the phase with the given parity; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+// Bounded wait for the phase with the given parity; false if the limit (nanoseconds of %globaltimer) ran out.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity, unsigned long long limit_ns = kWaitLimitNs) {
     const unsigned addr = smem_u32(bar);
     unsigned long long t0 = 0;
     for (unsigned spin = 0;; ++spin) {
@@ -45,7 +45,7 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
             unsigned long long now;
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
             if (t0 == 0) t0 = now;
-            else if (now - t0 > kWaitLimitNs) return false;
+            else if (now - t0 > limit_ns) return false;
         }
         if (spin > (1u << 30)) return false;
     }

@@ -73,3 +73,34 @@ LI_EXPORT int li_tcgen05_status() {
     if (tc::setup(&f, &h, &d)) return -1;
     return *h;
 }
+
+// Clears the status word (after a test made a wait run out; a real run-out means the results since are invalid).
+LI_EXPORT void li_tcgen05_clear_status() {
+    tc::EncodeTiledFn f;
+    int *h = nullptr, *d = nullptr;
+    if (tc::setup(&f, &h, &d) == 0) *h = 0;
+}
+
+namespace {
+// One thread waits, with a short limit, on a barrier that nobody arrives on: the wait runs out, the thread raises the
+// status word and returns.  Nothing is in flight and no tensor memory is held, so there is nothing to clean up.
+__global__ void wait_runs_out_kernel(unsigned long long limit_ns, int* error_flag, int code) {
+    __shared__ unsigned long long bar;
+    if (threadIdx.x == 0) {
+        tc::mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (!tc::mbar_wait(&bar, 0, limit_ns)) atomicExch(error_flag, code);
+    }
+}
+}  // namespace
+
+// For tests: exercises the path a bounded wait takes when its limit runs out (limit in microseconds, at most a second).
+// Afterwards li_tcgen05_status() reads 99 until li_tcgen05_clear_status().
+LI_EXPORT int li_tcgen05_wait_selftest(int limit_us, cudaStream_t stream) {
+    LI_REQUIRE(limit_us >= 1 && limit_us <= 1000000, "tcgen05 wait self-test: limit of %d us is outside [1, 1000000]", limit_us);
+    tc::EncodeTiledFn f;
+    int *h = nullptr, *d = nullptr;
+    if (int rc = tc::setup(&f, &h, &d)) return rc;
+    wait_runs_out_kernel<<<1, 32, 0, stream>>>((unsigned long long)limit_us * 1000ull, d, 99);
+    return li_check_launch("tcgen05 wait self-test");
+}

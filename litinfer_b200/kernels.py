@@ -146,6 +146,21 @@ def residual_add(x32: torch.Tensor, delta: torch.Tensor) -> None:
     _check(library().li_residual_add(_p(x32), _p(delta), _i(_dt(delta)), _l(x32.numel()), _stream(x32)), "residual_add")
 
 
+def fill_normal(out: torch.Tensor, key: int, mean: float, std: float) -> None:
+    """``out[i] = mean + std * n(key, i)`` (flat index i) with n standard normal from the library's counter-based
+    generator; float32 or bfloat16.  ``litinfer_b200.weights.random_init`` restates the recipe on the host."""
+    _need(out, "fill_normal output")
+    _check(library().li_fill_normal(_p(out), _i(_dt(out)), _l(out.numel()), ctypes.c_ulonglong(key & ((1 << 64) - 1)), _f(mean), _f(std),
+                                    _stream(out)), "fill_normal")
+
+
+def fill_randint(out: torch.Tensor, key: int, high: int) -> None:
+    """``out[i]`` = an integer in [0, high) from (key, i); int32."""
+    _need(out, "fill_randint output", torch.int32)
+    _check(library().li_fill_randint(_p(out), _l(out.numel()), ctypes.c_ulonglong(key & ((1 << 64) - 1)), _i(high), _stream(out)),
+           "fill_randint")
+
+
 def scale_inplace(x32: torch.Tensor, factor: float) -> None:
     """x32 *= factor (float32, in place)."""
     _need(x32, "scale operand", torch.float32)

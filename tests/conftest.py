@@ -61,7 +61,15 @@ TINY_C = dict(
     rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=1024,
     eos_token_id=None, use_sliding_window=False)
 
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# The second configuration exactly as the benchmark description gives it (no window, round sizes): the variant above is
+# the harder test, this one has nothing in it that LitInfer's own code does not pin.
+TINY_B0 = dict(
+    architectures=["Qwen2ForCausalLM"], torch_dtype="float32", num_hidden_layers=3, hidden_size=96,
+    num_attention_heads=3, num_key_value_heads=1, head_dim=32, intermediate_size=256, vocab_size=384,
+    rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False, max_position_embeddings=256,
+    eos_token_id=None, use_sliding_window=False)
+
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "B0": TINY_B0}
 
 
 def _qwen2(layers, hidden, heads, kv_heads, head_dim, intermediate, vocab, theta=10000.0, eps=1e-6, tie=False, window=None,
@@ -92,7 +100,7 @@ def model_dirs(tmp_path_factory):
     out = {}
     for name, cfg in TINY.items():
         d = tmp_path_factory.mktemp(f"tiny{name}")
-        write_model_folder(d, dict(cfg), seed=1234 + ord(name), store_dtype="float32")
+        write_model_folder(d, dict(cfg), seed=1234 + sum(map(ord, name)), store_dtype="float32")
         out[name] = d
     return out
 

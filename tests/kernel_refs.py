@@ -164,6 +164,37 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, 
     _store(out, res.reshape(T, num_heads * head_dim))
 
 
+def paged_attention_dense(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
+                          num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None,
+                          singles=0):
+    """The same formula as :func:`paged_attention`, a sequence at a time instead of a token and a head at a time (for
+    contexts of thousands of keys): scores of all the sequence's tokens against all its keys in float32, keys outside
+    [p - window + 1, p] masked, softmax, weighted sum."""
+    T = qkv.shape[0]
+    page_size = k_cache.shape[2]
+    group = num_heads // num_kv_heads
+    q = qkv[:, :num_heads * head_dim].reshape(T, num_heads, head_dim).float()
+    res = torch.zeros(T, num_heads, head_dim, dtype=torch.float32, device=qkv.device)
+    starts, lens = q_start.tolist(), ctx_lens.tolist()
+    for s, c in enumerate(lens):
+        lo, hi = starts[s], starts[s + 1]
+        if hi == lo:
+            continue
+        keys = torch.arange(c, device=qkv.device)
+        pages = block_table[s].long()[keys // page_size]
+        offs = keys % page_size
+        k = k_cache[pages, :, offs].float().repeat_interleave(group, dim=1)          # [c, heads, dh]
+        v = v_cache[pages, :, :, offs].float().repeat_interleave(group, dim=1)
+        pos = positions[lo:hi].long()
+        sc = torch.einsum("thd,chd->htc", q[lo:hi], k) * scale
+        seen = keys[None, :] <= pos[:, None]
+        if window:
+            seen &= keys[None, :] > pos[:, None] - window
+        sc = sc.masked_fill(~seen[None], float("-inf"))
+        res[lo:hi] = torch.einsum("htc,chd->thd", torch.softmax(sc, dim=-1), v)
+    _store(out, res.reshape(T, num_heads * head_dim))
+
+
 def scale_inplace(x32, factor):
     x32.mul_(factor)
 

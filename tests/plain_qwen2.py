@@ -269,16 +269,35 @@ def plain_candidates(logits, temperature, top_k, top_p):
     return order, pr
 
 
-def plain_greedy(cfg, w, prompt, n_new, schedule=None):
-    """n_new greedy tokens by recomputing the whole sequence each time; also
-    the smallest margin between the best and second logit that was seen."""
+def plain_greedy_margins(cfg, w, prompt, n_new, schedule=None):
+    """n_new greedy tokens by recomputing the whole sequence each time, and for each of them the margin
+    between the best and the second logit."""
     toks = list(prompt)
-    out, margin = [], float("inf")
+    out, margins = [], []
     for _ in range(n_new):
         lg = plain_forward(cfg, w, toks, schedule)[-1]
         top2 = torch.topk(lg, 2).values
-        margin = min(margin, float(top2[0] - top2[1]))
+        margins.append(float(top2[0] - top2[1]))
         t = plain_argmax(lg)
         out.append(t)
         toks.append(t)
-    return out, margin
+    return out, margins
+
+
+def plain_greedy(cfg, w, prompt, n_new, schedule=None):
+    """The tokens of :func:`plain_greedy_margins` and the smallest margin that was seen."""
+    out, margins = plain_greedy_margins(cfg, w, prompt, n_new, schedule)
+    return out, min(margins, default=float("inf"))
+
+
+def same_up_to_a_near_tie(got, ref, margins, small=0.05) -> bool:
+    """Whether greedy tokens ``got`` of an implementation that rounds differently (bfloat16) are acceptable against
+    the plain ``ref``: equal, or equal up to a position at which the plain model's own margin is below ``small``, where
+    rounding may legitimately pick the runner-up (after that the two sequences are different texts and nothing can
+    be said).  A difference at a position with a clear margin is a fault."""
+    if len(got) != len(ref):
+        return False
+    for i, (a, b) in enumerate(zip(got, ref)):
+        if a != b:
+            return margins[i] < small
+    return True

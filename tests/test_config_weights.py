@@ -259,3 +259,32 @@ def test_random_weights_mode(tmp_path):
     # the folder loads back through the name path
     m = DecoderModel.from_dir(d1, "float32", "cpu")
     assert torch.equal(m.blocks[0].feed_forward.down.weight, w)
+
+
+def test_the_generator_of_random_weights_against_its_plain_restatement():
+    """The package's NumPy path (what writes model folders) gives, bit for bit, what the element-at-a-time restatement in
+    tests/plain_random.py gives; the series inside it are accurate; a tensor depends on the seed and its own name only."""
+    import numpy as np
+
+    import plain_random as PR
+    from litinfer_b200.weights.random_init import tensor_key
+
+    assert tensor_key(11, "model.norm.weight") == PR.tensor_key(11, "model.norm.weight")
+    for name, shape, init, std in (("a.weight", (7, 9), "normal", 0.02), ("b.weight", (64,), "ones_normal", 0.02), ("c", (1001,), "normal", 0.5)):
+        got = random_tensor(ParamSpec(name, shape, init=init, std=std), 11).numpy().reshape(-1)
+        mean, sd = (1.0, 0.1) if init == "ones_normal" else (0.0, std)
+        want = PR.normal(PR.tensor_key(11, name), got.size, mean, sd)
+        assert got.dtype == np.float32 and np.array_equal(got.view(np.uint32), want.view(np.uint32)), name
+    ids = random_tensor(ParamSpec("t", (33,), role="table", init="randint"), 11)
+    assert ids.dtype == torch.int32 and np.array_equal(ids.numpy(), PR.randint(PR.tensor_key(11, "t"), 33, 1 << 15))
+    # a large tensor is drawn in slabs on several threads: the same values as in one piece
+    from litinfer_b200.weights.random_init import _host_normal, normal_pairs
+
+    n = (1 << 20) + 3
+    whole = _host_normal(5, n, 0.0, 1.0).numpy()
+    piece = normal_pairs(5, 0, (n + 1) // 2).reshape(-1)[:n]
+    assert np.array_equal(whole, piece)
+    assert abs(float(whole.mean())) < 0.005 and abs(float(whole.std()) - 1.0) < 0.005 and 4.0 < float(np.abs(whole).max()) < 6.5
+    assert abs(float((np.abs(whole) > 2.0).mean()) - 0.0455) < 0.002
+    worst_ln, worst_sc = PR.series_errors()
+    assert worst_ln < 2e-6 and worst_sc < 3e-7, (worst_ln, worst_sc)

@@ -16,14 +16,14 @@ pytestmark = pytest.mark.gpu
 
 
 def plain_generate(cfg, w, prompt, n_new, params=None, schedule=None):
-    """Tokens of the plain model with the engine's sampling rule, and the smallest
-    margin between the chosen token's score and the runner-up (greedy only)."""
-    toks, out, margin = list(prompt), [], float("inf")
+    """Tokens of the plain model with the engine's sampling rule, and per token the margin between the chosen token's
+    score and the runner-up (greedy only)."""
+    toks, out, margin = list(prompt), [], []
     for i in range(n_new):
         lg = P.plain_forward(cfg, w, toks, schedule)[-1]
         if params is None:
             top2 = torch.topk(lg, 2).values
-            margin = min(margin, float(top2[0] - top2[1]))
+            margin.append(float(top2[0] - top2[1]))
             t = P.plain_argmax(lg)
         else:
             t, _ = R.sample_row(lg, params["temperature"], params["top_k"], params["top_p"], params["seed"], i)
@@ -40,17 +40,20 @@ def test_greedy_generation_through_entry_point(dtype, model_dirs):
     if dtype == "bfloat16":
         w = bf16_round(w)
     model = Qwen2(str(model_dirs["A"]), dtype=dtype)
+    exact = 0
     for n in (5, 11, 17):
         prompt = random_tokens(n, cfg["vocab_size"], 300 + n)
-        ref, margin = plain_generate(cfg, w, prompt, 8)
+        ref, margins = plain_generate(cfg, w, prompt, 8)
         got = model.generate(prompt, max_new_tokens=8)
         assert len(got) == 8
+        exact += got == ref
         if dtype == "float32":
-            assert margin > 1e-4
+            assert min(margins) > 1e-4
             assert got == ref
         else:
-            # bfloat16 may legitimately pick the runner-up where the plain model's margin is tiny
-            assert got == ref or margin < 0.05, f"prompt {n}: {got} vs {ref}, margin {margin}"
+            # bfloat16 may legitimately pick the runner-up, but only where the plain model's own margin is tiny
+            assert P.same_up_to_a_near_tie(got, ref, margins), f"prompt {n}: {got} vs {ref}, margins {margins}"
+    assert exact >= 2, "bfloat16 flipped a near-tie in more than one prompt of three"
     assert model.generate(prompt, max_new_tokens=0) == []
     assert len(model.generate(prompt)) == 1                      # None means one token (qwen2.py:324)
     with pytest.raises(ValueError):
@@ -60,13 +63,15 @@ def test_greedy_generation_through_entry_point(dtype, model_dirs):
     assert list(model.generate_stream(prompt, max_new_tokens=4)) == toks
 
 
-def test_engine_sampling_is_reproducible_and_batch_independent(model_dirs):
+@pytest.mark.parametrize("name", ["B", "B0"])
+def test_engine_sampling_is_reproducible_and_batch_independent(name, model_dirs):
     """Config B's workload: prompts of 1/9/33/40 tokens in 16-token portions mixed with
-    decoding, temperature 0.8 from a fixed seed, 12 tokens each."""
+    decoding, temperature 0.8 from a fixed seed, 12 tokens each; on the configuration exactly as given and on its
+    variant with a window and sizes that are no round numbers."""
     from litinfer_b200 import Qwen2
 
-    cfg, w = P.read_model_folder(model_dirs["B"])
-    model = Qwen2(str(model_dirs["B"]), dtype="float32", num_pages=24, max_num_seqs=4, max_tokens_per_step=32, prefill_chunk=16)
+    cfg, w = P.read_model_folder(model_dirs[name])
+    model = Qwen2(str(model_dirs[name]), dtype="float32", num_pages=24, max_num_seqs=4, max_tokens_per_step=32, prefill_chunk=16)
     prompts = [random_tokens(n, cfg["vocab_size"], 500 + n) for n in (1, 9, 33, 40)]
     par = dict(temperature=0.8, top_k=0, top_p=1.0)
     model.engine_start()
@@ -144,8 +149,8 @@ def test_engine_preempts_and_recomputes_when_pages_run_out(model_dirs):
     eng.manager.check()
     assert eng.manager.num_free_pages(0) == 7
     for rid, p in zip(ids, prompts):
-        ref, margin = plain_generate(cfg, w, p, 24)
-        assert margin > 1e-4
+        ref, margins = plain_generate(cfg, w, p, 24)
+        assert min(margins) > 1e-4
         assert eng.get_output(rid) == ref
 
 
@@ -552,9 +557,8 @@ def run_toy_feed_forward_and_positions(model_dirs, device, dtype):
         scale = float(whole.abs().max())
         assert (whole - cut).abs().max() <= (1e-4 if dtype == "float32" else 0.03 * scale)
         other = logits_of(1.0, [50])
-        # with random weights attention is nearly uniform and positions move the logits little: measurable in float32,
-        # within rounding in bfloat16 (there only: not the same numbers)
-        assert (whole[10:] - other[10:]).abs().max() > (1e-3 if dtype == "float32" else 0.0), "the stretch of the positions must matter"
+        # with random weights attention is nearly uniform and positions move the logits little, but measurably
+        assert (whole[10:] - other[10:]).abs().max() > 1e-3, "the stretch of the positions must matter"
     finally:
         FEED_FORWARDS.unregister("toy_routed")
         POSITIONS.unregister("toy_stretched_rope")
@@ -573,10 +577,10 @@ def test_prompts_that_come_back_run_from_captured_shapes(dtype, model_dirs):
         w = bf16_round(w)
     front = Qwen2(str(model_dirs["C"]), dtype=dtype, max_num_seqs=4, max_tokens_per_step=96, prefill_chunk=80)
     prompt = random_tokens(150, cfg["vocab_size"], 321)
-    ref, margin = plain_generate(cfg, w, prompt, 6)
+    ref, margins = plain_generate(cfg, w, prompt, 6)
     for _ in range(3):
         got = front.generate(prompt, max_new_tokens=6)
-        assert got == ref or (dtype == "bfloat16" and margin < 0.05), f"{got} vs {ref} (margin {margin})"
+        assert got == ref or (dtype == "bfloat16" and P.same_up_to_a_near_tie(got, ref, margins)), f"{got} vs {ref} (margins {margins})"
     assert len(front._single.runner._step_graphs) >= 1, "the portions of 80 and 70 tokens came back and were meant to be captured"
     prompts = [random_tokens(n, cfg["vocab_size"], 700 + n) for n in (150, 97, 130, 66)]
     front.engine_start()
@@ -586,6 +590,9 @@ def test_prompts_that_come_back_run_from_captured_shapes(dtype, model_dirs):
     outs = [front.engine_get_output(i) for i in ids]
     assert front._eng().runner.graph_replays > 0
     front.engine_stop()
+    exact = 0
     for p, o in zip(prompts, outs):
         r, m = plain_generate(cfg, w, p, 5)
-        assert o == r or (dtype == "bfloat16" and m < 0.05), f"prompt of {len(p)}: {o} vs {r} (margin {m})"
+        exact += o == r
+        assert o == r or (dtype == "bfloat16" and P.same_up_to_a_near_tie(o, r, m)), f"prompt of {len(p)}: {o} vs {r} (margins {m})"
+    assert exact >= len(prompts) - 1

@@ -452,16 +452,16 @@ def make_attention_case(q_lens, ctx_lens, nh, nkv, dh, page, dtype, seed=0, extr
                 ctx_lens=list(ctx_lens), q_lens=list(q_lens), nh=nh, nkv=nkv, dh=dh, dtype=dtype)
 
 
-def run_attention_case(c, window, implementation=None, old_lens=None, singles=0):
+def run_attention_case(c, window, implementation=None, old_lens=None, singles=0, dense_reference=False):
     d = dev()
     page, nkv, dh = c["page"], c["nkv"], c["dh"]
     kc = torch.zeros(c["pages"], nkv, page, dh, dtype=c["dtype"])
     vc = torch.zeros(c["pages"], nkv, dh, page, dtype=c["dtype"])
     for s in range(c["S"]):
-        for t in range(c["ctx_lens"][s]):
-            p = int(c["bt"][s, t // page])
-            kc[p, :, t % page] = c["keys"][s][t]
-            vc[p, :, :, t % page] = c["vals"][s][t]
+        t = torch.arange(c["ctx_lens"][s])
+        pages, offs = c["bt"][s].long()[t // page], t % page
+        kc[pages, :, offs] = c["keys"][s]
+        vc[pages, :, :, offs] = c["vals"][s]
     args = dict(
         qkv=c["qkv"].to(d), k_cache=kc.to(d), v_cache=vc.to(d), block_table=c["bt"].to(d),
         q_start=torch.tensor(c["q_start"], dtype=torch.int32, device=d), ctx_lens=torch.tensor(c["ctx_lens"], dtype=torch.int32, device=d),
@@ -473,8 +473,9 @@ def run_attention_case(c, window, implementation=None, old_lens=None, singles=0)
     K().paged_attention(args["qkv"], out, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
                         args["seq_of_token"], args["positions"], *tail, implementation=implementation,
                         old_lens=None if old_lens is None else torch.tensor(old_lens, dtype=torch.int32, device=d), singles=singles)
-    R.paged_attention(args["qkv"], ref, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
-                      args["seq_of_token"], args["positions"], *tail)
+    reference = R.paged_attention_dense if dense_reference else R.paged_attention
+    reference(args["qkv"], ref, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
+              args["seq_of_token"], args["positions"], *tail)
     return out, ref
 
 
@@ -631,6 +632,68 @@ def test_attention_tcgen05_far_key_and_window_edge():
         assert bool(near) == visible, f"key {key_pos} should be {'visible' if visible else 'hidden'}"
 
 
+def _planted_value_comes_out(c, out, s, h_kv, key_pos, q_token, what):
+    nh, nkv, dh = c["nh"], c["nkv"], c["dh"]
+    v = c["vals"][s][key_pos, h_kv].float().to(out.device)
+    got = out[q_token].float().view(nh, dh)[h_kv * (nh // nkv)]
+    assert (got - v).abs().max() < 0.1 * v.abs().max() + 0.05, f"{what}: the planted key {key_pos} of sequence {s} did not carry the answer"
+
+
+def test_the_two_reference_attentions_agree():
+    c = make_attention_case([37, 20, 1, 2], [37, 75, 33, 130], 6, 2, 48, 16, torch.float32, seed=8)
+    for window in (None, 24):
+        _, a = run_attention_case(c, window)
+        _, b = run_attention_case(c, window, dense_reference=True)
+        assert (a - b).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("heads", [(12, 2, 128), (28, 4, 128)])
+@pytest.mark.parametrize("many", [False, True], ids=["split_context", "whole_context"])
+def test_attention_decode_at_benchmark_lengths(heads, many):
+    """Contexts of 2,049 to 4,096 keys, where the benchmark decodes: nine to sixteen splits of 256 keys merged by the CTA
+    that finishes last (few sequences), or a CTA walking a whole context (from 120 sequence x kv-head pairs on).  One
+    planted key in a split from the ninth on and one in the last, ragged split carry the answer of their sequences."""
+    nh, nkv, dh = heads
+    ctx_lens = [2049, 2304, 4095, 4096, 2074, 3000]
+    if many:
+        g = torch.Generator().manual_seed(6)
+        ctx_lens += torch.randint(1, 2600, (128 // nkv - 2,), generator=g).tolist()
+    S = len(ctx_lens)
+    assert (S * nkv >= 120) == many
+    c = make_attention_case([1] * S, ctx_lens, nh, nkv, dh, 16, torch.bfloat16, seed=61)
+    plants = [(0, 0, 2048), (1, nkv - 1, 2100), (2, 0, 4090), (3, nkv - 1, 2305), (5, 0, 2999)]
+    for s, h, key in plants:
+        _plant(c, s, h, key, s)
+    for window in (None, 1000):
+        out, ref = run_attention_case(c, window, implementation="decode", dense_reference=True)
+        close(out, ref, torch.bfloat16, f"decode at long contexts heads={heads} many={many} window={window}")
+        for s, h, key in plants:
+            if window is None or ctx_lens[s] - 1 - key < window:
+                _planted_value_comes_out(c, out, s, h, key, s, f"heads={heads} many={many} window={window}")
+    out32, ref32 = run_attention_case(make_attention_case([1] * 6, ctx_lens[:6], nh, nkv, dh, 16, torch.float32, seed=62), None, dense_reference=True)
+    close(out32, ref32, torch.float32, f"general kernel at long contexts heads={heads}", f32_tol=2e-5)
+
+
+@pytest.mark.parametrize("heads", [(12, 2, 128), (28, 4, 128)])
+def test_attention_tcgen05_at_benchmark_lengths(heads):
+    """A whole prompt of 2,048 tokens (sixteen token tiles against up to sixteen key tiles) and a portion of 512 tokens
+    behind 1,536 cached keys, with a planted key in the tenth key tile and beyond."""
+    nh, nkv, dh = heads
+    for q_lens, ctx_lens, plants in (([2048], [2048], [(0, 0, 1300, 1500), (0, nkv - 1, 1999, 2047)]),
+                                     ([512, 3], [2048, 700], [(0, 0, 1200, 0), (0, nkv - 1, 1700, 400), (1, 0, 690, 514)])):
+        c = make_attention_case(q_lens, ctx_lens, nh, nkv, dh, 16, torch.bfloat16, seed=71)
+        for s, h, key, tok in plants:
+            _plant(c, s, h, key, tok)
+        for window, impl in ((None, "prefill_tcgen05"), (900, "prefill_tcgen05"), (None, None)):
+            out, ref = run_attention_case(c, window, implementation=impl, dense_reference=True)
+            close(out, ref, torch.bfloat16, f"prefill at 2,048 keys heads={heads} q={q_lens} window={window} {impl}")
+            for s, h, key, tok in plants:
+                pos = c["pos"][tok]
+                if window is None or pos - key < window:
+                    _planted_value_comes_out(c, out, s, h, key, tok, f"heads={heads} q={q_lens} window={window}")
+    assert K().library().li_tcgen05_status() == 0
+
+
 @pytest.mark.parametrize("heads", [(12, 2, 128), (4, 2, 16), (6, 2, 48), (8, 8, 64)])
 def test_attention_decode_large_batch(heads):
     """From 120 (sequence, kv head) pairs on, a CTA takes a whole context instead of a 128-key split."""
@@ -696,6 +759,61 @@ def test_attention_window_edge(dtype):
             got = out[-1].float().view(nh, dh)[0]
             near = (got - v).abs().max() < 0.1 * v.abs().max() + 0.05
             assert bool(near) == visible, f"key {key_pos} should be {'visible' if visible else 'hidden'}"
+
+
+def test_a_bounded_wait_that_runs_out_raises_the_status_and_leaves_the_device_usable():
+    """Every wait in the tcgen05 kernels has a limit; when it runs out the kernel raises a status word in mapped host
+    memory and returns, and the launches after it refuse to run until the word is cleared.  Exercised here without any
+    kernel at fault: one thread waits a millisecond on a barrier that nobody arrives on."""
+    import ctypes
+
+    k = K()
+    lib = k.library()
+    assert lib.li_tcgen05_status() == 0
+    a = rnd(200, 256, dtype=torch.bfloat16, seed=1).to(dev())
+    w = rnd(384, 256, dtype=torch.bfloat16, seed=2, scale=0.05).to(dev())
+    out = torch.empty(200, 384, dtype=torch.bfloat16, device=dev())
+    k.linear_with("tcgen05", a, w, None, out)
+    want = out.clone()
+    rc = lib.li_tcgen05_wait_selftest(ctypes.c_int(1000), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert lib.li_tcgen05_status() == 99
+    with pytest.raises(k.KernelError, match="gave up waiting"):
+        k.linear_with("tcgen05", a, w, None, out)
+    lib.li_tcgen05_clear_status()
+    assert lib.li_tcgen05_status() == 0
+    out.zero_()
+    k.linear_with("tcgen05", a, w, None, out)
+    torch.cuda.synchronize()
+    assert torch.equal(out, want)
+    assert lib.li_tcgen05_wait_selftest(ctypes.c_int(0), ctypes.c_void_p(0)) != 0          # a limit outside the range is refused
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_fill_normal_gives_the_bits_of_the_host_restatement(dtype):
+    """Random weights drawn on the device by the library's kernel equal, bit for bit, those the host draws for a model
+    folder (NumPy in the package, checked against tests/plain_random.py on the CPU): float32 and rounded to bfloat16, odd
+    and even sizes, a size beyond one block, other means and deviations; integer tables too."""
+    import numpy as np
+
+    import plain_random as PR
+    from litinfer_b200.weights.loader import ParamSpec
+    from litinfer_b200.weights.random_init import random_tensor
+
+    for name, shape, init, std in (("a.weight", (7, 9), "normal", 0.02), ("b.weight", (64,), "ones_normal", 0.02), ("c", (1001,), "normal", 0.5),
+                                   ("big", (1025, 513), "normal", 0.02)):
+        p = ParamSpec(name, shape, init=init, std=std)
+        on_device = random_tensor(p, 11, dev(), dtype)
+        on_host = random_tensor(p, 11, "cpu", dtype)
+        assert on_device.dtype == dtype and on_device.is_cuda
+        assert torch.equal(on_device.cpu(), on_host), f"{name}: {(on_device.cpu().float() - on_host.float()).abs().max()}"
+        if dtype == torch.float32 and on_host.numel() < 2000:
+            mean, sd = (1.0, 0.1) if init == "ones_normal" else (0.0, std)
+            want = PR.normal(PR.tensor_key(11, name), on_host.numel(), mean, sd)
+            assert np.array_equal(on_device.cpu().numpy().reshape(-1), want)
+    t = ParamSpec("t", (1000,), role="table", init="randint")
+    assert torch.equal(random_tensor(t, 3, dev()).cpu(), random_tensor(t, 3, "cpu"))
 
 
 # --------------------------------------------------------------------------

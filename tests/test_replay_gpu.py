@@ -86,7 +86,7 @@ def build_trace(vocab: int, max_pos: int, main_len: int = 100, portions=PORTIONS
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "B0"])
 def test_replay_all_cuts(name, dtype, model_dirs, tmp_path):
     cfg = TINY[name]
     vocab = cfg["vocab_size"]
@@ -202,6 +202,46 @@ def test_replay_real_layer_sizes(dtype, real_size_dir, tmp_path):
     for rid, ref in (("a", ref_a), ("b", ref_b)):
         rows = sorted(got[rid])
         check_logits(stack(got[rid]), ref[rows], dtype, f"real layer sizes {dtype} request {rid}")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_real_layer_sizes_four_live_requests(dtype, real_size_dir, tmp_path):
+    """Every cut at the sizes the kernels are built for: whole, the last 32 tokens one by one, portions of changing size
+    (some of 64 tokens and more, where the tensor-memory kernels run), and up to four live requests with portions of some
+    beside decoded tokens of others, in a pool so small that pages are used again."""
+    vocab = REAL_SIZES["vocab_size"]
+    tr, seqs, need = build_trace(vocab, REAL_SIZES["max_position_embeddings"], main_len=200, portions=[70, 2, 33, 5, 64, 17, 3, 6],
+                                 mix_portions=[65, 2, 40, 9, 33, 70, 2, 21], mix_lens=[150, 130, 100, 90, 70])
+    got = run_trace(real_size_dir, dtype, tr, tmp_path / "out", need, vocab)
+    refs = {}
+    for rid, toks in seqs.items():
+        key = tuple(toks)
+        if key not in refs:
+            refs[key] = plain_logits(real_size_dir, toks, dtype)
+        lg = stack(got[rid])
+        assert lg.shape[0] == len(toks), f"{rid}: {lg.shape[0]} rows for {len(toks)} tokens"
+        check_logits(lg, refs[key], dtype, f"real layer sizes {dtype} request {rid}")
+    if dtype == "float32":
+        whole = stack(got["whole"])
+        for rid in ("tail", "cut", "mix0"):
+            assert torch.equal(whole, stack(got[rid])), f"float32: '{rid}' differs from 'whole'"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_at_the_benchmark_length(dtype, real_size_dir, tmp_path):
+    """What the benchmark times, held to the plain model: a prompt of 2,048 tokens in one step, then 32 tokens one by
+    one at contexts of 2,049 to 2,080 keys."""
+    vocab = REAL_SIZES["vocab_size"]
+    toks = random_tokens(2080, vocab, 301)
+    tr = Trace()
+    tr.step([("a", toks[:2048], list(range(2040, 2048)))])
+    for i in range(2048, 2080):
+        tr.step([("a", [toks[i]], True)], end=["a"] if i == 2079 else [])
+    got = run_trace(real_size_dir, dtype, tr, tmp_path / "out", round64(2080), vocab)
+    ref = plain_logits(real_size_dir, toks, dtype)
+    rows = sorted(got["a"])
+    assert rows == list(range(2040, 2080))
+    check_logits(stack(got["a"]), ref[rows], dtype, f"2,048-token prompt and 32 decoded tokens, {dtype}")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -1,10 +1,11 @@
 """The entry point for callers that may not allocate device memory
 (litinfer_b200/csrc/no_alloc.h): li_linear_gemv_static, called through its
-exported C symbol, against the ordinary weight-streaming kernel.
+exported C symbol, against the ordinary weight-streaming kernel and against the
+plain float32 product.
 
 Some hosts of this library cannot let it call cudaMalloc: a server that owns
 the whole device arena, a latency-critical loop where an allocation would
-synchronise the device, code running under stream capture.  The ordinary kernel
+synchronise the device.  The ordinary kernel
 allocates its split-k workspace on first use; this variant keeps partial sums
 and arrival counters in fixed __device__ arrays inside the library instead.
 
@@ -20,6 +21,8 @@ import ctypes
 
 import pytest
 import torch
+
+import kernel_refs as R
 
 pytestmark = pytest.mark.gpu
 
@@ -53,6 +56,8 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(shape):
     for out_dtype, b in ((torch.bfloat16, None), (torch.float32, bias)):
         ref = torch.empty(M, N, dtype=out_dtype, device=dev)
         K.linear_with("gemv", a, w, b, ref)
+        plain = torch.empty(M, N, dtype=torch.float32, device=dev)
+        R.linear(a, w, b, plain)                   # the product in float32 on the same bfloat16 operands
         # two calls in a row: the second finds the scratch as the first left it
         for call in range(2):
             out = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev)
@@ -62,7 +67,9 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(shape):
             scale = float(ref.float().abs().max())
             tol = 2.0 ** -7 * scale if out_dtype == torch.bfloat16 else 1e-5 * (Kd ** 0.5) * max(scale, 1.0)
             err = float((out.float() - ref.float()).abs().max())
-            assert err <= tol, f"call {call}, {shape}, {out_dtype}: max |diff| {err:.3e} > {tol:.3e}"
+            assert err <= tol, f"call {call}, {shape}, {out_dtype}: max |diff| {err:.3e} > {tol:.3e} against the ordinary kernel"
+            err = float((out.float() - plain).abs().max())
+            assert err <= tol, f"call {call}, {shape}, {out_dtype}: max |diff| {err:.3e} > {tol:.3e} against the plain product"
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
