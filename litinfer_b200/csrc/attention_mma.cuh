@@ -28,7 +28,10 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], unsigned a0, unsigned a1
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint2 ld8(const bf16* p) { return *reinterpret_cast<const uint2*>(p); }
+// Queries are read past L1 (from L2): inside a persistent kernel they were written a moment ago by another
+// multiprocessor, and L1 is not kept coherent with that.
+__device__ __forceinline__ uint2 ld8(const bf16* p) { return __ldcg(reinterpret_cast<const uint2*>(p)); }
+__device__ __forceinline__ uint4 ld16(const bf16* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 
 __device__ __forceinline__ uint2 ld8_stream(const bf16* p) {
     uint2 v;
@@ -172,8 +175,8 @@ __device__ __forceinline__ void load_q32(unsigned (&qa)[DH / 16][4], const bf16*
     constexpr int F = DH / 32, R = (DH % 32) / 16;
 #pragma unroll
     for (int f = 0; f < F; ++f) {
-        const uint4 a = row_lo ? *reinterpret_cast<const uint4*>(row_lo + f * 32 + t * 8) : make_uint4(0, 0, 0, 0);
-        const uint4 b = row_hi ? *reinterpret_cast<const uint4*>(row_hi + f * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+        const uint4 a = row_lo ? ld16(row_lo + f * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+        const uint4 b = row_hi ? ld16(row_hi + f * 32 + t * 8) : make_uint4(0, 0, 0, 0);
         qa[2 * f][0] = a.x; qa[2 * f][1] = b.x; qa[2 * f][2] = a.y; qa[2 * f][3] = b.y;
         qa[2 * f + 1][0] = a.z; qa[2 * f + 1][1] = b.z; qa[2 * f + 1][2] = a.w; qa[2 * f + 1][3] = b.w;
     }

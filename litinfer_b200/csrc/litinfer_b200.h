@@ -36,6 +36,13 @@ int li_paged_attention_with(int which, const void* qkv, void* out, const void* k
     int* positions, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window, int
     max_q_len, int max_ctx_len, const int* old_lens, int singles, cudaStream_t stream);
 
+/* ---- decode_step.cu: a decode step as one persistent kernel (decode_step.h has the structures) ---- */
+struct LiDecodeStep;
+int li_decode_step_accepts(int M, int hidden, int heads, int kv_heads, int head_dim, int intermediate, int vocab, int page_size);
+int li_decode_step_plan(int M, int hidden, int heads, int kv_heads, int head_dim, int splits, int* stage_k, int* stages, int* x_cols, int*
+    scratch_bytes);
+int li_decode_step(const LiDecodeStep* step, cudaStream_t stream);
+
 /* ---- elementwise.cu ---- */
 /* out[t] = table[ids[t]] as float. */
 int li_embedding(const void* table, int dtype, const int* ids, float* out, int T, int H, int V, cudaStream_t stream);
@@ -150,6 +157,9 @@ int li_tcgen05_status();
 /* Tests: clear the status word; make a bounded wait run out on purpose (one thread, a barrier nobody arrives on,
  * a limit in microseconds): the status then reads 99. */
 void li_tcgen05_clear_status();
+
+/* Progress marks of kernels launched with their debug flag (host memory, readable while they run). */
+int li_tcgen05_progress(int* out, int n);
 int li_tcgen05_wait_selftest(int limit_us, cudaStream_t stream);
 
 #ifdef __cplusplus

@@ -19,9 +19,9 @@ int setup(EncodeTiledFn* encode, int** error_host, int** error_dev) {
         g_encode = reinterpret_cast<EncodeTiledFn>(fn);
     }
     if (!g_error_host) {
-        cudaError_t e = cudaHostAlloc((void**)&g_error_host, sizeof(int), cudaHostAllocMapped);
+        cudaError_t e = cudaHostAlloc((void**)&g_error_host, 1024 * sizeof(int), cudaHostAllocMapped);      // [0]: the status word; the rest: progress marks of kernels that are asked to leave them
         if (e != cudaSuccess) return li_fail("tcgen05: cannot allocate the status word: %s", cudaGetErrorString(e));
-        *g_error_host = 0;
+        for (int i = 0; i < 1024; ++i) g_error_host[i] = 0;
         e = cudaHostGetDevicePointer((void**)&g_error_dev, g_error_host, 0);
         if (e != cudaSuccess) return li_fail("tcgen05: cannot map the status word: %s", cudaGetErrorString(e));
     }
@@ -103,4 +103,14 @@ LI_EXPORT int li_tcgen05_wait_selftest(int limit_us, cudaStream_t stream) {
     if (int rc = tc::setup(&f, &h, &d)) return rc;
     wait_runs_out_kernel<<<1, 32, 0, stream>>>((unsigned long long)limit_us * 1000ull, d, 99);
     return li_check_launch("tcgen05 wait self-test");
+}
+
+// Progress marks (words 1..1023 of the mapped status area), for kernels launched with their debug flag: what each CTA
+// reached last.  Readable while a kernel is still running.
+LI_EXPORT int li_tcgen05_progress(int* out, int n) {
+    tc::EncodeTiledFn f;
+    int *h = nullptr, *d = nullptr;
+    if (tc::setup(&f, &h, &d)) return -1;
+    for (int i = 0; i < n && i < 1023; ++i) out[i] = h[1 + i];
+    return 0;
 }

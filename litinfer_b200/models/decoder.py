@@ -56,6 +56,7 @@ class DecoderModel:
         self.embedding: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
         self.head_is_tied = False
+        self._fused = None                                     # models/fused_decode.py, made at the first step
 
     # ------------------------------------------------------------------
     def params(self) -> List[ParamSpec]:
@@ -114,6 +115,15 @@ class DecoderModel:
     def forward(self, ctx, caches) -> torch.Tensor:
         """Run the step's tokens; float32 logits ``[len(ctx.logit_rows), vocab]``."""
         s = self.spec
+        if self.device.type == "cuda" and self.dtype == torch.bfloat16:
+            # steps of single tokens of few sequences: one persistent kernel, if every part is one it is built for
+            if self._fused is None:
+                from .fused_decode import FusedDecode
+
+                self._fused = FusedDecode(self)
+            logits = self._fused.run(ctx, caches)
+            if logits is not None:
+                return logits
         x32 = torch.empty((ctx.num_tokens, s.hidden_size), dtype=torch.float32, device=self.device)
         K.embedding(self.embedding, ctx.token_ids, x32)
         if s.embedding_scale is not None:

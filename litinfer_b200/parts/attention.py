@@ -62,6 +62,14 @@ class PagedAttention(Mixer):
     def cache_requirement(self):
         return PagedKV(self.num_kv_heads, self.head_dim, self.window)
 
+    def fused_decode(self):
+        rope = self.position.fused_decode() if self.position is not None else None
+        if type(self) is not PagedAttention or rope is None or rope["rotary_dim"] != self.head_dim or self.out.bias is not None:
+            return None
+        return {"w_qkv": self.qkv.weight, "b_qkv": self.qkv.bias, "w_o": self.out.weight, "hidden": self.hidden, "heads": self.num_heads,
+                "kv_heads": self.num_kv_heads, "head_dim": self.head_dim, "scale": self.scale, "window": self.window,
+                "rope_denominators": rope["denominators"]}
+
     def forward(self, h, ctx, cache):
         return self.out(self._attend(h, ctx, cache))
 

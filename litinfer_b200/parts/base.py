@@ -92,6 +92,12 @@ class Part:
         """Sub-parts, so that params() and bind() reach them."""
         return []
 
+    def fused_decode(self) -> Optional[dict]:
+        """What the fused decode step (``models/fused_decode.py``) needs of this part, tensors and constants under the
+        names that file reads, or None: the part is not one the fused kernel is built for, and a model that holds it
+        runs part by part.  The default is None, so that parts registered from outside are never fused by accident."""
+        return None
+
     # helpers -----------------------------------------------------------
     def all_params(self) -> List[ParamSpec]:
         out = list(self.params())

@@ -35,6 +35,15 @@ class PreNormBlock(Block):
     def entry(self):
         return Tail(None, self.mixer_norm, self.mixer.takes_deferred)
 
+    def fused_decode(self):
+        if type(self) is not PreNormBlock or self.feed_forward is None:
+            return None
+        mixer, ff = self.mixer.fused_decode(), self.feed_forward.fused_decode()
+        n1, n2 = self.mixer_norm.fused_decode(), self.feed_forward_norm.fused_decode()
+        if None in (mixer, ff, n1, n2) or mixer["hidden"] != ff["hidden"] or n1["size"] != mixer["hidden"] or n2["size"] != mixer["hidden"]:
+            return None
+        return dict(mixer, **ff, norm_first=n1, norm_ffn=n2)
+
     def forward(self, x32, ctx, cache, carry, next_entry=None):
         if carry is None:
             h = self.mixer_norm.forward(x32)

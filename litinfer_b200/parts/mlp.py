@@ -35,6 +35,11 @@ class SwiGLU(FeedForward):
         self.gate_up.bind(tensors)
         self.down.bind(tensors)
 
+    def fused_decode(self):
+        if type(self) is not SwiGLU or not self.gate_up.fused_activation or self.down.bias is not None:
+            return None
+        return {"w_gate_up": self.gate_up.weight, "w_down": self.down.weight, "hidden": self.hidden, "intermediate": self.intermediate}
+
     def forward(self, h, ctx):
         return self.down(self.gate_up.activation(h))
 

@@ -35,6 +35,9 @@ class RMSNorm(Norm):
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors.pop(self.prefix + "weight")
 
+    def fused_decode(self):
+        return {"weight": self.weight, "eps": self.eps, "size": self.size} if type(self) is RMSNorm and self.weight is not None else None
+
     def forward(self, x32):
         out = torch.empty(x32.shape, dtype=self.dtype, device=x32.device)
         K.rmsnorm(x32, self.weight, self.eps, out)

@@ -34,6 +34,9 @@ class RotaryEmbedding(Position):
     # rotate in their epilogue read it); shorter steps compute the angles where they rotate.
     TABLE_FROM_TOKENS = 65
 
+    def fused_decode(self):
+        return {"denominators": self.denominators, "rotary_dim": self.rotary_dim} if type(self) is RotaryEmbedding else None
+
     def rotary(self, ctx) -> Rotary:
         return Rotary(self.denominators, self.rotary_dim, self.table(ctx))
 

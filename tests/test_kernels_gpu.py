@@ -460,8 +460,8 @@ def run_attention_case(c, window, implementation=None, old_lens=None, singles=0,
     for s in range(c["S"]):
         t = torch.arange(c["ctx_lens"][s])
         pages, offs = c["bt"][s].long()[t // page], t % page
-        kc[pages, :, offs] = c["keys"][s]
-        vc[pages, :, :, offs] = c["vals"][s]
+        kc[pages, :, offs] = c["keys"][s][:len(t)]
+        vc[pages, :, :, offs] = c["vals"][s][:len(t)]
     args = dict(
         qkv=c["qkv"].to(d), k_cache=kc.to(d), v_cache=vc.to(d), block_table=c["bt"].to(d),
         q_start=torch.tensor(c["q_start"], dtype=torch.int32, device=d), ctx_lens=torch.tensor(c["ctx_lens"], dtype=torch.int32, device=d),
