@@ -24,6 +24,20 @@ Weights (3 GB) are larger than L2, so nothing stays cached between steps.
 ``--only decode|prefill|mixed|kernels-decode|kernels-prefill`` measures one part and prints a short line (for
 profiling runs and the summaries under ``profiles/``); ``mixed`` is a step of ``--batch`` requests decoding at
 ``--context`` beside a portion of ``--prefill-tokens`` prompt tokens.
+
+``--shape 1.5b|7b|14b`` chooses the layer sizes (default 1.5b, the headline; the other two are the larger workloads of
+the benchmark description and run behind the flag only):
+
+* ``--shape 7b --only serve``: continuous batching through ``Engine`` of 64 requests with prompts of 128 to 2,048
+  tokens and 128 to 512 new tokens each under a real page budget: total tokens per second, mean and 95th-percentile
+  step time, preemptions, steps by launch path.  LitInfer's own harness likewise times whole generations with the
+  warm-up excluded (scripts/benchmark_cpu.py:202-253).
+* ``--shape 14b --only chunked``: a 2,048-token prompt fed in portions of 512 tokens beside 32 requests decoding at a
+  context of 4,096: milliseconds per step and the fractions of the roofline of its bytes and of its flops.
+
+The default line also carries ``fp32_check``: the largest difference between the engine's float32 logits and the plain
+implementation of the tests (tests/plain_qwen2.py) on two layers of the benchmark's sizes with the same random weights,
+which the device draws with the library's kernel and the host restates bit for bit.
 """
 
 from __future__ import annotations
@@ -58,13 +72,26 @@ def load_peaks():
     return dict(FALLBACK_PEAKS)
 
 
-def bench_config():
-    """configs[2] of BASELINE.json: the 1.5B shape."""
-    return dict(
-        architectures=["Qwen2ForCausalLM"], torch_dtype="bfloat16", num_hidden_layers=28, hidden_size=1536,
-        num_attention_heads=12, num_key_value_heads=2, head_dim=128, intermediate_size=8960, vocab_size=151936,
-        rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=4096,
-        eos_token_id=None, use_sliding_window=False)
+SHAPES = {
+    # configs[2] of the benchmark description: the 1.5B shape (LitInfer's own benchmark model)
+    "1.5b": dict(name="DeepSeek-R1-Distill-Qwen-1.5B shape (Qwen2)", num_hidden_layers=28, hidden_size=1536, num_attention_heads=12,
+                 num_key_value_heads=2, head_dim=128, intermediate_size=8960, vocab_size=151936, rope_theta=10000.0, rms_norm_eps=1e-6,
+                 max_position_embeddings=4096),
+    # configs[3]: the Qwen2-7B shape
+    "7b": dict(name="Qwen2-7B shape", num_hidden_layers=28, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+               intermediate_size=18944, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-6, max_position_embeddings=4096),
+    # configs[4]: the Qwen2.5-14B shape
+    "14b": dict(name="Qwen2.5-14B shape", num_hidden_layers=48, hidden_size=5120, num_attention_heads=40, num_key_value_heads=8, head_dim=128,
+                intermediate_size=13824, vocab_size=152064, rope_theta=1e6, rms_norm_eps=1e-5, max_position_embeddings=8192),
+}
+
+
+def bench_config(shape: str = "1.5b"):
+    """The configuration of a shape of the benchmark description (default: configs[2], the 1.5B shape)."""
+    d = dict(SHAPES[shape])
+    d.pop("name")
+    return dict(architectures=["Qwen2ForCausalLM"], torch_dtype="bfloat16", tie_word_embeddings=False, eos_token_id=None,
+                use_sliding_window=False, **d)
 
 
 class ClockSampler:
@@ -373,6 +400,143 @@ def time_mixed(model, batch, context, portion, repeats=4):
     return statistics.median(times)
 
 
+def time_serve(model, cfg, requests=64, seed=11, max_tokens_per_step=4096, page_budget_tokens=None):
+    """Continuous batching of ``requests`` requests with prompts of 128 to 2,048 tokens and 128 to 512 new tokens each
+    through the engine (scheduler, step function, sampler), host tokens in and out.  The pool holds
+    ``page_budget_tokens`` tokens (default: three quarters of what all requests would need at their longest, so that
+    admission and preemption have to work).  A warm-up pass with the same requests comes first and is not timed."""
+    import torch
+
+    from litinfer_b200.engine import Engine, EngineConfig
+
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(128, 2049, (requests,), generator=g).tolist()
+    news = torch.randint(128, 513, (requests,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    need = sum(-(-(n + m) // 16) for n, m in zip(lens, news)) * 16
+    budget = int(page_budget_tokens or need * 3 // 4)
+    eng = Engine(model, EngineConfig(num_pages=budget // 16, max_num_seqs=requests, max_tokens_per_step=max_tokens_per_step,
+                                     prefill_chunk=2048, run_ahead=True))
+    out = {}
+    for timed in (False, True):
+        ids = [eng.add_request(p, m) for p, m in zip(prompts, news)]
+        steps, pre0, replay0 = [], eng.scheduler.num_preemptions, eng.runner.graph_replays
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        while eng.has_unfinished():
+            t = time.perf_counter()
+            eng.step()
+            steps.append(time.perf_counter() - t)
+        eng.drain()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        produced = sum(len(eng.get_output(i)) for i in ids)
+        for i in ids:
+            eng.scheduler.forget(i)
+        steps.sort()
+        out = dict(seconds=dt, generated=produced, prompt_tokens=sum(lens), tok_s=produced / dt, total_tok_s=(produced + sum(lens)) / dt,
+                   steps=len(steps), mean_step_ms=1e3 * sum(steps) / len(steps), p95_step_ms=1e3 * steps[int(0.95 * (len(steps) - 1))],
+                   preemptions=eng.scheduler.num_preemptions - pre0, steps_from_graphs=eng.runner.graph_replays - replay0,
+                   steps_launched_plainly=len(steps) - (eng.runner.graph_replays - replay0), pool_tokens=budget, needed_tokens=need)
+    return out
+
+
+def time_chunked(model, cfg, decoding=32, context=4096, prompt=2048, portion=512, peaks=None):
+    """A prompt of ``prompt`` tokens fed in portions of ``portion`` beside ``decoding`` requests that decode at a context of
+    ``context``: device milliseconds of each of the prompt's steps (median over three prompts, after one for warm-up and
+    graph capture), and what fraction of the roofline of its bytes (weights once, the caches read) and of its flops that is."""
+    import torch
+
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.engine import ModelRunner, StepItem
+
+    spec = model.spec
+    pages = (decoding * (context + 64) + 2 * prompt + 4096) // 16
+    manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], pages, 16, decoding + 2, model.dtype, model.device)
+    for grp in manager.groups:
+        grp.kv.normal_(0.0, 0.5)
+    runner = ModelRunner(model, manager, use_graphs=True, max_context=min(spec.max_position_embeddings, context + 64))
+    g = torch.Generator().manual_seed(4)
+    live = []
+    for i in range(decoding):
+        rc = manager.admit(i)
+        manager.extend(rc, context)
+        manager.commit(rc, context)                         # the cache holds random values: a decode step's time does not depend on them
+        live.append(rc)
+    next_id = decoding
+    per_step = [[] for _ in range(prompt // portion)]
+    for rep in range(4):
+        incoming = manager.admit(next_id)
+        next_id += 1
+        toks = torch.randint(0, spec.vocab_size, (prompt,), generator=g).tolist()
+        for k in range(prompt // portion):
+            items = []
+            for rc in live:
+                if rc.length + 1 > context + 48:              # keep the decoding requests near the context asked for
+                    manager.commit(rc, context)
+                manager.extend(rc, rc.length + 1)
+                items.append(StepItem(rc, [5], (0,)))
+            manager.extend(incoming, incoming.length + portion)
+            items.append(StepItem(incoming, toks[k * portion:(k + 1) * portion], (portion - 1,)))
+            torch.cuda.synchronize()
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            runner.step(items)
+            stop.record()
+            torch.cuda.synchronize()
+            if rep >= 1:
+                per_step[k].append(start.elapsed_time(stop))
+        manager.release(incoming)
+    ms = [statistics.median(x) for x in per_step]
+    H, I, L = cfg["hidden_size"], cfg["intermediate_size"], cfg["num_hidden_layers"]
+    nh, nkv, dh = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    wbytes = weight_bytes(model)
+    kv_token = 2 * L * nkv * dh * 2
+    out = []
+    for k, m in enumerate(ms):
+        cached = k * portion
+        tokens = decoding + portion
+        flops = 2 * (H * (nh + 2 * nkv) * dh + nh * dh * H + 3 * H * I) * L * tokens + 2 * H * cfg["vocab_size"] * (decoding + 1)
+        flops += 2 * 2 * nh * dh * L * (decoding * context + portion * cached + portion * (portion + 1) // 2)
+        nbytes = wbytes + kv_token * (decoding * context + cached + portion)
+        out.append(dict(step=k, cached_prompt_tokens=cached, ms=round(m, 3), hbm_frac=round(nbytes / (m / 1e3) / (peaks["hbm_gbs"] * 1e9), 4),
+                        flops_frac=round(flops / (m / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)))
+    return out
+
+
+def fp32_check(cfg, layers=2, tokens=48, seed=3):
+    """The largest |difference| between the engine's float32 logits and the plain implementation of the tests on ``layers``
+    layers of the benchmark's sizes: the same random weights on both sides (drawn on the device by the library's kernel,
+    restated on the host bit for bit), a prompt of ``tokens`` tokens whole."""
+    import torch
+
+    sys.path.insert(0, str(ROOT / "tests"))
+    import plain_qwen2 as P
+
+    from litinfer_b200.cache import CacheManager
+    from litinfer_b200.config import config_from_dict
+    from litinfer_b200.engine import ModelRunner, StepItem
+    from litinfer_b200.models import DecoderModel
+    from litinfer_b200.models.decoder import declared_params
+    from litinfer_b200.weights.random_init import random_tensor
+
+    small = dict(cfg, num_hidden_layers=layers, torch_dtype="float32")
+    spec = config_from_dict(small).to_model_spec()
+    model = DecoderModel.from_random(spec, seed, "float32", "cuda:0")
+    manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], -(-tokens // 16) + 1, 16, 1, model.dtype, model.device)
+    runner = ModelRunner(model, manager)
+    g = torch.Generator().manual_seed(seed)
+    toks = torch.randint(0, small["vocab_size"], (tokens,), generator=g).tolist()
+    rc = manager.admit(0)
+    manager.extend(rc, tokens)
+    got = runner.step([StepItem(rc, toks, list(range(tokens)))]).cpu()
+    del model, runner, manager
+    torch.cuda.empty_cache()
+    weights = {p.name: random_tensor(p, seed, "cpu", torch.float32) for p in declared_params(spec) if p.draw}
+    ref = P.plain_forward(dict(small), weights, toks)
+    return dict(layers=layers, tokens=tokens, max_abs_err=float((got - ref).abs().max()), max_abs_logit=float(ref.abs().max()))
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -383,7 +547,8 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "mixed", "kernels-decode", "kernels-prefill"],
+    ap.add_argument("--shape", default="1.5b", choices=sorted(SHAPES), help="layer sizes: the headline 1.5B shape, or the 7B / 14B shapes of the larger workloads")
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "mixed", "kernels-decode", "kernels-prefill", "serve", "chunked", "fp32"],
                     help="measure one part and print a short line (for profiling runs); kernels-*: a table of the "
                          "kernels' device times from torch.profiler; mixed: --batch requests decoding at --context beside "
                          "a portion of --prefill-tokens prompt tokens")
@@ -407,8 +572,11 @@ def main() -> int:
     from litinfer_b200.config import config_from_dict
     from litinfer_b200.models import DecoderModel
 
-    cfg = bench_config()
+    cfg = bench_config(args.shape)
     full_layers = cfg["num_hidden_layers"]
+    if args.only == "fp32":
+        print(json.dumps({"only": "fp32", "shape": args.shape, **fp32_check(cfg)}))
+        return 0
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
     peaks = load_peaks()
@@ -436,6 +604,16 @@ def main() -> int:
         r = time_decode(model, args.batch, args.context, args.steps, warmup, graphs=not args.no_graphs)
         print(json.dumps({"only": "decode", "batch": args.batch, "context": args.context, "layers_run": cfg["num_hidden_layers"],
                           "graphs": not args.no_graphs, **{k: round(v, 4) for k, v in r.items()}}))
+        return 0
+    if args.only == "serve":
+        r = time_serve(model, cfg)
+        print(json.dumps({"only": "serve", "shape": args.shape, "model": SHAPES[args.shape]["name"], "layers_run": cfg["num_hidden_layers"],
+                          "requests": 64, **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()}}))
+        return 0
+    if args.only == "chunked":
+        r = time_chunked(model, cfg, peaks=peaks)
+        print(json.dumps({"only": "chunked", "shape": args.shape, "model": SHAPES[args.shape]["name"], "layers_run": cfg["num_hidden_layers"],
+                          "decoding": 32, "context": 4096, "prompt": 2048, "portion": 512, "peaks": peaks["source"], "steps": r}))
         return 0
     if args.only == "mixed":
         ms = time_mixed(model, args.batch, args.context, args.prefill_tokens)
@@ -466,9 +644,12 @@ def main() -> int:
             points[f"decode_b{b}"] = round(time_decode(model, b, args.context, min(args.steps, 64), warmup)["tok_s"], 1)
         points["first_token_ms_prompt16"] = round(time_first_token(model, cfg), 3)
     e2e = time_e2e(model, cfg, args.batch, args.context, 256, args.steps)
+    del model
+    torch.cuda.empty_cache()
+    check = fp32_check(cfg)
 
     line = {
-        "metric": "decode tok/s @ batch 8 (1.5B shape, context 2048+)",
+        "metric": f"decode tok/s @ batch {args.batch} ({args.shape.upper()} shape, context {args.context}+)",
         "value": round(main_run["tok_s"], 1),
         "unit": "tokens/s",
         "n_gpus": 1,
@@ -482,11 +663,11 @@ def main() -> int:
         "data": "synthetic: random-init weights N(0, 0.02), random token ids",
         "impl": "ours",
         "config": {
-            "model": "DeepSeek-R1-Distill-Qwen-1.5B shape (Qwen2)", "layers": full_layers, "layers_run": cfg["num_hidden_layers"],
+            "model": SHAPES[args.shape]["name"], "layers": full_layers, "layers_run": cfg["num_hidden_layers"],
             "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
             "global_batch": args.batch, "seq_len": args.context, "new_tokens": args.steps + warmup, "context_cap": 4096,
-            "page_size": 16, "parallelism": "single GPU", "cache_refresh": "inputs larger than L2 (3 GB of weights per step)",
+            "page_size": 16, "parallelism": "single GPU", "cache_refresh": f"inputs larger than L2 ({wbytes / 1e9:.1f} GB of weights per step)",
             "peaks": peaks["source"],
         },
         "e2e": {"value": round(e2e["value"], 1), "unit": "tokens/s", "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
@@ -498,6 +679,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / peaks["hbm_gbs"], 4)},
         "points": points,
+        "fp32_check": {k: (round(v, 7) if isinstance(v, float) else v) for k, v in check.items()},
         "kernel_library": kernels.library_file(),
     }
     print(json.dumps(line))
