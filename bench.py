@@ -537,6 +537,76 @@ def fp32_check(cfg, layers=2, tokens=48, seed=3):
     return dict(layers=layers, tokens=tokens, max_abs_err=float((got - ref).abs().max()), max_abs_logit=float(ref.abs().max()))
 
 
+def run_reference(args):
+    """The reference arm: the unmodified LitInfer (built with g++ by baseline/build_reference.py, since its own build
+    needs xmake) through its stock ``Qwen2(...).engine_*`` path on the CPU, which is the only device it runs on, for
+    the same metric and configuration.  A one-layer run comes first; if the full run would not fit the time this arm
+    may take (LITINFER_REF_BUDGET_S, default 900 s) the line says `unavailable` with the measured extrapolation."""
+    import shutil
+    import tempfile
+
+    sys.path.insert(0, str(ROOT / "baseline"))
+    try:
+        import build_reference
+
+        build_reference.build(verbose=True)
+    except Exception as e:                                   # no sources, no compiler, a compile error
+        return {"impl": "reference", "unavailable": f"LitInfer's native library could not be built here: {str(e)[:300]}"}
+    from litinfer_b200.weights import write_model_folder      # writes files only: no model, kernel or engine of this repository
+
+    budget = float(os.environ.get("LITINFER_REF_BUDGET_S", "900"))
+    cfg = bench_config(args.shape)
+    cfg["eos_token_id"] = -1                                  # LitInfer wants an integer; no token has this id
+    warmup = max(args.warmup, 3)
+    cores = os.cpu_count() or 1
+
+    def run(layers, batch, context, steps, warm):
+        d = tempfile.mkdtemp(prefix="litinfer_ref_")
+        try:
+            write_model_folder(d, dict(cfg, num_hidden_layers=layers), seed=0, store_dtype="bfloat16")
+            pages = batch * (-(-(context + steps + warm + 4) // 16)) + 8
+            env = dict(os.environ, LLAISYS_NUM_BLOCKS=str(pages))          # LitInfer's own knob for the size of its page pool
+            r = subprocess.run([sys.executable, str(ROOT / "baseline" / "run_reference.py"), "--model", d, "--batch", str(batch), "--context",
+                                str(context), "--steps", str(steps), "--warmup", str(warm), "--vocab", str(cfg["vocab_size"])],
+                               capture_output=True, text=True, env=env, timeout=max(budget * 2, 600))
+            if r.returncode != 0:
+                raise RuntimeError((r.stderr or r.stdout)[-400:])
+            return json.loads(r.stdout.strip().splitlines()[-1])
+        finally:
+            shutil.rmtree(d, ignore_errors=True)
+
+    try:
+        cal = run(1, args.batch, 256, 3, 1)
+    except Exception as e:
+        return {"impl": "reference", "unavailable": f"LitInfer's CPU engine failed on a one-layer model of this configuration: {str(e)[:300]}"}
+    L = cfg["num_hidden_layers"]
+    est_prefill = cal["prefill_s"] * (args.batch * args.context / cal["prefill_tokens"]) * L
+    est_decode = cal["ms_per_step"] / 1e3 * L * (args.steps + warmup)
+    est = cal["load_s"] * L / 2 + est_prefill + est_decode
+    calibration = {"layers": 1, "cpu_cores": cores, "prefill_tok_s": round(cal["prefill_tokens"] / cal["prefill_s"], 1),
+                   "decode_ms_per_step": round(cal["ms_per_step"], 2), "estimated_full_run_s": round(est, 0)}
+    if est > budget:
+        return {"impl": "reference", "calibration": calibration, "unavailable":
+                f"LitInfer has no GPU path; its CPU engine, measured here on one layer of this configuration ({cores} cores: "
+                f"{calibration['prefill_tok_s']} prompt tokens/s, {calibration['decode_ms_per_step']} ms a decode step at batch {args.batch}), would need "
+                f"about {est:.0f} s for the {L}-layer run (prefill of {args.batch} x {args.context} tokens, then {args.steps + warmup} steps): "
+                f"beyond the {budget:.0f} s this arm may take"}
+    try:
+        full = run(L, args.batch, args.context, args.steps, warmup)
+    except Exception as e:
+        return {"impl": "reference", "calibration": calibration, "unavailable": f"LitInfer's CPU engine failed on the full configuration: {str(e)[:300]}"}
+    return {
+        "metric": f"decode tok/s @ batch {args.batch} ({args.shape.upper()} shape, context {args.context}+)", "value": round(full["tok_s"], 2),
+        "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(full["ms_per_step"], 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (LitInfer runs bfloat16 files as float16)",
+        "data": "synthetic: random-init weights N(0, 0.02), random token ids", "impl": "reference", "device": f"cpu ({cores} cores)",
+        "config": {"model": SHAPES[args.shape]["name"], "layers": L, "global_batch": args.batch, "seq_len": args.context,
+                   "new_tokens": args.steps + warmup, "page_size": 16, "parallelism": "CPU, OpenMP"},
+        "prefill": {"value": round(full["prefill_tokens"] / full["prefill_s"], 1), "tokens": full["prefill_tokens"], "ms": round(full["prefill_s"] * 1e3, 1)},
+        "calibration": calibration,
+    }
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -557,9 +627,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "LitInfer installs offline only as its Python layer (its native library needs xmake, which is absent) "
-                          "and it has no GPU path; its CPU engine cannot run this configuration in bounded time"}))
+        print(json.dumps(run_reference(args)))
         return 0
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")

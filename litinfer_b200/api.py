@@ -41,7 +41,7 @@ class CausalLM:
 
     def __init__(self, model_path, device="cuda:0", quantize=None, dtype: Optional[str] = None,
                  num_pages: Optional[int] = None, max_num_seqs: int = 64, max_tokens_per_step: int = 2048,
-                 prefill_chunk: int = 2048, use_graphs: bool = True, run_ahead: bool = False,
+                 prefill_chunk: int = 2048, use_graphs: bool = True, run_ahead: bool = True,
                  model: Optional[DecoderModel] = None) -> None:
         if quantize is not None:
             raise ValueError("quantized weights are not supported by this engine")
@@ -85,7 +85,7 @@ class CausalLM:
         pages = self._default_pages(opts["max_num_seqs"])
         cfg = EngineConfig(num_pages=pages, page_size=16, max_num_seqs=opts["max_num_seqs"],
                            max_tokens_per_step=opts["max_tokens_per_step"], prefill_chunk=opts["prefill_chunk"],
-                           use_graphs=opts["use_graphs"], run_ahead=bool(opts.get("run_ahead", False)))
+                           use_graphs=opts["use_graphs"], run_ahead=bool(opts.get("run_ahead", True)))
         return Engine(self.model, cfg)
 
     # ------------------------------------------------------------------
@@ -135,6 +135,12 @@ class CausalLM:
         if self._single is None:
             self._single = self._make_engine(max_num_seqs=1)
         eng = self._single
+        from . import kernels as K
+
+        if K.TRACE:                                  # LitInfer prints the same kind of line (python/llaisys/models/qwen2.py:351-357)
+            import sys
+
+            print(f"[LLAISYS] Calling generate ntokens={len(prompt)} max_new_tokens={max_new_tokens}", file=sys.stderr, flush=True)
         rid = eng.add_request(prompt, max_new_tokens, SamplingParams(temperature, top_k, top_p, seed))
         sent = 0
         try:

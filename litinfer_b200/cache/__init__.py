@@ -1,4 +1,4 @@
 from .manager import CacheManager, EntryCache, Group, RequestCache
-from .pool import OutOfPages, PagePool, PoolError
+from .pool import OutOfPages, PoolError
 
-__all__ = ["CacheManager", "EntryCache", "Group", "OutOfPages", "PagePool", "PoolError", "RequestCache"]
+__all__ = ["CacheManager", "EntryCache", "Group", "OutOfPages", "PoolError", "RequestCache"]

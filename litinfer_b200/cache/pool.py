@@ -1,5 +1,6 @@
-"""Host-side bookkeeping of one pool of pages (or slots): a LIFO free list with
-ownership checks, kept by the host runtime (``csrc/host/runtime.cpp``).
+"""Host-side bookkeeping of the pools of pages (and slots): LIFO free lists with
+ownership checks, kept by the host runtime (``csrc/host/runtime.cpp``); here the view of one of a
+manager's pools.  (The runtime's pool on its own, ``li_pool_*``, is driven by the tests: tests/pool_face.py.)
 
 LitInfer keeps one such list per layer and checks only the range of a freed
 id (src/llaisys/kv_cache/block_kv_cache.hpp:34-59).  Here one list serves a
@@ -15,49 +16,7 @@ import ctypes
 from . import native
 from .native import OutOfPages, PoolError
 
-__all__ = ["OutOfPages", "PagePool", "PoolError"]
-
-
-class PagePool:
-    FREE = -1
-
-    def __init__(self, num_pages: int, what: str = "page") -> None:
-        if num_pages <= 0:
-            raise ValueError(f"a pool needs at least one {what}")
-        self.num_pages = int(num_pages)
-        self.what = what
-        self._lib = native.library()
-        self._h = self._lib.li_pool_create(self.num_pages, what.encode())
-        if not self._h:
-            raise PoolError(f"cannot create a pool of {num_pages} {what}s")
-
-    def __del__(self) -> None:
-        h, self._h = getattr(self, "_h", None), None
-        if h:
-            self._lib.li_pool_destroy(h)
-
-    @property
-    def num_free(self) -> int:
-        return self._lib.li_pool_num_free(self._h)
-
-    @property
-    def num_used(self) -> int:
-        return self.num_pages - self.num_free
-
-    def owner_of(self, page: int) -> int:
-        return self._lib.li_pool_owner(self._h, int(page))
-
-    def alloc(self, owner: int) -> int:
-        page = ctypes.c_int(0)
-        native.check(self._lib.li_pool_alloc(self._h, int(owner), ctypes.byref(page)))
-        return page.value
-
-    def free(self, page: int, owner: int) -> None:
-        native.check(self._lib.li_pool_free(self._h, int(page), int(owner)))
-
-    def check(self) -> None:
-        """Every page is either free exactly once or owned, never both."""
-        native.check(self._lib.li_pool_check(self._h))
+__all__ = ["OutOfPages", "PoolError", "PoolView"]
 
 
 class PoolView:

@@ -220,6 +220,27 @@ __global__ void logit_cap_kernel(float* __restrict__ x, long long n, float cap) 
 }
 }  // namespace
 
+namespace {
+// out[r, :] = src[rows[r], :] for float rows (the wanted logits out of a captured step's fixed layout)
+__global__ void gather_rows_kernel(const float* __restrict__ src, const int* __restrict__ rows, float* __restrict__ out, int n_src, long long width) {
+    pdl_launch_dependents();
+    pdl_wait();
+    int r = rows[blockIdx.y];
+    r = r < 0 ? 0 : (r >= n_src ? n_src - 1 : r);          // validated on the host; never read outside the source
+    const float* s = src + (size_t)r * width;
+    float* o = out + (size_t)blockIdx.y * width;
+    for (long long j = (long long)blockIdx.x * blockDim.x + threadIdx.x; j < width; j += (long long)gridDim.x * blockDim.x) o[j] = s[j];
+}
+}  // namespace
+
+LI_EXPORT int li_gather_rows(const float* src, const int* rows, float* out, int n_src, int n_rows, long long width, cudaStream_t stream) {
+    LI_REQUIRE(n_src >= 1 && n_rows >= 0 && n_rows <= 65535 && width >= 1, "gather_rows: bad sizes (%d source rows, %d rows, width %lld)", n_src, n_rows, width);
+    if (n_rows == 0) return 0;
+    const unsigned bx = (unsigned)((width + 1023) / 1024 < 64 ? (width + 1023) / 1024 : 64);
+    li_launch_pdl(gather_rows_kernel, dim3(bx, n_rows), dim3(256), 0, stream, src, rows, out, n_src, width);
+    return li_check_launch("gather_rows");
+}
+
 LI_EXPORT int li_scale_inplace(float* x, long long n, float factor, cudaStream_t stream) {
     LI_REQUIRE(n >= 0 && n <= (1LL << 40), "scale: bad size %lld", n);
     if (n == 0) return 0;

@@ -16,8 +16,10 @@
 // order.  When 16-row tiles alone do not fill the GPU, k is split over
 // several CTAs (split count depends on N and K only, never on M): each writes
 // float partial sums to a workspace, and the CTA that arrives last (a counter
-// per tile) adds them in split order.  A token's result therefore does not
-// depend on how many other tokens are in the batch.
+// per tile) adds them in split order.  Within this kernel a token's result
+// therefore does not depend on how many other tokens are in the batch; which
+// kernel a product goes to does depend on the step's size (linear.cu), so across
+// those choices a token's result is the same up to rounding only.
 //
 // Requires K % 8 == 0 and 16-byte aligned operands; M <= 64.
 #include "common.cuh"

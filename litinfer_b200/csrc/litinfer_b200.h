@@ -61,6 +61,9 @@ int li_gather_rmsnorm(const float* x, const int* rows, const float* w, float eps
 /* x += delta over n elements. */
 int li_residual_add(float* x, const void* delta, int dtype, long long n, cudaStream_t stream);
 
+/* out[r, :] = src[rows[r], :] for n_rows rows of `width` floats. */
+int li_gather_rows(const float* src, const int* rows, float* out, int n_src, int n_rows, long long width, cudaStream_t stream);
+
 /* x *= factor over n floats (an embedding scale). */
 int li_scale_inplace(float* x, long long n, float factor, cudaStream_t stream);
 

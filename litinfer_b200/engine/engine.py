@@ -44,7 +44,7 @@ class EngineConfig:
     prefill_chunk: int = 2048
     use_graphs: bool = True
     max_context: Optional[int] = None    # longest context a captured decode step must cover
-    run_ahead: bool = False              # launch a decode step before the tokens of the one before it are read
+    run_ahead: bool = True               # launch a decode step before the tokens of the one before it are read
 
 
 @dataclass

@@ -63,6 +63,10 @@ class ModelRunner:
         # warm-up, and a captured step would freeze which slots it updates)
         self._may_split = not any(isinstance(r, FixedState) for r in model.cache_requirements())
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and self._may_split
+        from .. import kernels as K
+
+        if K.profile.enabled:
+            self.use_graphs = False                        # LLAISYS_PROFILE times kernel launches: a replayed graph has none to time
         # a captured attention launch has to cover the longest context it may meet (its grid and workspace
         # are sized for it), so that length is capped; steps with a longer context run without a graph
         self.max_context = min(int(max_context or model.spec.max_position_embeddings), self.GRAPH_CONTEXT_CAP)
@@ -113,6 +117,15 @@ class ModelRunner:
         trip through the host."""
         items = list(items)
         decode_only = all(len(it.tokens) == 1 for it in items)
+        from .. import kernels as K
+
+        if K.profile.enabled:
+            K.profile.phase = "decode" if decode_only else "prefill"
+        if K.TRACE:
+            import sys
+
+            print(f"[LLAISYS] step sequences={len(items)} tokens={sum(len(it.tokens) for it in items)} "
+                  f"wanted={sum(len(it.want) for it in items)} graphs={self.use_graphs}", file=sys.stderr, flush=True)
         if token_source is not None and (not decode_only or token_source.numel() != len(items)):
             raise ValueError("token_source needs one token per item and items of one token each")
         fits = decode_only and max(it.cache.length for it in items) + 1 <= self.max_context
@@ -226,9 +239,15 @@ class ModelRunner:
         self.graph_replays += 1
         if rows is None:
             rows = [i for i, w in enumerate(wanted) if w]
-        if rows == list(range(B)):
-            return g.logits
-        return g.logits[torch.tensor(rows, dtype=torch.long, device=self.device)] if rows else g.logits[:0]
+        if not rows:
+            return g.logits[:0]
+        if rows == list(range(rows[0], rows[0] + len(rows))):
+            return g.logits[rows[0]:rows[0] + len(rows)]        # a run of rows (the usual case: every item's, or the last token's): a view
+        from .. import kernels as K
+
+        out = torch.empty((len(rows), g.logits.shape[1]), dtype=torch.float32, device=self.device)
+        K.gather_rows(g.logits, torch.tensor(rows, dtype=torch.int32, device=self.device), out)
+        return out
 
     def _capture(self, B: Optional[int], max_blocks: int, buf: np.ndarray, layout, max_q_len: int = 1, singles: int = 0) -> _DecodeGraph:
         """Capture the model's forward pass over the packed step.  ``B``: the decode bucket it is kept under (None: the

@@ -161,6 +161,14 @@ def fill_randint(out: torch.Tensor, key: int, high: int) -> None:
            "fill_randint")
 
 
+def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[r] = src[rows[r]]`` for float32 rows (int32 ``rows`` on the device)."""
+    _need(src, "gather source", torch.float32)
+    _need(rows, "gather rows", torch.int32, (out.shape[0],))
+    _need(out, "gather output", torch.float32, (rows.shape[0], src.shape[1]))
+    _check(library().li_gather_rows(_p(src), _p(rows), _p(out), _i(src.shape[0]), _i(rows.shape[0]), _l(src.shape[1]), _stream(out)), "gather_rows")
+
+
 def scale_inplace(x32: torch.Tensor, factor: float) -> None:
     """x32 *= factor (float32, in place)."""
     _need(x32, "scale operand", torch.float32)
@@ -435,3 +443,91 @@ def sample(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor) -> Non
     _need(params, "sampling parameters", torch.int32, (R, 6))
     _need(out, "sample output", torch.int32, (R,))
     _check(library().li_sample(_p(logits), _p(params), _p(out), _i(R), _i(V), _stream(out)), "sample")
+
+
+# --------------------------------------------------------------------------
+# LLAISYS_PROFILE=1: device time per kernel function, keyed by phase, reported at exit
+# --------------------------------------------------------------------------
+# LitInfer's switch of the same name (src/utils/profiler.cpp:47-104) times every operator call on the CPU and prints
+# a table of "phase/op  calls  time(ms)  pct(%)" to standard error when the process ends.  Here an operator call is a
+# kernel launch, so the time is the device's: a pair of CUDA events around each call, read when the report is made.
+# While the switch is on the step function launches every kernel from the host (no captured graphs: a replayed graph
+# runs without passing through these functions).
+
+def _env_on(name: str) -> bool:
+    import os
+
+    return os.environ.get(name, "").lower() in ("1", "true", "on")
+
+
+class Profile:
+    def __init__(self) -> None:
+        self.enabled = _env_on("LLAISYS_PROFILE")
+        self.phase = ""
+        self._pending = []                                 # (key, start event, stop event)
+        self.total_ms = {}
+        self.calls = {}
+        if self.enabled:
+            import atexit
+
+            atexit.register(self.report)
+
+    def reset(self) -> None:
+        self._pending.clear()
+        self.total_ms.clear()
+        self.calls.clear()
+
+    def wrap(self, name, fn):
+        import functools
+
+        @functools.wraps(fn)
+        def timed(*args, **kwargs):
+            if not self.enabled or not torch.cuda.is_available():
+                return fn(*args, **kwargs)
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            try:
+                return fn(*args, **kwargs)
+            finally:
+                stop.record()
+                self._pending.append(((self.phase + "/" + name) if self.phase else name, start, stop))
+                if len(self._pending) >= 4096:
+                    self.collect()
+
+        return timed
+
+    def collect(self) -> None:
+        if self._pending:
+            torch.cuda.synchronize()
+        for key, start, stop in self._pending:
+            self.total_ms[key] = self.total_ms.get(key, 0.0) + start.elapsed_time(stop)
+            self.calls[key] = self.calls.get(key, 0) + 1
+        self._pending.clear()
+
+    def report(self, out=None) -> None:
+        import sys
+
+        out = out or sys.stderr
+        self.collect()
+        grand = sum(self.total_ms.values())
+        print("\n================ LLAISYS PROFILE ================", file=out)
+        if grand <= 0.0:
+            print("(no profiled operations)\n================================================", file=out)
+            return
+        print(f"  total op time: {grand:.3f} ms (device time of kernel launches)", file=out)
+        print("------------------------------------------------", file=out)
+        print("  op                          calls     time(ms)    pct(%)", file=out)
+        for key, ms in sorted(self.total_ms.items(), key=lambda kv: -kv[1]):
+            print(f"  {key:<28}{self.calls[key]:>8}{ms:>12.3f}{100.0 * ms / grand:>9.2f}", file=out)
+        print("================================================", file=out, flush=True)
+
+
+profile = Profile()
+TRACE = _env_on("LLAISYS_TRACE")          # LitInfer's other switch (src/llaisys/models/qwen2.cpp:17-26): a line per call on standard error
+
+_TIMED = ("embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "linear_add_scaled", "apply_row_scale",
+          "rope_kv_write", "linear_rope_kv", "rope_table", "paged_attention", "swiglu", "argmax", "sample", "gather_rows", "scale_inplace",
+          "logit_cap")
+if profile.enabled:
+    for _name in _TIMED:
+        globals()[_name] = profile.wrap(_name, globals()[_name])

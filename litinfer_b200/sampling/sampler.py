@@ -46,6 +46,34 @@ class Sampler:
 
     def __init__(self, device) -> None:
         self.device = torch.device(device)
+        # the rows' parameters go to the device through pinned memory, without blocking the host (two buffers in turn:
+        # a step may be launched before the one before it has been read)
+        self._pinned: List[torch.Tensor] = []
+        self._on_device: List[torch.Tensor] = []
+        self._copied: List = []
+        self._turn = 0
+
+    def _upload(self, packed: np.ndarray) -> torch.Tensor:
+        if self.device.type != "cuda":
+            return torch.from_numpy(packed.copy())
+        R = packed.shape[0]
+        if not self._pinned or self._pinned[0].shape[0] < R:
+            for ev in self._copied:
+                ev.synchronize()
+            cap = max(64, 2 * R)
+            self._pinned = [torch.empty((cap, 6), dtype=torch.int32).pin_memory() for _ in range(2)]
+            self._on_device = [torch.empty((cap, 6), dtype=torch.int32, device=self.device) for _ in range(2)]
+            self._copied = [torch.cuda.Event() for _ in range(2)]
+            for ev in self._copied:
+                ev.record(torch.cuda.current_stream(self.device))
+        t = self._turn
+        self._turn ^= 1
+        self._copied[t].synchronize()                     # the copy that last used this pinned buffer has finished
+        self._pinned[t].numpy()[:R] = packed
+        dst = self._on_device[t][:R]
+        dst.copy_(self._pinned[t][:R], non_blocking=True)
+        self._copied[t].record(torch.cuda.current_stream(self.device))
+        return dst
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], output_index: Sequence[int]) -> torch.Tensor:
         """``logits`` float32 [R, V]; returns int32 [R] on the device."""
@@ -68,7 +96,7 @@ class Sampler:
         packed[:, 3] = (seeds & np.uint64(0xFFFF_FFFF)).astype(np.uint32).view(np.int32)
         packed[:, 4] = (seeds >> np.uint64(32)).astype(np.uint32).view(np.int32)
         packed[:, 5] = [int(i) for i in output_index]
-        K.sample(logits, torch.from_numpy(packed).to(logits.device), out)
+        K.sample(logits, self._upload(packed), out)
         return out
 
 

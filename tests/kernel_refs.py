@@ -195,6 +195,10 @@ def paged_attention_dense(qkv, out, k_cache, v_cache, block_table, q_start, ctx_
     _store(out, res.reshape(T, num_heads * head_dim))
 
 
+def gather_rows(src, rows, out):
+    out.copy_(src[rows.long()])
+
+
 def scale_inplace(x32, factor):
     x32.mul_(factor)
 
@@ -283,5 +287,5 @@ def sample(logits, params, out):
     out.copy_(torch.tensor(res, dtype=torch.int32))
 
 
-ALL = ["scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
+ALL = ["gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]

@@ -10,7 +10,8 @@ import random
 import pytest
 import torch
 
-from litinfer_b200.cache import CacheManager, OutOfPages, PagePool, PoolError
+from litinfer_b200.cache import CacheManager, OutOfPages, PoolError
+from pool_face import PagePool
 from litinfer_b200.engine import RequestRefused, Scheduler, SchedulerConfig
 from litinfer_b200.parts import FixedState, PagedKV
 from litinfer_b200.sampling import SamplingParams

@@ -434,3 +434,27 @@ def test_toy_positions_and_block_arrangements_on_cpu_references(model_dirs, cpu_
     from test_engine_gpu import run_toy_positions_and_blocks
 
     run_toy_positions_and_blocks(model_dirs, "cpu", "float32")
+
+
+def test_profile_switch_reports_per_phase_and_op(model_dirs, cpu_kernels, monkeypatch, capsys):
+    """LLAISYS_PROFILE (LitInfer: src/utils/profiler.cpp): every kernel call is recorded under phase/op and a table is
+    printed; on the CPU twin there is no device to time, so calls are counted through the same wrapper with timing off."""
+    import io
+
+    from litinfer_b200 import kernels
+
+    prof = kernels.Profile()
+    prof.enabled = True
+    calls = []
+    wrapped = prof.wrap("linear", lambda *a, **k: calls.append(a))
+    prof.phase = "prefill"
+    wrapped(1, 2)
+    assert calls == [(1, 2)]                               # without a CUDA device the call goes straight through
+    prof.total_ms = {"prefill/linear": 3.0, "decode/linear": 1.0}
+    prof.calls = {"prefill/linear": 2, "decode/linear": 5}
+    out = io.StringIO()
+    prof.report(out)
+    text = out.getvalue()
+    assert "LLAISYS PROFILE" in text and "total op time: 4.000 ms" in text
+    assert text.index("prefill/linear") < text.index("decode/linear")          # sorted by time
+    assert "75.00" in text and "25.00" in text

@@ -596,3 +596,26 @@ def test_prompts_that_come_back_run_from_captured_shapes(dtype, model_dirs):
         exact += o == r
         assert o == r or (dtype == "bfloat16" and P.same_up_to_a_near_tie(o, r, m)), f"prompt of {len(p)}: {o} vs {r} (margins {m})"
     assert exact >= len(prompts) - 1
+
+
+def test_profile_and_trace_switches_of_the_command_line(model_dirs):
+    """LLAISYS_PROFILE=1 and LLAISYS_TRACE=1 (LitInfer's switches) on the command line as a user runs it: a table of device
+    time per phase and kernel at exit, a line per call, and the same tokens as without them."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    cmd = [sys.executable, "-m", "litinfer_b200", "--model", str(model_dirs["A"]), "--prompt", "5 17 3 200 41", "--max_steps", "6", "--test"]
+    plain = subprocess.run(cmd, capture_output=True, text=True, cwd=root, timeout=600)
+    assert plain.returncode == 0, plain.stderr[-2000:]
+    env = dict(os.environ, LLAISYS_PROFILE="1", LLAISYS_TRACE="1")
+    prof = subprocess.run(cmd, capture_output=True, text=True, cwd=root, timeout=600, env=env)
+    assert prof.returncode == 0, prof.stderr[-2000:]
+    assert prof.stdout == plain.stdout
+    err = prof.stderr
+    assert "LLAISYS PROFILE" in err and "total op time" in err
+    assert "prefill/linear" in err and "decode/paged_attention" in err and "decode/linear_rope_kv" in err
+    assert "[LLAISYS] Calling generate ntokens=5" in err and "[LLAISYS] step sequences=1" in err
+    assert "LLAISYS PROFILE" not in plain.stderr

@@ -83,6 +83,24 @@ def test_rmsnorm_family(dtype, H):
     assert torch.equal(x1, x2)
 
 
+def test_gather_rows_scale_and_logit_cap():
+    k = K()
+    g = torch.Generator().manual_seed(9)
+    src = torch.randn(37, 4099, generator=g).to(dev())
+    rows = torch.tensor([36, 0, 5, 5, 17], dtype=torch.int32, device=dev())
+    out = torch.empty(5, 4099, dtype=torch.float32, device=dev())
+    k.gather_rows(src, rows, out)
+    assert torch.equal(out, src[rows.long()])
+    x = src.clone()
+    k.scale_inplace(x, 3.0)
+    assert torch.equal(x, src * 3.0)
+    y = (src * 4).clone()
+    k.logit_cap(y, 2.5)
+    ref = (src * 4).clone()
+    R.logit_cap(ref, 2.5)
+    assert (y - ref).abs().max() < 1e-6 and float(y.abs().max()) <= 2.5
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_swiglu(dtype):
     T, I = 5, 272

@@ -334,3 +334,37 @@ def test_captured_decode_step_of_many_requests(tmp_path):
         check_logits(x.cpu(), ref, "bfloat16", f"70 requests, token -{j}, launched plainly")
         check_logits(y.cpu(), ref, "bfloat16", f"70 requests, token -{j}, from the captured step")
     assert captured.runner.graph_replays == 4
+
+
+def test_a_request_across_the_kernel_choices_of_a_step(tmp_path):
+    """In bfloat16 which kernels run depends on the step's size: up to 16 tokens the norms ride on the products, from 17 on
+    they are kernels of their own; from 120 (sequence, key head) pairs on decode attention walks a whole context per CTA
+    instead of splitting it; from 65 tokens on the products go to the tensor-memory kernels.  The same request decoded alone
+    and among 15, 16, 70 and 127 others must give the plain model's logits every time, and the same logits up to rounding."""
+    from litinfer_b200.engine.replay import Replayer
+    from litinfer_b200.models import DecoderModel
+    from litinfer_b200.weights import write_model_folder
+
+    cfg = MID["head128"]
+    folder = tmp_path / "model"
+    write_model_folder(folder, dict(cfg), seed=79, store_dtype="float32")
+    vocab = cfg["vocab_size"]
+    model = DecoderModel.from_dir(folder, "bfloat16", torch.device("cuda:0"))
+    main = random_tokens(203, vocab, 1000)
+    ref = plain_logits(folder, main, "bfloat16")[200:203]
+    seen = {}
+    for others in (0, 15, 16, 70, 127):
+        rp = Replayer(model, 256 + 64 * others, max_live=others + 1, use_graphs=False)
+        rp.step(dict(step=0, entries=[dict(id="main", tokens=main[:200], want=[])]))
+        side = [random_tokens(9 + (i * 5) % 30, vocab, 2000 + i) for i in range(others)]
+        if others:
+            rp.step(dict(step=1, entries=[dict(id=f"o{i}", tokens=p[:-3], want=[]) for i, p in enumerate(side)]))
+        rows = []
+        for j in range(3):
+            entries = [dict(id="main", tokens=[main[200 + j]], want=[0])] + [dict(id=f"o{i}", tokens=[p[len(p) - 3 + j]], want=[]) for i, p in enumerate(side)]
+            rows.append(rp.step(dict(step=2 + j, entries=entries))[0].clone().cpu())
+        seen[others] = torch.stack(rows)
+        check_logits(seen[others], ref, "bfloat16", f"the request among {others} others")
+    scale = float(ref.abs().max())
+    for others, lg in seen.items():
+        assert (lg - seen[0]).abs().max() <= 0.02 * scale, f"among {others} others the logits move by {(lg - seen[0]).abs().max()} (scale {scale})"
