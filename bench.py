@@ -427,6 +427,10 @@ def time_serve(model, cfg, requests=64, seed=11, max_tokens_per_step=4096, page_
             t = time.perf_counter()
             eng.step()
             steps.append(time.perf_counter() - t)
+            if len(steps) % 200 == 0:
+                print(f"[serve] {'timed' if timed else 'warm-up'} pass: step {len(steps)}, {len(eng.scheduler.running)} running, "
+                      f"{len(eng.scheduler.waiting)} waiting, {eng.tokens_run} tokens run, {time.perf_counter() - t0:.1f} s",
+                      file=sys.stderr, flush=True)
         eng.drain()
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
@@ -608,6 +612,10 @@ def run_reference(args):
 
 
 def main() -> int:
+    if os.environ.get("LITINFER_BENCH_STACKS"):          # where the program is, every so many seconds, on stderr
+        import faulthandler
+
+        faulthandler.dump_traceback_later(float(os.environ["LITINFER_BENCH_STACKS"]), repeat=True)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)

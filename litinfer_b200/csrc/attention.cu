@@ -19,7 +19,7 @@ int li_attention_generic(const void* qkv, void* out, const void* kcache, const v
 bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                         const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                        float scale, int window, int max_ctx_len, cudaStream_t stream);
+                        float scale, int window, int max_ctx_len, int expected, cudaStream_t stream);
 bool li_attention_prefill_accepts(int nh, int nkv, int dh, int page_size);
 int li_attention_prefill(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size,
@@ -49,9 +49,12 @@ static int attention_portions(const void* qkv, void* out, const void* kcache, co
     const bool tc = max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size);
     if (!tc && !li_attention_prefill_accepts(nh, nkv, dh, page_size)) return 0;
     const int split = (singles != 0 && max_q_len > 1 && li_attention_decode_accepts(nh, nkv, dh, page_size)) ? 1 : 0;
+    // how many sequences the decode kernel will find: the count if it is known, else (a captured step, whose sequences are
+    // rounded up to the next power of two) at least half of them
+    const int expected = singles > 0 ? singles : (S + 1) / 2;
     if (split)
         if (int rc = li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, dh,
-                                         page_size, num_pages, scale, window, max_ctx_len, stream))
+                                         page_size, num_pages, scale, window, max_ctx_len, expected, stream))
             return rc;
     *done = true;
     if (tc)
@@ -72,7 +75,7 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
     if (dtype == LI_BF16) {
         if (max_q_len == 1 && T == S && li_attention_decode_accepts(nh, nkv, dh, page_size))
             return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, nullptr, S, nh, nkv, dh, page_size,
-                                       num_pages, scale, window, max_ctx_len, stream);
+                                       num_pages, scale, window, max_ctx_len, S, stream);
         bool done = false;
         const int rc = attention_portions(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                           num_pages, scale, window, max_q_len, max_ctx_len, old_lens, singles, &done, stream);
@@ -103,7 +106,7 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
         LI_REQUIRE(max_q_len == 1 && T == S, "attention: the decode kernel takes one token per sequence");
         LI_REQUIRE(li_attention_decode_accepts(nh, nkv, dh, page_size), "attention: the decode kernel refuses heads=%d/%d head_dim=%d page=%d", nh, nkv, dh, page_size);
         return li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, nullptr, S, nh, nkv, dh, page_size, num_pages,
-                                   scale, window, max_ctx_len, stream);
+                                   scale, window, max_ctx_len, S, stream);
     }
     if (which == 2 || which == 3) {
         if (which == 2) {
@@ -114,7 +117,7 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
         const int split = (singles != 0 && max_q_len > 1 && li_attention_decode_accepts(nh, nkv, dh, page_size)) ? 1 : 0;
         if (split)
             if (int rc = li_attention_decode(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, dh,
-                                             page_size, num_pages, scale, window, max_ctx_len, stream))
+                                             page_size, num_pages, scale, window, max_ctx_len, singles > 0 ? singles : (S + 1) / 2, stream))
                 return rc;
         if (which == 2)
             return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,

@@ -168,10 +168,12 @@ int ensure_workspace(size_t floats, float** buf, unsigned** counters) {
 template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
            const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int page_size, int num_pages, float scale,
-           int window, int max_ctx_len, cudaStream_t stream) {
+           int window, int max_ctx_len, int expected, cudaStream_t stream) {
     const int G = nh / nkv;
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
-    if ((long long)S * nkv >= kWholeFrom) {
+    // `expected`: how many of the S sequences are this kernel's (a step may hold portions beside them, and a captured step
+    // is padded with empty sequences): that count, not S, says whether one CTA per sequence and kv head fills the GPU
+    if ((long long)(expected > 0 && expected < S ? expected : S) * nkv >= kWholeFrom) {
         // one CTA per (sequence, kv head) fills the GPU: no split of the context
         constexpr int W = 8, KB = DH <= 128 ? 32 : 16;
         const size_t wsmem = (2 * W * 16 + (size_t)W * G * DH) * sizeof(float);
@@ -221,11 +223,11 @@ bool li_attention_decode_accepts(int nh, int nkv, int dh, int page_size) {
 
 int li_attention_decode(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                         const int* ctx_lens, const int* old_lens, const int* q_start, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                        float scale, int window, int max_ctx_len, cudaStream_t stream) {
+                        float scale, int window, int max_ctx_len, int expected, cudaStream_t stream) {
 #define LI_CASE(D)                                                                                                             \
     case D:                                                                                                                    \
         return launch<D>(qkv, out, kcache, vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, S, nh, nkv, page_size, num_pages, scale, \
-                         window, max_ctx_len, stream);
+                         window, max_ctx_len, expected, stream);
     switch (dh) {
         LI_CASE(16) LI_CASE(32) LI_CASE(48) LI_CASE(64) LI_CASE(80) LI_CASE(96) LI_CASE(112) LI_CASE(128) LI_CASE(256)
         default:

@@ -179,7 +179,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int k = 0; k < kKeys / 16; ++k) {
                     const unsigned long long da = umma_desc(sm.p + (k >> 2) * (kRows * 128)) + (unsigned long long)((k & 3) * 2);
                     const unsigned long long db = umma_desc_sw32(sm.v[b] + k * (DH * 32));
-                    umma_bf16(tmem_pv, da, db, idesc_pv, k ? 1u : 0u);
+                    umma_bf16(tmem_pv, da, db, idesc_pv, (j | k) ? 1u : 0u);     // the output accumulates over the tiles
                 }
                 umma_commit(&sm.pv_full);
                 umma_commit(&sm.v_empty[b]);
@@ -197,9 +197,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int p = valid ? p_first + r : -1;                  // its position; no key is visible to an unused row
         const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
         const float scale_log2 = scale * 1.4426950408889634f;
-        float o[HD];
-#pragma unroll
-        for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+        // m: the maximum the exponentials are taken against.  It follows the true maximum lazily: only when that has grown by
+        // more than kLazy (in powers of two) is the output so far, which accumulates in tensor memory, scaled down to the
+        // new one.  Until then the probabilities may reach 2^kLazy, which costs bfloat16 and the float sums nothing, and
+        // the quotient at the end is the same.
+        constexpr float kLazy = 8.0f;
         float m = -INFINITY, l = 0.0f;
         unsigned char* prow = sm.p + half * (kRows * 128) + (r >> 3) * 1024 + (r & 7) * 128;      // panel `half` holds this thread's 64 keys
         bool ok = true;
@@ -231,14 +233,36 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             mx = fmaxf(mine, sm.mx[j & 1][half ^ 1][r]);
             return true;
         };
-        float mx = -INFINITY;
-        ok = tile_max(0, mx);
         for (int j = 0; j < ntiles && ok; ++j) {
+            float mx;
+            ok = tile_max(j, mx);
+            if (!ok) break;
             const int key0 = (kt_first + j) * kKeys + half * HK;
             const bool whole = key0 >= lo && key0 + HK - 1 <= p;
-            const float m_new = fmaxf(m, mx * scale_log2);           // scale > 0: the order is the same
+            const float m_true = fmaxf(m, mx * scale_log2);          // scale > 0: the order is the same
+            const bool grow = m_true > m + kLazy;                    // also the first visible key of a row (m = -inf)
+            const float m_new = grow ? m_true : m;
             const float ms = (m_new == -INFINITY) ? 0.0f : m_new;
-            const float alpha = fast_exp2(m - ms);
+            // P V of the tile before has read the operand tile that this one overwrites, and has added to the output
+            if (j > 0) {
+                ok = mbar_wait(&sm.pv_full, (j - 1) & 1);
+                if (!ok) break;
+                if (__any_sync(0xffffffffu, grow)) {                 // whole warps: the accesses to tensor memory are warp-wide
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const float alpha = grow ? fast_exp2(m - ms) : 1.0f;
+#pragma unroll
+                    for (int c = 0; c < HD / 32; ++c) {
+                        float v[32];
+                        tmem_ld_32x32(tmem_pv + lane_addr + half * HD + c * 32, v);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] *= alpha;
+                        tmem_st_32x32(tmem_pv + lane_addr + half * HD + c * 32, v);
+                    }
+                    tmem_st_wait();
+                    l *= alpha;
+                }
+            }
+            m = m_new;
             // second pass: probabilities, rounded to bfloat16, into the operand tile
             float sum = 0.0f;
 #pragma unroll
@@ -272,25 +296,22 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     *reinterpret_cast<uint4*>(prow + ch * 16) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
                 }
             }
-            l = l * alpha + sum;
-            m = m_new;
+            l += sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&sm.p_full);
-            // while the tensor cores multiply P V: the maximum of the next tile, whose scores are ready by now
-            if (j + 1 < ntiles) {
-                ok = tile_max(j + 1, mx);
-                if (!ok) break;
-            }
-            ok = mbar_wait(&sm.pv_full, j & 1);
-            if (!ok) break;
+        }
+        // the output of the last product
+        float o[HD];
+        if (ok) ok = mbar_wait(&sm.pv_full, (ntiles - 1) & 1);
+        if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
             for (int c = 0; c < HD / 32; ++c) {
                 float v[32];
                 tmem_ld_32x32(tmem_pv + lane_addr + half * HD + c * 32, v);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + v[i];
+                for (int i = 0; i < 32; ++i) o[c * 32 + i] = v[i];
             }
         }
         // the row's denominator: the sums of its two threads (both ran with the same maxima)

@@ -70,8 +70,10 @@ struct __align__(1024) SharedStorage {
 // One head (128 columns at `col0` of the accumulator row of token `row`) of the q|k|v product: bias, rotation of q and k
 // by the step's table, q into the output row, k into the paged cache, v into it transposed (rope_epilogue.cuh).
 // Called by whole warps (the loads from tensor memory are warp-wide); `valid`: this thread's row is a row of the product.
+// Two threads share a row (the warps w and w + 4 reach the same lanes of tensor memory): `part` 0 takes the first half of
+// the head's rotation pairs (or of a value head's columns), `part` 1 the second.
 __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_tile, int row, bool valid, int head, const float* __restrict__ bias,
-                                                bf16* __restrict__ out, int N, const RopeEpilogue& re) {
+                                                bf16* __restrict__ out, int N, const RopeEpilogue& re, int part) {
     const int slot = valid ? re.slot_mapping[row] : -1;
     const int page = slot / re.page_size, off = slot - page * re.page_size;
     const bool cache_ok = valid && re.write && slot >= 0 && page < re.num_pages;       // validated on the host; never write outside the cache
@@ -82,8 +84,8 @@ __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_ti
                     : (is_q ? out + (size_t)row * N + (size_t)head * 128
                             : re.kcache + (((size_t)page * re.nkv + (head - re.nh)) * re.page_size + off) * 128);
         const float2* cs = reinterpret_cast<const float2*>(re.cos_sin) + (size_t)(valid ? row : 0) * 64;
-#pragma unroll 1
-        for (int c = 0; c < 2; ++c) {
+        {
+            const int c = part;
             float lo[32], hi[32];
             tc::tmem_ld_32x32(tmem_row + (unsigned)(col_in_tile + c * 32), lo);
             tc::tmem_ld_32x32(tmem_row + (unsigned)(col_in_tile + c * 32 + 64), hi);
@@ -123,7 +125,7 @@ __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_ti
     } else {
         bf16* dst = cache_ok ? re.vcache + ((size_t)page * re.nkv + (head - re.nh - re.nkv)) * 128 * re.page_size + off : nullptr;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 2 * part; c < 2 * part + 2; ++c) {
             float v[32];
             tc::tmem_ld_32x32(tmem_row + (unsigned)(col_in_tile + c * 32), v);
             if (cache_ok) {
@@ -137,8 +139,13 @@ __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_ti
     }
 }
 
+// threads of a CTA: producer warp, issuing warp, four epilogue warps; eight with the rotary epilogue, the longest one for
+// its product (a k of `hidden` only, and per row a table read, a rotation and scattered stores): two threads share a row
+template <bool kRope>
+constexpr int threads_of() { return kRope ? 320 : kThreads; }
+
 template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false, bool kRope = false>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_of<kRope>(), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, Tout* __restrict__ out, int M, int N, int K, int* __restrict__ error_flag,
                     float* __restrict__ partial, unsigned* __restrict__ counters, int ksplit, const RopeEpilogue rope) {
@@ -288,7 +295,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 for (int hl = 0; hl < BN / 128; ++hl) {
                     const int head = n0 / 128 + hl;
                     if (head * 128 < N)                            // the same for the whole CTA
-                        rope_store_head(tmem_acc + ((unsigned)(quarter * 32) << 16), hl * 128, row, row < M, head, bias, reinterpret_cast<bf16*>(out), N, rope);
+                        rope_store_head(tmem_acc + ((unsigned)(quarter * 32) << 16), hl * 128, row, row < M, head, bias, reinterpret_cast<bf16*>(out), N, rope,
+                                        (warp - 2) >> 2);
                 }
             } else if (ksplit == 1) {
 #pragma unroll 1
@@ -418,7 +426,7 @@ int launch_tile(const void* a, const void* w, const float* bias, void* out, int 
         LI_REQUIRE((size_t)grid.x * grid.y <= (size_t)kSplitCounters, "linear (tcgen05): too many tiles for a split of k");
         if (int rc = split_workspace((size_t)ksplit * grid.x * grid.y * BM * BN, &ws)) return rc;
     }
-    li_launch_pdl(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu, kPair, kRope>, grid, dim3(kThreads), smem, stream, dim3(kPair ? 2 : 1, 1, 1), map_a, map_w,
+    li_launch_pdl(gemm_tcgen05_kernel<BM, BN, Tout, kSwiglu, kPair, kRope>, grid, dim3(threads_of<kRope>()), smem, stream, dim3(kPair ? 2 : 1, 1, 1), map_a, map_w,
                   bias, (Tout*)out, M, N, K, g_error_dev, ws->partial, ws->counters, ksplit, rope);
     return li_check_launch("linear (tcgen05)");
 }
