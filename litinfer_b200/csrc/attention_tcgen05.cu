@@ -37,7 +37,7 @@ using namespace tc;
 
 constexpr int kRows = 128;          // tokens per CTA
 constexpr int kKeys = 128;          // keys per tile
-constexpr int kThreads = 320;        // producer warp, tensor-core warp, eight softmax warps
+constexpr int kThreads = 352;        // warp 0 loads keys (and the queries), warp 1 issues the products, warps 2-9 softmax, warp 10 loads values
 constexpr int kBuffers = 2;
 
 template <int DH>
@@ -45,22 +45,33 @@ struct __align__(1024) Smem {
     unsigned char q[kRows * DH * 2];                 // DH / 64 panels of [128 rows][64] (128-byte swizzle)
     unsigned char k[kBuffers][kKeys * DH * 2];       // the same for keys
     unsigned char v[kBuffers][kKeys * DH * 2];       // 8 pages of [DH rows][16 keys] (32-byte swizzle)
-    unsigned char p[kRows * kKeys * 2];              // 2 panels of [128 rows][64 keys] (128-byte swizzle)
-    unsigned long long q_full, p_full, pv_full;
+    unsigned char p[2][kRows * kKeys * 2];           // per tile parity: 2 panels of [128 rows][64 keys] (128-byte swizzle)
+    unsigned long long q_full, p_full[2], pv_full[2];      // P written / P V done, by tile parity
     unsigned long long s_full[2], mx_full[2];
     float mx[2][2][kRows];                           // [tile parity][half of the keys][row]: maxima, exchanged between a row's two threads
     unsigned long long k_full[kBuffers], k_empty[kBuffers], v_full[kBuffers], v_empty[kBuffers];
     unsigned tmem_base;
 };
 
+// bytes of dynamic shared memory beyond the structure, for its alignment: all that a CTA may have, up to a kilobyte
+template <int DH>
+__host__ __device__ constexpr size_t smem_pad() {
+    return sizeof(Smem<DH>) + 1024 <= 232448 ? 1024 : 232448 - sizeof(Smem<DH>);
+}
+
 template <int DH>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
                             int max_blocks, const int* __restrict__ q_start, const int* __restrict__ ctx_lens, int nh, int nkv,
-                            int page_size, int num_pages, float scale, int window, int skip_single, int* __restrict__ error_flag) {
+                            int page_size, int num_pages, float scale, int window, int skip_single, int* __restrict__ error_flag, int trace) {
     extern __shared__ unsigned char smem_raw[];
     Smem<DH>& sm = *reinterpret_cast<Smem<DH>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // the tiles want 1024-byte alignment; with head_dim 128 there is not a whole kilobyte to spare for it
+    if ((size_t)(reinterpret_cast<unsigned char*>(&sm) - smem_raw) > smem_pad<DH>()) {
+        if (threadIdx.x == 0) atomicExch(error_flag, 14);
+        return;
+    }
     constexpr int kPanels = DH / 64;
     constexpr unsigned kTmemCols = 512;              // S of two tiles: 128 columns each; PV: up to 128
     // CTAs start in the order x, y, z: all heads of a sequence's last tile of tokens (which sees the most keys) first, then
@@ -82,10 +93,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         mbar_init(&sm.q_full, 1);
         mbar_init(&sm.s_full[0], 1);
         mbar_init(&sm.s_full[1], 1);
-        mbar_init(&sm.p_full, 256);
+        mbar_init(&sm.p_full[0], 256);
+        mbar_init(&sm.p_full[1], 256);
         mbar_init(&sm.mx_full[0], 256);
         mbar_init(&sm.mx_full[1], 256);
-        mbar_init(&sm.pv_full, 1);
+        mbar_init(&sm.pv_full[0], 1);
+        mbar_init(&sm.pv_full[1], 1);
         for (int b = 0; b < kBuffers; ++b) {
             mbar_init(&sm.k_full[b], 1);
             mbar_init(&sm.k_empty[b], 1);
@@ -104,46 +117,63 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const unsigned tmem_s = sm.tmem_base, tmem_pv = sm.tmem_base + 256;      // S of tile j at tmem_s + 128 (j & 1)
     pdl_launch_dependents();
     pdl_wait();
+    // Debugging aid (LITINFER_B200_ATTN_TRACE): the first CTA leaves the clock at which each role passed each point of each
+    // of its first 16 key tiles in the mapped status area, [role][point][tile] from word 16 on.
+    const bool tracing = trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    auto stamp = [&](int role, int point, int j) {
+        if (tracing && j < 16) error_flag[16 + (role * 8 + point) * 16 + j] = (int)clock64();
+    };
 
-    if (warp == 0) {
-        if (lane == 0) {
+    if (warp == 0 || warp == 10) {
+        // The loading warps: warp 0 the keys (and, first, the queries), warp 10 the values.  A tile of 128 keys is eight
+        // blocks of 16 keys, each in one page; lane b looks block b's page up (for the next tile while this one's copies are
+        // issued) and issues that block's copies, so that the lookups and the issue of a tile's 8 or 16 copies run side by
+        // side instead of one after another in a single thread.  Lane 0 waits for the buffer and announces the bytes.
+        const bool keys = warp == 0;
+        if (keys && lane == 0) {
             mbar_expect_tx(&sm.q_full, kRows * DH * 2);
 #pragma unroll
             for (int pn = 0; pn < kPanels; ++pn) tma_load_2d(sm.q + pn * (kRows * 128), &map_q, h * DH + pn * 64, tok0 + cta_i0, &sm.q_full);
-            const int* bt = block_table + (size_t)s * max_blocks;
-            bool ok = true;
-            // keys of a tile as soon as the product S two tiles back has read its buffer, values once P V has
-            for (int j = 0; j < ntiles && ok; ++j) {
-                const int b = j % kBuffers;
-                const unsigned free_parity = ((j / kBuffers) & 1) ^ 1;
-                const int key0 = (kt_first + j) * kKeys;
-                int pages[kKeys / 16], offs[kKeys / 16];
-#pragma unroll
-                for (int pg = 0; pg < kKeys / 16; ++pg) {
-                    const int key = key0 + pg * 16;
-                    const int idx = key / page_size;
-                    int page = (key < ctx && idx < max_blocks) ? bt[idx] : 0;
-                    if (page < 0 || page >= num_pages) page = 0;
-                    pages[pg] = page;
-                    offs[pg] = key % page_size;
-                }
-                ok = mbar_wait(&sm.k_empty[b], free_parity);
-                if (!ok) break;
-                mbar_expect_tx(&sm.k_full[b], kKeys * DH * 2);
-#pragma unroll
-                for (int pg = 0; pg < kKeys / 16; ++pg)
+        }
+        const int* bt = block_table + (size_t)s * max_blocks;
+        auto look_up = [&](int j, int& page, int& off) {
+            const int key = (kt_first + j) * kKeys + (lane & 7) * 16;
+            const int idx = key / page_size;
+            page = (j < ntiles && key < ctx && idx < max_blocks) ? bt[idx] : 0;
+            if (page < 0 || page >= num_pages) page = 0;
+            off = key - idx * page_size;
+        };
+        int page, off;
+        look_up(0, page, off);
+        bool ok = true;
+        // keys of a tile as soon as the product S two tiles back has read its buffer, values once P V has
+        for (int j = 0; j < ntiles; ++j) {
+            const int b = j % kBuffers;
+            const unsigned free_parity = ((j / kBuffers) & 1) ^ 1;
+            int next_page, next_off;
+            look_up(j + 1, next_page, next_off);
+            if (lane == 0) {
+                stamp(keys ? 0 : 4, 0, j);
+                ok = mbar_wait(keys ? &sm.k_empty[b] : &sm.v_empty[b], free_parity);
+                if (ok) mbar_expect_tx(keys ? &sm.k_full[b] : &sm.v_full[b], kKeys * DH * 2);
+                stamp(keys ? 0 : 4, 1, j);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
+            if (lane < kKeys / 16) {
+                if (keys) {
 #pragma unroll
                     for (int pn = 0; pn < kPanels; ++pn)
-                        tma_load_2d(sm.k[b] + pn * (kKeys * 128) + pg * 2048, &map_k, pn * 64, (pages[pg] * nkv + kvh) * page_size + offs[pg], &sm.k_full[b]);
-                ok = mbar_wait(&sm.v_empty[b], free_parity);
-                if (!ok) break;
-                mbar_expect_tx(&sm.v_full[b], kKeys * DH * 2);
-#pragma unroll
-                for (int pg = 0; pg < kKeys / 16; ++pg)
-                    tma_load_2d(sm.v[b] + pg * (DH * 32), &map_v, offs[pg], (pages[pg] * nkv + kvh) * DH, &sm.v_full[b]);
+                        tma_load_2d(sm.k[b] + pn * (kKeys * 128) + lane * 2048, &map_k, pn * 64, (page * nkv + kvh) * page_size + off, &sm.k_full[b]);
+                } else {
+                    tma_load_2d(sm.v[b] + lane * (DH * 32), &map_v, off, (page * nkv + kvh) * DH, &sm.v_full[b]);
+                }
             }
-            if (!ok) atomicExch(error_flag, 11);
+            if (lane == 0) stamp(keys ? 0 : 4, 2, j);
+            page = next_page;
+            off = next_off;
         }
+        if (!ok && lane == 0) atomicExch(error_flag, 11);
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr unsigned idesc_s = umma_idesc(kRows, kKeys), idesc_pv = umma_idesc(kRows, DH);
@@ -151,7 +181,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // S of tile j + 1 is issued before P V of tile j: the tensor cores work on it while the softmax of tile j runs
             auto issue_s = [&](int j) {
                 const int b = j % kBuffers;
+                stamp(1, 0, j);
                 if (!mbar_wait(&sm.k_full[b], (j / kBuffers) & 1)) return false;
+                stamp(1, 1, j);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
@@ -170,19 +202,23 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     ok = issue_s(j + 1);
                     if (!ok) break;
                 }
+                stamp(1, 2, j);
                 ok = mbar_wait(&sm.v_full[b], (j / kBuffers) & 1);
                 if (!ok) break;
-                ok = mbar_wait(&sm.p_full, j & 1);
+                stamp(1, 3, j);
+                ok = mbar_wait(&sm.p_full[j & 1], (j >> 1) & 1);
                 if (!ok) break;
+                stamp(1, 4, j);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k) {
-                    const unsigned long long da = umma_desc(sm.p + (k >> 2) * (kRows * 128)) + (unsigned long long)((k & 3) * 2);
+                    const unsigned long long da = umma_desc(sm.p[j & 1] + (k >> 2) * (kRows * 128)) + (unsigned long long)((k & 3) * 2);
                     const unsigned long long db = umma_desc_sw32(sm.v[b] + k * (DH * 32));
                     umma_bf16(tmem_pv, da, db, idesc_pv, (j | k) ? 1u : 0u);     // the output accumulates over the tiles
                 }
-                umma_commit(&sm.pv_full);
+                umma_commit(&sm.pv_full[j & 1]);
                 umma_commit(&sm.v_empty[b]);
+                stamp(1, 5, j);
             }
             if (!ok) atomicExch(error_flag, 12);
         }
@@ -203,107 +239,98 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // the quotient at the end is the same.
         constexpr float kLazy = 8.0f;
         float m = -INFINITY, l = 0.0f;
-        unsigned char* prow = sm.p + half * (kRows * 128) + (r >> 3) * 1024 + (r & 7) * 128;      // panel `half` holds this thread's 64 keys
+        const int prow = half * (kRows * 128) + (r >> 3) * 1024 + (r & 7) * 128;      // within a P tile: panel `half` holds this thread's 64 keys
         bool ok = true;
-        // the row's maximum over tile j (first pass over the scores); keys that the row sees whole need no mask
-        auto tile_max = [&](int j, float& mx) {
+        for (int j = 0; j < ntiles && ok; ++j) {
             const int key0 = (kt_first + j) * kKeys + half * HK;
-            if (!mbar_wait(&sm.s_full[j & 1], (j >> 1) & 1)) return false;
+            if (lane == 0 && quarter == 0) stamp(2 + half, 0, j);
+            ok = mbar_wait(&sm.s_full[j & 1], (j >> 1) & 1);
+            if (!ok) break;
+            if (lane == 0 && quarter == 0) stamp(2 + half, 1, j);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // this thread's 64 scores of the tile, read once and kept for both passes; a key the row does not see reads -inf
+            float v[HK];
+            tmem_ld_32x64(tmem_s + 128 * (j & 1) + lane_addr + half * HK, v);
             const bool whole = key0 >= lo && key0 + HK - 1 <= p;
+            if (!whole) {
+#pragma unroll
+                for (int i = 0; i < HK; ++i)
+                    if (key0 + i < lo || key0 + i > p) v[i] = -INFINITY;
+            }
+            // the row's maximum over the tile: this half's, then the other thread's through shared memory
             float mine = -INFINITY;
 #pragma unroll
-            for (int c = 0; c < HK / 32; ++c) {
-                float v[32];
-                tmem_ld_32x32(tmem_s + 128 * (j & 1) + lane_addr + half * HK + c * 32, v);
-                if (whole) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) mine = fmaxf(mine, v[i]);
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int key = key0 + c * 32 + i;
-                        if (key >= lo && key <= p) mine = fmaxf(mine, v[i]);
-                    }
-                }
-            }
+            for (int i = 0; i < HK; ++i) mine = fmaxf(mine, v[i]);
             sm.mx[j & 1][half][r] = mine;
+            if (lane == 0 && quarter == 0) stamp(2 + half, 2, j);
             mbar_arrive(&sm.mx_full[j & 1]);
-            if (!mbar_wait(&sm.mx_full[j & 1], (j >> 1) & 1)) return false;
-            mx = fmaxf(mine, sm.mx[j & 1][half ^ 1][r]);
-            return true;
-        };
-        for (int j = 0; j < ntiles && ok; ++j) {
-            float mx;
-            ok = tile_max(j, mx);
+            ok = mbar_wait(&sm.mx_full[j & 1], (j >> 1) & 1);
             if (!ok) break;
-            const int key0 = (kt_first + j) * kKeys + half * HK;
-            const bool whole = key0 >= lo && key0 + HK - 1 <= p;
+            if (lane == 0 && quarter == 0) stamp(2 + half, 3, j);
+            const float mx = fmaxf(mine, sm.mx[j & 1][half ^ 1][r]);
             const float m_true = fmaxf(m, mx * scale_log2);          // scale > 0: the order is the same
             const bool grow = m_true > m + kLazy;                    // also the first visible key of a row (m = -inf)
             const float m_new = grow ? m_true : m;
             const float ms = (m_new == -INFINITY) ? 0.0f : m_new;
-            // P V of the tile before has read the operand tile that this one overwrites, and has added to the output
-            if (j > 0) {
-                ok = mbar_wait(&sm.pv_full, (j - 1) & 1);
+            // P V two tiles back has read the operand tile that this one overwrites
+            if (j > 1) {
+                ok = mbar_wait(&sm.pv_full[j & 1], ((j - 2) >> 1) & 1);
                 if (!ok) break;
+            }
+            if (lane == 0 && quarter == 0) stamp(2 + half, 4, j);
+            if (j > 0) {
                 if (__any_sync(0xffffffffu, grow)) {                 // whole warps: the accesses to tensor memory are warp-wide
+                    // the output so far is complete once P V of the tile before is
+                    ok = mbar_wait(&sm.pv_full[(j - 1) & 1], ((j - 1) >> 1) & 1);
+                    if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const float alpha = grow ? fast_exp2(m - ms) : 1.0f;
 #pragma unroll
                     for (int c = 0; c < HD / 32; ++c) {
-                        float v[32];
-                        tmem_ld_32x32(tmem_pv + lane_addr + half * HD + c * 32, v);
+                        float w[32];
+                        tmem_ld_32x32(tmem_pv + lane_addr + half * HD + c * 32, w);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] *= alpha;
-                        tmem_st_32x32(tmem_pv + lane_addr + half * HD + c * 32, v);
+                        for (int i = 0; i < 32; ++i) w[i] *= alpha;
+                        tmem_st_32x32(tmem_pv + lane_addr + half * HD + c * 32, w);
                     }
                     tmem_st_wait();
                     l *= alpha;
                 }
             }
             m = m_new;
-            // second pass: probabilities, rounded to bfloat16, into the operand tile
+            if (lane == 0 && quarter == 0) stamp(2 + half, 5, j);
+            // second pass: probabilities (2^-inf = 0 for the keys not seen), rounded to bfloat16, into the operand tile
+            // The special-function unit delivers 16 exponentials a clock, and a tile has 16,384: where all of this thread's
+            // keys are seen (no -inf among the scores) every fourth one is computed by a polynomial instead.
             float sum = 0.0f;
+            const float neg_ms = -ms;
+            auto second_pass = [&](auto fourth) {
 #pragma unroll
-            for (int c = 0; c < HK / 32; ++c) {
-                float v[32];
-                tmem_ld_32x32(tmem_s + 128 * (j & 1) + lane_addr + half * HK + c * 32, v);
-                unsigned pk[16];
-                if (whole) {
+                for (int c = 0; c < HK / 8; ++c) {
+                    unsigned pk[4];
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const float e0 = fast_exp2(fmaf(v[i], scale_log2, -ms)), e1 = fast_exp2(fmaf(v[i + 1], scale_log2, -ms));
+                    for (int i = 0; i < 4; ++i) {
+                        const float x0 = fmaf(v[c * 8 + 2 * i], scale_log2, neg_ms), x1 = fmaf(v[c * 8 + 2 * i + 1], scale_log2, neg_ms);
+                        const float e0 = fast_exp2(x0), e1 = (i & 1) ? fourth(x1) : fast_exp2(x1);
                         sum += e0 + e1;
                         __nv_bfloat162 t2 = __floats2bfloat162_rn(e0, e1);
-                        pk[i >> 1] = *reinterpret_cast<unsigned*>(&t2);
+                        pk[i] = *reinterpret_cast<unsigned*>(&t2);
                     }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        const int key = key0 + c * 32 + i;
-                        const float e0 = (key >= lo && key <= p) ? fast_exp2(fmaf(v[i], scale_log2, -ms)) : 0.0f;
-                        const float e1 = (key + 1 >= lo && key + 1 <= p) ? fast_exp2(fmaf(v[i + 1], scale_log2, -ms)) : 0.0f;
-                        sum += e0 + e1;
-                        __nv_bfloat162 t2 = __floats2bfloat162_rn(e0, e1);
-                        pk[i >> 1] = *reinterpret_cast<unsigned*>(&t2);
-                    }
+                    // 8 keys = one 16-byte chunk of the row, swizzled by the row
+                    *reinterpret_cast<uint4*>(sm.p[j & 1] + prow + ((c ^ (r & 7)) * 16)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
                 }
-                // 32 keys = four 16-byte chunks of the row, chunks 4 c .. 4 c + 3, swizzled by the row
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const int ch = (c * 4 + q) ^ (r & 7);
-                    *reinterpret_cast<uint4*>(prow + ch * 16) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-                }
-            }
+            };
+            if (whole) second_pass([](float x) { return poly_exp2(x); });
+            else second_pass([](float x) { return fast_exp2(x); });
             l += sum;
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(&sm.p_full);
+            mbar_arrive(&sm.p_full[j & 1]);
+            if (lane == 0 && quarter == 0) stamp(2 + half, 6, j);
         }
         // the output of the last product
         float o[HD];
-        if (ok) ok = mbar_wait(&sm.pv_full, (ntiles - 1) & 1);
+        if (ok) ok = mbar_wait(&sm.pv_full[(ntiles - 1) & 1], ((ntiles - 1) >> 1) & 1);
         if (ok) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -362,7 +389,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     if (int rc = make_map_ex(&map_q, qkv, (unsigned long long)T, row_elems, 64, kRows, 128)) return rc;
     if (int rc = make_map_ex(&map_k, kcache, (unsigned long long)num_pages * nkv * page_size, DH, 64, 16, 128)) return rc;
     if (int rc = make_map_ex(&map_v, vcache, (unsigned long long)num_pages * nkv * DH, (unsigned long long)page_size, 16, DH, 32)) return rc;
-    const size_t smem = sizeof(Smem<DH>) + 1024;
+    const size_t smem = sizeof(Smem<DH>) + smem_pad<DH>();
     static bool raised = false;
     if (!raised) {
         cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<DH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -371,8 +398,9 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     }
     LI_REQUIRE(S <= 65535 && ceil_div(max_q_len, kRows) <= 65535, "attention (tcgen05): batch %d or portions of %d tokens too large for one launch", S, max_q_len);
     dim3 grid(nh, ceil_div(max_q_len, kRows), S);
+    static const int trace = getenv("LITINFER_B200_ATTN_TRACE") ? 1 : 0;
     li_launch_pdl(prefill_attention_tc_kernel<DH>, grid, dim3(kThreads), smem, stream, map_q, map_k, map_v, (bf16*)out, block_table, max_blocks,
-                  q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, skip_single, err_dev);
+                  q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, skip_single, err_dev, trace);
     return li_check_launch("attention (tcgen05)");
 }
 

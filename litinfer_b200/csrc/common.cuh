@@ -71,6 +71,22 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// 2^x without the special-function unit, for -125 <= x < 128 (below that it returns 2^-125, not 0): x = n + f with n the
+// nearest integer (read off the low mantissa bits of x + 1.5 * 2^23) and |f| <= 1/2, 2^f by a quartic (relative error
+// below 3e-6), n added to the exponent.  Where a kernel's exponentials outnumber what that unit delivers (16 a clock
+// and multiprocessor), some of them go this way through the multiply-add pipe.
+__device__ __forceinline__ float poly_exp2(float x) {
+    x = fmaxf(x, -125.0f);
+    const float t = x + 12582912.0f;
+    const float f = x - (t - 12582912.0f);
+    float p = 0.009570099413394928f;
+    p = fmaf(p, f, 0.05591785907745361f);
+    p = fmaf(p, f, 0.240247443318367f);
+    p = fmaf(p, f, 0.6931217908859253f);
+    p = fmaf(p, f, 0.9999992847442627f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 // up * gate / (1 + exp(-gate)) (src/ops/swiglu/op.cpp:17-23) in float.  For an output that is rounded to 16 bits the
 // exponential and the quotient come from the fast units (errors near 2^-21, far below that rounding): an epilogue in which
 // one warp works through its row alone is bound by the length of this chain of instructions.
