@@ -1,20 +1,23 @@
 // Prefill attention on the fifth-generation tensor cores: long portions of prompts over the paged cache,
 // causal, grouped-query, bfloat16.
 //
-// Grid (query head, tile of 128 tokens, sequence).  A CTA of six warps works on 128 consecutive tokens of a
+// Grid (query head, tile of 128 tokens, sequence).  A CTA of eleven warps works on 128 consecutive tokens of a
 // portion for one head, against tiles of 128 keys:
-//   warp 0     one thread brings Q (once) and, two tiles ahead, K and V of each tile into shared memory with
-//              TMA, page by page through the block table: a page of keys is 16 rows of the K operand
-//              ([keys, head_dim], 128-byte swizzle), a page of values (cached transposed, [head_dim, 16 slots])
-//              is the V operand of one k-step ([head_dim, 16 keys], 32-byte swizzle);
+//   warp 0     brings K of each tile into shared memory with TMA, up to three tiles ahead, page by page through the
+//              block table, a lane per block of 16 keys: a block is 16 rows of the K operand ([keys, head_dim],
+//              128-byte swizzle);
+//   warp 10    the same for V: a block of values (cached transposed, [head_dim, 16 slots]) is the V operand of
+//              one k-step ([head_dim, 16 keys], 32-byte swizzle);
 //   warp 1     one thread issues the products with tcgen05.mma, accumulators in tensor memory:
-//              S = Q K^T (128 x 128) and, once the probabilities are in shared memory, PV = P V (128 x head_dim);
-//   warps 2-9  two threads per token, each with half of a tile's keys and half of the output columns: they read
-//              their part of the token's row of S from tensor memory, apply scale and mask, keep the running
+//              S = Q K^T (128 x 128, two buffers) and O += P V (128 x head_dim), with Q and P as operands FROM
+//              tensor memory: shared memory, whose bandwidth bounded the kernel when Q and P were read from it
+//              as well, then carries K and V only;
+//   warps 2-9  two threads per token, each with half of a tile's keys: they put the token's row of Q into tensor
+//              memory once; per tile they read their part of the row of S, apply scale and mask, keep the
 //              maximum (exchanged between the two) and sum of the online softmax in float
-//              (src/ops/paged_attention/op.cpp:194-234), write P as bfloat16 in the operand layout, then add
-//              PV to the output row in registers, O = O alpha + PV.  The maximum of tile j + 1 is taken while
-//              the tensor cores multiply P V of tile j, and S of tile j + 1 was issued before that.
+//              (src/ops/paged_attention/op.cpp:194-234), and write P as bfloat16 over the first half of that S
+//              buffer.  O stays in tensor memory; it is scaled down only when a row's maximum has grown by more
+//              than 2^8 (see kLazy).  S of tile j + 1 is issued before P V of tile j.
 // Keys and values of the portion itself are already in the cache (the rope kernel ran before).  Token i of a
 // portion of n tokens in a context of c sits at position p = c - n + i and sees keys max(0, p - window + 1) .. p.
 // Keys of a tile that lie past the context are read from whatever page the table names (page 0 if none) and get
@@ -38,14 +41,12 @@ using namespace tc;
 constexpr int kRows = 128;          // tokens per CTA
 constexpr int kKeys = 128;          // keys per tile
 constexpr int kThreads = 352;        // warp 0 loads keys (and the queries), warp 1 issues the products, warps 2-9 softmax, warp 10 loads values
-constexpr int kBuffers = 2;
+constexpr int kBuffers = 3;
 
 template <int DH>
 struct __align__(1024) Smem {
-    unsigned char q[kRows * DH * 2];                 // DH / 64 panels of [128 rows][64] (128-byte swizzle)
-    unsigned char k[kBuffers][kKeys * DH * 2];       // the same for keys
-    unsigned char v[kBuffers][kKeys * DH * 2];       // 8 pages of [DH rows][16 keys] (32-byte swizzle)
-    unsigned char p[2][kRows * kKeys * 2];           // per tile parity: 2 panels of [128 rows][64 keys] (128-byte swizzle)
+    unsigned char k[kBuffers][kKeys * DH * 2];       // DH / 64 panels of [128 keys][64] (128-byte swizzle)
+    unsigned char v[kBuffers][kKeys * DH * 2];       // 8 blocks of [DH rows][16 keys] (32-byte swizzle)
     unsigned long long q_full, p_full[2], pv_full[2];      // P written / P V done, by tile parity
     unsigned long long s_full[2], mx_full[2];
     float mx[2][2][kRows];                           // [tile parity][half of the keys][row]: maxima, exchanged between a row's two threads
@@ -61,7 +62,7 @@ __host__ __device__ constexpr size_t smem_pad() {
 
 template <int DH>
 __global__ void __launch_bounds__(kThreads, 1)
-prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
                             int max_blocks, const int* __restrict__ q_start, const int* __restrict__ ctx_lens, int nh, int nkv,
                             int page_size, int num_pages, float scale, int window, int skip_single, int* __restrict__ error_flag, int trace) {
@@ -73,7 +74,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         return;
     }
     constexpr int kPanels = DH / 64;
-    constexpr unsigned kTmemCols = 512;              // S of two tiles: 128 columns each; PV: up to 128
+    constexpr unsigned kTmemCols = 512;              // S of two tiles: 128 columns each; O: up to 128; Q: up to 64
     // CTAs start in the order x, y, z: all heads of a sequence's last tile of tokens (which sees the most keys) first, then
     // all heads of the tile before it, and so on, so that the long CTAs do not start late
     const int s = blockIdx.z, h = blockIdx.x;
@@ -90,7 +91,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int ntiles = kt_last - kt_first + 1;
 
     if (threadIdx.x == 0) {
-        mbar_init(&sm.q_full, 1);
+        mbar_init(&sm.q_full, 256);
         mbar_init(&sm.s_full[0], 1);
         mbar_init(&sm.s_full[1], 1);
         mbar_init(&sm.p_full[0], 256);
@@ -114,7 +115,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const unsigned tmem_s = sm.tmem_base, tmem_pv = sm.tmem_base + 256;      // S of tile j at tmem_s + 128 (j & 1)
+    // S of tile j at tmem_s + 128 (j & 1), and P of tile j over its first 64 columns (two bfloat16 a column)
+    const unsigned tmem_s = sm.tmem_base, tmem_pv = sm.tmem_base + 256, tmem_q = sm.tmem_base + 384;
     pdl_launch_dependents();
     pdl_wait();
     // Debugging aid (LITINFER_B200_ATTN_TRACE): the first CTA leaves the clock at which each role passed each point of each
@@ -125,16 +127,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     };
 
     if (warp == 0 || warp == 10) {
-        // The loading warps: warp 0 the keys (and, first, the queries), warp 10 the values.  A tile of 128 keys is eight
+        // The loading warps: warp 0 the keys, warp 10 the values.  A tile of 128 keys is eight
         // blocks of 16 keys, each in one page; lane b looks block b's page up (for the next tile while this one's copies are
         // issued) and issues that block's copies, so that the lookups and the issue of a tile's 8 or 16 copies run side by
         // side instead of one after another in a single thread.  Lane 0 waits for the buffer and announces the bytes.
         const bool keys = warp == 0;
-        if (keys && lane == 0) {
-            mbar_expect_tx(&sm.q_full, kRows * DH * 2);
-#pragma unroll
-            for (int pn = 0; pn < kPanels; ++pn) tma_load_2d(sm.q + pn * (kRows * 128), &map_q, h * DH + pn * 64, tok0 + cta_i0, &sm.q_full);
-        }
         const int* bt = block_table + (size_t)s * max_blocks;
         auto look_up = [&](int j, int& page, int& off) {
             const int key = (kt_first + j) * kKeys + (lane & 7) * 16;
@@ -178,6 +175,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (lane == 0) {
             constexpr unsigned idesc_s = umma_idesc(kRows, kKeys), idesc_pv = umma_idesc(kRows, DH);
             bool ok = mbar_wait(&sm.q_full, 0);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             // S of tile j + 1 is issued before P V of tile j: the tensor cores work on it while the softmax of tile j runs
             auto issue_s = [&](int j) {
                 const int b = j % kBuffers;
@@ -187,9 +185,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int k = 0; k < DH / 16; ++k) {
-                    const unsigned long long da = umma_desc(sm.q + (k >> 2) * (kRows * 128)) + (unsigned long long)((k & 3) * 2);
                     const unsigned long long db = umma_desc(sm.k[b] + (k >> 2) * (kKeys * 128)) + (unsigned long long)((k & 3) * 2);
-                    umma_bf16(tmem_s + 128 * (j & 1), da, db, idesc_s, k ? 1u : 0u);
+                    umma_bf16_ta(tmem_s + 128 * (j & 1), tmem_q + 8 * k, db, idesc_s, k ? 1u : 0u);
                 }
                 umma_commit(&sm.s_full[j & 1]);
                 umma_commit(&sm.k_empty[b]);
@@ -212,9 +209,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int k = 0; k < kKeys / 16; ++k) {
-                    const unsigned long long da = umma_desc(sm.p[j & 1] + (k >> 2) * (kRows * 128)) + (unsigned long long)((k & 3) * 2);
                     const unsigned long long db = umma_desc_sw32(sm.v[b] + k * (DH * 32));
-                    umma_bf16(tmem_pv, da, db, idesc_pv, (j | k) ? 1u : 0u);     // the output accumulates over the tiles
+                    umma_bf16_ta(tmem_pv, tmem_s + 128 * (j & 1) + 8 * k, db, idesc_pv, (j | k) ? 1u : 0u);     // the output accumulates over the tiles
                 }
                 umma_commit(&sm.pv_full[j & 1]);
                 umma_commit(&sm.v_empty[b]);
@@ -239,8 +235,27 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // the quotient at the end is the same.
         constexpr float kLazy = 8.0f;
         float m = -INFINITY, l = 0.0f;
-        const int prow = half * (kRows * 128) + (r >> 3) * 1024 + (r & 7) * 128;      // within a P tile: panel `half` holds this thread's 64 keys
         bool ok = true;
+        // The token's row of Q into tensor memory, the operand layout of the product S = Q K^T: two bfloat16 a column, this
+        // thread the 64 dimensions from 64 * half on (with head_dim 64 the first thread of the row has them all).
+        if (half * 64 < DH) {                                    // the same for the whole warp
+            unsigned qw[32];
+            if (valid) {
+                const uint4* src = reinterpret_cast<const uint4*>(qkv + (size_t)(tok0 + cta_i0 + r) * row_elems + (size_t)h * DH + half * 64);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 t4 = __ldg(src + i);
+                    qw[4 * i] = t4.x, qw[4 * i + 1] = t4.y, qw[4 * i + 2] = t4.z, qw[4 * i + 3] = t4.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) qw[i] = 0u;
+            }
+            tmem_st_32x32(tmem_q + lane_addr + half * 32, qw);
+            tmem_st_wait();
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        mbar_arrive(&sm.q_full);
         for (int j = 0; j < ntiles && ok; ++j) {
             const int key0 = (kt_first + j) * kKeys + half * HK;
             if (lane == 0 && quarter == 0) stamp(2 + half, 0, j);
@@ -272,11 +287,6 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const bool grow = m_true > m + kLazy;                    // also the first visible key of a row (m = -inf)
             const float m_new = grow ? m_true : m;
             const float ms = (m_new == -INFINITY) ? 0.0f : m_new;
-            // P V two tiles back has read the operand tile that this one overwrites
-            if (j > 1) {
-                ok = mbar_wait(&sm.pv_full[j & 1], ((j - 2) >> 1) & 1);
-                if (!ok) break;
-            }
             if (lane == 0 && quarter == 0) stamp(2 + half, 4, j);
             if (j > 0) {
                 if (__any_sync(0xffffffffu, grow)) {                 // whole warps: the accesses to tensor memory are warp-wide
@@ -299,31 +309,29 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             m = m_new;
             if (lane == 0 && quarter == 0) stamp(2 + half, 5, j);
-            // second pass: probabilities (2^-inf = 0 for the keys not seen), rounded to bfloat16, into the operand tile
+            // second pass: probabilities (2^-inf = 0 for the keys not seen), rounded to bfloat16, over the first half of this
+            // tile's S, in the operand layout of the product P V: both threads of the row have their scores in registers
+            // by now (the exchange above), and the S that will overwrite them is issued after that product.
             // The special-function unit delivers 16 exponentials a clock, and a tile has 16,384: where all of this thread's
             // keys are seen (no -inf among the scores) every fourth one is computed by a polynomial instead.
             float sum = 0.0f;
             const float neg_ms = -ms;
+            unsigned pk[HK / 2];
             auto second_pass = [&](auto fourth) {
 #pragma unroll
-                for (int c = 0; c < HK / 8; ++c) {
-                    unsigned pk[4];
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float x0 = fmaf(v[c * 8 + 2 * i], scale_log2, neg_ms), x1 = fmaf(v[c * 8 + 2 * i + 1], scale_log2, neg_ms);
-                        const float e0 = fast_exp2(x0), e1 = (i & 1) ? fourth(x1) : fast_exp2(x1);
-                        sum += e0 + e1;
-                        __nv_bfloat162 t2 = __floats2bfloat162_rn(e0, e1);
-                        pk[i] = *reinterpret_cast<unsigned*>(&t2);
-                    }
-                    // 8 keys = one 16-byte chunk of the row, swizzled by the row
-                    *reinterpret_cast<uint4*>(sm.p[j & 1] + prow + ((c ^ (r & 7)) * 16)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                for (int i = 0; i < HK / 2; ++i) {
+                    const float x0 = fmaf(v[2 * i], scale_log2, neg_ms), x1 = fmaf(v[2 * i + 1], scale_log2, neg_ms);
+                    const float e0 = fast_exp2(x0), e1 = (i & 1) ? fourth(x1) : fast_exp2(x1);
+                    sum += e0 + e1;
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(e0, e1);
+                    pk[i] = *reinterpret_cast<unsigned*>(&t2);
                 }
             };
             if (whole) second_pass([](float x) { return poly_exp2(x); });
             else second_pass([](float x) { return fast_exp2(x); });
             l += sum;
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tmem_st_32x32(tmem_s + 128 * (j & 1) + lane_addr + half * (HK / 2), pk);
+            tmem_st_wait();
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(&sm.p_full[j & 1]);
             if (lane == 0 && quarter == 0) stamp(2 + half, 6, j);
@@ -384,9 +392,8 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     if (int rc = setup(&encode, &err_host, &err_dev)) return rc;
     if (*err_host != 0)
         return li_fail("attention (tcgen05): an earlier launch gave up waiting on a barrier (status %d); the results since then are invalid", *err_host);
-    CUtensorMap map_q, map_k, map_v;
-    const unsigned long long row_elems = (unsigned long long)(nh + 2 * nkv) * DH;
-    if (int rc = make_map_ex(&map_q, qkv, (unsigned long long)T, row_elems, 64, kRows, 128)) return rc;
+    CUtensorMap map_k, map_v;
+    const long long row_elems = (long long)(nh + 2 * nkv) * DH;
     if (int rc = make_map_ex(&map_k, kcache, (unsigned long long)num_pages * nkv * page_size, DH, 64, 16, 128)) return rc;
     if (int rc = make_map_ex(&map_v, vcache, (unsigned long long)num_pages * nkv * DH, (unsigned long long)page_size, 16, DH, 32)) return rc;
     const size_t smem = sizeof(Smem<DH>) + smem_pad<DH>();
@@ -399,7 +406,7 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     LI_REQUIRE(S <= 65535 && ceil_div(max_q_len, kRows) <= 65535, "attention (tcgen05): batch %d or portions of %d tokens too large for one launch", S, max_q_len);
     dim3 grid(nh, ceil_div(max_q_len, kRows), S);
     static const int trace = getenv("LITINFER_B200_ATTN_TRACE") ? 1 : 0;
-    li_launch_pdl(prefill_attention_tc_kernel<DH>, grid, dim3(kThreads), smem, stream, map_q, map_k, map_v, (bf16*)out, block_table, max_blocks,
+    li_launch_pdl(prefill_attention_tc_kernel<DH>, grid, dim3(kThreads), smem, stream, (const bf16*)qkv, row_elems, map_k, map_v, (bf16*)out, block_table, max_blocks,
                   q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, skip_single, err_dev, trace);
     return li_check_launch("attention (tcgen05)");
 }
