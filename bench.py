@@ -21,7 +21,7 @@ One JSON line is printed:
 
 Weights (3 GB) are larger than L2, so nothing stays cached between steps.
 
-``--only decode|prefill|mixed|kernels-decode|kernels-prefill`` measures one part and prints a short line (for
+``--only decode|prefill|mixed|kernels-decode|kernels-prefill|kernels-mixed`` measures one part and prints a short line (for
 profiling runs and the summaries under ``profiles/``); ``mixed`` is a step of ``--batch`` requests decoding at
 ``--context`` beside a portion of ``--prefill-tokens`` prompt tokens.
 
@@ -355,10 +355,13 @@ def time_first_token(model, cfg, prompt_len=16, repeats=7):
     return statistics.median(times)
 
 
-def time_mixed(model, batch, context, portion, repeats=4):
+def time_mixed(model, batch, context, portion, repeats=4, graphs=True, profiler=None):
     """Median device time of a step that holds ``batch`` requests decoding at about ``context`` tokens beside a portion of
     ``portion`` prompt tokens of another request (what a continuous-batching engine runs while a prompt comes in): as the
-    engine runs it, from the captured graph of its shape once that has come back."""
+    engine runs it, from the captured graph of its shape once that has come back (``graphs``).  ``profiler``: a context
+    manager factory entered around the timed steps (for the table of kernels, with the launches made plainly)."""
+    import contextlib
+
     import torch
 
     from litinfer_b200.cache import CacheManager
@@ -367,7 +370,8 @@ def time_mixed(model, batch, context, portion, repeats=4):
     spec = model.spec
     pages = (batch * (context + 64) + 2 * portion + 4096) // 16
     manager = CacheManager(model.cache_requirements(), [e.cache_from for e in spec.schedule], pages, 16, batch + 2, model.dtype, model.device)
-    runner = ModelRunner(model, manager, use_graphs=True)
+    runner = ModelRunner(model, manager, use_graphs=graphs)
+    watch = contextlib.ExitStack()
     g = torch.Generator().manual_seed(4)
     live = []
     for i in range(batch):
@@ -390,6 +394,8 @@ def time_mixed(model, batch, context, portion, repeats=4):
         manager.extend(incoming, incoming.length + portion)
         items.append(StepItem(incoming, torch.randint(0, spec.vocab_size, (portion,), generator=g).tolist(), (portion - 1,)))
         torch.cuda.synchronize()
+        if it == 3 and profiler is not None:
+            watch.enter_context(profiler())
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         runner.step(items)
@@ -397,6 +403,7 @@ def time_mixed(model, batch, context, portion, repeats=4):
         torch.cuda.synchronize()
         if it >= 3:
             times.append(start.elapsed_time(stop))
+    watch.close()
     return statistics.median(times)
 
 
@@ -626,7 +633,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--shape", default="1.5b", choices=sorted(SHAPES), help="layer sizes: the headline 1.5B shape, or the 7B / 14B shapes of the larger workloads")
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "mixed", "kernels-decode", "kernels-prefill", "serve", "chunked", "fp32"],
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "mixed", "kernels-decode", "kernels-prefill", "kernels-mixed", "serve", "chunked", "fp32"],
                     help="measure one part and print a short line (for profiling runs); kernels-*: a table of the "
                          "kernels' device times from torch.profiler; mixed: --batch requests decoding at --context beside "
                          "a portion of --prefill-tokens prompt tokens")
@@ -661,7 +668,7 @@ def main() -> int:
     wbytes = weight_bytes(model)
     kv_per_token = 2 * cfg["num_hidden_layers"] * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
 
-    if args.only in ("kernels-decode", "kernels-prefill"):
+    if args.only in ("kernels-decode", "kernels-prefill", "kernels-mixed"):
         from torch.profiler import ProfilerActivity, profile
 
         if args.only == "kernels-decode":
@@ -669,6 +676,17 @@ def main() -> int:
             with profile(activities=[ProfilerActivity.CUDA]) as prof:
                 r = time_decode(model, args.batch, args.context, args.steps, warmup)
             print(json.dumps({"only": args.only, "batch": args.batch, "steps": args.steps + warmup, **{k: round(v, 4) for k, v in r.items()}}))
+        elif args.only == "kernels-mixed":
+            holder = {}
+
+            def watching():
+                holder["prof"] = profile(activities=[ProfilerActivity.CUDA])
+                return holder["prof"]
+
+            ms = time_mixed(model, args.batch, args.context, args.prefill_tokens, graphs=False, profiler=watching)
+            prof = holder["prof"]
+            print(json.dumps({"only": args.only, "decoding": args.batch, "context": args.context, "portion": args.prefill_tokens,
+                              "ms_launched_plainly": round(ms, 3), "steps_in_table": 4}))
         else:
             time_prefill(model, args.prefill_tokens, repeats=1, graphs=False)
             with profile(activities=[ProfilerActivity.CUDA]) as prof:

@@ -28,7 +28,7 @@ int li_attention_prefill(const void* qkv, void* out, const void* kcache, const v
 bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const void* vcache, int nh, int nkv, int dh, int page_size);
 int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                         float scale, int window, int max_q_len, int skip_single, cudaStream_t stream);
+                         float scale, int window, int max_q_len, int skip_single, const int* units, int unit_slots, cudaStream_t stream);
 
 static int validate(int T, int S, int nh, int nkv, int dh, int page_size, int window) {
     LI_REQUIRE(T >= 0 && S > 0, "attention: bad batch T=%d S=%d", T, S);
@@ -43,8 +43,8 @@ static int validate(int T, int S, int nh, int nkv, int dh, int page_size, int wi
 // `singles` the sequences of one token first, on the decode kernel.
 static int attention_portions(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                               const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                              float scale, int window, int max_q_len, int max_ctx_len, const int* old_lens, int singles, bool* done,
-                              cudaStream_t stream) {
+                              float scale, int window, int max_q_len, int max_ctx_len, const int* old_lens, int singles, const int* units,
+                              int slots_portions, int slots_all, bool* done, cudaStream_t stream) {
     *done = false;
     const bool tc = max_q_len >= 64 && scale > 0.0f && li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size);
     if (!tc && !li_attention_prefill_accepts(nh, nkv, dh, page_size)) return 0;
@@ -59,17 +59,20 @@ static int attention_portions(const void* qkv, void* out, const void* kcache, co
     *done = true;
     if (tc)
         return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                    num_pages, scale, window, max_q_len, split, stream);
+                                    num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, stream);
     return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                 num_pages, scale, window, max_q_len, split, stream);
 }
 
 // singles: how many sequences of the step have one token beside longer ones (0: none; negative: not known, there may be).
+// units (may be null): the work list of the kernel for long portions (attention_tcgen05.cu), with the number of entries to
+// launch when the single tokens are another kernel's and when they are not.
 LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype,
                                  const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens,
                                  const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
                                  int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
-                                 const int* old_lens, int singles, cudaStream_t stream) {
+                                 const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
+                                 cudaStream_t stream) {
     if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
     if (T == 0) return 0;
     if (dtype == LI_BF16) {
@@ -78,7 +81,8 @@ LI_EXPORT int li_paged_attention(const void* qkv, void* out, const void* kcache,
                                        num_pages, scale, window, max_ctx_len, S, stream);
         bool done = false;
         const int rc = attention_portions(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                          num_pages, scale, window, max_q_len, max_ctx_len, old_lens, singles, &done, stream);
+                                          num_pages, scale, window, max_q_len, max_ctx_len, old_lens, singles, units, slots_portions, slots_all,
+                                          &done, stream);
         if (rc || done) return rc;
     }
     return li_attention_generic(qkv, out, kcache, vcache, dtype, block_table, max_blocks, seq_of_token, positions, T, nh, nkv, dh,
@@ -95,7 +99,8 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
                                       const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens,
                                       const int* seq_of_token, const int* positions, int T, int S, int nh, int nkv, int dh,
                                       int page_size, int num_pages, float scale, int window, int max_q_len, int max_ctx_len,
-                                      const int* old_lens, int singles, cudaStream_t stream) {
+                                      const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
+                                      cudaStream_t stream) {
     if (int rc = validate(T, S, nh, nkv, dh, page_size, window)) return rc;
     if (T == 0) return 0;
     if (which == 0)
@@ -123,7 +128,7 @@ LI_EXPORT int li_paged_attention_with(int which, const void* qkv, void* out, con
             return li_attention_prefill(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
                                         num_pages, scale, window, max_q_len, split, stream);
         return li_attention_tcgen05(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, dh, page_size,
-                                    num_pages, scale, window, max_q_len, split, stream);
+                                    num_pages, scale, window, max_q_len, split, units, split ? slots_portions : slots_all, stream);
     }
     return li_fail("attention: unknown implementation %d", which);
 }

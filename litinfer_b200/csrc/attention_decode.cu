@@ -34,7 +34,7 @@
 
 namespace {
 
-constexpr int kWholeFrom = 120;        // (sequences x kv heads) from which a CTA takes a whole context
+constexpr int kWholeFrom = 60;         // (sequences x kv heads) from which a CTA takes a whole context (measured at a context of 2,048: 32 x 2 is faster whole, 24 x 2 split)
 
 struct Workspace {
     float* buf = nullptr;
@@ -173,7 +173,8 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     // `expected`: how many of the S sequences are this kernel's (a step may hold portions beside them, and a captured step
     // is padded with empty sequences): that count, not S, says whether one CTA per sequence and kv head fills the GPU
-    if ((long long)(expected > 0 && expected < S ? expected : S) * nkv >= kWholeFrom) {
+    static const int whole_from = getenv("LITINFER_B200_DECODE_WHOLE_FROM") ? atoi(getenv("LITINFER_B200_DECODE_WHOLE_FROM")) : kWholeFrom;
+    if ((long long)(expected > 0 && expected < S ? expected : S) * nkv >= whole_from) {
         // one CTA per (sequence, kv head) fills the GPU: no split of the context
         constexpr int W = 8, KB = DH <= 128 ? 32 : 16;
         const size_t wsmem = (2 * W * 16 + (size_t)W * G * DH) * sizeof(float);

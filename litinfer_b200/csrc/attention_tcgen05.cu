@@ -42,6 +42,8 @@ constexpr int kRows = 128;          // tokens per CTA
 constexpr int kKeys = 128;          // keys per tile
 constexpr int kThreads = 352;        // warp 0 loads keys (and the queries), warp 1 issues the products, warps 2-9 softmax, warp 10 loads values
 constexpr int kBuffers = 3;
+constexpr int kPartTiles = 2;        // fewest key tiles a CTA takes when a tile of tokens is shared out
+constexpr int kMultiprocessors = 148;
 
 template <int DH>
 struct __align__(1024) Smem {
@@ -50,6 +52,8 @@ struct __align__(1024) Smem {
     unsigned long long q_full, p_full[2], pv_full[2];      // P written / P V done, by tile parity
     unsigned long long s_full[2], mx_full[2];
     float mx[2][2][kRows];                           // [tile parity][half of the keys][row]: maxima, exchanged between a row's two threads
+    int is_last;                                     // of the CTAs that share a tile of tokens, this one finished last
+    int failed;                                      // a softmax thread gave up waiting
     unsigned long long k_full[kBuffers], k_empty[kBuffers], v_full[kBuffers], v_empty[kBuffers];
     unsigned tmem_base;
 };
@@ -65,7 +69,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
                             int max_blocks, const int* __restrict__ q_start, const int* __restrict__ ctx_lens, int nh, int nkv,
-                            int page_size, int num_pages, float scale, int window, int skip_single, int* __restrict__ error_flag, int trace) {
+                            int page_size, int num_pages, float scale, int window, int skip_single, int* __restrict__ error_flag, int trace,
+                            const int* __restrict__ units, float* __restrict__ partial, unsigned* __restrict__ counters) {
     extern __shared__ unsigned char smem_raw[];
     Smem<DH>& sm = *reinterpret_cast<Smem<DH>*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // the tiles want 1024-byte alignment; with head_dim 128 there is not a whole kilobyte to spare for it
@@ -75,11 +80,23 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
     }
     constexpr int kPanels = DH / 64;
     constexpr unsigned kTmemCols = 512;              // S of two tiles: 128 columns each; O: up to 128; Q: up to 64
-    // CTAs start in the order x, y, z: all heads of a sequence's last tile of tokens (which sees the most keys) first, then
-    // all heads of the tile before it, and so on, so that the long CTAs do not start late
-    const int s = blockIdx.z, h = blockIdx.x;
+    // What this CTA works on.  With a work list (`units`, made on the host with the step's other metadata: two counts, two
+    // unused words, then per entry sequence, tile of tokens, part | parts << 8, unused; heaviest first, the parts of a tile
+    // next to each other) blockIdx.y is an entry; entries past the count (the first: portions of two tokens and more,
+    // the second: all) are not there.  Without one the grid is (head, tile of tokens, sequence), the last tiles (which see
+    // the most keys) first, all heads of a tile together, so that the long CTAs do not start late.
+    const int h = blockIdx.x;
+    int s, tile, part = 0, parts_asked = 1, first_entry = 0;
+    if (units) {
+        const int u = blockIdx.y;
+        if (u >= units[skip_single ? 0 : 1]) return;
+        const int4 e = *reinterpret_cast<const int4*>(units + 4 + 4 * u);
+        s = e.x, tile = e.y, part = e.z & 0xff, parts_asked = partial ? (e.z >> 8) : 1, first_entry = u - part;
+    } else {
+        s = blockIdx.z, tile = (int)gridDim.y - 1 - (int)blockIdx.y;
+    }
     const int tok0 = q_start[s], n = q_start[s + 1] - tok0;
-    const int cta_i0 = ((int)gridDim.y - 1 - (int)blockIdx.y) * kRows;
+    const int cta_i0 = tile * kRows;
     if (cta_i0 >= n || (skip_single && n == 1)) return;          // skip_single: sequences of one token are another kernel's
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ctx = ctx_lens[s];
@@ -87,10 +104,30 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
     const int cta_rows = min(kRows, n - cta_i0);
     const int p_first = ctx - n + cta_i0, p_last = p_first + cta_rows - 1;
     const int key_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
-    const int kt_first = key_lo / kKeys, kt_last = p_last / kKeys;
-    const int ntiles = kt_last - kt_first + 1;
+    // The key tiles of this tile of tokens.  When the step has so few tiles of tokens that multiprocessors would stand idle,
+    // the work list shares them out among several CTAs (entries with parts > 1), at least kPartTiles each, and the last
+    // CTA to finish adds the partial results up.  The workspace has room for one partial result per multiprocessor.
+    const int tiles_all = p_last / kKeys - key_lo / kKeys + 1;
+    int parts = min(parts_asked, (tiles_all + kPartTiles - 1) / kPartTiles);
+    if ((first_entry + parts_asked) * nh > kMultiprocessors) parts = 1;
+    if (part >= parts) return;
+    const int kt_first = key_lo / kKeys + (int)((long long)part * tiles_all / parts);
+    const int ntiles = key_lo / kKeys + (int)((long long)(part + 1) * tiles_all / parts) - kt_first;
+    // the page of each 16-key block of a tile, for the lanes of the loading warps; the first tile's as early as possible
+    // (the table and the lengths were written before the step's first kernel started, so they may be read before pdl_wait)
+    const int* bt = block_table + (size_t)s * max_blocks;
+    auto look_up = [&](int j, int& page, int& off) {
+        const int key = (kt_first + j) * kKeys + (lane & 7) * 16;
+        const int idx = key / page_size;
+        page = (j < ntiles && key < ctx && idx < max_blocks) ? bt[idx] : 0;
+        if (page < 0 || page >= num_pages) page = 0;
+        off = key - idx * page_size;
+    };
+    int page = 0, off = 0;
+    if (warp == 0 || warp == 10) look_up(0, page, off);
 
     if (threadIdx.x == 0) {
+        sm.failed = 0;
         mbar_init(&sm.q_full, 256);
         mbar_init(&sm.s_full[0], 1);
         mbar_init(&sm.s_full[1], 1);
@@ -132,16 +169,6 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
         // issued) and issues that block's copies, so that the lookups and the issue of a tile's 8 or 16 copies run side by
         // side instead of one after another in a single thread.  Lane 0 waits for the buffer and announces the bytes.
         const bool keys = warp == 0;
-        const int* bt = block_table + (size_t)s * max_blocks;
-        auto look_up = [&](int j, int& page, int& off) {
-            const int key = (kt_first + j) * kKeys + (lane & 7) * 16;
-            const int idx = key / page_size;
-            page = (j < ntiles && key < ctx && idx < max_blocks) ? bt[idx] : 0;
-            if (page < 0 || page >= num_pages) page = 0;
-            off = key - idx * page_size;
-        };
-        int page, off;
-        look_up(0, page, off);
         bool ok = true;
         // keys of a tile as soon as the product S two tiles back has read its buffer, values once P V has
         for (int j = 0; j < ntiles; ++j) {
@@ -357,9 +384,54 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
             ok = mbar_wait(&sm.mx_full[jx & 1], (jx >> 1) & 1);
             if (ok) l = sm.mx[jx & 1][0][r] + sm.mx[jx & 1][1][r];
         }
+        bool store = valid;
+        if (parts > 1) {                                          // the same for the whole CTA; every softmax thread takes part, failed or not
+            // Shared tile of tokens: this CTA's output (unnormalised, against its maximum m), m and the sum l go to the
+            // workspace, [column][row] so that a warp writes consecutive words.  The CTA that arrives last adds all parts
+            // up in their order, whichever it is itself, so the result does not depend on the order of arrival.
+            constexpr int kPartFloats = kRows * (DH + 2);
+            const size_t unit = (size_t)first_entry * nh + h;      // the tile's first entry stands for it
+            if (ok) {
+                float* mine = partial + ((size_t)(first_entry + part) * nh + h) * kPartFloats;
+#pragma unroll
+                for (int d = 0; d < HD; ++d) mine[(half * HD + d) * kRows + r] = o[d];
+                if (half == 0) {
+                    mine[DH * kRows + r] = m;
+                    mine[(DH + 1) * kRows + r] = l;
+                }
+                __threadfence();
+            } else {
+                sm.failed = 1;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (warp == 2 && lane == 0) sm.is_last = (!sm.failed && atomicAdd(&counters[unit], 1u) == (unsigned)(parts - 1)) ? 1 : 0;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (sm.failed) ok = false;
+            if (ok && sm.is_last) {
+                __threadfence();
+                const float* first = partial + unit * kPartFloats;
+                const size_t stride = (size_t)nh * kPartFloats;     // from one part of the tile to the next
+                float m_all = -INFINITY;
+                for (int q = 0; q < parts; ++q) m_all = fmaxf(m_all, __ldcg(first + q * stride + DH * kRows + r));
+                const float ref = (m_all == -INFINITY) ? 0.0f : m_all;
+#pragma unroll
+                for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+                l = 0.0f;
+                for (int q = 0; q < parts; ++q) {
+                    const float* theirs = first + q * stride;
+                    const float w = exp2f(__ldcg(theirs + DH * kRows + r) - ref);
+                    l += __ldcg(theirs + (DH + 1) * kRows + r) * w;
+#pragma unroll
+                    for (int d = 0; d < HD; ++d) o[d] += __ldcg(theirs + (half * HD + d) * kRows + r) * w;
+                }
+                if (warp == 2 && lane == 0) counters[unit] = 0;           // ready for the next launch
+            } else {
+                store = false;                                    // the last CTA writes the tokens' output
+            }
+        }
         if (!ok) {
             if (lane == 0) atomicExch(error_flag, 13);
-        } else if (valid) {
+        } else if (store) {
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             bf16* dst = out + ((size_t)(tok0 + cta_i0 + r) * nh + h) * DH + half * HD;
 #pragma unroll
@@ -383,10 +455,43 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
     }
 }
 
+// Workspace of the CTAs that share a tile of tokens: their partial outputs and a counter per tile and head.  One per process,
+// of a fixed size (as many partial outputs of head_dim 128 as there are multiprocessors: 10 MB), allocated at the first launch
+// that wants it; launches that use it are in stream order (the library runs a model's step on one stream).
+struct SplitSpace {
+    float* partial = nullptr;
+    unsigned* counters = nullptr;
+    // false if there is none and none can be made now (a stream capture is under way): the launch then shares nothing out
+    bool ready(cudaStream_t stream, int* rc) {
+        *rc = 0;
+        if (partial) return true;
+        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(stream, &st) != cudaSuccess || st != cudaStreamCaptureStatusNone) {
+            cudaGetLastError();
+            return false;
+        }
+        const size_t bytes = (size_t)kMultiprocessors * kRows * (128 + 2) * sizeof(float);
+        cudaError_t e = cudaMalloc((void**)&partial, bytes);
+        if (e == cudaSuccess) e = cudaMalloc((void**)&counters, kMultiprocessors * sizeof(unsigned));
+        if (e == cudaSuccess) e = cudaMemset(counters, 0, kMultiprocessors * sizeof(unsigned));
+        if (e != cudaSuccess) {
+            *rc = li_fail("attention (tcgen05): cannot allocate %zu bytes of workspace: %s", bytes, cudaGetErrorString(e));
+            partial = nullptr;
+            return false;
+        }
+        return true;
+    }
+};
+
+SplitSpace& split_space() {
+    static SplitSpace space;
+    return space;
+}
+
 template <int DH>
 int launch(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks, const int* q_start,
            const int* ctx_lens, int T, int S, int nh, int nkv, int page_size, int num_pages, float scale, int window, int max_q_len,
-           int skip_single, cudaStream_t stream) {
+           int skip_single, const int* units, int unit_slots, cudaStream_t stream) {
     EncodeTiledFn encode = nullptr;
     int *err_host = nullptr, *err_dev = nullptr;
     if (int rc = setup(&encode, &err_host, &err_dev)) return rc;
@@ -404,10 +509,24 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
         raised = true;
     }
     LI_REQUIRE(S <= 65535 && ceil_div(max_q_len, kRows) <= 65535, "attention (tcgen05): batch %d or portions of %d tokens too large for one launch", S, max_q_len);
-    dim3 grid(nh, ceil_div(max_q_len, kRows), S);
+    // With a work list the grid is (head, entry); a step with few tiles of tokens (a portion of a prompt behind a long
+    // context) would leave multiprocessors idle while each CTA walks many key tiles, so its list shares the key tiles of
+    // a tile of tokens out among as many CTAs as still run all at once.  (Measured: with more CTAs than multiprocessors
+    // the fixed cost of the extra CTAs outweighs the shorter walks, 29 -> 38 us for 2,048 tokens x 12 heads.)
+    SplitSpace& space = split_space();
+    float* partial = nullptr;
+    if (units) {
+        LI_REQUIRE(unit_slots >= 0 && unit_slots <= 65535, "attention (tcgen05): a work list of %d entries", unit_slots);
+        if (unit_slots == 0) return 0;
+        int rc = 0;
+        if (space.ready(stream, &rc)) partial = space.partial;
+        if (rc) return rc;
+    }
+    const dim3 grid = units ? dim3(nh, unit_slots, 1) : dim3(nh, ceil_div(max_q_len, kRows), S);
     static const int trace = getenv("LITINFER_B200_ATTN_TRACE") ? 1 : 0;
     li_launch_pdl(prefill_attention_tc_kernel<DH>, grid, dim3(kThreads), smem, stream, (const bf16*)qkv, row_elems, map_k, map_v, (bf16*)out, block_table, max_blocks,
-                  q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, skip_single, err_dev, trace);
+                  q_start, ctx_lens, nh, nkv, page_size, num_pages, scale, window, skip_single, err_dev, trace, units, partial,
+                  space.counters);
     return li_check_launch("attention (tcgen05)");
 }
 
@@ -420,13 +539,13 @@ bool li_attention_tcgen05_accepts(const void* qkv, const void* kcache, const voi
 
 int li_attention_tcgen05(const void* qkv, void* out, const void* kcache, const void* vcache, const int* block_table, int max_blocks,
                          const int* q_start, const int* ctx_lens, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages,
-                         float scale, int window, int max_q_len, int skip_single, cudaStream_t stream) {
+                         float scale, int window, int max_q_len, int skip_single, const int* units, int unit_slots, cudaStream_t stream) {
     LI_REQUIRE(li_attention_tcgen05_accepts(qkv, kcache, vcache, nh, nkv, dh, page_size),
                "attention (tcgen05): refuses heads=%d/%d head_dim=%d page=%d (head_dim 64 or 128, pages a multiple of 16)", nh, nkv, dh, page_size);
     LI_REQUIRE(scale > 0.0f, "attention (tcgen05): the scale must be positive");
     if (dh == 64)
         return launch<64>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
-                          window, max_q_len, skip_single, stream);
+                          window, max_q_len, skip_single, units, unit_slots, stream);
     return launch<128>(qkv, out, kcache, vcache, block_table, max_blocks, q_start, ctx_lens, T, S, nh, nkv, page_size, num_pages, scale,
-                       window, max_q_len, skip_single, stream);
+                       window, max_q_len, skip_single, units, unit_slots, stream);
 }

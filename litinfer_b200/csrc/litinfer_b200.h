@@ -23,18 +23,22 @@ int li_check_device();
 /* Causal grouped-query attention of a step's tokens over the paged cache.  qkv [T, (nh + 2 nkv) dh] with q
  * rotated; out [T, nh dh]; token t of sequence s at position p sees the cached keys max(0, p - window + 1) .. p
  * through block_table[s]; singles: how many sequences of a step with longer portions have one token (negative: not
- * known). */
+ * known); units (may be NULL): the work list of the kernel for long portions, made with the step's metadata (two counts,
+ * two unused words, then per entry: sequence, tile of 128 tokens, part | parts << 8, unused), with the number of entries
+ * to launch when the single tokens go to the decode kernel and when they do not. */
 int li_paged_attention(const void* qkv, void* out, const void* kcache, const void* vcache, int dtype, const int*
     block_table, int max_blocks, const int* q_start, const int* ctx_lens, const int* seq_of_token, const int*
     positions, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window, int
-    max_q_len, int max_ctx_len, const int* old_lens, int singles, cudaStream_t stream);
+    max_q_len, int max_ctx_len, const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
+    cudaStream_t stream);
 
 /* The same through one implementation: 0 general, 1 decode, 2 mma.sync tiles, 3 tcgen05 tiles (tests and
  * measurements). */
 int li_paged_attention_with(int which, const void* qkv, void* out, const void* kcache, const void* vcache, int dtype,
     const int* block_table, int max_blocks, const int* q_start, const int* ctx_lens, const int* seq_of_token, const
     int* positions, int T, int S, int nh, int nkv, int dh, int page_size, int num_pages, float scale, int window, int
-    max_q_len, int max_ctx_len, const int* old_lens, int singles, cudaStream_t stream);
+    max_q_len, int max_ctx_len, const int* old_lens, int singles, const int* units, int slots_portions, int slots_all,
+    cudaStream_t stream);
 
 /* ---- decode_step.cu: a decode step as one persistent kernel (decode_step.h has the structures) ---- */
 struct LiDecodeStep;

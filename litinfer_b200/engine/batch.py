@@ -9,7 +9,8 @@ copy; LitInfer rebuilds and uploads its block table per layer
 
 Layout of the packed buffer (all int32): token_ids[T] | positions[T] |
 seq_of_token[T] | q_start[S+1] | ctx_lens[S] | old_lens[S] | state_slots[S] |
-logit_rows[R] | per group: slot_mapping[T] | block_table[S * max_blocks].  With ``pad_seqs``
+logit_rows[R] | per group: slot_mapping[T] | block_table[S * max_blocks] | attn_units (steps with portions of prompts:
+the work list of the attention kernel for long portions, :func:`attention_units`).  With ``pad_seqs``
 the batch is padded to that many one-token items that write to the sink page
 and whose results nobody reads (a captured decode step has a fixed size); with
 ``pad_tokens`` to a fixed count of tokens, sequences and rows (a captured step
@@ -71,6 +72,10 @@ class StepContext:
     # how many sequences of a step with longer portions have one token (they can go to a decode kernel); negative: not
     # known (a captured step that may hold any)
     num_single: int = 0
+    # steps with portions of prompts: the attention work list (attention_units) and how many of its entries to launch
+    # when single tokens go to a kernel of their own / when they do not
+    attn_units: Optional[torch.Tensor] = None
+    attn_unit_slots: tuple = (0, 0)
     # what parts make once per step and share between the layers (keyed by the part), e.g. a table of rotation angles
     scratch: dict = field(default_factory=dict)
 
@@ -116,10 +121,51 @@ def split_into_tokens(items: Sequence[StepItem]) -> List[StepItem]:
 _FIELDS = ("token_ids", "positions", "seq_of_token", "q_start", "ctx_lens", "old_lens", "state_slots", "logit_rows")
 
 
+TOKEN_TILE = 128          # tokens of a portion that one CTA of the attention kernel for long portions takes
+KEY_TILE = 128            # keys it walks at a time
+MIN_PART_TILES = 2        # fewest key tiles a CTA takes when a tile of tokens is shared out
+MAX_PARTS = 8             # most CTAs that share a tile of tokens
+
+
+def attention_units(q_lens: Sequence[int], ctx_lens: Sequence[int], work_budget: int = 0) -> np.ndarray:
+    """The work list of the attention kernel for long portions (csrc/attention_tcgen05.cu): one entry per tile of 128
+    tokens of every sequence of the step, the tile that walks the most keys first (the kernel's time is that of its
+    longest CTA, so the long ones must not start late).  ``work_budget``: how many entries keep every multiprocessor
+    busy at once (multiprocessors // CTAs per entry).  A step with at most half that many tiles of tokens (a portion
+    of a prompt behind a long context) has each tile's keys shared out among up to MAX_PARTS entries of at least
+    MIN_PART_TILES key tiles, next to each other in the list; the kernel adds their partial results up.
+
+    int32: [entries of portions (two tokens and more), all entries, 0, 0, then per entry: sequence, tile,
+    part | parts << 8, 0].  The sequences of one token come last: they are launched only where no decode kernel takes
+    them."""
+    tiles, singles = [], []
+    for s, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+        if n == 1:
+            singles.append(s)
+        for t in range(-(-n // TOKEN_TILE) if n > 1 else 0):
+            last = c - n + min(n, (t + 1) * TOKEN_TILE) - 1          # position of the tile's last token = the last key it sees
+            tiles.append((last // KEY_TILE + 1, s, t))
+    nsplit = 1
+    if tiles and 2 * len(tiles) <= work_budget:
+        nsplit = min(MAX_PARTS, work_budget // len(tiles))
+    entries = []
+    weighed = [(k, s, t, max(1, min(nsplit, -(-k // MIN_PART_TILES)))) for k, s, t in tiles]
+    weighed.sort(key=lambda e: -(e[0] / e[3]))
+    for _, s, t, parts in weighed:
+        entries.extend((s, t, part | (parts << 8), 0) for part in range(parts))
+    portions = len(entries)
+    entries.extend((s, 0, 1 << 8, 0) for s in singles)
+    out = np.zeros(4 + 4 * len(entries), dtype=np.int32)
+    out[0], out[1] = portions, len(entries)
+    if entries:
+        out[4:] = np.asarray(entries, dtype=np.int32).reshape(-1)
+    return out
+
+
 @functools.lru_cache(maxsize=512)
-def _fields(T: int, S: int, R: int, G: int, mb: int):
-    """Where each field starts in the packed buffer (16-byte aligned starts), the buffer's length, and the starts as
-    the array the host runtime takes."""
+def _fields(T: int, S: int, R: int, G: int, mb: int, U: int = 0):
+    """Where each field starts in the packed buffer (16-byte aligned starts), the buffer's length (the host runtime's
+    fields, then ``U`` words of attention work list), and the starts as the array the host runtime takes."""
     fields = {}
     off = 0
     for name, n in zip(_FIELDS, (T, T, T, S + 1, S, S, S, R)):
@@ -131,6 +177,9 @@ def _fields(T: int, S: int, R: int, G: int, mb: int):
         fields[f"block_table{gid}"] = (off, S * mb)
         off += _round_up(max(S * mb, 1), 4)
     starts = np.asarray([o for o, _ in fields.values()], dtype=np.int32)
+    if U:
+        fields["attn_units"] = (off, U)
+        off += _round_up(U, 4)
     return fields, off, starts
 
 
@@ -140,7 +189,7 @@ def _ints(values) -> np.ndarray:
 
 def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int, pad_seqs: int = 0,
               max_blocks: Optional[int] = None, tokens_of_one_request: bool = False, pad_tokens: int = 0,
-              pad_rows: int = 0):
+              pad_rows: int = 0, work_budget: int = 0):
     """Host side: validate the items and fill the packed int32 array (the host runtime does both, in C++).
 
     Returns (array, layout) where layout maps field name -> (offset, length) and
@@ -151,6 +200,8 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
     the padding tokens; it starts at position 0, writes to the sink page and sees nothing else; the real rows come
     first among the logit rows, and ``layout["R_real"]`` says how many they are.  Without ``pad_tokens`` the padding
     sequences hold one token each and want its row.
+    ``work_budget``: see :func:`attention_units`; a step with portions of prompts carries that list (a padded one with
+    room for the most entries its shape can have).
     """
     S_real = len(items)
     if S_real == 0:
@@ -178,8 +229,20 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
         T, R = T_real + S - S_real, R_real + S - S_real
     G = len(manager.groups)
     mb = max(need_blocks, max_blocks or 0, 1)
-    fields, total, offsets = _fields(T, S, R, G, mb)
+    units = None
+    lens_all, ctx_all = list(q_lens), [st + n for st, n in zip(starts, q_lens)]
+    if pad_tokens and rest > 0:                            # the padding tokens are the last sequence's, from position 0
+        lens_all += [0] * (S - S_real - 1) + [rest]
+        ctx_all += [0] * (S - S_real - 1) + [rest]
+    if max(lens_all) > 1:
+        units = attention_units(lens_all, ctx_all, work_budget)
+        # a padded step is replayed from a captured launch, whose list has room for any step of its shape
+        U = 4 + 4 * (pad_tokens // TOKEN_TILE + S + work_budget) if pad_tokens else len(units)
+    fields, total, offsets = _fields(T, S, R, G, mb, U if units is not None else 0)
     buf = np.zeros(total, dtype=np.int32)
+    if units is not None:
+        o = fields["attn_units"][0]
+        buf[o:o + len(units)] = units
     if T_real == S_real:
         tokens = _ints([it.tokens[0] for it in items])
     else:
@@ -198,6 +261,7 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
 
     layout = dict(fields=fields, T=T, S=S, R=R, R_real=int(info[0]), G=G, max_blocks=mb, singles=int(info[3]),
                   max_q_len=int(info[1]), max_ctx_len=int(info[2]),
+                  unit_slots=(int(units[0]), int(units[1])) if units is not None else (0, 0),
                   q_start=host("q_start"), ctx_lens=host("ctx_lens"), state_slots=host("state_slots"))
     return buf, layout
 
@@ -218,4 +282,5 @@ def context_from(device_buf: torch.Tensor, layout, page_size: int) -> StepContex
         q_start=view("q_start"), ctx_lens=view("ctx_lens"), state_slots=view("state_slots"), old_lens=view("old_lens"),
         logit_rows=view("logit_rows"), groups=groups,
         max_q_len=layout["max_q_len"], max_ctx_len=layout["max_ctx_len"], num_single=layout.get("singles", 0),
+        attn_units=view("attn_units") if "attn_units" in f else None, attn_unit_slots=tuple(layout.get("unit_slots", (0, 0))),
         host_q_start=layout["q_start"], host_ctx_lens=layout["ctx_lens"], host_state_slots=layout["state_slots"])

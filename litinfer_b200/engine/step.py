@@ -70,6 +70,17 @@ class ModelRunner:
         # a captured attention launch has to cover the longest context it may meet (its grid and workspace
         # are sized for it), so that length is capped; steps with a longer context run without a graph
         self.max_context = min(int(max_context or model.spec.max_position_embeddings), self.GRAPH_CONTEXT_CAP)
+        # entries of the attention work list that keep every multiprocessor busy at once (engine.batch.attention_units)
+        self.work_budget = 0
+        if self.device.type == "cuda":
+            def widths(part):
+                yield getattr(part, "ctas_per_work_unit", 0)
+                for child in part.parts():
+                    yield from widths(child)
+
+            widest = max((w for b in model.blocks for w in widths(b)), default=0)
+            if widest:
+                self.work_budget = torch.cuda.get_device_properties(self.device).multi_processor_count // widest
         self._graphs: Dict[int, _DecodeGraph] = {}
         # shapes of steps with portions of prompts: how often each came, and the captured ones; a shape is captured
         # when it comes for the (step_graph_after + 1)-th time, since a capture costs three plain runs
@@ -140,7 +151,7 @@ class ModelRunner:
         elif self.use_graphs and not decode_only and (shape := self._step_shape(items)) is not None:
             logits = self._step_shape_graph(items, shape)
         else:
-            buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size)
+            buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size, work_budget=self.work_budget)
             ctx = context_from(self._upload(buf), layout, self.manager.page_size)
             if token_source is not None:
                 ctx.token_ids[:len(items)].copy_(token_source)
@@ -201,7 +212,7 @@ class ModelRunner:
         Tp, Sp, Rp, singles = shape
         max_blocks = -(-self.max_context // self.manager.page_size)
         buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size, pad_seqs=Sp, max_blocks=max_blocks,
-                                pad_tokens=Tp, pad_rows=Rp)
+                                pad_tokens=Tp, pad_rows=Rp, work_budget=self.work_budget)
         g = self._step_graphs.get(shape)
         if g is None:
             # the attention launch is sized for the longest portion and the longest context the shape may hold
@@ -260,6 +271,9 @@ class ModelRunner:
         lay["max_ctx_len"] = self.max_context
         lay["max_q_len"] = max_q_len
         lay["singles"] = singles
+        if "attn_units" in lay["fields"]:                  # the captured launch covers every entry the list has room for
+            room = (lay["fields"]["attn_units"][1] - 4) // 4
+            lay["unit_slots"] = (room, room)
         ctx = context_from(meta, lay, self.manager.page_size)
         stream = torch.cuda.Stream(self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))

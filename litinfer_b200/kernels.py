@@ -14,7 +14,7 @@ from __future__ import annotations
 
 import ctypes
 import threading
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -376,7 +376,8 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
                     seq_of_token: torch.Tensor, positions: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
                     max_q_len: int, max_ctx_len: int, implementation: Optional[str] = None,
-                    old_lens: Optional[torch.Tensor] = None, singles: int = 0) -> None:
+                    old_lens: Optional[torch.Tensor] = None, singles: int = 0,
+                    units: Optional[torch.Tensor] = None, unit_slots: Tuple[int, int] = (0, 0)) -> None:
     """Causal grouped-query attention of the step's tokens over the paged cache.
 
     Queries are the first ``num_heads * head_dim`` columns of ``qkv`` (already
@@ -387,7 +388,9 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     ``old_lens`` (int32 ``[S]``): how many keys of each sequence were in the cache before this step; needed when
     several sequences of the step are tokens of one request (None: all but each sequence's last key).
     ``singles``: how many sequences of a step with longer portions have one token (negative: not known).  They then
-    go to the decode kernel, the rest to the kernel for portions (bfloat16)."""
+    go to the decode kernel, the rest to the kernel for portions (bfloat16).
+    ``units`` (int32, from ``engine.batch.attention_units``): the work list of the kernel for long portions, with
+    ``unit_slots`` = how many entries to launch when the single tokens are the decode kernel's, and when not."""
     T = qkv.shape[0]
     S = ctx_lens.shape[0]
     _need(qkv, "qkv", None, (T, (num_heads + 2 * num_kv_heads) * head_dim))
@@ -408,10 +411,15 @@ def paged_attention(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         raise KernelError(f"block table of {block_table.shape[1]} pages cannot cover a context of {max_ctx_len}")
     if old_lens is not None:
         _need(old_lens, "old_lens", torch.int32, (S,))
+    if units is not None:
+        _need(units, "attention work list", torch.int32)
+        if units.numel() < 4 + 4 * max(unit_slots) or units.data_ptr() % 16:
+            raise KernelError(f"attention work list of {units.numel()} words cannot hold {max(unit_slots)} entries (or is not 16-byte aligned)")
     args = (_p(qkv), _p(out), _p(k_cache), _p(v_cache), _i(_dt(qkv)), _p(block_table), _i(block_table.shape[1]),
             _p(q_start), _p(ctx_lens), _p(seq_of_token), _p(positions), _i(T), _i(S),
             _i(num_heads), _i(num_kv_heads), _i(head_dim), _i(page_size), _i(pages), _f(scale),
-            _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _p(old_lens), _i(int(singles)), _stream(out))
+            _i(0 if window is None else int(window)), _i(max_q_len), _i(max_ctx_len), _p(old_lens), _i(int(singles)),
+            _p(units), _i(int(unit_slots[0])), _i(int(unit_slots[1])), _stream(out))
     if implementation is None:
         _check(library().li_paged_attention(*args), "paged_attention")
     else:

@@ -33,6 +33,7 @@ class PagedAttention(Mixer):
         super().__init__(spec, prefix, dtype, device)
         self.hidden = int(spec["hidden_size"])
         self.num_heads = int(spec["num_heads"])
+        self.ctas_per_work_unit = self.num_heads           # the kernel for long portions runs one CTA per head and entry
         self.num_kv_heads = int(spec["num_kv_heads"])
         self.head_dim = int(spec["head_dim"])
         self.scale = float(spec["scale"])
@@ -91,5 +92,6 @@ class PagedAttention(Mixer):
         K.paged_attention(
             qkv, o, cache.k, cache.v, view.block_table, ctx.q_start, ctx.ctx_lens, ctx.seq_of_token, ctx.positions,
             self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window,
-            ctx.max_q_len, ctx.max_ctx_len, old_lens=ctx.old_lens, singles=ctx.num_single)
+            ctx.max_q_len, ctx.max_ctx_len, old_lens=ctx.old_lens, singles=ctx.num_single,
+            units=ctx.attn_units, unit_slots=ctx.attn_unit_slots)
         return o

@@ -167,6 +167,9 @@ class Carry:
 
 class Mixer(Part):
     takes_deferred = False           # whether forward accepts a Deferred activation as h
+    # how many CTAs one entry of the step's attention work list becomes in this mixer's kernel (0: it does not read the
+    # list); the step function sizes the list so that the entries of all such mixers fill the GPU (engine.batch.attention_units)
+    ctas_per_work_unit = 0
 
     def cache_requirement(self):
         """PagedKV, FixedState or None."""

@@ -139,9 +139,10 @@ def rope_table(positions, denominators, out):
 
 
 def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
-                    num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None, singles=0):
-    # old_lens only tells a kernel which keys it may read early, singles which kernel takes which sequence; the result
-    # does not depend on them
+                    num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None, singles=0,
+                    units=None, unit_slots=(0, 0)):
+    # old_lens only tells a kernel which keys it may read early, singles which kernel takes which sequence, units how a
+    # kernel shares its work out; the result does not depend on them
     T = qkv.shape[0]
     page_size = k_cache.shape[2]
     group = num_heads // num_kv_heads
@@ -166,7 +167,7 @@ def paged_attention(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, 
 
 def paged_attention_dense(qkv, out, k_cache, v_cache, block_table, q_start, ctx_lens, seq_of_token, positions,
                           num_heads, num_kv_heads, head_dim, scale, window, max_q_len, max_ctx_len, implementation=None, old_lens=None,
-                          singles=0):
+                          singles=0, units=None, unit_slots=(0, 0)):
     """The same formula as :func:`paged_attention`, a sequence at a time instead of a token and a head at a time (for
     contexts of thousands of keys): scores of all the sequence's tokens against all its keys in float32, keys outside
     [p - window + 1, p] masked, softmax, weighted sum."""

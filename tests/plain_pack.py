@@ -12,9 +12,43 @@ def _round_up(x: int, m: int) -> int:
     return -(-x // m) * m
 
 
+def attention_units(q_lens, ctx_lens, work_budget=0):
+    """The attention work list, restated: every 128 tokens of a sequence of two tokens or more are a tile; a tile whose
+    last token stands at position p walks p // 128 + 1 key tiles.  If the tiles are at most half of ``work_budget``, every
+    tile is cut into min(8, work_budget // tiles, ceil(key tiles / 2)) parts.  Entries: tiles by key tiles per part,
+    most first (ties in the order found), a tile's parts in a row; then the sequences of one token."""
+    found = []
+    for seq in range(len(q_lens)):
+        n, c = q_lens[seq], ctx_lens[seq]
+        if n < 2:
+            continue
+        tile = 0
+        while tile * 128 < n:
+            last_token = min(n, tile * 128 + 128) - 1
+            position = c - n + last_token
+            found.append([position // 128 + 1, seq, tile])
+            tile += 1
+    cut = 1
+    if found and len(found) * 2 <= work_budget:
+        cut = min(8, work_budget // len(found))
+    for f in found:
+        f.append(max(1, min(cut, (f[0] + 1) // 2)))
+    order = sorted(range(len(found)), key=lambda i: (-found[i][0] / found[i][3], i))
+    words = []
+    for i in order:
+        key_tiles, seq, tile, parts = found[i]
+        for part in range(parts):
+            words += [seq, tile, part + 256 * parts, 0]
+    portions = len(words) // 4
+    for seq in range(len(q_lens)):
+        if q_lens[seq] == 1:
+            words += [seq, 0, 256, 0]
+    return np.asarray([portions, len(words) // 4, 0, 0] + words, dtype=np.int32)
+
+
 def pack_step(items: Sequence, manager, vocab_size: int, pad_seqs: int = 0,
               max_blocks: Optional[int] = None, tokens_of_one_request: bool = False, pad_tokens: int = 0,
-              pad_rows: int = 0):
+              pad_rows: int = 0, work_budget: int = 0):
     """Host side: validate the items and fill the packed int32 array.
 
     Returns (array, layout) where layout maps field name -> (offset, length) and
@@ -102,7 +136,16 @@ def pack_step(items: Sequence, manager, vocab_size: int, pad_seqs: int = 0,
     for gid in range(G):
         place(f"slot_mapping{gid}", T)
         place(f"block_table{gid}", S * mb)
+    units = attention_units(q_lens, ctx.tolist(), work_budget) if max(q_lens) > 1 else None
+    if units is not None:
+        # a step padded to a shape keeps room for the most entries the shape can have
+        room = 4 + 4 * (pad_tokens // 128 + S + work_budget) if pad_tokens else len(units)
+        fields["attn_units"] = (off, room)
+        off += _round_up(room, 4)
     buf = np.zeros(off, dtype=np.int32)
+    if units is not None:
+        o = fields["attn_units"][0]
+        buf[o:o + len(units)] = units
 
     def put(name, arr):
         o, n = fields[name]
@@ -139,5 +182,6 @@ def pack_step(items: Sequence, manager, vocab_size: int, pad_seqs: int = 0,
         put(f"slot_mapping{gid}", sm)
     singles = sum(1 for q in q_lens[:S_real] if q == 1) if max(q_lens) > 1 else 0
     layout = dict(fields=fields, T=T, S=S, R=R, R_real=R_real, G=G, max_blocks=mb, singles=singles, max_q_len=max(q_lens), max_ctx_len=int(ctx.max()),
+                  unit_slots=(int(units[0]), int(units[1])) if units is not None else (0, 0),
                   q_start=q_start.tolist(), ctx_lens=ctx.tolist(), state_slots=slots.tolist())
     return buf, layout

@@ -280,6 +280,7 @@ def test_packed_steps_equal_the_plain_packer(seed, window):
         cases.append(dict(pad_seqs=S + 2, max_blocks=16, pad_tokens=T + 21, pad_rows=max(R, S + 2)))
         cases.append(dict(pad_seqs=S, max_blocks=16, pad_tokens=T, pad_rows=R + 1))
         for kw in cases:
+            kw = dict(kw, work_budget=rnd.choice([0, 3, 12, 40]))
             a, la = pack_step(items, m, vocab, **kw)
             b, lb = plain_pack.pack_step(items, m, vocab, **kw)
             assert np.array_equal(a, b), f"buffers differ for {kw}"

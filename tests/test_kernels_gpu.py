@@ -470,7 +470,8 @@ def make_attention_case(q_lens, ctx_lens, nh, nkv, dh, page, dtype, seed=0, extr
                 ctx_lens=list(ctx_lens), q_lens=list(q_lens), nh=nh, nkv=nkv, dh=dh, dtype=dtype)
 
 
-def run_attention_case(c, window, implementation=None, old_lens=None, singles=0, dense_reference=False):
+def run_attention_case(c, window, implementation=None, old_lens=None, singles=0, dense_reference=False, work_budget=None):
+    """``work_budget``: run with the attention work list that the step function would pack for this budget."""
     d = dev()
     page, nkv, dh = c["page"], c["nkv"], c["dh"]
     kc = torch.zeros(c["pages"], nkv, page, dh, dtype=c["dtype"])
@@ -488,9 +489,15 @@ def run_attention_case(c, window, implementation=None, old_lens=None, singles=0,
     ref = torch.empty_like(out)
     scale = 1.0 / math.sqrt(dh)
     tail = (c["nh"], nkv, dh, scale, window, max(c["q_lens"]), max(c["ctx_lens"]))
+    more = {}
+    if work_budget is not None:
+        from litinfer_b200.engine.batch import attention_units
+
+        units = attention_units(c["q_lens"], c["ctx_lens"], work_budget)
+        more = dict(units=torch.from_numpy(units).to(d), unit_slots=(int(units[0]), int(units[1])))
     K().paged_attention(args["qkv"], out, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
                         args["seq_of_token"], args["positions"], *tail, implementation=implementation,
-                        old_lens=None if old_lens is None else torch.tensor(old_lens, dtype=torch.int32, device=d), singles=singles)
+                        old_lens=None if old_lens is None else torch.tensor(old_lens, dtype=torch.int32, device=d), singles=singles, **more)
     reference = R.paged_attention_dense if dense_reference else R.paged_attention
     reference(args["qkv"], ref, args["k_cache"], args["v_cache"], args["block_table"], args["q_start"], args["ctx_lens"],
               args["seq_of_token"], args["positions"], *tail)
@@ -709,6 +716,34 @@ def test_attention_tcgen05_at_benchmark_lengths(heads):
                 pos = c["pos"][tok]
                 if window is None or pos - key < window:
                     _planted_value_comes_out(c, out, s, h, key, tok, f"heads={heads} q={q_lens} window={window}")
+    assert K().library().li_tcgen05_status() == 0
+
+
+@pytest.mark.parametrize("heads", [(12, 2, 128), (4, 4, 64), (28, 4, 128)])
+def test_attention_tcgen05_with_a_work_list(heads):
+    """The kernel for long portions driven by the step's work list: a portion behind a long context whose key tiles are
+    shared out among several CTAs (with a planted key in a late part, a window that cuts parts away, two portions at
+    once, single tokens beside them), and lists that share nothing out.  Twice in a row: the counters of the shared
+    tiles are left ready for the next launch."""
+    from litinfer_b200.engine.batch import attention_units
+
+    nh, nkv, dh = heads
+    budget = 148 // nh
+    c = make_attention_case([384], [3500], nh, nkv, dh, 16, torch.bfloat16, seed=81)
+    _plant(c, 0, nkv - 1, 2900, 200)
+    units = attention_units(c["q_lens"], c["ctx_lens"], budget)
+    assert (units[0] > 3) == (6 <= budget) and units[0] <= max(budget, 3), "three tiles of tokens, shared out where the budget allows"
+    for window, b in ((None, budget), (None, budget), (700, budget), (None, 0), (130, budget)):
+        out, ref = run_attention_case(c, window, implementation="prefill_tcgen05", dense_reference=True, work_budget=b)
+        close(out, ref, torch.bfloat16, f"work list heads={heads} window={window} budget={b}")
+        if window is None:
+            _planted_value_comes_out(c, out, 0, nkv - 1, 2900, 200, f"work list heads={heads} budget={b}")
+    c = make_attention_case([130, 1, 70, 1, 1], [1500, 900, 70, 2048, 1], nh, nkv, dh, 16, torch.bfloat16, seed=82)
+    for singles in (0, 3):
+        out, ref = run_attention_case(c, None, implementation="prefill_tcgen05", dense_reference=True, work_budget=budget, singles=singles)
+        close(out, ref, torch.bfloat16, f"work list, portions beside single tokens, heads={heads} singles={singles}")
+    out, ref = run_attention_case(c, None, dense_reference=True, work_budget=budget, singles=3)
+    close(out, ref, torch.bfloat16, f"work list through the dispatcher, heads={heads}")
     assert K().library().li_tcgen05_status() == 0
 
 
