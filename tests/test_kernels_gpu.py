@@ -541,9 +541,12 @@ def test_attention_decode_kernel_alone(heads, page):
     for window in (None, 100, 300):
         out, ref = run_attention_case(c, window, implementation="decode")
         close(out, ref, torch.bfloat16, f"decode kernel heads={heads} page={page} window={window}")
-    # alone or in the batch: the same bits
+    # alone or in the batch: the same bits, as long as the batch is one that the same kernel takes (from 60 pairs of
+    # sequence and kv head on, a CTA walks a whole context and the sums come in another order)
+    few = min(len(ctx_lens), 59 // nkv)
+    c = make_attention_case([1] * few, ctx_lens[:few], nh, nkv, dh, page, torch.bfloat16, seed=31)
     out_all, _ = run_attention_case(c, None, implementation="decode")
-    c1 = make_attention_case([1] * len(ctx_lens), ctx_lens, nh, nkv, dh, page, torch.bfloat16, seed=31)
+    c1 = make_attention_case([1] * few, ctx_lens[:few], nh, nkv, dh, page, torch.bfloat16, seed=31)
     for key in ("q_lens", "ctx_lens"):
         c1[key] = c1[key][4:5]
     c1.update(S=1, T=1, bt=c1["bt"][4:5], qkv=c1["qkv"][4:5], keys=c1["keys"][4:5], vals=c1["vals"][4:5], q_start=[0, 1], seq_of=[0],
@@ -602,7 +605,12 @@ def test_attention_single_tokens_beside_portions(heads, many):
     alone["keys"], alone["vals"], alone["bt"] = c["keys"], c["vals"], c["bt"]
     out_alone, _ = run_attention_case(alone, None, implementation="decode")
     out_mixed, _ = run_attention_case(c, None, singles=n1)
-    assert torch.equal(out_alone[0], out_mixed[tok0])
+    # (which of the two decode kernels runs depends on how many single tokens there are: from 60 pairs of sequence and
+    # kv head on, a CTA walks a whole context, and the sums come in another order)
+    if (len(q_lens) * nkv >= 60) == (n1 * nkv >= 60):
+        assert torch.equal(out_alone[0], out_mixed[tok0])
+    else:
+        close(out_mixed[tok0:tok0 + 1], out_alone[0:1], torch.bfloat16, "a single token alone and beside portions, through different kernels")
 
 
 @pytest.mark.parametrize("heads", [(4, 2, 16), (3, 1, 32), (6, 2, 48), (12, 2, 128), (8, 8, 64), (14, 2, 80), (28, 4, 128)])
