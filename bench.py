@@ -425,6 +425,21 @@ def time_serve(model, cfg, requests=64, seed=11, max_tokens_per_step=4096, page_
     eng = Engine(model, EngineConfig(num_pages=budget // 16, max_num_seqs=requests, max_tokens_per_step=max_tokens_per_step,
                                      prefill_chunk=2048, run_ahead=True))
     out = {}
+    # a step that does not come back within the limit ends the run with what is known: the status word of the kernels'
+    # bounded waits, and the step that was running
+    watch = {"at": time.perf_counter(), "what": "start", "stop": False}
+
+    def watchdog(limit=float(os.environ.get("LITINFER_BENCH_STEP_LIMIT_S", "45"))):
+        from litinfer_b200 import kernels as K
+
+        while not watch["stop"]:
+            time.sleep(1.0)
+            if time.perf_counter() - watch["at"] > limit:
+                print(f"[serve] no step for {limit:.0f} s; kernels' status word {K.library().li_tcgen05_status()}; last: {watch['what']}",
+                      file=sys.stderr, flush=True)
+                os._exit(7)
+
+    threading.Thread(target=watchdog, daemon=True).start()
     for timed in (False, True):
         ids = [eng.add_request(p, m) for p, m in zip(prompts, news)]
         steps, pre0, replay0 = [], eng.scheduler.num_preemptions, eng.runner.graph_replays
@@ -432,6 +447,10 @@ def time_serve(model, cfg, requests=64, seed=11, max_tokens_per_step=4096, page_
         t0 = time.perf_counter()
         while eng.has_unfinished():
             t = time.perf_counter()
+            running = eng.scheduler.running
+            watch["at"], watch["what"] = t, (f"{'timed' if timed else 'warm-up'} step {len(steps)}: {len(running)} running "
+                                             f"(cached {[r.num_cached for r in running][:70]}), {len(eng.scheduler.waiting)} waiting, "
+                                             f"graph replays {eng.runner.graph_replays}")
             eng.step()
             steps.append(time.perf_counter() - t)
             if len(steps) % 200 == 0:
@@ -449,6 +468,7 @@ def time_serve(model, cfg, requests=64, seed=11, max_tokens_per_step=4096, page_
                    steps=len(steps), mean_step_ms=1e3 * sum(steps) / len(steps), p95_step_ms=1e3 * steps[int(0.95 * (len(steps) - 1))],
                    preemptions=eng.scheduler.num_preemptions - pre0, steps_from_graphs=eng.runner.graph_replays - replay0,
                    steps_launched_plainly=len(steps) - (eng.runner.graph_replays - replay0), pool_tokens=budget, needed_tokens=need)
+    watch["stop"] = True
     return out
 
 

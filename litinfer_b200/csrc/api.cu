@@ -1,5 +1,6 @@
 // Error channel of the C interface, and a query of the device the library
 // was built for.
+#include <atomic>
 #include "common.cuh"
 
 #include <cstdlib>
@@ -23,12 +24,25 @@ int li_check_launch(const char* what) {
     return li_fail("%s: launch failed: %s", what, cudaGetErrorString(e));
 }
 
-bool li_pdl_enabled() {
+// Whether the caller wants its next launches to overlap at all (li_pdl_allow).  The step function allows it for steps of
+// few tokens only: there the chain of short kernels gains from it, while steps of thousands of tokens gain nothing, and
+// such steps of a 7B-shaped model have stopped making progress with it (some wait that is not one of the bounded ones;
+// with the overlap off for any one kind of kernel, or for all, they never did).
+static std::atomic<int> g_pdl_allowed{1};
+
+LI_EXPORT void li_pdl_allow(int allow) { g_pdl_allowed.store(allow ? 1 : 0, std::memory_order_relaxed); }
+
+bool li_pdl_enabled(int kind) {
+    if (!g_pdl_allowed.load(std::memory_order_relaxed)) return false;
     static const bool on = [] {
         const char* v = getenv("LITINFER_B200_PDL");
         return !(v && v[0] == '0');
     }();
-    return on;
+    static const int off_mask = [] {
+        const char* v = getenv("LITINFER_B200_PDL_OFF");
+        return v ? atoi(v) : 0;
+    }();
+    return on && !(off_mask & kind);
 }
 
 LI_EXPORT const char* li_last_error() { return g_error; }

@@ -30,6 +30,7 @@
 //
 // Requires head_dim in {16, 32, ..., 128, 256}, at most 16 query heads per
 // key/value head, page_size a multiple of 16.
+#define LI_PDL_KIND 4
 #include "attention_decode_unit.cuh"
 
 namespace {

@@ -27,6 +27,7 @@
 // CTA leaves, freeing its tensor memory.
 //
 // Requires head_dim 64 or 128 and page_size a multiple of 16.
+#define LI_PDL_KIND 4
 #include "tcgen05.cuh"
 
 namespace tc {

@@ -105,7 +105,13 @@ __device__ __forceinline__ float swiglu_of(float gate, float up) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-bool li_pdl_enabled();      // LITINFER_B200_PDL=0 in the environment turns the overlap off (for measurements)
+// LITINFER_B200_PDL=0 in the environment turns the overlap off (for measurements); LITINFER_B200_PDL_OFF=<mask> turns it
+// off for the kernels of some source files only (LI_PDL_KIND of the file: 1 tcgen05 GEMM, 2 weight-streaming products,
+// 4 attention, 8 the rest), to find which overlap a fault needs.
+bool li_pdl_enabled(int kind);
+#ifndef LI_PDL_KIND
+#define LI_PDL_KIND 8
+#endif
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t li_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
@@ -116,7 +122,7 @@ static inline cudaError_t li_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = li_pdl_enabled() ? 1 : 0;
+    attr[0].val.programmaticStreamSerializationAllowed = li_pdl_enabled(LI_PDL_KIND) ? 1 : 0;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
@@ -141,7 +147,7 @@ static inline cudaError_t li_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim
         attr[na].val.clusterDim.z = cluster.z;
         ++na;
     }
-    if (li_pdl_enabled()) {
+    if (li_pdl_enabled(LI_PDL_KIND)) {
         attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;

@@ -28,6 +28,7 @@
 // Every wait on an mbarrier is bounded.  A wait that runs out raises a flag in
 // mapped host memory (li_tcgen05_status() reads it), the CTA waits, again
 // bounded, for the copies it has in flight, frees its tensor memory and returns.
+#define LI_PDL_KIND 1
 #include "gemm_epilogue.cuh"
 #include "rope_epilogue.cuh"
 #include "tcgen05.cuh"

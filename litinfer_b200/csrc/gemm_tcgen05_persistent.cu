@@ -14,6 +14,7 @@
 // commit that frees a stage arrives in both); acc_full per accumulator (commit to both CTAs); acc_empty per accumulator in
 // the first CTA, on which the epilogue warps of both CTAs arrive.  Every wait is bounded; a wait that runs out raises the
 // status word of the tcgen05 kernels, and every role leaves its loops and meets the others at the final barriers.
+#define LI_PDL_KIND 1
 #include "gemm_epilogue.cuh"
 #include "tcgen05.cuh"
 

@@ -22,6 +22,7 @@
 // those choices a token's result is the same up to rounding only.
 //
 // Requires K % 8 == 0 and 16-byte aligned operands; M <= 64.
+#define LI_PDL_KIND 2
 #include "common.cuh"
 #include "no_alloc.h"
 #include "gemv_epilogue.cuh"

@@ -17,6 +17,7 @@
 // (up * gate / (1 + exp(-gate)), src/ops/swiglu/op.cpp:17-23).
 //
 // K a multiple of 8; waits bounded as in the other tcgen05 kernel.
+#define LI_PDL_KIND 2
 #include "row_scale.cuh"
 #include "tcgen05.cuh"
 
@@ -141,7 +142,7 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 issued = i + 1;
             }
             if (!ok) {
-                atomicExch(error_flag, 1);
+                atomicExch(error_flag, 31);
                 for (int i = (issued > kStages ? issued - kStages : 0); i < issued; ++i) mbar_wait(&sm.full[i % kStages], (i / kStages) & 1);
             }
         }
@@ -161,7 +162,7 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                 umma_commit(&sm.empty[s]);
             }
             if (ok) umma_commit(&sm.accum);
-            else atomicExch(error_flag, 2);
+            else atomicExch(error_flag, 32);
         }
     } else {
         pdl_wait();
@@ -182,7 +183,7 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
         const bool ok = mbar_wait(&sm.accum, 0);
         if (!ok) {
-            if (lane == 0) atomicExch(error_flag, 3);
+            if (lane == 0) atomicExch(error_flag, 33);
         } else {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             float v[BT];

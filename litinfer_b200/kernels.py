@@ -169,6 +169,12 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> Non
     _check(library().li_gather_rows(_p(src), _p(rows), _p(out), _i(src.shape[0]), _i(rows.shape[0]), _l(src.shape[1]), _stream(out)), "gather_rows")
 
 
+def allow_overlap(allow: bool) -> None:
+    """Whether the launches that follow may begin while the kernel before them still runs (programmatic dependent
+    launch).  The step function allows it for steps of few tokens, where a step is a chain of short kernels."""
+    library().li_pdl_allow(ctypes.c_int(1 if allow else 0))
+
+
 def scale_inplace(x32: torch.Tensor, factor: float) -> None:
     """x32 *= factor (float32, in place)."""
     _need(x32, "scale operand", torch.float32)
