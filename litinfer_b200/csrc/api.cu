@@ -24,16 +24,14 @@ int li_check_launch(const char* what) {
     return li_fail("%s: launch failed: %s", what, cudaGetErrorString(e));
 }
 
-// Whether the caller wants its next launches to overlap at all (li_pdl_allow).  The step function allows it for steps of
-// few tokens only: there the chain of short kernels gains from it, while steps of thousands of tokens gain nothing, and
-// such steps of a 7B-shaped model have stopped making progress with it (some wait that is not one of the bounded ones;
-// with the overlap off for any one kind of kernel, or for all, they never did).
-static std::atomic<int> g_pdl_allowed{1};
+// Which of the caller's next launches may overlap (li_pdl_allow): a mask of kinds (LI_PDL_KIND) that may NOT.  The step
+// function sets it per step.
+static std::atomic<int> g_pdl_off{0};
 
-LI_EXPORT void li_pdl_allow(int allow) { g_pdl_allowed.store(allow ? 1 : 0, std::memory_order_relaxed); }
+LI_EXPORT void li_pdl_allow(int kinds_off) { g_pdl_off.store(kinds_off, std::memory_order_relaxed); }
 
 bool li_pdl_enabled(int kind) {
-    if (!g_pdl_allowed.load(std::memory_order_relaxed)) return false;
+    if (g_pdl_off.load(std::memory_order_relaxed) & kind) return false;
     static const bool on = [] {
         const char* v = getenv("LITINFER_B200_PDL");
         return !(v && v[0] == '0');

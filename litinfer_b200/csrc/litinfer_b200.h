@@ -18,9 +18,10 @@ const char* li_last_error();
 
 /* 0 if the current device is a B200 (sm_100); the library has code for no other. */
 int li_check_device();
-/* Whether the launches that follow may overlap with the kernel before them (programmatic dependent launch); the step
- * function switches it per step.  On by default; LITINFER_B200_PDL=0 in the environment keeps it off. */
-void li_pdl_allow(int allow);
+/* Which of the launches that follow may NOT begin while the kernel before them still runs (programmatic dependent
+ * launch): a mask of 1 tcgen05 GEMMs, 2 weight-streaming products, 4 attention, 8 the rest; 0 lets all overlap (the
+ * default), 15 none.  The step function sets it per step.  LITINFER_B200_PDL=0 in the environment keeps all off. */
+void li_pdl_allow(int kinds_off);
 
 /* ---- attention.cu ---- */
 /* Causal grouped-query attention of a step's tokens over the paged cache.  qkv [T, (nh + 2 nkv) dh] with q

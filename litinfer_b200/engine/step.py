@@ -50,11 +50,16 @@ class ModelRunner:
     # empty but the last, which takes the padding tokens), logit rows to the sequences or, if more are wanted, to the
     # tokens.
     STEP_GRAPH_TOKENS = 2048
-    # steps of at most this many tokens launch their kernels so that each may begin while the one before still runs
-    # (kernels.allow_overlap): a step of few tokens is a chain of short kernels (1.44 -> 1.31 ms at batch 8), a step of
-    # hundreds of tokens gains nothing.  The padded sizes of captured steps are multiples of 64, so a graph is always
-    # replayed for steps of the class it was captured for.
-    OVERLAP_TOKENS = 64
+    # Every kernel of a step may begin while the one before it still runs (programmatic dependent launch,
+    # kernels.allow_overlap): a step of few tokens is a chain of short kernels (1.44 -> 1.31 ms at batch 8).  In steps of
+    # more than this many tokens the kernels that take a multiprocessor each (the tcgen05 GEMMs and the attention for
+    # long portions) are launched plainly: with them waiting resident for the kernel before, steps of thousands of tokens
+    # of a 7B-shaped model stopped making progress in four runs of ten (no bounded wait ran out; never with a 1.5B
+    # shape, never with either those or the small kernels launched plainly: 0 of 11, 0 of 11, 0 of 10 runs).  It costs
+    # such steps a microsecond per launch (2,048 tokens: 5.86 -> 6.16 ms).  The padded sizes of captured steps are
+    # multiples of 64, so a graph is always replayed for steps of the class it was captured for.
+    OVERLAP_TOKENS = 256
+    BIG_STEP_NO_OVERLAP = ("gemm", "attention")
     STEP_GRAPH_LIMIT = 48               # captured shapes kept; further shapes are launched plainly
     STEP_GRAPH_LOGITS = 1 << 26         # logits (floats) a captured shape may hold
 
@@ -137,7 +142,8 @@ class ModelRunner:
 
         if self.device.type == "cuda":
             # a captured graph keeps what held when it was captured; every shape is of one size class
-            K.allow_overlap(sum(len(it.tokens) for it in items) <= self.OVERLAP_TOKENS)
+            big = sum(len(it.tokens) for it in items) > self.OVERLAP_TOKENS
+            K.allow_overlap(but=self.BIG_STEP_NO_OVERLAP if big else ())
 
         if K.profile.enabled:
             K.profile.phase = "decode" if decode_only else "prefill"

@@ -169,10 +169,13 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> Non
     _check(library().li_gather_rows(_p(src), _p(rows), _p(out), _i(src.shape[0]), _i(rows.shape[0]), _l(src.shape[1]), _stream(out)), "gather_rows")
 
 
-def allow_overlap(allow: bool) -> None:
-    """Whether the launches that follow may begin while the kernel before them still runs (programmatic dependent
-    launch).  The step function allows it for steps of few tokens, where a step is a chain of short kernels."""
-    library().li_pdl_allow(ctypes.c_int(1 if allow else 0))
+OVERLAP_KINDS = {"gemm": 1, "streaming_products": 2, "attention": 4, "rest": 8}
+
+
+def allow_overlap(but: tuple = ()) -> None:
+    """The launches that follow may begin while the kernel before them still runs (programmatic dependent launch),
+    except the kinds of kernel named in ``but`` (keys of OVERLAP_KINDS).  The step function sets this per step."""
+    library().li_pdl_allow(ctypes.c_int(sum(OVERLAP_KINDS[k] for k in but)))
 
 
 def scale_inplace(x32: torch.Tensor, factor: float) -> None:
