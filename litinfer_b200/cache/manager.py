@@ -53,6 +53,9 @@ class Group:
     entries: List[int]
     pool: Optional[PoolView]
     kv: Optional[torch.Tensor]
+    # the device's resident copy of the requests' block tables: int32 [max_requests + 1, table_blocks], a row per state
+    # slot, the last row (the padding sequences') all sink page; a step uploads what changed (engine.batch.pack_step)
+    tables: Optional[torch.Tensor] = None
 
 
 class RequestCache:
@@ -82,7 +85,8 @@ class CacheManager:
     RELEASED = -1
 
     def __init__(self, requirements: Sequence, cache_from: Sequence[Optional[int]], num_pages: int, page_size: int,
-                 max_requests: int, dtype: torch.dtype, device, allocate: bool = True) -> None:
+                 max_requests: int, dtype: torch.dtype, device, allocate: bool = True, table_blocks: Optional[int] = None) -> None:
+        """``table_blocks``: how many pages the longest request's table can name (default: 65,536 tokens' worth)."""
         if page_size < 16 or page_size & (page_size - 1):
             raise ValueError(f"page_size must be a power of two of at least 16, got {page_size}")
         self.page_size = int(page_size)
@@ -113,8 +117,10 @@ class CacheManager:
         self.slots = PoolView(self, -1, self.max_requests)
         for gid, g in enumerate(self.groups):
             g.pool = PoolView(self, gid, self.num_pages)
+        self.table_blocks = int(table_blocks or -(-65536 // self.page_size))
         for g in self.groups:
             if allocate:
+                g.tables = torch.full((self.max_requests + 1, self.table_blocks), self.num_pages, dtype=torch.int32, device=self.device)
                 g.kv = torch.zeros((len(g.entries), 2, self.num_pages + 1, g.key.num_kv_heads, self.page_size * g.key.head_dim),
                                    dtype=dtype, device=self.device)
         for i, req in enumerate(requirements):

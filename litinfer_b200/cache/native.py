@@ -56,7 +56,8 @@ _SIGNATURES = {
     "li_sched_update": (I, [P, I, P, P, P, P]),
     "li_sched_abort": (I, [P, I, IP]),
     "li_sched_forget": (I, [P, I]),
-    "li_cm_pack_step": (I, [P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, ctypes.c_longlong, P]),
+    "li_cm_pack_step": (I, [P, I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, ctypes.c_longlong, P, I]),
+    "li_cm_table_updates_bound": (I, [P, I, P, P, P, P]),
 }
 
 

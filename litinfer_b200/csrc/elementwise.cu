@@ -204,6 +204,39 @@ LI_EXPORT int li_residual_add(float* x, const void* delta, int dtype, long long 
     return li_check_launch("residual_add");
 }
 
+// The device's resident copy of the requests' block tables (a row per state slot) and the step's view of it.  `updates`
+// (from the host runtime's packer): a count, then triples (slot, logical page, page id).  CTA s brings the row of
+// sequence s up to date (the triples of its slot; two sequences of one request write the same values) and copies its
+// first max_blocks entries into the step's table, the sink page beyond the row's width.  LitInfer builds and uploads a
+// table per layer and step (src/llaisys/models/qwen2.cpp:993-1003); here a step uploads what changed.
+namespace {
+__global__ void table_gather_kernel(int* __restrict__ resident, int rows, int cols, const int* __restrict__ updates, int update_cap,
+                                    const int* __restrict__ slots, int* __restrict__ out, int max_blocks, int trash_page) {
+    const int s = blockIdx.x;
+    int slot = slots[s];
+    if (slot < 0 || slot >= rows) slot = rows - 1;                  // the last row is never written: all sink page
+    int n = updates[0];
+    if (n > update_cap) n = update_cap;
+    int* row = resident + (size_t)slot * cols;
+    if (slot != rows - 1)
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const int* u = updates + 1 + 3 * i;
+            if (u[0] == slot && u[1] >= 0 && u[1] < cols) row[u[1]] = u[2];
+        }
+    __syncthreads();
+    for (int b = threadIdx.x; b < max_blocks; b += blockDim.x) out[(size_t)s * max_blocks + b] = b < cols ? row[b] : trash_page;
+}
+}  // namespace
+
+LI_EXPORT int li_table_gather(int* resident, int rows, int cols, const int* updates, int update_cap, const int* slots, int* out, int S,
+                              int max_blocks, int trash_page, cudaStream_t stream) {
+    LI_REQUIRE(rows >= 1 && cols >= 1 && S >= 0 && max_blocks >= 1 && update_cap >= 0, "table_gather: bad sizes rows=%d cols=%d S=%d max_blocks=%d cap=%d",
+               rows, cols, S, max_blocks, update_cap);
+    if (S == 0) return 0;
+    table_gather_kernel<<<S, 128, 0, stream>>>(resident, rows, cols, updates, update_cap, slots, out, max_blocks, trash_page);
+    return li_check_launch("table_gather");
+}
+
 // x *= factor (an embedding scale) and x = cap * tanh(x / cap) (a cap on the logits), in place on float32.
 namespace {
 __global__ void scale_kernel(float* __restrict__ x, long long n, float factor) {

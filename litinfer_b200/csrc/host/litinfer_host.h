@@ -89,7 +89,12 @@ int li_cm_check(void* h);
 int li_cm_pack_step(void* h, int n_items, const int* request_ids, const int* q_lens, const int* starts, const int*
     olds, const int* tokens, const int* want_counts, const int* wants, int vocab, int S, int T, int R, int pad_tokens,
     int max_blocks, int allow_repeat, int trash_page, int trash_slot, const int* offsets, int* buf, long long buf_len,
-    int* info /* R_real, max_q_len, max_ctx_len, singles */);
+    int* info /* R_real, max_q_len, max_ctx_len, singles */, int update_cap);
+
+/* Resident tables (li_cm_pack_step with update_cap >= 0: the field of a group's block tables then holds a count and
+ * triples (state slot, logical page, page id) that bring the device's copy of the step's requests' tables up to date,
+ * and what is written counts as sent): an upper bound of how many triples a group can need for these items. */
+int li_cm_table_updates_bound(void* h, int n_items, const int* request_ids, const int* q_lens, const int* starts, int* bound);
 
 /* ---- scheduler.cpp ---- */
 /* A scheduler over a manager (which must outlive it). */

@@ -77,6 +77,8 @@ int li_host::cm_admit(Manager* m, int id, int* slot) {
     r.id = id;
     r.slot = *slot;
     r.tables.resize(m->pools.size());
+    r.sent.assign(m->pools.size(), 0);
+    r.trash_sent.assign(m->pools.size(), 0);
     m->live.emplace(id, std::move(r));
     return LI_HOST_OK;
 }
@@ -204,10 +206,35 @@ LI_HOST_EXPORT int li_cm_check(void* h) {
 // tokens.  The batch is padded to S sequences, T tokens and R rows (their meaning as in batch.py: with pad_tokens the
 // padding sequences are empty but the last, else they hold one token each and want its row).  The buffer must be
 // zeroed and sized by the caller; T, S, R and the width of the block tables are the caller's too, checked here.
+//
+// Resident tables (update_cap >= 0): the device keeps a copy of every request's tables, a row per state slot, and the
+// step's sequences name their row by state_slots.  The field that would hold a group's block tables then holds what
+// that copy lacks for the step's requests: a count, then triples (slot, logical page, page id; the sink page for a page
+// that was given back), at most update_cap of them (li_cm_table_updates_bound says how many it can be).  What is written
+// counts as sent: the caller uploads the buffer and applies it (kernels.table_gather) before anything else is packed.
+LI_HOST_EXPORT int li_cm_table_updates_bound(void* h, int n_items, const int* request_ids, const int* q_lens, const int* starts, int* bound) {
+    Manager* m = static_cast<Manager*>(h);
+    const int G = (int)m->pools.size();
+    long long most = 0;
+    for (int g = 0; g < G; ++g) {
+        long long n = 0;
+        for (int s = 0; s < n_items; ++s) {
+            FIND(m, r, request_ids[s]);
+            const int start = starts && starts[s] >= 0 ? starts[s] : r->length;
+            const int nb = m->blocks(start + q_lens[s]);
+            n += std::max(0, nb - std::min(r->sent[(size_t)g], nb));
+            n += std::max(0, std::min(m->first_needed_page(g, r->length), nb) - r->trash_sent[(size_t)g]);
+        }
+        most = std::max(most, n);
+    }
+    *bound = (int)std::min<long long>(most, 1 << 30);
+    return LI_HOST_OK;
+}
+
 LI_HOST_EXPORT int li_cm_pack_step(void* h, int n_items, const int* request_ids, const int* q_lens, const int* starts, const int* olds,
                                    const int* tokens, const int* want_counts, const int* wants, int vocab, int S, int T, int R,
                                    int pad_tokens, int max_blocks, int allow_repeat, int trash_page, int trash_slot, const int* offsets,
-                                   int* buf, long long buf_len, int* info /* R_real, max_q_len, max_ctx_len, singles */) {
+                                   int* buf, long long buf_len, int* info /* R_real, max_q_len, max_ctx_len, singles */, int update_cap) {
     Manager* m = static_cast<Manager*>(h);
     const int G = (int)m->pools.size(), page = m->page_size;
     if (n_items <= 0) return fail(LI_HOST_VALUE, "a step needs at least one item");
@@ -229,11 +256,12 @@ LI_HOST_EXPORT int li_cm_pack_step(void* h, int n_items, const int* request_ids,
         t_pad = pad_seq;
         if (t_real + t_pad != T || r_real + pad_seq != R) return fail(LI_HOST_VALUE, "the step's sizes do not match its items");
     }
+    const bool resident = update_cap >= 0;
     // the fields must fit the buffer
     const int n_fields = 8 + 2 * G;
     const long long sizes[8] = {T, T, T, (long long)S + 1, S, S, S, R};
     for (int f = 0; f < n_fields; ++f) {
-        const long long len = f < 8 ? sizes[f] : ((f - 8) % 2 == 0 ? (long long)T : (long long)S * max_blocks);
+        const long long len = f < 8 ? sizes[f] : ((f - 8) % 2 == 0 ? (long long)T : (resident ? 1 + 3LL * update_cap : (long long)S * max_blocks));
         if (offsets[f] < 0 || offsets[f] + len > buf_len) return fail(LI_HOST_VALUE, "field %d does not fit the step's buffer", f);
     }
     int* token_ids = buf + offsets[0];
@@ -276,9 +304,31 @@ LI_HOST_EXPORT int li_cm_pack_step(void* h, int n_items, const int* request_ids,
             const std::vector<int>& table = r->tables[(size_t)g];
             if ((int)table.size() < nb)
                 return fail(LI_HOST_RUNTIME, "request %d: pages for %d tokens are not allocated (group %d)", id, ctx, g);
-            int* bt = buf + offsets[8 + 2 * g + 1] + (size_t)s * max_blocks;
-            for (int b = 0; b < nb; ++b) bt[b] = table[(size_t)b] == kReleased ? trash_page : table[(size_t)b];
-            for (int b = nb; b < max_blocks; ++b) bt[b] = trash_page;
+            if (resident) {
+                int* upd = buf + offsets[8 + 2 * g + 1];           // [0]: count so far, then the triples
+                int& given_back = r->trash_sent[(size_t)g];
+                int& sent = r->sent[(size_t)g];
+                auto emit = [&](int b, int pg) {
+                    if (upd[0] >= update_cap) return false;
+                    int* t3 = upd + 1 + 3 * upd[0]++;
+                    t3[0] = r->slot, t3[1] = b, t3[2] = pg;
+                    return true;
+                };
+                bool room = true;
+                while (room && given_back < nb && table[(size_t)given_back] == kReleased) {
+                    if (given_back < sent) room = emit(given_back, trash_page);      // else the loop below sends it, as given back
+                    if (room) ++given_back;
+                }
+                while (room && sent < nb) {
+                    room = emit(sent, table[(size_t)sent] == kReleased ? trash_page : table[(size_t)sent]);
+                    if (room) ++sent;
+                }
+                if (!room) return fail(LI_HOST_VALUE, "request %d: more than %d changes of its block table in one step (group %d)", id, update_cap, g);
+            } else {
+                int* bt = buf + offsets[8 + 2 * g + 1] + (size_t)s * max_blocks;
+                for (int b = 0; b < nb; ++b) bt[b] = table[(size_t)b] == kReleased ? trash_page : table[(size_t)b];
+                for (int b = nb; b < max_blocks; ++b) bt[b] = trash_page;
+            }
             int* sm = buf + offsets[8 + 2 * g] + tok;
             for (int j = 0; j < n; ++j) {
                 const int pos = start + j, pg = table[(size_t)(pos / page)];
@@ -308,7 +358,7 @@ LI_HOST_EXPORT int li_cm_pack_step(void* h, int n_items, const int* request_ids,
         ctx_lens[s] = n;
         old_lens[s] = 0;
         state_slots[s] = trash_slot;
-        for (int g = 0; g < G; ++g) {
+        for (int g = 0; g < G && !resident; ++g) {
             int* bt = buf + offsets[8 + 2 * g + 1] + (size_t)s * max_blocks;
             for (int b = 0; b < max_blocks; ++b) bt[b] = trash_page;
         }

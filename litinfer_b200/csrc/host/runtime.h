@@ -68,6 +68,10 @@ struct Pool {
 struct Request {
     int id = 0, slot = 0, length = 0;
     std::vector<std::vector<int>> tables;          // per group: logical page -> page id, kReleased once given back
+    // What the device's resident copy of the tables holds of this request (li_cm_pack_step in resident mode): per group,
+    // logical pages below sent[g] have been sent with the page id they had then, and those below trash_sent[g] have been
+    // sent again as given back (pages go back as a growing prefix, li_cm_commit).
+    std::vector<int> sent, trash_sent;
 };
 
 struct Manager {

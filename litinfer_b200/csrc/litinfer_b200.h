@@ -23,6 +23,13 @@ int li_check_device();
  * default), 15 none.  The step function sets it per step.  LITINFER_B200_PDL=0 in the environment keeps all off. */
 void li_pdl_allow(int kinds_off);
 
+/* ---- resident block tables (elementwise.cu) ---- */
+/* resident [rows, cols] int32: a row per state slot, the last row all sink page.  updates: a count, then triples (slot,
+ * logical page, page id).  Applies the triples of each of the S sequences' slots, then copies the first max_blocks
+ * entries of each sequence's row into out [S, max_blocks]. */
+int li_table_gather(int* resident, int rows, int cols, const int* updates, int update_cap, const int* slots, int* out, int S, int
+    max_blocks, int trash_page, cudaStream_t stream);
+
 /* ---- attention.cu ---- */
 /* Causal grouped-query attention of a step's tokens over the paged cache.  qkv [T, (nh + 2 nkv) dh] with q
  * rotated; out [T, nh dh]; token t of sequence s at position p sees the cached keys max(0, p - window + 1) .. p

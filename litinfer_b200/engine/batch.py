@@ -20,6 +20,7 @@ with portions of prompts).  The buffer is filled by the host runtime
 
 from __future__ import annotations
 
+import ctypes
 import functools
 import itertools
 from dataclasses import dataclass, field
@@ -76,8 +77,18 @@ class StepContext:
     # when single tokens go to a kernel of their own / when they do not
     attn_units: Optional[torch.Tensor] = None
     attn_unit_slots: tuple = (0, 0)
+    # resident block tables: per group (the resident tensor, the step's changes, the step's table to fill, the sink page)
+    pending_tables: list = field(default_factory=list)
     # what parts make once per step and share between the layers (keyed by the part), e.g. a table of rotation angles
     scratch: dict = field(default_factory=dict)
+
+    def sync_tables(self) -> None:
+        """Apply the step's changes to the resident block tables and fill the step's tables from them (one small kernel
+        per cache group).  Applying twice gives the same."""
+        from .. import kernels as K
+
+        for tables, updates, out, trash in self.pending_tables:
+            K.table_gather(tables, updates, self.state_slots, out, trash)
 
     def group(self, gid: int) -> GroupView:
         return self.groups[gid]
@@ -163,9 +174,10 @@ def attention_units(q_lens: Sequence[int], ctx_lens: Sequence[int], work_budget:
 
 
 @functools.lru_cache(maxsize=512)
-def _fields(T: int, S: int, R: int, G: int, mb: int, U: int = 0):
+def _fields(T: int, S: int, R: int, G: int, mb: int, U: int = 0, cap: int = -1):
     """Where each field starts in the packed buffer (16-byte aligned starts), the buffer's length (the host runtime's
-    fields, then ``U`` words of attention work list), and the starts as the array the host runtime takes."""
+    fields, then ``U`` words of attention work list), and the starts as the array the host runtime takes.  ``cap`` >= 0:
+    instead of a group's block tables the buffer carries up to that many changes of the resident ones."""
     fields = {}
     off = 0
     for name, n in zip(_FIELDS, (T, T, T, S + 1, S, S, S, R)):
@@ -174,8 +186,12 @@ def _fields(T: int, S: int, R: int, G: int, mb: int, U: int = 0):
     for gid in range(G):
         fields[f"slot_mapping{gid}"] = (off, T)
         off += _round_up(max(T, 1), 4)
-        fields[f"block_table{gid}"] = (off, S * mb)
-        off += _round_up(max(S * mb, 1), 4)
+        if cap >= 0:
+            fields[f"table_updates{gid}"] = (off, 1 + 3 * cap)
+            off += _round_up(1 + 3 * cap, 4)
+        else:
+            fields[f"block_table{gid}"] = (off, S * mb)
+            off += _round_up(max(S * mb, 1), 4)
     starts = np.asarray([o for o, _ in fields.values()], dtype=np.int32)
     if U:
         fields["attn_units"] = (off, U)
@@ -189,7 +205,7 @@ def _ints(values) -> np.ndarray:
 
 def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int, pad_seqs: int = 0,
               max_blocks: Optional[int] = None, tokens_of_one_request: bool = False, pad_tokens: int = 0,
-              pad_rows: int = 0, work_budget: int = 0):
+              pad_rows: int = 0, work_budget: int = 0, resident: bool = False, update_cap: Optional[int] = None):
     """Host side: validate the items and fill the packed int32 array (the host runtime does both, in C++).
 
     Returns (array, layout) where layout maps field name -> (offset, length) and
@@ -202,6 +218,10 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
     sequences hold one token each and want its row.
     ``work_budget``: see :func:`attention_units`; a step with portions of prompts carries that list (a padded one with
     room for the most entries its shape can have).
+    ``resident``: the device keeps the requests' block tables (``manager.groups[g].tables``, a row per state slot); the
+    buffer then carries, instead of a table per sequence, what those lack for this step's requests (a count and
+    triples of slot, logical page, page id; room for ``update_cap`` of them, by default as many as it can be), and what
+    is packed counts as sent: the caller uploads it and applies it (``StepContext.sync_tables``) before packing again.
     """
     S_real = len(items)
     if S_real == 0:
@@ -238,7 +258,19 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
         units = attention_units(lens_all, ctx_all, work_budget)
         # a padded step is replayed from a captured launch, whose list has room for any step of its shape
         U = 4 + 4 * (pad_tokens // TOKEN_TILE + S + work_budget) if pad_tokens else len(units)
-    fields, total, offsets = _fields(T, S, R, G, mb, U if units is not None else 0)
+    ids = _ints([c.request_id for c in caches])
+    lens, first = _ints(q_lens), _ints(starts)
+    cap = -1
+    if resident:
+        if mb > manager.table_blocks:
+            raise ValueError(f"a context of {mb} pages is beyond the resident block tables ({manager.table_blocks} pages a request)")
+        cap = update_cap
+        if cap is None:
+            bound = ctypes.c_int(0)
+            native.check(manager._lib.li_cm_table_updates_bound(manager._h, S_real, ids.ctypes.data, lens.ctypes.data, first.ctypes.data,
+                                                                ctypes.byref(bound)))
+            cap = bound.value
+    fields, total, offsets = _fields(T, S, R, G, mb, U if units is not None else 0, cap)
     buf = np.zeros(total, dtype=np.int32)
     if units is not None:
         o = fields["attn_units"][0]
@@ -248,12 +280,12 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
     else:
         tokens = _ints(list(itertools.chain.from_iterable(it.tokens for it in items)))
     wants = _ints(list(itertools.chain.from_iterable(it.want for it in items))) if R_real else _ints(())
-    ids, lens, first, old, cnt = _ints([c.request_id for c in caches]), _ints(q_lens), _ints(starts), _ints(olds), _ints(counts)
+    old, cnt = _ints(olds), _ints(counts)
     info = np.zeros(4, dtype=np.int32)
     native.check(manager._lib.li_cm_pack_step(
         manager._h, S_real, ids.ctypes.data, lens.ctypes.data, first.ctypes.data, old.ctypes.data, tokens.ctypes.data,
         cnt.ctypes.data, wants.ctypes.data, int(vocab_size), S, T, R, int(pad_tokens), mb, 1 if tokens_of_one_request else 0,
-        manager.trash_page, manager.trash_slot, offsets.ctypes.data, buf.ctypes.data, total, info.ctypes.data))
+        manager.trash_page, manager.trash_slot, offsets.ctypes.data, buf.ctypes.data, total, info.ctypes.data, cap))
 
     def host(name):
         o, n = fields[name]
@@ -266,8 +298,10 @@ def pack_step(items: Sequence[StepItem], manager: CacheManager, vocab_size: int,
     return buf, layout
 
 
-def context_from(device_buf: torch.Tensor, layout, page_size: int) -> StepContext:
-    """Views into the uploaded buffer."""
+def context_from(device_buf: torch.Tensor, layout, page_size: int, resident: Optional[CacheManager] = None) -> StepContext:
+    """Views into the uploaded buffer.  ``resident``: the manager whose resident block tables the step was packed for;
+    the step's own tables are then made on the device by :meth:`StepContext.sync_tables`, which the caller runs before
+    the model (inside the capture, for a captured step)."""
     f = layout["fields"]
 
     def view(name):
@@ -275,8 +309,19 @@ def context_from(device_buf: torch.Tensor, layout, page_size: int) -> StepContex
         return device_buf[o:o + n]
 
     S, mb = layout["S"], layout["max_blocks"]
-    groups = [GroupView(view(f"block_table{g}").view(S, mb), view(f"slot_mapping{g}"), mb, page_size) for g in range(layout["G"])]
+    pending = []
+    if "table_updates0" in f or (layout["G"] and "block_table0" not in f):
+        if resident is None:
+            raise ValueError("this step was packed for resident block tables: context_from needs the manager")
+        groups = []
+        for g in range(layout["G"]):
+            table = torch.empty((S, mb), dtype=torch.int32, device=device_buf.device)
+            pending.append((resident.groups[g].tables, view(f"table_updates{g}"), table, resident.trash_page))
+            groups.append(GroupView(table, view(f"slot_mapping{g}"), mb, page_size))
+    else:
+        groups = [GroupView(view(f"block_table{g}").view(S, mb), view(f"slot_mapping{g}"), mb, page_size) for g in range(layout["G"])]
     return StepContext(
+        pending_tables=pending,
         num_tokens=layout["T"], num_seqs=S, num_logit_rows=layout["R"],
         token_ids=view("token_ids"), positions=view("positions"), seq_of_token=view("seq_of_token"),
         q_start=view("q_start"), ctx_lens=view("ctx_lens"), state_slots=view("state_slots"), old_lens=view("old_lens"),

@@ -18,11 +18,13 @@ of a few hundred tokens is bound by the host's launches, not by the device.
 
 from __future__ import annotations
 
+import ctypes
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
 import torch
 
+from ..cache import native
 from ..cache.manager import CacheManager
 from ..models.decoder import DecoderModel
 from ..parts.base import FixedState
@@ -72,6 +74,8 @@ class ModelRunner:
         # runs: its portions are never split, and nothing of such a model is captured (capturing runs the step for
         # warm-up, and a captured step would freeze which slots it updates)
         self._may_split = not any(isinstance(r, FixedState) for r in model.cache_requirements())
+        # the block tables stay on the device (manager.groups[g].tables); a step uploads what changed
+        self.resident = bool(manager.groups) and all(g.tables is not None for g in manager.groups)
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and self._may_split
         from .. import kernels as K
 
@@ -166,16 +170,35 @@ class ModelRunner:
         elif self.use_graphs and not decode_only and (shape := self._step_shape(items)) is not None:
             logits = self._step_shape_graph(items, shape)
         else:
-            buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size, work_budget=self.work_budget)
-            ctx = context_from(self._upload(buf), layout, self.manager.page_size)
+            buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size, work_budget=self.work_budget, resident=self.resident)
+            ctx = context_from(self._upload(buf), layout, self.manager.page_size, self.manager)
             if token_source is not None:
                 ctx.token_ids[:len(items)].copy_(token_source)
+            ctx.sync_tables()
             logits = self.model.forward(ctx, self.manager.entries)
         self.manager.commit_many([it.cache for it in items], [it.cache.length + len(it.tokens) for it in items])
         self.steps_run += 1
         return logits
 
     # ------------------------------------------------------------------
+    def _update_room(self, items: Sequence[StepItem], T: int, S: int, one_request: bool = False) -> Optional[int]:
+        """How many changes of the resident block tables a captured step of T tokens in S sequences has room for (a
+        function of its shape): every sequence's new pages and as many given back.  If these items need more (requests
+        that were extended without ever running), the surplus is sent now, by a small step of its own."""
+        if not self.resident:
+            return None
+        room = 2 * (T // self.manager.page_size + S) + 2
+        ids = np.asarray([it.cache.request_id for it in items], dtype=np.int32)
+        lens = np.asarray([len(it.tokens) for it in items], dtype=np.int32)
+        first = np.asarray([it.cache.length for it in items], dtype=np.int32)
+        bound = ctypes.c_int(0)
+        native.check(self.manager._lib.li_cm_table_updates_bound(self.manager._h, len(items), ids.ctypes.data, lens.ctypes.data,
+                                                                 first.ctypes.data, ctypes.byref(bound)))
+        if bound.value > room:
+            buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size, resident=True, tokens_of_one_request=one_request)
+            context_from(self._upload(buf), layout, self.manager.page_size, self.manager).sync_tables()
+        return room
+
     def _bucket(self, n: int) -> int:
         for b in self.GRAPH_BUCKETS:
             if n <= b:
@@ -226,8 +249,9 @@ class ModelRunner:
         """A step with portions of prompts through the captured graph of its padded shape."""
         Tp, Sp, Rp, singles = shape
         max_blocks = -(-self.max_context // self.manager.page_size)
+        cap = self._update_room(items, Tp, Sp)
         buf, layout = pack_step(items, self.manager, self.model.spec.vocab_size, pad_seqs=Sp, max_blocks=max_blocks,
-                                pad_tokens=Tp, pad_rows=Rp, work_budget=self.work_budget)
+                                pad_tokens=Tp, pad_rows=Rp, work_budget=self.work_budget, resident=self.resident, update_cap=cap)
         g = self._step_graphs.get(shape)
         if g is None:
             # the attention launch is sized for the longest portion and the longest context the shape may hold
@@ -251,8 +275,9 @@ class ModelRunner:
         wanted = [bool(len(it.want)) for it in items]
         g = self._graphs.get(B)
         full = [StepItem(it.cache, it.tokens, (0,)) for it in items]
+        cap = self._update_room(full, B, B, one_request=split)
         buf, layout = pack_step(full, self.manager, self.model.spec.vocab_size, pad_seqs=B, max_blocks=max_blocks,
-                                tokens_of_one_request=split)
+                                tokens_of_one_request=split, resident=self.resident, update_cap=cap)
         if g is None:
             g = self._capture(B, max_blocks, buf, layout)
         if layout["fields"] != g.layout["fields"]:
@@ -289,12 +314,13 @@ class ModelRunner:
         if "attn_units" in lay["fields"]:                  # the captured launch covers every entry the list has room for
             room = (lay["fields"]["attn_units"][1] - 4) // 4
             lay["unit_slots"] = (room, room)
-        ctx = context_from(meta, lay, self.manager.page_size)
+        ctx = context_from(meta, lay, self.manager.page_size, self.manager)
         stream = torch.cuda.Stream(self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(stream):
             for _ in range(2):                    # warm-up outside capture (first-call set-up, allocator)
                 ctx.scratch.clear()
+                ctx.sync_tables()
                 self.model.forward(ctx, self.manager.entries)
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
@@ -305,6 +331,7 @@ class ModelRunner:
         # metadata, not taken over from the warm-up runs
         ctx.scratch.clear()
         with torch.cuda.graph(graph, pool=None if B is not None else self._step_pool):
+            ctx.sync_tables()                          # the step's block tables from the resident ones: part of every replay
             logits = self.model.forward(ctx, self.manager.entries)
         g = _DecodeGraph(graph, meta, logits, lay)
         if B is not None:

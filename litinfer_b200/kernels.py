@@ -169,6 +169,21 @@ def gather_rows(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> Non
     _check(library().li_gather_rows(_p(src), _p(rows), _p(out), _i(src.shape[0]), _i(rows.shape[0]), _l(src.shape[1]), _stream(out)), "gather_rows")
 
 
+def table_gather(resident: torch.Tensor, updates: torch.Tensor, slots: torch.Tensor, out: torch.Tensor, trash_page: int) -> None:
+    """Bring the resident block tables (int32 ``[slots + 1, cols]``, the last row all sink page) up to date with
+    ``updates`` (a count, then triples of slot, logical page, page id) for the step's sequences (``slots`` int32 ``[S]``)
+    and copy each sequence's row into the step's table ``out`` (int32 ``[S, max_blocks]``)."""
+    _need(resident, "resident block tables", torch.int32)
+    _need(updates, "table updates", torch.int32)
+    _need(slots, "state slots", torch.int32)
+    S = slots.shape[0]
+    _need(out, "the step's block table", torch.int32, (S, out.shape[1]))
+    if resident.dim() != 2 or updates.numel() < 1 or (updates.numel() - 1) % 3:
+        raise KernelError(f"table_gather: resident {tuple(resident.shape)}, {updates.numel()} words of updates")
+    _check(library().li_table_gather(_p(resident), _i(resident.shape[0]), _i(resident.shape[1]), _p(updates), _i((updates.numel() - 1) // 3),
+                                     _p(slots), _p(out), _i(S), _i(out.shape[1]), _i(int(trash_page)), _stream(out)), "table_gather")
+
+
 OVERLAP_KINDS = {"gemm": 1, "streaming_products": 2, "attention": 4, "rest": 8}
 
 

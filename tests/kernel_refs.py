@@ -288,5 +288,20 @@ def sample(logits, params, out):
     out.copy_(torch.tensor(res, dtype=torch.int32))
 
 
-ALL = ["gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
+def table_gather(resident, updates, slots, out, trash_page):
+    """The resident block tables brought up to date and a row per sequence copied out: plain loops."""
+    rows, cols = resident.shape
+    n = int(updates[0])
+    wanted = set(int(x) for x in slots.tolist())
+    for i in range(n):
+        slot, block, page = (int(x) for x in updates[1 + 3 * i:4 + 3 * i].tolist())
+        if slot in wanted and slot != rows - 1 and 0 <= block < cols:
+            resident[slot, block] = page
+    for s, slot in enumerate(slots.tolist()):
+        slot = slot if 0 <= slot < rows else rows - 1
+        for b in range(out.shape[1]):
+            out[s, b] = resident[slot, b] if b < cols else trash_page
+
+
+ALL = ["table_gather", "gather_rows", "scale_inplace", "logit_cap", "rope_table", "linear_scaled_accepts", "linear_add_scaled_parts", "linear_add_scaled", "apply_row_scale", "linear_rope_kv", "interleave_gate_up", "embedding", "rmsnorm", "add_rmsnorm", "gather_rmsnorm", "residual_add", "linear", "rope_kv_write",
        "paged_attention", "swiglu", "argmax", "sample"]

@@ -185,3 +185,39 @@ def pack_step(items: Sequence, manager, vocab_size: int, pad_seqs: int = 0,
                   unit_slots=(int(units[0]), int(units[1])) if units is not None else (0, 0),
                   q_start=q_start.tolist(), ctx_lens=ctx.tolist(), state_slots=slots.tolist())
     return buf, layout
+
+
+class PlainResidentTables:
+    """What a step has to send so that a device copy of the requests' block tables (a row per state slot) is up to date,
+    restated: for every live request (``forget`` when it is released: an id admitted anew starts afresh) remember how many leading
+    logical pages were sent, and how many of those were sent again as given back.  Per item and group, in the order of
+    the items: first the pages that have been given back since (they go back as a growing prefix), then the pages not
+    sent yet, each as (slot, logical page, page id or the sink page)."""
+
+    def __init__(self, manager):
+        self.manager = manager
+        self.state = {}                      # request id -> per group [sent, given_back]
+
+    def forget(self, request_id):
+        self.state.pop(request_id, None)
+
+    def updates(self, items):
+        m = self.manager
+        out = [[] for _ in m.groups]
+        for it in items:
+            rc = it.cache
+            live = m.live[rc.request_id]
+            st = self.state.setdefault(rc.request_id, [[0, 0] for _ in m.groups])
+            nb = -(-(rc.length + len(it.tokens)) // m.page_size)
+            for g in range(len(m.groups)):
+                table = m.table(live, g)
+                sent, back = st[g]
+                while back < nb and table[back] < 0:
+                    if back < sent:
+                        out[g].append((live.slot, back, m.trash_page))
+                    back += 1
+                while sent < nb:
+                    out[g].append((live.slot, sent, m.trash_page if table[sent] < 0 else table[sent]))
+                    sent += 1
+                st[g] = [sent, back]
+        return out

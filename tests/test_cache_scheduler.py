@@ -294,6 +294,81 @@ def test_packed_steps_equal_the_plain_packer(seed, window):
         m.check()
 
 
+@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("window", [None, 20])
+def test_resident_tables_get_what_they_lack(seed, window):
+    """Steps packed for resident block tables, over the life of random requests (admitted, extended in portions and
+    single tokens, committed so that pages behind a window go back, released and their ids and slots used again): the
+    changes a step carries are those of the plain restatement, and a copy of the tables kept up to date with them
+    holds, for every sequence of the step, the table that the step would otherwise have carried."""
+    import numpy as np
+
+    import plain_pack
+    from litinfer_b200.engine import StepItem
+    from litinfer_b200.engine.batch import pack_step
+
+    rnd = random.Random(100 + seed)
+    m = manager(num_pages=120, max_requests=6, window=window, two_groups=True)
+    plain = plain_pack.PlainResidentTables(m)
+    G, vocab = len(m.groups), 300
+    copy = [np.full((m.max_requests + 1, 64), m.trash_page, dtype=np.int32) for _ in range(G)]
+    live, next_id = {}, 0
+    for step in range(60):
+        while len(live) < 6 and rnd.random() < 0.5:
+            rid = next_id % 9                                      # ids come back
+            next_id += 1
+            if rid in live:
+                continue
+            live[rid] = m.admit(rid)
+            if rnd.random() < 0.3:                                 # extended before its first step
+                n = rnd.choice([5, 16, 33])
+                m.extend(live[rid], n)
+                m.commit(live[rid], n)
+        if not live:
+            continue
+        chosen = rnd.sample(sorted(live), rnd.randint(1, len(live)))
+        items = []
+        for rid in chosen:
+            rc = live[rid]
+            q = rnd.choice([1, 1, 1, 2, 17, 40])
+            if rc.length + q > 64 * 16 - 1:
+                continue
+            m.extend(rc, rc.length + q)
+            items.append(StepItem(rc, [rnd.randrange(vocab) for _ in range(q)], ()))
+        if not items:
+            continue
+        want = plain.updates(items)
+        full, lf = plain_pack.pack_step(items, m, vocab, max_blocks=64)
+        buf, lay = pack_step(items, m, vocab, max_blocks=64, resident=True)
+        S = lay["S"]
+        for name in ("token_ids", "positions", "q_start", "ctx_lens", "state_slots", "slot_mapping0"):
+            o, n = lay["fields"][name]
+            o2, _ = lf["fields"][name]
+            assert np.array_equal(buf[o:o + n], full[o2:o2 + n]), name
+        for g in range(G):
+            o, n = lay["fields"][f"table_updates{g}"]
+            count = int(buf[o])
+            got = [tuple(int(x) for x in buf[o + 1 + 3 * i:o + 4 + 3 * i]) for i in range(count)]
+            assert got == want[g], f"step {step} group {g}"
+            for slot, block, page in got:
+                copy[g][slot, block] = page
+            o2, _ = lf["fields"][f"block_table{g}"]
+            tables = full[o2:o2 + S * 64].reshape(S, 64)
+            for s_, it in enumerate(items):
+                nb = -(-(it.cache.length + len(it.tokens)) // 16)
+                assert np.array_equal(copy[g][it.cache.slot, :nb], tables[s_, :nb]), f"step {step} group {g} sequence {s_}"
+        # nothing is sent twice
+        again, la = pack_step(items, m, vocab, max_blocks=64, resident=True)
+        assert all(int(again[la["fields"][f"table_updates{g}"][0]]) == 0 for g in range(G))
+        for it in items:
+            m.commit(it.cache, it.cache.length + len(it.tokens))
+        for rid in list(live):
+            if rnd.random() < 0.15:
+                m.release(live.pop(rid))
+                plain.forget(rid)
+        m.check()
+
+
 def test_the_packer_refuses_what_the_plain_one_refuses():
     from litinfer_b200.engine import StepItem
     from litinfer_b200.engine.batch import pack_step

@@ -391,14 +391,16 @@ def test_captured_paths_of_the_runner_with_the_capture_emulated(name, model_dirs
             meta = torch.zeros(buf.shape[0], dtype=torch.int32)
             self._upload(buf, meta)
             lay = dict(layout, max_ctx_len=self.max_context, max_q_len=max_q_len, singles=singles)
-            ctx = context_from(meta, lay, self.manager.page_size)
+            ctx = context_from(meta, lay, self.manager.page_size, self.manager)
             runner = self
 
             class Graph:
                 def replay(self):
                     ctx.scratch.clear()
+                    ctx.sync_tables()
                     g.logits.copy_(runner.model.forward(ctx, runner.manager.entries))
 
+            ctx.sync_tables()
             g = step_module._DecodeGraph(Graph(), meta, self.model.forward(ctx, self.manager.entries).clone(), lay)
             if B is not None:
                 self._graphs[B] = g

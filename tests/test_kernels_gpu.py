@@ -83,6 +83,30 @@ def test_rmsnorm_family(dtype, H):
     assert torch.equal(x1, x2)
 
 
+def test_table_gather_applies_changes_and_copies_rows():
+    """The resident block tables: changes of the step's slots applied (others' and out-of-range ones ignored, the last
+    row never written), each sequence's row copied out, the sink page beyond the row's width; twice gives the same."""
+    g = torch.Generator().manual_seed(12)
+    rows, cols, trash = 9, 37, 500
+    resident = torch.randint(0, 400, (rows, cols), generator=g, dtype=torch.int32)
+    resident[rows - 1] = trash
+    slots = torch.tensor([3, 0, 8, 3, 5, 77], dtype=torch.int32)
+    triples = [(3, 0, 11), (3, 36, 12), (0, 5, 13), (4, 2, 14), (5, 40, 15), (8, 1, 16), (5, 7, 17), (3, 9, trash)]
+    cap = 12
+    updates = torch.zeros(1 + 3 * cap, dtype=torch.int32)
+    updates[0] = len(triples)
+    updates[1:1 + 3 * len(triples)] = torch.tensor(triples, dtype=torch.int32).reshape(-1)
+    for mb in (5, 37, 50):
+        want_res, want_out = resident.clone(), torch.empty(len(slots), mb, dtype=torch.int32)
+        R.table_gather(want_res, updates, slots, want_out, trash)
+        got_res, got_out = resident.clone().to(dev()), torch.empty(len(slots), mb, dtype=torch.int32, device=dev())
+        for _ in range(2):
+            K().table_gather(got_res, updates.to(dev()), slots.to(dev()), got_out, trash)
+            assert torch.equal(got_out.cpu(), want_out) and torch.equal(got_res.cpu(), want_res)
+        assert int(want_res[4, 2]) == int(resident[4, 2]), "a slot that is not in the step is left alone"
+        assert torch.equal(want_out[2], torch.full((mb,), trash, dtype=torch.int32)), "the padding sequences' row is all sink page"
+
+
 def test_gather_rows_scale_and_logit_cap():
     k = K()
     g = torch.Generator().manual_seed(9)
