@@ -19,6 +19,7 @@ of a few hundred tokens is bound by the host's launches, not by the device.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List, Optional, Sequence
 
 import numpy as np
@@ -37,6 +38,7 @@ class _DecodeGraph:
         self.meta_buf = meta_buf
         self.logits = logits
         self.layout = layout
+        self.ctx = None                  # the captured step's context: tensors that the replays write (the step's block tables)
 
 
 class ModelRunner:
@@ -75,7 +77,7 @@ class ModelRunner:
         # warm-up, and a captured step would freeze which slots it updates)
         self._may_split = not any(isinstance(r, FixedState) for r in model.cache_requirements())
         # the block tables stay on the device (manager.groups[g].tables); a step uploads what changed
-        self.resident = bool(manager.groups) and all(g.tables is not None for g in manager.groups)
+        self.resident = bool(manager.groups) and all(g.tables is not None for g in manager.groups) and os.environ.get("LITINFER_B200_RESIDENT_TABLES", "1") != "0"
         self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and self._may_split
         from .. import kernels as K
 
@@ -334,6 +336,7 @@ class ModelRunner:
             ctx.sync_tables()                          # the step's block tables from the resident ones: part of every replay
             logits = self.model.forward(ctx, self.manager.entries)
         g = _DecodeGraph(graph, meta, logits, lay)
+        g.ctx = ctx                                    # the step's block tables, which every replay fills again, live as long as the graph
         if B is not None:
             self._graphs[B] = g
         return g
