@@ -237,8 +237,11 @@ def time_decode(model, batch, context, steps, warmup, graphs=True):
     for k in range(total):
         for rc in reqs:
             manager.extend(rc, rc.length + 1)
-        buf, layout = pack_step([StepItem(rc, [toks[k + 1][b]], (0,)) for b, rc in enumerate(reqs)], manager, vocab,
-                                pad_seqs=runner._bucket(batch), max_blocks=max_blocks)
+        items = [StepItem(rc, [toks[k + 1][b]], (0,)) for b, rc in enumerate(reqs)]
+        bucket = runner._bucket(batch)
+        # as the runner packs a captured decode step: the block tables are resident, a step carries their changes
+        buf, layout = pack_step(items, manager, vocab, pad_seqs=bucket, max_blocks=max_blocks, resident=runner.resident,
+                                update_cap=runner._update_room(items, bucket, bucket))
         assert layout["fields"] == graph.layout["fields"]
         staged.append(torch.from_numpy(buf))
         for rc in reqs:
