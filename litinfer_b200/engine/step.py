@@ -97,6 +97,8 @@ class ModelRunner:
             widest = max((w for b in model.blocks for w in widths(b)), default=0)
             if widest:
                 self.work_budget = torch.cuda.get_device_properties(self.device).multi_processor_count // widest
+        if os.environ.get("LITINFER_B200_WORK_BUDGET"):
+            self.work_budget = int(os.environ["LITINFER_B200_WORK_BUDGET"])       # for measurements: 0 shares nothing out
         self._graphs: Dict[int, _DecodeGraph] = {}
         # shapes of steps with portions of prompts: how often each came, and the captured ones; a shape is captured
         # when it comes for the (step_graph_after + 1)-th time, since a capture costs three plain runs
