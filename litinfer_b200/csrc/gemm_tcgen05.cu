@@ -73,8 +73,9 @@ struct __align__(1024) SharedStorage {
 // Called by whole warps (the loads from tensor memory are warp-wide); `valid`: this thread's row is a row of the product.
 // Two threads share a row (the warps w and w + 4 reach the same lanes of tensor memory): `part` 0 takes the first half of
 // the head's rotation pairs (or of a value head's columns), `part` 1 the second.
+// `cs`: this row's 64 (cos, sin) pairs, staged in shared memory by the caller (rope_stage_table).
 __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_tile, int row, bool valid, int head, const float* __restrict__ bias,
-                                                bf16* __restrict__ out, int N, const RopeEpilogue& re, int part) {
+                                                bf16* __restrict__ out, int N, const RopeEpilogue& re, int part, const float2* cs) {
     const int slot = valid ? re.slot_mapping[row] : -1;
     const int page = slot / re.page_size, off = slot - page * re.page_size;
     const bool cache_ok = valid && re.write && slot >= 0 && page < re.num_pages;       // validated on the host; never write outside the cache
@@ -84,7 +85,6 @@ __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_ti
         bf16* dst = !store ? nullptr
                     : (is_q ? out + (size_t)row * N + (size_t)head * 128
                             : re.kcache + (((size_t)page * re.nkv + (head - re.nh)) * re.page_size + off) * 128);
-        const float2* cs = reinterpret_cast<const float2*>(re.cos_sin) + (size_t)(valid ? row : 0) * 64;
         {
             const int c = part;
             float lo[32], hi[32];
@@ -105,7 +105,7 @@ __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_ti
                     // q and k are rounded to bfloat16 by the projection before they are rotated, as in the unfused path
                     a = __bfloat162float(__float2bfloat16_rn(a));
                     b = __bfloat162float(__float2bfloat16_rn(b));
-                    const float2 t2 = __ldg(cs + j);
+                    const float2 t2 = cs[j];
                     y[e] = a * t2.x - b * t2.y;
                     y[2 + e] = b * t2.x + a * t2.y;
                 }
@@ -137,6 +137,19 @@ __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_ti
                 }
             }
         }
+    }
+}
+
+// The step's table of cosines and sines for the tile's 128 rows, from global memory (64 pairs = 512 bytes a row) into shared
+// memory with coalesced loads, a row every 65 pairs so that the lanes of a warp, a row each, read different banks.  Read
+// row by row straight from global memory, every load of a warp touched 32 lines: the load/store unit then bounded the
+// epilogue (26 us for q|k|v of 2,048 tokens at hidden 1536, of which the tensor pipe works 6).
+constexpr int kRopeRowPairs = 65;
+__device__ __forceinline__ void rope_stage_table(float2* cs_sm, const float* __restrict__ cos_sin, int m0, int M, int tid, int nthreads) {
+    const float2* src = reinterpret_cast<const float2*>(cos_sin);
+    for (int i = tid; i < 128 * 64; i += nthreads) {
+        const int r = i >> 6, j = i & 63;
+        cs_sm[r * kRopeRowPairs + j] = (m0 + r < M) ? __ldg(src + (size_t)(m0 + r) * 64 + j) : make_float2(1.0f, 0.0f);
     }
 }
 
@@ -292,12 +305,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // the q|k|v product of a prefill step: a tile of 128 or 256 columns is one or two heads of 128; never split along k
                 static_assert(!kRope || (BM == 128 && BN % 128 == 0 && sizeof(Tout) == 2 && !kSwiglu), "the rope epilogue is for tiles of whole heads of 128 in bfloat16");
                 const int row = m0 + quarter * 32 + lane;
+                // the accumulator is complete, so every product has read its operands and every copy has landed: the
+                // stages of the a operand are free to hold the table
+                static_assert(sizeof(sm.a) >= 128 * kRopeRowPairs * sizeof(float2), "the rotary table of a tile fits the a stages");
+                float2* cs_sm = reinterpret_cast<float2*>(&sm.a[0][0]);
+                rope_stage_table(cs_sm, rope.cos_sin, m0, M, threadIdx.x - 64, 256);          // the eight epilogue warps
+                asm volatile("bar.sync 2, 256;" ::: "memory");
 #pragma unroll 1
                 for (int hl = 0; hl < BN / 128; ++hl) {
                     const int head = n0 / 128 + hl;
                     if (head * 128 < N)                            // the same for the whole CTA
                         rope_store_head(tmem_acc + ((unsigned)(quarter * 32) << 16), hl * 128, row, row < M, head, bias, reinterpret_cast<bf16*>(out), N, rope,
-                                        (warp - 2) >> 2);
+                                        (warp - 2) >> 2, cs_sm + (quarter * 32 + lane) * kRopeRowPairs);
                 }
             } else if (ksplit == 1) {
 #pragma unroll 1
