@@ -73,7 +73,7 @@ struct __align__(1024) SharedStorage {
 // Called by whole warps (the loads from tensor memory are warp-wide); `valid`: this thread's row is a row of the product.
 // Two threads share a row (the warps w and w + 4 reach the same lanes of tensor memory): `part` 0 takes the first half of
 // the head's rotation pairs (or of a value head's columns), `part` 1 the second.
-// `cs`: this row's 64 (cos, sin) pairs, staged in shared memory by the caller (rope_stage_table).
+// `cs`: this row's 64 (cos, sin) pairs, in the step's table or staged in shared memory by the caller (rope_stage_table).
 __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_tile, int row, bool valid, int head, const float* __restrict__ bias,
                                                 bf16* __restrict__ out, int N, const RopeEpilogue& re, int part, const float2* cs) {
     const int slot = valid ? re.slot_mapping[row] : -1;
@@ -145,11 +145,20 @@ __device__ __forceinline__ void rope_store_head(unsigned tmem_row, int col_in_ti
 // row by row straight from global memory, every load of a warp touched 32 lines: the load/store unit then bounded the
 // epilogue (26 us for q|k|v of 2,048 tokens at hidden 1536, of which the tensor pipe works 6).
 constexpr int kRopeRowPairs = 65;
-__device__ __forceinline__ void rope_stage_table(float2* cs_sm, const float* __restrict__ cos_sin, int m0, int M, int tid, int nthreads) {
-    const float2* src = reinterpret_cast<const float2*>(cos_sin);
-    for (int i = tid; i < 128 * 64; i += nthreads) {
-        const int r = i >> 6, j = i & 63;
-        cs_sm[r * kRopeRowPairs + j] = (m0 + r < M) ? __ldg(src + (size_t)(m0 + r) * 64 + j) : make_float2(1.0f, 0.0f);
+__device__ __forceinline__ void rope_stage_table(float2* cs_sm, const float* __restrict__ cos_sin, int m0, int M, int tid) {
+    // 256 threads, 16 loads of two pairs each, all in flight at once (a loop of single loads cost their latency 32 times)
+    const float4* src = reinterpret_cast<const float4*>(cos_sin);
+    float4 t4[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const int i = tid + k * 256, r = i >> 5;                 // pair 2 (i & 31) of row r
+        t4[k] = (m0 + r < M) ? __ldg(src + (size_t)(m0 + r) * 32 + (i & 31)) : make_float4(1.0f, 0.0f, 1.0f, 0.0f);
+    }
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+        const int i = tid + k * 256, r = i >> 5, j = 2 * (i & 31);
+        cs_sm[r * kRopeRowPairs + j] = make_float2(t4[k].x, t4[k].y);
+        cs_sm[r * kRopeRowPairs + j + 1] = make_float2(t4[k].z, t4[k].w);
     }
 }
 
@@ -308,15 +317,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 // the accumulator is complete, so every product has read its operands and every copy has landed: the
                 // stages of the a operand are free to hold the table
                 static_assert(sizeof(sm.a) >= 128 * kRopeRowPairs * sizeof(float2), "the rotary table of a tile fits the a stages");
+                // (a tile of one head gains nothing from the detour: 17.6 -> 18.6 us for 544 tokens; it reads the table in place)
+                constexpr bool kStaged = BN >= 256;
                 float2* cs_sm = reinterpret_cast<float2*>(&sm.a[0][0]);
-                rope_stage_table(cs_sm, rope.cos_sin, m0, M, threadIdx.x - 64, 256);          // the eight epilogue warps
-                asm volatile("bar.sync 2, 256;" ::: "memory");
+                if constexpr (kStaged) {
+                    rope_stage_table(cs_sm, rope.cos_sin, m0, M, threadIdx.x - 64);      // the eight epilogue warps
+                    asm volatile("bar.sync 2, 256;" ::: "memory");
+                }
+                const float2* cs_row = kStaged ? cs_sm + (quarter * 32 + lane) * kRopeRowPairs
+                                               : reinterpret_cast<const float2*>(rope.cos_sin) + (size_t)(row < M ? row : 0) * 64;
 #pragma unroll 1
                 for (int hl = 0; hl < BN / 128; ++hl) {
                     const int head = n0 / 128 + hl;
                     if (head * 128 < N)                            // the same for the whole CTA
                         rope_store_head(tmem_acc + ((unsigned)(quarter * 32) << 16), hl * 128, row, row < M, head, bias, reinterpret_cast<bf16*>(out), N, rope,
-                                        (warp - 2) >> 2, cs_sm + (quarter * 32 + lane) * kRopeRowPairs);
+                                        (warp - 2) >> 2, cs_row);
                 }
             } else if (ksplit == 1) {
 #pragma unroll 1

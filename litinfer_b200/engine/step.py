@@ -60,7 +60,7 @@ class ModelRunner:
     # long portions) are launched plainly: with them waiting resident for the kernel before, steps of thousands of tokens
     # of a 7B-shaped model stopped making progress in four runs of ten (no bounded wait ran out; never with a 1.5B
     # shape, never with either those or the small kernels launched plainly: 0 of 11, 0 of 11, 0 of 10 runs).  It costs
-    # such steps a microsecond per launch (2,048 tokens: 5.86 -> 6.16 ms).  The padded sizes of captured steps are
+    # such steps a microsecond per launch (2,048 tokens: about 0.3 ms of 6).  The padded sizes of captured steps are
     # multiples of 64, so a graph is always replayed for steps of the class it was captured for.
     OVERLAP_TOKENS = 256
     BIG_STEP_NO_OVERLAP = ("gemm", "attention")
