@@ -4,6 +4,7 @@ float32 on the float32 residual stream; one rounding of y to the run dtype."""
 
 from __future__ import annotations
 
+import os
 from typing import Dict, List
 
 import torch
@@ -12,13 +13,16 @@ from .. import kernels as K
 from ..weights.loader import ParamSpec
 from .base import NORMS, Deferred, Norm
 
+DEFER_UP_TO = int(os.environ.get("LITINFER_B200_DEFER_UP_TO", "32"))
+
 
 def defers(tokens: int) -> bool:
-    """Whether the norm between two products rides on them for a step of this many tokens.  Measured: up to 16 tokens it
-    saves two kernels a layer; with more, the weight-streaming kernels' registers are too short for the extra work.  (Tried
-    in the tensor-memory GEMM of prefill too: there the residual stream read and written by the epilogue's threads, a row
-    each, cost more than the norm kernels it replaced.)"""
-    return 0 < tokens <= 16
+    """Whether the norm between two products rides on them for a step of this many tokens.  Measured (1.5B shape, a
+    context of 2,048): it saves two kernels a layer and 4-9 % of the step up to 32 tokens (24 tokens 2.12 -> 2.03 ms, 32
+    tokens 2.12 -> 2.04 ms); at 64 tokens the epilogues of the weight-streaming products carry too much (2.54 -> 2.78
+    ms).  (Tried in the tensor-memory GEMM of prefill too: there the residual stream read and written by the epilogue's
+    threads, a row each, cost more than the norm kernels it replaced.)"""
+    return 0 < tokens <= DEFER_UP_TO
 
 
 @NORMS.register("rmsnorm")
