@@ -146,6 +146,10 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // Tensor memory is taken only once the kernel before this one has finished: a CTA that waits for that kernel must not
+    // hold what a CTA of it may still ask for (gemm_tcgen05.cu has the story).
+    pdl_launch_dependents();
+    pdl_wait();
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -155,8 +159,6 @@ prefill_attention_tc_kernel(const bf16* __restrict__ qkv, long long row_elems, c
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     // S of tile j at tmem_s + 128 (j & 1), and P of tile j over its first 64 columns (two bfloat16 a column)
     const unsigned tmem_s = sm.tmem_base, tmem_pv = sm.tmem_base + 256, tmem_q = sm.tmem_base + 384;
-    pdl_launch_dependents();
-    pdl_wait();
     // Debugging aid (LITINFER_B200_ATTN_TRACE): the first CTA leaves the clock at which each role passed each point of each
     // of its first 16 key tiles in the mapped status area, [role][point][tile] from word 16 on.
     const bool tracing = trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;

@@ -63,6 +63,7 @@ struct __align__(1024) SharedStorage {
     unsigned long long full[Tile<BM, BN, kPair>::kStages];
     unsigned long long empty[Tile<BM, BN, kPair>::kStages];
     unsigned long long accum;
+    unsigned long long peer_alloc;       // a pair: the second CTA has its tensor memory
     unsigned tmem_base;
     int failed;
     int is_last;
@@ -165,7 +166,7 @@ __device__ __forceinline__ void rope_stage_table(float2* cs_sm, const float* __r
 // threads of a CTA: producer warp, issuing warp, four epilogue warps; eight with the rotary epilogue, the longest one for
 // its product (a k of `hidden` only, and per row a table read, a rotation and scattered stores): two threads share a row
 template <bool kRope>
-constexpr int threads_of() { return kRope ? 320 : kThreads; }
+__host__ __device__ constexpr int threads_of() { return kRope ? 320 : kThreads; }
 
 template <int BM, int BN, typename Tout, bool kSwiglu, bool kPair = false, bool kRope = false>
 __global__ void __launch_bounds__(threads_of<kRope>(), 1)
@@ -195,10 +196,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             mbar_init(&sm.empty[s], 1);
         }
         mbar_init(&sm.accum, 1);
+        mbar_init(&sm.peer_alloc, 1);
         sm.failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1) {
+    __syncthreads();
+    if constexpr (kPair) cluster_sync_all();          // the other CTA's barriers are set up before anything arrives on them
+    // Tensor memory is taken only once the kernel before this one has finished (warp 1, below): a CTA that waits for
+    // that kernel must not hold what a CTA of it may still ask for.  With the accumulators taken first and every launch a
+    // dependent one, steps of thousands of tokens of a 7B-shaped model stopped in tcgen05.alloc about two runs in five.
+    // The warps that read the accumulator meet warp 1 at a named barrier once it has the address.
+    constexpr int kAllocMeet = 32 + (threads_of<kRope>() - 64);
+    auto take_tensor_memory = [&]() {
+        pdl_wait();
         if constexpr (kPair) {
             asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kCols)
                          : "memory");
@@ -208,12 +218,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                          : "memory");
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
         }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    if constexpr (kPair) cluster_sync_all();          // the other CTA's barriers are set up before anything arrives on them
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const unsigned tmem_acc = sm.tmem_base;
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    };
+    auto meet_tensor_memory = [&]() {
+        asm volatile("bar.sync 3, %0;" ::"n"(kAllocMeet) : "memory");
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        return sm.tmem_base;
+    };
     // programmatic dependent launch: everything up to here overlapped the end of the kernel before this one; what reads
     // its results (the producer) or writes over memory it may still read (the epilogue) waits for it
     pdl_launch_dependents();
@@ -266,9 +277,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
     } else if (warp == 1) {
+        take_tensor_memory();
+        const unsigned tmem_acc = meet_tensor_memory();
+        if constexpr (kPair) {
+            if (lane == 0 && pair_rank == 1) mbar_arrive_remote(&sm.peer_alloc, 0);
+        }
         if (lane == 0 && pair_rank == 0) {                 // in a pair the first CTA issues the products of both
             const unsigned idesc = umma_idesc(kPair ? 256 : 128, BN);
             bool ok = true;
+            if constexpr (kPair) ok = mbar_wait(&sm.peer_alloc, 0);       // the products write the second CTA's tensor memory too
             for (int kb = 0; kb < nkb && ok; ++kb) {
                 const int s = kb % kStages;
                 const unsigned phase = (kb / kStages) & 1;
@@ -301,6 +318,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // epilogue: warp w may read the tensor-memory lanes 32 (w % 4) .. 32 (w % 4) + 31
         const int quarter = warp & 3;
+        const unsigned tmem_acc = meet_tensor_memory();
         const bool ok = mbar_wait(&sm.accum, 0);
         if (!ok) {
             if (lane == 0) atomicExch(error_flag, 3);
@@ -392,8 +410,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if constexpr (kPair) cluster_sync_all();          // neither CTA frees tensor memory or leaves while the other may still use it
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if constexpr (kPair) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kCols) : "memory");
-        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(kCols) : "memory");
+        if constexpr (kPair) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(sm.tmem_base), "r"(kCols) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(sm.tmem_base), "r"(kCols) : "memory");
     }
 }
 

@@ -65,6 +65,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // Tensor memory is taken only once the kernel before this one has finished: a CTA that waits for that kernel must not
+    // hold what a CTA of it may still ask for (gemm_tcgen05.cu has the story).  Nothing here could start before that anyway.
+    pdl_launch_dependents();
+    pdl_wait();
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
@@ -74,11 +78,9 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     cluster_sync_all();                               // the other CTA's barriers are set up before anything arrives on them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const unsigned tmem_acc = sm.tmem_base;
-    pdl_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
-            pdl_wait();
             bool ok = true;
             int it = 0;                               // k-blocks loaded so far, over all tiles
             for (int t = pair; t < total && ok; t += npairs) {
@@ -122,7 +124,6 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const 
     } else {
         // epilogue: warp w may read the tensor-memory lanes 32 (w % 4) .. 32 (w % 4) + 31
         const int quarter = warp & 3;
-        pdl_wait();
         bool ok = true;
         int ti = 0;
         for (int t = pair; t < total && ok; t += npairs, ++ti) {

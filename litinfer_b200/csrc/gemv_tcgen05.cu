@@ -110,6 +110,10 @@ gemv_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         mbar_init(&sm.accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // (The other tcgen05 kernels take their tensor memory only after the kernel before them has finished, see
+    // gemm_tcgen05.cu.  This one takes its 32 or 64 of the 512 columns at once: with the allocation behind the wait a decode
+    // step of batch 8 went from 1.311 to 1.337 ms, and a CTA that holds so little while it waits leaves room for any other
+    // kernel's CTAs; in all runs that stopped, this kernel launched plainly made no difference.)
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");

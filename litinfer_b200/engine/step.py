@@ -55,15 +55,15 @@ class ModelRunner:
     # tokens.
     STEP_GRAPH_TOKENS = 2048
     # Every kernel of a step may begin while the one before it still runs (programmatic dependent launch,
-    # kernels.allow_overlap): a step of few tokens is a chain of short kernels (1.44 -> 1.31 ms at batch 8).  In steps of
-    # more than this many tokens the kernels that take a multiprocessor each (the tcgen05 GEMMs and the attention for
-    # long portions) are launched plainly: with them waiting resident for the kernel before, steps of thousands of tokens
-    # of a 7B-shaped model stopped making progress in four runs of ten (no bounded wait ran out; never with a 1.5B
-    # shape, never with either those or the small kernels launched plainly: 0 of 11, 0 of 11, 0 of 10 runs).  It costs
-    # such steps a microsecond per launch (2,048 tokens: about 0.3 ms of 6).  The padded sizes of captured steps are
-    # multiples of 64, so a graph is always replayed for steps of the class it was captured for.
+    # kernels.allow_overlap): a step of few tokens is a chain of short kernels (1.44 -> 1.31 ms at batch 8).  Which kinds
+    # of kernel a step of more than OVERLAP_TOKENS tokens launches plainly instead is a setting (none now).  It was the
+    # tcgen05 GEMMs and the attention for long portions while steps of thousands of tokens of a 7B-shaped model stopped
+    # making progress about two runs in five; the cause was a CTA that held its tensor memory while it waited for the
+    # kernel before (csrc/gemm_tcgen05.cu), and those kernels now take it after the wait (0 of 22 runs since, every launch
+    # a dependent one).  The padded sizes of captured steps are multiples of 64, so a graph is always replayed for steps
+    # of the class it was captured for.
     OVERLAP_TOKENS = 256
-    BIG_STEP_NO_OVERLAP = ("gemm", "attention")
+    BIG_STEP_NO_OVERLAP = ()
     STEP_GRAPH_LIMIT = 48               # captured shapes kept; further shapes are launched plainly
     STEP_GRAPH_LOGITS = 1 << 26         # logits (floats) a captured shape may hold
 
