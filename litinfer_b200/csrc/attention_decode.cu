@@ -4,7 +4,9 @@
 // Two kernels share one inner step.  Few sequences: grid (split, kv head,
 // sequence); a CTA of 8 warps covers 256 keys at fixed absolute positions
 // [256 s, 256 s + 256), each warp 32 of them (all its loads are in flight at
-// once: one round trip to memory).  Many sequences (sequences x kv heads >= 120):
+// once: one round trip to memory); with more sequences longer ranges, each warp
+// walking every 8th block of its CTA's range, so that about one CTA per
+// multiprocessor is left.  Many sequences (a CTA per pair fills the GPU):
 // one CTA per (sequence, kv head) whose warps walk every 8th block of 32 keys;
 // nothing to merge across CTAs.  Either way a warp works for all query heads of
 // one key/value head at once (they share every K and V byte read; heads are the
@@ -25,7 +27,8 @@
 // CTA that finishes last (a counter per sequence and kv head), both in fixed
 // order: which keys a warp or a CTA takes depends on absolute key positions
 // only, so a sequence's result does not depend on the batch it is in, as long
-// as the same kernel runs (the choice depends on the number of sequences).
+// as the contexts are cut the same way (how long a CTA's range is depends on the
+// number of sequences and on the longest context of the step).
 // Window: keys below p - window + 1 are masked, blocks wholly below it skipped.
 //
 // Requires head_dim in {16, 32, ..., 128, 256}, at most 16 query heads per
@@ -35,7 +38,6 @@
 
 namespace {
 
-constexpr int kWholeFrom = 60;         // (sequences x kv heads) from which a CTA takes a whole context (measured at a context of 2,048: 32 x 2 is faster whole, 24 x 2 split)
 
 struct Workspace {
     float* buf = nullptr;
@@ -48,19 +50,19 @@ Workspace g_ws[16];
 using namespace attn;
 using namespace attn_decode;
 
-template <int DH, int KB>
+template <int DH, int KB, bool kCut>
 __global__ void __launch_bounds__(kWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ ctx_lens,
                         const int* __restrict__ old_lens, const int* __restrict__ q_start, float* __restrict__ part,
                         unsigned* __restrict__ counters, bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages,
-                        float scale, int window, int nsplit) {
+                        float scale, int window, int nsplit, int want) {
     extern __shared__ float sm[];
     __shared__ int is_last;
     pdl_launch_dependents();
-    decode_attention_unit<DH, KB>((int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, qkv, kcache, vcache, block_table, max_blocks,
+    decode_attention_unit<DH, KB, kCut>((int)blockIdx.x, (int)blockIdx.y, (int)blockIdx.z, (int)threadIdx.x, qkv, kcache, vcache, block_table, max_blocks,
                                   ctx_lens, old_lens, q_start, part, counters, out, nh, nkv, page_size, num_pages, scale, window, nsplit, sm,
-                                  &is_last, [] { __syncthreads(); }, [] { pdl_wait(); });
+                                  &is_last, [] { __syncthreads(); }, [] { pdl_wait(); }, want);
 }
 
 // Many sequences at once: with one CTA per (sequence, kv head) the GPU is already full, and splitting the
@@ -173,11 +175,24 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     const int G = nh / nkv;
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     // `expected`: how many of the S sequences are this kernel's (a step may hold portions beside them, and a captured step
-    // is padded with empty sequences): that count, not S, says whether one CTA per sequence and kv head fills the GPU
-    static const int whole_from = getenv("LITINFER_B200_DECODE_WHOLE_FROM") ? atoi(getenv("LITINFER_B200_DECODE_WHOLE_FROM")) : kWholeFrom;
-    if ((long long)(expected > 0 && expected < S ? expected : S) * nkv >= whole_from) {
+    // is padded with empty sequences): that count, not S, says how the contexts are best cut.  A CTA takes kSplit keys of
+    // one (sequence, kv head): a block of 32 per warp and round.  With few pairs one round, so that every load of a CTA is
+    // in flight at once and the splits of all pairs fill the GPU (batch 8: 16 pairs x 9 splits of 256 keys).  With more
+    // pairs that many CTAs run in several waves, each paying its start, its merge and its exit, so the units get longer:
+    // every sequence's context is cut into as many units as leave about one CTA per multiprocessor, of as many rounds as
+    // that takes; with one unit per pair, the kernel without a merge takes it.
+    constexpr int KBS = DH <= 128 ? 32 : 16;
+    const long long pairs = (long long)(expected > 0 && expected < S ? expected : S) * nkv;
+    static const int sms = [] {
+        int dev = 0, n = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        return n;
+    }();
+    const int blocks = ceil_div(max_ctx_len > 0 ? max_ctx_len : 1, KBS * kWarps);          // units of one round that the longest context can have
+    const int want = (int)(pairs >= sms ? 1 : sms / pairs);                              // units per pair that fill the GPU once
+    if (want == 1 && blocks > 1) {
         // one CTA per (sequence, kv head) fills the GPU: no split of the context
-        constexpr int W = 8, KB = DH <= 128 ? 32 : 16;
+        constexpr int W = 8, KB = KBS;
         const size_t wsmem = (2 * W * 16 + (size_t)W * G * DH) * sizeof(float);
         if (wsmem <= 200 * 1024) {
             static bool raised = false;
@@ -191,9 +206,12 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
             return li_check_launch("attention (decode, whole context)");
         }
     }
-    constexpr int KBS = DH <= 128 ? 32 : 16;
-    constexpr int kSplit = KBS * kWarps;
-    const int nsplit = ceil_div(max_ctx_len > 0 ? max_ctx_len : 1, kSplit);
+    // Units of one round for every context up to the longest, if those are at most about two waves of CTAs (the kernel
+    // of one round is the leaner one: batch 8 at a context of 2,048, 1.311 against 1.324 ms a step).  Else every
+    // sequence's own context is cut into at most `want` units (attention_decode_unit.cuh): a launch whose longest context
+    // is only a bound (a captured step) still gives every sequence units of equal length.
+    const bool cut = want < blocks && pairs * blocks > 2LL * sms;
+    const int nsplit = cut ? want : blocks;
     float* part = nullptr;
     unsigned* counters = nullptr;
     if (int rc = ensure_workspace((size_t)S * nh * nsplit * (DH + 2), &part, &counters)) return rc;
@@ -203,16 +221,22 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
     const size_t smem = smem_floats * sizeof(float);
     static bool attr_set = false;
     if (!attr_set && smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<DH, KBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<DH, KBS, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(decode_attention_kernel<DH, KBS, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return li_fail("attention (decode): cannot raise shared memory: %s", cudaGetErrorString(e));
         attr_set = true;
     }
     LI_REQUIRE(smem <= 200 * 1024, "attention (decode): shared memory %zu too large", smem);
     LI_REQUIRE(S <= 65535 && nkv <= 65535, "attention (decode): batch %d or kv heads %d too large for one launch", S, nkv);
     dim3 grid(nsplit, nkv, S);
-    li_launch_pdl(decode_attention_kernel<DH, KBS>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache, (const bf16*)vcache,
-                                                                      block_table, max_blocks, ctx_lens, old_lens, q_start, part, counters, (bf16*)out,
-                                                                      nh, nkv, page_size, num_pages, scale, window, nsplit);
+    if (cut)
+        li_launch_pdl(decode_attention_kernel<DH, KBS, true>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache,
+                      (const bf16*)vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, part, counters, (bf16*)out, nh, nkv, page_size,
+                      num_pages, scale, window, nsplit, want);
+    else
+        li_launch_pdl(decode_attention_kernel<DH, KBS, false>, dim3(grid), dim3(kWarps * 32), smem, stream, (const bf16*)qkv, (const bf16*)kcache,
+                      (const bf16*)vcache, block_table, max_blocks, ctx_lens, old_lens, q_start, part, counters, (bf16*)out, nh, nkv, page_size,
+                      num_pages, scale, window, nsplit, 0);
     return li_check_launch("attention (decode)");
 }
 

@@ -66,15 +66,20 @@ __device__ __forceinline__ void block_load32(KFrag32<DH>& kf, VFrag32<DH>& vf, c
     load_v32<DH>(vf, vcache + ((size_t)vpage * nkv + kvh) * DH * page_size + vk % page_size, page_size, g);
 }
 
-template <int DH, int KB, typename Sync, typename Wait>
+template <int DH, int KB, bool kCut = false, typename Sync, typename Wait>
 __device__ __forceinline__ void decode_attention_unit(int split, int kvh, int s, int tid, const bf16* __restrict__ qkv, const bf16* __restrict__ kcache,
                                                       const bf16* __restrict__ vcache, const int* __restrict__ block_table, int max_blocks,
                                                       const int* __restrict__ ctx_lens, const int* __restrict__ old_lens,
                                                       const int* __restrict__ q_start, float* __restrict__ part, unsigned* __restrict__ counters,
                                                       bf16* __restrict__ out, int nh, int nkv, int page_size, int num_pages, float scale, int window,
-                                                      int nsplit, float* sm, int* is_last, Sync sync, Wait wait_for_queries) {
-    constexpr int kSplit = KB * kWarps;                // one block of KB keys per warp: one round trip to memory
-        const int ctx = ctx_lens[s];                       // the step's metadata is in place before its first kernel starts
+                                                      int nsplit, float* sm, int* is_last, Sync sync, Wait wait_for_queries, int want = 0) {
+    const int ctx = ctx_lens[s];                           // the step's metadata is in place before its first kernel starts
+    // A unit covers KB keys per warp and round.  One round (one round trip to memory) where the units of all sequences
+    // fit the GPU at once (want = 0).  Else the sequence's own context is cut into `want` units of as many rounds as that
+    // takes, each warp walking every eighth block of its unit: the cut depends on the sequence and on `want` alone.
+    // (kCut says at compile time whether that can be: the kernel of one round stays as lean as it was)
+    const int rounds = (kCut && want > 0) ? max(1, ((ctx + KB * kWarps - 1) / (KB * kWarps) + want - 1) / want) : 1;
+    const int kSplit = KB * kWarps * rounds;
     const int p = ctx - 1;
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int k_begin = split * kSplit;
@@ -122,6 +127,14 @@ __device__ __forceinline__ void decode_attention_unit(int split, int kvh, int s,
             compute32<DH>(st, qa, kf_early, vf_early, my_key0, lo2, hi2, scale, t);
         } else {
             block_step<DH, KB>(st, qa, kcache, vcache, bt, my_key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t);
+        }
+    }
+    if constexpr (kCut) {
+#pragma unroll 1
+        for (int rd = 1; rd < rounds; ++rd) {
+            const int key0 = k_begin + (rd * kWarps + warp) * KB;
+            if (key0 < k_end && key0 + KB > lo)            // warp-uniform
+                block_step<DH, KB>(st, qa, kcache, vcache, bt, key0, kvh, nkv, page_size, num_pages, lo2, hi2, scale, g, t);
         }
     }
     const float m0 = st.m[0], m1 = st.m[1];

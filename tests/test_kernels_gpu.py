@@ -465,6 +465,22 @@ def test_linear_row_scale_refused():
 # attention
 # --------------------------------------------------------------------------
 
+def decode_cut(pairs, max_ctx, ctx, dh):
+    """How the decode attention kernel cuts the context ``ctx`` of a sequence in a step with ``pairs`` pairs of
+    (sequence, kv head) whose longest context is ``max_ctx`` (restating the choice in csrc/attention_decode.cu): the keys
+    a CTA takes, or None for a whole context per CTA.  A sequence's result is the same bit for bit only between steps
+    that cut it alike."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    unit = (32 if dh <= 128 else 16) * 8
+    most = -(-max(max_ctx, 1) // unit)
+    want = 1 if pairs >= sms else sms // pairs
+    if want == 1 and most > 1:
+        return None
+    if want >= most or pairs * most <= 2 * sms:
+        return unit
+    return unit * max(1, -(-(-(-ctx // unit)) // want))
+
+
 def make_attention_case(q_lens, ctx_lens, nh, nkv, dh, page, dtype, seed=0, extra_pages=5):
     """A ragged batch with scrambled page tables.  Returns the kernel arguments and the
     logical (per sequence) keys and values so that tests can plant special ones."""
@@ -565,18 +581,18 @@ def test_attention_decode_kernel_alone(heads, page):
     for window in (None, 100, 300):
         out, ref = run_attention_case(c, window, implementation="decode")
         close(out, ref, torch.bfloat16, f"decode kernel heads={heads} page={page} window={window}")
-    # alone or in the batch: the same bits, as long as the batch is one that the same kernel takes (from 60 pairs of
-    # sequence and kv head on, a CTA walks a whole context and the sums come in another order)
-    few = min(len(ctx_lens), 59 // nkv)
-    c = make_attention_case([1] * few, ctx_lens[:few], nh, nkv, dh, page, torch.bfloat16, seed=31)
+    # alone or in the batch: the same bits, as long as the contexts are cut the same way
     out_all, _ = run_attention_case(c, None, implementation="decode")
-    c1 = make_attention_case([1] * few, ctx_lens[:few], nh, nkv, dh, page, torch.bfloat16, seed=31)
+    c1 = make_attention_case([1] * len(ctx_lens), ctx_lens, nh, nkv, dh, page, torch.bfloat16, seed=31)
     for key in ("q_lens", "ctx_lens"):
         c1[key] = c1[key][4:5]
     c1.update(S=1, T=1, bt=c1["bt"][4:5], qkv=c1["qkv"][4:5], keys=c1["keys"][4:5], vals=c1["vals"][4:5], q_start=[0, 1], seq_of=[0],
               pos=[ctx_lens[4] - 1])
     out_one, _ = run_attention_case(c1, None, implementation="decode")
-    assert torch.equal(out_one[0], out_all[4])
+    if decode_cut(len(ctx_lens) * nkv, max(ctx_lens), ctx_lens[4], dh) == decode_cut(nkv, ctx_lens[4], ctx_lens[4], dh):
+        assert torch.equal(out_one[0], out_all[4])
+    else:
+        close(out_one[0:1], out_all[4:5], torch.bfloat16, f"a sequence alone and in a batch that is cut differently, heads={heads}")
 
 
 @pytest.mark.parametrize("heads", [(4, 2, 16), (12, 2, 128)])
@@ -629,9 +645,8 @@ def test_attention_single_tokens_beside_portions(heads, many):
     alone["keys"], alone["vals"], alone["bt"] = c["keys"], c["vals"], c["bt"]
     out_alone, _ = run_attention_case(alone, None, implementation="decode")
     out_mixed, _ = run_attention_case(c, None, singles=n1)
-    # (which of the two decode kernels runs depends on how many single tokens there are: from 60 pairs of sequence and
-    # kv head on, a CTA walks a whole context, and the sums come in another order)
-    if (len(q_lens) * nkv >= 60) == (n1 * nkv >= 60):
+    # (how the contexts are cut depends on how many single tokens there are: the sums then come in another order)
+    if decode_cut(len(q_lens) * nkv, max(ctx_lens), ctx_lens[0], dh) == decode_cut(n1 * nkv, max(ctx_lens), ctx_lens[0], dh):
         assert torch.equal(out_alone[0], out_mixed[tok0])
     else:
         close(out_mixed[tok0:tok0 + 1], out_alone[0:1], torch.bfloat16, "a single token alone and beside portions, through different kernels")
