@@ -206,11 +206,13 @@ int launch(const void* qkv, void* out, const void* kcache, const void* vcache, c
             return li_check_launch("attention (decode, whole context)");
         }
     }
-    // Units of one round for every context up to the longest, if those are at most about two waves of CTAs (the kernel
-    // of one round is the leaner one: batch 8 at a context of 2,048, 1.311 against 1.324 ms a step).  Else every
-    // sequence's own context is cut into at most `want` units (attention_decode_unit.cuh): a launch whose longest context
-    // is only a bound (a captured step) still gives every sequence units of equal length.
-    const bool cut = want < blocks && pairs * blocks > 2LL * sms;
+    // Units of one round if every context up to the longest has no more of them than `want`.  Else every sequence's own
+    // context is cut into at most `want` units (attention_decode_unit.cuh): a launch whose longest context is only a bound
+    // (a captured step) still gives every sequence units of equal length.  Measured (1.5B shape, contexts of 2,048-2,185,
+    // ms a step; units per sequence 2 / 3 / 4 / 6 / 9 = one round): 8 sequences 1.66 / 1.48 / 1.49 / 1.40 / 1.31;
+    // 16 sequences 1.75 / 1.58 / 1.59 / 1.63 / 1.64; 32 sequences 1.87 / 2.02 / 2.02 / 2.02 / - (a whole context per CTA
+    // 2.04): multiprocessors // pairs, that is 9, 4 and 2, is the best or next to it each time.
+    const bool cut = want < blocks;
     const int nsplit = cut ? want : blocks;
     float* part = nullptr;
     unsigned* counters = nullptr;

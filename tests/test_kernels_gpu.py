@@ -476,7 +476,7 @@ def decode_cut(pairs, max_ctx, ctx, dh):
     want = 1 if pairs >= sms else sms // pairs
     if want == 1 and most > 1:
         return None
-    if want >= most or pairs * most <= 2 * sms:
+    if want >= most:
         return unit
     return unit * max(1, -(-(-(-ctx // unit)) // want))
 
