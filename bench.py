@@ -685,6 +685,9 @@ def main() -> int:
         return 0
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
+    if args.only in ("decode", "kernels-decode") and args.context + 4096 > cfg["max_position_embeddings"]:
+        # a longer context than the shape's own limit, on request: the measurement's model allows it
+        cfg["max_position_embeddings"] = args.context + 4096
     peaks = load_peaks()
     spec = config_from_dict(cfg).to_model_spec()
     model = DecoderModel.from_random(spec, 0, "bfloat16", "cuda:0")

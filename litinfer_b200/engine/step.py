@@ -43,7 +43,10 @@ class _DecodeGraph:
 
 class ModelRunner:
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
-    GRAPH_CONTEXT_CAP = 8192            # a captured step covers contexts up to this; longer ones are launched plainly
+    # A captured step covers contexts up to this (its block tables are that wide); longer ones are launched plainly.  The
+    # attention launches do not grow with it: decode attention cuts every sequence's own context into a number of units
+    # that the batch decides, and portions walk a work list.
+    GRAPH_CONTEXT_CAP = 32768
     # A step of few tokens that holds portions of prompts runs through the captured decode step too, every token an item
     # of its own (batch.split_into_tokens): launched plainly, a step costs the host about 250 launches (3 ms), more than
     # the device needs for it.  Every token then reads its context by itself, so the contexts together are bounded.
@@ -83,8 +86,8 @@ class ModelRunner:
 
         if K.profile.enabled:
             self.use_graphs = False                        # LLAISYS_PROFILE times kernel launches: a replayed graph has none to time
-        # a captured attention launch has to cover the longest context it may meet (its grid and workspace
-        # are sized for it), so that length is capped; steps with a longer context run without a graph
+        # a captured step has to cover the longest context it may meet (the width of its block tables), so that
+        # length is capped; steps with a longer context run without a graph
         self.max_context = min(int(max_context or model.spec.max_position_embeddings), self.GRAPH_CONTEXT_CAP)
         # entries of the attention work list that keep every multiprocessor busy at once (engine.batch.attention_units)
         self.work_budget = 0
