@@ -336,6 +336,46 @@ def test_captured_decode_step_of_many_requests(tmp_path):
     assert captured.runner.graph_replays == 4
 
 
+def test_captured_decode_steps_at_a_context_beyond_8192(tmp_path):
+    """A model that allows 32,768 positions: the captured decode step is made for contexts up to that bound, and decode
+    attention cuts every sequence's own context (9,000 keys here, beside a request of 40) into units of several rounds.
+    The same logits as with every kernel launched plainly for the contexts as they are; for the short request, whose
+    plain logits cost little, the plain model's."""
+    from litinfer_b200.engine.replay import Replayer
+    from litinfer_b200.models import DecoderModel
+    from litinfer_b200.weights import write_model_folder
+
+    cfg = dict(MID["head128"], max_position_embeddings=32768)
+    folder = tmp_path / "model"
+    write_model_folder(folder, cfg, seed=79, store_dtype="float32")
+    vocab = cfg["vocab_size"]
+    long_one, short_one = random_tokens(9006, vocab, 950), random_tokens(46, vocab, 951)
+    model = DecoderModel.from_dir(folder, "bfloat16", torch.device("cuda:0"))
+    need = round64(len(long_one)) + round64(len(short_one))
+    plainly = Replayer(model, need, max_live=2, use_graphs=False)
+    captured = Replayer(model, need, max_live=2, use_graphs=True)
+    assert captured.runner.max_context > 9006
+    step = 0
+    for start in range(0, 9000, 1500):
+        rec = dict(step=step, entries=[dict(id="long", tokens=long_one[start:start + 1500], want=[])])
+        plainly.step(rec)
+        captured.step(rec)
+        step += 1
+    rec = dict(step=step, entries=[dict(id="short", tokens=short_one[:40], want=[])])
+    plainly.step(rec)
+    captured.step(rec)
+    before = captured.runner.graph_replays
+    ref_short = plain_logits(folder, short_one, "bfloat16")
+    for j in range(6):
+        step += 1
+        rec = dict(step=step, entries=[dict(id="long", tokens=[long_one[9000 + j]], want=[0]), dict(id="short", tokens=[short_one[40 + j]], want=[0])])
+        x = plainly.step(rec).clone().cpu()
+        y = captured.step(rec).clone().cpu()
+        check_logits(y, x, "bfloat16", f"9,000 keys and 40 keys, decoded token {j}: captured against launched plainly")
+        check_logits(y[1:2], ref_short[40 + j:41 + j], "bfloat16", f"the request of 40 keys beside one of 9,000, decoded token {j}")
+    assert captured.runner.graph_replays == before + 6 and plainly.runner.graph_replays == 0
+
+
 def test_a_request_across_the_kernel_choices_of_a_step(tmp_path):
     """In bfloat16 which kernels run depends on the step's size: up to 16 tokens the norms ride on the products, from 17 on
     they are kernels of their own; from 120 (sequence, key head) pairs on decode attention walks a whole context per CTA
