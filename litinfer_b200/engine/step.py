@@ -28,7 +28,7 @@ import torch
 from ..cache import native
 from ..cache.manager import CacheManager
 from ..models.decoder import DecoderModel
-from ..parts.base import FixedState
+from ..parts.base import FixedState, Mixer
 from .batch import StepContext, StepItem, context_from, pack_step, split_into_tokens
 
 
@@ -77,11 +77,22 @@ class ModelRunner:
         self.device = model.device
         # a mixer with state of its own takes a request's tokens in order and advances its state every time the step
         # runs: its portions are never split, and nothing of such a model is captured (capturing runs the step for
-        # warm-up, and a captured step would freeze which slots it updates)
+        # warm-up, and a captured step would freeze which slots it updates) ...
         self._may_split = not any(isinstance(r, FixedState) for r in model.cache_requirements())
+
+        def mixers_with_state(part):
+            if isinstance(part, Mixer) and isinstance(part.cache_requirement(), FixedState):
+                yield part
+            for child in part.parts():
+                yield from mixers_with_state(child)
+
+        # ... except decode steps, if every such mixer says that it takes them from the device's copy of the step
+        # (parts.base.Mixer.decodes_from_device); the warm-up runs of a capture then go to the spare slot
+        stateful = [m for b in model.blocks for m in mixers_with_state(b)]
+        self._state_in_graphs = bool(stateful) and all(getattr(m, "decodes_from_device", False) for m in stateful)
         # the block tables stay on the device (manager.groups[g].tables); a step uploads what changed
         self.resident = bool(manager.groups) and all(g.tables is not None for g in manager.groups) and os.environ.get("LITINFER_B200_RESIDENT_TABLES", "1") != "0"
-        self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and self._may_split
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and (self._may_split or self._state_in_graphs)
         from .. import kernels as K
 
         if K.profile.enabled:
@@ -325,12 +336,20 @@ class ModelRunner:
         stream = torch.cuda.Stream(self.device)
         stream.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(stream):
+            if not self._may_split:
+                # state of fixed size: the warm-up runs must advance nobody's, so every sequence names the spare slot
+                # meanwhile (its row of the resident block tables names the sink page: keys and values of the step's
+                # tokens go there too, and are written to their places by the first replay)
+                o, n = lay["fields"]["state_slots"]
+                meta[o:o + n].fill_(self.manager.max_requests)
             for _ in range(2):                    # warm-up outside capture (first-call set-up, allocator)
                 ctx.scratch.clear()
                 ctx.sync_tables()
                 self.model.forward(ctx, self.manager.entries)
         torch.cuda.current_stream(self.device).wait_stream(stream)
         torch.cuda.synchronize(self.device)
+        if not self._may_split:
+            self._upload(buf, meta)
         graph = torch.cuda.CUDAGraph()
         if B is None and self._step_pool is None:
             self._step_pool = torch.cuda.graph_pool_handle()

@@ -170,6 +170,13 @@ class Mixer(Part):
     # how many CTAs one entry of the step's attention work list becomes in this mixer's kernel (0: it does not read the
     # list); the step function sizes the list so that the entries of all such mixers fill the GPU (engine.batch.attention_units)
     ctas_per_work_unit = 0
+    # A mixer with state of its own (FixedState) advances that state every time it runs, so the step function never
+    # splits its portions and captures nothing of its model, unless the mixer sets this: it promises that in a step of
+    # single tokens (ctx.max_q_len == 1: token s is sequence s) it reads the step only through the context's device
+    # tensors (ctx.state_slots and the like) and launches the same kernels whatever they hold.  Such steps are then
+    # captured and replayed like those of a model without state; the runs that warm a capture up point every sequence at
+    # the spare slot (the one that padded sequences of a captured step name), so they advance nobody's state.
+    decodes_from_device = False
 
     def cache_requirement(self):
         """PagedKV, FixedState or None."""

@@ -432,6 +432,12 @@ def test_toy_mixer_with_state_through_the_engine_on_cpu_references(model_dirs, c
     run_toy_mixer_through_engine(model_dirs, "cpu")
 
 
+def test_toy_mixer_that_decodes_from_the_device_on_cpu_references(model_dirs, cpu_kernels):
+    from test_engine_gpu import run_toy_mixer_in_captured_steps
+
+    run_toy_mixer_in_captured_steps(model_dirs, "cpu")
+
+
 def test_toy_positions_and_block_arrangements_on_cpu_references(model_dirs, cpu_kernels):
     from test_engine_gpu import run_toy_positions_and_blocks
 

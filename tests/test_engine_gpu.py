@@ -292,6 +292,86 @@ def run_toy_mixer_through_engine(model_dirs, device):
         MIXERS.unregister("toy_ema")
 
 
+def _ema_mixer_on_device_class():
+    """The same toy mixer, which takes steps of single tokens from the device's copy of the step: its decode steps may
+    be captured (parts.base.Mixer.decodes_from_device)."""
+    host = _ema_mixer_class()
+
+    class EmaMixerOnDevice(host):
+        decodes_from_device = True
+
+        def forward(self, h, ctx, cache):
+            if ctx.max_q_len != 1:
+                return super().forward(h, ctx, cache)
+            u = self.proj(h).float()                       # token s is sequence s
+            slots = ctx.state_slots.long()
+            st = cache.state.index_select(0, slots) * self.decay + (1 - self.decay) * u
+            cache.state.index_copy_(0, slots, st)          # padded sequences of a captured step all name the spare slot
+            return st.to(self.dtype)
+
+    return EmaMixerOnDevice
+
+
+def test_toy_mixer_with_state_in_captured_decode_steps(model_dirs):
+    run_toy_mixer_in_captured_steps(model_dirs, "cuda:0")
+
+
+def run_toy_mixer_in_captured_steps(model_dirs, device):
+    """A mixer with state of its own that says it decodes from the device's copy of the step: its model's decode steps are
+    captured and replayed (portions of prompts still run plainly and unsplit), the runs that warm a capture up advance
+    nobody's state, and every request gives the tokens of the mixer that walks the step on the host: alone, and three
+    together in a pool so small that one is preempted and recomputed."""
+    from dataclasses import replace
+
+    from litinfer_b200 import DecoderModel, Engine, EngineConfig
+    from litinfer_b200.config import PartSpec, load_config
+    from litinfer_b200.parts import MIXERS
+
+    MIXERS.register("toy_ema", _ema_mixer_class())
+    MIXERS.register("toy_ema_on_device", _ema_mixer_on_device_class())
+    try:
+        base = load_config(model_dirs["A"]).to_model_spec()
+        models = {}
+        for kind in ("toy_ema", "toy_ema_on_device"):
+            blocks = list(base.blocks)
+            blocks[1] = blocks[1].with_part("mixer", PartSpec(kind, {"hidden_size": base.hidden_size, "decay": 0.75}), "ema.")
+            models[kind] = DecoderModel.from_random(replace(base, blocks=tuple(blocks)), 5, "float32", device)
+        prompts = [random_tokens(n, base.vocab_size, 900 + n) for n in (30, 28, 27)]
+        on_gpu = torch.device(device).type == "cuda"
+
+        def alone(model, p):
+            eng = Engine(model, EngineConfig(num_pages=16, max_num_seqs=1))          # use_graphs is on by default
+            rid = eng.add_request(p, 24)
+            eng.run_to_completion()
+            return eng, eng.get_output(rid)
+
+        want = []
+        for p in prompts:
+            eng, out = alone(models["toy_ema"], p)
+            assert not eng.runner.use_graphs and eng.runner.graph_replays == 0
+            want.append(out)
+            eng, out = alone(models["toy_ema_on_device"], p)
+            assert eng.runner.use_graphs == on_gpu and not eng.runner._may_split
+            assert (eng.runner.graph_replays >= 20) == on_gpu and not eng.runner._step_graphs
+            assert out == want[-1], "decoding from the device's copy of the step gives other tokens than the walk on the host"
+        assert len({tuple(a) for a in want}) == 3
+
+        for run_ahead in (False, True):
+            eng = Engine(models["toy_ema_on_device"],
+                         EngineConfig(num_pages=7, max_num_seqs=4, max_tokens_per_step=64, prefill_chunk=16, run_ahead=run_ahead))
+            ids = [eng.add_request(p, 24) for p in prompts]
+            eng.run_to_completion()
+            assert eng.scheduler.num_preemptions > 0, "the pool was meant to be too small for all three"
+            eng.manager.check()
+            assert eng.manager.num_free_pages(0) == 7 and eng.manager.num_free_slots() == 4
+            assert (eng.runner.graph_replays > 0) == on_gpu
+            for rid, a in zip(ids, want):
+                assert eng.get_output(rid) == a, f"request {rid} (run_ahead {run_ahead}): tokens differ from the request run alone"
+    finally:
+        MIXERS.unregister("toy_ema")
+        MIXERS.unregister("toy_ema_on_device")
+
+
 # --------------------------------------------------------------------------
 # toy position encodings that are no rotation, and a block of another shape
 # --------------------------------------------------------------------------
