@@ -309,13 +309,17 @@ int g_forced_ksplit = 0;          // > 0: this many splits of k whatever the sha
 // Splits of k: a function of N, K and the token tile (16, 32 or 64 columns), never of the number of tokens itself.
 int choose_ksplit(int N, int K, int bt) {
     const int tiles = ceil_div(N, BR), nkb = ceil_div(K, BK);
-    if (g_forced_ksplit > 0) return g_forced_ksplit < nkb ? g_forced_ksplit : nkb;
-    int ks = kTargetCtas / tiles;
-    if (ks < 1) ks = 1;
-    if (bt == 64 && ks > 8) ks = 8;                                   // 32 KB of partial sums a split: the merge by one CTA grows with them (measured)
-    const int by_work = nkb / 2 > 0 ? nkb / 2 : 1;                    // at least two k-blocks a CTA
-    if (ks > by_work) ks = by_work;
-    while (ks > 1 && (size_t)ks * tiles * 64 * BR > kWorkspaceFloats) --ks;      // sized for 64 tokens whatever M is
+    int ks;
+    if (g_forced_ksplit > 0) {
+        ks = g_forced_ksplit < nkb ? g_forced_ksplit : nkb;
+    } else {
+        ks = kTargetCtas / tiles;
+        if (ks < 1) ks = 1;
+        if (bt == 64 && ks > 8) ks = 8;                               // 32 KB of partial sums a split: the merge by one CTA grows with them (measured)
+        const int by_work = nkb / 2 > 0 ? nkb / 2 : 1;                // at least two k-blocks a CTA
+        if (ks > by_work) ks = by_work;
+    }
+    while (ks > 1 && (size_t)ks * tiles * 64 * BR > kWorkspaceFloats) --ks;      // the partial sums fit the workspace: sized for 64 tokens whatever M is
     return ks;
 }
 
@@ -332,6 +336,8 @@ int launch(const void* a, const void* w, const float* bias, void* out, int M, in
     const int tiles = ceil_div(N, BR);
     const int ksplit = choose_ksplit(N, K, BT);
     LI_REQUIRE(tiles <= kMaxTiles, "linear (tcgen05 gemv): N=%d has too many tiles", N);
+    LI_REQUIRE(ksplit == 1 || (size_t)ksplit * tiles * BT * BR <= kWorkspaceFloats, "linear (tcgen05 gemv): %d splits of %d tiles do not fit the workspace",
+               ksplit, tiles);
     CUtensorMap map_w, map_x;
     if (int rc = make_map(&map_w, w, N, K, BR)) return rc;
     if (int rc = make_map(&map_x, a, M, K, BT)) return rc;

@@ -251,6 +251,27 @@ def test_linear_swiglu_epilogue(which, shape, forced_tile, forced_ksplit):
     close(out, ref2, torch.bfloat16, f"{which} swiglu {shape} against the reference of the fused call")
 
 
+@pytest.mark.parametrize("forced", [2, 3, 16])
+def test_gemv_tcgen05_forced_splits_fit_the_workspace(forced):
+    """The measurement switch for splits of k: more splits than the fixed workspace of partial sums holds are cut down
+    to what fits (140 tiles of gate|up: three), and the result is the product whatever was asked for."""
+    lib = K().library()
+    M, N, Kd = 8, 17920, 1536
+    a = rnd(M, Kd, dtype=torch.bfloat16, seed=46)
+    w = rnd(N, Kd, dtype=torch.bfloat16, seed=47, scale=0.05)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+    ref = torch.empty_like(out)
+    lib.li_gemv_tcgen05_force_ksplit(forced)
+    try:
+        K().linear_with("gemv_tcgen05", a, w, None, out)
+        torch.cuda.synchronize()
+    finally:
+        lib.li_gemv_tcgen05_force_ksplit(0)
+    R.linear(a, w, None, ref)
+    close(out, ref, torch.bfloat16, f"swapped tcgen05 kernel with {forced} splits asked for")
+    assert lib.li_tcgen05_status() == 0
+
+
 @pytest.mark.parametrize("shape", LINEAR_SHAPES)
 def test_linear_simt_rows_do_not_depend_on_batch(shape):
     """float32: a row's result is the same bits whether it runs alone or among others."""
