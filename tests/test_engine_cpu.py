@@ -438,6 +438,13 @@ def test_toy_mixer_that_decodes_from_the_device_on_cpu_references(model_dirs, cp
     run_toy_mixer_in_captured_steps(model_dirs, "cpu")
 
 
+@pytest.mark.parametrize("name", ["A", "B0"])
+def test_toy_architecture_from_a_folder_on_cpu_references(name, model_dirs, cpu_kernels, tmp_path):
+    from test_engine_gpu import run_toy_architecture
+
+    run_toy_architecture(name, "float32", model_dirs, tmp_path, "cpu")
+
+
 def test_toy_positions_and_block_arrangements_on_cpu_references(model_dirs, cpu_kernels):
     from test_engine_gpu import run_toy_positions_and_blocks
 

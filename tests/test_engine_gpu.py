@@ -10,7 +10,7 @@ import torch
 import kernel_refs as R
 import plain_qwen2 as P
 from conftest import TINY
-from helpers import bf16_round, check_logits, random_tokens
+from helpers import bf16_round, check_logits, plain_logits, random_tokens
 
 pytestmark = pytest.mark.gpu
 
@@ -370,6 +370,136 @@ def run_toy_mixer_in_captured_steps(model_dirs, device):
     finally:
         MIXERS.unregister("toy_ema")
         MIXERS.unregister("toy_ema_on_device")
+
+
+# --------------------------------------------------------------------------
+# a whole architecture from outside the package: its own config.json keys and tensor names
+# --------------------------------------------------------------------------
+
+def _toy_architecture_class():
+    """A configuration class that shares nothing with Qwen2's: other config.json keys, other tensor-name stems.  What it
+    describes is the same arithmetic, so that the plain model can say what the logits must be."""
+    import math
+    from dataclasses import dataclass
+
+    from litinfer_b200.config import BlockSpec, ModelSpec, PartSpec
+    from litinfer_b200.config.spec import default_schedule
+
+    @dataclass(frozen=True)
+    class ToyConfig:
+        width: int
+        depth: int
+        heads: int
+        groups: int
+        head_size: int
+        inner: int
+        vocab: int
+        limit: int
+        eps: float
+        theta: float
+        own_head: bool
+        torch_dtype: str = "float32"
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(int(d["toy_width"]), int(d["toy_depth"]), int(d["toy_heads"]), int(d["toy_groups"]), int(d["toy_head_size"]),
+                       int(d["toy_inner"]), int(d["toy_vocab"]), int(d["toy_limit"]), float(d["toy_eps"]), float(d["toy_theta"]),
+                       bool(d["toy_own_head"]), str(d.get("torch_dtype", "float32")))
+
+        def to_model_spec(self):
+            norm = PartSpec("rmsnorm", {"size": self.width, "eps": self.eps})
+            rope = PartSpec("rope", {"theta": self.theta, "rotary_dim": self.head_size, "pairing": "half"})
+            ffn = PartSpec("swiglu", {"hidden_size": self.width, "intermediate_size": self.inner})
+            mixer = PartSpec("attention", {"hidden_size": self.width, "num_heads": self.heads, "num_kv_heads": self.groups,
+                                           "head_dim": self.head_size, "qkv_bias": True, "out_bias": False,
+                                           "scale": 1.0 / math.sqrt(self.head_size), "window": None, "position": rope})
+            stems = {"mixer": "mix.", "feed_forward": "ffn.", "mixer_norm": "ln1.", "feed_forward_norm": "ln2."}
+            blocks = tuple(BlockSpec.of("prenorm", f"net.h.{i}.", stems, mixer=mixer, feed_forward=ffn, mixer_norm=norm, feed_forward_norm=norm)
+                           for i in range(self.depth))
+            return ModelSpec(architecture="ToyForCausalLM", vocab_size=self.vocab, hidden_size=self.width, blocks=blocks,
+                             schedule=default_schedule(self.depth), final_norm=norm, tie_word_embeddings=not self.own_head,
+                             max_position_embeddings=self.limit, embedding_name="net.tok.weight", final_norm_prefix="net.ln_out.",
+                             lm_head_name="net.head.weight")
+
+    return ToyConfig
+
+
+_TOY_STEMS = ((".self_attn.", ".mix."), (".mlp.", ".ffn."), (".input_layernorm.", ".ln1."), (".post_attention_layernorm.", ".ln2."),
+              ("model.layers.", "net.h."), ("model.embed_tokens.", "net.tok."), ("model.norm.", "net.ln_out."), ("lm_head.", "net.head."))
+
+
+def test_toy_architecture_from_a_folder(model_dirs, tmp_path):
+    run_toy_architecture("A", "float32", model_dirs, tmp_path, "cuda:0")
+
+
+def run_toy_architecture(name, dtype, model_dirs, tmp_path, device):
+    """An architecture registered from outside the package, with config.json keys and tensor names of its own, goes the
+    whole way without a change to the package: configuration by name, weights by name (with the loader's one error for
+    what does not match), the generic model, the step function in portions and single tokens, random weights into a
+    folder, the front end.  Its folder holds a tiny Qwen2 model's tensors under the toy names, so the plain model of that
+    Qwen2 folder says what the logits are."""
+    import json
+
+    from litinfer_b200 import CausalLM, DecoderModel
+    from litinfer_b200.config import ConfigError, load_config, register_architecture, registry, supported_architectures
+    from litinfer_b200.engine.replay import Replayer
+    from litinfer_b200.weights import WeightError, iter_tensors, write_file, write_model_folder
+
+    cfg = TINY[name]
+    toy_cfg = dict(architectures=["ToyForCausalLM"], torch_dtype="float32", toy_width=cfg["hidden_size"], toy_depth=cfg["num_hidden_layers"],
+                   toy_heads=cfg["num_attention_heads"], toy_groups=cfg["num_key_value_heads"], toy_head_size=cfg["head_dim"],
+                   toy_inner=cfg["intermediate_size"], toy_vocab=cfg["vocab_size"], toy_limit=cfg["max_position_embeddings"],
+                   toy_eps=cfg["rms_norm_eps"], toy_theta=cfg["rope_theta"], toy_own_head=not cfg["tie_word_embeddings"])
+    folder = tmp_path / "toy"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(toy_cfg))
+    tensors = {}
+    for tensor_name, t in iter_tensors(model_dirs[name] / "model.safetensors"):
+        for old, new in _TOY_STEMS:
+            tensor_name = tensor_name.replace(old, new)
+        tensors[tensor_name] = t
+    write_file(folder / "model.safetensors", tensors)
+
+    with pytest.raises(ConfigError, match="ToyForCausalLM"):
+        load_config(folder)
+    register_architecture("ToyForCausalLM", _toy_architecture_class())
+    try:
+        assert "ToyForCausalLM" in supported_architectures()
+        spec = load_config(folder).to_model_spec()
+        assert spec.architecture == "ToyForCausalLM" and len(spec.blocks) == cfg["num_hidden_layers"]
+        model = DecoderModel.from_dir(folder, dtype, torch.device(device))
+        toks = random_tokens(40, cfg["vocab_size"], 77)
+        ref = plain_logits(model_dirs[name], toks, dtype)
+        rp = Replayer(model, 64, max_live=2, use_graphs=True)
+        got = [rp.step(dict(step=0, entries=[dict(id="a", tokens=toks[:23], want=[0, 22])])).clone().cpu()]
+        got.append(rp.step(dict(step=1, entries=[dict(id="a", tokens=toks[23:30], want=[6])])).clone().cpu())
+        for i in range(30, 40):
+            got.append(rp.step(dict(step=i, entries=[dict(id="a", tokens=[toks[i]], want=[0])])).clone().cpu())
+        check_logits(torch.cat(got), ref[[0, 22, 29] + list(range(30, 40))], dtype, f"toy architecture over the tensors of {name}, {dtype}")
+
+        # a tensor under a name the toy architecture does not declare, and one it declares missing: one error for both
+        broken = tmp_path / "broken"
+        broken.mkdir()
+        (broken / "config.json").write_text(json.dumps(toy_cfg))
+        wrong = dict(tensors)
+        wrong["model.norm.weight"] = wrong.pop("net.ln_out.weight")
+        write_file(broken / "model.safetensors", wrong)
+        with pytest.raises(WeightError) as err:
+            DecoderModel.from_dir(broken, dtype, torch.device(device))
+        assert "net.ln_out.weight" in str(err.value) and "model.norm.weight" in str(err.value)
+
+        # random weights into a folder (the same for the same seed, others for another) and the front end's generate
+        outs, drawn = [], []
+        for seed, sub in ((11, "r1"), (11, "r2"), (12, "r3")):
+            d = write_model_folder(tmp_path / sub, dict(toy_cfg), seed=seed, store_dtype="float32")
+            drawn.append(dict(iter_tensors(d / "model.safetensors")))
+            front = CausalLM(None, device=device, model=DecoderModel.from_dir(d, dtype, torch.device(device)), num_pages=8)
+            outs.append(front.generate(toks[:12], max_new_tokens=8))
+        assert sorted(drawn[0]) == sorted(tensors) and all(drawn[0][k].shape == tensors[k].shape for k in tensors)
+        assert all(torch.equal(drawn[0][k], drawn[1][k]) for k in tensors) and not torch.equal(drawn[0]["net.tok.weight"], drawn[2]["net.tok.weight"])
+        assert len(outs[0]) == 8 and outs[0] == outs[1]
+    finally:
+        registry._ARCHITECTURES.pop("ToyForCausalLM", None)
 
 
 # --------------------------------------------------------------------------
