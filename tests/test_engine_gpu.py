@@ -348,10 +348,10 @@ def run_toy_mixer_in_captured_steps(model_dirs, device):
         want = []
         for p in prompts:
             eng, out = alone(models["toy_ema"], p)
-            assert not eng.runner.use_graphs and eng.runner.graph_replays == 0
+            assert not eng.runner.use_graphs and eng.runner.graph_replays == 0 and not eng.runner._state_in_graphs
             want.append(out)
             eng, out = alone(models["toy_ema_on_device"], p)
-            assert eng.runner.use_graphs == on_gpu and not eng.runner._may_split
+            assert eng.runner.use_graphs == on_gpu and not eng.runner._may_split and eng.runner._state_in_graphs
             assert (eng.runner.graph_replays >= 20) == on_gpu and not eng.runner._step_graphs
             assert out == want[-1], "decoding from the device's copy of the step gives other tokens than the walk on the host"
         assert len({tuple(a) for a in want}) == 3
